@@ -1,0 +1,280 @@
+/*
+ * ribn_b200 — C ABI of the B200-native (sm_100a) batched decode / chunked-prefill
+ * executor that stands behind ribn's `GenerationExecutor` trait.
+ *
+ * Every entry point takes plain pointers and sizes; the library owns all
+ * device memory; the caller owns its host arrays only for the duration of a
+ * call.  All calls on one executor must come from one thread (the reference's
+ * trait is `Send`, not `Sync`: crates/runtime/src/executor.rs:171).
+ *
+ * There is no CPU fallback: every compute entry point runs CUDA kernels and
+ * returns RIBN_B200_ERROR when no usable device exists.
+ */
+#ifndef RIBN_B200_H
+#define RIBN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define RIBN_B200_API __attribute__((visibility("default")))
+#else
+#define RIBN_B200_API
+#endif
+
+/* GGML tensor value types accepted by the loader (crates/gguf/src/lib.rs
+ * tensor_layout; numbering is GGUF's). */
+enum {
+    RIBN_B200_F32 = 0,
+    RIBN_B200_F16 = 1,
+    RIBN_B200_Q8_0 = 8,
+    RIBN_B200_Q4_K = 12,
+    RIBN_B200_Q6_K = 14
+};
+
+/* Return codes.  ERROR corresponds to `Err(ExecutionError)` (faults the
+ * engine); REJECTED / DEFERRED to `Admission::Rejected` / `Admission::Deferred`
+ * (crates/runtime/src/executor.rs:109-129); PENDING to `poll -> Ok(None)`. */
+enum {
+    RIBN_B200_OK = 0,
+    RIBN_B200_PENDING = 1,
+    RIBN_B200_REJECTED = 2,
+    RIBN_B200_DEFERRED = 3,
+    RIBN_B200_ERROR = -1
+};
+
+/* StepKind (crates/runtime/src/executor.rs:35-39). */
+enum { RIBN_B200_PREFILL = 0, RIBN_B200_DECODE = 1 };
+
+/* Quantisation schemes of the seeded synthetic checkpoints. */
+enum {
+    RIBN_B200_SCHEME_Q8_0 = 0,   /* every matrix Q8_0 */
+    RIBN_B200_SCHEME_Q4_K_M = 1  /* Q4_K; Q6_K for attn_v, ffn_down, output */
+};
+
+typedef struct ribn_b200_executor ribn_b200_executor;
+
+/* Dense Qwen3-architecture geometry plus the executor's scheduling limits
+ * (GenerationLimits, crates/runtime/src/executor.rs:43-51; QwenLoadOptions,
+ * crates/qwen/src/loading.rs:29-81). */
+typedef struct {
+    int32_t layers;
+    int32_t hidden;
+    int32_t q_heads;
+    int32_t kv_heads;
+    int32_t head_dim;
+    int32_t ffn;
+    int32_t vocab;
+    float rope_base;
+    float rms_eps;
+    int32_t context_tokens;   /* longest prompt + output of one sequence */
+    int32_t max_sequences;    /* concurrent sequences */
+    int32_t max_batch_tokens; /* tokens per submitted batch */
+    int32_t kv_pages;         /* 16-token pages in the shared KV arena; 0 = enough for
+                                 max_sequences full contexts */
+    int32_t device;           /* CUDA ordinal */
+    int32_t flags;            /* RIBN_B200_FLAG_* */
+} ribn_b200_config;
+
+enum {
+    RIBN_B200_FLAG_KEEP_LOGITS = 1,   /* keep F32 logits of sampling rows for copy_logits */
+    RIBN_B200_FLAG_REFERENCE_KERNELS = 2, /* run the plain one-warp-per-row CUDA kernels
+                                             (slow; used to cross-check the fast path) */
+    RIBN_B200_FLAG_NO_GRAPH = 4       /* launch kernels directly instead of replaying graphs */
+};
+
+/* GenerationLimits (crates/runtime/src/executor.rs:43-51). */
+typedef struct {
+    uint32_t context_tokens;
+    uint32_t max_sequences;
+    uint32_t max_batch_tokens;
+    uint32_t max_decode_tokens; /* always 1 */
+    uint32_t kv_page_tokens;    /* 16: crates/qwen/src/gguf.rs:16 */
+    uint32_t kv_pages_total;
+    uint32_t kv_pages_free;
+} ribn_b200_limits;
+
+/* BatchItem (crates/runtime/src/executor.rs:67-79). */
+typedef struct {
+    uint64_t sequence;
+    uint32_t kind;          /* RIBN_B200_PREFILL / RIBN_B200_DECODE */
+    uint32_t prefix;
+    uint32_t token_budget;
+    uint32_t output_budget;
+} ribn_b200_batch_item;
+
+/* StepCompletion (crates/runtime/src/executor.rs:101-106); max_decode_tokens
+ * is 1, so a row carries at most one sampled token. */
+typedef struct {
+    uint64_t sequence;
+    uint32_t prefix;    /* absolute prefix after this step */
+    uint32_t n_tokens;  /* 0 or 1 */
+    uint32_t token;
+    uint32_t reserved;
+} ribn_b200_completion;
+
+/* ---- lifecycle ---------------------------------------------------------- */
+
+/* Replaces QwenCuda::load_gguf's executor construction
+ * (crates/qwen/src/cuda.rs:16-53, crates/qwen/src/loading.rs:93-190). */
+RIBN_B200_API int ribn_b200_create(const ribn_b200_config* config, ribn_b200_executor** out,
+                                   char* error, size_t error_capacity);
+/* Drop (crates/qwen/src/cuda.rs:111-121): synchronises, then frees. */
+RIBN_B200_API int ribn_b200_destroy(ribn_b200_executor* executor);
+
+/* Upload one GGUF tensor's encoded bytes verbatim.  Matrices are
+ * `[rows = out][cols = in, contiguous]` blocks, norms are F32 vectors with
+ * rows = 1.  Names are GGUF's (`blk.N.attn_q.weight`, `token_embd.weight`,
+ * `output_norm.weight`, `output.weight`, ...).  Replaces
+ * CudaQwen35Weights::stage (crates/nvidia/src/staging.rs:263-315,
+ * crates/nvidia/src/cuda.rs:320-387). */
+RIBN_B200_API int ribn_b200_load_tensor(ribn_b200_executor* executor, const char* name,
+                                        int32_t ggml_type, int64_t rows, int64_t cols,
+                                        const void* bytes, size_t byte_count);
+/* Fill every tensor with seeded N(0, 0.02) weights quantised on the device
+ * (norm weights 1.0).  No reference counterpart: the reference has no
+ * quantiser; the encoded bytes are the ground truth shared with any checker. */
+RIBN_B200_API int ribn_b200_init_synthetic(ribn_b200_executor* executor, uint64_t seed, int32_t scheme);
+/* Copy a loaded tensor's encoded GGUF bytes back to the host
+ * (CudaWeightStore::copy_quantized_to_host, crates/nvidia/tests/cuda_reference.rs:244-248).
+ * Any of the out pointers may be NULL; `bytes` may be NULL to query the size. */
+RIBN_B200_API int ribn_b200_read_tensor(ribn_b200_executor* executor, const char* name,
+                                        int32_t* ggml_type, int64_t* rows, int64_t* cols,
+                                        void* bytes, size_t capacity, size_t* byte_count);
+/* Validate the model plan, repack weights for the fast kernels, allocate the
+ * KV arena and step scratch (validate_model_plan, crates/nvidia/src/decode.rs:364-368;
+ * loading.rs:93-190).  Must be called once before admit. */
+RIBN_B200_API int ribn_b200_finalize(ribn_b200_executor* executor);
+
+/* ---- GenerationExecutor (crates/runtime/src/executor.rs:171-254) -------- */
+
+/* info() */
+RIBN_B200_API int ribn_b200_info(ribn_b200_executor* executor, ribn_b200_limits* out);
+/* admit(): OK = Admission::Ready (pages for prompt + max_output reserved),
+ * REJECTED, DEFERRED, or ERROR (duplicate sequence / faulted executor).
+ * Semantics follow QwenExecution::admit (crates/qwen/src/execution.rs:80-162). */
+RIBN_B200_API int ribn_b200_admit(ribn_b200_executor* executor, uint64_t request_id, uint64_t sequence,
+                                  const uint32_t* tokens, uint32_t token_count,
+                                  uint32_t max_output_tokens, float temperature,
+                                  const uint32_t* stop_tokens, uint32_t stop_count);
+/* prepare(): OK = BatchPreparation::Ready.  Never advances state
+ * (crates/qwen/src/execution.rs:164-269). */
+RIBN_B200_API int ribn_b200_prepare(ribn_b200_executor* executor, const ribn_b200_batch_item* items,
+                                    uint32_t count);
+/* abandon_preparation(): idempotent. */
+RIBN_B200_API int ribn_b200_abandon_preparation(ribn_b200_executor* executor);
+/* submit(): asynchronous; must repeat the prepared rows
+ * (crates/qwen/src/execution.rs:275-316). */
+RIBN_B200_API int ribn_b200_submit(ribn_b200_executor* executor, const ribn_b200_batch_item* items,
+                                   uint32_t count, uint64_t* submission);
+/* poll(): PENDING while the device is busy, else OK with exactly one row per
+ * submitted row, in order (crates/qwen/src/execution.rs:329-414). */
+RIBN_B200_API int ribn_b200_poll(ribn_b200_executor* executor, uint64_t submission,
+                                 ribn_b200_completion* rows, uint32_t capacity, uint32_t* count);
+/* release(): idempotent (crates/qwen/src/execution.rs:416-440). */
+RIBN_B200_API int ribn_b200_release(ribn_b200_executor* executor, uint64_t sequence);
+/* synchronize(): block until every queued launch has finished. */
+RIBN_B200_API int ribn_b200_synchronize(ribn_b200_executor* executor);
+/* ExecutionError text of the last failing call, at most 4096 bytes
+ * (crates/runtime/src/executor.rs:134-152).  Returns the length written. */
+RIBN_B200_API size_t ribn_b200_last_error(ribn_b200_executor* executor, char* buffer, size_t capacity);
+
+/* ---- parity / measurement taps ------------------------------------------ */
+
+/* F32 logits of sampling row `row` of the last completed submission
+ * (CudaQwen35Decode::copy_logits, crates/nvidia/src/decode.rs:788).
+ * Needs RIBN_B200_FLAG_KEEP_LOGITS. */
+RIBN_B200_API int ribn_b200_copy_logits(ribn_b200_executor* executor, uint32_t row, float* out,
+                                        size_t capacity);
+/* F16 K (which = 0) or V (which = 1) rows of one layer for the first `tokens`
+ * positions of a sequence, gathered through its page table into
+ * `[token][kv_head][head_dim]`. */
+RIBN_B200_API int ribn_b200_copy_kv(ribn_b200_executor* executor, uint64_t sequence, int32_t layer,
+                                    int32_t which, uint32_t tokens, uint16_t* out);
+/* Measurement aid: mark `tokens` positions of an admitted sequence as already
+ * consumed, with its KV pages filled with seeded F16 values and `next_token`
+ * as its pending decode input, so steady-state decode at a long context can
+ * be timed without running the prefill. */
+RIBN_B200_API int ribn_b200_debug_set_context(ribn_b200_executor* executor, uint64_t sequence,
+                                              uint32_t tokens, uint32_t next_token, uint64_t seed);
+/* Device time (CUDA events on the executor's stream) of the last completed
+ * submission, and how many kernels it launched. */
+RIBN_B200_API int ribn_b200_last_step_stats(ribn_b200_executor* executor, float* device_ms,
+                                            uint32_t* kernel_launches);
+/* Algorithmic HBM bytes of one decode step: quantised weight bytes read once
+ * plus `context_tokens_total` tokens of F16 K and V over all layers. */
+RIBN_B200_API int ribn_b200_step_bytes(ribn_b200_executor* executor, uint64_t context_tokens_total,
+                                       uint64_t* weight_bytes, uint64_t* kv_bytes);
+
+/* ---- single operators (host pointers in, host pointers out) ------------- */
+/* Each runs the same device kernels the executor uses, on `device`, and is
+ * what the per-primitive parity tests call.  They replace the operator
+ * wrappers of crates/nvidia/src/quantized.rs and crates/nvidia/src/model_ops.rs. */
+
+/* dequantize_block over `rows x cols` (crates/gguf/src/lib.rs:508-535), bit-exact. */
+RIBN_B200_API int ribn_b200_op_dequantize(int32_t device, int32_t ggml_type, const void* bytes,
+                                          int64_t rows, int64_t cols, float* out);
+/* y[m][n] = sum_k deq(W[n][k]) x[m][k] (CudaQuantizedGemv::execute_warp /
+ * gemv_batch, crates/nvidia/src/quantized.rs:303-436).  variant 0 = fast
+ * kernels, 1 = one-warp-per-row reference kernels. */
+RIBN_B200_API int ribn_b200_op_gemv(int32_t device, int32_t ggml_type, const void* weights,
+                                    int64_t rows, int64_t cols, const float* x, int32_t members,
+                                    float* y, int32_t variant);
+/* rms_norm(_batch) (crates/nvidia/src/model_ops.rs:108-201). */
+RIBN_B200_API int ribn_b200_op_rms_norm(int32_t device, const float* x, const float* weight,
+                                        int32_t members, int32_t length, float eps, float* out);
+/* silu_mul (model_ops.rs:318-330). */
+RIBN_B200_API int ribn_b200_op_silu_mul(int32_t device, const float* gate, const float* up,
+                                        int64_t length, float* out);
+/* argmax(_batch) (model_ops.rs:203-316): lowest index on ties, NaN skipped. */
+RIBN_B200_API int ribn_b200_op_argmax(int32_t device, const float* logits, int32_t members,
+                                      int64_t length, uint32_t* out);
+/* rope_neox(_batch) (model_ops.rs:395-425, 1178-1211): in place on
+ * `[members][heads][head_dim]`, one position per member. */
+RIBN_B200_API int ribn_b200_op_rope_neox(int32_t device, float* values, const int64_t* positions,
+                                         int32_t members, int32_t heads, int32_t head_dim,
+                                         int32_t rot_dims, float base);
+/* f32_to_f16_bits as used by kv_append_f16 (model_ops.rs:1213-1277). */
+RIBN_B200_API int ribn_b200_op_f32_to_f16(int32_t device, const float* in, int64_t length,
+                                          uint16_t* out);
+/* attn_score_gqa_paged without the Qwen3.5 output gate (model_ops.rs:441-589):
+ * `rows` consecutive query positions of one sequence whose cache holds
+ * `tokens` keys; row r attends tokens - rows + 1 + r keys.  K/V are F16
+ * `[physical_token][kv_head][head_dim]`, `page_table[logical / page_tokens]`
+ * gives the physical page.  window = 0 means full causal attention;
+ * variant as in op_gemv. */
+RIBN_B200_API int ribn_b200_op_attention(int32_t device, const float* q, const uint16_t* keys,
+                                         const uint16_t* values, const int32_t* page_table,
+                                         int32_t page_tokens, int32_t physical_tokens,
+                                         int32_t tokens, int32_t rows, int32_t q_heads,
+                                         int32_t kv_heads, int32_t head_dim, int32_t window,
+                                         float* out, int32_t variant);
+/* Ragged batch metadata built on the device from per-row (prefix, tokens)
+ * records: cu_seqlens[rows + 1], and per token its row, position and physical
+ * KV slot.  Supersedes the host-built DescriptorPacket
+ * (crates/nvidia/src/member_descriptor.rs:6-108). */
+RIBN_B200_API int ribn_b200_op_batch_metadata(int32_t device, const int32_t* row_slot,
+                                              const int32_t* row_prefix, const int32_t* row_tokens,
+                                              int32_t rows, const int32_t* page_tables,
+                                              int32_t pages_per_sequence, int32_t page_tokens,
+                                              int32_t* cu_seqlens, int32_t* token_row,
+                                              int32_t* token_position, int32_t* token_kv_slot);
+
+/* Host-side tile-major repack used by finalize (no device work): writes the
+ * packed form of raw GGUF rows and returns its size; `out` may be NULL to
+ * query the size.  No reference counterpart: the reference uploads GGUF bytes
+ * verbatim (crates/nvidia/src/cuda.rs:320-387). */
+RIBN_B200_API int ribn_b200_debug_repack(int32_t ggml_type, const void* raw, int64_t rows, int64_t cols,
+                                         void* out, size_t capacity, size_t* byte_count);
+
+/* Library build identification (git-free; the CUDA arch it was built for). */
+RIBN_B200_API const char* ribn_b200_build_info(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RIBN_B200_H */

@@ -1,0 +1,107 @@
+"""ctypes binding of ``libribn_b200.so`` — exactly the symbols declared in
+``include/ribn_b200.h``.  There is no fallback: a missing library raises."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+F32, F16, Q8_0, Q4_K, Q6_K = 0, 1, 8, 12, 14
+OK, PENDING, REJECTED, DEFERRED, ERROR = 0, 1, 2, 3, -1
+PREFILL, DECODE = 0, 1
+SCHEME_Q8_0, SCHEME_Q4_K_M = 0, 1
+FLAG_KEEP_LOGITS, FLAG_REFERENCE_KERNELS, FLAG_NO_GRAPH = 1, 2, 4
+
+
+class Config(C.Structure):
+    _fields_ = [
+        ("layers", C.c_int32), ("hidden", C.c_int32), ("q_heads", C.c_int32), ("kv_heads", C.c_int32),
+        ("head_dim", C.c_int32), ("ffn", C.c_int32), ("vocab", C.c_int32),
+        ("rope_base", C.c_float), ("rms_eps", C.c_float),
+        ("context_tokens", C.c_int32), ("max_sequences", C.c_int32), ("max_batch_tokens", C.c_int32),
+        ("kv_pages", C.c_int32), ("device", C.c_int32), ("flags", C.c_int32),
+    ]
+
+
+class Limits(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in (
+        "context_tokens", "max_sequences", "max_batch_tokens", "max_decode_tokens", "kv_page_tokens",
+        "kv_pages_total", "kv_pages_free")]
+
+
+class BatchItemC(C.Structure):
+    _fields_ = [("sequence", C.c_uint64), ("kind", C.c_uint32), ("prefix", C.c_uint32),
+                ("token_budget", C.c_uint32), ("output_budget", C.c_uint32)]
+
+
+class CompletionC(C.Structure):
+    _fields_ = [("sequence", C.c_uint64), ("prefix", C.c_uint32), ("n_tokens", C.c_uint32),
+                ("token", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+_P = C.c_void_p
+# name -> (restype, argtypes); one entry per declaration in include/ribn_b200.h
+SIGNATURES = {
+    "ribn_b200_create": (C.c_int, [C.POINTER(Config), C.POINTER(_P), C.c_char_p, C.c_size_t]),
+    "ribn_b200_destroy": (C.c_int, [_P]),
+    "ribn_b200_load_tensor": (C.c_int, [_P, C.c_char_p, C.c_int32, C.c_int64, C.c_int64, _P, C.c_size_t]),
+    "ribn_b200_init_synthetic": (C.c_int, [_P, C.c_uint64, C.c_int32]),
+    "ribn_b200_read_tensor": (C.c_int, [_P, C.c_char_p, C.POINTER(C.c_int32), C.POINTER(C.c_int64),
+                                        C.POINTER(C.c_int64), _P, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "ribn_b200_finalize": (C.c_int, [_P]),
+    "ribn_b200_info": (C.c_int, [_P, C.POINTER(Limits)]),
+    "ribn_b200_admit": (C.c_int, [_P, C.c_uint64, C.c_uint64, _P, C.c_uint32, C.c_uint32, C.c_float, _P,
+                                  C.c_uint32]),
+    "ribn_b200_prepare": (C.c_int, [_P, C.POINTER(BatchItemC), C.c_uint32]),
+    "ribn_b200_abandon_preparation": (C.c_int, [_P]),
+    "ribn_b200_submit": (C.c_int, [_P, C.POINTER(BatchItemC), C.c_uint32, C.POINTER(C.c_uint64)]),
+    "ribn_b200_poll": (C.c_int, [_P, C.c_uint64, C.POINTER(CompletionC), C.c_uint32, C.POINTER(C.c_uint32)]),
+    "ribn_b200_release": (C.c_int, [_P, C.c_uint64]),
+    "ribn_b200_synchronize": (C.c_int, [_P]),
+    "ribn_b200_last_error": (C.c_size_t, [_P, C.c_char_p, C.c_size_t]),
+    "ribn_b200_copy_logits": (C.c_int, [_P, C.c_uint32, _P, C.c_size_t]),
+    "ribn_b200_copy_kv": (C.c_int, [_P, C.c_uint64, C.c_int32, C.c_int32, C.c_uint32, _P]),
+    "ribn_b200_debug_set_context": (C.c_int, [_P, C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint64]),
+    "ribn_b200_last_step_stats": (C.c_int, [_P, C.POINTER(C.c_float), C.POINTER(C.c_uint32)]),
+    "ribn_b200_step_bytes": (C.c_int, [_P, C.c_uint64, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "ribn_b200_op_dequantize": (C.c_int, [C.c_int32, C.c_int32, _P, C.c_int64, C.c_int64, _P]),
+    "ribn_b200_op_gemv": (C.c_int, [C.c_int32, C.c_int32, _P, C.c_int64, C.c_int64, _P, C.c_int32, _P, C.c_int32]),
+    "ribn_b200_op_rms_norm": (C.c_int, [C.c_int32, _P, _P, C.c_int32, C.c_int32, C.c_float, _P]),
+    "ribn_b200_op_silu_mul": (C.c_int, [C.c_int32, _P, _P, C.c_int64, _P]),
+    "ribn_b200_op_argmax": (C.c_int, [C.c_int32, _P, C.c_int32, C.c_int64, _P]),
+    "ribn_b200_op_rope_neox": (C.c_int, [C.c_int32, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float]),
+    "ribn_b200_op_f32_to_f16": (C.c_int, [C.c_int32, _P, C.c_int64, _P]),
+    "ribn_b200_op_attention": (C.c_int, [C.c_int32, _P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                         C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, C.c_int32]),
+    "ribn_b200_op_batch_metadata": (C.c_int, [C.c_int32, _P, _P, _P, C.c_int32, _P, C.c_int32, C.c_int32, _P, _P,
+                                              _P, _P]),
+    "ribn_b200_debug_repack": (C.c_int, [C.c_int32, _P, C.c_int64, C.c_int64, _P, C.c_size_t,
+                                         C.POINTER(C.c_size_t)]),
+    "ribn_b200_build_info": (C.c_char_p, []),
+}
+
+_LIB = None
+
+
+def library_path() -> str:
+    return os.path.join(HERE, "libribn_b200.so")
+
+
+def lib() -> C.CDLL:
+    """Load the CUDA library.  Raises if it has not been built: the product
+    path has no CPU implementation to fall back to."""
+    global _LIB
+    if _LIB is None:
+        path = library_path()
+        if not os.path.exists(path):
+            raise RuntimeError(
+                f"{path} is missing: build it with `python -m ribn_b200.build` (needs nvcc); "
+                "ribn_b200 has no CPU fallback")
+        handle = C.CDLL(path)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError if the library lacks a declared symbol
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _LIB = handle
+    return _LIB

@@ -1,0 +1,849 @@
+// The executor behind the C ABI: model plan, paged KV arena, admission,
+// prepare / submit / poll, and the per-step launch sequence.
+//
+// Protocol semantics follow QwenExecution (crates/qwen/src/execution.rs) and
+// the GenerationExecutor contract (crates/runtime/src/executor.rs:171-254).
+// The device side is new: one ragged batch of T tokens (decode rows and
+// prefill chunks together) flows through every layer in a single launch
+// sequence, with the batch metadata built on the device from 32-byte row
+// records, instead of the reference's one-launch-sequence-per-member decode
+// (crates/nvidia/src/decode.rs:550-640, 2161-2334).
+#include "executor.h"
+
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <thread>
+
+#include "blocks.cuh"
+
+using namespace ribn;
+
+namespace {
+
+constexpr size_t kMaxError = 4096;  // ExecutionError bound, crates/runtime/src/executor.rs:134-152
+
+int fail(ribn_b200_executor* ex, const char* fmt, ...) {
+    char buf[kMaxError];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    ex->error = buf;
+    return RIBN_B200_ERROR;
+}
+
+int soft(ribn_b200_executor* ex, int code, const char* fmt, ...) {
+    char buf[kMaxError];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    ex->error = buf;
+    return code;
+}
+
+#define CU_TRY(ex, expr)                                                                       \
+    do {                                                                                       \
+        cudaError_t e_ = (expr);                                                               \
+        if (e_ != cudaSuccess) {                                                               \
+            (ex)->faulted = true;                                                              \
+            return fail((ex), "CUDA error %s at %s:%d (%s)", cudaGetErrorString(e_), __FILE__, \
+                        __LINE__, #expr);                                                      \
+        }                                                                                      \
+    } while (0)
+
+template <typename T>
+cudaError_t dev_alloc(ribn_b200_executor* ex, T** out, size_t count) {
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, std::max<size_t>(count, 1) * sizeof(T));
+    if (e == cudaSuccess) {
+        ex->allocations.push_back(p);
+        *out = (T*)p;
+    }
+    return e;
+}
+
+const char* kLayerNames[kLayerTensors] = {
+    "attn_norm.weight", "attn_q.weight", "attn_k.weight", "attn_v.weight", "attn_q_norm.weight",
+    "attn_k_norm.weight", "attn_output.weight", "ffn_norm.weight", "ffn_gate.weight", "ffn_up.weight",
+    "ffn_down.weight"};
+
+Tensor* find_tensor(ribn_b200_executor* ex, const char* name) {
+    if (!strcmp(name, "token_embd.weight")) return &ex->token_embd;
+    if (!strcmp(name, "output_norm.weight")) return &ex->output_norm;
+    if (!strcmp(name, "output.weight")) return &ex->output;
+    int layer = -1;
+    char rest[64];
+    if (sscanf(name, "blk.%d.%63s", &layer, rest) != 2 || layer < 0 || layer >= ex->cfg.layers) return nullptr;
+    for (int i = 0; i < kLayerTensors; ++i) {
+        if (!strcmp(rest, kLayerNames[i])) return &ex->lt(layer, i);
+    }
+    return nullptr;
+}
+
+// Expected (rows, cols) of every tensor of the dense-Qwen3 plan.
+void expected_shape(const ribn_b200_config& c, int which, long long* rows, long long* cols) {
+    const long long H = c.hidden, QD = (long long)c.q_heads * c.head_dim, KD = (long long)c.kv_heads * c.head_dim,
+                    F = c.ffn;
+    switch (which) {
+        case kAttnNorm: case kFfnNorm: *rows = 1; *cols = H; break;
+        case kAttnQ: *rows = QD; *cols = H; break;
+        case kAttnK: case kAttnV: *rows = KD; *cols = H; break;
+        case kAttnQNorm: case kAttnKNorm: *rows = 1; *cols = c.head_dim; break;
+        case kAttnOutput: *rows = H; *cols = QD; break;
+        case kFfnGate: case kFfnUp: *rows = F; *cols = H; break;
+        case kFfnDown: *rows = H; *cols = F; break;
+    }
+}
+
+bool is_norm(int which) {
+    return which == kAttnNorm || which == kFfnNorm || which == kAttnQNorm || which == kAttnKNorm;
+}
+
+int set_tensor_storage(ribn_b200_executor* ex, Tensor* t, int type, long long rows, long long cols) {
+    const int elems = block_elems(type);
+    if (elems == 0 || rows <= 0 || cols <= 0 || cols % elems != 0) {
+        return fail(ex, "tensor type %d with shape [%lld, %lld] is not supported", type, rows, cols);
+    }
+    const size_t bytes = (size_t)rows * (size_t)(cols / elems) * (size_t)block_bytes(type);
+    if (t->raw == nullptr || t->bytes != bytes) {
+        // A replaced tensor's old storage stays owned by the executor until destroy.
+        CU_TRY(ex, dev_alloc(ex, &t->raw, bytes));
+    }
+    t->type = type;
+    t->rows = rows;
+    t->cols = cols;
+    t->bytes = bytes;
+    t->packed = PackedMatrix{};
+    return RIBN_B200_OK;
+}
+
+int check_open(ribn_b200_executor* ex) {
+    if (ex == nullptr) return RIBN_B200_ERROR;
+    if (ex->faulted) return fail(ex, "executor is faulted");
+    return RIBN_B200_OK;
+}
+
+int pages_for(uint32_t tokens) { return (int)((tokens + kPageTokens - 1) / kPageTokens); }
+
+// ---------------------------------------------------------------------------
+// the step
+// ---------------------------------------------------------------------------
+struct StepPlan {
+    int n_rows = 0, n_tokens = 0, n_sample = 0, n_prompt_tokens = 0;
+};
+
+#define STEP_TRY(expr)                          \
+    do {                                        \
+        cudaError_t e_ = (expr);                \
+        if (e_ != cudaSuccess) return e_;       \
+        ++launches;                             \
+    } while (0)
+
+bool fast_ok(const ribn_b200_executor* ex, const Tensor& t, int members) {
+    return !(ex->cfg.flags & RIBN_B200_FLAG_REFERENCE_KERNELS) && t.packed.ready() &&
+           members <= kGemvMaxMembers;
+}
+
+// y = W x for `members` vectors, optionally with a fused RMSNorm of x and a
+// residual or SwiGLU epilogue, on whichever kernel family applies.
+cudaError_t project(ribn_b200_executor* ex, int& launches, const Tensor* w, int n_mats, const float* x,
+                    const float* norm_weight, float* normed_tmp, int members, float* const* y, int epilogue) {
+    const ribn_b200_config& c = ex->cfg;
+    bool fast = true;
+    for (int i = 0; i < n_mats; ++i) fast = fast && fast_ok(ex, w[i], members);
+    if (fast) {
+        GemvArgs a{};
+        a.n_segments = n_mats;
+        for (int i = 0; i < n_mats; ++i) {
+            a.seg[i] = GemvSegment{w[i].packed.data, w[i].type, (int)w[i].rows, w[i].packed.row_tiles, y[i]};
+        }
+        a.k = (int)w[0].cols;
+        a.members = members;
+        a.x = x;
+        a.norm_weight = norm_weight;
+        a.eps = c.rms_eps;
+        a.epilogue = epilogue;
+        STEP_TRY(launch_gemv_mma(ex->stream, a, false));
+        return cudaSuccess;
+    }
+    const float* in = x;
+    if (norm_weight != nullptr) {
+        STEP_TRY(launch_rms_norm(ex->stream, x, norm_weight, members, (int)w[0].cols, c.rms_eps, normed_tmp));
+        in = normed_tmp;
+    }
+    if (epilogue == kSwiGLU) {
+        // gate -> ex->gate, up -> ex->up, product -> y[0]
+        STEP_TRY(launch_gemv_ref(ex->stream, w[0].type, w[0].raw, w[0].rows, w[0].cols, in, members, ex->gate, false));
+        STEP_TRY(launch_gemv_ref(ex->stream, w[1].type, w[1].raw, w[1].rows, w[1].cols, in, members, ex->up, false));
+        STEP_TRY(launch_silu_mul(ex->stream, ex->gate, ex->up, (long long)members * w[0].rows, y[0]));
+        return cudaSuccess;
+    }
+    for (int i = 0; i < n_mats; ++i) {
+        STEP_TRY(launch_gemv_ref(ex->stream, w[i].type, w[i].raw, w[i].rows, w[i].cols, in, members, y[i],
+                                 epilogue == kResidual));
+    }
+    return cudaSuccess;
+}
+
+cudaError_t run_step(ribn_b200_executor* ex, const StepPlan& plan, int& launches) {
+    const ribn_b200_config& c = ex->cfg;
+    cudaStream_t s = ex->stream;
+    const int T = plan.n_tokens;
+    launches = 0;
+    STEP_TRY(launch_step_metadata(s, ex->d_rows, plan.n_rows, T, ex->d_tokens, ex->d_next_token,
+                                  ex->d_page_tables, ex->pages_per_sequence, ex->meta));
+    STEP_TRY(launch_embedding(s, ex->token_embd.type, ex->token_embd.raw, c.hidden, c.vocab, ex->meta.token_id, T,
+                              ex->hidden));
+    for (int l = 0; l < c.layers; ++l) {
+        Tensor* t = &ex->lt(l, 0);
+        {
+            Tensor qkv[3] = {t[kAttnQ], t[kAttnK], t[kAttnV]};
+            float* outs[3] = {ex->q, ex->k, ex->v};
+            // q|k|v share the fused-norm input; K and V may differ in type (Q4_K / Q6_K).
+            cudaError_t e = project(ex, launches, qkv, 3, ex->hidden, (const float*)t[kAttnNorm].raw, ex->normed, T,
+                                    outs, kStore);
+            if (e != cudaSuccess) return e;
+        }
+        __half* ck = ex->cache_k + (long long)l * ex->layer_stride;
+        __half* cv = ex->cache_v + (long long)l * ex->layer_stride;
+        STEP_TRY(launch_qk_norm_rope_append(s, ex->q, ex->k, ex->v, (const float*)t[kAttnQNorm].raw,
+                                            (const float*)t[kAttnKNorm].raw, ex->inv_freq, ex->meta.token_pos,
+                                            ex->meta.token_slot, T, c.q_heads, c.kv_heads, c.head_dim, c.rms_eps,
+                                            ck, cv));
+        STEP_TRY(launch_attention_ref(s, ex->q, ck, cv, ex->d_page_tables, ex->pages_per_sequence,
+                                      ex->meta.token_seq, ex->meta.token_pos, T, c.q_heads, c.kv_heads, c.head_dim,
+                                      0, ex->attn));
+        {
+            float* outs[1] = {ex->hidden};
+            cudaError_t e = project(ex, launches, &t[kAttnOutput], 1, ex->attn, nullptr, nullptr, T, outs, kResidual);
+            if (e != cudaSuccess) return e;
+        }
+        {
+            Tensor gu[2] = {t[kFfnGate], t[kFfnUp]};
+            float* outs[2] = {ex->gate, ex->up};
+            cudaError_t e = project(ex, launches, gu, 2, ex->hidden, (const float*)t[kFfnNorm].raw, ex->normed, T,
+                                    outs, kSwiGLU);
+            if (e != cudaSuccess) return e;
+        }
+        {
+            float* outs[1] = {ex->hidden};
+            cudaError_t e = project(ex, launches, &t[kFfnDown], 1, ex->gate, nullptr, nullptr, T, outs, kResidual);
+            if (e != cudaSuccess) return e;
+        }
+    }
+    if (plan.n_sample > 0) {
+        // Only sampling rows reach the head (crates/nvidia/src/decode.rs:686-704).
+        STEP_TRY(launch_rms_norm_gather(s, ex->hidden, ex->meta.sample_token, (const float*)ex->output_norm.raw,
+                                        plan.n_sample, c.hidden, c.rms_eps, ex->head_in));
+        for (int m0 = 0; m0 < plan.n_sample; m0 += kGemvMaxMembers) {
+            const int members = std::min(kGemvMaxMembers, plan.n_sample - m0);
+            float* outs[1] = {ex->logits + (long long)m0 * c.vocab};
+            if (fast_ok(ex, ex->output, members)) {
+                cudaError_t e = project(ex, launches, &ex->output, 1, ex->head_in + (long long)m0 * c.hidden, nullptr,
+                                        nullptr, members, outs, kStore);
+                if (e != cudaSuccess) return e;
+            } else {
+                STEP_TRY(launch_gemv_ref(s, ex->output.type, ex->output.raw, ex->output.rows, ex->output.cols,
+                                         ex->head_in, plan.n_sample, ex->logits, false));
+                break;
+            }
+        }
+        STEP_TRY(launch_argmax(s, ex->logits, plan.n_sample, c.vocab, ex->d_sampled, ex->meta.sample_slot,
+                               ex->d_next_token));
+    }
+    return cudaSuccess;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------
+extern "C" {
+
+#define RIBN_STR2(x) #x
+#define RIBN_STR(x) RIBN_STR2(x)
+const char* ribn_b200_build_info(void) {
+    return "ribn_b200 sm_100a cuda " RIBN_STR(__CUDACC_VER_MAJOR__) "." RIBN_STR(__CUDACC_VER_MINOR__);
+}
+
+int ribn_b200_create(const ribn_b200_config* config, ribn_b200_executor** out, char* error, size_t error_capacity) {
+    auto report = [&](const char* msg) {
+        if (error != nullptr && error_capacity > 0) snprintf(error, error_capacity, "%s", msg);
+        return RIBN_B200_ERROR;
+    };
+    if (config == nullptr || out == nullptr) return report("null argument");
+    const ribn_b200_config& c = *config;
+    if (c.layers <= 0 || c.hidden <= 0 || c.q_heads <= 0 || c.kv_heads <= 0 || c.head_dim <= 0 || c.ffn <= 0 ||
+        c.vocab <= 0 || c.q_heads % c.kv_heads != 0) {
+        return report("model geometry must be positive and q_heads a multiple of kv_heads");
+    }
+    if (c.head_dim != 32 && c.head_dim != 64 && c.head_dim != 128 && c.head_dim != 256) {
+        return report("head_dim must be 32, 64, 128 or 256");
+    }
+    // GenerationLimits::validate, crates/runtime/src/executor.rs:53-63
+    if (c.context_tokens <= 0 || c.max_sequences <= 0 || c.max_batch_tokens <= 0) {
+        return report("prepared model limits must be nonzero");
+    }
+    if (c.max_sequences > 1024) return report("max_sequences above 1024 is not supported");
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        return report("no CUDA device: this library has no CPU path");
+    }
+    if (c.device < 0 || c.device >= count) return report("CUDA device ordinal out of range");
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, c.device) != cudaSuccess) return report("cannot query the CUDA device");
+    if (prop.major != 10) {
+        return report("kernels are built for sm_100a only; this device is not a Blackwell B200-class GPU");
+    }
+    if (cudaSetDevice(c.device) != cudaSuccess) return report("cannot select the CUDA device");
+    auto* ex = new ribn_b200_executor();
+    ex->cfg = c;
+    ex->layer_tensors.resize((size_t)c.layers * kLayerTensors);
+    if (cudaStreamCreateWithFlags(&ex->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreate(&ex->ev_start) != cudaSuccess || cudaEventCreate(&ex->ev_done) != cudaSuccess) {
+        delete ex;
+        return report("cannot create CUDA stream/events");
+    }
+    *out = ex;
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_destroy(ribn_b200_executor* ex) {
+    if (ex == nullptr) return RIBN_B200_OK;
+    cudaSetDevice(ex->cfg.device);
+    // Never free device memory while completion is uncertain: leak instead
+    // (crates/runtime/src/engine.rs:597-607).
+    if (cudaStreamSynchronize(ex->stream) != cudaSuccess) return RIBN_B200_ERROR;
+    for (void* p : ex->allocations) cudaFree(p);
+    if (ex->h_rows) cudaFreeHost(ex->h_rows);
+    if (ex->h_tokens) cudaFreeHost(ex->h_tokens);
+    if (ex->h_sampled) cudaFreeHost(ex->h_sampled);
+    cudaEventDestroy(ex->ev_start);
+    cudaEventDestroy(ex->ev_done);
+    cudaStreamDestroy(ex->stream);
+    delete ex;
+    return RIBN_B200_OK;
+}
+
+size_t ribn_b200_last_error(ribn_b200_executor* ex, char* buffer, size_t capacity) {
+    if (ex == nullptr || buffer == nullptr || capacity == 0) return 0;
+    const size_t n = std::min(std::min(ex->error.size(), capacity - 1), kMaxError);
+    memcpy(buffer, ex->error.data(), n);
+    buffer[n] = 0;
+    return n;
+}
+
+int ribn_b200_load_tensor(ribn_b200_executor* ex, const char* name, int32_t type, int64_t rows, int64_t cols,
+                          const void* bytes, size_t byte_count) {
+    if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    if (ex->finalized) return fail(ex, "tensors cannot change after finalize");
+    cudaSetDevice(ex->cfg.device);
+    Tensor* t = name ? find_tensor(ex, name) : nullptr;
+    if (t == nullptr) return fail(ex, "unknown tensor name '%s'", name ? name : "(null)");
+    if (set_tensor_storage(ex, t, type, rows, cols) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    if (byte_count != t->bytes || bytes == nullptr) {
+        return fail(ex, "tensor '%s' needs %zu encoded bytes, got %zu", name, t->bytes, byte_count);
+    }
+    CU_TRY(ex, cudaMemcpyAsync(t->raw, bytes, byte_count, cudaMemcpyHostToDevice, ex->stream));
+    CU_TRY(ex, cudaStreamSynchronize(ex->stream));
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_init_synthetic(ribn_b200_executor* ex, uint64_t seed, int32_t scheme) {
+    if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    if (ex->finalized) return fail(ex, "tensors cannot change after finalize");
+    if (scheme != RIBN_B200_SCHEME_Q8_0 && scheme != RIBN_B200_SCHEME_Q4_K_M) return fail(ex, "unknown scheme");
+    cudaSetDevice(ex->cfg.device);
+    const ribn_b200_config& c = ex->cfg;
+    const int base = scheme == RIBN_B200_SCHEME_Q8_0 ? kQ8_0 : kQ4_K;
+    const int wide = scheme == RIBN_B200_SCHEME_Q8_0 ? kQ8_0 : kQ6_K;  // attn_v, ffn_down, output
+    uint64_t index = 0;
+    auto fill = [&](Tensor* t, int type, long long rows, long long cols) -> int {
+        if (set_tensor_storage(ex, t, type, rows, cols) != RIBN_B200_OK) return RIBN_B200_ERROR;
+        const uint64_t tensor_seed = seed * 0x9e3779b97f4a7c15ull + (++index) * 0xd1342543de82ef95ull;
+        if (type == kF32) {
+            CU_TRY(ex, launch_fill_f32(ex->stream, (float*)t->raw, rows * cols, 1.0f));
+        } else {
+            CU_TRY(ex, launch_synth_quantized(ex->stream, type, t->raw, rows, cols, tensor_seed, 0.02f));
+        }
+        return RIBN_B200_OK;
+    };
+    for (int l = 0; l < c.layers; ++l) {
+        for (int w = 0; w < kLayerTensors; ++w) {
+            long long rows, cols;
+            expected_shape(c, w, &rows, &cols);
+            int type = is_norm(w) ? kF32 : ((w == kAttnV || w == kFfnDown) ? wide : base);
+            if (fill(&ex->lt(l, w), type, rows, cols) != RIBN_B200_OK) return RIBN_B200_ERROR;
+        }
+    }
+    if (fill(&ex->token_embd, base, c.vocab, c.hidden) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    if (fill(&ex->output_norm, kF32, 1, c.hidden) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    if (fill(&ex->output, wide, c.vocab, c.hidden) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    CU_TRY(ex, cudaStreamSynchronize(ex->stream));
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_read_tensor(ribn_b200_executor* ex, const char* name, int32_t* type, int64_t* rows, int64_t* cols,
+                          void* bytes, size_t capacity, size_t* byte_count) {
+    if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    cudaSetDevice(ex->cfg.device);
+    Tensor* t = name ? find_tensor(ex, name) : nullptr;
+    if (t == nullptr || !t->loaded()) return fail(ex, "tensor '%s' is not loaded", name ? name : "(null)");
+    if (type) *type = t->type;
+    if (rows) *rows = t->rows;
+    if (cols) *cols = t->cols;
+    if (byte_count) *byte_count = t->bytes;
+    if (bytes != nullptr) {
+        if (capacity < t->bytes) return fail(ex, "buffer too small for tensor '%s'", name);
+        CU_TRY(ex, cudaMemcpyAsync(bytes, t->raw, t->bytes, cudaMemcpyDeviceToHost, ex->stream));
+        CU_TRY(ex, cudaStreamSynchronize(ex->stream));
+    }
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_finalize(ribn_b200_executor* ex) {
+    if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    if (ex->finalized) return fail(ex, "finalize called twice");
+    cudaSetDevice(ex->cfg.device);
+    const ribn_b200_config& c = ex->cfg;
+    // Model plan validation (validate_model_plan, crates/nvidia/src/decode.rs:364-368).
+    for (int l = 0; l < c.layers; ++l) {
+        for (int w = 0; w < kLayerTensors; ++w) {
+            const Tensor& t = ex->lt(l, w);
+            long long rows, cols;
+            expected_shape(c, w, &rows, &cols);
+            if (!t.loaded()) return fail(ex, "missing tensor blk.%d.%s", l, kLayerNames[w]);
+            if (t.rows * t.cols != rows * cols || (!is_norm(w) && (t.rows != rows || t.cols != cols))) {
+                return fail(ex, "tensor blk.%d.%s has shape [%lld, %lld], expected [%lld, %lld]", l, kLayerNames[w],
+                            t.rows, t.cols, rows, cols);
+            }
+            if (is_norm(w) ? t.type != kF32 : (t.type != kQ8_0 && t.type != kQ4_K && t.type != kQ6_K)) {
+                return fail(ex, "tensor blk.%d.%s has unsupported type %d", l, kLayerNames[w], t.type);
+            }
+        }
+    }
+    if (!ex->token_embd.loaded() || ex->token_embd.rows != c.vocab || ex->token_embd.cols != c.hidden) {
+        return fail(ex, "token_embd.weight must be [vocab, hidden]");
+    }
+    if (!ex->output_norm.loaded() || ex->output_norm.type != kF32 || ex->output_norm.rows * ex->output_norm.cols != c.hidden) {
+        return fail(ex, "output_norm.weight must be F32 [hidden]");
+    }
+    if (!ex->output.loaded() || ex->output.rows != c.vocab || ex->output.cols != c.hidden ||
+        (ex->output.type != kQ8_0 && ex->output.type != kQ4_K && ex->output.type != kQ6_K)) {
+        return fail(ex, "output.weight must be a quantised [vocab, hidden] matrix");
+    }
+
+    // Tile-major repack for the tensor-core GEMV.
+    if (!(c.flags & RIBN_B200_FLAG_REFERENCE_KERNELS)) {
+        std::vector<Tensor*> mats;
+        for (int l = 0; l < c.layers; ++l) {
+            for (int w = 0; w < kLayerTensors; ++w) if (!is_norm(w)) mats.push_back(&ex->lt(l, w));
+        }
+        mats.push_back(&ex->output);
+        size_t largest = 0;
+        for (Tensor* t : mats) if (packable(t->type, t->rows, t->cols)) largest = std::max(largest, t->bytes);
+        std::vector<unsigned char> raw(largest), packed;
+        const int threads = (int)std::max(1u, std::min(32u, std::thread::hardware_concurrency()));
+        for (Tensor* t : mats) {
+            if (!packable(t->type, t->rows, t->cols)) continue;
+            PackedMatrix& p = t->packed;
+            p.type = t->type; p.n = t->rows; p.k = t->cols;
+            p.row_tiles = (int)((t->rows + kTileRows - 1) / kTileRows);
+            p.k_tiles = (int)(t->cols / kTileCols);
+            p.bytes = packed_bytes(t->type, t->rows, t->cols);
+            packed.resize(p.bytes);
+            CU_TRY(ex, cudaMemcpy(raw.data(), t->raw, t->bytes, cudaMemcpyDeviceToHost));
+            repack_host(t->type, raw.data(), t->rows, t->cols, packed.data(), threads);
+            CU_TRY(ex, dev_alloc(ex, &p.data, p.bytes));
+            CU_TRY(ex, cudaMemcpy(p.data, packed.data(), p.bytes, cudaMemcpyHostToDevice));
+        }
+    }
+
+    // Rotary table on the host, with the host libm's powf, so theta matches
+    // `pos as f32 * base.powf(-(2 pair) / rot)` bit for bit
+    // (crates/nvidia/src/qwen_reference.rs:414-415).
+    {
+        std::vector<float> table((size_t)c.head_dim / 2);
+        for (int p = 0; p < c.head_dim / 2; ++p) {
+            table[p] = powf(c.rope_base, -(2.0f * (float)p) / (float)c.head_dim);
+        }
+        CU_TRY(ex, dev_alloc(ex, &ex->inv_freq, table.size()));
+        CU_TRY(ex, cudaMemcpy(ex->inv_freq, table.data(), table.size() * sizeof(float), cudaMemcpyHostToDevice));
+    }
+
+    // Paged KV arena (KvStateSpec, crates/core/src/state.rs:37-173): one shared
+    // pool of 16-token pages; a sequence's table maps logical to physical pages.
+    ex->pages_per_sequence = pages_for((uint32_t)c.context_tokens);
+    ex->kv_pages = c.kv_pages > 0 ? c.kv_pages : ex->pages_per_sequence * c.max_sequences;
+    const long long row_elems = (long long)c.kv_heads * c.head_dim;
+    ex->layer_stride = (long long)ex->kv_pages * kPageTokens * row_elems;
+    CU_TRY(ex, dev_alloc(ex, &ex->cache_k, (size_t)ex->layer_stride * c.layers));
+    CU_TRY(ex, dev_alloc(ex, &ex->cache_v, (size_t)ex->layer_stride * c.layers));
+    CU_TRY(ex, cudaMemsetAsync(ex->cache_k, 0, (size_t)ex->layer_stride * c.layers * sizeof(__half), ex->stream));
+    CU_TRY(ex, cudaMemsetAsync(ex->cache_v, 0, (size_t)ex->layer_stride * c.layers * sizeof(__half), ex->stream));
+    ex->free_pages.resize(ex->kv_pages);
+    for (int i = 0; i < ex->kv_pages; ++i) ex->free_pages[i] = ex->kv_pages - 1 - i;
+    ex->free_slots.resize(c.max_sequences);
+    for (int i = 0; i < c.max_sequences; ++i) ex->free_slots[i] = c.max_sequences - 1 - i;
+    CU_TRY(ex, dev_alloc(ex, &ex->d_page_tables, (size_t)c.max_sequences * ex->pages_per_sequence));
+    CU_TRY(ex, cudaMemsetAsync(ex->d_page_tables, 0, (size_t)c.max_sequences * ex->pages_per_sequence * 4, ex->stream));
+    CU_TRY(ex, dev_alloc(ex, &ex->d_next_token, (size_t)c.max_sequences));
+    CU_TRY(ex, cudaMemsetAsync(ex->d_next_token, 0, (size_t)c.max_sequences * 4, ex->stream));
+
+    // Step buffers.
+    const size_t T = (size_t)c.max_batch_tokens, S = (size_t)c.max_sequences;
+    const size_t QD = (size_t)c.q_heads * c.head_dim, KD = (size_t)c.kv_heads * c.head_dim;
+    CU_TRY(ex, cudaMallocHost((void**)&ex->h_rows, S * sizeof(RowDesc)));
+    CU_TRY(ex, cudaMallocHost((void**)&ex->h_tokens, T * sizeof(uint32_t)));
+    CU_TRY(ex, cudaMallocHost((void**)&ex->h_sampled, S * sizeof(uint32_t)));
+    CU_TRY(ex, dev_alloc(ex, &ex->d_rows, S));
+    CU_TRY(ex, dev_alloc(ex, &ex->d_tokens, T));
+    CU_TRY(ex, dev_alloc(ex, &ex->d_sampled, S));
+    CU_TRY(ex, dev_alloc(ex, &ex->meta.cu_seqlens, S + 1));
+    CU_TRY(ex, dev_alloc(ex, &ex->meta.token_row, T));
+    CU_TRY(ex, dev_alloc(ex, &ex->meta.token_pos, T));
+    CU_TRY(ex, dev_alloc(ex, &ex->meta.token_slot, T));
+    CU_TRY(ex, dev_alloc(ex, &ex->meta.token_id, T));
+    CU_TRY(ex, dev_alloc(ex, &ex->meta.token_seq, T));
+    CU_TRY(ex, dev_alloc(ex, &ex->meta.sample_token, S));
+    CU_TRY(ex, dev_alloc(ex, &ex->meta.sample_slot, S));
+    CU_TRY(ex, dev_alloc(ex, &ex->hidden, T * c.hidden));
+    CU_TRY(ex, dev_alloc(ex, &ex->normed, T * std::max<size_t>(c.hidden, 1)));
+    CU_TRY(ex, dev_alloc(ex, &ex->q, T * QD));
+    CU_TRY(ex, dev_alloc(ex, &ex->k, T * KD));
+    CU_TRY(ex, dev_alloc(ex, &ex->v, T * KD));
+    CU_TRY(ex, dev_alloc(ex, &ex->attn, T * QD));
+    CU_TRY(ex, dev_alloc(ex, &ex->gate, T * c.ffn));
+    CU_TRY(ex, dev_alloc(ex, &ex->up, T * c.ffn));
+    CU_TRY(ex, dev_alloc(ex, &ex->head_in, S * c.hidden));
+    CU_TRY(ex, dev_alloc(ex, &ex->logits, S * c.vocab));
+    CU_TRY(ex, cudaStreamSynchronize(ex->stream));
+    ex->finalized = true;
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_info(ribn_b200_executor* ex, ribn_b200_limits* out) {
+    if (ex == nullptr || out == nullptr) return RIBN_B200_ERROR;
+    out->context_tokens = (uint32_t)ex->cfg.context_tokens;
+    out->max_sequences = (uint32_t)ex->cfg.max_sequences;
+    out->max_batch_tokens = (uint32_t)ex->cfg.max_batch_tokens;
+    out->max_decode_tokens = 1;
+    out->kv_page_tokens = kPageTokens;
+    out->kv_pages_total = (uint32_t)ex->kv_pages;
+    out->kv_pages_free = (uint32_t)ex->free_pages.size();
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_admit(ribn_b200_executor* ex, uint64_t request_id, uint64_t sequence, const uint32_t* tokens,
+                    uint32_t token_count, uint32_t max_output_tokens, float temperature, const uint32_t* stop_tokens,
+                    uint32_t stop_count) {
+    (void)request_id;
+    if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    if (!ex->finalized) return fail(ex, "executor is not finalized");
+    if (ex->sequences.count(sequence)) return fail(ex, "duplicate sequence");
+    const ribn_b200_config& c = ex->cfg;
+    const uint64_t total = (uint64_t)token_count + max_output_tokens;
+    bool bad = token_count == 0 || max_output_tokens == 0 || total > (uint64_t)c.context_tokens ||
+               (token_count > 0 && tokens == nullptr) || (stop_count > 0 && stop_tokens == nullptr);
+    for (uint32_t i = 0; !bad && i < token_count; ++i) bad = tokens[i] >= (uint32_t)c.vocab;
+    for (uint32_t i = 0; !bad && i < stop_count; ++i) bad = stop_tokens[i] >= (uint32_t)c.vocab;
+    if (bad) return soft(ex, RIBN_B200_REJECTED, "Qwen input/output limits or token IDs are invalid");
+    if (temperature != 0.0f) {
+        return soft(ex, RIBN_B200_REJECTED, "the executor currently supports greedy sampling only");
+    }
+    if ((int)ex->sequences.size() >= c.max_sequences || ex->free_slots.empty()) {
+        return soft(ex, RIBN_B200_DEFERRED, "all sequence slots are in use");
+    }
+    // Reserve the request-reachable envelope atomically (execution.rs:125-149).
+    const int need = pages_for((uint32_t)total);
+    if (need > ex->kv_pages) {
+        return soft(ex, RIBN_B200_REJECTED, "request needs %d KV pages, above the %d-page arena", need, ex->kv_pages);
+    }
+    if (need > (int)ex->free_pages.size()) return soft(ex, RIBN_B200_DEFERRED, "KV arena has no free pages");
+    Sequence seq;
+    seq.id = sequence;
+    seq.slot = ex->free_slots.back();
+    seq.prompt.assign(tokens, tokens + token_count);
+    seq.prompt_len = token_count;
+    seq.max_output = max_output_tokens;
+    seq.pages.resize(need);
+    for (int i = 0; i < need; ++i) {
+        seq.pages[i] = ex->free_pages.back();
+        ex->free_pages.pop_back();
+    }
+    cudaSetDevice(c.device);
+    cudaError_t e = cudaMemcpyAsync(ex->d_page_tables + (size_t)seq.slot * ex->pages_per_sequence, seq.pages.data(),
+                                    (size_t)need * sizeof(int32_t), cudaMemcpyHostToDevice, ex->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ex->stream);  // pageable source: keep it simple and safe
+    if (e != cudaSuccess) {
+        for (int p : seq.pages) ex->free_pages.push_back(p);
+        ex->faulted = true;
+        return fail(ex, "page table upload failed: %s", cudaGetErrorString(e));
+    }
+    ex->free_slots.pop_back();
+    ex->sequences.emplace(sequence, std::move(seq));
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_prepare(ribn_b200_executor* ex, const ribn_b200_batch_item* items, uint32_t count) {
+    if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    if (!ex->finalized) return fail(ex, "executor is not finalized");
+    if (ex->pending.active || ex->prepared) return fail(ex, "Qwen execution is faulted or busy");
+    const ribn_b200_config& c = ex->cfg;
+    uint64_t tokens = 0;
+    for (uint32_t i = 0; i < count; ++i) tokens += items[i].token_budget;
+    if (count == 0 || count > (uint32_t)c.max_sequences || tokens > (uint64_t)c.max_batch_tokens) {
+        return fail(ex, "Qwen batch exceeds prepared limits");
+    }
+    for (uint32_t i = 0; i < count; ++i) {
+        const ribn_b200_batch_item& it = items[i];
+        auto found = ex->sequences.find(it.sequence);
+        if (found == ex->sequences.end()) return fail(ex, "unknown Qwen sequence");
+        const Sequence& s = found->second;
+        if (s.in_flight) return fail(ex, "Qwen sequence is in flight");
+        for (uint32_t j = 0; j < i; ++j) {
+            if (items[j].sequence == it.sequence) return fail(ex, "duplicate sequence in batch");
+        }
+        const uint64_t end = (uint64_t)it.prefix + it.token_budget;
+        if (it.token_budget == 0 || s.position != it.prefix || end > (uint64_t)c.context_tokens) {
+            return fail(ex, "Qwen work does not match the sequence prefix/capacity");
+        }
+        if (it.kind == RIBN_B200_PREFILL) {
+            if (end > s.prompt_len || it.output_budget != (end == s.prompt_len ? 1u : 0u)) {
+                return fail(ex, "Qwen prefill boundary/output mismatch");
+            }
+        } else if (it.kind == RIBN_B200_DECODE) {
+            if (it.token_budget != 1 || it.output_budget != 1 || it.prefix < s.prompt_len) {
+                return fail(ex, "Qwen adapter only supports one-token ordinary decode");
+            }
+            if (!s.has_next) return fail(ex, "Qwen decode has no next token");
+            if (end > (uint64_t)s.prompt_len + s.max_output) {
+                return fail(ex, "Qwen work does not match the sequence prefix/capacity");
+            }
+        } else {
+            return fail(ex, "unknown step kind");
+        }
+    }
+    ex->prepared_items.assign(items, items + count);
+    ex->prepared = true;
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_abandon_preparation(ribn_b200_executor* ex) {
+    if (ex == nullptr) return RIBN_B200_ERROR;
+    ex->prepared = false;
+    ex->prepared_items.clear();
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_submit(ribn_b200_executor* ex, const ribn_b200_batch_item* items, uint32_t count, uint64_t* submission) {
+    if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    if (!ex->prepared) return fail(ex, "submit without a preparation");
+    if (count != ex->prepared_items.size() ||
+        memcmp(items, ex->prepared_items.data(), count * sizeof(ribn_b200_batch_item)) != 0) {
+        return fail(ex, "submitted rows differ from the prepared rows");
+    }
+    cudaSetDevice(ex->cfg.device);
+    Pending& p = ex->pending;
+    p.items = ex->prepared_items;
+    p.sample_row.assign(count, -1);
+    StepPlan plan;
+    plan.n_rows = (int)count;
+    for (uint32_t i = 0; i < count; ++i) {
+        const ribn_b200_batch_item& it = items[i];
+        Sequence& s = ex->sequences.find(it.sequence)->second;
+        RowDesc& r = ex->h_rows[i];
+        r.slot = s.slot;
+        r.prefix = (int32_t)it.prefix;
+        r.tokens = (int32_t)it.token_budget;
+        if (it.kind == RIBN_B200_PREFILL) {
+            r.token_offset = plan.n_prompt_tokens;
+            memcpy(ex->h_tokens + plan.n_prompt_tokens, s.prompt.data() + it.prefix, it.token_budget * sizeof(uint32_t));
+            plan.n_prompt_tokens += (int)it.token_budget;
+        } else {
+            r.token_offset = -1;
+        }
+        r.sample_row = it.output_budget > 0 ? plan.n_sample++ : -1;
+        p.sample_row[i] = r.sample_row;
+        r.pad[0] = r.pad[1] = r.pad[2] = 0;
+        plan.n_tokens += (int)it.token_budget;
+    }
+    p.n_sample = plan.n_sample;
+    // Mark ownership before the first launch: if anything below fails the
+    // executor faults and keeps everything until synchronize.
+    for (uint32_t i = 0; i < count; ++i) ex->sequences.find(items[i].sequence)->second.in_flight = true;
+    ex->prepared = false;
+    p.active = true;
+    p.id = ex->next_submission++;
+    CU_TRY(ex, cudaEventRecord(ex->ev_start, ex->stream));
+    CU_TRY(ex, cudaMemcpyAsync(ex->d_rows, ex->h_rows, count * sizeof(RowDesc), cudaMemcpyHostToDevice, ex->stream));
+    if (plan.n_prompt_tokens > 0) {
+        CU_TRY(ex, cudaMemcpyAsync(ex->d_tokens, ex->h_tokens, (size_t)plan.n_prompt_tokens * sizeof(uint32_t),
+                                   cudaMemcpyHostToDevice, ex->stream));
+    }
+    int launches = 0;
+    CU_TRY(ex, run_step(ex, plan, launches));
+    p.launches = launches;
+    if (plan.n_sample > 0) {
+        CU_TRY(ex, cudaMemcpyAsync(ex->h_sampled, ex->d_sampled, (size_t)plan.n_sample * sizeof(uint32_t),
+                                   cudaMemcpyDeviceToHost, ex->stream));
+    }
+    CU_TRY(ex, cudaEventRecord(ex->ev_done, ex->stream));
+    *submission = p.id;
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_poll(ribn_b200_executor* ex, uint64_t submission, ribn_b200_completion* rows, uint32_t capacity,
+                   uint32_t* count) {
+    if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    Pending& p = ex->pending;
+    if (!p.active) return fail(ex, "unknown Qwen submission");
+    if (p.id != submission) return fail(ex, "Qwen submission identity mismatch");
+    cudaSetDevice(ex->cfg.device);
+    cudaError_t q = cudaEventQuery(ex->ev_done);
+    if (q == cudaErrorNotReady) return RIBN_B200_PENDING;
+    if (q != cudaSuccess) {
+        // Any status other than NOT_READY is a fault (crates/nvidia/src/serving.rs:624-635).
+        ex->faulted = true;
+        return fail(ex, "device work failed: %s", cudaGetErrorString(q));
+    }
+    if (capacity < p.items.size()) return fail(ex, "completion buffer too small");
+    cudaEventElapsedTime(&ex->last_ms, ex->ev_start, ex->ev_done);
+    ex->last_launches = (uint32_t)p.launches;
+    ex->last_n_sample = p.n_sample;
+    for (size_t i = 0; i < p.items.size(); ++i) {
+        const ribn_b200_batch_item& it = p.items[i];
+        Sequence& s = ex->sequences.find(it.sequence)->second;
+        ribn_b200_completion& out = rows[i];
+        out.sequence = it.sequence;
+        out.prefix = it.prefix + it.token_budget;
+        out.n_tokens = 0;
+        out.token = 0;
+        out.reserved = 0;
+        if (p.sample_row[i] >= 0) {
+            const uint32_t token = ex->h_sampled[p.sample_row[i]];
+            if (token >= (uint32_t)ex->cfg.vocab) {
+                ex->faulted = true;
+                return fail(ex, "Qwen completion does not match submitted work");
+            }
+            out.n_tokens = 1;
+            out.token = token;
+            s.has_next = true;
+        }
+        s.position = out.prefix;
+        s.in_flight = false;
+        if (s.position >= s.prompt_len) std::vector<uint32_t>().swap(s.prompt);
+    }
+    *count = (uint32_t)p.items.size();
+    p.active = false;
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_release(ribn_b200_executor* ex, uint64_t sequence) {
+    if (ex == nullptr) return RIBN_B200_ERROR;
+    auto found = ex->sequences.find(sequence);
+    if (found == ex->sequences.end()) return RIBN_B200_OK;  // idempotent
+    if (found->second.in_flight) return fail(ex, "sequence is referenced by in-flight work");
+    for (int32_t page : found->second.pages) ex->free_pages.push_back(page);
+    ex->free_slots.push_back(found->second.slot);
+    ex->sequences.erase(found);
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_synchronize(ribn_b200_executor* ex) {
+    if (ex == nullptr) return RIBN_B200_ERROR;
+    cudaSetDevice(ex->cfg.device);
+    ex->prepared = false;
+    cudaError_t e = cudaStreamSynchronize(ex->stream);
+    if (e != cudaSuccess) {
+        ex->faulted = true;
+        return fail(ex, "synchronize failed: %s", cudaGetErrorString(e));
+    }
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_copy_logits(ribn_b200_executor* ex, uint32_t row, float* out, size_t capacity) {
+    if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    if (ex->pending.active) return fail(ex, "a submission is still pending");
+    if ((int)row >= ex->last_n_sample) return fail(ex, "no logits for row %u", row);
+    if (capacity < (size_t)ex->cfg.vocab) return fail(ex, "logit buffer too small");
+    cudaSetDevice(ex->cfg.device);
+    CU_TRY(ex, cudaMemcpyAsync(out, ex->logits + (size_t)row * ex->cfg.vocab, (size_t)ex->cfg.vocab * sizeof(float),
+                               cudaMemcpyDeviceToHost, ex->stream));
+    CU_TRY(ex, cudaStreamSynchronize(ex->stream));
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_copy_kv(ribn_b200_executor* ex, uint64_t sequence, int32_t layer, int32_t which, uint32_t tokens,
+                      uint16_t* out) {
+    if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    auto found = ex->sequences.find(sequence);
+    if (found == ex->sequences.end()) return fail(ex, "unknown Qwen sequence");
+    const ribn_b200_config& c = ex->cfg;
+    if (layer < 0 || layer >= c.layers || tokens > (uint32_t)found->second.pages.size() * kPageTokens) {
+        return fail(ex, "copy_kv range is outside the sequence's reservation");
+    }
+    cudaSetDevice(c.device);
+    const int row_elems = c.kv_heads * c.head_dim;
+    __half* tmp = nullptr;
+    CU_TRY(ex, cudaMalloc((void**)&tmp, std::max<size_t>((size_t)tokens * row_elems, 1) * sizeof(__half)));
+    const __half* cache = (which ? ex->cache_v : ex->cache_k) + (long long)layer * ex->layer_stride;
+    cudaError_t e = launch_gather_kv(ex->stream, cache, ex->d_page_tables + (size_t)found->second.slot * ex->pages_per_sequence,
+                                     (int)tokens, row_elems, tmp);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(out, tmp, (size_t)tokens * row_elems * 2, cudaMemcpyDeviceToHost, ex->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ex->stream);
+    cudaFree(tmp);
+    CU_TRY(ex, e);
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_debug_set_context(ribn_b200_executor* ex, uint64_t sequence, uint32_t tokens, uint32_t next_token,
+                                uint64_t seed) {
+    if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    auto found = ex->sequences.find(sequence);
+    if (found == ex->sequences.end()) return fail(ex, "unknown Qwen sequence");
+    Sequence& s = found->second;
+    if (s.in_flight || tokens != s.prompt_len || next_token >= (uint32_t)ex->cfg.vocab) {
+        return fail(ex, "set_context needs an idle sequence, tokens == prompt length and a valid token");
+    }
+    cudaSetDevice(ex->cfg.device);
+    const ribn_b200_config& c = ex->cfg;
+    CU_TRY(ex, launch_synth_kv(ex->stream, ex->cache_k, ex->cache_v, ex->layer_stride, c.layers,
+                               ex->d_page_tables + (size_t)s.slot * ex->pages_per_sequence, (int)tokens,
+                               c.kv_heads * c.head_dim, seed));
+    CU_TRY(ex, cudaMemcpyAsync(ex->d_next_token + s.slot, &next_token, sizeof(uint32_t), cudaMemcpyHostToDevice,
+                               ex->stream));
+    CU_TRY(ex, cudaStreamSynchronize(ex->stream));
+    s.position = tokens;
+    s.has_next = true;
+    std::vector<uint32_t>().swap(s.prompt);
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_last_step_stats(ribn_b200_executor* ex, float* device_ms, uint32_t* kernel_launches) {
+    if (ex == nullptr) return RIBN_B200_ERROR;
+    if (device_ms) *device_ms = ex->last_ms;
+    if (kernel_launches) *kernel_launches = ex->last_launches;
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_step_bytes(ribn_b200_executor* ex, uint64_t context_tokens_total, uint64_t* weight_bytes,
+                         uint64_t* kv_bytes) {
+    if (ex == nullptr) return RIBN_B200_ERROR;
+    const ribn_b200_config& c = ex->cfg;
+    uint64_t w = 0;
+    for (const Tensor& t : ex->layer_tensors) w += t.bytes;
+    w += ex->output_norm.bytes + ex->output.bytes;
+    if (weight_bytes) *weight_bytes = w;
+    if (kv_bytes) *kv_bytes = context_tokens_total * (uint64_t)c.layers * 2ull * c.kv_heads * c.head_dim * 2ull;
+    return RIBN_B200_OK;
+}
+
+}  // extern "C"

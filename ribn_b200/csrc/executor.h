@@ -1,0 +1,101 @@
+// Host-side state of one executor: model plan, paged KV arena, per-sequence
+// continuation, and the single in-flight submission.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/ribn_b200.h"
+#include "gemv.cuh"
+#include "kernels.cuh"
+
+namespace ribn {
+
+struct Tensor {
+    int type = -1;
+    long long rows = 0, cols = 0;
+    size_t bytes = 0;
+    unsigned char* raw = nullptr;  // encoded GGUF bytes, verbatim
+    PackedMatrix packed;           // tile-major repack for the fast kernels (matrices only)
+    bool loaded() const { return raw != nullptr; }
+};
+
+enum LayerTensor {
+    kAttnNorm, kAttnQ, kAttnK, kAttnV, kAttnQNorm, kAttnKNorm, kAttnOutput,
+    kFfnNorm, kFfnGate, kFfnUp, kFfnDown, kLayerTensors
+};
+
+struct Sequence {
+    uint64_t id = 0;
+    int slot = -1;
+    std::vector<uint32_t> prompt;
+    uint32_t prompt_len = 0;
+    uint32_t max_output = 0;
+    uint32_t position = 0;      // committed prefix
+    bool has_next = false;      // a sampled token is pending as the next decode input
+    bool in_flight = false;
+    std::vector<int32_t> pages;
+};
+
+struct Pending {
+    bool active = false;
+    uint64_t id = 0;
+    std::vector<ribn_b200_batch_item> items;
+    std::vector<int> sample_row;  // per item: index into the pinned result slots, or -1
+    int n_sample = 0;
+    int launches = 0;
+};
+
+}  // namespace ribn
+
+struct ribn_b200_executor {
+    ribn_b200_config cfg{};
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev_start = nullptr, ev_done = nullptr;
+    std::string error;
+    bool faulted = false, finalized = false;
+
+    std::vector<ribn::Tensor> layer_tensors;  // [layers][kLayerTensors]
+    ribn::Tensor token_embd, output_norm, output;
+    float* inv_freq = nullptr;  // [head_dim / 2]
+
+    // paged KV arena: [layer][page * 16 + offset][kv_head][head_dim], F16
+    __half* cache_k = nullptr;
+    __half* cache_v = nullptr;
+    long long layer_stride = 0;  // elements per layer
+    int kv_pages = 0, pages_per_sequence = 0;
+    std::vector<int32_t> free_pages;
+    int32_t* d_page_tables = nullptr;  // [max_sequences][pages_per_sequence]
+    uint32_t* d_next_token = nullptr;  // [max_sequences]
+
+    std::unordered_map<uint64_t, ribn::Sequence> sequences;
+    std::vector<int> free_slots;
+
+    // one outstanding preparation, one outstanding submission
+    bool prepared = false;
+    std::vector<ribn_b200_batch_item> prepared_items;
+    ribn::Pending pending;
+    uint64_t next_submission = 1;
+    float last_ms = 0.0f;
+    uint32_t last_launches = 0;
+    int last_n_sample = 0;
+
+    // pinned staging + device step buffers
+    ribn::RowDesc* h_rows = nullptr;
+    uint32_t* h_tokens = nullptr;
+    uint32_t* h_sampled = nullptr;
+    ribn::RowDesc* d_rows = nullptr;
+    uint32_t* d_tokens = nullptr;
+    uint32_t* d_sampled = nullptr;
+    ribn::StepMeta meta{};
+    float *hidden = nullptr, *normed = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr,
+          *gate = nullptr, *up = nullptr, *proj = nullptr, *head_in = nullptr, *logits = nullptr;
+    ribn::StepScratch scratch;
+    std::vector<void*> allocations;
+
+    ribn::Tensor& lt(int layer, int which) { return layer_tensors[(size_t)layer * ribn::kLayerTensors + which]; }
+};

@@ -1,0 +1,104 @@
+// Launchers of every device kernel of the decode / chunked-prefill step.
+// All pointers are device pointers; every launcher enqueues on `stream` and
+// returns the CUDA error of the launch.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ribn {
+
+constexpr int kPageTokens = 16;  // KV_PAGE_TOKENS, crates/qwen/src/gguf.rs:16
+
+// Per-row scheduling record uploaded by the host each step (16 bytes/row).
+struct RowDesc {
+    int32_t slot;          // executor sequence slot (page-table row, next-token row)
+    int32_t prefix;        // tokens already in the cache
+    int32_t tokens;        // tokens this step
+    int32_t token_offset;  // >= 0: offset into the uploaded prompt-token array;
+                           //  < 0: decode row, input is next_token[slot]
+    int32_t sample_row;    // >= 0: index of this row in the sampling list; < 0: no output
+    int32_t pad[3];
+};
+
+struct StepMeta {
+    int32_t* cu_seqlens;    // [rows + 1]
+    int32_t* token_row;     // [T]
+    int32_t* token_pos;     // [T] absolute position in the sequence
+    int32_t* token_slot;    // [T] physical KV token index (page * 16 + offset)
+    uint32_t* token_id;     // [T] input token ids
+    int32_t* token_seq;     // [T] executor sequence slot of the token's row
+    int32_t* sample_token;  // [sampling rows] index into [T] of the row's last token
+    int32_t* sample_slot;   // [sampling rows] sequence slot that receives the sampled token
+};
+
+cudaError_t launch_step_metadata(cudaStream_t stream, const RowDesc* rows, int n_rows, int n_tokens,
+                                 const uint32_t* prompt_tokens, const uint32_t* next_token,
+                                 const int32_t* page_tables, int pages_per_sequence, StepMeta meta);
+
+// Plain metadata (the C-ABI operator): cu_seqlens / row / position / slot only.
+cudaError_t launch_batch_metadata(cudaStream_t stream, const int32_t* row_slot, const int32_t* row_prefix,
+                                  const int32_t* row_tokens, int n_rows, int n_tokens,
+                                  const int32_t* page_tables, int pages_per_sequence, int page_tokens,
+                                  int32_t* cu_seqlens, int32_t* token_row, int32_t* token_pos,
+                                  int32_t* token_slot);
+
+// hidden[t][:] = dequantised row token_id[t] of the raw-layout embedding table.
+cudaError_t launch_embedding(cudaStream_t stream, int type, const unsigned char* table, int hidden,
+                             int vocab, const uint32_t* token_id, int n_tokens, float* out);
+
+// out[rows][cols] = decoded elements of raw-layout encoded rows.
+cudaError_t launch_dequantize(cudaStream_t stream, int type, const unsigned char* bytes, long long rows,
+                              long long cols, float* out);
+
+cudaError_t launch_rms_norm(cudaStream_t stream, const float* x, const float* weight, int members,
+                            int length, float eps, float* out);
+// Gathers rows `index[m]` of x (index == nullptr: identity) before normalising.
+cudaError_t launch_rms_norm_gather(cudaStream_t stream, const float* x, const int32_t* index,
+                                   const float* weight, int members, int length, float eps, float* out);
+
+// Reference GEMV: one warp per output row over raw GGUF blocks.
+// y[m][n] (+)= sum_k deq(W[n][k]) * x[m][k]
+cudaError_t launch_gemv_ref(cudaStream_t stream, int type, const unsigned char* w, long long n, long long k,
+                            const float* x, int members, float* y, bool accumulate);
+
+cudaError_t launch_silu_mul(cudaStream_t stream, const float* gate, const float* up, long long length,
+                            float* out);
+cudaError_t launch_residual_add(cudaStream_t stream, float* acc, const float* inc, long long length);
+// out[m] = argmax of row m; when `slot` is given, next_token[slot[m]] gets it too.
+cudaError_t launch_argmax(cudaStream_t stream, const float* logits, int members, long long length,
+                          uint32_t* out, const int32_t* slot = nullptr, uint32_t* next_token = nullptr);
+cudaError_t launch_f32_to_f16(cudaStream_t stream, const float* in, long long length, uint16_t* out);
+cudaError_t launch_rope_neox(cudaStream_t stream, float* values, const long long* positions, int members,
+                             int heads, int head_dim, int rot_dims, const float* inv_freq);
+
+// Per-head Q/K RMSNorm, NeoX rotary, and the F16 append of K/V into the paged
+// cache, for every token of the step.  q: [T][q_heads][hd] (in place),
+// k, v: [T][kv_heads][hd] (k normalised and rotated in place).
+cudaError_t launch_qk_norm_rope_append(cudaStream_t stream, float* q, float* k, const float* v,
+                                       const float* q_norm, const float* k_norm, const float* inv_freq,
+                                       const int32_t* token_pos, const int32_t* token_slot, int n_tokens,
+                                       int q_heads, int kv_heads, int head_dim, float eps,
+                                       __half* cache_k, __half* cache_v);
+
+// Reference attention: one warp per (token, q head), online softmax over the
+// sequence's pages.  Token t attends keys [max(0, pos - window + 1), pos]
+// (window <= 0: from 0).
+cudaError_t launch_attention_ref(cudaStream_t stream, const float* q, const __half* cache_k,
+                                 const __half* cache_v, const int32_t* page_tables, int pages_per_sequence,
+                                 const int32_t* token_seq, const int32_t* token_pos, int n_tokens,
+                                 int q_heads, int kv_heads, int head_dim, int window, float* out);
+
+// Seeded F16 K/V for the first `tokens` logical positions of one sequence, every layer.
+cudaError_t launch_synth_kv(cudaStream_t stream, __half* cache_k, __half* cache_v, long long layer_stride,
+                            int layers, const int32_t* page_table, int tokens, int row_elems, uint64_t seed);
+// out[token][row_elems] = cache rows of logical tokens [0, tokens) through the page table.
+cudaError_t launch_gather_kv(cudaStream_t stream, const __half* cache, const int32_t* page_table, int tokens,
+                             int row_elems, __half* out);
+
+// Seeded synthetic tensors.
+cudaError_t launch_fill_f32(cudaStream_t stream, float* out, long long n, float value);
+cudaError_t launch_synth_quantized(cudaStream_t stream, int type, unsigned char* out, long long rows,
+                                   long long cols, uint64_t seed, float stddev);
+cudaError_t launch_synth_f16(cudaStream_t stream, __half* out, long long n, uint64_t seed, float stddev);
+
+}  // namespace ribn

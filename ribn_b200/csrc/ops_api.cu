@@ -1,0 +1,254 @@
+// Single-operator C-ABI entry points: host pointers in, host pointers out.
+// Each stages its operands in device memory, runs the same kernels the
+// executor's step uses, and copies the result back.  They exist so that
+// per-primitive parity tests can be written the way the reference's device
+// tests are (crates/nvidia/tests/cuda_reference.rs).
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <string.h>
+
+#include <algorithm>
+#include <thread>
+#include <vector>
+
+#include "../../include/ribn_b200.h"
+#include "blocks.cuh"
+#include "gemv.cuh"
+#include "kernels.cuh"
+
+using namespace ribn;
+
+namespace {
+
+struct Scope {
+    cudaStream_t stream = nullptr;
+    std::vector<void*> owned;
+    bool ok = false;
+    explicit Scope(int device) {
+        int count = 0;
+        if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return;
+        if (cudaSetDevice(device) != cudaSuccess) return;
+        ok = cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) == cudaSuccess;
+    }
+    ~Scope() {
+        if (stream) {
+            cudaStreamSynchronize(stream);
+            cudaStreamDestroy(stream);
+        }
+        for (void* p : owned) cudaFree(p);
+    }
+    template <typename T>
+    T* alloc(size_t count) {
+        void* p = nullptr;
+        if (cudaMalloc(&p, std::max<size_t>(count, 1) * sizeof(T)) != cudaSuccess) return nullptr;
+        owned.push_back(p);
+        return (T*)p;
+    }
+    template <typename T>
+    T* upload(const T* host, size_t count) {
+        T* d = alloc<T>(count);
+        if (d && count && cudaMemcpyAsync(d, host, count * sizeof(T), cudaMemcpyHostToDevice, stream) != cudaSuccess) {
+            return nullptr;
+        }
+        return d;
+    }
+    template <typename T>
+    bool download(T* host, const T* dev, size_t count) {
+        if (count && cudaMemcpyAsync(host, dev, count * sizeof(T), cudaMemcpyDeviceToHost, stream) != cudaSuccess) {
+            return false;
+        }
+        return cudaStreamSynchronize(stream) == cudaSuccess;
+    }
+};
+
+#define OP_TRY(expr) do { if ((expr) != cudaSuccess) return RIBN_B200_ERROR; } while (0)
+#define OP_PTR(p) do { if ((p) == nullptr) return RIBN_B200_ERROR; } while (0)
+
+size_t encoded_bytes(int type, long long rows, long long cols) {
+    const int e = block_elems(type);
+    if (e == 0 || cols % e != 0) return 0;
+    return (size_t)rows * (size_t)(cols / e) * (size_t)block_bytes(type);
+}
+
+}  // namespace
+
+extern "C" {
+
+int ribn_b200_debug_repack(int32_t type, const void* raw, int64_t rows, int64_t cols, void* out, size_t capacity,
+                           size_t* byte_count) {
+    if (!packable(type, rows, cols) || raw == nullptr) return RIBN_B200_ERROR;
+    const size_t need = packed_bytes(type, rows, cols);
+    if (byte_count) *byte_count = need;
+    if (out == nullptr) return RIBN_B200_OK;
+    if (capacity < need) return RIBN_B200_ERROR;
+    repack_host(type, (const unsigned char*)raw, rows, cols, (unsigned char*)out, 1);
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_op_dequantize(int32_t device, int32_t type, const void* bytes, int64_t rows, int64_t cols, float* out) {
+    const size_t n = encoded_bytes(type, rows, cols);
+    if (n == 0 || bytes == nullptr || out == nullptr) return RIBN_B200_ERROR;
+    Scope s(device);
+    if (!s.ok) return RIBN_B200_ERROR;
+    unsigned char* d_in = s.upload((const unsigned char*)bytes, n);
+    float* d_out = s.alloc<float>((size_t)rows * cols);
+    OP_PTR(d_in); OP_PTR(d_out);
+    OP_TRY(launch_dequantize(s.stream, type, d_in, rows, cols, d_out));
+    return s.download(out, d_out, (size_t)rows * cols) ? RIBN_B200_OK : RIBN_B200_ERROR;
+}
+
+int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t rows, int64_t cols, const float* x,
+                      int32_t members, float* y, int32_t variant) {
+    const size_t n = encoded_bytes(type, rows, cols);
+    if (n == 0 || weights == nullptr || x == nullptr || y == nullptr || members <= 0) return RIBN_B200_ERROR;
+    Scope s(device);
+    if (!s.ok) return RIBN_B200_ERROR;
+    float* d_x = s.upload(x, (size_t)members * cols);
+    float* d_y = s.alloc<float>((size_t)members * rows);
+    OP_PTR(d_x); OP_PTR(d_y);
+    if (variant == 1) {
+        unsigned char* d_w = s.upload((const unsigned char*)weights, n);
+        OP_PTR(d_w);
+        OP_TRY(launch_gemv_ref(s.stream, type, d_w, rows, cols, d_x, members, d_y, false));
+    } else {
+        if (!packable(type, rows, cols)) return RIBN_B200_ERROR;
+        std::vector<unsigned char> packed(packed_bytes(type, rows, cols));
+        repack_host(type, (const unsigned char*)weights, rows, cols, packed.data(),
+                    (int)std::max(1u, std::min(16u, std::thread::hardware_concurrency())));
+        unsigned char* d_w = s.upload(packed.data(), packed.size());
+        OP_PTR(d_w);
+        for (int m0 = 0; m0 < members; m0 += kGemvMaxMembers) {
+            GemvArgs a{};
+            a.n_segments = 1;
+            a.seg[0] = GemvSegment{d_w, type, (int)rows, (int)((rows + kTileRows - 1) / kTileRows),
+                                   d_y + (size_t)m0 * rows};
+            a.k = (int)cols;
+            a.members = std::min(kGemvMaxMembers, members - m0);
+            a.x = d_x + (size_t)m0 * cols;
+            a.norm_weight = nullptr;
+            a.eps = 0.0f;
+            a.epilogue = kStore;
+            OP_TRY(launch_gemv_mma(s.stream, a, false));
+        }
+    }
+    return s.download(y, d_y, (size_t)members * rows) ? RIBN_B200_OK : RIBN_B200_ERROR;
+}
+
+int ribn_b200_op_rms_norm(int32_t device, const float* x, const float* weight, int32_t members, int32_t length,
+                          float eps, float* out) {
+    Scope s(device);
+    if (!s.ok || members <= 0 || length <= 0) return RIBN_B200_ERROR;
+    float* d_x = s.upload(x, (size_t)members * length);
+    float* d_w = s.upload(weight, (size_t)length);
+    float* d_o = s.alloc<float>((size_t)members * length);
+    OP_PTR(d_x); OP_PTR(d_w); OP_PTR(d_o);
+    OP_TRY(launch_rms_norm(s.stream, d_x, d_w, members, length, eps, d_o));
+    return s.download(out, d_o, (size_t)members * length) ? RIBN_B200_OK : RIBN_B200_ERROR;
+}
+
+int ribn_b200_op_silu_mul(int32_t device, const float* gate, const float* up, int64_t length, float* out) {
+    Scope s(device);
+    if (!s.ok || length <= 0) return RIBN_B200_ERROR;
+    float* d_g = s.upload(gate, (size_t)length);
+    float* d_u = s.upload(up, (size_t)length);
+    float* d_o = s.alloc<float>((size_t)length);
+    OP_PTR(d_g); OP_PTR(d_u); OP_PTR(d_o);
+    OP_TRY(launch_silu_mul(s.stream, d_g, d_u, length, d_o));
+    return s.download(out, d_o, (size_t)length) ? RIBN_B200_OK : RIBN_B200_ERROR;
+}
+
+int ribn_b200_op_argmax(int32_t device, const float* logits, int32_t members, int64_t length, uint32_t* out) {
+    Scope s(device);
+    if (!s.ok || members <= 0 || length <= 0) return RIBN_B200_ERROR;
+    float* d_l = s.upload(logits, (size_t)members * length);
+    uint32_t* d_o = s.alloc<uint32_t>((size_t)members);
+    OP_PTR(d_l); OP_PTR(d_o);
+    OP_TRY(launch_argmax(s.stream, d_l, members, length, d_o));
+    return s.download(out, d_o, (size_t)members) ? RIBN_B200_OK : RIBN_B200_ERROR;
+}
+
+int ribn_b200_op_rope_neox(int32_t device, float* values, const int64_t* positions, int32_t members, int32_t heads,
+                           int32_t head_dim, int32_t rot_dims, float base) {
+    Scope s(device);
+    if (!s.ok || members <= 0 || rot_dims <= 0 || rot_dims > head_dim || (rot_dims & 1)) return RIBN_B200_ERROR;
+    const size_t n = (size_t)members * heads * head_dim;
+    std::vector<float> table((size_t)rot_dims / 2);
+    for (int p = 0; p < rot_dims / 2; ++p) table[p] = powf(base, -(2.0f * (float)p) / (float)rot_dims);
+    std::vector<long long> pos(positions, positions + members);
+    float* d_v = s.upload(values, n);
+    float* d_t = s.upload(table.data(), table.size());
+    long long* d_p = s.upload(pos.data(), pos.size());
+    OP_PTR(d_v); OP_PTR(d_t); OP_PTR(d_p);
+    OP_TRY(launch_rope_neox(s.stream, d_v, d_p, members, heads, head_dim, rot_dims, d_t));
+    return s.download(values, d_v, n) ? RIBN_B200_OK : RIBN_B200_ERROR;
+}
+
+int ribn_b200_op_f32_to_f16(int32_t device, const float* in, int64_t length, uint16_t* out) {
+    Scope s(device);
+    if (!s.ok || length <= 0) return RIBN_B200_ERROR;
+    float* d_i = s.upload(in, (size_t)length);
+    uint16_t* d_o = s.alloc<uint16_t>((size_t)length);
+    OP_PTR(d_i); OP_PTR(d_o);
+    OP_TRY(launch_f32_to_f16(s.stream, d_i, length, d_o));
+    return s.download(out, d_o, (size_t)length) ? RIBN_B200_OK : RIBN_B200_ERROR;
+}
+
+int ribn_b200_op_attention(int32_t device, const float* q, const uint16_t* keys, const uint16_t* values,
+                           const int32_t* page_table, int32_t page_tokens, int32_t physical_tokens, int32_t tokens,
+                           int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t window,
+                           float* out, int32_t variant) {
+    Scope s(device);
+    if (!s.ok || rows <= 0 || tokens < rows || page_tokens != kPageTokens || q_heads % kv_heads != 0) {
+        return RIBN_B200_ERROR;
+    }
+    const int pages = (tokens + page_tokens - 1) / page_tokens;
+    const size_t kv_elems = (size_t)physical_tokens * kv_heads * head_dim;
+    float* d_q = s.upload(q, (size_t)rows * q_heads * head_dim);
+    __half* d_k = (__half*)s.upload(keys, kv_elems);
+    __half* d_v = (__half*)s.upload(values, kv_elems);
+    int32_t* d_table = s.upload(page_table, (size_t)pages);
+    std::vector<int32_t> seq(rows, 0), pos(rows);
+    for (int r = 0; r < rows; ++r) pos[r] = tokens - rows + r;  // row r attends tokens - rows + 1 + r keys
+    int32_t* d_seq = s.upload(seq.data(), seq.size());
+    int32_t* d_pos = s.upload(pos.data(), pos.size());
+    float* d_o = s.alloc<float>((size_t)rows * q_heads * head_dim);
+    OP_PTR(d_q); OP_PTR(d_k); OP_PTR(d_v); OP_PTR(d_table); OP_PTR(d_seq); OP_PTR(d_pos); OP_PTR(d_o);
+    (void)variant;
+    OP_TRY(launch_attention_ref(s.stream, d_q, d_k, d_v, d_table, pages, d_seq, d_pos, rows, q_heads, kv_heads,
+                                head_dim, window, d_o));
+    return s.download(out, d_o, (size_t)rows * q_heads * head_dim) ? RIBN_B200_OK : RIBN_B200_ERROR;
+}
+
+int ribn_b200_op_batch_metadata(int32_t device, const int32_t* row_slot, const int32_t* row_prefix,
+                                const int32_t* row_tokens, int32_t rows, const int32_t* page_tables,
+                                int32_t pages_per_sequence, int32_t page_tokens, int32_t* cu_seqlens,
+                                int32_t* token_row, int32_t* token_position, int32_t* token_kv_slot) {
+    Scope s(device);
+    if (!s.ok || rows <= 0 || page_tokens <= 0) return RIBN_B200_ERROR;
+    int total = 0, max_slot = 0;
+    for (int r = 0; r < rows; ++r) {
+        if (row_tokens[r] < 0 || row_slot[r] < 0) return RIBN_B200_ERROR;
+        total += row_tokens[r];
+        max_slot = std::max(max_slot, row_slot[r]);
+    }
+    int32_t* d_slot = s.upload(row_slot, (size_t)rows);
+    int32_t* d_prefix = s.upload(row_prefix, (size_t)rows);
+    int32_t* d_tokens = s.upload(row_tokens, (size_t)rows);
+    int32_t* d_tables = s.upload(page_tables, (size_t)(max_slot + 1) * pages_per_sequence);
+    int32_t* d_cu = s.alloc<int32_t>((size_t)rows + 1);
+    int32_t* d_row = s.alloc<int32_t>((size_t)total);
+    int32_t* d_pos = s.alloc<int32_t>((size_t)total);
+    int32_t* d_kv = s.alloc<int32_t>((size_t)total);
+    OP_PTR(d_slot); OP_PTR(d_prefix); OP_PTR(d_tokens); OP_PTR(d_tables); OP_PTR(d_cu); OP_PTR(d_row); OP_PTR(d_pos);
+    OP_PTR(d_kv);
+    OP_TRY(launch_batch_metadata(s.stream, d_slot, d_prefix, d_tokens, rows, total, d_tables, pages_per_sequence,
+                                 page_tokens, d_cu, d_row, d_pos, d_kv));
+    bool ok = s.download(cu_seqlens, d_cu, (size_t)rows + 1);
+    ok = ok && s.download(token_row, d_row, (size_t)total);
+    ok = ok && s.download(token_position, d_pos, (size_t)total);
+    ok = ok && s.download(token_kv_slot, d_kv, (size_t)total);
+    return ok ? RIBN_B200_OK : RIBN_B200_ERROR;
+}
+
+}  // extern "C"

@@ -1,0 +1,115 @@
+"""Single operators through the C ABI (host arrays in, host arrays out).
+Mirrors the operator wrappers of the reference's ``CudaQuantizedGemv`` /
+``CudaQwen35Ops`` (crates/nvidia/src/quantized.rs, crates/nvidia/src/model_ops.rs)
+so per-primitive parity tests read like the reference's device tests."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from ._lib import OK, lib
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _check(rc: int, what: str):
+    if rc != OK:
+        raise RuntimeError(f"ribn_b200 {what} failed (is a B200 visible? there is no CPU path)")
+
+
+def dequantize(ggml_type: int, encoded, rows: int, cols: int, device: int = 0) -> np.ndarray:
+    enc = np.ascontiguousarray(np.frombuffer(bytes(encoded), dtype=np.uint8) if not isinstance(encoded, np.ndarray)
+                               else encoded.view(np.uint8).reshape(-1))
+    out = np.empty((rows, cols), dtype=np.float32)
+    _check(lib().ribn_b200_op_dequantize(device, ggml_type, _p(enc), rows, cols, _p(out)), "dequantize")
+    return out
+
+
+def gemv(ggml_type: int, weights, rows: int, cols: int, x, variant: int = 0, device: int = 0) -> np.ndarray:
+    w = np.ascontiguousarray(weights).view(np.uint8).reshape(-1)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    members = 1 if x.ndim == 1 else x.shape[0]
+    y = np.empty((members, rows), dtype=np.float32)
+    _check(lib().ribn_b200_op_gemv(device, ggml_type, _p(w), rows, cols, _p(x), members, _p(y), variant), "gemv")
+    return y[0] if x.ndim == 1 else y
+
+
+def rms_norm(x, weight, eps: float, device: int = 0) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = np.ascontiguousarray(weight, dtype=np.float32)
+    members = 1 if x.ndim == 1 else x.shape[0]
+    out = np.empty_like(x)
+    _check(lib().ribn_b200_op_rms_norm(device, _p(x), _p(w), members, x.shape[-1], eps, _p(out)), "rms_norm")
+    return out
+
+
+def silu_mul(gate, up, device: int = 0) -> np.ndarray:
+    g = np.ascontiguousarray(gate, dtype=np.float32)
+    u = np.ascontiguousarray(up, dtype=np.float32)
+    out = np.empty_like(g)
+    _check(lib().ribn_b200_op_silu_mul(device, _p(g), _p(u), g.size, _p(out)), "silu_mul")
+    return out
+
+
+def argmax(logits, device: int = 0):
+    l = np.ascontiguousarray(logits, dtype=np.float32)
+    members = 1 if l.ndim == 1 else l.shape[0]
+    out = np.empty(members, dtype=np.uint32)
+    _check(lib().ribn_b200_op_argmax(device, _p(l), members, l.shape[-1], _p(out)), "argmax")
+    return int(out[0]) if l.ndim == 1 else out
+
+
+def rope_neox(values, positions, heads: int, head_dim: int, rot_dims: int, base: float, device: int = 0) -> np.ndarray:
+    v = np.ascontiguousarray(values, dtype=np.float32).copy()
+    pos = np.ascontiguousarray(np.atleast_1d(positions), dtype=np.int64)
+    _check(lib().ribn_b200_op_rope_neox(device, _p(v), _p(pos), pos.size, heads, head_dim, rot_dims, base), "rope")
+    return v
+
+
+def f32_to_f16_bits(values, device: int = 0) -> np.ndarray:
+    v = np.ascontiguousarray(values, dtype=np.float32)
+    out = np.empty(v.shape, dtype=np.uint16)
+    _check(lib().ribn_b200_op_f32_to_f16(device, _p(v), v.size, _p(out)), "f32_to_f16")
+    return out
+
+
+def attention(q, keys_f16, values_f16, page_table, tokens: int, rows: int, q_heads: int, kv_heads: int,
+              head_dim: int, window: int = 0, variant: int = 0, device: int = 0) -> np.ndarray:
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    k = np.ascontiguousarray(keys_f16, dtype=np.uint16)
+    v = np.ascontiguousarray(values_f16, dtype=np.uint16)
+    table = np.ascontiguousarray(page_table, dtype=np.int32)
+    physical = k.size // (kv_heads * head_dim)
+    out = np.empty((rows, q_heads * head_dim), dtype=np.float32)
+    _check(lib().ribn_b200_op_attention(device, _p(q), _p(k), _p(v), _p(table), 16, physical, tokens, rows, q_heads,
+                                        kv_heads, head_dim, window, _p(out), variant), "attention")
+    return out
+
+
+def batch_metadata(row_slot, row_prefix, row_tokens, page_tables, page_tokens: int = 16, device: int = 0):
+    slot = np.ascontiguousarray(row_slot, dtype=np.int32)
+    prefix = np.ascontiguousarray(row_prefix, dtype=np.int32)
+    tokens = np.ascontiguousarray(row_tokens, dtype=np.int32)
+    tables = np.ascontiguousarray(page_tables, dtype=np.int32)
+    total = int(tokens.sum())
+    cu = np.empty(slot.size + 1, dtype=np.int32)
+    row = np.empty(total, dtype=np.int32)
+    pos = np.empty(total, dtype=np.int32)
+    kv = np.empty(total, dtype=np.int32)
+    _check(lib().ribn_b200_op_batch_metadata(device, _p(slot), _p(prefix), _p(tokens), slot.size, _p(tables),
+                                             tables.shape[1], page_tokens, _p(cu), _p(row), _p(pos), _p(kv)),
+           "batch_metadata")
+    return cu, row, pos, kv
+
+
+def repack(ggml_type: int, raw, rows: int, cols: int) -> np.ndarray:
+    """Host-side tile-major repack (no device needed)."""
+    raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+    need = C.c_size_t(0)
+    _check(lib().ribn_b200_debug_repack(ggml_type, _p(raw), rows, cols, None, 0, C.byref(need)), "repack size")
+    out = np.empty(need.value, dtype=np.uint8)
+    _check(lib().ribn_b200_debug_repack(ggml_type, _p(raw), rows, cols, _p(out), out.size, C.byref(need)), "repack")
+    return out
