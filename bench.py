@@ -1,0 +1,338 @@
+#!/usr/bin/env python
+"""Decode benchmark: Qwen3-8B-architecture, Q4_K_M-style GGUF weights, paged F16 KV.
+
+One "step" is one decode step of the whole batch through the executor's public
+protocol (prepare -> submit -> poll).  Metric: decode tok/s per GPU at batch 1
+(`value`) and batch 64 (`batch64`), with the step's fraction of the HBM
+roofline (bytes of quantised weights + KV read per step over measured HBM
+bandwidth).  Weights are seeded N(0, 0.02) quantised on the device; token ids
+and cached K/V are seeded synthetic; every step streams 4.9 GB of weights, far
+beyond L2, so no explicit L2 flush is needed between steps.
+
+`--impl reference` times the reference's host CPU decoder (restated in
+oracle/oracle.c; the Rust original cannot be built here) on the same weights.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODELS = {
+    "qwen3-8b": dict(layers=36, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, ffn=12288, vocab=151936,
+                     rope_base=1.0e6, rms_eps=1.0e-6),
+    "qwen3-0.6b": dict(layers=28, hidden=1024, q_heads=16, kv_heads=8, head_dim=128, ffn=3072, vocab=151936,
+                       rope_base=1.0e6, rms_eps=1.0e-6),
+    "tiny": dict(layers=2, hidden=512, q_heads=8, kv_heads=2, head_dim=128, ffn=1024, vocab=2048,
+                 rope_base=1.0e6, rms_eps=1.0e-6),
+}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6 and parts[0].isdigit():
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": statistics.median(int(s[0]) for s in self.samples), "sm_max_mhz": int(self.samples[0][1]),
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return rank, world, local, dist
+    return rank, world, local, None
+
+
+def all_max(dist, value: float, device: int) -> float:
+    if dist is None:
+        return value
+    import torch
+    t = torch.tensor([value], dtype=torch.float64, device=f"cuda:{device}")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(dist, device: int):
+    if dist is not None:
+        import torch
+        dist.barrier()
+        torch.cuda.synchronize(device)
+
+
+def build_executor(model: dict, batch: int, context: int, decode_tokens: int, device: int, keep_logits: bool):
+    import ribn_b200
+    span = context + decode_tokens + 16
+    ex = ribn_b200.QwenB200(model, context_tokens=span, max_sequences=batch, max_batch_tokens=max(batch, 16),
+                            device=device, flags=ribn_b200.FLAG_KEEP_LOGITS if keep_logits else 0)
+    ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q4_K_M)
+    return ex
+
+
+def seed_sequences(ex, model: dict, batch: int, context: int, decode_tokens: int, seed: int):
+    rng = np.random.default_rng(seed)
+    for s in range(batch):
+        prompt = rng.integers(0, model["vocab"], size=context, dtype=np.uint32)
+        adm = ex.admit(s + 1, s + 1, prompt, decode_tokens + 8)
+        if not adm.ready:
+            raise RuntimeError(f"admission failed: {adm}")
+        ex.debug_set_context(s + 1, context, int(rng.integers(0, model["vocab"])), seed=seed * 1000 + s)
+
+
+def decode_steps(ex, sequences, positions, steps: int):
+    """Runs `steps` decode steps over `sequences`; returns (wall seconds, [device ms], launches)."""
+    from ribn_b200 import BatchItem, StepKind
+    device_ms, launches = [], 0
+    ex.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        items = [BatchItem(s, StepKind.DECODE, positions[s], 1, 1) for s in sequences]
+        ex.prepare(items)
+        done = ex.wait(ex.submit(items))          # H2D of the row records and D2H of the sampled tokens inside
+        for row in done:
+            positions[row.sequence] = row.prefix
+        ms, n = ex.last_step_stats()
+        device_ms.append(ms)
+        launches += n
+    ex.synchronize()
+    return time.perf_counter() - t0, device_ms, launches
+
+
+def oracle_for(ex, model: dict, context_capacity: int):
+    from oracle import binding as orc
+    tensors = {name: ex.read_tensor(name) for name in ex.tensor_names()}
+    cfg = dict(model, context=context_capacity, eps=model["rms_eps"])
+    cfg.pop("rms_eps")
+    return orc, orc.Qwen3Oracle(cfg, tensors)
+
+
+def oracle_sequence(orc, oracle, ex, model, sequence: int, context: int):
+    seq = oracle.new_sequence()
+    row = model["kv_heads"] * model["head_dim"]
+    keys = np.empty((model["layers"], context * row), dtype=np.uint16)
+    values = np.empty_like(keys)
+    for l in range(model["layers"]):
+        keys[l] = ex.copy_kv(sequence, l, 0, context)
+        values[l] = ex.copy_kv(sequence, l, 1, context)
+    seq.fill(keys, values, context)
+    return seq
+
+
+def run_ours(args):
+    rank, world, local, dist = dist_setup(args.gpus)
+    import ribn_b200
+    model = MODELS[args.model]
+    B = args.batch
+    total_steps = args.steps + args.warmup + 2
+    ex = build_executor(model, B, args.context, 2 * total_steps + 4, local, keep_logits=True)
+    ex.finalize()
+    seed_sequences(ex, model, B, args.context, 2 * total_steps + 4, seed=1 + rank)
+    positions = {s + 1: args.context for s in range(B)}
+    hbm_gbs, peak_kind = measured_peaks()
+
+    # ---- CPU baseline + full-size parity on rank 0, one GPU only --------------------------
+    cpu = None
+    parity = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        orc, oracle = oracle_for(ex, model, args.context + 8)
+        cores = os.cpu_count() or 1
+        orc.set_threads(cores)
+        seq = oracle_sequence(orc, oracle, ex, model, 1, args.context)
+        from ribn_b200 import BatchItem, StepKind
+        # the device's pending input token for sequence 1 is reproduced from the seeding rule
+        rng = np.random.default_rng(1 + rank)
+        rng.integers(0, model["vocab"], size=args.context, dtype=np.uint32)
+        token = int(rng.integers(0, model["vocab"]))
+        item = BatchItem(1, StepKind.DECODE, positions[1], 1, 1)
+        ex.prepare([item])
+        done = ex.wait(ex.submit([item]))
+        positions[1] = done[0].prefix
+        got = ex.copy_logits(0)
+        t0 = time.perf_counter()
+        want = seq.step(token)
+        cpu_s = time.perf_counter() - t0
+        err = np.abs(got - want)
+        parity = {"max_abs_logit_diff": float(err.max()), "argmax_equal": bool(orc.argmax(want) == done[0].tokens[0]),
+                  "tolerance": "max-abs 2e-2 / rel 1e-2"}
+        cpu = {"value": 1.0 / cpu_s, "unit": "tok/s", "cores": cores, "kind": "port",
+               "sample": f"1 decode token at batch 1, context {args.context}, {args.model} Q4_K_M-style, "
+                         f"oracle/oracle.c with OpenMP over output rows"}
+        seq.close(); oracle.close()
+
+    def phase(sequences):
+        decode_steps(ex, sequences, positions, args.warmup)
+        barrier(dist, local)
+        with ClockSampler(local) as clocks:
+            wall, device_ms, launches = decode_steps(ex, sequences, positions, args.steps)
+        barrier(dist, local)
+        wall = all_max(dist, wall, local)
+        dev = all_max(dist, sum(device_ms) / 1e3, local)
+        return wall, dev, launches, clocks.summary()
+
+    def roofline(batch_rows, dev_seconds):
+        ctx_avg = args.context + args.warmup + args.steps / 2.0
+        w_bytes, kv_bytes = ex.step_bytes(int(batch_rows * ctx_avg))
+        per_step = w_bytes + kv_bytes
+        achieved = per_step / (dev_seconds / args.steps) / 1e9
+        return {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
+                "traffic": None, "of": peak_kind, "kernel": "whole decode step (every kernel of the step)",
+                "algorithmic_bytes_per_step": per_step, "weight_bytes": w_bytes, "kv_bytes": kv_bytes}
+
+    # ---- batch 1 -----------------------------------------------------------------------
+    wall1, dev1, launches1, clocks1 = phase([1])
+    value1 = world * 1 * args.steps / dev1
+    e2e1 = world * 1 * args.steps / wall1
+    out = {
+        "metric": f"{args.model} Q4_K_M decode tok/s at batch 1 (per GPU x replicas)", "value": value1,
+        "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dev1 / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 activations / f16 tensor-core operands over Q4_K,Q6_K weights, f16 KV",
+        "data": "synthetic",
+        "config": {"workload": f"{args.model} Q4_K_M-style decode, batch 1 and {B}, context {args.context}, "
+                               f"16-token KV pages, one replica per GPU",
+                   "l2": "inputs larger than L2 (4.9 GB of weights streamed per step)",
+                   "parallelism": f"replicas x{world}"},
+        "e2e": {"value": e2e1, "unit": "tok/s", "h2d_bytes_per_step": 32, "d2h_bytes_per_step": 4},
+        "gpu_launches": launches1, "roofline": roofline(1, dev1), "clocks": clocks1,
+    }
+    if cpu:
+        out["cpu_baseline"] = cpu
+        out["parity"] = parity
+    # ---- batch B -------------------------------------------------------------------------
+    if B > 1:
+        wallb, devb, launchesb, clocksb = phase(list(range(1, B + 1)))
+        out["batch64"] = {"batch": B, "value": world * B * args.steps / devb, "unit": "tok/s",
+                          "ms_per_step": devb / args.steps * 1e3,
+                          "e2e": {"value": world * B * args.steps / wallb, "unit": "tok/s",
+                                  "h2d_bytes_per_step": 32 * B, "d2h_bytes_per_step": 4 * B},
+                          "gpu_launches": launchesb, "roofline": roofline(B, devb), "clocks": clocksb,
+                          "x_batch1": (world * B * args.steps / devb) / value1}
+    ex.close()
+    if rank == 0:
+        print(json.dumps(out))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    """The reference's host CPU decoder (restated: oracle/oracle.c) on the GPU box's host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    model = MODELS[args.model]
+    cores = os.cpu_count() or 1
+    # The synthetic checkpoint comes from the library's device generator (not timed).
+    ex = build_executor(model, 1, args.context, 8, 0, keep_logits=False)
+    ex.finalize()
+    seed_sequences(ex, model, 1, args.context, 8, seed=1)
+    orc, oracle = oracle_for(ex, model, args.context + args.steps + args.warmup + 8)
+    orc.set_threads(cores)
+    seq = oracle_sequence(orc, oracle, ex, model, 1, args.context)
+    ex.close()
+    token = 1
+    budget, t_start = 240.0, time.perf_counter()
+    for _ in range(args.warmup):
+        token = orc.argmax(seq.step(token))
+        if time.perf_counter() - t_start > budget / 3:
+            break
+    times = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        token = orc.argmax(seq.step(token))
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_start > budget:
+            break
+    total = sum(times)
+    value = len(times) / total
+    sample = (f"{len(times)} decode tokens at batch 1, context {args.context}, {args.model} Q4_K_M-style, "
+              f"oracle/oracle.c (restated host decoder), OpenMP over output rows")
+    print(json.dumps({
+        "impl": "reference", "metric": f"{args.model} Q4_K_M decode tok/s at batch 1 (per GPU x replicas)",
+        "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup,
+        "ms_per_step": total / len(times) * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.model} Q4_K_M-style decode, batch 1, context {args.context}"},
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="qwen3-8b", choices=sorted(MODELS))
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--context", type=int, default=1024)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / full-size parity leg")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

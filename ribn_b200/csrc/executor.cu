@@ -135,6 +135,7 @@ int pages_for(uint32_t tokens) { return (int)((tokens + kPageTokens - 1) / kPage
 // ---------------------------------------------------------------------------
 struct StepPlan {
     int n_rows = 0, n_tokens = 0, n_sample = 0, n_prompt_tokens = 0;
+    int max_keys = 0;  // longest prefix + tokens of any row
 };
 
 #define STEP_TRY(expr)                          \
@@ -215,9 +216,17 @@ cudaError_t run_step(ribn_b200_executor* ex, const StepPlan& plan, int& launches
                                             (const float*)t[kAttnKNorm].raw, ex->inv_freq, ex->meta.token_pos,
                                             ex->meta.token_slot, T, c.q_heads, c.kv_heads, c.head_dim, c.rms_eps,
                                             ck, cv));
-        STEP_TRY(launch_attention_ref(s, ex->q, ck, cv, ex->d_page_tables, ex->pages_per_sequence,
-                                      ex->meta.token_seq, ex->meta.token_pos, T, c.q_heads, c.kv_heads, c.head_dim,
-                                      0, ex->attn));
+        if (c.flags & RIBN_B200_FLAG_REFERENCE_KERNELS) {
+            STEP_TRY(launch_attention_ref(s, ex->q, ck, cv, ex->d_page_tables, ex->pages_per_sequence,
+                                          ex->meta.token_seq, ex->meta.token_pos, T, c.q_heads, c.kv_heads,
+                                          c.head_dim, 0, ex->attn));
+        } else {
+            cudaError_t e = launch_attention(s, ex->q, ck, cv, ex->d_page_tables, ex->pages_per_sequence,
+                                             ex->meta.token_seq, ex->meta.token_pos, T, c.q_heads, c.kv_heads,
+                                             c.head_dim, 0, plan.max_keys, ex->scratch.attn_partial,
+                                             ex->scratch.attn_partial_bytes, ex->attn, &launches);
+            if (e != cudaSuccess) return e;
+        }
         {
             float* outs[1] = {ex->hidden};
             cudaError_t e = project(ex, launches, &t[kAttnOutput], 1, ex->attn, nullptr, nullptr, T, outs, kResidual);
@@ -524,6 +533,14 @@ int ribn_b200_finalize(ribn_b200_executor* ex) {
     CU_TRY(ex, dev_alloc(ex, &ex->up, T * c.ffn));
     CU_TRY(ex, dev_alloc(ex, &ex->head_in, S * c.hidden));
     CU_TRY(ex, dev_alloc(ex, &ex->logits, S * c.vocab));
+    {
+        // Span accumulators: enough for every token of a full batch when that is small, capped at 256 MiB
+        // (longer batches run the attention in several launches).
+        const size_t spans = ((size_t)c.context_tokens + kAttnSpanKeys - 1) / kAttnSpanKeys;
+        const size_t per_token = (size_t)c.q_heads * spans * (c.head_dim + 2) * sizeof(float);
+        ex->scratch.attn_partial_bytes = std::max(per_token, std::min(per_token * T, (size_t)256 << 20));
+        CU_TRY(ex, dev_alloc(ex, (unsigned char**)&ex->scratch.attn_partial, ex->scratch.attn_partial_bytes));
+    }
     CU_TRY(ex, cudaStreamSynchronize(ex->stream));
     ex->finalized = true;
     return RIBN_B200_OK;
@@ -674,6 +691,7 @@ int ribn_b200_submit(ribn_b200_executor* ex, const ribn_b200_batch_item* items, 
         p.sample_row[i] = r.sample_row;
         r.pad[0] = r.pad[1] = r.pad[2] = 0;
         plan.n_tokens += (int)it.token_budget;
+        plan.max_keys = std::max(plan.max_keys, (int)(it.prefix + it.token_budget));
     }
     p.n_sample = plan.n_sample;
     // Mark ownership before the first launch: if anything below fails the

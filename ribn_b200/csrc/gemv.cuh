@@ -83,10 +83,10 @@ cudaError_t launch_gemv_mma(cudaStream_t stream, const GemvArgs& args, bool depe
 
 constexpr int kGemvMaxMembers = 4;
 
-// Scratch shared by the step kernels (split-KV attention partials).
+// Scratch shared by the step kernels: per-span attention accumulators.
 struct StepScratch {
-    float* attn_partial = nullptr;  // [tokens][q_heads][splits][head_dim + 2]
-    int attn_splits = 0;
+    float* attn_partial = nullptr;
+    size_t attn_partial_bytes = 0;
 };
 
 }  // namespace ribn

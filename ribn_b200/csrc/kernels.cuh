@@ -2,6 +2,7 @@
 // All pointers are device pointers; every launcher enqueues on `stream` and
 // returns the CUDA error of the launch.
 #pragma once
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -87,6 +88,19 @@ cudaError_t launch_attention_ref(cudaStream_t stream, const float* q, const __ha
                                  const __half* cache_v, const int32_t* page_tables, int pages_per_sequence,
                                  const int32_t* token_seq, const int32_t* token_pos, int n_tokens,
                                  int q_heads, int kv_heads, int head_dim, int window, float* out);
+
+// Split-KV attention: fixed spans of kAttnSpanKeys keys per CTA, merged in span
+// order.  `max_keys` bounds the longest key range of any token in the launch
+// (it sizes the grid only; results do not depend on it).  `partial` is scratch
+// of `partial_bytes` for the per-span accumulators; tokens are processed in
+// as many launches as that scratch requires.  `launches` (optional) is
+// incremented per kernel launch.
+constexpr int kAttnSpanKeys = 64;
+cudaError_t launch_attention(cudaStream_t stream, const float* q, const __half* cache_k, const __half* cache_v,
+                             const int32_t* page_tables, int pages_per_sequence, const int32_t* token_seq,
+                             const int32_t* token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,
+                             int window, int max_keys, float* partial, size_t partial_bytes, float* out,
+                             int* launches);
 
 // Seeded F16 K/V for the first `tokens` logical positions of one sequence, every layer.
 cudaError_t launch_synth_kv(cudaStream_t stream, __half* cache_k, __half* cache_v, long long layer_stride,

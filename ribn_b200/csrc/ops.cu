@@ -383,10 +383,9 @@ __device__ __forceinline__ float normal_at(uint64_t seed, uint64_t index, float 
 }
 
 __device__ __forceinline__ void store_f16(unsigned char* p, float v, float* rounded) {
+    // Every f16 field of the three block formats sits at an even offset of an even-sized block.
     const __half h = __float2half_rn(v);
-    const unsigned short bits = __half_as_ushort(h);
-    p[0] = (unsigned char)(bits & 0xff);
-    p[1] = (unsigned char)(bits >> 8);
+    *reinterpret_cast<unsigned short*>(p) = __half_as_ushort(h);
     *rounded = __half2float(h);
 }
 

@@ -214,9 +214,17 @@ int ribn_b200_op_attention(int32_t device, const float* q, const uint16_t* keys,
     int32_t* d_pos = s.upload(pos.data(), pos.size());
     float* d_o = s.alloc<float>((size_t)rows * q_heads * head_dim);
     OP_PTR(d_q); OP_PTR(d_k); OP_PTR(d_v); OP_PTR(d_table); OP_PTR(d_seq); OP_PTR(d_pos); OP_PTR(d_o);
-    (void)variant;
-    OP_TRY(launch_attention_ref(s.stream, d_q, d_k, d_v, d_table, pages, d_seq, d_pos, rows, q_heads, kv_heads,
-                                head_dim, window, d_o));
+    if (variant == 1) {
+        OP_TRY(launch_attention_ref(s.stream, d_q, d_k, d_v, d_table, pages, d_seq, d_pos, rows, q_heads, kv_heads,
+                                    head_dim, window, d_o));
+    } else {
+        const size_t spans = ((size_t)tokens + kAttnSpanKeys - 1) / kAttnSpanKeys;
+        const size_t bytes = (size_t)rows * q_heads * spans * (head_dim + 2) * sizeof(float);
+        float* d_partial = s.alloc<float>(bytes / sizeof(float));
+        OP_PTR(d_partial);
+        OP_TRY(launch_attention(s.stream, d_q, d_k, d_v, d_table, pages, d_seq, d_pos, rows, q_heads, kv_heads,
+                                head_dim, window, tokens, d_partial, bytes, d_o, nullptr));
+    }
     return s.download(out, d_o, (size_t)rows * q_heads * head_dim) ? RIBN_B200_OK : RIBN_B200_ERROR;
 }
 

@@ -1,0 +1,184 @@
+"""Host scheduling rules, checked against a fake executor in the style of the
+reference's runtime contract tests (crates/runtime/tests/contract.rs:12-178):
+a shared control block of fault switches, a delayed first poll, and a record
+of every batch the engine offered."""
+from dataclasses import dataclass, field
+
+import pytest
+
+from ribn_b200.engine import Engine, EngineConfig, SchedulePolicy, TokenRequest
+from ribn_b200.executor import (Admission, ExecutionError, ExecutorInfo, GenerationLimits, StepCompletion,
+                                StepKind)
+
+
+@dataclass
+class Control:
+    defer: bool = False
+    reject_admission: bool = False
+    fail_submit: bool = False
+    fail_poll: bool = False
+    malformed: bool = False
+    delay: int = 0
+    batches: list = field(default_factory=list)
+    released: list = field(default_factory=list)
+
+
+class Fake:
+    def __init__(self, control, max_sequences=8, max_batch_tokens=64):
+        self.c = control
+        self.limits = GenerationLimits(256, max_sequences, max_batch_tokens, 1)
+        self.pending = None
+        self.prepared = None
+        self.sid = 0
+
+    def info(self):
+        return ExecutorInfo("fake", self.limits)
+
+    def admit(self, request_id, sequence, tokens, max_output_tokens, temperature=0.0, stop_tokens=()):
+        if self.c.defer:
+            return Admission(Admission.DEFERRED, "no capacity")
+        if self.c.reject_admission:
+            return Admission(Admission.REJECTED, "refused")
+        return Admission(Admission.READY)
+
+    def prepare(self, batch):
+        assert self.pending is None and self.prepared is None
+        self.prepared = list(batch)
+        return "ready"
+
+    def submit(self, batch):
+        assert list(batch) == self.prepared
+        self.prepared = None
+        if self.c.fail_submit:
+            raise ExecutionError("submit failed")
+        self.c.batches.append(list(batch))
+        self.sid += 1
+        self.pending = (self.sid, list(batch), self.c.delay)
+        return self.sid
+
+    def poll(self, sid):
+        if self.c.fail_poll:
+            raise ExecutionError("poll failed")
+        pid, batch, delay = self.pending
+        assert pid == sid
+        if delay > 0:
+            self.pending = (pid, batch, delay - 1)
+            return None
+        self.pending = None
+        rows = []
+        for it in batch:
+            tokens = [100 + it.prefix] if it.output_budget else []
+            rows.append(StepCompletion(it.sequence, it.prefix + it.token_budget, tokens))
+        if self.c.malformed:
+            rows[0] = StepCompletion(rows[0].sequence, rows[0].prefix + 1, rows[0].tokens)
+        return rows
+
+    def release(self, sequence):
+        self.c.released.append(sequence)
+
+
+def run(engine, limit=10000):
+    for _ in range(limit):
+        if engine.idle():
+            return
+        engine.step()
+    raise AssertionError("engine did not drain")
+
+
+def test_prefill_is_chunked_then_decode_runs_one_token_steps():
+    c = Control()
+    e = Engine(Fake(c), EngineConfig(max_active_requests=4), SchedulePolicy(64, 16, 1, 8))
+    rid = e.enqueue(TokenRequest(list(range(40)), 3))
+    run(e)
+    kinds = [(b[0].kind, b[0].prefix, b[0].token_budget, b[0].output_budget) for b in c.batches]
+    assert kinds[:3] == [(StepKind.PREFILL, 0, 16, 0), (StepKind.PREFILL, 16, 16, 0), (StepKind.PREFILL, 32, 8, 1)]
+    assert kinds[3:] == [(StepKind.DECODE, 40, 1, 1), (StepKind.DECODE, 41, 1, 1)]
+    done = e.finished[rid]
+    assert done.finish == "length" and done.output == [132, 140, 141] and c.released == [rid]
+
+
+def test_decode_rows_come_first_and_share_the_token_budget():
+    c = Control()
+    e = Engine(Fake(c, max_batch_tokens=20), EngineConfig(max_active_requests=4), SchedulePolicy(20, 16, 1, 8))
+    a = e.enqueue(TokenRequest(list(range(4)), 50))
+    e.step(); e.step()          # prefill a (one chunk), then its first decode is built with...
+    b = e.enqueue(TokenRequest(list(range(100)), 2))
+    e.step()
+    batch = c.batches[-1]
+    assert [it.kind for it in batch] == [StepKind.DECODE, StepKind.PREFILL]
+    assert batch[1].token_budget == 16 and sum(it.token_budget for it in batch) <= 20
+    assert a != b
+
+
+def test_forced_prefill_after_decode_only_steps():
+    c = Control()
+    # budget 1: a decode row always exhausts it, so prefill starves until forced
+    e = Engine(Fake(c), EngineConfig(max_active_requests=4), SchedulePolicy(1, 1, 1, 3))
+    e.enqueue(TokenRequest([1], 100))
+    e.step(); e.step()
+    e.enqueue(TokenRequest([1, 2, 3], 1))
+    for _ in range(12):
+        e.step()
+    kinds = [b[0].kind for b in c.batches]
+    window = kinds[2:10]
+    assert StepKind.PREFILL in window
+    first = window.index(StepKind.PREFILL)
+    assert first <= 4  # at most max_decode_only_steps (+1 in flight) decode-only steps before the forced prefill
+
+
+def test_pending_poll_makes_no_progress_and_keeps_one_batch_in_flight():
+    c = Control(delay=2)
+    e = Engine(Fake(c), EngineConfig(max_active_requests=2), SchedulePolicy(64, 64, 1, 8))
+    e.enqueue(TokenRequest([1, 2, 3], 1))
+    assert e.step() is True
+    assert e.step() is False and e.step() is False
+    assert len(c.batches) == 1
+    run(e)
+    assert len(c.batches) == 1 and len(e.finished) == 1
+
+
+def test_malformed_completion_faults_before_any_commit():
+    c = Control(malformed=True)
+    e = Engine(Fake(c), EngineConfig(max_active_requests=2), SchedulePolicy(64, 64, 1, 8))
+    rid = e.enqueue(TokenRequest([1, 2, 3], 4))
+    e.step()
+    with pytest.raises(ExecutionError):
+        e.step()
+    assert e.faulted and e.slots[rid].prefix == 0 and e.slots[rid].output == []
+    with pytest.raises(ExecutionError):
+        e.step()
+
+
+@pytest.mark.parametrize("switch", ["fail_submit", "fail_poll"])
+def test_executor_errors_fault_the_engine(switch):
+    c = Control()
+    e = Engine(Fake(c), EngineConfig(max_active_requests=2), SchedulePolicy(64, 64, 1, 8))
+    e.enqueue(TokenRequest([1, 2, 3], 4))
+    if switch == "fail_poll":
+        e.step()
+    setattr(c, switch, True)
+    with pytest.raises(ExecutionError):
+        e.step()
+    assert e.faulted
+
+
+def test_rejected_and_deferred_admission():
+    c = Control(reject_admission=True)
+    e = Engine(Fake(c), EngineConfig(max_active_requests=2), SchedulePolicy(64, 64, 1, 8))
+    rid = e.enqueue(TokenRequest([1], 1))
+    e.step()
+    assert e.finished[rid].finish.startswith("rejected") and e.idle()
+    c.reject_admission, c.defer = False, True
+    rid2 = e.enqueue(TokenRequest([1], 1))
+    e.step()
+    assert list(e.waiting) == [rid2] and not c.batches
+    c.defer = False
+    run(e)
+    assert e.finished[rid2].finish == "length"
+
+
+def test_policy_must_fit_executor_limits():
+    with pytest.raises(ValueError):
+        Engine(Fake(Control(), max_batch_tokens=32), EngineConfig(2), SchedulePolicy(64, 16, 1, 8))
+    with pytest.raises(ValueError):
+        Engine(Fake(Control(), max_sequences=2), EngineConfig(4), SchedulePolicy(32, 16, 1, 8))

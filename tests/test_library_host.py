@@ -1,0 +1,180 @@
+"""CPU-only checks of the CUDA library's host side: it loads, exports every
+symbol the header declares, and its tile-major repack feeds the tensor-core
+A fragment the integers the raw GGUF blocks hold (emulated in numpy with the
+kernel's own masks and shifts).  No device work is issued here."""
+import os
+import re
+
+import numpy as np
+import pytest
+
+from tests import helpers as H
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol(built_library):
+    import ribn_b200
+    from ribn_b200 import _lib
+    header = open(os.path.join(ROOT, "include", "ribn_b200.h")).read()
+    declared = set(re.findall(r"\b(ribn_b200_[a-z0-9_]+)\s*\(", header))
+    assert declared, "header declares nothing?"
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+    handle = ribn_b200.lib()
+    for name in declared:
+        assert hasattr(handle, name)
+    assert b"sm_100a" in handle.ribn_b200_build_info()
+
+
+def test_product_package_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "ribn_b200")
+    for dirpath, _dirs, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.lower() or f == "__init__.py" and "oracle" not in text.lower(), f
+
+
+LOW, HIGH, TOP = 0x000F000F, 0x00F000F0, 0x00300030
+
+
+def _halves(reg):
+    return reg & 0xFFFF, (reg >> 16) & 0xFFFF
+
+
+def _place(Q, g, t, kbase, regs):
+    """regs = (a0, a1, a2, a3) of mma.m16n8k16: rows g / g+8, inputs 4t..4t+3 of a 16-wide step."""
+    for ri, reg in enumerate(regs):
+        row = g + (8 if ri & 1 else 0)
+        k = kbase + 4 * t + (2 if ri >= 2 else 0)
+        lo, hi = _halves(int(reg))
+        Q[row, k], Q[row, k + 1] = lo, hi
+
+
+def _words(tile, off):
+    return np.frombuffer(tile[off:off + 16].tobytes(), dtype="<u4").astype(np.int64)
+
+
+def emulate_q4k(tile):
+    Q = np.zeros((16, 256), dtype=np.int64)
+    for lane in range(32):
+        g, t = lane >> 2, lane & 3
+        for j in range(4):
+            r0a, r0b, r1a, r1b = _words(tile, j * 512 + lane * 16)
+            ke, ko = 2 * j * 32, (2 * j + 1) * 32
+            _place(Q, g, t, ke, (r0a & LOW, r1a & LOW, (r0a >> 8) & LOW, (r1a >> 8) & LOW))
+            _place(Q, g, t, ke + 16, (r0b & LOW, r1b & LOW, (r0b >> 8) & LOW, (r1b >> 8) & LOW))
+            # high nibbles sit four mantissa bits higher: value * 16
+            hi = [x >> 4 for x in (r0a & HIGH, r1a & HIGH, (r0a >> 8) & HIGH, (r1a >> 8) & HIGH)]
+            _place(Q, g, t, ko, hi)
+            hi = [x >> 4 for x in (r0b & HIGH, r1b & HIGH, (r0b >> 8) & HIGH, (r1b >> 8) & HIGH)]
+            _place(Q, g, t, ko + 16, hi)
+    return Q
+
+
+def emulate_q6k(tile):
+    Q = np.zeros((16, 256), dtype=np.int64)
+    for lane in range(32):
+        g, t = lane >> 2, lane & 3
+        for c in range(2):
+            qh = _words(tile, 2048 + c * 512 + lane * 16)
+            for h in range(2):
+                la0, lb0, la1, lb1 = _words(tile, (c * 2 + h) * 512 + lane * 16)
+                wh0, wh1 = (qh[0], qh[1]) if h == 0 else (qh[2], qh[3])
+                for v in range(4):
+                    l0, l1 = (lb0, lb1) if v & 1 else (la0, la1)
+                    ls = 0 if v < 2 else 4
+                    sh = 4 - 2 * v
+                    def top(w, extra):
+                        s = sh - extra
+                        return ((w << s) if s >= 0 else (w >> -s)) & TOP
+                    regs = (((l0 >> ls) & LOW) | top(wh0, 0), ((l1 >> ls) & LOW) | top(wh1, 0),
+                            ((l0 >> (ls + 8)) & LOW) | top(wh0, 8), ((l1 >> (ls + 8)) & LOW) | top(wh1, 8))
+                    _place(Q, g, t, (c * 4 + v) * 32 + 16 * h, regs)
+    return Q
+
+
+def _prmt(w, sel):
+    b = [(w >> (8 * i)) & 0xFF for i in range(4)] + [0, 0, 0, 0]
+    out = 0
+    for i in range(4):
+        out |= b[(sel >> (4 * i)) & 0xF] << (8 * i)
+    return out
+
+
+def emulate_q8_0(tile):
+    Q = np.zeros((16, 256), dtype=np.int64)
+    for lane in range(32):
+        g, t = lane >> 2, lane & 3
+        for b in range(8):
+            x, y, z, w = _words(tile, b * 512 + lane * 16)
+            _place(Q, g, t, b * 32, (_prmt(x, 0x4140), _prmt(z, 0x4140), _prmt(x, 0x4342), _prmt(z, 0x4342)))
+            _place(Q, g, t, b * 32 + 16, (_prmt(y, 0x4140), _prmt(w, 0x4140), _prmt(y, 0x4342), _prmt(w, 0x4342)))
+    return Q
+
+
+def raw_integers(kind, raw, rows, cols):
+    elems, size = H.BLOCK[kind]
+    blocks = raw.reshape(rows, cols // elems, size)
+    if kind == H.Q4_K:
+        qs = blocks[:, :, 16:].reshape(rows, -1, 4, 32)
+        q = np.empty((rows, cols // 256, 8, 32), dtype=np.int64)
+        q[:, :, 0::2] = qs & 0x0F
+        q[:, :, 1::2] = qs >> 4
+        return q.reshape(rows, cols)
+    if kind == H.Q6_K:
+        ql = blocks[:, :, :128].reshape(rows, -1, 2, 2, 32)
+        qh = blocks[:, :, 128:192].reshape(rows, -1, 2, 32)
+        q = np.empty((rows, cols // 256, 2, 4, 32), dtype=np.int64)
+        for v in range(4):
+            q[:, :, :, v] = ((ql[:, :, :, v & 1] >> (0 if v < 2 else 4)) & 0x0F) | (((qh >> (2 * v)) & 3) << 4)
+        return q.reshape(rows, cols)
+    return (blocks[:, :, 2:].view(np.int8).astype(np.int64) + 128).reshape(rows, cols)
+
+
+@pytest.mark.parametrize("kind,tile_bytes,emulate", [(H.Q4_K, 2304, emulate_q4k), (H.Q6_K, 3360, emulate_q6k),
+                                                     (H.Q8_0, 4352, emulate_q8_0)])
+def test_repack_feeds_the_mma_fragment_the_raw_integers(built_library, kind, tile_bytes, emulate):
+    from ribn_b200 import ops
+    rng = np.random.default_rng(kind)
+    rows, cols = 40, 512  # 3 row tiles (last one ragged), 2 k tiles
+    elems, size = H.BLOCK[kind]
+    raw = rng.integers(0, 256, size=rows * (cols // elems) * size, dtype=np.uint8)
+    packed = ops.repack(kind, raw, rows, cols)
+    assert packed.size == 3 * 2 * tile_bytes
+    want = raw_integers(kind, raw, rows, cols)
+    blocks = raw.reshape(rows, cols // elems, size)
+    for rt in range(3):
+        for kb in range(2):
+            tile = packed[(rt * 2 + kb) * tile_bytes:(rt * 2 + kb + 1) * tile_bytes]
+            got = emulate(tile)
+            live = min(16, rows - rt * 16)
+            assert np.array_equal(got[:live], want[rt * 16:rt * 16 + live, kb * 256:(kb + 1) * 256])
+            if kind == H.Q8_0:
+                assert np.all(got[live:] == 128)          # padding rows decode to q = 0
+            else:
+                assert np.all(got[live:] == 0)
+            for r in range(live):
+                row = rt * 16 + r
+                if kind == H.Q4_K:
+                    assert np.array_equal(tile[2048 + r * 16:2048 + r * 16 + 16], blocks[row, kb, :16])
+                elif kind == H.Q6_K:
+                    assert np.array_equal(tile[3072 + r * 16:3072 + r * 16 + 16], blocks[row, kb, 192:208])
+                    assert np.array_equal(tile[3328 + r * 2:3328 + r * 2 + 2], blocks[row, kb, 208:210])
+                else:
+                    for b in range(8):
+                        assert np.array_equal(tile[4096 + r * 16 + b * 2:4096 + r * 16 + b * 2 + 2],
+                                              blocks[row, kb * 8 + b, 0:2])
+
+
+def test_compute_entry_points_fail_loudly_without_a_gpu(built_library):
+    """On a machine without a CUDA device every compute call reports an error
+    instead of computing on the CPU."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    import ribn_b200
+    with pytest.raises(ribn_b200.ExecutionError, match="no CUDA device"):
+        ribn_b200.QwenB200(H.TINY)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ribn_b200.ops.rms_norm(np.ones(4, np.float32), np.ones(4, np.float32), 1e-6)
