@@ -5,17 +5,28 @@
 // One CTA serves one (token, kv head, span); its warps are the q heads of the
 // GQA group, so the group's K/V rows are fetched once per CTA and shared
 // through L1.  Inside a warp the 32 lanes first take 32 different keys (a full
-// head_dim dot product each, no cross-lane reduction), then switch to owning
-// head_dim / 32 output dims for the P.V accumulation.  Spans depend only on
-// the token's own key range, never on what else is in the batch, so a token's
-// result is bit-identical whatever it is batched with and wherever its pages
-// live.  The reference's two-pass form with a global scores buffer
+// head_dim dot product each, no cross-lane reduction, all loads in flight at
+// once), then regroup as 4 key groups x 8 dim chunks for P.V, so every lane
+// again issues independent 128-bit loads; the key groups are folded together
+// once at the end of the span.  Spans depend only on the token's own key
+// range, never on what else is in the batch, so a token's result is
+// bit-identical whatever it is batched with and wherever its pages live.
+//
+// The decode form (FUSED) also applies the per-head Q/K RMSNorm and the NeoX
+// rotary and appends the new K/V row to the paged cache: the CTA that owns
+// the span holding the token's own position computes that row, stores it, and
+// serves it to its warps from shared memory.  Results leave in F32 and,
+// optionally, in the tensor-core operand form the output projection consumes.
+//
+// The reference's two-pass form with a global scores buffer
 // (crates/nvidia/src/model_ops.rs:441-545) is replaced, not translated.
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math.h>
 
 #include <algorithm>
 
+#include "gemv.cuh"
 #include "kernels.cuh"
 
 namespace ribn {
@@ -33,40 +44,121 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+__device__ __forceinline__ float split3(float v, __nv_bfloat16& hi, __nv_bfloat16& mid, __nv_bfloat16& lo) {
+    hi = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(hi);
+    mid = __float2bfloat16_rn(r1);
+    const float r2 = r1 - __bfloat162float(mid);
+    lo = __float2bfloat16_rn(r2);
+    return __bfloat162float(hi) + __bfloat162float(mid) + __bfloat162float(lo);
+}
+
+struct AttnArgs {
+    const float* q;            // [T][q_heads][HD]; raw projections when fused
+    const float* k_new;        // [T][kv_heads][HD] raw (fused only)
+    const float* v_new;        // [T][kv_heads][HD] (fused only)
+    const float* q_norm;       // [HD] (fused only)
+    const float* k_norm;       // [HD] (fused only)
+    const float* inv_freq;     // [HD / 2] (fused only)
+    float eps;
+    __half* cache_k;
+    __half* cache_v;
+    const int32_t* page_tables;
+    int pages_per_sequence;
+    const int32_t* token_seq;
+    const int32_t* token_pos;
+    const int32_t* token_slot; // physical slot of the token's own position (fused only)
+    int token_base;
+    int q_heads, kv_heads, window, max_spans;
+    float* partial;
+    float* out;                // [T][q_heads][HD]
+    ActOperand operand;        // optional operand form of `out`, K = q_heads * HD
+};
+
+// RMSNorm + NeoX rotary of one head vector held lane-strided: element i of a
+// lane is dimension lane + 32 i, so dimension d and its partner d + HD/2 sit
+// in the same lane (i and i + DPL/2).
 template <int HD>
-__global__ void attention_span_kernel(const float* __restrict__ q, const __half* __restrict__ cache_k,
-                                      const __half* __restrict__ cache_v, const int32_t* __restrict__ page_tables,
-                                      int pages_per_sequence, const int32_t* __restrict__ token_seq,
-                                      const int32_t* __restrict__ token_pos, int token_base, int q_heads,
-                                      int kv_heads, int window, int max_spans, float* __restrict__ partial,
-                                      float* __restrict__ out) {
-    constexpr int DPL = HD / 32;  // output dims per lane
-    extern __shared__ float q_smem[];  // [warps][HD]
+__device__ __forceinline__ void norm_rope(float (&x)[HD / 32], const float* weight, const float* inv_freq, float eps,
+                                          float pos, int lane) {
+    constexpr int DPL = HD / 32;
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) ss = fmaf(x[i], x[i], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) x[i] = x[i] * inv * weight[lane + 32 * i];
+#pragma unroll
+    for (int i = 0; i < DPL / 2; ++i) {
+        const float theta = pos * inv_freq[lane + 32 * i];
+        const float s = sinf(theta), c = cosf(theta);
+        const float x0 = x[i], x1 = x[i + DPL / 2];
+        x[i] = x0 * c - x1 * s;
+        x[i + DPL / 2] = x0 * s + x1 * c;
+    }
+}
+
+template <int HD, bool FUSED>
+__global__ void attention_span_kernel(const AttnArgs a) {
+    constexpr int DPL = HD / 32;  // dims per lane in the lane-strided layout
+    constexpr int CH = HD / 8;    // dims per lane in the P.V phase (8 chunks x 4 key groups)
+    extern __shared__ __align__(16) unsigned char attn_smem[];
+    float* q_smem = reinterpret_cast<float*>(attn_smem);                                 // [warps][HD]
+    __half* k_self = reinterpret_cast<__half*>(attn_smem + (size_t)(blockDim.x >> 5) * HD * sizeof(float));  // [HD]
+    __half* v_self = k_self + HD;                                                         // [HD]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int q_per_kv = q_heads / kv_heads;
-    const int t = token_base + blockIdx.x / kv_heads, kvh = blockIdx.x % kv_heads;
+    const int q_per_kv = a.q_heads / a.kv_heads;
+    const int t = a.token_base + blockIdx.x / a.kv_heads, kvh = blockIdx.x % a.kv_heads;
     const int span = blockIdx.y;
     const int qh = kvh * q_per_kv + warp;
-    const int pos = token_pos[t];
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int pos = a.token_pos[t];
+    const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const int n_keys = pos + 1 - first;
     const int spans = (n_keys + kAttnSpanKeys - 1) / kAttnSpanKeys;
     if (span >= spans) return;
     const int begin = first + span * kAttnSpanKeys;
     const int end = min(pos + 1, begin + kAttnSpanKeys);
-    const int32_t* table = page_tables + (long long)token_seq[t] * pages_per_sequence;
+    const int32_t* table = a.page_tables + (long long)a.token_seq[t] * a.pages_per_sequence;
     const float scale = 1.0f / sqrtf((float)HD);
+    const long long row_stride = (long long)a.kv_heads * HD;
+    const bool owns_self = FUSED && span == spans - 1;  // this CTA's span holds the token's own position
 
     float* qs = q_smem + warp * HD;
-    const float* qp = q + ((long long)t * q_heads + qh) * HD;
-    for (int d = lane; d < HD; d += 32) qs[d] = qp[d];
-    __syncwarp();
-
-    float acc[DPL];
+    {
+        const float* qp = a.q + ((long long)t * a.q_heads + qh) * HD;
+        float x[DPL];
 #pragma unroll
-    for (int d = 0; d < DPL; ++d) acc[d] = 0.0f;
+        for (int i = 0; i < DPL; ++i) x[i] = qp[lane + 32 * i];
+        if (FUSED) norm_rope<HD>(x, a.q_norm, a.inv_freq, a.eps, (float)pos, lane);
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) qs[lane + 32 * i] = x[i];
+    }
+    if (owns_self && warp == 0) {
+        // The token's own K (normalised, rotated) and V, rounded to F16 exactly as the cache holds them.
+        const float* kp = a.k_new + ((long long)t * a.kv_heads + kvh) * HD;
+        const float* vp = a.v_new + ((long long)t * a.kv_heads + kvh) * HD;
+        float x[DPL];
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) x[i] = kp[lane + 32 * i];
+        norm_rope<HD>(x, a.k_norm, a.inv_freq, a.eps, (float)pos, lane);
+        __half* ck = a.cache_k + (long long)a.token_slot[t] * row_stride + (long long)kvh * HD;
+        __half* cv = a.cache_v + (long long)a.token_slot[t] * row_stride + (long long)kvh * HD;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int d = lane + 32 * i;
+            const __half kh = __float2half_rn(x[i]), vh = __float2half_rn(vp[d]);
+            k_self[d] = kh; v_self[d] = vh;
+            ck[d] = kh; cv[d] = vh;
+        }
+    }
+    if (FUSED) __syncthreads(); else __syncwarp();
+
+    const int kg = lane >> 3, dc = lane & 7;
+    float acc[CH];
+#pragma unroll
+    for (int d = 0; d < CH; ++d) acc[d] = 0.0f;
     float run_max = -INFINITY, total = 0.0f;
-    const long long row_stride = (long long)kv_heads * HD;
     for (int base = begin; base < end; base += 32) {
         const int key = base + lane;
         const bool live = key < end;
@@ -74,17 +166,21 @@ __global__ void attention_span_kernel(const float* __restrict__ q, const __half*
         float s = -INFINITY;
         if (live) {
             phys = (long long)table[key / kPageTokens] * kPageTokens + key % kPageTokens;
-            const uint4* kp = reinterpret_cast<const uint4*>(cache_k + phys * row_stride + (long long)kvh * HD);
+            const uint4* kp = (owns_self && key == pos)
+                                  ? reinterpret_cast<const uint4*>(k_self)
+                                  : reinterpret_cast<const uint4*>(a.cache_k + phys * row_stride + (long long)kvh * HD);
+            uint4 kk[HD / 8];
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) kk[i] = kp[i];
             float dot = 0.0f;
-#pragma unroll 4
+#pragma unroll
             for (int i = 0; i < HD / 8; ++i) {
-                const uint4 kk = __ldg(kp + i);
                 const float4 qa = *reinterpret_cast<const float4*>(qs + i * 8);
                 const float4 qb = *reinterpret_cast<const float4*>(qs + i * 8 + 4);
-                const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kk.x));
-                const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kk.y));
-                const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kk.z));
-                const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kk.w));
+                const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].x));
+                const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].y));
+                const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].z));
+                const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].w));
                 dot = fmaf(qa.x, k0.x, dot); dot = fmaf(qa.y, k0.y, dot);
                 dot = fmaf(qa.z, k1.x, dot); dot = fmaf(qa.w, k1.y, dot);
                 dot = fmaf(qb.x, k2.x, dot); dot = fmaf(qb.y, k2.y, dot);
@@ -97,91 +193,162 @@ __global__ void attention_span_kernel(const float* __restrict__ q, const __half*
         const float p = live ? expf(s - new_max) : 0.0f;
         total = total * factor + warp_sum(p);
 #pragma unroll
-        for (int d = 0; d < DPL; ++d) acc[d] *= factor;
+        for (int d = 0; d < CH; ++d) acc[d] *= factor;
         run_max = new_max;
         const int count = min(32, end - base);
-        for (int j = 0; j < count; ++j) {
-            const float pj = __shfl_sync(0xffffffffu, p, j);
-            const long long pj_phys = __shfl_sync(0xffffffffu, phys, j);
-            const __half* vp = cache_v + pj_phys * row_stride + (long long)kvh * HD + lane * DPL;
-            if (DPL == 4) {
-                const uint2 vv = __ldg(reinterpret_cast<const uint2*>(vp));
-                const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&vv.x));
-                const float2 v1 = __half22float2(*reinterpret_cast<const __half2*>(&vv.y));
-                acc[0] = fmaf(pj, v0.x, acc[0]); acc[1] = fmaf(pj, v0.y, acc[1]);
-                acc[2 % DPL] = fmaf(pj, v1.x, acc[2 % DPL]); acc[3 % DPL] = fmaf(pj, v1.y, acc[3 % DPL]);
+        // P.V: lane (kg, dc) takes keys j = 4 jj + kg and dims [dc * CH, dc * CH + CH)
+        uint4 vv[8][CH / 8];
+        float pj[8];
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+            const int j = jj * 4 + kg;
+            pj[jj] = __shfl_sync(0xffffffffu, p, j);
+            const long long pphys = __shfl_sync(0xffffffffu, phys, j);
+            const bool self = owns_self && base + j == pos;
+            const __half* vp = self ? v_self : a.cache_v + pphys * row_stride + (long long)kvh * HD;
+            if (j < count) {
+#pragma unroll
+                for (int c = 0; c < CH / 8; ++c) vv[jj][c] = *reinterpret_cast<const uint4*>(vp + dc * CH + c * 8);
             } else {
 #pragma unroll
-                for (int d = 0; d < DPL; ++d) acc[d] = fmaf(pj, __half2float(vp[d]), acc[d]);
+                for (int c = 0; c < CH / 8; ++c) vv[jj][c] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+#pragma unroll
+            for (int c = 0; c < CH / 8; ++c) {
+                const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].x));
+                const float2 v1 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].y));
+                const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].z));
+                const float2 v3 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].w));
+                float* o = acc + c * 8;
+                o[0] = fmaf(pj[jj], v0.x, o[0]); o[1] = fmaf(pj[jj], v0.y, o[1]);
+                o[2] = fmaf(pj[jj], v1.x, o[2]); o[3] = fmaf(pj[jj], v1.y, o[3]);
+                o[4] = fmaf(pj[jj], v2.x, o[4]); o[5] = fmaf(pj[jj], v2.y, o[5]);
+                o[6] = fmaf(pj[jj], v3.x, o[6]); o[7] = fmaf(pj[jj], v3.y, o[7]);
             }
         }
     }
+    // Fold the four key groups (fixed order: xor 8, then xor 16).
+#pragma unroll
+    for (int d = 0; d < CH; ++d) {
+        acc[d] += __shfl_xor_sync(0xffffffffu, acc[d], 8);
+        acc[d] += __shfl_xor_sync(0xffffffffu, acc[d], 16);
+    }
+    if (kg != 0) return;
     if (spans == 1) {
-        float* op = out + ((long long)t * q_heads + qh) * HD + lane * DPL;
         const float inv = 1.0f / total;
+        float* op = a.out + ((long long)t * a.q_heads + qh) * HD + dc * CH;
 #pragma unroll
-        for (int d = 0; d < DPL; ++d) op[d] = acc[d] * inv;
+        for (int d = 0; d < CH; ++d) { acc[d] *= inv; op[d] = acc[d]; }
+        if (a.operand.x != nullptr) {
+            const int K = a.q_heads * HD, m = t - a.token_base;
+            __nv_bfloat16* ox = a.operand.x + (size_t)m * 3 * K + (size_t)qh * HD + dc * CH;
+#pragma unroll
+            for (int c = 0; c < CH / 16; ++c) {
+                float sum = 0.0f;
+#pragma unroll
+                for (int d = 0; d < 16; ++d) {
+                    __nv_bfloat16 hi, mid, lo;
+                    sum += split3(acc[c * 16 + d], hi, mid, lo);
+                    ox[c * 16 + d] = hi; ox[K + c * 16 + d] = mid; ox[2 * (size_t)K + c * 16 + d] = lo;
+                }
+                a.operand.s16[(size_t)m * (K / 16) + (qh * HD + dc * CH) / 16 + c] = sum;
+            }
+        }
     } else {
-        float* pp = partial + (((long long)(t - token_base) * q_heads + qh) * max_spans + span) * (HD + 2);
+        float* pp = a.partial + (((long long)(t - a.token_base) * a.q_heads + qh) * a.max_spans + span) * (HD + 2);
 #pragma unroll
-        for (int d = 0; d < DPL; ++d) pp[lane * DPL + d] = acc[d];
-        if (lane == 0) { pp[HD] = run_max; pp[HD + 1] = total; }
+        for (int d = 0; d < CH; ++d) pp[dc * CH + d] = acc[d];
+        if (dc == 0) { pp[HD] = run_max; pp[HD + 1] = total; }
     }
 }
 
 // Merge a token's spans in span order: out = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M).
+// One block of HD threads per (token, q head).
 template <int HD>
-__global__ void attention_merge_kernel(const float* __restrict__ partial, const int32_t* __restrict__ token_pos,
-                                       int token_base, int q_heads, int window, int max_spans,
-                                       float* __restrict__ out) {
-    const int t = token_base + blockIdx.x / q_heads, qh = blockIdx.x % q_heads;
-    const int pos = token_pos[t];
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+__global__ void attention_merge_kernel(const AttnArgs a) {
+    __shared__ float weight[kAttnMaxSpans];
+    __shared__ float denom_s;
+    const int t = a.token_base + blockIdx.x / a.q_heads, qh = blockIdx.x % a.q_heads;
+    const int pos = a.token_pos[t];
+    const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const int spans = (pos + 1 - first + kAttnSpanKeys - 1) / kAttnSpanKeys;
     if (spans <= 1) return;  // written directly by the span kernel
-    const float* pp = partial + ((long long)(t - token_base) * q_heads + qh) * max_spans * (HD + 2);
-    float top = -INFINITY;
-    for (int s = 0; s < spans; ++s) top = fmaxf(top, pp[s * (HD + 2) + HD]);
-    float denom = 0.0f;
-    for (int s = 0; s < spans; ++s) denom += pp[s * (HD + 2) + HD + 1] * expf(pp[s * (HD + 2) + HD] - top);
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float sum = 0.0f;
-        for (int s = 0; s < spans; ++s) sum = fmaf(pp[s * (HD + 2) + d], expf(pp[s * (HD + 2) + HD] - top), sum);
-        out[((long long)t * q_heads + qh) * HD + d] = sum / denom;
+    const float* pp = a.partial + ((long long)(t - a.token_base) * a.q_heads + qh) * a.max_spans * (HD + 2);
+    if (threadIdx.x < 32) {
+        float top = -INFINITY;
+        for (int s = threadIdx.x; s < spans; s += 32) top = fmaxf(top, pp[s * (HD + 2) + HD]);
+        top = warp_max(top);
+        float denom = 0.0f;  // per-lane partial sums in span order, folded in a fixed shuffle order
+        for (int s = threadIdx.x; s < spans; s += 32) {
+            const float w = expf(pp[s * (HD + 2) + HD] - top);
+            weight[s] = w;
+            denom += pp[s * (HD + 2) + HD + 1] * w;
+        }
+        denom = warp_sum(denom);
+        if (threadIdx.x == 0) denom_s = denom;
+    }
+    __syncthreads();
+    const int d = threadIdx.x;
+    float sum = 0.0f;
+    for (int s = 0; s < spans; ++s) sum = fmaf(pp[s * (HD + 2) + d], weight[s], sum);
+    const float value = sum / denom_s;
+    a.out[((long long)t * a.q_heads + qh) * HD + d] = value;
+    if (a.operand.x != nullptr) {
+        const int K = a.q_heads * HD, m = t - a.token_base;
+        __nv_bfloat16 hi, mid, lo;
+        float recon = split3(value, hi, mid, lo);
+        __nv_bfloat16* ox = a.operand.x + (size_t)m * 3 * K + (size_t)qh * HD + d;
+        ox[0] = hi; ox[K] = mid; ox[2 * (size_t)K] = lo;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) recon += __shfl_xor_sync(0xffffffffu, recon, o);
+        if ((d & 15) == 0) a.operand.s16[(size_t)m * (K / 16) + (qh * HD + d) / 16] = recon;
     }
 }
 
 template <int HD>
-cudaError_t launch_hd(cudaStream_t stream, const float* q, const __half* cache_k, const __half* cache_v,
-                      const int32_t* page_tables, int pages_per_sequence, const int32_t* token_seq,
-                      const int32_t* token_pos, int n_tokens, int q_heads, int kv_heads, int window, int max_keys,
-                      float* partial, size_t partial_bytes, float* out, int* launches) {
-    const int q_per_kv = q_heads / kv_heads;
-    const int max_spans = (max_keys + kAttnSpanKeys - 1) / kAttnSpanKeys;
-    const size_t per_token = (size_t)q_heads * max_spans * (HD + 2) * sizeof(float);
+cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens, int max_keys, size_t partial_bytes,
+                      int* launches) {
+    const int q_per_kv = a.q_heads / a.kv_heads;
+    a.max_spans = (max_keys + kAttnSpanKeys - 1) / kAttnSpanKeys;
+    if (a.max_spans > kAttnMaxSpans) return cudaErrorInvalidValue;
+    const size_t per_token = (size_t)a.q_heads * a.max_spans * (HD + 2) * sizeof(float);
     int chunk = n_tokens;
-    if (max_spans > 1) {
-        if (partial == nullptr || partial_bytes < per_token) return cudaErrorInvalidValue;
+    if (a.max_spans > 1) {
+        if (a.partial == nullptr || partial_bytes < per_token) return cudaErrorInvalidValue;
         chunk = (int)std::min<size_t>((size_t)n_tokens, partial_bytes / per_token);
     }
+    if (a.operand.x != nullptr && chunk < n_tokens) return cudaErrorInvalidValue;  // operand rows are launch-relative
+    const size_t smem = (size_t)q_per_kv * HD * sizeof(float) + 2 * HD * sizeof(__half);
     for (int base = 0; base < n_tokens; base += chunk) {
         const int n = std::min(chunk, n_tokens - base);
-        dim3 grid(n * kv_heads, max_spans);
-        attention_span_kernel<HD><<<grid, q_per_kv * 32, q_per_kv * HD * sizeof(float), stream>>>(
-            q, cache_k, cache_v, page_tables, pages_per_sequence, token_seq, token_pos, base, q_heads, kv_heads,
-            window, max_spans, partial, out);
+        a.token_base = base;
+        dim3 grid(n * a.kv_heads, a.max_spans);
+        if (fused) attention_span_kernel<HD, true><<<grid, q_per_kv * 32, smem, stream>>>(a);
+        else attention_span_kernel<HD, false><<<grid, q_per_kv * 32, smem, stream>>>(a);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
         if (launches) ++*launches;
-        if (max_spans > 1) {
-            attention_merge_kernel<HD><<<n * q_heads, HD < 128 ? 64 : 128, 0, stream>>>(partial, token_pos, base, q_heads,
-                                                                                     window, max_spans, out);
+        if (a.max_spans > 1) {
+            attention_merge_kernel<HD><<<n * a.q_heads, HD, 0, stream>>>(a);
             e = cudaGetLastError();
             if (e != cudaSuccess) return e;
             if (launches) ++*launches;
         }
     }
     return cudaSuccess;
+}
+
+cudaError_t dispatch(cudaStream_t stream, const AttnArgs& a, bool fused, int head_dim, int n_tokens, int max_keys,
+                     size_t partial_bytes, int* launches) {
+    switch (head_dim) {
+        case 64: return launch_hd<64>(stream, a, fused, n_tokens, max_keys, partial_bytes, launches);
+        case 128: return launch_hd<128>(stream, a, fused, n_tokens, max_keys, partial_bytes, launches);
+        case 256: return launch_hd<256>(stream, a, fused, n_tokens, max_keys, partial_bytes, launches);
+        default: return cudaErrorInvalidValue;
+    }
 }
 
 }  // namespace
@@ -193,18 +360,43 @@ cudaError_t launch_attention(cudaStream_t stream, const float* q, const __half* 
                              int* launches) {
     if (n_tokens <= 0) return cudaSuccess;
     if (q_heads % kv_heads != 0 || q_heads / kv_heads > 32 || max_keys <= 0) return cudaErrorInvalidValue;
-    if (window > 0) max_keys = std::min(max_keys, window);
-#define RIBN_ATTN(D)                                                                                          \
-    return launch_hd<D>(stream, q, cache_k, cache_v, page_tables, pages_per_sequence, token_seq, token_pos, \
-                        n_tokens, q_heads, kv_heads, window, max_keys, partial, partial_bytes, out, launches)
-    switch (head_dim) {
-        case 32: RIBN_ATTN(32);
-        case 64: RIBN_ATTN(64);
-        case 128: RIBN_ATTN(128);
-        case 256: RIBN_ATTN(256);
-        default: return cudaErrorInvalidValue;
+    if (head_dim == 32) {
+        // Below 64 dims the span kernel's lane layout does not apply: the plain kernel serves.
+        cudaError_t e = launch_attention_ref(stream, q, cache_k, cache_v, page_tables, pages_per_sequence, token_seq,
+                                             token_pos, n_tokens, q_heads, kv_heads, head_dim, window, out);
+        if (e == cudaSuccess && launches) ++*launches;
+        return e;
     }
-#undef RIBN_ATTN
+    if (window > 0) max_keys = std::min(max_keys, window);
+    AttnArgs a{};
+    a.q = q;
+    a.cache_k = const_cast<__half*>(cache_k);
+    a.cache_v = const_cast<__half*>(cache_v);
+    a.page_tables = page_tables;
+    a.pages_per_sequence = pages_per_sequence;
+    a.token_seq = token_seq;
+    a.token_pos = token_pos;
+    a.q_heads = q_heads;
+    a.kv_heads = kv_heads;
+    a.window = window;
+    a.partial = partial;
+    a.out = out;
+    return dispatch(stream, a, false, head_dim, n_tokens, max_keys, partial_bytes, launches);
+}
+
+cudaError_t launch_attention_decode(cudaStream_t stream, const DecodeAttention& d, int* launches) {
+    if (d.n_tokens <= 0) return cudaSuccess;
+    if (d.q_heads % d.kv_heads != 0 || d.q_heads / d.kv_heads > 32 || d.max_keys <= 0) return cudaErrorInvalidValue;
+    AttnArgs a{};
+    a.q = d.q; a.k_new = d.k; a.v_new = d.v;
+    a.q_norm = d.q_norm; a.k_norm = d.k_norm; a.inv_freq = d.inv_freq; a.eps = d.eps;
+    a.cache_k = d.cache_k; a.cache_v = d.cache_v;
+    a.page_tables = d.page_tables; a.pages_per_sequence = d.pages_per_sequence;
+    a.token_seq = d.token_seq; a.token_pos = d.token_pos; a.token_slot = d.token_slot;
+    a.q_heads = d.q_heads; a.kv_heads = d.kv_heads; a.window = d.window;
+    a.partial = d.partial; a.out = d.out; a.operand = d.operand;
+    const int max_keys = d.window > 0 ? std::min(d.max_keys, d.window) : d.max_keys;
+    return dispatch(stream, a, true, d.head_dim, d.n_tokens, max_keys, d.partial_bytes, launches);
 }
 
 }  // namespace ribn

@@ -145,50 +145,174 @@ struct StepPlan {
         ++launches;                             \
     } while (0)
 
-bool fast_ok(const ribn_b200_executor* ex, const Tensor& t, int members) {
-    return !(ex->cfg.flags & RIBN_B200_FLAG_REFERENCE_KERNELS) && t.packed.ready() &&
-           members <= kGemvMaxMembers;
-}
-
-// y = W x for `members` vectors, optionally with a fused RMSNorm of x and a
-// residual or SwiGLU epilogue, on whichever kernel family applies.
-cudaError_t project(ribn_b200_executor* ex, int& launches, const Tensor* w, int n_mats, const float* x,
-                    const float* norm_weight, float* normed_tmp, int members, float* const* y, int epilogue) {
+// ---- reference family: plain kernels over raw GGUF blocks, any number of tokens ----------
+cudaError_t run_layers_reference(ribn_b200_executor* ex, const StepPlan& plan, int& launches) {
     const ribn_b200_config& c = ex->cfg;
-    bool fast = true;
-    for (int i = 0; i < n_mats; ++i) fast = fast && fast_ok(ex, w[i], members);
-    if (fast) {
-        GemvArgs a{};
-        a.n_segments = n_mats;
-        for (int i = 0; i < n_mats; ++i) {
-            a.seg[i] = GemvSegment{w[i].packed.data, w[i].type, (int)w[i].rows, w[i].packed.row_tiles, y[i]};
+    cudaStream_t s = ex->stream;
+    const int T = plan.n_tokens;
+    const bool plain_attention = (c.flags & RIBN_B200_FLAG_REFERENCE_KERNELS) != 0;
+    for (int l = 0; l < c.layers; ++l) {
+        Tensor* t = &ex->lt(l, 0);
+        STEP_TRY(launch_rms_norm(s, ex->hidden, (const float*)t[kAttnNorm].raw, T, c.hidden, c.rms_eps, ex->normed));
+        STEP_TRY(launch_gemv_ref(s, t[kAttnQ].type, t[kAttnQ].raw, t[kAttnQ].rows, c.hidden, ex->normed, T, ex->q, false));
+        STEP_TRY(launch_gemv_ref(s, t[kAttnK].type, t[kAttnK].raw, t[kAttnK].rows, c.hidden, ex->normed, T, ex->k, false));
+        STEP_TRY(launch_gemv_ref(s, t[kAttnV].type, t[kAttnV].raw, t[kAttnV].rows, c.hidden, ex->normed, T, ex->v, false));
+        __half* ck = ex->cache_k + (long long)l * ex->layer_stride;
+        __half* cv = ex->cache_v + (long long)l * ex->layer_stride;
+        STEP_TRY(launch_qk_norm_rope_append(s, ex->q, ex->k, ex->v, (const float*)t[kAttnQNorm].raw,
+                                            (const float*)t[kAttnKNorm].raw, ex->inv_freq, ex->meta.token_pos,
+                                            ex->meta.token_slot, T, c.q_heads, c.kv_heads, c.head_dim, c.rms_eps,
+                                            ck, cv));
+        if (plain_attention) {
+            STEP_TRY(launch_attention_ref(s, ex->q, ck, cv, ex->d_page_tables, ex->pages_per_sequence,
+                                          ex->meta.token_seq, ex->meta.token_pos, T, c.q_heads, c.kv_heads,
+                                          c.head_dim, 0, ex->attn));
+        } else {
+            cudaError_t e = launch_attention(s, ex->q, ck, cv, ex->d_page_tables, ex->pages_per_sequence,
+                                             ex->meta.token_seq, ex->meta.token_pos, T, c.q_heads, c.kv_heads,
+                                             c.head_dim, 0, plan.max_keys, ex->scratch.attn_partial,
+                                             ex->scratch.attn_partial_bytes, ex->attn, &launches);
+            if (e != cudaSuccess) return e;
         }
-        a.k = (int)w[0].cols;
-        a.members = members;
-        a.x = x;
-        a.norm_weight = norm_weight;
-        a.eps = c.rms_eps;
-        a.epilogue = epilogue;
-        STEP_TRY(launch_gemv_mma(ex->stream, a, false));
-        return cudaSuccess;
+        STEP_TRY(launch_gemv_ref(s, t[kAttnOutput].type, t[kAttnOutput].raw, c.hidden, t[kAttnOutput].cols, ex->attn, T,
+                                 ex->hidden, true));
+        STEP_TRY(launch_rms_norm(s, ex->hidden, (const float*)t[kFfnNorm].raw, T, c.hidden, c.rms_eps, ex->normed));
+        STEP_TRY(launch_gemv_ref(s, t[kFfnGate].type, t[kFfnGate].raw, c.ffn, c.hidden, ex->normed, T, ex->gate, false));
+        STEP_TRY(launch_gemv_ref(s, t[kFfnUp].type, t[kFfnUp].raw, c.ffn, c.hidden, ex->normed, T, ex->up, false));
+        STEP_TRY(launch_silu_mul(s, ex->gate, ex->up, (long long)T * c.ffn, ex->gate));
+        STEP_TRY(launch_gemv_ref(s, t[kFfnDown].type, t[kFfnDown].raw, c.hidden, c.ffn, ex->gate, T, ex->hidden, true));
     }
-    const float* in = x;
-    if (norm_weight != nullptr) {
-        STEP_TRY(launch_rms_norm(ex->stream, x, norm_weight, members, (int)w[0].cols, c.rms_eps, normed_tmp));
-        in = normed_tmp;
-    }
-    if (epilogue == kSwiGLU) {
-        // gate -> ex->gate, up -> ex->up, product -> y[0]
-        STEP_TRY(launch_gemv_ref(ex->stream, w[0].type, w[0].raw, w[0].rows, w[0].cols, in, members, ex->gate, false));
-        STEP_TRY(launch_gemv_ref(ex->stream, w[1].type, w[1].raw, w[1].rows, w[1].cols, in, members, ex->up, false));
-        STEP_TRY(launch_silu_mul(ex->stream, ex->gate, ex->up, (long long)members * w[0].rows, y[0]));
-        return cudaSuccess;
-    }
-    for (int i = 0; i < n_mats; ++i) {
-        STEP_TRY(launch_gemv_ref(ex->stream, w[i].type, w[i].raw, w[i].rows, w[i].cols, in, members, y[i],
-                                 epilogue == kResidual));
+    if (plan.n_sample > 0) {
+        // Only sampling rows reach the head (crates/nvidia/src/decode.rs:686-704).
+        STEP_TRY(launch_rms_norm_gather(s, ex->hidden, ex->meta.sample_token, (const float*)ex->output_norm.raw,
+                                        plan.n_sample, c.hidden, c.rms_eps, ex->head_in));
+        STEP_TRY(launch_gemv_ref(s, ex->output.type, ex->output.raw, ex->output.rows, ex->output.cols, ex->head_in,
+                                 plan.n_sample, ex->logits, false));
     }
     return cudaSuccess;
+}
+
+// ---- decode family: tensor-core GEMV chain over operand-form activations (<= 2 tokens) ---------
+GemvSegment segment_of(const Tensor& t, float* y) {
+    return GemvSegment{t.packed.data, t.type, (int)t.rows, t.packed.row_tiles, y};
+}
+
+cudaError_t run_layers_decode(ribn_b200_executor* ex, const StepPlan& plan, int& launches) {
+    const ribn_b200_config& c = ex->cfg;
+    cudaStream_t s = ex->stream;
+    const int T = plan.n_tokens;
+    const bool pdl = !(c.flags & RIBN_B200_FLAG_NO_GRAPH);
+    STEP_TRY(launch_to_operand(s, ex->hidden, nullptr, (const float*)ex->lt(0, kAttnNorm).raw, T, c.hidden,
+                               ex->op_hidden));
+    for (int l = 0; l < c.layers; ++l) {
+        Tensor* t = &ex->lt(l, 0);
+        GemvArgs a{};
+        a.members = T;
+        a.eps = c.rms_eps;
+        a.error_flag = ex->d_error;
+        // q | k | v from the normalised residual stream
+        a.n_segments = 3;
+        a.seg[0] = segment_of(t[kAttnQ], ex->q);
+        a.seg[1] = segment_of(t[kAttnK], ex->k);
+        a.seg[2] = segment_of(t[kAttnV], ex->v);
+        a.k = c.hidden;
+        a.in = ex->op_hidden;
+        a.in_has_norm = 1;
+        a.epilogue = kStore;
+        STEP_TRY(launch_gemv_mma(s, a, pdl));
+        __half* ck = ex->cache_k + (long long)l * ex->layer_stride;
+        __half* cv = ex->cache_v + (long long)l * ex->layer_stride;
+        if (plan.n_rows == T && c.head_dim >= 64) {
+            // every row adds one token: norm, rotary, cache append, attention and operand form in one pass
+            DecodeAttention d{};
+            d.q = ex->q; d.k = ex->k; d.v = ex->v;
+            d.q_norm = (const float*)t[kAttnQNorm].raw; d.k_norm = (const float*)t[kAttnKNorm].raw;
+            d.inv_freq = ex->inv_freq; d.eps = c.rms_eps;
+            d.cache_k = ck; d.cache_v = cv;
+            d.page_tables = ex->d_page_tables; d.pages_per_sequence = ex->pages_per_sequence;
+            d.token_seq = ex->meta.token_seq; d.token_pos = ex->meta.token_pos; d.token_slot = ex->meta.token_slot;
+            d.n_tokens = T; d.q_heads = c.q_heads; d.kv_heads = c.kv_heads; d.head_dim = c.head_dim;
+            d.window = 0; d.max_keys = plan.max_keys;
+            d.partial = ex->scratch.attn_partial; d.partial_bytes = ex->scratch.attn_partial_bytes;
+            d.out = ex->attn; d.operand = ex->op_attn;
+            cudaError_t e = launch_attention_decode(s, d, &launches);
+            if (e != cudaSuccess) return e;
+        } else {
+            STEP_TRY(launch_qk_norm_rope_append(s, ex->q, ex->k, ex->v, (const float*)t[kAttnQNorm].raw,
+                                                (const float*)t[kAttnKNorm].raw, ex->inv_freq, ex->meta.token_pos,
+                                                ex->meta.token_slot, T, c.q_heads, c.kv_heads, c.head_dim,
+                                                c.rms_eps, ck, cv));
+            cudaError_t e = launch_attention(s, ex->q, ck, cv, ex->d_page_tables, ex->pages_per_sequence,
+                                             ex->meta.token_seq, ex->meta.token_pos, T, c.q_heads, c.kv_heads,
+                                             c.head_dim, 0, plan.max_keys, ex->scratch.attn_partial,
+                                             ex->scratch.attn_partial_bytes, ex->attn, &launches);
+            if (e != cudaSuccess) return e;
+            STEP_TRY(launch_to_operand(s, ex->attn, nullptr, nullptr, T, c.q_heads * c.head_dim, ex->op_attn));
+        }
+        // attention output projection, residual add, operand form of ffn_norm(hidden)
+        a = GemvArgs{};
+        a.members = T; a.eps = c.rms_eps; a.error_flag = ex->d_error;
+        a.n_segments = 1;
+        a.seg[0] = segment_of(t[kAttnOutput], ex->hidden);
+        a.k = c.q_heads * c.head_dim;
+        a.in = ex->op_attn;
+        a.in_has_norm = 0;
+        a.epilogue = kResidual;
+        a.out = ex->op_hidden;
+        a.out_norm_weight = (const float*)t[kFfnNorm].raw;
+        STEP_TRY(launch_gemv_mma(s, a, pdl));
+        // gate | up with the SwiGLU epilogue, operand form of the gated product
+        a = GemvArgs{};
+        a.members = T; a.eps = c.rms_eps; a.error_flag = ex->d_error;
+        a.n_segments = 2;
+        a.seg[0] = segment_of(t[kFfnGate], ex->gate);
+        a.seg[1] = segment_of(t[kFfnUp], ex->up);
+        a.k = c.hidden;
+        a.in = ex->op_hidden;
+        a.in_has_norm = 1;
+        a.epilogue = kSwiGLU;
+        a.out = ex->op_act;
+        STEP_TRY(launch_gemv_mma(s, a, pdl));
+        // down projection, residual add, operand form of the next norm (next layer's or the output norm)
+        a = GemvArgs{};
+        a.members = T; a.eps = c.rms_eps; a.error_flag = ex->d_error;
+        a.n_segments = 1;
+        a.seg[0] = segment_of(t[kFfnDown], ex->hidden);
+        a.k = c.ffn;
+        a.in = ex->op_act;
+        a.in_has_norm = 0;
+        a.epilogue = kResidual;
+        a.out = ex->op_hidden;
+        a.out_norm_weight = l + 1 < c.layers ? (const float*)ex->lt(l + 1, kAttnNorm).raw : (const float*)ex->output_norm.raw;
+        STEP_TRY(launch_gemv_mma(s, a, pdl));
+    }
+    if (plan.n_sample > 0) {
+        ActOperand head = ex->op_hidden;  // already normalised with output_norm
+        if (plan.n_sample != T) {
+            STEP_TRY(launch_to_operand(s, ex->hidden, ex->meta.sample_token, (const float*)ex->output_norm.raw,
+                                       plan.n_sample, c.hidden, ex->op_head));
+            head = ex->op_head;
+        }
+        GemvArgs a{};
+        a.members = plan.n_sample; a.eps = c.rms_eps; a.error_flag = ex->d_error;
+        a.n_segments = 1;
+        a.seg[0] = segment_of(ex->output, ex->logits);
+        a.k = c.hidden;
+        a.in = head;
+        a.in_has_norm = 1;
+        a.epilogue = kStore;
+        STEP_TRY(launch_gemv_mma(s, a, pdl));
+    }
+    return cudaSuccess;
+}
+
+bool decode_family_applies(const ribn_b200_executor* ex, const StepPlan& plan) {
+    if (ex->cfg.flags & RIBN_B200_FLAG_REFERENCE_KERNELS) return false;
+    if (plan.n_tokens > kGemvMaxMembers || !ex->output.packed.ready()) return false;
+    for (const Tensor& t : ex->layer_tensors) {
+        if (t.type != kF32 && !t.packed.ready()) return false;
+    }
+    return true;
 }
 
 cudaError_t run_step(ribn_b200_executor* ex, const StepPlan& plan, int& launches) {
@@ -200,68 +324,10 @@ cudaError_t run_step(ribn_b200_executor* ex, const StepPlan& plan, int& launches
                                   ex->d_page_tables, ex->pages_per_sequence, ex->meta));
     STEP_TRY(launch_embedding(s, ex->token_embd.type, ex->token_embd.raw, c.hidden, c.vocab, ex->meta.token_id, T,
                               ex->hidden));
-    for (int l = 0; l < c.layers; ++l) {
-        Tensor* t = &ex->lt(l, 0);
-        {
-            Tensor qkv[3] = {t[kAttnQ], t[kAttnK], t[kAttnV]};
-            float* outs[3] = {ex->q, ex->k, ex->v};
-            // q|k|v share the fused-norm input; K and V may differ in type (Q4_K / Q6_K).
-            cudaError_t e = project(ex, launches, qkv, 3, ex->hidden, (const float*)t[kAttnNorm].raw, ex->normed, T,
-                                    outs, kStore);
-            if (e != cudaSuccess) return e;
-        }
-        __half* ck = ex->cache_k + (long long)l * ex->layer_stride;
-        __half* cv = ex->cache_v + (long long)l * ex->layer_stride;
-        STEP_TRY(launch_qk_norm_rope_append(s, ex->q, ex->k, ex->v, (const float*)t[kAttnQNorm].raw,
-                                            (const float*)t[kAttnKNorm].raw, ex->inv_freq, ex->meta.token_pos,
-                                            ex->meta.token_slot, T, c.q_heads, c.kv_heads, c.head_dim, c.rms_eps,
-                                            ck, cv));
-        if (c.flags & RIBN_B200_FLAG_REFERENCE_KERNELS) {
-            STEP_TRY(launch_attention_ref(s, ex->q, ck, cv, ex->d_page_tables, ex->pages_per_sequence,
-                                          ex->meta.token_seq, ex->meta.token_pos, T, c.q_heads, c.kv_heads,
-                                          c.head_dim, 0, ex->attn));
-        } else {
-            cudaError_t e = launch_attention(s, ex->q, ck, cv, ex->d_page_tables, ex->pages_per_sequence,
-                                             ex->meta.token_seq, ex->meta.token_pos, T, c.q_heads, c.kv_heads,
-                                             c.head_dim, 0, plan.max_keys, ex->scratch.attn_partial,
-                                             ex->scratch.attn_partial_bytes, ex->attn, &launches);
-            if (e != cudaSuccess) return e;
-        }
-        {
-            float* outs[1] = {ex->hidden};
-            cudaError_t e = project(ex, launches, &t[kAttnOutput], 1, ex->attn, nullptr, nullptr, T, outs, kResidual);
-            if (e != cudaSuccess) return e;
-        }
-        {
-            Tensor gu[2] = {t[kFfnGate], t[kFfnUp]};
-            float* outs[2] = {ex->gate, ex->up};
-            cudaError_t e = project(ex, launches, gu, 2, ex->hidden, (const float*)t[kFfnNorm].raw, ex->normed, T,
-                                    outs, kSwiGLU);
-            if (e != cudaSuccess) return e;
-        }
-        {
-            float* outs[1] = {ex->hidden};
-            cudaError_t e = project(ex, launches, &t[kFfnDown], 1, ex->gate, nullptr, nullptr, T, outs, kResidual);
-            if (e != cudaSuccess) return e;
-        }
-    }
+    cudaError_t e = decode_family_applies(ex, plan) ? run_layers_decode(ex, plan, launches)
+                                                    : run_layers_reference(ex, plan, launches);
+    if (e != cudaSuccess) return e;
     if (plan.n_sample > 0) {
-        // Only sampling rows reach the head (crates/nvidia/src/decode.rs:686-704).
-        STEP_TRY(launch_rms_norm_gather(s, ex->hidden, ex->meta.sample_token, (const float*)ex->output_norm.raw,
-                                        plan.n_sample, c.hidden, c.rms_eps, ex->head_in));
-        for (int m0 = 0; m0 < plan.n_sample; m0 += kGemvMaxMembers) {
-            const int members = std::min(kGemvMaxMembers, plan.n_sample - m0);
-            float* outs[1] = {ex->logits + (long long)m0 * c.vocab};
-            if (fast_ok(ex, ex->output, members)) {
-                cudaError_t e = project(ex, launches, &ex->output, 1, ex->head_in + (long long)m0 * c.hidden, nullptr,
-                                        nullptr, members, outs, kStore);
-                if (e != cudaSuccess) return e;
-            } else {
-                STEP_TRY(launch_gemv_ref(s, ex->output.type, ex->output.raw, ex->output.rows, ex->output.cols,
-                                         ex->head_in, plan.n_sample, ex->logits, false));
-                break;
-            }
-        }
         STEP_TRY(launch_argmax(s, ex->logits, plan.n_sample, c.vocab, ex->d_sampled, ex->meta.sample_slot,
                                ex->d_next_token));
     }
@@ -334,6 +400,7 @@ int ribn_b200_destroy(ribn_b200_executor* ex) {
     if (ex->h_rows) cudaFreeHost(ex->h_rows);
     if (ex->h_tokens) cudaFreeHost(ex->h_tokens);
     if (ex->h_sampled) cudaFreeHost(ex->h_sampled);
+    if (ex->h_error) cudaFreeHost(ex->h_error);
     cudaEventDestroy(ex->ev_start);
     cudaEventDestroy(ex->ev_done);
     cudaStreamDestroy(ex->stream);
@@ -541,6 +608,22 @@ int ribn_b200_finalize(ribn_b200_executor* ex) {
         ex->scratch.attn_partial_bytes = std::max(per_token, std::min(per_token * T, (size_t)256 << 20));
         CU_TRY(ex, dev_alloc(ex, (unsigned char**)&ex->scratch.attn_partial, ex->scratch.attn_partial_bytes));
     }
+    {
+        auto alloc_operand = [&](ActOperand* op, int k) -> cudaError_t {
+            cudaError_t e = dev_alloc(ex, &op->x, act_operand_x_elems(kGemvMaxMembers, k));
+            if (e == cudaSuccess) e = dev_alloc(ex, &op->s16, (size_t)kGemvMaxMembers * (k / 16));
+            if (e == cudaSuccess) e = dev_alloc(ex, &op->ss16, (size_t)kGemvMaxMembers * (k / 16));
+            return e;
+        };
+        CU_TRY(ex, alloc_operand(&ex->op_hidden, c.hidden));
+        CU_TRY(ex, alloc_operand(&ex->op_attn, c.q_heads * c.head_dim));
+        CU_TRY(ex, alloc_operand(&ex->op_act, c.ffn));
+        CU_TRY(ex, alloc_operand(&ex->op_head, c.hidden));
+        CU_TRY(ex, dev_alloc(ex, &ex->d_error, 1));
+        CU_TRY(ex, cudaMemsetAsync(ex->d_error, 0, sizeof(int), ex->stream));
+        CU_TRY(ex, cudaMallocHost((void**)&ex->h_error, sizeof(int)));
+        *ex->h_error = 0;
+    }
     CU_TRY(ex, cudaStreamSynchronize(ex->stream));
     ex->finalized = true;
     return RIBN_B200_OK;
@@ -713,6 +796,7 @@ int ribn_b200_submit(ribn_b200_executor* ex, const ribn_b200_batch_item* items, 
         CU_TRY(ex, cudaMemcpyAsync(ex->h_sampled, ex->d_sampled, (size_t)plan.n_sample * sizeof(uint32_t),
                                    cudaMemcpyDeviceToHost, ex->stream));
     }
+    CU_TRY(ex, cudaMemcpyAsync(ex->h_error, ex->d_error, sizeof(int), cudaMemcpyDeviceToHost, ex->stream));
     CU_TRY(ex, cudaEventRecord(ex->ev_done, ex->stream));
     *submission = p.id;
     return RIBN_B200_OK;
@@ -731,6 +815,10 @@ int ribn_b200_poll(ribn_b200_executor* ex, uint64_t submission, ribn_b200_comple
         // Any status other than NOT_READY is a fault (crates/nvidia/src/serving.rs:624-635).
         ex->faulted = true;
         return fail(ex, "device work failed: %s", cudaGetErrorString(q));
+    }
+    if (*ex->h_error != 0) {
+        ex->faulted = true;
+        return fail(ex, "a device-side bounded wait expired (code %d)", *ex->h_error);
     }
     if (capacity < p.items.size()) return fail(ex, "completion buffer too small");
     cudaEventElapsedTime(&ex->last_ms, ex->ev_start, ex->ev_done);

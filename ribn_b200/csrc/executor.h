@@ -95,6 +95,10 @@ struct ribn_b200_executor {
     float *hidden = nullptr, *normed = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr,
           *gate = nullptr, *up = nullptr, *proj = nullptr, *head_in = nullptr, *logits = nullptr;
     ribn::StepScratch scratch;
+    // tensor-core operand forms of the activations (decode rows on the fast path)
+    ribn::ActOperand op_hidden, op_attn, op_act, op_head;
+    int* d_error = nullptr;    // raised by a kernel whose bounded wait expired
+    int* h_error = nullptr;    // pinned copy read at poll
     std::vector<void*> allocations;
 
     ribn::Tensor& lt(int layer, int which) { return layer_tensors[(size_t)layer * ribn::kLayerTensors + which]; }

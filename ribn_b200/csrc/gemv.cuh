@@ -1,16 +1,18 @@
 // Tile-major weight repack and the tensor-core GEMV built on it.
 //
 // A packed matrix is a sequence of tiles of 16 output rows x 256 inputs,
-// ordered k-tile-major inside each row tile, so that one warp streams
-// contiguous 16-byte-aligned memory with 128-bit loads.  The byte order
-// inside a tile is chosen so that each lane's loads are exactly the operands
-// of its `mma.sync.m16n8k16` A fragment (rows g and g + 8, g = lane / 4;
-// for each 16-wide k step the four inputs 4t .. 4t + 3, t = lane % 4).
-// Per type (sizes per tile equal 16 raw GGUF blocks, no padding bytes):
+// ordered k-tile-major inside each row tile, so that a CTA streams one
+// contiguous, 16-byte-aligned byte range with bulk (TMA) copies.  The byte
+// order inside a tile is chosen so that each lane's 128-bit shared-memory
+// reads are exactly the operands of its `mma.sync.m16n8k16` A fragment (rows
+// g and g + 8, g = lane / 4; for each 16-wide k step the four inputs
+// 4t .. 4t + 3, t = lane % 4).  Per type (a tile is exactly 16 raw GGUF
+// super-blocks' worth of bytes, no padding):
 //   Q4_K 2304 B: 4 x 512 B nibble chunks (group pairs) + 16 x 16 B headers
 //   Q6_K 3360 B: 4 x 512 B low nibbles + 2 x 512 B high bits + 16 x 16 B scales + 16 x 2 B d
 //   Q8_0 4352 B: 8 x 512 B offset-binary bytes (q + 128) + 16 x 16 B of f16 d
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -52,6 +54,29 @@ inline size_t packed_bytes(int type, long long n, long long k) {
 void repack_host(int type, const unsigned char* raw, long long n, long long k, unsigned char* out,
                  int threads);
 
+// Activations in tensor-core operand form.  Each input vector x[K] is carried
+// as three bfloat16 vectors hi + mid + lo (8 + 8 + 8 significant bits: the
+// F32 value to within one ulp, with F32's range), plus the F32 sums of the
+// reconstructed values over every 16 consecutive inputs, and -- when an
+// RMSNorm precedes the projection -- the sums of squares of the *unscaled*
+// input over the same 16-element spans.  The norm weight is already folded
+// into x; the consumer multiplies its result by 1 / sqrt(mean square + eps).
+// The kernel that produces x writes this form in its epilogue, so the
+// consuming GEMV loads its B operand with plain bulk copies.
+struct ActOperand {
+    __nv_bfloat16* x = nullptr;  // [members][3][k]
+    float* s16 = nullptr;        // [members][k / 16]
+    float* ss16 = nullptr;       // [members][k / 16]
+};
+
+inline size_t act_operand_x_elems(int members, int k) { return (size_t)members * 3 * k; }
+
+// f32 activations -> operand form (standalone; producers fuse the same math).
+// norm_weight == nullptr: x is used as is and ss16 is not written.
+// `index` (optional) gathers rows of x.
+cudaError_t launch_to_operand(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,
+                              int members, int k, ActOperand out);
+
 // One fused GEMV launch covers up to three matrices that share the input
 // vector (q|k|v, gate|up) as consecutive row-tile segments.
 struct GemvSegment {
@@ -59,29 +84,38 @@ struct GemvSegment {
     int type;
     int n;          // valid output rows
     int row_tiles;
-    float* y;       // [members][n] output (or residual stream for kResidual)
+    float* y;       // [members][n] F32 output (the residual stream for kResidual)
 };
 
 enum GemvEpilogue : int {
     kStore = 0,     // y = W x
     kResidual = 1,  // y += W x           (y is the residual stream)
-    kSwiGLU = 2     // two segments (gate, up): out = silu(gate x) * (up x), written to segment 0's y
+    kSwiGLU = 2     // two segments (gate, up): silu(gate x) * (up x)
 };
 
 struct GemvArgs {
     GemvSegment seg[3];
     int n_segments;
     int k;
-    int members;             // 1..4 input vectors
-    const float* x;          // [members][k] F32 activations
-    const float* norm_weight;  // optional RMSNorm weight applied to x first (nullptr: none)
+    int members;          // 1..kGemvMaxMembers input vectors
+    ActOperand in;        // B operand
+    int in_has_norm;      // multiply the result by rsqrt(mean(ss16) + eps)
     float eps;
     int epilogue;
+    // Optional operand-form copy of the result (kResidual: of the updated
+    // residual stream times `out_norm_weight`; kSwiGLU: of the gated product).
+    ActOperand out;
+    const float* out_norm_weight;
+    float* swiglu_f32;    // optional F32 copy of the gated product [members][n]
+    int* error_flag;      // set non-zero when a bounded wait gives up
 };
 
-cudaError_t launch_gemv_mma(cudaStream_t stream, const GemvArgs& args, bool dependent_launch);
+constexpr int kGemvMaxMembers = 2;
 
-constexpr int kGemvMaxMembers = 4;
+// Enqueue the GEMV.  `programmatic` launches it as a programmatic dependent of
+// the previous kernel in the stream, so its weight prefetch overlaps that
+// kernel's tail.
+cudaError_t launch_gemv_mma(cudaStream_t stream, const GemvArgs& args, bool programmatic);
 
 // Scratch shared by the step kernels: per-span attention accumulators.
 struct StepScratch {

@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "gemv.cuh"
+
 namespace ribn {
 
 constexpr int kPageTokens = 16;  // KV_PAGE_TOKENS, crates/qwen/src/gguf.rs:16
@@ -96,11 +98,39 @@ cudaError_t launch_attention_ref(cudaStream_t stream, const float* q, const __ha
 // as many launches as that scratch requires.  `launches` (optional) is
 // incremented per kernel launch.
 constexpr int kAttnSpanKeys = 64;
+constexpr int kAttnMaxSpans = 1024;  // 65536 keys per token
 cudaError_t launch_attention(cudaStream_t stream, const float* q, const __half* cache_k, const __half* cache_v,
                              const int32_t* page_tables, int pages_per_sequence, const int32_t* token_seq,
                              const int32_t* token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,
                              int window, int max_keys, float* partial, size_t partial_bytes, float* out,
                              int* launches);
+
+// Decode form of the same attention for rows that add exactly one token: it
+// also applies the per-head Q/K RMSNorm and rotary to the raw projections,
+// appends the token's K/V row to the paged cache, and can emit the result in
+// tensor-core operand form (K = q_heads * head_dim) for the output projection.
+struct DecodeAttention {
+    const float* q;   // [T][q_heads][hd] raw q projection
+    const float* k;   // [T][kv_heads][hd] raw k projection
+    const float* v;   // [T][kv_heads][hd]
+    const float* q_norm;
+    const float* k_norm;
+    const float* inv_freq;
+    float eps;
+    __half* cache_k;
+    __half* cache_v;
+    const int32_t* page_tables;
+    int pages_per_sequence;
+    const int32_t* token_seq;
+    const int32_t* token_pos;
+    const int32_t* token_slot;
+    int n_tokens, q_heads, kv_heads, head_dim, window, max_keys;
+    float* partial;
+    size_t partial_bytes;
+    float* out;
+    ActOperand operand;
+};
+cudaError_t launch_attention_decode(cudaStream_t stream, const DecodeAttention& d, int* launches);
 
 // Seeded F16 K/V for the first `tokens` logical positions of one sequence, every layer.
 cudaError_t launch_synth_kv(cudaStream_t stream, __half* cache_k, __half* cache_v, long long layer_stride,

@@ -118,6 +118,14 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
                     (int)std::max(1u, std::min(16u, std::thread::hardware_concurrency())));
         unsigned char* d_w = s.upload(packed.data(), packed.size());
         OP_PTR(d_w);
+        ActOperand op;
+        op.x = (__nv_bfloat16*)s.alloc<unsigned short>(act_operand_x_elems(members, (int)cols));
+        op.s16 = s.alloc<float>((size_t)members * (cols / 16));
+        op.ss16 = nullptr;
+        int* d_err = s.alloc<int>(1);
+        OP_PTR(op.x); OP_PTR(op.s16); OP_PTR(d_err);
+        OP_TRY(cudaMemsetAsync(d_err, 0, sizeof(int), s.stream));
+        OP_TRY(launch_to_operand(s.stream, d_x, nullptr, nullptr, members, (int)cols, op));
         for (int m0 = 0; m0 < members; m0 += kGemvMaxMembers) {
             GemvArgs a{};
             a.n_segments = 1;
@@ -125,12 +133,16 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
                                    d_y + (size_t)m0 * rows};
             a.k = (int)cols;
             a.members = std::min(kGemvMaxMembers, members - m0);
-            a.x = d_x + (size_t)m0 * cols;
-            a.norm_weight = nullptr;
+            a.in.x = op.x + (size_t)m0 * 3 * cols;
+            a.in.s16 = op.s16 + (size_t)m0 * (cols / 16);
+            a.in_has_norm = 0;
             a.eps = 0.0f;
             a.epilogue = kStore;
+            a.error_flag = d_err;
             OP_TRY(launch_gemv_mma(s.stream, a, false));
         }
+        int err = 0;
+        if (!s.download(&err, d_err, 1) || err != 0) return RIBN_B200_ERROR;
     }
     return s.download(y, d_y, (size_t)members * rows) ? RIBN_B200_OK : RIBN_B200_ERROR;
 }
