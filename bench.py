@@ -33,6 +33,9 @@ MODELS = {
                      rope_base=1.0e6, rms_eps=1.0e-6),
     "qwen3-0.6b": dict(layers=28, hidden=1024, q_heads=16, kv_heads=8, head_dim=128, ffn=3072, vocab=151936,
                        rope_base=1.0e6, rms_eps=1.0e-6),
+    # profiling aid: Qwen3-8B layer and head shapes, 4 layers (fits an ncu capture's size rule)
+    "qwen3-8b-4l": dict(layers=4, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, ffn=12288, vocab=151936,
+                        rope_base=1.0e6, rms_eps=1.0e-6),
     "tiny": dict(layers=2, hidden=512, q_heads=8, kv_heads=2, head_dim=128, ffn=1024, vocab=2048,
                  rope_base=1.0e6, rms_eps=1.0e-6),
 }

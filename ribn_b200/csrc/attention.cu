@@ -20,7 +20,6 @@
 //
 // The reference's two-pass form with a global scores buffer
 // (crates/nvidia/src/model_ops.rs:441-545) is replaced, not translated.
-#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math.h>
 
@@ -28,6 +27,7 @@
 
 #include "gemv.cuh"
 #include "kernels.cuh"
+#include "operand.cuh"
 
 namespace ribn {
 
@@ -42,15 +42,6 @@ __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
-}
-
-__device__ __forceinline__ float split3(float v, __nv_bfloat16& hi, __nv_bfloat16& mid, __nv_bfloat16& lo) {
-    hi = __float2bfloat16_rn(v);
-    const float r1 = v - __bfloat162float(hi);
-    mid = __float2bfloat16_rn(r1);
-    const float r2 = r1 - __bfloat162float(mid);
-    lo = __float2bfloat16_rn(r2);
-    return __bfloat162float(hi) + __bfloat162float(mid) + __bfloat162float(lo);
 }
 
 struct AttnArgs {
@@ -236,28 +227,23 @@ __global__ void attention_span_kernel(const AttnArgs a) {
         acc[d] += __shfl_xor_sync(0xffffffffu, acc[d], 8);
         acc[d] += __shfl_xor_sync(0xffffffffu, acc[d], 16);
     }
-    if (kg != 0) return;
     if (spans == 1) {
-        const float inv = 1.0f / total;
-        float* op = a.out + ((long long)t * a.q_heads + qh) * HD + dc * CH;
+        if (kg == 0) {
+            const float inv = 1.0f / total;
+            float* op = a.out + ((long long)t * a.q_heads + qh) * HD + dc * CH;
 #pragma unroll
-        for (int d = 0; d < CH; ++d) { acc[d] *= inv; op[d] = acc[d]; }
-        if (a.operand.x != nullptr) {
-            const int K = a.q_heads * HD, m = t - a.token_base;
-            __nv_bfloat16* ox = a.operand.x + (size_t)m * 3 * K + (size_t)qh * HD + dc * CH;
-#pragma unroll
-            for (int c = 0; c < CH / 16; ++c) {
-                float sum = 0.0f;
-#pragma unroll
-                for (int d = 0; d < 16; ++d) {
-                    __nv_bfloat16 hi, mid, lo;
-                    sum += split3(acc[c * 16 + d], hi, mid, lo);
-                    ox[c * 16 + d] = hi; ox[K + c * 16 + d] = mid; ox[2 * (size_t)K + c * 16 + d] = lo;
-                }
-                a.operand.s16[(size_t)m * (K / 16) + (qh * HD + dc * CH) / 16 + c] = sum;
-            }
+            for (int d = 0; d < CH; ++d) { acc[d] *= inv; op[d] = acc[d]; qs[dc * CH + d] = acc[d]; }
         }
-    } else {
+        if (a.operand.dig != nullptr) {
+            // back to one input per lane: lane takes dims lane + 32 i of this head
+            __syncwarp();
+            ActOperand op = a.operand;
+            op.ss32 = nullptr;
+            const int K = a.q_heads * HD, m = t - a.token_base;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) operand_store_span(op, m, K, (qh * HD) / 32 + i, lane, qs[lane + 32 * i], 0.0f);
+        }
+    } else if (kg == 0) {
         float* pp = a.partial + (((long long)(t - a.token_base) * a.q_heads + qh) * a.max_spans + span) * (HD + 2);
 #pragma unroll
         for (int d = 0; d < CH; ++d) pp[dc * CH + d] = acc[d];
@@ -296,15 +282,10 @@ __global__ void attention_merge_kernel(const AttnArgs a) {
     for (int s = 0; s < spans; ++s) sum = fmaf(pp[s * (HD + 2) + d], weight[s], sum);
     const float value = sum / denom_s;
     a.out[((long long)t * a.q_heads + qh) * HD + d] = value;
-    if (a.operand.x != nullptr) {
-        const int K = a.q_heads * HD, m = t - a.token_base;
-        __nv_bfloat16 hi, mid, lo;
-        float recon = split3(value, hi, mid, lo);
-        __nv_bfloat16* ox = a.operand.x + (size_t)m * 3 * K + (size_t)qh * HD + d;
-        ox[0] = hi; ox[K] = mid; ox[2 * (size_t)K] = lo;
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) recon += __shfl_xor_sync(0xffffffffu, recon, o);
-        if ((d & 15) == 0) a.operand.s16[(size_t)m * (K / 16) + (qh * HD + d) / 16] = recon;
+    if (a.operand.dig != nullptr) {
+        ActOperand op = a.operand;
+        op.ss32 = nullptr;
+        operand_store_span(op, t - a.token_base, a.q_heads * HD, (qh * HD + d) / 32, d & 31, value, 0.0f);
     }
 }
 
@@ -320,7 +301,7 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
         if (a.partial == nullptr || partial_bytes < per_token) return cudaErrorInvalidValue;
         chunk = (int)std::min<size_t>((size_t)n_tokens, partial_bytes / per_token);
     }
-    if (a.operand.x != nullptr && chunk < n_tokens) return cudaErrorInvalidValue;  // operand rows are launch-relative
+    if (a.operand.dig != nullptr && chunk < n_tokens) return cudaErrorInvalidValue;  // operand rows are launch-relative
     const size_t smem = (size_t)q_per_kv * HD * sizeof(float) + 2 * HD * sizeof(__half);
     for (int base = 0; base < n_tokens; base += chunk) {
         const int n = std::min(chunk, n_tokens - base);

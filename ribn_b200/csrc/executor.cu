@@ -610,9 +610,10 @@ int ribn_b200_finalize(ribn_b200_executor* ex) {
     }
     {
         auto alloc_operand = [&](ActOperand* op, int k) -> cudaError_t {
-            cudaError_t e = dev_alloc(ex, &op->x, act_operand_x_elems(kGemvMaxMembers, k));
-            if (e == cudaSuccess) e = dev_alloc(ex, &op->s16, (size_t)kGemvMaxMembers * (k / 16));
-            if (e == cudaSuccess) e = dev_alloc(ex, &op->ss16, (size_t)kGemvMaxMembers * (k / 16));
+            cudaError_t e = dev_alloc(ex, &op->dig, (size_t)kGemvMaxMembers * 3 * k);
+            if (e == cudaSuccess) e = dev_alloc(ex, &op->sx, (size_t)kGemvMaxMembers * (k / 32));
+            if (e == cudaSuccess) e = dev_alloc(ex, &op->sxs16, (size_t)kGemvMaxMembers * (k / 16));
+            if (e == cudaSuccess) e = dev_alloc(ex, &op->ss32, (size_t)kGemvMaxMembers * (k / 32));
             return e;
         };
         CU_TRY(ex, alloc_operand(&ex->op_hidden, c.hidden));

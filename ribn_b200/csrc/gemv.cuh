@@ -12,7 +12,6 @@
 //   Q6_K 3360 B: 4 x 512 B low nibbles + 2 x 512 B high bits + 16 x 16 B scales + 16 x 2 B d
 //   Q8_0 4352 B: 8 x 512 B offset-binary bytes (q + 128) + 16 x 16 B of f16 d
 #pragma once
-#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -54,25 +53,34 @@ inline size_t packed_bytes(int type, long long n, long long k) {
 void repack_host(int type, const unsigned char* raw, long long n, long long k, unsigned char* out,
                  int threads);
 
-// Activations in tensor-core operand form.  Each input vector x[K] is carried
-// as three bfloat16 vectors hi + mid + lo (8 + 8 + 8 significant bits: the
-// F32 value to within one ulp, with F32's range), plus the F32 sums of the
-// reconstructed values over every 16 consecutive inputs, and -- when an
-// RMSNorm precedes the projection -- the sums of squares of the *unscaled*
-// input over the same 16-element spans.  The norm weight is already folded
-// into x; the consumer multiplies its result by 1 / sqrt(mean square + eps).
-// The kernel that produces x writes this form in its epilogue, so the
-// consuming GEMV loads its B operand with plain bulk copies.
+// Activations in tensor-core operand form: signed 8-bit digits for the
+// integer MMA.  Every 32 consecutive inputs share a scale sx = max|x| / 127 and
+// each input is carried as three digits d1, d2, d3 in [-127, 127] with
+//     x ~= sx * (d1 + d2 / 128 + d3 / 16384)           (|error| <= max|x| * 2.4e-7)
+// so the integer dot products are exact and the only rounding is this one.
+// Inside a 32-span the bytes are permuted so that lane t's MMA fragment
+// (inputs 4t..4t+3 and 16+4t..16+4t+3) is one 8-byte word:
+//     position(k) = ((k & 15) >> 2) * 8 + ((k >> 4) & 1) * 4 + (k & 3).
+// Alongside: `sxs16` = sx * (sum of the digit values over each 16-span), used
+// to remove the formats' offsets (Q4_K minimum, Q6_K -32, Q8_0 -128), and,
+// when an RMSNorm precedes the projection, `ss32` = sums of squares of the
+// *unscaled* input per 32-span.  The norm weight is already folded into x; the
+// consumer multiplies its result by 1 / sqrt(mean square + eps).  The kernel
+// that produces x writes this form in its epilogue, so the consuming GEMV
+// loads its B operand with plain bulk copies.
 struct ActOperand {
-    __nv_bfloat16* x = nullptr;  // [members][3][k]
-    float* s16 = nullptr;        // [members][k / 16]
-    float* ss16 = nullptr;       // [members][k / 16]
+    signed char* dig = nullptr;  // [members][3][k]
+    float* sx = nullptr;         // [members][k / 32]
+    float* sxs16 = nullptr;      // [members][k / 16]
+    float* ss32 = nullptr;       // [members][k / 32]
 };
 
-inline size_t act_operand_x_elems(int members, int k) { return (size_t)members * 3 * k; }
+__host__ __device__ inline int operand_position(int k) {
+    return (k & ~31) + (((k & 15) >> 2) * 8) + (((k >> 4) & 1) * 4) + (k & 3);
+}
 
 // f32 activations -> operand form (standalone; producers fuse the same math).
-// norm_weight == nullptr: x is used as is and ss16 is not written.
+// norm_weight == nullptr: x is used as is and ss32 is not written.
 // `index` (optional) gathers rows of x.
 cudaError_t launch_to_operand(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,
                               int members, int k, ActOperand out);
@@ -99,7 +107,7 @@ struct GemvArgs {
     int k;
     int members;          // 1..kGemvMaxMembers input vectors
     ActOperand in;        // B operand
-    int in_has_norm;      // multiply the result by rsqrt(mean(ss16) + eps)
+    int in_has_norm;      // multiply the result by rsqrt(mean(ss32) + eps)
     float eps;
     int epilogue;
     // Optional operand-form copy of the result (kResidual: of the updated

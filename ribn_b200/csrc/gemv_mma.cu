@@ -2,27 +2,30 @@
 //
 // Why tensor cores for a GEMV: at B200's HBM rate one SM receives ~41 Q4_K
 // weights per clock, which leaves ~3 issue slots per weight across its 128
-// lanes.  A SIMT decode (extract, int->float, FMA) needs more than that, so
-// the dot products run on `mma.sync.m16n8k16` and the lanes only unpack.
-// A weight enters the A operand as the bfloat16 `0x4300 | q` = 128 + q (one
-// LOP3 per two weights, exact); the 128 and the formats' own offsets (Q4_K
-// minimum, Q6_K -32, Q8_0 -128) are removed through per-16-input sums of the
-// activations.  Block scales multiply the F32 accumulator once per 32 (Q4_K,
-// Q8_0 nibble planes) or 16 (Q6_K) inputs.  Activations enter the B operand
-// as three bfloat16 columns per input vector (hi + mid + lo, see ActOperand),
-// produced by the previous kernel's epilogue.
+// lanes -- and integer/logic instructions issue at half rate.  A SIMT decode
+// (extract, int->float, FMA) needs far more than that, so the dot products run
+// on the integer tensor-core path, `mma.sync.m16n8k32.s32.u8.s8`, where a
+// quantised weight needs no conversion at all: four packed nibbles become four
+// u8 operands with one AND (a Q8_0 byte is an operand as stored), products and
+// sums are exact in int32, and one F32 scale per 32 (Q4_K, Q8_0) or 16 (Q6_K)
+// inputs folds the block's scale and the activation span's scale into the
+// accumulator.  The formats' offsets (Q4_K minimum, Q6_K -32, Q8_0 -128) are
+// removed through per-16-input sums of the activations.  Activations arrive as
+// three signed 8-bit digits per input (see ActOperand), produced by the
+// previous kernel's epilogue.
 //
 // Execution: one persistent CTA per SM.  A producer warp streams the CTA's
 // contiguous byte range of weight tiles into a shared-memory ring with bulk
 // (TMA) copies completing on mbarriers; it starts before the programmatic
 // dependency on the previous kernel resolves, so weights are already in
-// flight while that kernel drains.  Eight consumer warps split each row
-// tile's k tiles, reduce through shared memory in a fixed order
-// (deterministic results), and warp 0 runs the epilogue (store, residual add,
-// SwiGLU, and the operand form of the result for the next projection).
+// flight while that kernel drains.  Sixteen consumer warps in two teams take
+// alternate ring stages; each warp owns one 16 x 256 tile of a stage.  Per
+// unit of 32 output rows the warps leave their partial sums in shared memory
+// and move on; a dedicated epilogue warp adds them in a fixed order
+// (deterministic results) and applies the epilogue: store, residual add,
+// SwiGLU, and the operand form of the result for the next projection.
 // Every wait is bounded: on expiry the kernel raises an error flag and runs
 // to completion without waiting again.
-#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <string.h>
 
@@ -32,6 +35,7 @@
 
 #include "blocks.cuh"
 #include "gemv.cuh"
+#include "operand.cuh"
 
 namespace ribn {
 
@@ -40,9 +44,9 @@ namespace ribn {
 // ---------------------------------------------------------------------------
 namespace {
 
-// stored [k0, k2, k1, k3]: (w & 0x000F000F) -> (k0, k1), ((w >> 8) & ...) -> (k2, k3)
+// four consecutive inputs of one row: one 32-bit A-fragment register of the integer MMA
 inline void put4(unsigned char* dst, const unsigned char* src, unsigned char flip) {
-    dst[0] = src[0] ^ flip; dst[1] = src[2] ^ flip; dst[2] = src[1] ^ flip; dst[3] = src[3] ^ flip;
+    dst[0] = src[0] ^ flip; dst[1] = src[1] ^ flip; dst[2] = src[2] ^ flip; dst[3] = src[3] ^ flip;
 }
 
 void repack_tile(int type, const unsigned char* raw, long long n, long long k_blocks_per_row, int rt, int kb,
@@ -141,14 +145,19 @@ namespace {
 constexpr int kConsumerWarps = 16;  // two teams of eight; a team consumes every other stage
 constexpr int kTeamWarps = 8;
 constexpr int kStageTiles = 8;      // tiles per bulk copy / ring slot (one per warp of a team)
-constexpr int kHdrStride = 20;      // floats per header row (80 bytes: conflict-free across the 8 row groups)
+constexpr int kProducerWarp = kConsumerWarps;
+constexpr int kEpilogueWarp = kConsumerWarps + 1;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;  // + one producer warp
-constexpr int kXPad = 32;                        // elements of padding per activation column (64 bytes)
-constexpr uint32_t kSpinLimit = 1u << 22;        // bounded waits: iterations before giving up
-constexpr uint32_t kLowMask = 0x000F000Fu;
-constexpr uint32_t kTopMask = 0x00300030u;
-constexpr uint32_t kBias = 0x43004300u;          // bfloat16 128.0 in both halves: 0x4300 | q == 128 + q for q < 128
+constexpr int kThreads = (kConsumerWarps + 2) * 32;
+constexpr int kMaxRuns = 4;         // row-tile runs per unit: 2 tiles of one matrix, or 2 x (gate, up)
+constexpr int kHdrStride = 20;      // floats per header row: 16 scales + offset sum + pad (conflict-free rows)
+constexpr int kPlanePad = 32;       // bytes between activation digit planes (distinct banks per plane)
+constexpr uint32_t kSpinLimit = 1u << 22;  // bounded waits: iterations before giving up
+constexpr uint32_t kNibbles = 0x0F0F0F0Fu;
+constexpr uint32_t kTopBits = 0x30303030u;
+constexpr int kMagicInt = 0x4B400000;      // bits of 12582912.0f: int accumulate on top of it, read as float
+constexpr float kMagic = 12582912.0f;
+constexpr int kBarFull = 1, kBarFree = 3;  // named barriers: full[0..1] = 1, 2; free[0..1] = 3, 4
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -185,266 +194,271 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
+// Named barriers shared by the consumer warps and the epilogue warp (544 threads).
+__device__ __forceinline__ void bar_arrive(int id) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "n"(kConsumerThreads + 32) : "memory");
+}
+__device__ __forceinline__ void bar_sync(int id) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(kConsumerThreads + 32) : "memory");
+}
 __device__ __forceinline__ void consumer_barrier() {
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+    asm volatile("bar.sync 5, %0;" ::"n"(kConsumerThreads) : "memory");
 }
 
-__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
+// D = A(u8, 16 x 32) * B(s8, 32 x 8) + magic; the result registers are read as floats.
+__device__ __forceinline__ void imma_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
     asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(kMagicInt));
 }
-
-// (w & mask) | other in one LOP3
-__device__ __forceinline__ uint32_t pick(uint32_t w, uint32_t mask, uint32_t other = kBias) {
+__device__ __forceinline__ void imma_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(kMagicInt));
+}
+// (a & mask) | other in one LOP3
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t other) {
     uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(w), "r"(mask), "r"(other));  // (a & b) | c
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(other));
     return r;
+}
+// byte i of w as a float, without the conversion pipe
+__device__ __forceinline__ float byte_f32(uint32_t w, int i) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | (uint32_t)i)) - 8388608.0f;
 }
 
 struct Shared {
     unsigned char* ring;
-    __nv_bfloat16* xs;  // [cols][K + kXPad]
-    float* s16;         // [members][K / 16]
-    float* s32;         // [members][K / 32]
-    float* hdr;         // [kConsumerWarps][16][kHdrStride]
-    float* red;         // [2][kConsumerWarps][runs][16][8]
-    float* scale;       // [kGemvMaxMembers]
+    signed char* xq;   // [3 * members][K + kPlanePad] digit planes
+    float* sx;         // [members][K / 32]
+    float* sxs;        // [members][K / 16]
+    float* hdr;        // [kConsumerWarps][members][16][kHdrStride]
+    float* red;        // [2][kConsumerWarps][kMaxRuns][members][16]
+    float* scale;      // [kGemvMaxMembers]
     uint32_t full, empty, xbar;  // shared-space addresses of the mbarrier arrays
+    int K, members;
 };
 
 struct Accum {
     float c[4];  // (row g, col 2t), (row g, col 2t+1), (row g+8, col 2t), (row g+8, col 2t+1)
-    float s[2];  // offset terms of rows g, g+8 for the member whose sums this lane carries
+    float s[2];  // offset terms of rows g, g+8
 };
 
-__device__ __forceinline__ uint2 load_b(const Shared& sh, int stride, int g, int t, int cols, int k0) {
-    if (g < cols) return *reinterpret_cast<const uint2*>(sh.xs + (size_t)g * stride + k0 + 4 * t);
+// B fragment of MMA column g for the 32 inputs of span `span`: digit plane (g & 3) of member (g >> 2);
+// columns 3 and 7 and absent members are zero.
+__device__ __forceinline__ uint2 load_b(const Shared& sh, int g, int t, int span) {
+    if ((g & 3) < 3 && (g >> 2) < sh.members) {
+        const signed char* p = sh.xq + (size_t)((g >> 2) * 3 + (g & 3)) * (sh.K + kPlanePad) + span * 32 + 8 * t;
+        return *reinterpret_cast<const uint2*>(p);
+    }
     return make_uint2(0u, 0u);
 }
 
-__device__ __forceinline__ float byte_of(uint32_t w, int i) { return (float)((w >> (8 * i)) & 0xffu); }
-
-// One group of 32 (or 16) inputs: scale the MMA result into the accumulators
-// and add the offset term `coef * sum(x)` for the member this lane carries.
-__device__ __forceinline__ void fold(Accum& a, const float (&c)[4], float s0, float s1, float k0, float k1, float sv) {
-    a.c[0] = fmaf(s0, c[0], a.c[0]);
-    a.c[1] = fmaf(s0, c[1], a.c[1]);
-    a.c[2] = fmaf(s1, c[2], a.c[2]);
-    a.c[3] = fmaf(s1, c[3], a.c[3]);
-    a.s[0] = fmaf(k0, sv, a.s[0]);
-    a.s[1] = fmaf(k1, sv, a.s[1]);
+__device__ __forceinline__ void fold(Accum& a, const int (&c)[4], float s0, float s1) {
+    a.c[0] = fmaf(s0, __int_as_float(c[0]) - kMagic, a.c[0]);
+    a.c[1] = fmaf(s0, __int_as_float(c[1]) - kMagic, a.c[1]);
+    a.c[2] = fmaf(s1, __int_as_float(c[2]) - kMagic, a.c[2]);
+    a.c[3] = fmaf(s1, __int_as_float(c[3]) - kMagic, a.c[3]);
 }
 
-// ---- Q4_K: value = gs * q - gm, A = 128 + q  =>  gs * C - (128 gs + gm) * S --------
-__device__ __forceinline__ void tile_q4k(const unsigned char* tile, const Shared& sh, int stride, int cols, int members,
-                                         int kb, int warp, int lane, Accum& acc) {
-    const int g = lane >> 2, t = lane & 3;
-    uint4 qv[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) qv[j] = *reinterpret_cast<const uint4*>(tile + j * 512 + lane * 16);
-    float* hdr = sh.hdr + warp * (16 * kHdrStride);
+// ---- Q4_K: w = gs * q - gm  =>  (gs * sx) * C  -  gm * (sx * sum digits) ------------------------
+__device__ __forceinline__ void tile_q4k(const unsigned char* tile, const Shared& sh, int kb, float* hdr, int lane,
+                                         Accum& acc) {
+    const int g = lane >> 2, t = lane & 3, m = t >> 1;
     {
-        const int row = lane >> 1, sel = lane & 1;
+        // lane -> (row, half): scales and offsets of groups 4 half .. 4 half + 3, for every member
+        const int row = lane >> 1, half = lane & 1;
         const uint4 h = *reinterpret_cast<const uint4*>(tile + 2048 + row * 16);
         const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
         const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
-        const uint32_t sc_lo = h.y & 0x3F3F3F3Fu, sc_hi = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
-        const uint32_t mn_lo = h.z & 0x3F3F3F3Fu, mn_hi = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
-        float f[8];
+        const uint32_t sc = half ? ((h.w & kNibbles) | ((h.y >> 2) & kTopBits)) : (h.y & 0x3F3F3F3Fu);
+        const uint32_t mn = half ? (((h.w >> 4) & kNibbles) | ((h.z >> 2) & kTopBits)) : (h.z & 0x3F3F3F3Fu);
+        float gs[4], gm[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float gs_lo = d * byte_of(sc_lo, i), gs_hi = d * byte_of(sc_hi, i);
-            if (sel == 0) {
-                f[i] = gs_lo; f[4 + i] = gs_hi;
-            } else {
-                f[i] = -fmaf(128.0f, gs_lo, dmin * byte_of(mn_lo, i));
-                f[4 + i] = -fmaf(128.0f, gs_hi, dmin * byte_of(mn_hi, i));
-            }
+        for (int i = 0; i < 4; ++i) { gs[i] = d * byte_f32(sc, i); gm[i] = dmin * byte_f32(mn, i); }
+        for (int mm = 0; mm < sh.members; ++mm) {
+            const float4 sx = *reinterpret_cast<const float4*>(sh.sx + (size_t)mm * (sh.K / 32) + kb * 8 + half * 4);
+            const float4 sa = *reinterpret_cast<const float4*>(sh.sxs + (size_t)mm * (sh.K / 16) + kb * 16 + half * 8);
+            const float4 sb = *reinterpret_cast<const float4*>(sh.sxs + (size_t)mm * (sh.K / 16) + kb * 16 + half * 8 + 4);
+            float* out = hdr + (mm * 16 + row) * kHdrStride;
+            *reinterpret_cast<float4*>(out + half * 4) = make_float4(gs[0] * sx.x, gs[1] * sx.y, gs[2] * sx.z, gs[3] * sx.w);
+            float off = gm[0] * (sa.x + sa.y);
+            off = fmaf(gm[1], sa.z + sa.w, off);
+            off = fmaf(gm[2], sb.x + sb.y, off);
+            off = fmaf(gm[3], sb.z + sb.w, off);
+            off += __shfl_xor_sync(0xffffffffu, off, 1);
+            if (half == 0) out[16] = -off;
         }
-        float4* dst = reinterpret_cast<float4*>(hdr + row * kHdrStride + sel * 8);
-        dst[0] = make_float4(f[0], f[1], f[2], f[3]);
-        dst[1] = make_float4(f[4], f[5], f[6], f[7]);
     }
     __syncwarp();
-    const float* h0 = hdr + g * kHdrStride;
-    const float* h1 = hdr + (g + 8) * kHdrStride;
-    const float* s32 = sh.s32 + (size_t)(t < members ? t : 0) * (stride - kXPad) / 32;
-    const float live = t < members ? 1.0f : 0.0f;
-#pragma unroll
+    const float* h0 = hdr + (m * 16 + g) * kHdrStride;
+    const float* h1 = hdr + (m * 16 + g + 8) * kHdrStride;
+#pragma unroll 2
     for (int j = 0; j < 4; ++j) {
-        const uint32_t r0a = qv[j].x, r0b = qv[j].y, r1a = qv[j].z, r1b = qv[j].w;
-        const int ke = kb * 256 + (2 * j) * 32, ko = ke + 32;
-        float ce[4] = {0.f, 0.f, 0.f, 0.f}, co[4] = {0.f, 0.f, 0.f, 0.f};
-        uint2 b = load_b(sh, stride, g, t, cols, ke);
-        mma_bf16(ce, pick(r0a, kLowMask), pick(r1a, kLowMask), pick(r0a >> 8, kLowMask), pick(r1a >> 8, kLowMask), b.x, b.y);
-        b = load_b(sh, stride, g, t, cols, ke + 16);
-        mma_bf16(ce, pick(r0b, kLowMask), pick(r1b, kLowMask), pick(r0b >> 8, kLowMask), pick(r1b >> 8, kLowMask), b.x, b.y);
-        b = load_b(sh, stride, g, t, cols, ko);
-        mma_bf16(co, pick(r0a >> 4, kLowMask), pick(r1a >> 4, kLowMask), pick(r0a >> 12, kLowMask),
-                 pick(r1a >> 12, kLowMask), b.x, b.y);
-        b = load_b(sh, stride, g, t, cols, ko + 16);
-        mma_bf16(co, pick(r0b >> 4, kLowMask), pick(r1b >> 4, kLowMask), pick(r0b >> 12, kLowMask),
-                 pick(r1b >> 12, kLowMask), b.x, b.y);
-        const float2 sv = *reinterpret_cast<const float2*>(s32 + kb * 8 + 2 * j);
-        const float2 sc0 = *reinterpret_cast<const float2*>(h0 + 2 * j), sc1 = *reinterpret_cast<const float2*>(h1 + 2 * j);
-        const float2 of0 = *reinterpret_cast<const float2*>(h0 + 8 + 2 * j), of1 = *reinterpret_cast<const float2*>(h1 + 8 + 2 * j);
-        fold(acc, ce, sc0.x, sc1.x, of0.x, of1.x, sv.x * live);
-        fold(acc, co, sc0.y, sc1.y, of0.y, of1.y, sv.y * live);
+        const uint4 w = *reinterpret_cast<const uint4*>(tile + j * 512 + lane * 16);
+        const uint2 be = load_b(sh, g, t, kb * 8 + 2 * j), bo = load_b(sh, g, t, kb * 8 + 2 * j + 1);
+        int ce[4], co[4];
+        imma_k32(ce, w.x & kNibbles, w.z & kNibbles, w.y & kNibbles, w.w & kNibbles, be.x, be.y);
+        imma_k32(co, (w.x >> 4) & kNibbles, (w.z >> 4) & kNibbles, (w.y >> 4) & kNibbles, (w.w >> 4) & kNibbles, bo.x,
+                 bo.y);
+        const float2 f0 = *reinterpret_cast<const float2*>(h0 + 2 * j), f1 = *reinterpret_cast<const float2*>(h1 + 2 * j);
+        fold(acc, ce, f0.x, f1.x);
+        fold(acc, co, f0.y, f1.y);
     }
+    acc.s[0] += h0[16];
+    acc.s[1] += h1[16];
     __syncwarp();
 }
 
-// ---- Q6_K: value = gs * (q - 32), A = 128 + q  =>  gs * C - 160 gs * S (per 16 inputs) ---
-__device__ __forceinline__ void tile_q6k(const unsigned char* tile, const Shared& sh, int stride, int cols, int members,
-                                         int kb, int warp, int lane, Accum& acc) {
-    const int g = lane >> 2, t = lane & 3;
-    uint4 ql[4], qh[2];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) ql[i] = *reinterpret_cast<const uint4*>(tile + i * 512 + lane * 16);
-#pragma unroll
-    for (int c = 0; c < 2; ++c) qh[c] = *reinterpret_cast<const uint4*>(tile + 2048 + c * 512 + lane * 16);
-    float* hdr = sh.hdr + warp * (16 * kHdrStride);
+// ---- Q6_K: w = gs * (q - 32), one scale per 16 inputs (k16 MMA) ---------------------------------
+__device__ __forceinline__ void tile_q6k(const unsigned char* tile, const Shared& sh, int kb, float* hdr, int lane,
+                                         Accum& acc) {
+    const int g = lane >> 2, t = lane & 3, m = t >> 1;
     {
+        // lane -> (row, half): the eight 16-input scales half * 8 .. half * 8 + 7 (groups half * 4 ..)
         const int row = lane >> 1, half = lane & 1;
         const uint2 s8 = *reinterpret_cast<const uint2*>(tile + 3072 + row * 16 + half * 8);
         const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(tile + 3328 + row * 2)));
-        float f[8];
+        float gs[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            f[i] = d * (float)(signed char)((s8.x >> (8 * i)) & 0xffu);
-            f[4 + i] = d * (float)(signed char)((s8.y >> (8 * i)) & 0xffu);
+            // signed byte: flip the sign bit, convert as unsigned, subtract 128
+            gs[i] = d * (byte_f32(s8.x ^ 0x80808080u, i) - 128.0f);
+            gs[4 + i] = d * (byte_f32(s8.y ^ 0x80808080u, i) - 128.0f);
         }
-        float4* dst = reinterpret_cast<float4*>(hdr + row * kHdrStride + half * 8);
-        dst[0] = make_float4(f[0], f[1], f[2], f[3]);
-        dst[1] = make_float4(f[4], f[5], f[6], f[7]);
+        for (int mm = 0; mm < sh.members; ++mm) {
+            const float4 sx = *reinterpret_cast<const float4*>(sh.sx + (size_t)mm * (sh.K / 32) + kb * 8 + half * 4);
+            const float4 sa = *reinterpret_cast<const float4*>(sh.sxs + (size_t)mm * (sh.K / 16) + kb * 16 + half * 8);
+            const float4 sb = *reinterpret_cast<const float4*>(sh.sxs + (size_t)mm * (sh.K / 16) + kb * 16 + half * 8 + 4);
+            float* out = hdr + (mm * 16 + row) * kHdrStride;
+            *reinterpret_cast<float4*>(out + half * 8) = make_float4(gs[0] * sx.x, gs[1] * sx.x, gs[2] * sx.y, gs[3] * sx.y);
+            *reinterpret_cast<float4*>(out + half * 8 + 4) = make_float4(gs[4] * sx.z, gs[5] * sx.z, gs[6] * sx.w, gs[7] * sx.w);
+            float off = gs[0] * sa.x;
+            off = fmaf(gs[1], sa.y, off); off = fmaf(gs[2], sa.z, off); off = fmaf(gs[3], sa.w, off);
+            off = fmaf(gs[4], sb.x, off); off = fmaf(gs[5], sb.y, off); off = fmaf(gs[6], sb.z, off); off = fmaf(gs[7], sb.w, off);
+            off += __shfl_xor_sync(0xffffffffu, off, 1);
+            if (half == 0) out[16] = -32.0f * off;
+        }
     }
     __syncwarp();
-    const float* h0 = hdr + g * kHdrStride;
-    const float* h1 = hdr + (g + 8) * kHdrStride;
-    const float* s16 = sh.s16 + (size_t)(t < members ? t : 0) * (stride - kXPad) / 16;
-    const float live = t < members ? -160.0f : 0.0f;
-#pragma unroll
+    const float* h0 = hdr + (m * 16 + g) * kHdrStride;
+    const float* h1 = hdr + (m * 16 + g + 8) * kHdrStride;
+#pragma unroll 1
     for (int c = 0; c < 2; ++c) {
+        const uint4 qh = *reinterpret_cast<const uint4*>(tile + 2048 + c * 512 + lane * 16);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const uint4 w = ql[c * 2 + h];
-            const uint32_t wh0 = h == 0 ? qh[c].x : qh[c].z;
-            const uint32_t wh1 = h == 0 ? qh[c].y : qh[c].w;
+            const uint4 w = *reinterpret_cast<const uint4*>(tile + (c * 2 + h) * 512 + lane * 16);
+            const uint32_t wh0 = h == 0 ? qh.x : qh.z, wh1 = h == 0 ? qh.y : qh.w;
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
                 const uint32_t l0 = (v & 1) ? w.y : w.x, l1 = (v & 1) ? w.w : w.z;
-                const int ls = (v < 2) ? 0 : 4;
-                // high bits of variant v sit at bits 2v..2v+1 of each byte; move them to bits 4..5
-                uint32_t t0, t1, t2, t3;
-                if (v == 0) { t0 = wh0 << 4; t1 = wh1 << 4; t2 = wh0 >> 4; t3 = wh1 >> 4; }
-                else if (v == 1) { t0 = wh0 << 2; t1 = wh1 << 2; t2 = wh0 >> 6; t3 = wh1 >> 6; }
-                else if (v == 2) { t0 = wh0; t1 = wh1; t2 = wh0 >> 8; t3 = wh1 >> 8; }
-                else { t0 = wh0 >> 2; t1 = wh1 >> 2; t2 = wh0 >> 10; t3 = wh1 >> 10; }
-                const uint32_t a0 = pick(l0 >> ls, kLowMask, pick(t0, kTopMask));
-                const uint32_t a1 = pick(l1 >> ls, kLowMask, pick(t1, kTopMask));
-                const uint32_t a2 = pick(l0 >> (ls + 8), kLowMask, pick(t2, kTopMask));
-                const uint32_t a3 = pick(l1 >> (ls + 8), kLowMask, pick(t3, kTopMask));
+                // the variant's two high bits sit at bits 2v..2v+1 of each high-bit byte: move them to bits 4..5
+                uint32_t t0, t1;
+                if (v == 0) { t0 = wh0 << 4; t1 = wh1 << 4; }
+                else if (v == 1) { t0 = wh0 << 2; t1 = wh1 << 2; }
+                else if (v == 2) { t0 = wh0; t1 = wh1; }
+                else { t0 = wh0 >> 2; t1 = wh1 >> 2; }
+                const uint32_t a0 = and_or(v < 2 ? l0 : l0 >> 4, kNibbles, t0 & kTopBits);
+                const uint32_t a1 = and_or(v < 2 ? l1 : l1 >> 4, kNibbles, t1 & kTopBits);
                 const int group = c * 4 + v, sub = group * 2 + h;
-                const int k0 = kb * 256 + group * 32 + 16 * h;
-                float cc[4] = {0.f, 0.f, 0.f, 0.f};
-                const uint2 b = load_b(sh, stride, g, t, cols, k0);
-                mma_bf16(cc, a0, a1, a2, a3, b.x, b.y);
-                const float sv = s16[kb * 16 + sub] * live;
-                fold(acc, cc, h0[sub], h1[sub], h0[sub], h1[sub], sv);
+                const uint2 b = load_b(sh, g, t, kb * 8 + group);
+                int cc[4];
+                imma_k16(cc, a0, a1, h == 0 ? b.x : b.y);
+                fold(acc, cc, h0[sub], h1[sub]);
             }
         }
     }
+    acc.s[0] += h0[16];
+    acc.s[1] += h1[16];
     __syncwarp();
 }
 
-// ---- Q8_0: stored u = q + 128 = 16 * hn + ln; value = d * (16 (hn - 8) + ln) ------------
-//      two nibble planes, A = 128 + nibble  =>  d * (16 C_h + C_l) - d * (16 * 136 + 128) * S
-__device__ __forceinline__ void tile_q8_0(const unsigned char* tile, const Shared& sh, int stride, int cols, int members,
-                                          int kb, int warp, int lane, Accum& acc) {
-    const int g = lane >> 2, t = lane & 3;
-    float* hdr = sh.hdr + warp * (16 * kHdrStride);
+// ---- Q8_0: stored byte u = q + 128 is the u8 operand as is; w = d * (u - 128) -----------------------
+__device__ __forceinline__ void tile_q8_0(const unsigned char* tile, const Shared& sh, int kb, float* hdr, int lane,
+                                          Accum& acc) {
+    const int g = lane >> 2, t = lane & 3, m = t >> 1;
     {
         const int row = lane >> 1, half = lane & 1;
         const uint2 d4 = *reinterpret_cast<const uint2*>(tile + 4096 + row * 16 + half * 8);
-        float4 f;
-        f.x = __half2float(__ushort_as_half((unsigned short)(d4.x & 0xffffu)));
-        f.y = __half2float(__ushort_as_half((unsigned short)(d4.x >> 16)));
-        f.z = __half2float(__ushort_as_half((unsigned short)(d4.y & 0xffffu)));
-        f.w = __half2float(__ushort_as_half((unsigned short)(d4.y >> 16)));
-        *reinterpret_cast<float4*>(hdr + row * kHdrStride + half * 4) = f;
+        float d[4];
+        d[0] = __half2float(__ushort_as_half((unsigned short)(d4.x & 0xffffu)));
+        d[1] = __half2float(__ushort_as_half((unsigned short)(d4.x >> 16)));
+        d[2] = __half2float(__ushort_as_half((unsigned short)(d4.y & 0xffffu)));
+        d[3] = __half2float(__ushort_as_half((unsigned short)(d4.y >> 16)));
+        for (int mm = 0; mm < sh.members; ++mm) {
+            const float4 sx = *reinterpret_cast<const float4*>(sh.sx + (size_t)mm * (sh.K / 32) + kb * 8 + half * 4);
+            const float4 sa = *reinterpret_cast<const float4*>(sh.sxs + (size_t)mm * (sh.K / 16) + kb * 16 + half * 8);
+            const float4 sb = *reinterpret_cast<const float4*>(sh.sxs + (size_t)mm * (sh.K / 16) + kb * 16 + half * 8 + 4);
+            float* out = hdr + (mm * 16 + row) * kHdrStride;
+            *reinterpret_cast<float4*>(out + half * 4) = make_float4(d[0] * sx.x, d[1] * sx.y, d[2] * sx.z, d[3] * sx.w);
+            float off = d[0] * (sa.x + sa.y);
+            off = fmaf(d[1], sa.z + sa.w, off);
+            off = fmaf(d[2], sb.x + sb.y, off);
+            off = fmaf(d[3], sb.z + sb.w, off);
+            off += __shfl_xor_sync(0xffffffffu, off, 1);
+            if (half == 0) out[16] = -128.0f * off;
+        }
     }
     __syncwarp();
-    const float* h0 = hdr + g * kHdrStride;
-    const float* h1 = hdr + (g + 8) * kHdrStride;
-    const float* s32 = sh.s32 + (size_t)(t < members ? t : 0) * (stride - kXPad) / 32;
-    const float live = t < members ? -(16.0f * 136.0f + 128.0f) : 0.0f;
-#pragma unroll
+    const float* h0 = hdr + (m * 16 + g) * kHdrStride;
+    const float* h1 = hdr + (m * 16 + g + 8) * kHdrStride;
+#pragma unroll 2
     for (int b8 = 0; b8 < 8; ++b8) {
         const uint4 w = *reinterpret_cast<const uint4*>(tile + b8 * 512 + lane * 16);
-        const int k0 = kb * 256 + b8 * 32;
-        float cl[4] = {0.f, 0.f, 0.f, 0.f}, ch[4] = {0.f, 0.f, 0.f, 0.f};
-        uint2 b = load_b(sh, stride, g, t, cols, k0);
-        mma_bf16(cl, pick(w.x, kLowMask), pick(w.z, kLowMask), pick(w.x >> 8, kLowMask), pick(w.z >> 8, kLowMask), b.x, b.y);
-        mma_bf16(ch, pick(w.x >> 4, kLowMask), pick(w.z >> 4, kLowMask), pick(w.x >> 12, kLowMask),
-                 pick(w.z >> 12, kLowMask), b.x, b.y);
-        b = load_b(sh, stride, g, t, cols, k0 + 16);
-        mma_bf16(cl, pick(w.y, kLowMask), pick(w.w, kLowMask), pick(w.y >> 8, kLowMask), pick(w.w >> 8, kLowMask), b.x, b.y);
-        mma_bf16(ch, pick(w.y >> 4, kLowMask), pick(w.w >> 4, kLowMask), pick(w.y >> 12, kLowMask),
-                 pick(w.w >> 12, kLowMask), b.x, b.y);
-        float cc[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) cc[i] = fmaf(16.0f, ch[i], cl[i]);
-        const float sv = s32[kb * 8 + b8] * live;
-        fold(acc, cc, h0[b8], h1[b8], h0[b8], h1[b8], sv);
+        const uint2 b = load_b(sh, g, t, kb * 8 + b8);
+        int cc[4];
+        imma_k32(cc, w.x, w.z, w.y, w.w, b.x, b.y);
+        fold(acc, cc, h0[b8], h1[b8]);
     }
+    acc.s[0] += h0[16];
+    acc.s[1] += h1[16];
     __syncwarp();
 }
 
-// hi + mid + lo bfloat16 split of one value; returns the reconstructed sum.
-__device__ __forceinline__ float split3(float v, __nv_bfloat16& hi, __nv_bfloat16& mid, __nv_bfloat16& lo) {
-    hi = __float2bfloat16_rn(v);
-    const float r1 = v - __bfloat162float(hi);
-    mid = __float2bfloat16_rn(r1);
-    const float r2 = r1 - __bfloat162float(mid);
-    lo = __float2bfloat16_rn(r2);
-    return __bfloat162float(hi) + __bfloat162float(mid) + __bfloat162float(lo);
-}
+// Where a unit's rows live: segment index and first row tile.
+struct UnitPlace { int seg, rt0; };
 
-__device__ __forceinline__ float half_warp_sum(float v) {
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
+__device__ __forceinline__ UnitPlace place_unit(const GemvArgs& a, bool swiglu, int u) {
+    UnitPlace p{0, 2 * u};
+    if (!swiglu) {
+        while (p.seg + 1 < a.n_segments && p.rt0 >= ((a.seg[p.seg].row_tiles + 1) & ~1)) {
+            p.rt0 -= (a.seg[p.seg].row_tiles + 1) & ~1;
+            ++p.seg;
+        }
+    }
+    return p;
 }
 
 __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a, const int slots, const int slot_bytes) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int K = a.k, stride = K + kXPad, cols = 3 * a.members;
+    const int K = a.k, planes = 3 * a.members;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool swiglu = a.epilogue == kSwiGLU;
-    const int runs = swiglu ? 2 : 1;  // matrices per unit
+    const int runs = swiglu ? 4 : 2;  // row-tile runs per unit
     Shared sh;
     {
         unsigned char* p = smem_raw;
         sh.ring = p; p += (size_t)slots * slot_bytes;
-        sh.xs = reinterpret_cast<__nv_bfloat16*>(p); p += (size_t)cols * stride * sizeof(__nv_bfloat16);
-        sh.s16 = reinterpret_cast<float*>(p); p += (size_t)a.members * (K / 16) * sizeof(float);
-        sh.s32 = reinterpret_cast<float*>(p); p += (size_t)a.members * (K / 32) * sizeof(float);
-        sh.hdr = reinterpret_cast<float*>(p); p += (size_t)kConsumerWarps * 16 * kHdrStride * sizeof(float);
-        sh.red = reinterpret_cast<float*>(p); p += (size_t)2 * kConsumerWarps * runs * 128 * sizeof(float);
+        sh.xq = reinterpret_cast<signed char*>(p); p += (size_t)planes * (K + kPlanePad);
+        sh.sx = reinterpret_cast<float*>(p); p += (size_t)a.members * (K / 32) * sizeof(float);
+        sh.sxs = reinterpret_cast<float*>(p); p += (size_t)a.members * (K / 16) * sizeof(float);
+        sh.hdr = reinterpret_cast<float*>(p); p += (size_t)kConsumerWarps * a.members * 16 * kHdrStride * sizeof(float);
+        sh.red = reinterpret_cast<float*>(p); p += (size_t)2 * kConsumerWarps * kMaxRuns * a.members * 16 * sizeof(float);
         sh.scale = reinterpret_cast<float*>(p); p += 16;
         sh.full = smem_u32(p); p += (size_t)slots * 8;
         sh.empty = smem_u32(p); p += (size_t)slots * 8;
         sh.xbar = smem_u32(p);
+        sh.K = K; sh.members = a.members;
     }
     const int k_tiles = K / kTileCols;
     const int stages_per_run = (k_tiles + kStageTiles - 1) / kStageTiles;
-    const int stages_per_unit = runs * stages_per_run;
     int total_units = 0;
-    if (swiglu) total_units = a.seg[0].row_tiles;
-    else for (int i = 0; i < a.n_segments; ++i) total_units += a.seg[i].row_tiles;
+    if (swiglu) total_units = (a.seg[0].row_tiles + 1) / 2;
+    else for (int i = 0; i < a.n_segments; ++i) total_units += (a.seg[i].row_tiles + 1) / 2;
     const int u0 = (int)((long long)blockIdx.x * total_units / gridDim.x);
     const int u1 = (int)((long long)(blockIdx.x + 1) * total_units / gridDim.x);
 
@@ -457,18 +471,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
     // Let the next kernel in the stream begin (its weight prefetch does not depend on this one).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    if (warp == kConsumerWarps) {
+    if (warp == kProducerWarp) {
         // ---------------- producer: one bulk copy per stage of up to 8 contiguous tiles ----------------
         if (lane == 0) {
             bool alive = true;
             uint32_t n = 0;
             for (int u = u0; u < u1 && alive; ++u) {
-                int seg = 0, rt = u;
-                if (!swiglu) {
-                    while (seg + 1 < a.n_segments && rt >= a.seg[seg].row_tiles) { rt -= a.seg[seg].row_tiles; ++seg; }
-                }
+                const UnitPlace pl = place_unit(a, swiglu, u);
                 for (int r = 0; r < runs && alive; ++r) {
-                    const GemvSegment& s = a.seg[swiglu ? r : seg];
+                    const GemvSegment& s = a.seg[swiglu ? (r & 1) : pl.seg];
+                    const int rt = pl.rt0 + (swiglu ? (r >> 1) : r);
+                    if (rt >= s.row_tiles) continue;
                     const uint32_t tile_bytes = (uint32_t)packed_tile_bytes(s.type);
                     const unsigned char* run = s.data + (size_t)rt * k_tiles * tile_bytes;
                     for (int st = 0; st < stages_per_run; ++st, ++n) {
@@ -489,167 +502,161 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
         return;
     }
 
-    // ---------------- consumers ----------------
-    asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations come from the previous kernel
-    if (threadIdx.x == 0) {
-        const uint32_t col_bytes = (uint32_t)K * 2u, sum_bytes = (uint32_t)a.members * (K / 16) * 4u;
-        mbar_expect_tx(sh.xbar, col_bytes * (uint32_t)cols + sum_bytes);
-        for (int c = 0; c < cols; ++c) {
-            bulk_g2s(smem_u32(sh.xs + (size_t)c * stride), a.in.x + (size_t)c * K, col_bytes, sh.xbar);
-        }
-        bulk_g2s(smem_u32(sh.s16), a.in.s16, sum_bytes, sh.xbar);
-    }
-    if (warp < a.members) {
-        // RMSNorm factor of member `warp`: fixed-order sum of the producer's per-16 sums of squares.
-        float inv = 1.0f;
-        if (a.in_has_norm) {
-            const float* ss = a.in.ss16 + (size_t)warp * (K / 16);
-            float sum = 0.0f;
-            for (int i = lane; i < K / 16; i += 32) sum += ss[i];
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // activations and the residual come from the previous kernel
+
+    if (warp == kEpilogueWarp) {
+        // ---------------- epilogue warp: lane = one of the unit's 32 output rows ----------------
+        float inv_norm[kGemvMaxMembers];
+        for (int m = 0; m < a.members; ++m) {
+            // RMSNorm factor: fixed-order sum of the producer's per-32 sums of squares.
+            inv_norm[m] = 1.0f;
+            if (a.in_has_norm) {
+                const float* ss = a.in.ss32 + (size_t)m * (K / 32);
+                float sum = 0.0f;
+                for (int i = lane; i < K / 32; i += 32) sum += ss[i];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            inv = 1.0f / sqrtf(sum / (float)K + a.eps);
+                for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                inv_norm[m] = 1.0f / sqrtf(sum / (float)K + a.eps);
+            }
         }
-        if (lane == 0) sh.scale[warp] = inv;
+        int buf = 0;
+        for (int u = u0; u < u1; ++u, buf ^= 1) {
+            const UnitPlace pl = place_unit(a, swiglu, u);
+            const GemvSegment& s = a.seg[swiglu ? 0 : pl.seg];
+            const int half = lane >> 4, row = lane & 15;
+            const int rt = pl.rt0 + half;
+            const int n_index = rt * kTileRows + row;
+            bar_sync(kBarFull + buf);  // every consumer warp has left its partial sums of this unit
+            float v0[kGemvMaxMembers], v1[kGemvMaxMembers];
+            for (int m = 0; m < a.members; ++m) {
+                const float* base = sh.red + ((size_t)buf * kConsumerWarps * kMaxRuns * a.members) * 16;
+                const int run0 = swiglu ? 2 * half : half;
+                float x0 = 0.0f, x1 = 0.0f;
+#pragma unroll 4
+                for (int w = 0; w < kConsumerWarps; ++w) {
+                    x0 += base[(((size_t)w * kMaxRuns + run0) * a.members + m) * 16 + row];
+                    if (swiglu) x1 += base[(((size_t)w * kMaxRuns + run0 + 1) * a.members + m) * 16 + row];
+                }
+                v0[m] = x0 * inv_norm[m];
+                v1[m] = x1 * inv_norm[m];
+            }
+            __syncwarp();
+            bar_arrive(kBarFree + buf);  // the buffer may be overwritten
+            for (int m = 0; m < a.members; ++m) {
+                const bool valid = rt < s.row_tiles && n_index < s.n;
+                float result = 0.0f, square = 0.0f;
+                if (valid) {
+                    float* y = s.y + (size_t)m * s.n + n_index;
+                    if (a.epilogue == kResidual) {
+                        result = *y + v0[m];
+                        *y = result;
+                        square = result * result;
+                    } else if (swiglu) {
+                        result = v0[m] / (1.0f + expf(-v0[m])) * v1[m];
+                        if (a.swiglu_f32 != nullptr) a.swiglu_f32[(size_t)m * s.n + n_index] = result;
+                    } else {
+                        result = v0[m];
+                        *y = result;
+                    }
+                }
+                if (a.out.dig != nullptr && pl.rt0 * kTileRows < s.n) {
+                    float v = result;
+                    if (valid && a.out_norm_weight != nullptr) v *= a.out_norm_weight[n_index];
+                    ActOperand out = a.out;
+                    if (a.epilogue != kResidual) out.ss32 = nullptr;
+                    operand_store_span(out, m, s.n, pl.rt0 / 2, lane, v, square);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    if (threadIdx.x == 0) {
+        const uint32_t plane_bytes = (uint32_t)K, sx_bytes = (uint32_t)a.members * (K / 32) * 4u,
+                       sxs_bytes = (uint32_t)a.members * (K / 16) * 4u;
+        mbar_expect_tx(sh.xbar, plane_bytes * (uint32_t)planes + sx_bytes + sxs_bytes);
+        for (int c = 0; c < planes; ++c) {
+            bulk_g2s(smem_u32(sh.xq + (size_t)c * (K + kPlanePad)), a.in.dig + (size_t)c * K, plane_bytes, sh.xbar);
+        }
+        bulk_g2s(smem_u32(sh.sx), a.in.sx, sx_bytes, sh.xbar);
+        bulk_g2s(smem_u32(sh.sxs), a.in.sxs16, sxs_bytes, sh.xbar);
     }
     bool alive = mbar_wait(sh.xbar, 0, a.error_flag, 2);
-    for (int i = threadIdx.x; i < a.members * (K / 32); i += kConsumerThreads) {
-        const int m = i / (K / 32), grp = i - m * (K / 32);
-        sh.s32[i] = sh.s16[(size_t)m * (K / 16) + 2 * grp] + sh.s16[(size_t)m * (K / 16) + 2 * grp + 1];
-    }
-    consumer_barrier();
 
     const int g = lane >> 2, t = lane & 3;
     const int team = warp / kTeamWarps, member_warp = warp % kTeamWarps;
+    float* hdr = sh.hdr + (size_t)warp * a.members * 16 * kHdrStride;
+    uint32_t n = 0;  // stage counter, in step with the producer's
     int buf = 0;
-    for (int u = u0; u < u1; ++u) {
-        int seg = 0, rt = u;
-        if (!swiglu) {
-            while (seg + 1 < a.n_segments && rt >= a.seg[seg].row_tiles) { rt -= a.seg[seg].row_tiles; ++seg; }
-        }
-        Accum acc[2];
+    for (int u = u0; u < u1; ++u, buf ^= 1) {
+        const UnitPlace pl = place_unit(a, swiglu, u);
+        Accum acc[kMaxRuns];
 #pragma unroll
-        for (int w = 0; w < 2; ++w) {
-            acc[w].c[0] = acc[w].c[1] = acc[w].c[2] = acc[w].c[3] = 0.0f;
-            acc[w].s[0] = acc[w].s[1] = 0.0f;
+        for (int r = 0; r < kMaxRuns; ++r) {
+            acc[r].c[0] = acc[r].c[1] = acc[r].c[2] = acc[r].c[3] = 0.0f;
+            acc[r].s[0] = acc[r].s[1] = 0.0f;
         }
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
+        for (int r = 0; r < kMaxRuns; ++r) {
             if (r >= runs) break;
-            const int type = a.seg[swiglu ? r : seg].type;
+            const GemvSegment& s = a.seg[swiglu ? (r & 1) : pl.seg];
+            const int rt = pl.rt0 + (swiglu ? (r >> 1) : r);
+            if (rt >= s.row_tiles) continue;
+            const int type = s.type;
             const int tile_bytes = packed_tile_bytes(type);
-            for (int st = 0; st < stages_per_run; ++st) {
-                const uint32_t n = (uint32_t)(u - u0) * (uint32_t)stages_per_unit + (uint32_t)(r * stages_per_run + st);
+            for (int st = 0; st < stages_per_run; ++st, ++n) {
                 if ((int)(n & 1u) != team) continue;  // the other team's stage
                 const uint32_t slot = n % (uint32_t)slots;
                 if (alive) alive = mbar_wait(sh.full + slot * 8, (n / (uint32_t)slots) & 1u, a.error_flag, 3);
                 const int kb = st * kStageTiles + member_warp;
                 if (kb < k_tiles) {
                     const unsigned char* tile = sh.ring + (size_t)slot * slot_bytes + (size_t)member_warp * tile_bytes;
-                    if (type == kQ4_K) tile_q4k(tile, sh, stride, cols, a.members, kb, warp, lane, acc[r]);
-                    else if (type == kQ6_K) tile_q6k(tile, sh, stride, cols, a.members, kb, warp, lane, acc[r]);
-                    else tile_q8_0(tile, sh, stride, cols, a.members, kb, warp, lane, acc[r]);
+                    if (type == kQ4_K) tile_q4k(tile, sh, kb, hdr, lane, acc[r]);
+                    else if (type == kQ6_K) tile_q6k(tile, sh, kb, hdr, lane, acc[r]);
+                    else tile_q8_0(tile, sh, kb, hdr, lane, acc[r]);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sh.empty + slot * 8);  // this warp has left the stage
             }
         }
-        // Offset terms join the carrier column of this lane's member: member m's hi column is 3m,
-        // which is (t = 0, c[0]/c[2]) for m = 0 and (t = 1, c[1]/c[3]) for m = 1.
-        float* red = sh.red + ((size_t)buf * kConsumerWarps + warp) * runs * 128;
+        // Per-warp partial of (row, member): digits 1 and 2 are this lane's two columns, digit 3 is the
+        // first column of the next lane; lanes with even t own members t / 2.
+        if (u - u0 >= 2) bar_sync(kBarFree + buf);  // the epilogue warp has read this buffer's previous unit
+        float* red = sh.red + (((size_t)buf * kConsumerWarps + warp) * kMaxRuns) * a.members * 16;
 #pragma unroll
-        for (int w = 0; w < 2; ++w) {
-            if (w >= runs) break;
-            if (t == 0) { acc[w].c[0] += acc[w].s[0]; acc[w].c[2] += acc[w].s[1]; }
-            if (t == 1) { acc[w].c[1] += acc[w].s[0]; acc[w].c[3] += acc[w].s[1]; }
-            float* r = red + w * 128;
-            *reinterpret_cast<float2*>(r + g * 8 + 2 * t) = make_float2(acc[w].c[0], acc[w].c[1]);
-            *reinterpret_cast<float2*>(r + (g + 8) * 8 + 2 * t) = make_float2(acc[w].c[2], acc[w].c[3]);
-        }
-        consumer_barrier();
-        if (warp == 0) {
-            // ---------------- epilogue: lane -> (member, row) ----------------
-            const int m = lane >> 4, row = lane & 15;
-            const GemvSegment& s = a.seg[swiglu ? 0 : seg];
-            const int n_index = rt * kTileRows + row;
-            const bool valid = m < a.members && n_index < s.n;
-            const float* base = sh.red + (size_t)buf * kConsumerWarps * runs * 128;
-            float v0 = 0.0f, v1 = 0.0f;
-            if (m < a.members) {
-#pragma unroll 4
-                for (int w = 0; w < kConsumerWarps; ++w) {
-#pragma unroll
-                    for (int term = 0; term < 3; ++term) {
-                        v0 += base[(size_t)w * runs * 128 + row * 8 + m * 3 + term];
-                        if (swiglu) v1 += base[(size_t)w * runs * 128 + 128 + row * 8 + m * 3 + term];
-                    }
-                }
-                const float scale = sh.scale[m];
-                v0 *= scale;
-                v1 *= scale;
-            }
-            float result = 0.0f, square = 0.0f;
-            if (valid) {
-                float* y = s.y + (size_t)m * s.n + n_index;
-                if (a.epilogue == kResidual) {
-                    result = *y + v0;
-                    *y = result;
-                    square = result * result;
-                } else if (swiglu) {
-                    result = v0 / (1.0f + expf(-v0)) * v1;
-                    if (a.swiglu_f32 != nullptr) a.swiglu_f32[(size_t)m * s.n + n_index] = result;
-                } else {
-                    result = v0;
-                    *y = v0;
-                }
-            }
-            if (a.out.x != nullptr) {
-                float v = result;
-                if (valid && a.out_norm_weight != nullptr) v *= a.out_norm_weight[n_index];
-                __nv_bfloat16 hi, mid, lo;
-                const float recon = split3(v, hi, mid, lo);
-                if (valid) {
-                    __nv_bfloat16* ox = a.out.x + (size_t)m * 3 * s.n + n_index;
-                    ox[0] = hi; ox[s.n] = mid; ox[2 * (size_t)s.n] = lo;
-                }
-                const float sum = half_warp_sum(recon), sq = half_warp_sum(square);
-                if (row == 0 && m < a.members && rt * kTileRows < s.n) {
-                    a.out.s16[(size_t)m * (s.n / 16) + rt] = sum;
-                    if (a.out.ss16 != nullptr && a.epilogue == kResidual) a.out.ss16[(size_t)m * (s.n / 16) + rt] = sq;
-                }
+        for (int r = 0; r < kMaxRuns; ++r) {
+            if (r >= runs) break;
+            const float d3a = __shfl_down_sync(0xffffffffu, acc[r].c[0], 1);
+            const float d3b = __shfl_down_sync(0xffffffffu, acc[r].c[2], 1);
+            if ((t & 1) == 0 && (t >> 1) < a.members) {
+                const float va = acc[r].c[0] + acc[r].c[1] * (1.0f / 128.0f) + d3a * (1.0f / 16384.0f) + acc[r].s[0];
+                const float vb = acc[r].c[2] + acc[r].c[3] * (1.0f / 128.0f) + d3b * (1.0f / 16384.0f) + acc[r].s[1];
+                float* dst = red + ((size_t)r * a.members + (t >> 1)) * 16;
+                dst[g] = va;
+                dst[g + 8] = vb;
             }
         }
-        buf ^= 1;
+        __syncwarp();
+        bar_arrive(kBarFull + buf);
     }
 }
 
-// f32 rows -> operand form: one warp per 16 inputs of one member.
+// f32 rows -> operand form: one warp per 32-span of one member.
 __global__ void to_operand_kernel(const float* x, const int32_t* index, const float* norm_weight, int members, int k,
                                   ActOperand out) {
     const int lane = threadIdx.x & 31;
-    const long long pair = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;  // two 16-spans per warp
-    const long long span = pair * 2 + (lane >> 4);
-    const long long spans = (long long)members * (k / 16);
-    const bool live = span < spans;
-    const int m = live ? (int)(span / (k / 16)) : 0, sub = live ? (int)(span - (long long)m * (k / 16)) : 0;
-    const int kk = sub * 16 + (lane & 15);
-    float v = 0.0f, sq = 0.0f;
-    if (live) {
-        v = x[(size_t)(index ? index[m] : m) * k + kk];
-        sq = v * v;
-        if (norm_weight != nullptr) v *= norm_weight[kk];
-    }
-    __nv_bfloat16 hi, mid, lo;
-    const float recon = split3(v, hi, mid, lo);
-    if (live) {
-        __nv_bfloat16* ox = out.x + (size_t)m * 3 * k + kk;
-        ox[0] = hi; ox[k] = mid; ox[2 * (size_t)k] = lo;
-    }
-    const float sum = half_warp_sum(recon), ss = half_warp_sum(sq);
-    if (live && (lane & 15) == 0) {
-        out.s16[(size_t)m * (k / 16) + sub] = sum;
-        if (norm_weight != nullptr && out.ss16 != nullptr) out.ss16[(size_t)m * (k / 16) + sub] = ss;
-    }
+    const long long span_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long spans = (long long)members * (k / 32);
+    if (span_id >= spans) return;
+    const int m = (int)(span_id / (k / 32)), span = (int)(span_id - (long long)m * (k / 32));
+    const int kk = span * 32 + lane;
+    float v = x[(size_t)(index ? index[m] : m) * k + kk];
+    const float sq = v * v;
+    if (norm_weight != nullptr) v *= norm_weight[kk];
+    ActOperand o = out;
+    if (norm_weight == nullptr) o.ss32 = nullptr;
+    operand_store_span(o, m, k, span, lane, v, sq);
 }
 
 int sm_count() {
@@ -666,15 +673,15 @@ int sm_count() {
 
 cudaError_t launch_to_operand(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,
                               int members, int k, ActOperand out) {
-    if (members <= 0 || k % 16 != 0) return cudaErrorInvalidValue;
-    const long long warps = ((long long)members * (k / 16) + 1) / 2;
+    if (members <= 0 || k % 32 != 0) return cudaErrorInvalidValue;
+    const long long warps = (long long)members * (k / 32);
     to_operand_kernel<<<(unsigned int)((warps + 3) / 4), 128, 0, stream>>>(x, index, norm_weight, members, k, out);
     return cudaGetLastError();
 }
 
 cudaError_t launch_gemv_mma(cudaStream_t stream, const GemvArgs& args, bool programmatic) {
-    if (args.members < 1 || args.members > kGemvMaxMembers || args.k % kTileCols != 0 || args.in.x == nullptr ||
-        args.in.s16 == nullptr || (args.in_has_norm && args.in.ss16 == nullptr)) {
+    if (args.members < 1 || args.members > kGemvMaxMembers || args.k % kTileCols != 0 || args.in.dig == nullptr ||
+        args.in.sx == nullptr || args.in.sxs16 == nullptr || (args.in_has_norm && args.in.ss32 == nullptr)) {
         return cudaErrorInvalidValue;
     }
     int units = 0, slot_bytes = 0;
@@ -682,43 +689,25 @@ cudaError_t launch_gemv_mma(cudaStream_t stream, const GemvArgs& args, bool prog
         if (args.n_segments != 2 || args.seg[0].row_tiles != args.seg[1].row_tiles || args.seg[0].n != args.seg[1].n) {
             return cudaErrorInvalidValue;
         }
-        units = args.seg[0].row_tiles;
+        units = (args.seg[0].row_tiles + 1) / 2;
     } else {
-        for (int i = 0; i < args.n_segments; ++i) units += args.seg[i].row_tiles;
+        for (int i = 0; i < args.n_segments; ++i) units += (args.seg[i].row_tiles + 1) / 2;
     }
     for (int i = 0; i < args.n_segments; ++i) {
         const int b = packed_tile_bytes(args.seg[i].type);
         if (b == 0) return cudaErrorInvalidValue;
         slot_bytes = std::max(slot_bytes, b);
-        if (args.out.x != nullptr && args.seg[i].n % 16 != 0) return cudaErrorInvalidValue;
+        if (args.out.dig != nullptr && args.seg[i].n % 32 != 0) return cudaErrorInvalidValue;
     }
     if (units <= 0) return cudaSuccess;
-    const int K = args.k, cols = 3 * args.members, runs = args.epilogue == kSwiGLU ? 2 : 1;
+    const int K = args.k, planes = 3 * args.members;
     slot_bytes *= kStageTiles;
-    const size_t fixed = (size_t)cols * (K + kXPad) * 2 + (size_t)args.members * (K / 16) * 4 +
-                         (size_t)args.members * (K / 32) * 4 + (size_t)kConsumerWarps * 16 * kHdrStride * 4 +
-                         (size_t)2 * kConsumerWarps * runs * 128 * 4 + 16 + 8;
+    const size_t fixed = (size_t)planes * (K + kPlanePad) + (size_t)args.members * (K / 32) * 4 +
+                         (size_t)args.members * (K / 16) * 4 +
+                         (size_t)kConsumerWarps * args.members * 16 * kHdrStride * 4 +
+                         (size_t)2 * kConsumerWarps * kMaxRuns * args.members * 16 * 4 + 16 + 8;
     const size_t budget = 226 * 1024;
-    if (fixed + (size_t)2 * (slot_bytes + 16) > budget) {
-        if (args.members == 1) return cudaErrorInvalidValue;
-        // Too many activation columns for this K: one launch per input vector.
-        for (int m = 0; m < args.members; ++m) {
-            GemvArgs one = args;
-            one.members = 1;
-            for (int i = 0; i < args.n_segments; ++i) one.seg[i].y = args.seg[i].y + (size_t)m * args.seg[i].n;
-            one.in.x = args.in.x + (size_t)m * 3 * K;
-            one.in.s16 = args.in.s16 + (size_t)m * (K / 16);
-            if (args.in.ss16) one.in.ss16 = args.in.ss16 + (size_t)m * (K / 16);
-            const int n_out = args.seg[0].n;
-            if (args.out.x) one.out.x = args.out.x + (size_t)m * 3 * n_out;
-            if (args.out.s16) one.out.s16 = args.out.s16 + (size_t)m * (n_out / 16);
-            if (args.out.ss16) one.out.ss16 = args.out.ss16 + (size_t)m * (n_out / 16);
-            if (args.swiglu_f32) one.swiglu_f32 = args.swiglu_f32 + (size_t)m * n_out;
-            cudaError_t e = launch_gemv_mma(stream, one, programmatic);
-            if (e != cudaSuccess) return e;
-        }
-        return cudaSuccess;
-    }
+    if (fixed + (size_t)2 * (slot_bytes + 16) > budget) return cudaErrorInvalidValue;
     int slots = (int)std::min<size_t>(6, (budget - fixed) / ((size_t)slot_bytes + 16));
     const size_t smem = fixed + (size_t)slots * (slot_bytes + 16);
     static size_t configured = 0;

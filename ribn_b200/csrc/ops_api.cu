@@ -119,11 +119,12 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
         unsigned char* d_w = s.upload(packed.data(), packed.size());
         OP_PTR(d_w);
         ActOperand op;
-        op.x = (__nv_bfloat16*)s.alloc<unsigned short>(act_operand_x_elems(members, (int)cols));
-        op.s16 = s.alloc<float>((size_t)members * (cols / 16));
-        op.ss16 = nullptr;
+        op.dig = s.alloc<signed char>((size_t)members * 3 * cols);
+        op.sx = s.alloc<float>((size_t)members * (cols / 32));
+        op.sxs16 = s.alloc<float>((size_t)members * (cols / 16));
+        op.ss32 = nullptr;
         int* d_err = s.alloc<int>(1);
-        OP_PTR(op.x); OP_PTR(op.s16); OP_PTR(d_err);
+        OP_PTR(op.dig); OP_PTR(op.sx); OP_PTR(op.sxs16); OP_PTR(d_err);
         OP_TRY(cudaMemsetAsync(d_err, 0, sizeof(int), s.stream));
         OP_TRY(launch_to_operand(s.stream, d_x, nullptr, nullptr, members, (int)cols, op));
         for (int m0 = 0; m0 < members; m0 += kGemvMaxMembers) {
@@ -133,8 +134,9 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
                                    d_y + (size_t)m0 * rows};
             a.k = (int)cols;
             a.members = std::min(kGemvMaxMembers, members - m0);
-            a.in.x = op.x + (size_t)m0 * 3 * cols;
-            a.in.s16 = op.s16 + (size_t)m0 * (cols / 16);
+            a.in.dig = op.dig + (size_t)m0 * 3 * cols;
+            a.in.sx = op.sx + (size_t)m0 * (cols / 32);
+            a.in.sxs16 = op.sxs16 + (size_t)m0 * (cols / 16);
             a.in_has_norm = 0;
             a.eps = 0.0f;
             a.epilogue = kStore;

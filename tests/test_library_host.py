@@ -35,29 +35,27 @@ def test_product_package_never_imports_the_oracle():
                 assert "oracle" not in text.lower(), f
 
 
-LOW, TOP, BIAS = 0x000F000F, 0x00300030, 0x43004300
+NIB, TOPBITS = 0x0F0F0F0F, 0x30303030
 
 
-def pick(w, mask, other=BIAS):
-    """(w & mask) | other -- the kernel's single LOP3."""
-    return (int(w) & mask) | other
+def _bytes(reg):
+    return [(int(reg) >> (8 * i)) & 0xFF for i in range(4)]
 
 
-def _halves(reg):
-    """Each half of an A register is the bfloat16 0x4300 | q, i.e. 128 + q."""
-    lo, hi = reg & 0xFFFF, (reg >> 16) & 0xFFFF
-    assert lo & 0xFF80 == 0x4300 and hi & 0xFF80 == 0x4300
-    return lo & 0x7F, hi & 0x7F
-
-
-def _place(Q, g, t, kbase, regs, weight=1):
-    """regs = (a0, a1, a2, a3) of mma.m16n8k16: rows g / g+8, inputs 4t..4t+3 of a 16-wide step."""
+def _place32(Q, g, t, kbase, regs):
+    """regs = (a0, a1, a2, a3) of mma.m16n8k32 (u8): rows g / g+8, inputs 4t..4t+3 and 16+4t..16+4t+3."""
     for ri, reg in enumerate(regs):
         row = g + (8 if ri & 1 else 0)
-        k = kbase + 4 * t + (2 if ri >= 2 else 0)
-        lo, hi = _halves(int(reg))
-        Q[row, k] += weight * lo
-        Q[row, k + 1] += weight * hi
+        k = kbase + 4 * t + (16 if ri >= 2 else 0)
+        for i, b in enumerate(_bytes(reg)):
+            Q[row, k + i] = b
+
+
+def _place16(Q, g, t, kbase, regs):
+    """regs = (a0, a1) of mma.m16n8k16 (u8): rows g / g+8, inputs 4t..4t+3."""
+    for ri, reg in enumerate(regs):
+        for i, b in enumerate(_bytes(reg)):
+            Q[g + 8 * ri, kbase + 4 * t + i] = b
 
 
 def _words(tile, off):
@@ -69,12 +67,9 @@ def emulate_q4k(tile):
     for lane in range(32):
         g, t = lane >> 2, lane & 3
         for j in range(4):
-            r0a, r0b, r1a, r1b = _words(tile, j * 512 + lane * 16)
-            ke, ko = 2 * j * 32, (2 * j + 1) * 32
-            _place(Q, g, t, ke, (pick(r0a, LOW), pick(r1a, LOW), pick(r0a >> 8, LOW), pick(r1a >> 8, LOW)))
-            _place(Q, g, t, ke + 16, (pick(r0b, LOW), pick(r1b, LOW), pick(r0b >> 8, LOW), pick(r1b >> 8, LOW)))
-            _place(Q, g, t, ko, (pick(r0a >> 4, LOW), pick(r1a >> 4, LOW), pick(r0a >> 12, LOW), pick(r1a >> 12, LOW)))
-            _place(Q, g, t, ko + 16, (pick(r0b >> 4, LOW), pick(r1b >> 4, LOW), pick(r0b >> 12, LOW), pick(r1b >> 12, LOW)))
+            x, y, z, w = _words(tile, j * 512 + lane * 16)
+            _place32(Q, g, t, 2 * j * 32, (x & NIB, z & NIB, y & NIB, w & NIB))
+            _place32(Q, g, t, (2 * j + 1) * 32, ((x >> 4) & NIB, (z >> 4) & NIB, (y >> 4) & NIB, (w >> 4) & NIB))
     return Q
 
 
@@ -89,31 +84,32 @@ def emulate_q6k(tile):
                 wh0, wh1 = (qh[0], qh[1]) if h == 0 else (qh[2], qh[3])
                 for v in range(4):
                     l0, l1 = (lb0, lb1) if v & 1 else (la0, la1)
-                    ls = 0 if v < 2 else 4
                     sh = 4 - 2 * v
-
-                    def top(w, extra):
-                        s = sh - extra
-                        return pick((w << s) if s >= 0 else (w >> -s), TOP)
-                    regs = (pick(l0 >> ls, LOW, top(wh0, 0)), pick(l1 >> ls, LOW, top(wh1, 0)),
-                            pick(l0 >> (ls + 8), LOW, top(wh0, 8)), pick(l1 >> (ls + 8), LOW, top(wh1, 8)))
-                    _place(Q, g, t, (c * 4 + v) * 32 + 16 * h, regs)
+                    t0 = (wh0 << sh) if sh >= 0 else (wh0 >> -sh)
+                    t1 = (wh1 << sh) if sh >= 0 else (wh1 >> -sh)
+                    a0 = ((l0 if v < 2 else l0 >> 4) & NIB) | (t0 & TOPBITS)
+                    a1 = ((l1 if v < 2 else l1 >> 4) & NIB) | (t1 & TOPBITS)
+                    _place16(Q, g, t, (c * 4 + v) * 32 + 16 * h, (a0, a1))
     return Q
 
 
 def emulate_q8_0(tile):
-    """Two nibble planes: stored byte u = q + 128 = 16 * high + low."""
     Q = np.zeros((16, 256), dtype=np.int64)
     for lane in range(32):
         g, t = lane >> 2, lane & 3
         for b in range(8):
             x, y, z, w = _words(tile, b * 512 + lane * 16)
-            for word0, word1, off in ((x, z, 0), (y, w, 16)):
-                _place(Q, g, t, b * 32 + off, (pick(word0, LOW), pick(word1, LOW), pick(word0 >> 8, LOW),
-                                               pick(word1 >> 8, LOW)))
-                _place(Q, g, t, b * 32 + off, (pick(word0 >> 4, LOW), pick(word1 >> 4, LOW), pick(word0 >> 12, LOW),
-                                               pick(word1 >> 12, LOW)), weight=16)
+            _place32(Q, g, t, b * 32, (x, z, y, w))
     return Q
+
+
+def test_operand_position_is_a_permutation_matching_the_b_fragment():
+    # lane t's 8-byte word of a 32-span holds inputs 4t..4t+3 then 16+4t..16+4t+3
+    pos = [((k & 15) >> 2) * 8 + ((k >> 4) & 1) * 4 + (k & 3) for k in range(32)]
+    assert sorted(pos) == list(range(32))
+    for t in range(4):
+        assert [pos.index(8 * t + i) for i in range(8)] == [4 * t, 4 * t + 1, 4 * t + 2, 4 * t + 3,
+                                                          16 + 4 * t, 17 + 4 * t, 18 + 4 * t, 19 + 4 * t]
 
 
 def raw_integers(kind, raw, rows, cols):
