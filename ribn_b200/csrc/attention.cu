@@ -94,6 +94,10 @@ template <int HD, bool FUSED>
 __global__ void attention_span_kernel(const AttnArgs a) {
     constexpr int DPL = HD / 32;  // dims per lane in the lane-strided layout
     constexpr int CH = HD / 8;    // dims per lane in the P.V phase (8 chunks x 4 key groups)
+    // Programmatic dependent launch: wait for the projections that produced q/k/v, then let the next
+    // kernel (which first only prefetches weights) start.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ __align__(16) unsigned char attn_smem[];
     float* q_smem = reinterpret_cast<float*>(attn_smem);                                 // [warps][HD]
     __half* k_self = reinterpret_cast<__half*>(attn_smem + (size_t)(blockDim.x >> 5) * HD * sizeof(float));  // [HD]
@@ -257,6 +261,8 @@ template <int HD>
 __global__ void attention_merge_kernel(const AttnArgs a) {
     __shared__ float weight[kAttnMaxSpans];
     __shared__ float denom_s;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int t = a.token_base + blockIdx.x / a.q_heads, qh = blockIdx.x % a.q_heads;
     const int pos = a.token_pos[t];
     const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
@@ -289,9 +295,25 @@ __global__ void attention_merge_kernel(const AttnArgs a) {
     }
 }
 
+template <typename Kernel>
+cudaError_t launch_pdl(cudaStream_t stream, Kernel kernel, dim3 grid, int threads, size_t smem, const AttnArgs& a,
+                       bool programmatic) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3((unsigned int)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, a);
+}
+
 template <int HD>
 cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens, int max_keys, size_t partial_bytes,
-                      int* launches) {
+                      int* launches, bool programmatic = false) {
     const int q_per_kv = a.q_heads / a.kv_heads;
     a.max_spans = (max_keys + kAttnSpanKeys - 1) / kAttnSpanKeys;
     if (a.max_spans > kAttnMaxSpans) return cudaErrorInvalidValue;
@@ -307,14 +329,12 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
         const int n = std::min(chunk, n_tokens - base);
         a.token_base = base;
         dim3 grid(n * a.kv_heads, a.max_spans);
-        if (fused) attention_span_kernel<HD, true><<<grid, q_per_kv * 32, smem, stream>>>(a);
-        else attention_span_kernel<HD, false><<<grid, q_per_kv * 32, smem, stream>>>(a);
-        cudaError_t e = cudaGetLastError();
+        cudaError_t e = fused ? launch_pdl(stream, attention_span_kernel<HD, true>, grid, q_per_kv * 32, smem, a, programmatic)
+                              : launch_pdl(stream, attention_span_kernel<HD, false>, grid, q_per_kv * 32, smem, a, programmatic);
         if (e != cudaSuccess) return e;
         if (launches) ++*launches;
         if (a.max_spans > 1) {
-            attention_merge_kernel<HD><<<n * a.q_heads, HD, 0, stream>>>(a);
-            e = cudaGetLastError();
+            e = launch_pdl(stream, attention_merge_kernel<HD>, dim3(n * a.q_heads), HD, 0, a, programmatic);
             if (e != cudaSuccess) return e;
             if (launches) ++*launches;
         }
@@ -323,11 +343,11 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
 }
 
 cudaError_t dispatch(cudaStream_t stream, const AttnArgs& a, bool fused, int head_dim, int n_tokens, int max_keys,
-                     size_t partial_bytes, int* launches) {
+                     size_t partial_bytes, int* launches, bool programmatic = false) {
     switch (head_dim) {
-        case 64: return launch_hd<64>(stream, a, fused, n_tokens, max_keys, partial_bytes, launches);
-        case 128: return launch_hd<128>(stream, a, fused, n_tokens, max_keys, partial_bytes, launches);
-        case 256: return launch_hd<256>(stream, a, fused, n_tokens, max_keys, partial_bytes, launches);
+        case 64: return launch_hd<64>(stream, a, fused, n_tokens, max_keys, partial_bytes, launches, programmatic);
+        case 128: return launch_hd<128>(stream, a, fused, n_tokens, max_keys, partial_bytes, launches, programmatic);
+        case 256: return launch_hd<256>(stream, a, fused, n_tokens, max_keys, partial_bytes, launches, programmatic);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -377,7 +397,7 @@ cudaError_t launch_attention_decode(cudaStream_t stream, const DecodeAttention& 
     a.q_heads = d.q_heads; a.kv_heads = d.kv_heads; a.window = d.window;
     a.partial = d.partial; a.out = d.out; a.operand = d.operand;
     const int max_keys = d.window > 0 ? std::min(d.max_keys, d.window) : d.max_keys;
-    return dispatch(stream, a, true, d.head_dim, d.n_tokens, max_keys, d.partial_bytes, launches);
+    return dispatch(stream, a, true, d.head_dim, d.n_tokens, max_keys, d.partial_bytes, launches, d.programmatic);
 }
 
 }  // namespace ribn

@@ -235,6 +235,7 @@ cudaError_t run_layers_decode(ribn_b200_executor* ex, const StepPlan& plan, int&
             d.window = 0; d.max_keys = plan.max_keys;
             d.partial = ex->scratch.attn_partial; d.partial_bytes = ex->scratch.attn_partial_bytes;
             d.out = ex->attn; d.operand = ex->op_attn;
+            d.programmatic = pdl;
             cudaError_t e = launch_attention_decode(s, d, &launches);
             if (e != cudaSuccess) return e;
         } else {
@@ -396,6 +397,7 @@ int ribn_b200_destroy(ribn_b200_executor* ex) {
     // Never free device memory while completion is uncertain: leak instead
     // (crates/runtime/src/engine.rs:597-607).
     if (cudaStreamSynchronize(ex->stream) != cudaSuccess) return RIBN_B200_ERROR;
+    for (auto& g : ex->graphs) cudaGraphExecDestroy(g.second.exec);
     for (void* p : ex->allocations) cudaFree(p);
     if (ex->h_rows) cudaFreeHost(ex->h_rows);
     if (ex->h_tokens) cudaFreeHost(ex->h_tokens);
@@ -541,6 +543,8 @@ int ribn_b200_finalize(ribn_b200_executor* ex) {
             CU_TRY(ex, cudaMemcpy(p.data, packed.data(), p.bytes, cudaMemcpyHostToDevice));
         }
     }
+
+    CU_TRY(ex, gemv_prepare());
 
     // Rotary table on the host, with the host libm's powf, so theta matches
     // `pos as f32 * base.powf(-(2 pair) / rot)` bit for bit
@@ -784,20 +788,53 @@ int ribn_b200_submit(ribn_b200_executor* ex, const ribn_b200_batch_item* items, 
     ex->prepared = false;
     p.active = true;
     p.id = ex->next_submission++;
-    CU_TRY(ex, cudaEventRecord(ex->ev_start, ex->stream));
-    CU_TRY(ex, cudaMemcpyAsync(ex->d_rows, ex->h_rows, count * sizeof(RowDesc), cudaMemcpyHostToDevice, ex->stream));
-    if (plan.n_prompt_tokens > 0) {
-        CU_TRY(ex, cudaMemcpyAsync(ex->d_tokens, ex->h_tokens, (size_t)plan.n_prompt_tokens * sizeof(uint32_t),
-                                   cudaMemcpyHostToDevice, ex->stream));
-    }
+    // Everything the step does on the stream, in order: row records and prompt tokens in, kernels,
+    // sampled tokens and the error word out.
+    auto enqueue = [&](int& launches) -> cudaError_t {
+        cudaError_t e = cudaMemcpyAsync(ex->d_rows, ex->h_rows, count * sizeof(RowDesc), cudaMemcpyHostToDevice, ex->stream);
+        if (e == cudaSuccess && plan.n_prompt_tokens > 0) {
+            e = cudaMemcpyAsync(ex->d_tokens, ex->h_tokens, (size_t)plan.n_prompt_tokens * sizeof(uint32_t),
+                                cudaMemcpyHostToDevice, ex->stream);
+        }
+        if (e == cudaSuccess) e = run_step(ex, plan, launches);
+        if (e == cudaSuccess && plan.n_sample > 0) {
+            e = cudaMemcpyAsync(ex->h_sampled, ex->d_sampled, (size_t)plan.n_sample * sizeof(uint32_t),
+                                cudaMemcpyDeviceToHost, ex->stream);
+        }
+        if (e == cudaSuccess) e = cudaMemcpyAsync(ex->h_error, ex->d_error, sizeof(int), cudaMemcpyDeviceToHost, ex->stream);
+        return e;
+    };
     int launches = 0;
-    CU_TRY(ex, run_step(ex, plan, launches));
-    p.launches = launches;
-    if (plan.n_sample > 0) {
-        CU_TRY(ex, cudaMemcpyAsync(ex->h_sampled, ex->d_sampled, (size_t)plan.n_sample * sizeof(uint32_t),
-                                   cudaMemcpyDeviceToHost, ex->stream));
+    const bool graphable = !(ex->cfg.flags & RIBN_B200_FLAG_NO_GRAPH) && decode_family_applies(ex, plan) &&
+                           plan.n_rows == plan.n_tokens && plan.n_prompt_tokens == 0;
+    CU_TRY(ex, cudaEventRecord(ex->ev_start, ex->stream));
+    if (graphable) {
+        // Decode-only steps replay a captured graph.  The attention grid is sized by a bucket of the
+        // longest context (results do not depend on it), so a graph serves 512 consecutive positions.
+        const int bucket = (plan.max_keys + 511) / 512;
+        plan.max_keys = std::min(bucket * 512, ex->cfg.context_tokens);
+        const uint64_t key = (uint64_t)plan.n_tokens | ((uint64_t)plan.n_sample << 16) | ((uint64_t)bucket << 32);
+        auto found = ex->graphs.find(key);
+        if (found == ex->graphs.end()) {
+            cudaGraph_t graph = nullptr;
+            CU_TRY(ex, cudaStreamBeginCapture(ex->stream, cudaStreamCaptureModeThreadLocal));
+            cudaError_t e = enqueue(launches);
+            cudaError_t end = cudaStreamEndCapture(ex->stream, &graph);
+            CU_TRY(ex, e);
+            CU_TRY(ex, end);
+            ribn_b200_executor::StepGraph entry;
+            entry.launches = launches;
+            cudaError_t inst = cudaGraphInstantiate(&entry.exec, graph, 0);
+            cudaGraphDestroy(graph);
+            CU_TRY(ex, inst);
+            found = ex->graphs.emplace(key, entry).first;
+        }
+        launches = found->second.launches;
+        CU_TRY(ex, cudaGraphLaunch(found->second.exec, ex->stream));
+    } else {
+        CU_TRY(ex, enqueue(launches));
     }
-    CU_TRY(ex, cudaMemcpyAsync(ex->h_error, ex->d_error, sizeof(int), cudaMemcpyDeviceToHost, ex->stream));
+    p.launches = launches;
     CU_TRY(ex, cudaEventRecord(ex->ev_done, ex->stream));
     *submission = p.id;
     return RIBN_B200_OK;

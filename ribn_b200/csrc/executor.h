@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <map>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -97,6 +98,9 @@ struct ribn_b200_executor {
     ribn::StepScratch scratch;
     // tensor-core operand forms of the activations (decode rows on the fast path)
     ribn::ActOperand op_hidden, op_attn, op_act, op_head;
+    // Captured decode steps, keyed by (tokens, sampling rows, attention span bucket).
+    struct StepGraph { cudaGraphExec_t exec = nullptr; int launches = 0; };
+    std::map<uint64_t, StepGraph> graphs;
     int* d_error = nullptr;    // raised by a kernel whose bounded wait expired
     int* h_error = nullptr;    // pinned copy read at poll
     std::vector<void*> allocations;

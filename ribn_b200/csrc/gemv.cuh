@@ -124,6 +124,8 @@ constexpr int kGemvMaxMembers = 2;
 // the previous kernel in the stream, so its weight prefetch overlaps that
 // kernel's tail.
 cudaError_t launch_gemv_mma(cudaStream_t stream, const GemvArgs& args, bool programmatic);
+// One-time function attributes (call outside stream capture, with the device current).
+cudaError_t gemv_prepare();
 
 // Scratch shared by the step kernels: per-span attention accumulators.
 struct StepScratch {

@@ -142,13 +142,22 @@ void repack_host(int type, const unsigned char* raw, long long n, long long k, u
 // ---------------------------------------------------------------------------
 namespace {
 
-constexpr int kConsumerWarps = 16;  // two teams of eight; a team consumes every other stage
+// Measurement aid (never defined in the shipped build): 1 = consumers skip the tile math,
+// 2 = no weight copies and no waits (pure consumer instruction stream), 3 = as 2 and no epilogue
+// hand-off, 4 = as 3 with only the header decode of each tile, 5 = as 3 with only the MMA loop.
+#ifndef RIBN_PROBE
+#define RIBN_PROBE 0
+#endif
+
+constexpr int kConsumerWarps = 24;  // three teams of eight; team i consumes stages i, i + 3, ...
 constexpr int kTeamWarps = 8;
+constexpr int kTeams = kConsumerWarps / kTeamWarps;
 constexpr int kStageTiles = 8;      // tiles per bulk copy / ring slot (one per warp of a team)
 constexpr int kProducerWarp = kConsumerWarps;
-constexpr int kEpilogueWarp = kConsumerWarps + 1;
+constexpr int kEpilogueWarp = kConsumerWarps + 1;  // first of kEpilogueWarps: one per team
+constexpr int kEpilogueWarps = kTeams;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = (kConsumerWarps + 2) * 32;
+constexpr int kThreads = (kConsumerWarps + 1 + kEpilogueWarps) * 32;
 constexpr int kMaxRuns = 4;         // row-tile runs per unit: 2 tiles of one matrix, or 2 x (gate, up)
 constexpr int kHdrStride = 20;      // floats per header row: 16 scales + offset sum + pad (conflict-free rows)
 constexpr int kPlanePad = 32;       // bytes between activation digit planes (distinct banks per plane)
@@ -157,7 +166,7 @@ constexpr uint32_t kNibbles = 0x0F0F0F0Fu;
 constexpr uint32_t kTopBits = 0x30303030u;
 constexpr int kMagicInt = 0x4B400000;      // bits of 12582912.0f: int accumulate on top of it, read as float
 constexpr float kMagic = 12582912.0f;
-constexpr int kBarFull = 1, kBarFree = 3;  // named barriers: full[0..1] = 1, 2; free[0..1] = 3, 4
+constexpr int kBarFull = 1, kBarFree = 3;  // named barriers of team t, buffer b: full = 1 + 4 t + b, free = 3 + 4 t + b
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -194,12 +203,12 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
-// Named barriers shared by the consumer warps and the epilogue warp (544 threads).
-__device__ __forceinline__ void bar_arrive(int id) {
-    asm volatile("bar.arrive %0, %1;" ::"r"(id), "n"(kConsumerThreads + 32) : "memory");
+// Named barriers shared by the warps that cooperate on a unit and their epilogue warp.
+__device__ __forceinline__ void bar_arrive(int id, int threads) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
-__device__ __forceinline__ void bar_sync(int id) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(kConsumerThreads + 32) : "memory");
+__device__ __forceinline__ void bar_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 __device__ __forceinline__ void consumer_barrier() {
     asm volatile("bar.sync 5, %0;" ::"n"(kConsumerThreads) : "memory");
@@ -208,13 +217,13 @@ __device__ __forceinline__ void consumer_barrier() {
 // D = A(u8, 16 x 32) * B(s8, 32 x 8) + magic; the result registers are read as floats.
 __device__ __forceinline__ void imma_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(kMagicInt));
 }
 __device__ __forceinline__ void imma_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
         : "r"(a0), "r"(a1), "r"(b0), "r"(kMagicInt));
@@ -230,32 +239,77 @@ __device__ __forceinline__ float byte_f32(uint32_t w, int i) {
     return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | (uint32_t)i)) - 8388608.0f;
 }
 
+// Shared-memory accesses by 32-bit shared-space address: the hot loop then needs one add per access
+// instead of generic 64-bit pointer arithmetic.
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float4 lds128f(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float2 lds64f(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float lds32f(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint32_t v;
+    asm volatile("{\n\t.reg .u16 t;\n\tld.shared.u16 t, [%1];\n\tcvt.u32.u16 %0, t;\n\t}" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128f(uint32_t addr, float a, float b, float c, float d) {
+    asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void sts32f(uint32_t addr, float a) {
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(a) : "memory");
+}
+
+// Shared-memory map of the CTA (generic pointers for set-up and the epilogue warps).
 struct Shared {
     unsigned char* ring;
     signed char* xq;   // [3 * members][K + kPlanePad] digit planes
     float* sx;         // [members][K / 32]
     float* sxs;        // [members][K / 16]
     float* hdr;        // [kConsumerWarps][members][16][kHdrStride]
-    float* red;        // [2][kConsumerWarps][kMaxRuns][members][16]
+    float* red;        // [kTeams][2][kTeamWarps][kMaxRuns][members][16]
     float* scale;      // [kGemvMaxMembers]
     uint32_t full, empty, xbar;  // shared-space addresses of the mbarrier arrays
     int K, members;
 };
 
+// Per-lane shared-space addresses of a consumer warp, fixed for the whole kernel.
+struct Lane {
+    uint32_t b;        // this lane's MMA column in the digit planes (+ 8 t), or a zeroed word
+    uint32_t b_mask;   // all ones for a live column, zero for the empty columns (they read the zeroed word)
+    uint32_t sx, sxs;  // scale arrays
+    uint32_t hdr_wr;   // decode role: header row (lane >> 1) of member 0
+    uint32_t hdr_rd;   // fold role: header row g of this lane's member (row g + 8 is 8 rows further)
+    int members, K;
+    int half;          // decode role: which half of the row's scales
+};
+
+constexpr uint32_t kHdrRow = kHdrStride * 4;        // bytes per header row
+constexpr uint32_t kHdrMember = 16 * kHdrRow;       // bytes per member's header block
+constexpr uint32_t kHdrOff = 64;                    // byte offset of the row's offset sum
+
 struct Accum {
     float c[4];  // (row g, col 2t), (row g, col 2t+1), (row g+8, col 2t), (row g+8, col 2t+1)
     float s[2];  // offset terms of rows g, g+8
 };
-
-// B fragment of MMA column g for the 32 inputs of span `span`: digit plane (g & 3) of member (g >> 2);
-// columns 3 and 7 and absent members are zero.
-__device__ __forceinline__ uint2 load_b(const Shared& sh, int g, int t, int span) {
-    if ((g & 3) < 3 && (g >> 2) < sh.members) {
-        const signed char* p = sh.xq + (size_t)((g >> 2) * 3 + (g & 3)) * (sh.K + kPlanePad) + span * 32 + 8 * t;
-        return *reinterpret_cast<const uint2*>(p);
-    }
-    return make_uint2(0u, 0u);
-}
 
 __device__ __forceinline__ void fold(Accum& a, const int (&c)[4], float s0, float s1) {
     a.c[0] = fmaf(s0, __int_as_float(c[0]) - kMagic, a.c[0]);
@@ -264,64 +318,66 @@ __device__ __forceinline__ void fold(Accum& a, const int (&c)[4], float s0, floa
     a.c[3] = fmaf(s1, __int_as_float(c[3]) - kMagic, a.c[3]);
 }
 
+__device__ __forceinline__ uint2 load_b(const Lane& ln, uint32_t offset) {
+    return lds64(ln.b + (offset & ln.b_mask));
+}
+
 // ---- Q4_K: w = gs * q - gm  =>  (gs * sx) * C  -  gm * (sx * sum digits) ------------------------
-__device__ __forceinline__ void tile_q4k(const unsigned char* tile, const Shared& sh, int kb, float* hdr, int lane,
-                                         Accum& acc) {
-    const int g = lane >> 2, t = lane & 3, m = t >> 1;
-    {
+template <int MEMBERS>
+__device__ __forceinline__ void tile_q4k(uint32_t tile, const Lane& ln, int kb, int lane, Accum& acc) {
+    if (RIBN_PROBE != 5) {
         // lane -> (row, half): scales and offsets of groups 4 half .. 4 half + 3, for every member
-        const int row = lane >> 1, half = lane & 1;
-        const uint4 h = *reinterpret_cast<const uint4*>(tile + 2048 + row * 16);
+        const uint4 h = lds128(tile + 2048 + (lane >> 1) * 16);
         const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
         const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
-        const uint32_t sc = half ? ((h.w & kNibbles) | ((h.y >> 2) & kTopBits)) : (h.y & 0x3F3F3F3Fu);
-        const uint32_t mn = half ? (((h.w >> 4) & kNibbles) | ((h.z >> 2) & kTopBits)) : (h.z & 0x3F3F3F3Fu);
+        const uint32_t sc = ln.half ? ((h.w & kNibbles) | ((h.y >> 2) & kTopBits)) : (h.y & 0x3F3F3F3Fu);
+        const uint32_t mn = ln.half ? (((h.w >> 4) & kNibbles) | ((h.z >> 2) & kTopBits)) : (h.z & 0x3F3F3F3Fu);
         float gs[4], gm[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) { gs[i] = d * byte_f32(sc, i); gm[i] = dmin * byte_f32(mn, i); }
-        for (int mm = 0; mm < sh.members; ++mm) {
-            const float4 sx = *reinterpret_cast<const float4*>(sh.sx + (size_t)mm * (sh.K / 32) + kb * 8 + half * 4);
-            const float4 sa = *reinterpret_cast<const float4*>(sh.sxs + (size_t)mm * (sh.K / 16) + kb * 16 + half * 8);
-            const float4 sb = *reinterpret_cast<const float4*>(sh.sxs + (size_t)mm * (sh.K / 16) + kb * 16 + half * 8 + 4);
-            float* out = hdr + (mm * 16 + row) * kHdrStride;
-            *reinterpret_cast<float4*>(out + half * 4) = make_float4(gs[0] * sx.x, gs[1] * sx.y, gs[2] * sx.z, gs[3] * sx.w);
+#pragma unroll
+        for (int mm = 0; mm < MEMBERS; ++mm) {
+            const float4 sx = lds128f(ln.sx + (uint32_t)(mm * (ln.K / 32) + kb * 8 + ln.half * 4) * 4);
+            const uint32_t sxs = ln.sxs + (uint32_t)(mm * (ln.K / 16) + kb * 16 + ln.half * 8) * 4;
+            const float4 sa = lds128f(sxs), sb = lds128f(sxs + 16);
+            const uint32_t out = ln.hdr_wr + mm * kHdrMember;
+            sts128f(out + ln.half * 16, gs[0] * sx.x, gs[1] * sx.y, gs[2] * sx.z, gs[3] * sx.w);
             float off = gm[0] * (sa.x + sa.y);
             off = fmaf(gm[1], sa.z + sa.w, off);
             off = fmaf(gm[2], sb.x + sb.y, off);
             off = fmaf(gm[3], sb.z + sb.w, off);
             off += __shfl_xor_sync(0xffffffffu, off, 1);
-            if (half == 0) out[16] = -off;
+            if (ln.half == 0) sts32f(out + kHdrOff, -off);
         }
     }
     __syncwarp();
-    const float* h0 = hdr + (m * 16 + g) * kHdrStride;
-    const float* h1 = hdr + (m * 16 + g + 8) * kHdrStride;
-#pragma unroll 2
+    if (RIBN_PROBE == 4) return;
+    const uint32_t wbase = tile + lane * 16, bbase = kb * 256;
+#pragma unroll
     for (int j = 0; j < 4; ++j) {
-        const uint4 w = *reinterpret_cast<const uint4*>(tile + j * 512 + lane * 16);
-        const uint2 be = load_b(sh, g, t, kb * 8 + 2 * j), bo = load_b(sh, g, t, kb * 8 + 2 * j + 1);
+        const uint4 w = lds128(wbase + j * 512);
+        const uint2 be = load_b(ln, bbase + j * 64), bo = load_b(ln, bbase + j * 64 + 32);
+        const float2 f0 = lds64f(ln.hdr_rd + j * 8), f1 = lds64f(ln.hdr_rd + 8 * kHdrRow + j * 8);
         int ce[4], co[4];
         imma_k32(ce, w.x & kNibbles, w.z & kNibbles, w.y & kNibbles, w.w & kNibbles, be.x, be.y);
         imma_k32(co, (w.x >> 4) & kNibbles, (w.z >> 4) & kNibbles, (w.y >> 4) & kNibbles, (w.w >> 4) & kNibbles, bo.x,
                  bo.y);
-        const float2 f0 = *reinterpret_cast<const float2*>(h0 + 2 * j), f1 = *reinterpret_cast<const float2*>(h1 + 2 * j);
         fold(acc, ce, f0.x, f1.x);
         fold(acc, co, f0.y, f1.y);
     }
-    acc.s[0] += h0[16];
-    acc.s[1] += h1[16];
+    acc.s[0] += lds32f(ln.hdr_rd + kHdrOff);
+    acc.s[1] += lds32f(ln.hdr_rd + 8 * kHdrRow + kHdrOff);
     __syncwarp();
 }
 
 // ---- Q6_K: w = gs * (q - 32), one scale per 16 inputs (k16 MMA) ---------------------------------
-__device__ __forceinline__ void tile_q6k(const unsigned char* tile, const Shared& sh, int kb, float* hdr, int lane,
-                                         Accum& acc) {
-    const int g = lane >> 2, t = lane & 3, m = t >> 1;
-    {
+template <int MEMBERS>
+__device__ __forceinline__ void tile_q6k(uint32_t tile, const Lane& ln, int kb, int lane, Accum& acc) {
+    if (RIBN_PROBE != 5) {
         // lane -> (row, half): the eight 16-input scales half * 8 .. half * 8 + 7 (groups half * 4 ..)
-        const int row = lane >> 1, half = lane & 1;
-        const uint2 s8 = *reinterpret_cast<const uint2*>(tile + 3072 + row * 16 + half * 8);
-        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(tile + 3328 + row * 2)));
+        const int row = lane >> 1;
+        const uint2 s8 = lds64(tile + 3072 + row * 16 + ln.half * 8);
+        const float d = __half2float(__ushort_as_half((unsigned short)lds16(tile + 3328 + row * 2)));
         float gs[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -329,29 +385,30 @@ __device__ __forceinline__ void tile_q6k(const unsigned char* tile, const Shared
             gs[i] = d * (byte_f32(s8.x ^ 0x80808080u, i) - 128.0f);
             gs[4 + i] = d * (byte_f32(s8.y ^ 0x80808080u, i) - 128.0f);
         }
-        for (int mm = 0; mm < sh.members; ++mm) {
-            const float4 sx = *reinterpret_cast<const float4*>(sh.sx + (size_t)mm * (sh.K / 32) + kb * 8 + half * 4);
-            const float4 sa = *reinterpret_cast<const float4*>(sh.sxs + (size_t)mm * (sh.K / 16) + kb * 16 + half * 8);
-            const float4 sb = *reinterpret_cast<const float4*>(sh.sxs + (size_t)mm * (sh.K / 16) + kb * 16 + half * 8 + 4);
-            float* out = hdr + (mm * 16 + row) * kHdrStride;
-            *reinterpret_cast<float4*>(out + half * 8) = make_float4(gs[0] * sx.x, gs[1] * sx.x, gs[2] * sx.y, gs[3] * sx.y);
-            *reinterpret_cast<float4*>(out + half * 8 + 4) = make_float4(gs[4] * sx.z, gs[5] * sx.z, gs[6] * sx.w, gs[7] * sx.w);
+#pragma unroll
+        for (int mm = 0; mm < MEMBERS; ++mm) {
+            const float4 sx = lds128f(ln.sx + (uint32_t)(mm * (ln.K / 32) + kb * 8 + ln.half * 4) * 4);
+            const uint32_t sxs = ln.sxs + (uint32_t)(mm * (ln.K / 16) + kb * 16 + ln.half * 8) * 4;
+            const float4 sa = lds128f(sxs), sb = lds128f(sxs + 16);
+            const uint32_t out = ln.hdr_wr + mm * kHdrMember;
+            sts128f(out + ln.half * 32, gs[0] * sx.x, gs[1] * sx.x, gs[2] * sx.y, gs[3] * sx.y);
+            sts128f(out + ln.half * 32 + 16, gs[4] * sx.z, gs[5] * sx.z, gs[6] * sx.w, gs[7] * sx.w);
             float off = gs[0] * sa.x;
             off = fmaf(gs[1], sa.y, off); off = fmaf(gs[2], sa.z, off); off = fmaf(gs[3], sa.w, off);
             off = fmaf(gs[4], sb.x, off); off = fmaf(gs[5], sb.y, off); off = fmaf(gs[6], sb.z, off); off = fmaf(gs[7], sb.w, off);
             off += __shfl_xor_sync(0xffffffffu, off, 1);
-            if (half == 0) out[16] = -32.0f * off;
+            if (ln.half == 0) sts32f(out + kHdrOff, -32.0f * off);
         }
     }
     __syncwarp();
-    const float* h0 = hdr + (m * 16 + g) * kHdrStride;
-    const float* h1 = hdr + (m * 16 + g + 8) * kHdrStride;
-#pragma unroll 1
+    if (RIBN_PROBE == 4) return;
+    const uint32_t wbase = tile + lane * 16, bbase = kb * 256;
+#pragma unroll
     for (int c = 0; c < 2; ++c) {
-        const uint4 qh = *reinterpret_cast<const uint4*>(tile + 2048 + c * 512 + lane * 16);
+        const uint4 qh = lds128(wbase + 2048 + c * 512);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const uint4 w = *reinterpret_cast<const uint4*>(tile + (c * 2 + h) * 512 + lane * 16);
+            const uint4 w = lds128(wbase + (c * 2 + h) * 512);
             const uint32_t wh0 = h == 0 ? qh.x : qh.z, wh1 = h == 0 ? qh.y : qh.w;
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
@@ -364,58 +421,56 @@ __device__ __forceinline__ void tile_q6k(const unsigned char* tile, const Shared
                 else { t0 = wh0 >> 2; t1 = wh1 >> 2; }
                 const uint32_t a0 = and_or(v < 2 ? l0 : l0 >> 4, kNibbles, t0 & kTopBits);
                 const uint32_t a1 = and_or(v < 2 ? l1 : l1 >> 4, kNibbles, t1 & kTopBits);
-                const int group = c * 4 + v, sub = group * 2 + h;
-                const uint2 b = load_b(sh, g, t, kb * 8 + group);
+                const int sub = (c * 4 + v) * 2 + h;
+                const uint2 b = load_b(ln, bbase + (c * 4 + v) * 32);
                 int cc[4];
                 imma_k16(cc, a0, a1, h == 0 ? b.x : b.y);
-                fold(acc, cc, h0[sub], h1[sub]);
+                fold(acc, cc, lds32f(ln.hdr_rd + sub * 4), lds32f(ln.hdr_rd + 8 * kHdrRow + sub * 4));
             }
         }
     }
-    acc.s[0] += h0[16];
-    acc.s[1] += h1[16];
+    acc.s[0] += lds32f(ln.hdr_rd + kHdrOff);
+    acc.s[1] += lds32f(ln.hdr_rd + 8 * kHdrRow + kHdrOff);
     __syncwarp();
 }
 
 // ---- Q8_0: stored byte u = q + 128 is the u8 operand as is; w = d * (u - 128) -----------------------
-__device__ __forceinline__ void tile_q8_0(const unsigned char* tile, const Shared& sh, int kb, float* hdr, int lane,
-                                          Accum& acc) {
-    const int g = lane >> 2, t = lane & 3, m = t >> 1;
+template <int MEMBERS>
+__device__ __forceinline__ void tile_q8_0(uint32_t tile, const Lane& ln, int kb, int lane, Accum& acc) {
     {
-        const int row = lane >> 1, half = lane & 1;
-        const uint2 d4 = *reinterpret_cast<const uint2*>(tile + 4096 + row * 16 + half * 8);
+        const uint2 d4 = lds64(tile + 4096 + (lane >> 1) * 16 + ln.half * 8);
         float d[4];
         d[0] = __half2float(__ushort_as_half((unsigned short)(d4.x & 0xffffu)));
         d[1] = __half2float(__ushort_as_half((unsigned short)(d4.x >> 16)));
         d[2] = __half2float(__ushort_as_half((unsigned short)(d4.y & 0xffffu)));
         d[3] = __half2float(__ushort_as_half((unsigned short)(d4.y >> 16)));
-        for (int mm = 0; mm < sh.members; ++mm) {
-            const float4 sx = *reinterpret_cast<const float4*>(sh.sx + (size_t)mm * (sh.K / 32) + kb * 8 + half * 4);
-            const float4 sa = *reinterpret_cast<const float4*>(sh.sxs + (size_t)mm * (sh.K / 16) + kb * 16 + half * 8);
-            const float4 sb = *reinterpret_cast<const float4*>(sh.sxs + (size_t)mm * (sh.K / 16) + kb * 16 + half * 8 + 4);
-            float* out = hdr + (mm * 16 + row) * kHdrStride;
-            *reinterpret_cast<float4*>(out + half * 4) = make_float4(d[0] * sx.x, d[1] * sx.y, d[2] * sx.z, d[3] * sx.w);
+#pragma unroll
+        for (int mm = 0; mm < MEMBERS; ++mm) {
+            const float4 sx = lds128f(ln.sx + (uint32_t)(mm * (ln.K / 32) + kb * 8 + ln.half * 4) * 4);
+            const uint32_t sxs = ln.sxs + (uint32_t)(mm * (ln.K / 16) + kb * 16 + ln.half * 8) * 4;
+            const float4 sa = lds128f(sxs), sb = lds128f(sxs + 16);
+            const uint32_t out = ln.hdr_wr + mm * kHdrMember;
+            sts128f(out + ln.half * 16, d[0] * sx.x, d[1] * sx.y, d[2] * sx.z, d[3] * sx.w);
             float off = d[0] * (sa.x + sa.y);
             off = fmaf(d[1], sa.z + sa.w, off);
             off = fmaf(d[2], sb.x + sb.y, off);
             off = fmaf(d[3], sb.z + sb.w, off);
             off += __shfl_xor_sync(0xffffffffu, off, 1);
-            if (half == 0) out[16] = -128.0f * off;
+            if (ln.half == 0) sts32f(out + kHdrOff, -128.0f * off);
         }
     }
     __syncwarp();
-    const float* h0 = hdr + (m * 16 + g) * kHdrStride;
-    const float* h1 = hdr + (m * 16 + g + 8) * kHdrStride;
-#pragma unroll 2
+    const uint32_t wbase = tile + lane * 16, bbase = kb * 256;
+#pragma unroll
     for (int b8 = 0; b8 < 8; ++b8) {
-        const uint4 w = *reinterpret_cast<const uint4*>(tile + b8 * 512 + lane * 16);
-        const uint2 b = load_b(sh, g, t, kb * 8 + b8);
+        const uint4 w = lds128(wbase + b8 * 512);
+        const uint2 b = load_b(ln, bbase + b8 * 32);
         int cc[4];
         imma_k32(cc, w.x, w.z, w.y, w.w, b.x, b.y);
-        fold(acc, cc, h0[b8], h1[b8]);
+        fold(acc, cc, lds32f(ln.hdr_rd + b8 * 4), lds32f(ln.hdr_rd + 8 * kHdrRow + b8 * 4));
     }
-    acc.s[0] += h0[16];
-    acc.s[1] += h1[16];
+    acc.s[0] += lds32f(ln.hdr_rd + kHdrOff);
+    acc.s[1] += lds32f(ln.hdr_rd + 8 * kHdrRow + kHdrOff);
     __syncwarp();
 }
 
@@ -433,9 +488,19 @@ __device__ __forceinline__ UnitPlace place_unit(const GemvArgs& a, bool swiglu, 
     return p;
 }
 
-__global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a, const int slots, const int slot_bytes) {
+// A team's position in its own sequence of ring stages: unit, run within the unit, stage within the run.
+struct Cursor {
+    int u, r, st;
+};
+
+// SHARED = false: each team of eight warps owns whole units (many units per CTA: the output head).
+// SHARED = true: all 24 warps cooperate on every unit, the teams taking alternate stages (the layer
+// projections, which give a CTA only one to three units).
+template <int MEMBERS, bool SHARED>
+__global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a, const int slots_per_team,
+                                                               const int slot_bytes) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int K = a.k, planes = 3 * a.members;
+    const int K = a.k, planes = 3 * MEMBERS, slots = slots_per_team * kTeams;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool swiglu = a.epilogue == kSwiGLU;
     const int runs = swiglu ? 4 : 2;  // row-tile runs per unit
@@ -444,15 +509,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
         unsigned char* p = smem_raw;
         sh.ring = p; p += (size_t)slots * slot_bytes;
         sh.xq = reinterpret_cast<signed char*>(p); p += (size_t)planes * (K + kPlanePad);
-        sh.sx = reinterpret_cast<float*>(p); p += (size_t)a.members * (K / 32) * sizeof(float);
-        sh.sxs = reinterpret_cast<float*>(p); p += (size_t)a.members * (K / 16) * sizeof(float);
-        sh.hdr = reinterpret_cast<float*>(p); p += (size_t)kConsumerWarps * a.members * 16 * kHdrStride * sizeof(float);
-        sh.red = reinterpret_cast<float*>(p); p += (size_t)2 * kConsumerWarps * kMaxRuns * a.members * 16 * sizeof(float);
-        sh.scale = reinterpret_cast<float*>(p); p += 16;
+        sh.sx = reinterpret_cast<float*>(p); p += (size_t)MEMBERS * (K / 32) * sizeof(float);
+        sh.sxs = reinterpret_cast<float*>(p); p += (size_t)MEMBERS * (K / 16) * sizeof(float);
+        sh.hdr = reinterpret_cast<float*>(p); p += (size_t)kConsumerWarps * MEMBERS * 16 * kHdrStride * sizeof(float);
+        sh.red = reinterpret_cast<float*>(p); p += (size_t)2 * kConsumerWarps * kMaxRuns * MEMBERS * 16 * sizeof(float);
+        sh.scale = reinterpret_cast<float*>(p); p += 16;  // the zeroed word read by the empty MMA columns
         sh.full = smem_u32(p); p += (size_t)slots * 8;
         sh.empty = smem_u32(p); p += (size_t)slots * 8;
         sh.xbar = smem_u32(p);
-        sh.K = K; sh.members = a.members;
+        sh.K = K; sh.members = MEMBERS;
     }
     const int k_tiles = K / kTileCols;
     const int stages_per_run = (k_tiles + kStageTiles - 1) / kStageTiles;
@@ -465,36 +530,58 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
     if (threadIdx.x == 0) {
         for (int i = 0; i < slots; ++i) { mbar_init(sh.full + i * 8, 1); mbar_init(sh.empty + i * 8, kTeamWarps); }
         mbar_init(sh.xbar, 1);
+        sh.scale[0] = sh.scale[1] = sh.scale[2] = sh.scale[3] = 0.0f;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
     // Let the next kernel in the stream begin (its weight prefetch does not depend on this one).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
+    // Where run r of unit u lives; false when the unit has no such run (odd tail of a segment).
+    auto locate = [&](int u, int r, const GemvSegment*& seg, int& rt) -> bool {
+        const UnitPlace pl = place_unit(a, swiglu, u);
+        seg = &a.seg[swiglu ? (r & 1) : pl.seg];
+        rt = pl.rt0 + (swiglu ? (r >> 1) : r);
+        return rt < seg->row_tiles;
+    };
+
     if (warp == kProducerWarp) {
-        // ---------------- producer: one bulk copy per stage of up to 8 contiguous tiles ----------------
-        if (lane == 0) {
-            bool alive = true;
-            uint32_t n = 0;
-            for (int u = u0; u < u1 && alive; ++u) {
-                const UnitPlace pl = place_unit(a, swiglu, u);
-                for (int r = 0; r < runs && alive; ++r) {
-                    const GemvSegment& s = a.seg[swiglu ? (r & 1) : pl.seg];
-                    const int rt = pl.rt0 + (swiglu ? (r >> 1) : r);
-                    if (rt >= s.row_tiles) continue;
-                    const uint32_t tile_bytes = (uint32_t)packed_tile_bytes(s.type);
-                    const unsigned char* run = s.data + (size_t)rt * k_tiles * tile_bytes;
-                    for (int st = 0; st < stages_per_run; ++st, ++n) {
-                        const uint32_t slot = n % (uint32_t)slots;
-                        if (n >= (uint32_t)slots) {
-                            alive = mbar_wait(sh.empty + slot * 8, ((n / (uint32_t)slots) - 1u) & 1u, a.error_flag, 1);
-                            if (!alive) break;
-                        }
-                        const int tiles = min(kStageTiles, k_tiles - st * kStageTiles);
-                        const uint32_t bytes = (uint32_t)tiles * tile_bytes;
-                        mbar_expect_tx(sh.full + slot * 8, bytes);
-                        bulk_g2s(smem_u32(sh.ring + (size_t)slot * slot_bytes),
-                                 run + (size_t)st * kStageTiles * tile_bytes, bytes, sh.full + slot * 8);
+        // ---------------- producer: team t's k-th stage goes to slot (k % S) * 3 + t ----------------
+        if (lane == 0 && RIBN_PROBE < 2) {
+            constexpr int kCursors = SHARED ? 1 : kTeams;
+            const int unit_step = SHARED ? 1 : kTeams;
+            const uint32_t ring_len = SHARED ? (uint32_t)slots : (uint32_t)slots_per_team;  // slots a cursor cycles through
+            Cursor cur[kCursors];
+            uint32_t k[kCursors];
+            for (int t = 0; t < kCursors; ++t) { cur[t] = Cursor{u0 + t, 0, 0}; k[t] = 0; }
+            bool alive = true, any = true;
+            while (any && alive) {
+                any = false;
+                for (int t = 0; t < kCursors && alive; ++t) {
+                    Cursor& c = cur[t];
+                    const GemvSegment* seg = nullptr;
+                    int rt = 0;
+                    while (c.u < u1 && !locate(c.u, c.r, seg, rt)) {  // skip runs the unit does not have
+                        if (++c.r == runs) { c.r = 0; c.u += unit_step; }
+                    }
+                    if (c.u >= u1) continue;
+                    any = true;
+                    const uint32_t tile_bytes = (uint32_t)packed_tile_bytes(seg->type);
+                    const uint32_t slot = SHARED ? k[t] % ring_len : (k[t] % ring_len) * kTeams + t;
+                    if (k[t] >= ring_len) {
+                        alive = mbar_wait(sh.empty + slot * 8, ((k[t] / ring_len) - 1u) & 1u, a.error_flag, 1);
+                        if (!alive) break;
+                    }
+                    const int tiles = min(kStageTiles, k_tiles - c.st * kStageTiles);
+                    const uint32_t bytes = (uint32_t)tiles * tile_bytes;
+                    mbar_expect_tx(sh.full + slot * 8, bytes);
+                    bulk_g2s(smem_u32(sh.ring + (size_t)slot * slot_bytes),
+                             seg->data + ((size_t)rt * k_tiles + (size_t)c.st * kStageTiles) * tile_bytes, bytes,
+                             sh.full + slot * 8);
+                    ++k[t];
+                    if (++c.st == stages_per_run) {
+                        c.st = 0;
+                        if (++c.r == runs) { c.r = 0; c.u += unit_step; }
                     }
                 }
             }
@@ -504,10 +591,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
 
     asm volatile("griddepcontrol.wait;" ::: "memory");  // activations and the residual come from the previous kernel
 
-    if (warp == kEpilogueWarp) {
+    if (warp >= kEpilogueWarp && RIBN_PROBE >= 3) return;
+    if (warp > kEpilogueWarp && SHARED) return;  // one epilogue warp serves the single cooperating set
+    // cooperating set: its warps, barrier participants, and where its partial sums live
+    constexpr int kSetWarps = SHARED ? kConsumerWarps : kTeamWarps;
+    const int bar_threads = kSetWarps * 32 + 32;
+    const int unit_step = SHARED ? 1 : kTeams;
+    if (warp >= kEpilogueWarp) {
         // ---------------- epilogue warp: lane = one of the unit's 32 output rows ----------------
-        float inv_norm[kGemvMaxMembers];
-        for (int m = 0; m < a.members; ++m) {
+        const int team = SHARED ? 0 : warp - kEpilogueWarp;
+        float inv_norm[MEMBERS];
+#pragma unroll
+        for (int m = 0; m < MEMBERS; ++m) {
             // RMSNorm factor: fixed-order sum of the producer's per-32 sums of squares.
             inv_norm[m] = 1.0f;
             if (a.in_has_norm) {
@@ -520,61 +615,67 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
             }
         }
         int buf = 0;
-        for (int u = u0; u < u1; ++u, buf ^= 1) {
+        for (int u = u0 + team; u < u1; u += unit_step, buf ^= 1) {
             const UnitPlace pl = place_unit(a, swiglu, u);
             const GemvSegment& s = a.seg[swiglu ? 0 : pl.seg];
             const int half = lane >> 4, row = lane & 15;
             const int rt = pl.rt0 + half;
             const int n_index = rt * kTileRows + row;
-            bar_sync(kBarFull + buf);  // every consumer warp has left its partial sums of this unit
-            float v0[kGemvMaxMembers], v1[kGemvMaxMembers];
-            for (int m = 0; m < a.members; ++m) {
-                const float* base = sh.red + ((size_t)buf * kConsumerWarps * kMaxRuns * a.members) * 16;
-                const int run0 = swiglu ? 2 * half : half;
+            const bool valid = rt < s.row_tiles && n_index < s.n;
+            // Fetch what does not depend on the consumers before waiting for them.
+            float prior[MEMBERS];
+#pragma unroll
+            for (int m = 0; m < MEMBERS; ++m) {
+                prior[m] = (valid && a.epilogue == kResidual) ? s.y[(size_t)m * s.n + n_index] : 0.0f;
+            }
+            const float norm_w = (valid && a.out.dig != nullptr && a.out_norm_weight != nullptr) ? a.out_norm_weight[n_index] : 1.0f;
+            bar_sync(kBarFull + team * 4 + buf, bar_threads);  // the set's warps have left their partial sums of this unit
+            float v0[MEMBERS], v1[MEMBERS];
+            const float* base = sh.red + (size_t)(team * 2 + buf) * kSetWarps * kMaxRuns * MEMBERS * 16;
+            const int run0 = swiglu ? 2 * half : half;
+#pragma unroll
+            for (int m = 0; m < MEMBERS; ++m) {
                 float x0 = 0.0f, x1 = 0.0f;
-#pragma unroll 4
-                for (int w = 0; w < kConsumerWarps; ++w) {
-                    x0 += base[(((size_t)w * kMaxRuns + run0) * a.members + m) * 16 + row];
-                    if (swiglu) x1 += base[(((size_t)w * kMaxRuns + run0 + 1) * a.members + m) * 16 + row];
+#pragma unroll 8
+                for (int w = 0; w < kSetWarps; ++w) {
+                    x0 += base[(((size_t)w * kMaxRuns + run0) * MEMBERS + m) * 16 + row];
+                    if (swiglu) x1 += base[(((size_t)w * kMaxRuns + run0 + 1) * MEMBERS + m) * 16 + row];
                 }
                 v0[m] = x0 * inv_norm[m];
                 v1[m] = x1 * inv_norm[m];
             }
             __syncwarp();
-            bar_arrive(kBarFree + buf);  // the buffer may be overwritten
-            for (int m = 0; m < a.members; ++m) {
-                const bool valid = rt < s.row_tiles && n_index < s.n;
+            bar_arrive(kBarFree + team * 4 + buf, bar_threads);  // the buffer may be overwritten
+#pragma unroll
+            for (int m = 0; m < MEMBERS; ++m) {
                 float result = 0.0f, square = 0.0f;
                 if (valid) {
-                    float* y = s.y + (size_t)m * s.n + n_index;
                     if (a.epilogue == kResidual) {
-                        result = *y + v0[m];
-                        *y = result;
+                        result = prior[m] + v0[m];
+                        s.y[(size_t)m * s.n + n_index] = result;
                         square = result * result;
                     } else if (swiglu) {
                         result = v0[m] / (1.0f + expf(-v0[m])) * v1[m];
                         if (a.swiglu_f32 != nullptr) a.swiglu_f32[(size_t)m * s.n + n_index] = result;
                     } else {
                         result = v0[m];
-                        *y = result;
+                        s.y[(size_t)m * s.n + n_index] = result;
                     }
                 }
                 if (a.out.dig != nullptr && pl.rt0 * kTileRows < s.n) {
-                    float v = result;
-                    if (valid && a.out_norm_weight != nullptr) v *= a.out_norm_weight[n_index];
                     ActOperand out = a.out;
                     if (a.epilogue != kResidual) out.ss32 = nullptr;
-                    operand_store_span(out, m, s.n, pl.rt0 / 2, lane, v, square);
+                    operand_store_span(out, m, s.n, pl.rt0 / 2, lane, result * norm_w, square);
                 }
             }
         }
         return;
     }
 
-    // ---------------- consumers ----------------
+    // ---------------- consumers: a team of eight warps owns whole units; each warp takes one tile per stage ----------------
     if (threadIdx.x == 0) {
-        const uint32_t plane_bytes = (uint32_t)K, sx_bytes = (uint32_t)a.members * (K / 32) * 4u,
-                       sxs_bytes = (uint32_t)a.members * (K / 16) * 4u;
+        const uint32_t plane_bytes = (uint32_t)K, sx_bytes = (uint32_t)MEMBERS * (K / 32) * 4u,
+                       sxs_bytes = (uint32_t)MEMBERS * (K / 16) * 4u;
         mbar_expect_tx(sh.xbar, plane_bytes * (uint32_t)planes + sx_bytes + sxs_bytes);
         for (int c = 0; c < planes; ++c) {
             bulk_g2s(smem_u32(sh.xq + (size_t)c * (K + kPlanePad)), a.in.dig + (size_t)c * K, plane_bytes, sh.xbar);
@@ -583,14 +684,32 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
         bulk_g2s(smem_u32(sh.sxs), a.in.sxs16, sxs_bytes, sh.xbar);
     }
     bool alive = mbar_wait(sh.xbar, 0, a.error_flag, 2);
+    if (RIBN_PROBE >= 2) alive = false;
+    if (RIBN_PROBE == 7) return;  // launch, set-up and activation load only
 
     const int g = lane >> 2, t = lane & 3;
     const int team = warp / kTeamWarps, member_warp = warp % kTeamWarps;
-    float* hdr = sh.hdr + (size_t)warp * a.members * 16 * kHdrStride;
-    uint32_t n = 0;  // stage counter, in step with the producer's
-    int buf = 0;
-    for (int u = u0; u < u1; ++u, buf ^= 1) {
-        const UnitPlace pl = place_unit(a, swiglu, u);
+    Lane ln;
+    {
+        const uint32_t hdr = smem_u32(sh.hdr) + (uint32_t)warp * MEMBERS * kHdrMember;
+        const bool live = (g & 3) < 3 && (g >> 2) < MEMBERS;
+        ln.b_mask = live ? 0xffffffffu : 0u;
+        ln.b = live ? smem_u32(sh.xq) + (uint32_t)((g >> 2) * 3 + (g & 3)) * (uint32_t)(K + kPlanePad) + 8 * t
+                    : smem_u32(sh.scale);
+        ln.sx = smem_u32(sh.sx);
+        ln.sxs = smem_u32(sh.sxs);
+        ln.hdr_wr = hdr + (lane >> 1) * kHdrRow;
+        ln.hdr_rd = hdr + (uint32_t)(t >> 1) * kHdrMember + g * kHdrRow;
+        ln.members = MEMBERS;
+        ln.K = K;
+        ln.half = lane & 1;
+    }
+    const uint32_t ring = smem_u32(sh.ring);
+    const int set = SHARED ? 0 : team, set_warp = SHARED ? warp : member_warp;
+    const uint32_t ring_len = SHARED ? (uint32_t)slots : (uint32_t)slots_per_team;
+    uint32_t k = 0;   // the set's stage counter, in step with the producer's
+    int buf = 0, done = 0;
+    for (int u = u0 + set; u < u1; u += unit_step, buf ^= 1, ++done) {
         Accum acc[kMaxRuns];
 #pragma unroll
         for (int r = 0; r < kMaxRuns; ++r) {
@@ -600,45 +719,45 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
 #pragma unroll
         for (int r = 0; r < kMaxRuns; ++r) {
             if (r >= runs) break;
-            const GemvSegment& s = a.seg[swiglu ? (r & 1) : pl.seg];
-            const int rt = pl.rt0 + (swiglu ? (r >> 1) : r);
-            if (rt >= s.row_tiles) continue;
-            const int type = s.type;
+            const GemvSegment* seg = nullptr;
+            int rt = 0;
+            if (!locate(u, r, seg, rt)) continue;
+            const int type = seg->type;
             const int tile_bytes = packed_tile_bytes(type);
-            for (int st = 0; st < stages_per_run; ++st, ++n) {
-                if ((int)(n & 1u) != team) continue;  // the other team's stage
-                const uint32_t slot = n % (uint32_t)slots;
-                if (alive) alive = mbar_wait(sh.full + slot * 8, (n / (uint32_t)slots) & 1u, a.error_flag, 3);
+            for (int st = 0; st < stages_per_run; ++st, ++k) {
+                if (SHARED && (int)(k % (uint32_t)kTeams) != team) continue;  // another team's stage
+                const uint32_t slot = SHARED ? k % ring_len : (k % ring_len) * kTeams + team;
+                if (alive) alive = mbar_wait(sh.full + slot * 8, (k / ring_len) & 1u, a.error_flag, 3);
                 const int kb = st * kStageTiles + member_warp;
-                if (kb < k_tiles) {
-                    const unsigned char* tile = sh.ring + (size_t)slot * slot_bytes + (size_t)member_warp * tile_bytes;
-                    if (type == kQ4_K) tile_q4k(tile, sh, kb, hdr, lane, acc[r]);
-                    else if (type == kQ6_K) tile_q6k(tile, sh, kb, hdr, lane, acc[r]);
-                    else tile_q8_0(tile, sh, kb, hdr, lane, acc[r]);
+                if (kb < k_tiles && RIBN_PROBE != 1 && RIBN_PROBE != 6) {
+                    const uint32_t tile = ring + slot * (uint32_t)slot_bytes + (uint32_t)(member_warp * tile_bytes);
+                    if (type == kQ4_K) tile_q4k<MEMBERS>(tile, ln, kb, lane, acc[r]);
+                    else if (type == kQ6_K) tile_q6k<MEMBERS>(tile, ln, kb, lane, acc[r]);
+                    else tile_q8_0<MEMBERS>(tile, ln, kb, lane, acc[r]);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sh.empty + slot * 8);  // this warp has left the stage
             }
         }
         // Per-warp partial of (row, member): digits 1 and 2 are this lane's two columns, digit 3 is the
-        // first column of the next lane; lanes with even t own members t / 2.
-        if (u - u0 >= 2) bar_sync(kBarFree + buf);  // the epilogue warp has read this buffer's previous unit
-        float* red = sh.red + (((size_t)buf * kConsumerWarps + warp) * kMaxRuns) * a.members * 16;
+        // first column of the next lane; lanes with even t own member t / 2.
+        if (done >= 2 && RIBN_PROBE < 3) bar_sync(kBarFree + set * 4 + buf, bar_threads);  // the epilogue warp has read this buffer
+        float* red = sh.red + ((size_t)(set * 2 + buf) * kSetWarps + set_warp) * kMaxRuns * MEMBERS * 16;
 #pragma unroll
         for (int r = 0; r < kMaxRuns; ++r) {
             if (r >= runs) break;
             const float d3a = __shfl_down_sync(0xffffffffu, acc[r].c[0], 1);
             const float d3b = __shfl_down_sync(0xffffffffu, acc[r].c[2], 1);
-            if ((t & 1) == 0 && (t >> 1) < a.members) {
+            if ((t & 1) == 0 && (t >> 1) < MEMBERS) {
                 const float va = acc[r].c[0] + acc[r].c[1] * (1.0f / 128.0f) + d3a * (1.0f / 16384.0f) + acc[r].s[0];
                 const float vb = acc[r].c[2] + acc[r].c[3] * (1.0f / 128.0f) + d3b * (1.0f / 16384.0f) + acc[r].s[1];
-                float* dst = red + ((size_t)r * a.members + (t >> 1)) * 16;
+                float* dst = red + ((size_t)r * MEMBERS + (t >> 1)) * 16;
                 dst[g] = va;
                 dst[g + 8] = vb;
             }
         }
         __syncwarp();
-        bar_arrive(kBarFull + buf);
+        if (RIBN_PROBE < 3) bar_arrive(kBarFull + set * 4 + buf, bar_threads);
     }
 }
 
@@ -670,6 +789,24 @@ int sm_count() {
 }
 
 }  // namespace
+
+// Leaves a few KB of the SM's shared memory to small kernels that overlap this one's tail or head.
+constexpr size_t kSmemBudget = 208 * 1024;
+
+cudaError_t gemv_prepare() {
+    static bool configured = false;
+    if (!configured) {
+        const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
+        cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<1, false>, at, (int)kSmemBudget);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_mma_kernel<1, true>, at, (int)kSmemBudget);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_mma_kernel<2, false>, at, (int)kSmemBudget);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_mma_kernel<2, true>, at, (int)kSmemBudget);
+        if (e != cudaSuccess) return e;
+        sm_count();
+        configured = true;
+    }
+    return cudaSuccess;
+}
 
 cudaError_t launch_to_operand(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,
                               int members, int k, ActOperand out) {
@@ -706,15 +843,37 @@ cudaError_t launch_gemv_mma(cudaStream_t stream, const GemvArgs& args, bool prog
                          (size_t)args.members * (K / 16) * 4 +
                          (size_t)kConsumerWarps * args.members * 16 * kHdrStride * 4 +
                          (size_t)2 * kConsumerWarps * kMaxRuns * args.members * 16 * 4 + 16 + 8;
-    const size_t budget = 226 * 1024;
-    if (fixed + (size_t)2 * (slot_bytes + 16) > budget) return cudaErrorInvalidValue;
-    int slots = (int)std::min<size_t>(6, (budget - fixed) / ((size_t)slot_bytes + 16));
-    const size_t smem = fixed + (size_t)slots * (slot_bytes + 16);
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+    const size_t budget = kSmemBudget;
+    if (fixed + (size_t)kTeams * (slot_bytes + 16) > budget) {
+        if (args.members == 1) return cudaErrorInvalidValue;
+        // Too many activation columns for this K: one launch per input vector.
+        for (int m = 0; m < args.members; ++m) {
+            GemvArgs one = args;
+            one.members = 1;
+            for (int i = 0; i < args.n_segments; ++i) one.seg[i].y = args.seg[i].y + (size_t)m * args.seg[i].n;
+            one.in.dig = args.in.dig + (size_t)m * 3 * K;
+            one.in.sx = args.in.sx + (size_t)m * (K / 32);
+            one.in.sxs16 = args.in.sxs16 + (size_t)m * (K / 16);
+            if (args.in.ss32) one.in.ss32 = args.in.ss32 + (size_t)m * (K / 32);
+            const int n_out = args.seg[0].n;
+            if (args.out.dig) one.out.dig = args.out.dig + (size_t)m * 3 * n_out;
+            if (args.out.sx) one.out.sx = args.out.sx + (size_t)m * (n_out / 32);
+            if (args.out.sxs16) one.out.sxs16 = args.out.sxs16 + (size_t)m * (n_out / 16);
+            if (args.out.ss32) one.out.ss32 = args.out.ss32 + (size_t)m * (n_out / 32);
+            if (args.swiglu_f32) one.swiglu_f32 = args.swiglu_f32 + (size_t)m * n_out;
+            cudaError_t e = launch_gemv_mma(stream, one, programmatic);
+            if (e != cudaSuccess) return e;
+        }
+        return cudaSuccess;
+    }
+    // Every team has its own ring slots, so a warp observes each phase of the barriers it waits on
+    // (the one-bit parity wait requires that).
+    const int slots_per_team = (int)std::min<size_t>(3, (budget - fixed) / ((size_t)kTeams * (slot_bytes + 16)));
+    if (slots_per_team < 1) return cudaErrorInvalidValue;
+    const size_t smem = fixed + (size_t)slots_per_team * kTeams * (slot_bytes + 16);
+    {
+        cudaError_t e = gemv_prepare();
         if (e != cudaSuccess) return e;
-        configured = budget;
     }
     const int grid = std::min(units, sm_count());
     cudaLaunchConfig_t cfg = {};
@@ -727,7 +886,14 @@ cudaError_t launch_gemv_mma(cudaStream_t stream, const GemvArgs& args, bool prog
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = programmatic ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_mma_kernel, args, slots, slot_bytes);
+    // Few units per CTA: let all the warps cooperate on each unit.
+    const bool shared = units < 2 * kTeams * grid;
+    if (args.members == 1) {
+        return shared ? cudaLaunchKernelEx(&cfg, gemv_mma_kernel<1, true>, args, slots_per_team, slot_bytes)
+                      : cudaLaunchKernelEx(&cfg, gemv_mma_kernel<1, false>, args, slots_per_team, slot_bytes);
+    }
+    return shared ? cudaLaunchKernelEx(&cfg, gemv_mma_kernel<2, true>, args, slots_per_team, slot_bytes)
+                  : cudaLaunchKernelEx(&cfg, gemv_mma_kernel<2, false>, args, slots_per_team, slot_bytes);
 }
 
 }  // namespace ribn

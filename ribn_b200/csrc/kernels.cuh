@@ -129,6 +129,7 @@ struct DecodeAttention {
     size_t partial_bytes;
     float* out;
     ActOperand operand;
+    bool programmatic;  // launch as programmatic dependents of the previous kernel in the stream
 };
 cudaError_t launch_attention_decode(cudaStream_t stream, const DecodeAttention& d, int* launches);
 
