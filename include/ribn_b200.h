@@ -264,6 +264,23 @@ RIBN_B200_API int ribn_b200_op_batch_metadata(int32_t device, const int32_t* row
                                               int32_t* cu_seqlens, int32_t* token_row,
                                               int32_t* token_position, int32_t* token_kv_slot);
 
+/* Paged split-KV attention for callers that cannot allocate device memory (code running while a
+ * stream is being captured, or under a start-up-only allocation policy).  It has no counterpart
+ * in the reference.  Same arithmetic as ribn_b200_op_attention, but every pointer is a DEVICE
+ * pointer supplied by the caller, the work is enqueued on `stream` (a cudaStream_t), and the
+ * per-span scratch is an 8 MiB array built into the library, so the call performs no cudaMalloc,
+ * cudaFree or allocating library routine.  `token_pos[r]` is the position of query row r (it
+ * attends keys [0, token_pos[r]], or the last `window` of them); `max_tokens` is 1 + the largest
+ * position.  Refused with a message when rows * q_heads * ceil(keys / 64) * (head_dim + 2)
+ * exceeds 2 Mi floats.  Calls share the scratch: do not let two of them overlap on the GPU.
+ * The first call on a device resolves the scratch address; make it before any stream capture. */
+RIBN_B200_API int ribn_b200_attention_noalloc(int32_t device, void* stream, const float* q,
+                                              const uint16_t* keys, const uint16_t* values,
+                                              const int32_t* page_table, const int32_t* token_pos,
+                                              int32_t rows, int32_t max_tokens, int32_t q_heads,
+                                              int32_t kv_heads, int32_t head_dim, int32_t window,
+                                              float* out, char* error, size_t error_capacity);
+
 /* Host-side tile-major repack used by finalize (no device work): writes the
  * packed form of raw GGUF rows and returns its size; `out` may be NULL to
  * query the size.  No reference counterpart: the reference uploads GGUF bytes

@@ -76,6 +76,8 @@ SIGNATURES = {
                                          C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, C.c_int32]),
     "ribn_b200_op_batch_metadata": (C.c_int, [C.c_int32, _P, _P, _P, C.c_int32, _P, C.c_int32, C.c_int32, _P, _P,
                                               _P, _P]),
+    "ribn_b200_attention_noalloc": (C.c_int, [C.c_int32, _P, _P, _P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32,
+                                              C.c_int32, C.c_int32, C.c_int32, _P, C.c_char_p, C.c_size_t]),
     "ribn_b200_debug_repack": (C.c_int, [C.c_int32, _P, C.c_int64, C.c_int64, _P, C.c_size_t,
                                          C.POINTER(C.c_size_t)]),
     "ribn_b200_build_info": (C.c_char_p, []),

@@ -114,7 +114,7 @@ __global__ void attention_span_kernel(const AttnArgs a) {
     if (span >= spans) return;
     const int begin = first + span * kAttnSpanKeys;
     const int end = min(pos + 1, begin + kAttnSpanKeys);
-    const int32_t* table = a.page_tables + (long long)a.token_seq[t] * a.pages_per_sequence;
+    const int32_t* table = a.page_tables + (long long)(a.token_seq != nullptr ? a.token_seq[t] : 0) * a.pages_per_sequence;
     const float scale = 1.0f / sqrtf((float)HD);
     const long long row_stride = (long long)a.kv_heads * HD;
     const bool owns_self = FUSED && span == spans - 1;  // this CTA's span holds the token's own position

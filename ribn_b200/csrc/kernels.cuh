@@ -96,7 +96,8 @@ cudaError_t launch_attention_ref(cudaStream_t stream, const float* q, const __ha
 // (it sizes the grid only; results do not depend on it).  `partial` is scratch
 // of `partial_bytes` for the per-span accumulators; tokens are processed in
 // as many launches as that scratch requires.  `launches` (optional) is
-// incremented per kernel launch.
+// incremented per kernel launch.  `token_seq` may be null: every token then
+// belongs to sequence 0 (one page-table row).
 constexpr int kAttnSpanKeys = 64;
 constexpr int kAttnMaxSpans = 1024;  // 65536 keys per token
 cudaError_t launch_attention(cudaStream_t stream, const float* q, const __half* cache_k, const __half* cache_v,
