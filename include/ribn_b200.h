@@ -215,12 +215,18 @@ RIBN_B200_API int ribn_b200_step_bytes(ribn_b200_executor* executor, uint64_t co
  * what the per-primitive parity tests call.  They replace the operator
  * wrappers of crates/nvidia/src/quantized.rs and crates/nvidia/src/model_ops.rs. */
 
+/* Diagnostic of the calling thread's last failed ribn_b200_op_* call (the CUDA error and the step that
+ * raised it).  Returns the message length; copies at most capacity - 1 bytes plus a terminator.
+ * The operator wrappers of the reference return the same information as their Err value. */
+RIBN_B200_API size_t ribn_b200_op_last_error(char* buffer, size_t capacity);
+
 /* dequantize_block over `rows x cols` (crates/gguf/src/lib.rs:508-535), bit-exact. */
 RIBN_B200_API int ribn_b200_op_dequantize(int32_t device, int32_t ggml_type, const void* bytes,
                                           int64_t rows, int64_t cols, float* out);
 /* y[m][n] = sum_k deq(W[n][k]) x[m][k] (CudaQuantizedGemv::execute_warp /
  * gemv_batch, crates/nvidia/src/quantized.rs:303-436).  variant 0 = fast
- * kernels, 1 = one-warp-per-row reference kernels. */
+ * GEMV kernels (members in pairs), 1 = one-warp-per-row reference kernels,
+ * 2 = the batched tensor-core kernel (up to 64 members per launch). */
 RIBN_B200_API int ribn_b200_op_gemv(int32_t device, int32_t ggml_type, const void* weights,
                                     int64_t rows, int64_t cols, const float* x, int32_t members,
                                     float* y, int32_t variant);

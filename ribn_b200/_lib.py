@@ -60,6 +60,7 @@ SIGNATURES = {
     "ribn_b200_release": (C.c_int, [_P, C.c_uint64]),
     "ribn_b200_synchronize": (C.c_int, [_P]),
     "ribn_b200_last_error": (C.c_size_t, [_P, C.c_char_p, C.c_size_t]),
+    "ribn_b200_op_last_error": (C.c_size_t, [C.c_char_p, C.c_size_t]),
     "ribn_b200_copy_logits": (C.c_int, [_P, C.c_uint32, _P, C.c_size_t]),
     "ribn_b200_copy_kv": (C.c_int, [_P, C.c_uint64, C.c_int32, C.c_int32, C.c_uint32, _P]),
     "ribn_b200_debug_set_context": (C.c_int, [_P, C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint64]),

@@ -307,13 +307,120 @@ cudaError_t run_layers_decode(ribn_b200_executor* ex, const StepPlan& plan, int&
     return cudaSuccess;
 }
 
-bool decode_family_applies(const ribn_b200_executor* ex, const StepPlan& plan) {
+// ---- batch family: integer tensor-core GEMM over batch-operand activations (3+ tokens) --------
+// Tokens go through each projection in groups of up to kGemmMaxMembers; weights are read once per group.
+cudaError_t batch_project(ribn_b200_executor* ex, int& launches, const float* x, const int32_t* index,
+                          const float* norm_weight, int tokens, int k, const Tensor* const* mats, float* const* ys,
+                          int n_mats, int epilogue) {
+    cudaStream_t s = ex->stream;
+    for (int base = 0; base < tokens; base += kGemmMaxMembers) {
+        const int m = std::min(kGemmMaxMembers, tokens - base);
+        cudaError_t e = launch_to_batch_operand(s, index ? x : x + (size_t)base * k, index ? index + base : nullptr,
+                                                norm_weight, m, k, ex->cfg.rms_eps, ex->op_batch);
+        if (e != cudaSuccess) return e;
+        launches += 2;
+        GemmArgs a{};
+        a.n_segments = n_mats;
+        for (int i = 0; i < n_mats; ++i) {
+            a.seg[i] = GemvSegment{mats[i]->packed.data, mats[i]->type, (int)mats[i]->rows, mats[i]->packed.row_tiles,
+                                   ys[i] + (size_t)base * mats[i]->rows};
+        }
+        a.k = k;
+        a.members = m;
+        a.dig = ex->op_batch.dig;
+        a.sum16 = ex->op_batch.sum16;
+        a.member_scale = ex->op_batch.member_scale;
+        a.epilogue = epilogue;
+        a.error_flag = ex->d_error;
+        STEP_TRY(launch_gemm_imma(s, a));
+    }
+    return cudaSuccess;
+}
+
+cudaError_t run_layers_batch(ribn_b200_executor* ex, const StepPlan& plan, int& launches) {
+    const ribn_b200_config& c = ex->cfg;
+    cudaStream_t s = ex->stream;
+    const int T = plan.n_tokens;
+    const int QD = c.q_heads * c.head_dim;
+    for (int l = 0; l < c.layers; ++l) {
+        Tensor* t = &ex->lt(l, 0);
+        {
+            const Tensor* mats[3] = {&t[kAttnQ], &t[kAttnK], &t[kAttnV]};
+            float* ys[3] = {ex->q, ex->k, ex->v};
+            cudaError_t e = batch_project(ex, launches, ex->hidden, nullptr, (const float*)t[kAttnNorm].raw, T, c.hidden,
+                                          mats, ys, 3, kStore);
+            if (e != cudaSuccess) return e;
+        }
+        __half* ck = ex->cache_k + (long long)l * ex->layer_stride;
+        __half* cv = ex->cache_v + (long long)l * ex->layer_stride;
+        if (plan.n_rows == T && c.head_dim >= 64) {
+            DecodeAttention d{};
+            d.q = ex->q; d.k = ex->k; d.v = ex->v;
+            d.q_norm = (const float*)t[kAttnQNorm].raw; d.k_norm = (const float*)t[kAttnKNorm].raw;
+            d.inv_freq = ex->inv_freq; d.eps = c.rms_eps;
+            d.cache_k = ck; d.cache_v = cv;
+            d.page_tables = ex->d_page_tables; d.pages_per_sequence = ex->pages_per_sequence;
+            d.token_seq = ex->meta.token_seq; d.token_pos = ex->meta.token_pos; d.token_slot = ex->meta.token_slot;
+            d.n_tokens = T; d.q_heads = c.q_heads; d.kv_heads = c.kv_heads; d.head_dim = c.head_dim;
+            d.window = 0; d.max_keys = plan.max_keys;
+            d.partial = ex->scratch.attn_partial; d.partial_bytes = ex->scratch.attn_partial_bytes;
+            d.out = ex->attn;
+            d.programmatic = false;
+            cudaError_t e = launch_attention_decode(s, d, &launches);
+            if (e != cudaSuccess) return e;
+        } else {
+            STEP_TRY(launch_qk_norm_rope_append(s, ex->q, ex->k, ex->v, (const float*)t[kAttnQNorm].raw,
+                                                (const float*)t[kAttnKNorm].raw, ex->inv_freq, ex->meta.token_pos,
+                                                ex->meta.token_slot, T, c.q_heads, c.kv_heads, c.head_dim,
+                                                c.rms_eps, ck, cv));
+            cudaError_t e = launch_attention(s, ex->q, ck, cv, ex->d_page_tables, ex->pages_per_sequence,
+                                             ex->meta.token_seq, ex->meta.token_pos, T, c.q_heads, c.kv_heads,
+                                             c.head_dim, 0, plan.max_keys, ex->scratch.attn_partial,
+                                             ex->scratch.attn_partial_bytes, ex->attn, &launches);
+            if (e != cudaSuccess) return e;
+        }
+        {
+            const Tensor* mats[1] = {&t[kAttnOutput]};
+            float* ys[1] = {ex->hidden};
+            cudaError_t e = batch_project(ex, launches, ex->attn, nullptr, nullptr, T, QD, mats, ys, 1, kResidual);
+            if (e != cudaSuccess) return e;
+        }
+        {
+            const Tensor* mats[2] = {&t[kFfnGate], &t[kFfnUp]};
+            float* ys[2] = {ex->gate, ex->up};
+            cudaError_t e = batch_project(ex, launches, ex->hidden, nullptr, (const float*)t[kFfnNorm].raw, T, c.hidden,
+                                          mats, ys, 2, kSwiGLU);
+            if (e != cudaSuccess) return e;
+        }
+        {
+            const Tensor* mats[1] = {&t[kFfnDown]};
+            float* ys[1] = {ex->hidden};
+            cudaError_t e = batch_project(ex, launches, ex->gate, nullptr, nullptr, T, c.ffn, mats, ys, 1, kResidual);
+            if (e != cudaSuccess) return e;
+        }
+    }
+    if (plan.n_sample > 0) {
+        // Only sampling rows reach the head (crates/nvidia/src/decode.rs:686-704).
+        const Tensor* mats[1] = {&ex->output};
+        float* ys[1] = {ex->logits};
+        cudaError_t e = batch_project(ex, launches, ex->hidden, ex->meta.sample_token, (const float*)ex->output_norm.raw,
+                                      plan.n_sample, c.hidden, mats, ys, 1, kStore);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+bool packed_family_applies(const ribn_b200_executor* ex) {
     if (ex->cfg.flags & RIBN_B200_FLAG_REFERENCE_KERNELS) return false;
-    if (plan.n_tokens > kGemvMaxMembers || !ex->output.packed.ready()) return false;
+    if (!ex->output.packed.ready()) return false;
     for (const Tensor& t : ex->layer_tensors) {
         if (t.type != kF32 && !t.packed.ready()) return false;
     }
     return true;
+}
+
+bool decode_family_applies(const ribn_b200_executor* ex, const StepPlan& plan) {
+    return plan.n_tokens <= kGemvMaxMembers && packed_family_applies(ex);
 }
 
 cudaError_t run_step(ribn_b200_executor* ex, const StepPlan& plan, int& launches) {
@@ -326,6 +433,7 @@ cudaError_t run_step(ribn_b200_executor* ex, const StepPlan& plan, int& launches
     STEP_TRY(launch_embedding(s, ex->token_embd.type, ex->token_embd.raw, c.hidden, c.vocab, ex->meta.token_id, T,
                               ex->hidden));
     cudaError_t e = decode_family_applies(ex, plan) ? run_layers_decode(ex, plan, launches)
+                    : packed_family_applies(ex)     ? run_layers_batch(ex, plan, launches)
                                                     : run_layers_reference(ex, plan, launches);
     if (e != cudaSuccess) return e;
     if (plan.n_sample > 0) {
@@ -624,6 +732,15 @@ int ribn_b200_finalize(ribn_b200_executor* ex) {
         CU_TRY(ex, alloc_operand(&ex->op_attn, c.q_heads * c.head_dim));
         CU_TRY(ex, alloc_operand(&ex->op_act, c.ffn));
         CU_TRY(ex, alloc_operand(&ex->op_head, c.hidden));
+        {
+            const int kmax = std::max(std::max(c.hidden, c.ffn), c.q_heads * c.head_dim);
+            if (kmax % 256 == 0) {
+                CU_TRY(ex, dev_alloc(ex, &ex->op_batch.dig, batch_operand_digit_bytes(kGemmMaxMembers, kmax)));
+                CU_TRY(ex, dev_alloc(ex, &ex->op_batch.sum16, batch_operand_sum_floats(kGemmMaxMembers, kmax)));
+                CU_TRY(ex, dev_alloc(ex, &ex->op_batch.member_scale, kGemmMaxMembers));
+                CU_TRY(ex, dev_alloc(ex, &ex->op_batch.digit_inv, kGemmMaxMembers));
+            }
+        }
         CU_TRY(ex, dev_alloc(ex, &ex->d_error, 1));
         CU_TRY(ex, cudaMemsetAsync(ex->d_error, 0, sizeof(int), ex->stream));
         CU_TRY(ex, cudaMallocHost((void**)&ex->h_error, sizeof(int)));

@@ -10,6 +10,7 @@
 
 #include <algorithm>
 #include <thread>
+#include <string>
 #include <vector>
 
 #include "../../include/ribn_b200.h"
@@ -62,8 +63,16 @@ struct Scope {
     }
 };
 
-#define OP_TRY(expr) do { if ((expr) != cudaSuccess) return RIBN_B200_ERROR; } while (0)
-#define OP_PTR(p) do { if ((p) == nullptr) return RIBN_B200_ERROR; } while (0)
+// Why the calling thread's last operator call failed.
+thread_local std::string g_op_error;
+
+int op_fail(const char* what, cudaError_t e) {
+    g_op_error = std::string(what) + ": " + (e == cudaSuccess ? "failed" : cudaGetErrorString(e));
+    return RIBN_B200_ERROR;
+}
+
+#define OP_TRY(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) return op_fail(#expr, e_); } while (0)
+#define OP_PTR(p) do { if ((p) == nullptr) return op_fail("device allocation or upload of " #p, cudaGetLastError()); } while (0)
 
 size_t encoded_bytes(int type, long long rows, long long cols) {
     const int e = block_elems(type);
@@ -75,22 +84,31 @@ size_t encoded_bytes(int type, long long rows, long long cols) {
 
 extern "C" {
 
+size_t ribn_b200_op_last_error(char* buffer, size_t capacity) {
+    if (buffer != nullptr && capacity > 0) {
+        const size_t n = std::min(capacity - 1, g_op_error.size());
+        memcpy(buffer, g_op_error.data(), n);
+        buffer[n] = 0;
+    }
+    return g_op_error.size();
+}
+
 int ribn_b200_debug_repack(int32_t type, const void* raw, int64_t rows, int64_t cols, void* out, size_t capacity,
                            size_t* byte_count) {
-    if (!packable(type, rows, cols) || raw == nullptr) return RIBN_B200_ERROR;
+    if (!packable(type, rows, cols) || raw == nullptr) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
     const size_t need = packed_bytes(type, rows, cols);
     if (byte_count) *byte_count = need;
     if (out == nullptr) return RIBN_B200_OK;
-    if (capacity < need) return RIBN_B200_ERROR;
+    if (capacity < need) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
     repack_host(type, (const unsigned char*)raw, rows, cols, (unsigned char*)out, 1);
     return RIBN_B200_OK;
 }
 
 int ribn_b200_op_dequantize(int32_t device, int32_t type, const void* bytes, int64_t rows, int64_t cols, float* out) {
     const size_t n = encoded_bytes(type, rows, cols);
-    if (n == 0 || bytes == nullptr || out == nullptr) return RIBN_B200_ERROR;
+    if (n == 0 || bytes == nullptr || out == nullptr) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
     Scope s(device);
-    if (!s.ok) return RIBN_B200_ERROR;
+    if (!s.ok) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
     unsigned char* d_in = s.upload((const unsigned char*)bytes, n);
     float* d_out = s.alloc<float>((size_t)rows * cols);
     OP_PTR(d_in); OP_PTR(d_out);
@@ -101,9 +119,9 @@ int ribn_b200_op_dequantize(int32_t device, int32_t type, const void* bytes, int
 int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t rows, int64_t cols, const float* x,
                       int32_t members, float* y, int32_t variant) {
     const size_t n = encoded_bytes(type, rows, cols);
-    if (n == 0 || weights == nullptr || x == nullptr || y == nullptr || members <= 0) return RIBN_B200_ERROR;
+    if (n == 0 || weights == nullptr || x == nullptr || y == nullptr || members <= 0) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
     Scope s(device);
-    if (!s.ok) return RIBN_B200_ERROR;
+    if (!s.ok) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
     float* d_x = s.upload(x, (size_t)members * cols);
     float* d_y = s.alloc<float>((size_t)members * rows);
     OP_PTR(d_x); OP_PTR(d_y);
@@ -112,7 +130,7 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
         OP_PTR(d_w);
         OP_TRY(launch_gemv_ref(s.stream, type, d_w, rows, cols, d_x, members, d_y, false));
     } else {
-        if (!packable(type, rows, cols)) return RIBN_B200_ERROR;
+        if (!packable(type, rows, cols)) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
         std::vector<unsigned char> packed(packed_bytes(type, rows, cols));
         repack_host(type, (const unsigned char*)weights, rows, cols, packed.data(),
                     (int)std::max(1u, std::min(16u, std::thread::hardware_concurrency())));
@@ -126,6 +144,30 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
         int* d_err = s.alloc<int>(1);
         OP_PTR(op.dig); OP_PTR(op.sx); OP_PTR(op.sxs16); OP_PTR(d_err);
         OP_TRY(cudaMemsetAsync(d_err, 0, sizeof(int), s.stream));
+        if (variant == 2) {
+            // the batched kernel, in groups of up to kGemmMaxMembers members
+            BatchOperand bop;
+            const int group = std::min(members, kGemmMaxMembers);
+            bop.dig = s.alloc<signed char>(batch_operand_digit_bytes(group, (int)cols));
+            bop.sum16 = s.alloc<float>(batch_operand_sum_floats(group, (int)cols));
+            bop.member_scale = s.alloc<float>((size_t)group);
+            bop.digit_inv = s.alloc<float>((size_t)group);
+            OP_PTR(bop.dig); OP_PTR(bop.sum16); OP_PTR(bop.member_scale); OP_PTR(bop.digit_inv);
+            for (int m0 = 0; m0 < members; m0 += kGemmMaxMembers) {
+                const int m = std::min(kGemmMaxMembers, members - m0);
+                OP_TRY(launch_to_batch_operand(s.stream, d_x + (size_t)m0 * cols, nullptr, nullptr, m, (int)cols, 0.0f, bop));
+                GemmArgs a{};
+                a.n_segments = 1;
+                a.seg[0] = GemvSegment{d_w, type, (int)rows, (int)((rows + kTileRows - 1) / kTileRows),
+                                       d_y + (size_t)m0 * rows};
+                a.k = (int)cols;
+                a.members = m;
+                a.dig = bop.dig; a.sum16 = bop.sum16; a.member_scale = bop.member_scale;
+                a.epilogue = kStore;
+                a.error_flag = d_err;
+                OP_TRY(launch_gemm_imma(s.stream, a));
+            }
+        } else {
         OP_TRY(launch_to_operand(s.stream, d_x, nullptr, nullptr, members, (int)cols, op));
         for (int m0 = 0; m0 < members; m0 += kGemvMaxMembers) {
             GemvArgs a{};
@@ -143,8 +185,10 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
             a.error_flag = d_err;
             OP_TRY(launch_gemv_mma(s.stream, a, false));
         }
+        }
         int err = 0;
-        if (!s.download(&err, d_err, 1) || err != 0) return RIBN_B200_ERROR;
+        if (!s.download(&err, d_err, 1)) return op_fail("gemv", cudaGetLastError());
+        if (err != 0) return op_fail("gemv: a bounded wait inside the kernel expired", cudaSuccess);
     }
     return s.download(y, d_y, (size_t)members * rows) ? RIBN_B200_OK : RIBN_B200_ERROR;
 }
@@ -152,7 +196,7 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
 int ribn_b200_op_rms_norm(int32_t device, const float* x, const float* weight, int32_t members, int32_t length,
                           float eps, float* out) {
     Scope s(device);
-    if (!s.ok || members <= 0 || length <= 0) return RIBN_B200_ERROR;
+    if (!s.ok || members <= 0 || length <= 0) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
     float* d_x = s.upload(x, (size_t)members * length);
     float* d_w = s.upload(weight, (size_t)length);
     float* d_o = s.alloc<float>((size_t)members * length);
@@ -163,7 +207,7 @@ int ribn_b200_op_rms_norm(int32_t device, const float* x, const float* weight, i
 
 int ribn_b200_op_silu_mul(int32_t device, const float* gate, const float* up, int64_t length, float* out) {
     Scope s(device);
-    if (!s.ok || length <= 0) return RIBN_B200_ERROR;
+    if (!s.ok || length <= 0) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
     float* d_g = s.upload(gate, (size_t)length);
     float* d_u = s.upload(up, (size_t)length);
     float* d_o = s.alloc<float>((size_t)length);
@@ -174,7 +218,7 @@ int ribn_b200_op_silu_mul(int32_t device, const float* gate, const float* up, in
 
 int ribn_b200_op_argmax(int32_t device, const float* logits, int32_t members, int64_t length, uint32_t* out) {
     Scope s(device);
-    if (!s.ok || members <= 0 || length <= 0) return RIBN_B200_ERROR;
+    if (!s.ok || members <= 0 || length <= 0) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
     float* d_l = s.upload(logits, (size_t)members * length);
     uint32_t* d_o = s.alloc<uint32_t>((size_t)members);
     OP_PTR(d_l); OP_PTR(d_o);
@@ -185,7 +229,7 @@ int ribn_b200_op_argmax(int32_t device, const float* logits, int32_t members, in
 int ribn_b200_op_rope_neox(int32_t device, float* values, const int64_t* positions, int32_t members, int32_t heads,
                            int32_t head_dim, int32_t rot_dims, float base) {
     Scope s(device);
-    if (!s.ok || members <= 0 || rot_dims <= 0 || rot_dims > head_dim || (rot_dims & 1)) return RIBN_B200_ERROR;
+    if (!s.ok || members <= 0 || rot_dims <= 0 || rot_dims > head_dim || (rot_dims & 1)) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
     const size_t n = (size_t)members * heads * head_dim;
     std::vector<float> table((size_t)rot_dims / 2);
     for (int p = 0; p < rot_dims / 2; ++p) table[p] = powf(base, -(2.0f * (float)p) / (float)rot_dims);
@@ -200,7 +244,7 @@ int ribn_b200_op_rope_neox(int32_t device, float* values, const int64_t* positio
 
 int ribn_b200_op_f32_to_f16(int32_t device, const float* in, int64_t length, uint16_t* out) {
     Scope s(device);
-    if (!s.ok || length <= 0) return RIBN_B200_ERROR;
+    if (!s.ok || length <= 0) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
     float* d_i = s.upload(in, (size_t)length);
     uint16_t* d_o = s.alloc<uint16_t>((size_t)length);
     OP_PTR(d_i); OP_PTR(d_o);
@@ -214,7 +258,7 @@ int ribn_b200_op_attention(int32_t device, const float* q, const uint16_t* keys,
                            float* out, int32_t variant) {
     Scope s(device);
     if (!s.ok || rows <= 0 || tokens < rows || page_tokens != kPageTokens || q_heads % kv_heads != 0) {
-        return RIBN_B200_ERROR;
+        return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
     }
     const int pages = (tokens + page_tokens - 1) / page_tokens;
     const size_t kv_elems = (size_t)physical_tokens * kv_heads * head_dim;
@@ -247,10 +291,10 @@ int ribn_b200_op_batch_metadata(int32_t device, const int32_t* row_slot, const i
                                 int32_t pages_per_sequence, int32_t page_tokens, int32_t* cu_seqlens,
                                 int32_t* token_row, int32_t* token_position, int32_t* token_kv_slot) {
     Scope s(device);
-    if (!s.ok || rows <= 0 || page_tokens <= 0) return RIBN_B200_ERROR;
+    if (!s.ok || rows <= 0 || page_tokens <= 0) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
     int total = 0, max_slot = 0;
     for (int r = 0; r < rows; ++r) {
-        if (row_tokens[r] < 0 || row_slot[r] < 0) return RIBN_B200_ERROR;
+        if (row_tokens[r] < 0 || row_slot[r] < 0) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
         total += row_tokens[r];
         max_slot = std::max(max_slot, row_slot[r]);
     }

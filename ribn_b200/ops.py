@@ -17,7 +17,10 @@ def _p(a: np.ndarray):
 
 def _check(rc: int, what: str):
     if rc != OK:
-        raise RuntimeError(f"ribn_b200 {what} failed (is a B200 visible? there is no CPU path)")
+        buf = C.create_string_buffer(1024)
+        lib().ribn_b200_op_last_error(buf, len(buf))
+        why = buf.value.decode(errors="replace") or "is a B200 visible? there is no CPU path"
+        raise RuntimeError(f"ribn_b200 {what} failed: {why}")
 
 
 def dequantize(ggml_type: int, encoded, rows: int, cols: int, device: int = 0) -> np.ndarray:

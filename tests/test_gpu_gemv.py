@@ -2,7 +2,8 @@
 fixtures and tolerances (crates/nvidia/tests/cuda_reference.rs:690-846, 4842-4880,
 5172-5278), seeded N(0, 0.02) checkpoints of BASELINE shapes, ragged row counts,
 and batch-vs-single bit equality.  variant 0 = tensor-core kernels over the
-tile-major repack, variant 1 = the plain one-warp-per-row kernels."""
+tile-major repack, variant 1 = the plain one-warp-per-row kernels, variant 2 = the
+batched tensor-core kernel (3..64 members per launch, one activation scale per member)."""
 import numpy as np
 import pytest
 
@@ -114,3 +115,36 @@ def test_full_size_projection_fast_equals_reference_kernel_and_is_linear(ops):
         for r in spot:
             row_bytes = blocks.reshape(rows, -1)[r]
             assert abs(orc.gemv(kind, row_bytes, cols, 1, x1)[0] - fast[0][r]) / scale < 2e-5
+
+
+@pytest.mark.parametrize("kind", [H.Q8_0, H.Q4_K, H.Q6_K])
+@pytest.mark.parametrize("rows,cols,members", [(1, 256, 1), (5, 512, 3), (70, 1024, 9), (256, 4096, 64), (96, 12288, 17),
+                                               (40, 768, 131)])
+def test_batched_kernel_against_oracle(ops, kind, rows, cols, members):
+    rng = np.random.default_rng(rows * 11 + cols + kind + members)
+    enc = H.quantize(kind, rng.normal(0, 0.02, size=(rows, cols)).astype(np.float32))
+    xs = (rng.normal(0, 1, size=(members, cols)) * rng.uniform(0.1, 10, size=(members, 1))).astype(np.float32)
+    got = ops.gemv(kind, enc, rows, cols, xs, variant=2)
+    want = np.stack([orc.gemv(kind, enc, cols, rows, xs[m]) for m in range(members)])
+    for m in range(members):
+        scale = float(np.max(np.abs(want[m]))) + 1e-6
+        assert np.max(np.abs(got[m] - want[m])) / scale < 2e-5, m
+
+
+@pytest.mark.parametrize("kind", [H.Q8_0, H.Q4_K, H.Q6_K])
+def test_batched_kernel_random_bytes_and_member_independence(ops, kind):
+    rng = np.random.default_rng(kind + 77)
+    elems, size = H.BLOCK[kind]
+    rows, cols = 80, 1024
+    blocks = rng.integers(0, 256, size=(rows * cols // elems, size), dtype=np.uint8)
+    for off in ([0] if kind == H.Q8_0 else [0, 2] if kind == H.Q4_K else [208]):
+        blocks[:, off + 1] = (blocks[:, off + 1] & 0x83) | 0x10
+    xs = rng.normal(0, 1, size=(20, cols)).astype(np.float32)
+    got = ops.gemv(kind, blocks, rows, cols, xs, variant=2)
+    want = np.stack([orc.gemv(kind, blocks, cols, rows, xs[m]) for m in range(20)])
+    assert np.max(np.abs(got - want)) / np.max(np.abs(want)) < 2e-5
+    # a member's result does not depend on what it is batched with, nor on its place in the batch
+    alone = ops.gemv(kind, blocks, rows, cols, xs[[5, 0, 13]], variant=2)
+    assert np.array_equal(alone.view(np.uint32), got[[5, 0, 13]].view(np.uint32))
+    zero = ops.gemv(kind, blocks, rows, cols, np.zeros((3, cols), np.float32), variant=2)
+    assert np.all(zero == 0.0)

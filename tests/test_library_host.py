@@ -175,5 +175,5 @@ def test_compute_entry_points_fail_loudly_without_a_gpu(built_library):
     import ribn_b200
     with pytest.raises(ribn_b200.ExecutionError, match="no CUDA device"):
         ribn_b200.QwenB200(H.TINY)
-    with pytest.raises(RuntimeError, match="no CPU path"):
+    with pytest.raises(RuntimeError, match="no usable CUDA device"):
         ribn_b200.ops.rms_norm(np.ones(4, np.float32), np.ones(4, np.float32), 1e-6)
