@@ -3,12 +3,16 @@
 //
 // A CTA owns 4 row tiles (64 output rows) and walks the k tiles.  Per k tile the weights of its
 // row tiles and the activations' digit chunk for that k tile arrive by bulk (TMA) copies into a
-// two-deep shared-memory ring.  The eight warps split the *members* (8 each, four MMA column
-// tiles), so every warp reuses its B fragments across the CTA's row tiles and the activation
-// chunk is read from shared memory once per warp.  Block scales are folded per 32 (Q4_K, Q8_0)
-// or 16 (Q6_K) inputs exactly as in the GEMV; here each member has ONE activation scale for its
-// whole vector (applied in the epilogue), so the fold factor does not depend on the column.
-// The formats' offsets are removed with per-16-input digit sums supplied with the activations.
+// two-deep shared-memory ring.  The MMA columns are the flat list of (member, digit) pairs
+// (column 3 m + d), so 64 members fill 24 column tiles with no padding; the twelve warps take two
+// column tiles each and reuse their B fragments across the CTA's row tiles.  Block scales are
+// folded per 32 (Q4_K, Q8_0) or 16 (Q6_K) inputs exactly as in the GEMV; here each member has ONE
+// activation scale for its whole vector (applied in the epilogue), so the fold factor does not
+// depend on the column.  The formats' offsets (Q4_K minimum, Q6_K -32, Q8_0 -128) are removed with
+// per-16-input digit sums supplied with the activations: a second role of the same threads
+// accumulates sum_sub coef[row][sub] * sum16[sub][member] over the whole K loop.  At the end the
+// accumulators and the offset totals meet in shared memory, the three digits of each member are
+// combined, and outputs are written with consecutive threads on consecutive output rows.
 // Per-member work is independent of the other members and all sums are ordered: deterministic.
 #include <cuda_fp16.h>
 
@@ -21,13 +25,18 @@ namespace ribn {
 
 namespace {
 
-constexpr int kWarps = 8;
+constexpr int kWarps = 12;
 constexpr int kThreads = kWarps * 32;
 constexpr int kRowTiles = 4;            // row tiles per CTA
-constexpr int kMembersPerWarp = 8;      // 4 MMA column tiles of 2 members x (3 digits + pad)
-constexpr int kMaxMembers = kWarps * kMembersPerWarp;
-constexpr int kHdrStride = 36;          // floats per header row: 16 scales, 16 offset coefficients, pad
+constexpr int kCtaRows = kRowTiles * 16;
+constexpr int kColTiles = 2;            // MMA column tiles (8 columns each) per warp
+constexpr int kMaxMembers = kGemmMaxMembers;
+constexpr int kMemberPad = 8;           // members are padded to a multiple of this: 3 * 8 columns = 3 column tiles
+constexpr int kQuadFloats = 8 * 8 * 4;  // fold scales of one row tile: [pair of scales 8][g 8][4]
 constexpr int kPlane = kBatchPlaneBytes; // bytes per (member, digit) plane of one k tile: 256 digits + bank padding
+constexpr int kCoefStride = 20;         // floats per row of offset coefficients (16 + bank spread)
+constexpr int kExchStride = 3 * kMaxMembers + 1;  // floats per row of the accumulator exchange
+constexpr int kOffStride = kMaxMembers + 1;       // floats per row of the offset exchange
 constexpr uint32_t kNibbles = 0x0F0F0F0Fu;
 constexpr uint32_t kTopBits = 0x30303030u;
 constexpr int kMagicInt = 0x4B400000;
@@ -87,47 +96,52 @@ __device__ __forceinline__ void fold(float (&a)[4], const int (&c)[4], float s0,
     a[3] = fmaf(s1, __int_as_float(c[3]) - kMagic, a[3]);
 }
 
-// Header of one tile -> per row: 16 fold scales (one per 16 inputs; the 32-input formats repeat
-// theirs) and 16 offset coefficients (multiplying the per-16 digit sums).  lane -> (row, half).
-__device__ __forceinline__ void decode_header(int type, const unsigned char* tile, float* hdr, int lane) {
+// Header of one tile, decoded by one warp (lane -> row lane / 2, half lane % 2 of the row's scales):
+//   quads[pair][g][4] = {s(g, 2 pair), s(g, 2 pair + 1), s(g + 8, 2 pair), s(g + 8, 2 pair + 1)}
+//       fold scales as the MMA lanes read them (one 128-bit load per pair): 8 scales per row for the
+//       32-input formats (pairs 0..3), 16 for Q6_K (pairs 0..7);
+//   coef[row][16] offset coefficients multiplying the per-16-input digit sums.
+__device__ __forceinline__ void decode_header(int type, const unsigned char* tile, float* quads, float* coef, int lane) {
     const int row = lane >> 1, half = lane & 1;
-    float* out = hdr + row * kHdrStride + half * 8;
-    float sc[8], co[8];
+    float* q = quads + (row & 7) * 4 + (row >> 3) * 2;
+    float* co = coef + row * kCoefStride + half * 8;
     if (type == kQ4_K) {
         const uint4 h = *reinterpret_cast<const uint4*>(tile + 2048 + row * 16);
         const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
         const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
         const uint32_t s4 = half ? ((h.w & kNibbles) | ((h.y >> 2) & kTopBits)) : (h.y & 0x3F3F3F3Fu);
         const uint32_t m4 = half ? (((h.w >> 4) & kNibbles) | ((h.z >> 2) & kTopBits)) : (h.z & 0x3F3F3F3Fu);
+        float sc[4], mn[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            sc[2 * i] = sc[2 * i + 1] = d * byte_f32(s4, i);
-            co[2 * i] = co[2 * i + 1] = -(dmin * byte_f32(m4, i));
-        }
+        for (int i = 0; i < 4; ++i) { sc[i] = d * byte_f32(s4, i); mn[i] = -(dmin * byte_f32(m4, i)); }
+        *reinterpret_cast<float2*>(q + (half * 2) * 32) = make_float2(sc[0], sc[1]);
+        *reinterpret_cast<float2*>(q + (half * 2 + 1) * 32) = make_float2(sc[2], sc[3]);
+        *reinterpret_cast<float4*>(co) = make_float4(mn[0], mn[0], mn[1], mn[1]);
+        *reinterpret_cast<float4*>(co + 4) = make_float4(mn[2], mn[2], mn[3], mn[3]);
     } else if (type == kQ6_K) {
         const uint2 s8 = *reinterpret_cast<const uint2*>(tile + 3072 + row * 16 + half * 8);
         const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(tile + 3328 + row * 2)));
+        float sc[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             sc[i] = d * (byte_f32(s8.x ^ 0x80808080u, i) - 128.0f);
             sc[4 + i] = d * (byte_f32(s8.y ^ 0x80808080u, i) - 128.0f);
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) co[i] = -32.0f * sc[i];
+        for (int i = 0; i < 4; ++i) *reinterpret_cast<float2*>(q + (half * 4 + i) * 32) = make_float2(sc[2 * i], sc[2 * i + 1]);
+        *reinterpret_cast<float4*>(co) = make_float4(-32.0f * sc[0], -32.0f * sc[1], -32.0f * sc[2], -32.0f * sc[3]);
+        *reinterpret_cast<float4*>(co + 4) = make_float4(-32.0f * sc[4], -32.0f * sc[5], -32.0f * sc[6], -32.0f * sc[7]);
     } else {
         const uint2 d4 = *reinterpret_cast<const uint2*>(tile + 4096 + row * 16 + half * 8);
         const float d0 = __half2float(__ushort_as_half((unsigned short)(d4.x & 0xffffu)));
         const float d1 = __half2float(__ushort_as_half((unsigned short)(d4.x >> 16)));
         const float d2 = __half2float(__ushort_as_half((unsigned short)(d4.y & 0xffffu)));
         const float d3 = __half2float(__ushort_as_half((unsigned short)(d4.y >> 16)));
-        sc[0] = sc[1] = d0; sc[2] = sc[3] = d1; sc[4] = sc[5] = d2; sc[6] = sc[7] = d3;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) co[i] = -128.0f * sc[i];
+        *reinterpret_cast<float2*>(q + (half * 2) * 32) = make_float2(d0, d1);
+        *reinterpret_cast<float2*>(q + (half * 2 + 1) * 32) = make_float2(d2, d3);
+        *reinterpret_cast<float4*>(co) = make_float4(-128.0f * d0, -128.0f * d0, -128.0f * d1, -128.0f * d1);
+        *reinterpret_cast<float4*>(co + 4) = make_float4(-128.0f * d2, -128.0f * d2, -128.0f * d3, -128.0f * d3);
     }
-    *reinterpret_cast<float4*>(out) = make_float4(sc[0], sc[1], sc[2], sc[3]);
-    *reinterpret_cast<float4*>(out + 4) = make_float4(sc[4], sc[5], sc[6], sc[7]);
-    *reinterpret_cast<float4*>(out + 16) = make_float4(co[0], co[1], co[2], co[3]);
-    *reinterpret_cast<float4*>(out + 20) = make_float4(co[4], co[5], co[6], co[7]);
 }
 
 struct StageLayout {
@@ -137,13 +151,123 @@ struct StageLayout {
     int stage_bytes;
 };
 
+// MMA part of one k tile for the CTA's row tiles of one format (tiles of another format or absent
+// tiles have their bit in `mask` clear).  B fragments are loaded once and reused across the row tiles.
+__device__ __forceinline__ void mma_q4k(const unsigned char* wst, int tile_stride, const float* quads, int mask,
+                                        const signed char* const (&xcol)[kColTiles], int lane, int g,
+                                        float (&acc)[kRowTiles][kColTiles][4]) {
+#pragma unroll 1
+    for (int jj = 0; jj < 4; ++jj) {
+        uint2 be[kColTiles], bo[kColTiles];
+#pragma unroll
+        for (int j = 0; j < kColTiles; ++j) {
+            be[j] = *reinterpret_cast<const uint2*>(xcol[j] + (2 * jj) * 32);
+            bo[j] = *reinterpret_cast<const uint2*>(xcol[j] + (2 * jj + 1) * 32);
+        }
+#pragma unroll
+        for (int r = 0; r < kRowTiles; ++r) {
+            if (!(mask >> r & 1)) continue;
+            const uint4 w = *reinterpret_cast<const uint4*>(wst + r * tile_stride + jj * 512 + lane * 16);
+            const float4 sc = *reinterpret_cast<const float4*>(quads + r * kQuadFloats + jj * 32 + g * 4);
+            const uint32_t e0 = w.x & kNibbles, e1 = w.z & kNibbles, e2 = w.y & kNibbles, e3 = w.w & kNibbles;
+            const uint32_t o0 = (w.x >> 4) & kNibbles, o1 = (w.z >> 4) & kNibbles, o2 = (w.y >> 4) & kNibbles,
+                           o3 = (w.w >> 4) & kNibbles;
+#pragma unroll
+            for (int j = 0; j < kColTiles; ++j) {
+                int ce[4], co[4];
+                imma_k32(ce, e0, e1, e2, e3, be[j].x, be[j].y);
+                imma_k32(co, o0, o1, o2, o3, bo[j].x, bo[j].y);
+                fold(acc[r][j], ce, sc.x, sc.z);
+                fold(acc[r][j], co, sc.y, sc.w);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void mma_q8_0(const unsigned char* wst, int tile_stride, const float* quads, int mask,
+                                         const signed char* const (&xcol)[kColTiles], int lane, int g,
+                                         float (&acc)[kRowTiles][kColTiles][4]) {
+#pragma unroll 1
+    for (int jj = 0; jj < 4; ++jj) {
+        uint2 be[kColTiles], bo[kColTiles];
+#pragma unroll
+        for (int j = 0; j < kColTiles; ++j) {
+            be[j] = *reinterpret_cast<const uint2*>(xcol[j] + (2 * jj) * 32);
+            bo[j] = *reinterpret_cast<const uint2*>(xcol[j] + (2 * jj + 1) * 32);
+        }
+#pragma unroll
+        for (int r = 0; r < kRowTiles; ++r) {
+            if (!(mask >> r & 1)) continue;
+            const uint4 we = *reinterpret_cast<const uint4*>(wst + r * tile_stride + (2 * jj) * 512 + lane * 16);
+            const uint4 wo = *reinterpret_cast<const uint4*>(wst + r * tile_stride + (2 * jj + 1) * 512 + lane * 16);
+            const float4 sc = *reinterpret_cast<const float4*>(quads + r * kQuadFloats + jj * 32 + g * 4);
+#pragma unroll
+            for (int j = 0; j < kColTiles; ++j) {
+                int ce[4], co[4];
+                imma_k32(ce, we.x, we.z, we.y, we.w, be[j].x, be[j].y);
+                imma_k32(co, wo.x, wo.z, wo.y, wo.w, bo[j].x, bo[j].y);
+                fold(acc[r][j], ce, sc.x, sc.z);
+                fold(acc[r][j], co, sc.y, sc.w);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void mma_q6k(const unsigned char* wst, int tile_stride, const float* quads, int mask,
+                                        const signed char* const (&xcol)[kColTiles], int lane, int g,
+                                        float (&acc)[kRowTiles][kColTiles][4]) {
+#pragma unroll 1
+    for (int c = 0; c < 2; ++c) {
+        uint2 bb[4][kColTiles];
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+#pragma unroll
+            for (int j = 0; j < kColTiles; ++j) bb[v][j] = *reinterpret_cast<const uint2*>(xcol[j] + (c * 4 + v) * 32);
+#pragma unroll
+        for (int r = 0; r < kRowTiles; ++r) {
+            if (!(mask >> r & 1)) continue;
+            const unsigned char* tile = wst + r * tile_stride + lane * 16;
+            const uint4 qh = *reinterpret_cast<const uint4*>(tile + 2048 + c * 512);
+            const uint4 w0 = *reinterpret_cast<const uint4*>(tile + (c * 2) * 512);       // inputs 0..15 of each group
+            const uint4 w1 = *reinterpret_cast<const uint4*>(tile + (c * 2 + 1) * 512);   // inputs 16..31
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                // scales of 16-input halves 2 (4 c + v), + 1 for rows g and g + 8
+                const float4 sc = *reinterpret_cast<const float4*>(quads + r * kQuadFloats + (c * 4 + v) * 32 + g * 4);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint4 w = h == 0 ? w0 : w1;
+                    const uint32_t wh0 = h == 0 ? qh.x : qh.z, wh1 = h == 0 ? qh.y : qh.w;
+                    const uint32_t l0 = (v & 1) ? w.y : w.x, l1 = (v & 1) ? w.w : w.z;
+                    // the variant's two high bits sit at bits 2v..2v+1 of each high-bit byte: move them to bits 4..5
+                    uint32_t t0, t1;
+                    if (v == 0) { t0 = wh0 << 4; t1 = wh1 << 4; }
+                    else if (v == 1) { t0 = wh0 << 2; t1 = wh1 << 2; }
+                    else if (v == 2) { t0 = wh0; t1 = wh1; }
+                    else { t0 = wh0 >> 2; t1 = wh1 >> 2; }
+                    const uint32_t a0 = and_or(v < 2 ? l0 : l0 >> 4, kNibbles, t0 & kTopBits);
+                    const uint32_t a1 = and_or(v < 2 ? l1 : l1 >> 4, kNibbles, t1 & kTopBits);
+#pragma unroll
+                    for (int j = 0; j < kColTiles; ++j) {
+                        int cc[4];
+                        imma_k16(cc, a0, a1, h == 0 ? bb[v][j].x : bb[v][j].y);
+                        fold(acc[r][j], cc, h == 0 ? sc.x : sc.y, h == 0 ? sc.z : sc.w);
+                    }
+                }
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1) gemm_imma_kernel(const GemmArgs a, const StageLayout lay) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int K = a.k, k_tiles = K / kTileCols;
+    const int mp = (a.members + kMemberPad - 1) / kMemberPad * kMemberPad;
     unsigned char* stage[2] = {smem, smem + lay.stage_bytes};
-    float* hdr = reinterpret_cast<float*>(smem + 2 * lay.stage_bytes);              // [kRowTiles][16][kHdrStride]
-    const uint32_t bars = smem_u32(hdr + kRowTiles * 16 * kHdrStride);               // full[2]
+    float* quads = reinterpret_cast<float*>(smem + 2 * lay.stage_bytes);   // [kRowTiles][kQuadFloats]
+    float* coef = quads + kRowTiles * kQuadFloats;                          // [kCtaRows][kCoefStride]
+    const uint32_t bars = smem_u32(coef + kCtaRows * kCoefStride);          // full[2]
     const bool swiglu = a.epilogue == kSwiGLU;
 
     // This CTA's row tiles: kRowTiles consecutive tiles of one segment (SwiGLU: 2 gate + the 2 matching up tiles).
@@ -163,12 +287,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_imma_kernel(const GemmArgs a
 
     int tile_type[kRowTiles];              // -1: beyond the segment's last row tile
     const unsigned char* tile_src[kRowTiles];
+    int mask_q4k = 0, mask_q6k = 0, mask_q8 = 0;
 #pragma unroll
     for (int r = 0; r < kRowTiles; ++r) {
         const GemvSegment* s; int rt;
         const bool ok = tile_of(r, s, rt);
         tile_type[r] = ok ? s->type : -1;
         tile_src[r] = s->data + (size_t)rt * k_tiles * packed_tile_bytes(s->type);
+        if (tile_type[r] == kQ4_K) mask_q4k |= 1 << r;
+        if (tile_type[r] == kQ6_K) mask_q6k |= 1 << r;
+        if (tile_type[r] == kQ8_0) mask_q8 |= 1 << r;
     }
 
     if (threadIdx.x == 0) {
@@ -176,8 +304,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_imma_kernel(const GemmArgs a
         mbar_init(bars + 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // Coefficients of absent row tiles read as zero (their offset sums are computed but never stored).
+    for (int i = threadIdx.x; i < kCtaRows * kCoefStride; i += kThreads) coef[i] = 0.0f;
     __syncthreads();
 
+    const int tile_stride = lay.w_bytes / kRowTiles;
     auto issue = [&](int kb) {  // thread 0: fill stage kb & 1 with the weights and activations of k tile kb
         const int b = kb & 1;
         const uint32_t bar = bars + b * 8;
@@ -190,7 +321,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_imma_kernel(const GemmArgs a
         for (int r = 0; r < kRowTiles; ++r) {
             if (tile_type[r] >= 0) {
                 const uint32_t tb = (uint32_t)packed_tile_bytes(tile_type[r]);
-                bulk_g2s(smem_u32(stage[b] + r * (lay.w_bytes / kRowTiles)), tile_src[r] + (size_t)kb * tb, tb, bar);
+                bulk_g2s(smem_u32(stage[b] + r * tile_stride), tile_src[r] + (size_t)kb * tb, tb, bar);
             }
         }
         bulk_g2s(smem_u32(stage[b] + lay.w_bytes), a.dig + (size_t)kb * lay.x_bytes, (uint32_t)lay.x_bytes, bar);
@@ -202,165 +333,124 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_imma_kernel(const GemmArgs a
         if (k_tiles > 1) issue(1);
     }
 
-    float acc[kRowTiles][4][4];  // [row tile][column tile][c fragment]
+    float acc[kRowTiles][kColTiles][4];  // [row tile][column tile][c fragment]
 #pragma unroll
     for (int r = 0; r < kRowTiles; ++r)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[r][j][0] = acc[r][j][1] = acc[r][j][2] = acc[r][j][3] = 0.0f;
+        for (int j = 0; j < kColTiles; ++j) acc[r][j][0] = acc[r][j][1] = acc[r][j][2] = acc[r][j][3] = 0.0f;
+    // Offset role: row groups of four rows, `warp` and (for the first four warps) `warp + 12`;
+    // members lane and lane + 32.
+    float off[2][4][2];
+#pragma unroll
+    for (int p = 0; p < 2; ++p)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) off[p][i][0] = off[p][i][1] = 0.0f;
+    const bool off_live0 = lane < mp, off_live1 = lane + 32 < mp;
 
     bool alive = true;
-    const int member0 = warp * kMembersPerWarp;  // this warp's first member
-    // Warps whose members lie beyond the (padded) batch only help with headers and barriers:
-    // the stage holds digits for the padded member count and nothing further.
-    const bool warp_live = member0 < (a.members + kMembersPerWarp - 1) / kMembersPerWarp * kMembersPerWarp;
+    // Column tiles 2 warp, 2 warp + 1 of the 3 mp / 8 in use; warps beyond them skip the MMA part
+    // (the stage holds digit planes for the padded member count and nothing further).
+    const int col_tiles = 3 * mp / 8;
+    const bool warp_live = kColTiles * warp < col_tiles;
     for (int kb = 0; kb < k_tiles; ++kb) {
         const int b = kb & 1;
         if (alive) alive = mbar_wait(bars + b * 8, (kb >> 1) & 1, a.error_flag, 4);
         const unsigned char* wst = stage[b];
         const signed char* xst = reinterpret_cast<const signed char*>(stage[b] + lay.w_bytes);
-        const float* sst = reinterpret_cast<const float*>(stage[b] + lay.w_bytes + lay.x_bytes);
+        const float4* sst = reinterpret_cast<const float4*>(stage[b] + lay.w_bytes + lay.x_bytes);  // [4][mp]
 #pragma unroll
         for (int r = 0; r < kRowTiles; ++r)
             if (warp == r && tile_type[r] >= 0)
-                decode_header(tile_type[r], wst + r * (lay.w_bytes / kRowTiles), hdr + r * 16 * kHdrStride, lane);
+                decode_header(tile_type[r], wst + r * tile_stride, quads + r * kQuadFloats, coef + r * 16 * kCoefStride, lane);
         __syncthreads();
-        // B fragments: MMA column tile j holds members member0 + 2j (cols 0..2) and + 2j + 1 (cols 4..6).
-        const bool col_live = (g & 3) < 3;
-        const signed char* xcol[4];
+        // ---- offsets -------------------------------------------------------------------------------
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int m = member0 + 2 * j + (g >> 2);
-            xcol[j] = xst + ((size_t)m * 3 + (g & 3)) * kPlane + 8 * t;
+        for (int p = 0; p < 2; ++p) {
+            const int group = warp + p * kWarps;
+            if (group >= kCtaRows / 4) break;                                  // warp-uniform
+            const float* cf = coef + (size_t)(4 * group) * kCoefStride;        // warp-uniform: broadcast reads
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const float4 s0 = off_live0 ? sst[q4 * mp + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 s1 = off_live1 ? sst[q4 * mp + lane + 32] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float4 c = *reinterpret_cast<const float4*>(cf + i * kCoefStride + 4 * q4);
+                    off[p][i][0] = fmaf(c.x, s0.x, off[p][i][0]); off[p][i][0] = fmaf(c.y, s0.y, off[p][i][0]);
+                    off[p][i][0] = fmaf(c.z, s0.z, off[p][i][0]); off[p][i][0] = fmaf(c.w, s0.w, off[p][i][0]);
+                    off[p][i][1] = fmaf(c.x, s1.x, off[p][i][1]); off[p][i][1] = fmaf(c.y, s1.y, off[p][i][1]);
+                    off[p][i][1] = fmaf(c.z, s1.z, off[p][i][1]); off[p][i][1] = fmaf(c.w, s1.w, off[p][i][1]);
+                }
+            }
         }
+        // ---- integer MMAs: column 8 (2 warp + j) + g is digit plane number `column` of the stage --------
+        if (warp_live) {
+            const signed char* xcol[kColTiles];
 #pragma unroll
-        for (int r = 0; r < kRowTiles; ++r) {
-            const int type = warp_live ? tile_type[r] : -1;
-            if (type < 0) continue;
-            const unsigned char* tile = wst + r * (lay.w_bytes / kRowTiles);
-            const float* h0 = hdr + (r * 16 + g) * kHdrStride;
-            const float* h1 = h0 + 8 * kHdrStride;
-            if (type == kQ6_K) {
-#pragma unroll 1
-                for (int c = 0; c < 2; ++c) {
-                    const uint4 qh = *reinterpret_cast<const uint4*>(tile + 2048 + c * 512 + lane * 16);
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const uint4 w = *reinterpret_cast<const uint4*>(tile + (c * 2 + h) * 512 + lane * 16);
-                        const uint32_t wh0 = h == 0 ? qh.x : qh.z, wh1 = h == 0 ? qh.y : qh.w;
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            const uint32_t l0 = (v & 1) ? w.y : w.x, l1 = (v & 1) ? w.w : w.z;
-                            uint32_t t0, t1;
-                            if (v == 0) { t0 = wh0 << 4; t1 = wh1 << 4; }
-                            else if (v == 1) { t0 = wh0 << 2; t1 = wh1 << 2; }
-                            else if (v == 2) { t0 = wh0; t1 = wh1; }
-                            else { t0 = wh0 >> 2; t1 = wh1 >> 2; }
-                            const uint32_t a0 = and_or(v < 2 ? l0 : l0 >> 4, kNibbles, t0 & kTopBits);
-                            const uint32_t a1 = and_or(v < 2 ? l1 : l1 >> 4, kNibbles, t1 & kTopBits);
-                            const int group = c * 4 + v, sub = group * 2 + h;
-                            const float s0 = h0[sub], s1 = h1[sub];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const uint2 bb = col_live ? *reinterpret_cast<const uint2*>(xcol[j] + group * 32) : make_uint2(0u, 0u);
-                                int cc[4];
-                                imma_k16(cc, a0, a1, h == 0 ? bb.x : bb.y);
-                                fold(acc[r][j], cc, s0, s1);
-                            }
-                        }
-                    }
-                }
-            } else if (type == kQ4_K) {
-#pragma unroll 1
-                for (int jj = 0; jj < 4; ++jj) {
-                    const uint4 w = *reinterpret_cast<const uint4*>(tile + jj * 512 + lane * 16);
-                    const float se0 = h0[4 * jj], se1 = h1[4 * jj], so0 = h0[4 * jj + 2], so1 = h1[4 * jj + 2];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint2 be = col_live ? *reinterpret_cast<const uint2*>(xcol[j] + (2 * jj) * 32) : make_uint2(0u, 0u);
-                        const uint2 bo = col_live ? *reinterpret_cast<const uint2*>(xcol[j] + (2 * jj + 1) * 32) : make_uint2(0u, 0u);
-                        int ce[4], co[4];
-                        imma_k32(ce, w.x & kNibbles, w.z & kNibbles, w.y & kNibbles, w.w & kNibbles, be.x, be.y);
-                        imma_k32(co, (w.x >> 4) & kNibbles, (w.z >> 4) & kNibbles, (w.y >> 4) & kNibbles,
-                                 (w.w >> 4) & kNibbles, bo.x, bo.y);
-                        fold(acc[r][j], ce, se0, se1);
-                        fold(acc[r][j], co, so0, so1);
-                    }
-                }
-            } else {
-#pragma unroll 1
-                for (int b8 = 0; b8 < 8; ++b8) {
-                    const uint4 w = *reinterpret_cast<const uint4*>(tile + b8 * 512 + lane * 16);
-                    const float s0 = h0[2 * b8], s1 = h1[2 * b8];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint2 bb = col_live ? *reinterpret_cast<const uint2*>(xcol[j] + b8 * 32) : make_uint2(0u, 0u);
-                        int cc[4];
-                        imma_k32(cc, w.x, w.z, w.y, w.w, bb.x, bb.y);
-                        fold(acc[r][j], cc, s0, s1);
-                    }
-                }
+            for (int j = 0; j < kColTiles; ++j) {
+                // an odd count of column tiles leaves the last warp's second tile empty: it re-reads the first
+                const int ct = min(kColTiles * warp + j, col_tiles - 1);
+                xcol[j] = xst + (size_t)(8 * ct + g) * kPlane + 8 * t;
             }
-            // Offsets: lanes with even t own digit 1 of member member0 + 2j + t/2; add coef[row][sub] * sum16[sub][member].
-            if ((t & 1) == 0) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float* sums = sst + (size_t)(member0 + 2 * j + (t >> 1)) * 16;
-                    float o0 = 0.0f, o1 = 0.0f;
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        const float4 sv = *reinterpret_cast<const float4*>(sums + 4 * q4);
-                        const float4 c0 = *reinterpret_cast<const float4*>(h0 + 16 + 4 * q4);
-                        const float4 c1 = *reinterpret_cast<const float4*>(h1 + 16 + 4 * q4);
-                        o0 = fmaf(c0.x, sv.x, o0); o0 = fmaf(c0.y, sv.y, o0); o0 = fmaf(c0.z, sv.z, o0); o0 = fmaf(c0.w, sv.w, o0);
-                        o1 = fmaf(c1.x, sv.x, o1); o1 = fmaf(c1.y, sv.y, o1); o1 = fmaf(c1.z, sv.z, o1); o1 = fmaf(c1.w, sv.w, o1);
-                    }
-                    acc[r][j][0] += o0;
-                    acc[r][j][2] += o1;
-                }
-            }
+            if (mask_q4k) mma_q4k(wst, tile_stride, quads, mask_q4k, xcol, lane, g, acc);
+            if (mask_q6k) mma_q6k(wst, tile_stride, quads, mask_q6k, xcol, lane, g, acc);
+            if (mask_q8) mma_q8_0(wst, tile_stride, quads, mask_q8, xcol, lane, g, acc);
         }
         __syncthreads();  // everyone has left stage b and the headers
         if (threadIdx.x == 0 && kb + 2 < k_tiles) issue(kb + 2);
     }
 
-    // Epilogue: even-t lanes hold (rows g, g + 8) x member (member0 + 2j + t/2) once the digits are combined.
+    // Accumulators and offset totals meet in shared memory (the stages are free now).
+    float* exch = reinterpret_cast<float*>(smem);                  // [kCtaRows][kExchStride]: column 3 m + digit
+    float* offx = exch + kCtaRows * kExchStride;                   // [kCtaRows][kOffStride]
+    if (warp_live) {
 #pragma unroll
-    for (int r = 0; r < kRowTiles; ++r) {
+        for (int r = 0; r < kRowTiles; ++r)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float d3a = __shfl_down_sync(0xffffffffu, acc[r][j][0], 1);
-            const float d3b = __shfl_down_sync(0xffffffffu, acc[r][j][2], 1);
-            acc[r][j][0] = acc[r][j][0] + acc[r][j][1] * (1.0f / 128.0f) + d3a * (1.0f / 16384.0f);
-            acc[r][j][2] = acc[r][j][2] + acc[r][j][3] * (1.0f / 128.0f) + d3b * (1.0f / 16384.0f);
-        }
-    }
-    if ((t & 1) != 0) return;
-#pragma unroll
-    for (int r = 0; r < (swiglu ? kRowTiles / 2 : kRowTiles); ++r) {
-        // SwiGLU pairs accumulators (2r, 2r + 1) = (gate, up) of the same rows.
-        const int ra = swiglu ? 2 * r : r;
-        const GemvSegment* s; int rt;
-        if (!tile_of(ra, s, rt)) continue;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int m = member0 + 2 * j + (t >> 1);
-            if (m >= a.members) continue;
-            const float mult = a.member_scale[m];
-#pragma unroll
-            for (int hrow = 0; hrow < 2; ++hrow) {
-                const int n_index = rt * kTileRows + g + 8 * hrow;
-                if (n_index >= s->n) continue;
-                const float v = acc[ra][j][2 * hrow] * mult;
-                float* y = a.seg[swiglu ? 0 : seg].y + (size_t)m * s->n + n_index;
-                if (swiglu) {
-                    const float u = acc[ra + 1][j][2 * hrow] * mult;
-                    *y = v / (1.0f + expf(-v)) * u;
-                } else if (a.epilogue == kResidual) {
-                    *y += v;
-                } else {
-                    *y = v;
+            for (int j = 0; j < kColTiles; ++j) {
+                const int ct = kColTiles * warp + j;
+                if (ct < col_tiles) {
+                    float* e = exch + (size_t)(r * 16 + g) * kExchStride + 8 * ct + 2 * t;
+                    e[0] = acc[r][j][0]; e[1] = acc[r][j][1];
+                    e[8 * kExchStride] = acc[r][j][2]; e[8 * kExchStride + 1] = acc[r][j][3];
                 }
             }
+    }
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+        const int group = warp + p * kWarps;
+        if (group >= kCtaRows / 4) break;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            offx[(4 * group + i) * kOffStride + lane] = off[p][i][0];
+            offx[(4 * group + i) * kOffStride + lane + 32] = off[p][i][1];
+        }
+    }
+    __syncthreads();
+
+    // Epilogue: consecutive threads take consecutive output rows of one member.
+    const int out_rows = swiglu ? kCtaRows / 2 : kCtaRows;
+    for (int idx = threadIdx.x; idx < out_rows * a.members; idx += kThreads) {
+        const int m = idx / out_rows, o = idx % out_rows;
+        // SwiGLU: output row o of the unit is gate row (o / 16) * 32 + o % 16 of the CTA, its up row 16 further
+        const int row = swiglu ? (o >> 4) * 32 + (o & 15) : o;
+        const GemvSegment& s = a.seg[swiglu ? 0 : seg];
+        const int n_index = unit * out_rows + o;
+        if (n_index >= s.n) continue;
+        const float mult = a.member_scale[m];
+        auto value = [&](int rr) {
+            const float* e = exch + (size_t)rr * kExchStride + 3 * m;
+            return (e[0] + e[1] * (1.0f / 128.0f) + e[2] * (1.0f / 16384.0f) + offx[rr * kOffStride + m]) * mult;
+        };
+        const float v = value(row);
+        float* y = s.y + (size_t)m * s.n + n_index;
+        if (swiglu) {
+            const float u = value(row + 16);
+            *y = v / (1.0f + expf(-v)) * u;
+        } else if (a.epilogue == kResidual) {
+            *y += v;
+        } else {
+            *y = v;
         }
     }
 }
@@ -394,7 +484,7 @@ __global__ void batch_scale_kernel(const float* x, const int32_t* index, const f
     }
 }
 
-// Pass 2: digits and per-16 digit sums, laid out per k tile: dig[kt][member][digit][kBatchPlaneBytes], sum16[kt][member][16].
+// Pass 2: digits and per-16 digit sums, laid out per k tile: dig[kt][member][digit][kBatchPlaneBytes], sum16[kt][sub / 4][member][sub % 4].
 __global__ void batch_digits_kernel(const float* x, const int32_t* index, const float* norm_weight, int members,
                                     int members_padded, int k, const float* digit_inv, signed char* dig, float* sum16) {
     const int lane = threadIdx.x & 31;
@@ -422,36 +512,42 @@ __global__ void batch_digits_kernel(const float* x, const int32_t* index, const 
     base[0] = (signed char)(int)f1;
     base[kPlane] = (signed char)(int)f2;
     base[2 * kPlane] = (signed char)(int)f3;
-    if ((lane & 15) == 0) sum16[((size_t)kt * members_padded + m) * 16 + (in_tile >> 4)] = value;
+    if ((lane & 15) == 0) {
+        const int sub = in_tile >> 4;
+        sum16[(((size_t)kt * 4 + (sub >> 2)) * members_padded + m) * 4 + (sub & 3)] = value;
+    }
 }
 
 StageLayout layout_for(const GemmArgs& a) {
     StageLayout l{};
     int tile = 0;
     for (int i = 0; i < a.n_segments; ++i) tile = std::max(tile, packed_tile_bytes(a.seg[i].type));
-    const int members_padded = (a.members + kMembersPerWarp - 1) / kMembersPerWarp * kMembersPerWarp;
+    const int members_padded = (a.members + kMemberPad - 1) / kMemberPad * kMemberPad;
     l.w_bytes = kRowTiles * tile;
     l.x_bytes = members_padded * 3 * kPlane;
     l.s_bytes = members_padded * 16 * 4;
     l.stage_bytes = (l.w_bytes + l.x_bytes + l.s_bytes + 127) / 128 * 128;
+    // the epilogue's exchange arrays reuse the two stages
+    const int exchange = kCtaRows * (kExchStride + kOffStride) * 4;
+    if (2 * l.stage_bytes < exchange) l.stage_bytes = (exchange / 2 + 127) / 128 * 128;
     return l;
 }
 
 }  // namespace
 
 size_t batch_operand_digit_bytes(int members, int k) {
-    const int mp = (members + kMembersPerWarp - 1) / kMembersPerWarp * kMembersPerWarp;
+    const int mp = (members + kMemberPad - 1) / kMemberPad * kMemberPad;
     return (size_t)(k / 256) * mp * 3 * kPlane;
 }
 size_t batch_operand_sum_floats(int members, int k) {
-    const int mp = (members + kMembersPerWarp - 1) / kMembersPerWarp * kMembersPerWarp;
+    const int mp = (members + kMemberPad - 1) / kMemberPad * kMemberPad;
     return (size_t)(k / 256) * mp * 16;
 }
 
 cudaError_t launch_to_batch_operand(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,
                                     int members, int k, float eps, BatchOperand out) {
     if (members <= 0 || members > kMaxMembers || k % 256 != 0) return cudaErrorInvalidValue;
-    const int mp = (members + kMembersPerWarp - 1) / kMembersPerWarp * kMembersPerWarp;
+    const int mp = (members + kMemberPad - 1) / kMemberPad * kMemberPad;
     batch_scale_kernel<<<members, 256, 0, stream>>>(x, index, norm_weight, k, eps, out.digit_inv, out.member_scale);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
@@ -473,7 +569,9 @@ cudaError_t launch_gemm_imma(cudaStream_t stream, const GemmArgs& args) {
     }
     if (units <= 0) return cudaSuccess;
     const StageLayout lay = layout_for(args);
-    const size_t smem = (size_t)2 * lay.stage_bytes + (size_t)kRowTiles * 16 * kHdrStride * 4 + 16;
+    const size_t tail = (size_t)(kRowTiles * kQuadFloats + kCtaRows * kCoefStride) * 4 + 16;
+    const size_t exchange = (size_t)kCtaRows * (kExchStride + kOffStride) * 4;
+    const size_t smem = std::max((size_t)2 * lay.stage_bytes, exchange) + tail;
     static size_t configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_imma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);

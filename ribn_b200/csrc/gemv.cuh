@@ -133,7 +133,7 @@ cudaError_t gemv_prepare();
 // so that one bulk copy brings every member's digits of that k tile:
 //   dig[k tile][member][digit][kBatchPlaneBytes]   (256 digits in `operand_position` order + padding
 //                                                   that spreads the members over the shared-memory banks)
-//   sum16[k tile][member][16]                      digit-value sums per 16 inputs (offset removal)
+//   sum16[k tile][sub / 4][member][sub % 4]        digit-value sums per 16 inputs `sub` (offset removal)
 //   member_scale[member]                           digit scale, times the RMSNorm factor when a norm precedes
 // Members are padded to a multiple of 8 with zero digits.
 constexpr int kBatchPlaneBytes = 288;
