@@ -327,8 +327,7 @@ cudaError_t batch_project(ribn_b200_executor* ex, int& launches, const float* x,
         }
         a.k = k;
         a.members = m;
-        a.dig = ex->op_batch.dig;
-        a.sum16 = ex->op_batch.sum16;
+        a.chunks = ex->op_batch.chunks;
         a.member_scale = ex->op_batch.member_scale;
         a.epilogue = epilogue;
         a.error_flag = ex->d_error;
@@ -735,8 +734,7 @@ int ribn_b200_finalize(ribn_b200_executor* ex) {
         {
             const int kmax = std::max(std::max(c.hidden, c.ffn), c.q_heads * c.head_dim);
             if (kmax % 256 == 0) {
-                CU_TRY(ex, dev_alloc(ex, &ex->op_batch.dig, batch_operand_digit_bytes(kGemmMaxMembers, kmax)));
-                CU_TRY(ex, dev_alloc(ex, &ex->op_batch.sum16, batch_operand_sum_floats(kGemmMaxMembers, kmax)));
+                CU_TRY(ex, dev_alloc(ex, &ex->op_batch.chunks, batch_operand_bytes(kGemmMaxMembers, kmax)));
                 CU_TRY(ex, dev_alloc(ex, &ex->op_batch.member_scale, kGemmMaxMembers));
                 CU_TRY(ex, dev_alloc(ex, &ex->op_batch.digit_inv, kGemmMaxMembers));
             }

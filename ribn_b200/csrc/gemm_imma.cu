@@ -21,14 +21,19 @@
 #include "blocks.cuh"
 #include "gemv.cuh"
 
+// Measurement aid (0 in the shipped build): 1 = no MMA part, 2 = neither MMAs nor offsets, 3 = no offsets.
+#ifndef RIBN_GEMM_PROBE
+#define RIBN_GEMM_PROBE 0
+#endif
+
 namespace ribn {
 
 namespace {
 
-constexpr int kWarps = 12;
-constexpr int kThreads = kWarps * 32;
-constexpr int kRowTiles = 4;            // row tiles per CTA
-constexpr int kCtaRows = kRowTiles * 16;
+constexpr int kWarps = 12;              // MMA warps; two more serve them: one issues the copies, one decodes headers
+constexpr int kProducerWarp = kWarps, kHeaderWarp = kWarps + 1;
+constexpr int kThreads = (kWarps + 2) * 32;
+constexpr int kMaxRowTiles = 4;         // row tiles per CTA: 4, or 2 when that fills more SMs
 constexpr int kColTiles = 2;            // MMA column tiles (8 columns each) per warp
 constexpr int kMaxMembers = kGemmMaxMembers;
 constexpr int kMemberPad = 8;           // members are padded to a multiple of this: 3 * 8 columns = 3 column tiles
@@ -46,6 +51,9 @@ constexpr uint32_t kSpinLimit = 1u << 22;
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -145,17 +153,21 @@ __device__ __forceinline__ void decode_header(int type, const unsigned char* til
 }
 
 struct StageLayout {
-    int w_bytes;      // kRowTiles weight tiles
+    int w_bytes;      // the row tiles of the CTA
     int x_bytes;      // members_padded * 3 digit planes
     int s_bytes;      // members_padded * 16 floats of per-16 digit sums
     int stage_bytes;
 };
 
-// MMA part of one k tile for the CTA's row tiles of one format (tiles of another format or absent
-// tiles have their bit in `mask` clear).  B fragments are loaded once and reused across the row tiles.
+// MMA part of one k tile for the CTA's row tiles of one format.  B fragments are loaded once and
+// reused across the row tiles.  MASKED: tiles of another format or absent tiles have their bit in
+// `mask` clear and are skipped; otherwise all four row tiles are processed without branches (an
+// absent tile then computes on stale shared memory into accumulators that are never stored), which
+// lets the compiler interleave the independent MMA -> fold chains.
+template <int RT, bool MASKED>
 __device__ __forceinline__ void mma_q4k(const unsigned char* wst, int tile_stride, const float* quads, int mask,
                                         const signed char* const (&xcol)[kColTiles], int lane, int g,
-                                        float (&acc)[kRowTiles][kColTiles][4]) {
+                                        float (&acc)[RT][kColTiles][4]) {
 #pragma unroll 1
     for (int jj = 0; jj < 4; ++jj) {
         uint2 be[kColTiles], bo[kColTiles];
@@ -165,8 +177,8 @@ __device__ __forceinline__ void mma_q4k(const unsigned char* wst, int tile_strid
             bo[j] = *reinterpret_cast<const uint2*>(xcol[j] + (2 * jj + 1) * 32);
         }
 #pragma unroll
-        for (int r = 0; r < kRowTiles; ++r) {
-            if (!(mask >> r & 1)) continue;
+        for (int r = 0; r < RT; ++r) {
+            if (MASKED && !(mask >> r & 1)) continue;
             const uint4 w = *reinterpret_cast<const uint4*>(wst + r * tile_stride + jj * 512 + lane * 16);
             const float4 sc = *reinterpret_cast<const float4*>(quads + r * kQuadFloats + jj * 32 + g * 4);
             const uint32_t e0 = w.x & kNibbles, e1 = w.z & kNibbles, e2 = w.y & kNibbles, e3 = w.w & kNibbles;
@@ -184,9 +196,10 @@ __device__ __forceinline__ void mma_q4k(const unsigned char* wst, int tile_strid
     }
 }
 
+template <int RT, bool MASKED>
 __device__ __forceinline__ void mma_q8_0(const unsigned char* wst, int tile_stride, const float* quads, int mask,
                                          const signed char* const (&xcol)[kColTiles], int lane, int g,
-                                         float (&acc)[kRowTiles][kColTiles][4]) {
+                                         float (&acc)[RT][kColTiles][4]) {
 #pragma unroll 1
     for (int jj = 0; jj < 4; ++jj) {
         uint2 be[kColTiles], bo[kColTiles];
@@ -196,8 +209,8 @@ __device__ __forceinline__ void mma_q8_0(const unsigned char* wst, int tile_stri
             bo[j] = *reinterpret_cast<const uint2*>(xcol[j] + (2 * jj + 1) * 32);
         }
 #pragma unroll
-        for (int r = 0; r < kRowTiles; ++r) {
-            if (!(mask >> r & 1)) continue;
+        for (int r = 0; r < RT; ++r) {
+            if (MASKED && !(mask >> r & 1)) continue;
             const uint4 we = *reinterpret_cast<const uint4*>(wst + r * tile_stride + (2 * jj) * 512 + lane * 16);
             const uint4 wo = *reinterpret_cast<const uint4*>(wst + r * tile_stride + (2 * jj + 1) * 512 + lane * 16);
             const float4 sc = *reinterpret_cast<const float4*>(quads + r * kQuadFloats + jj * 32 + g * 4);
@@ -213,9 +226,10 @@ __device__ __forceinline__ void mma_q8_0(const unsigned char* wst, int tile_stri
     }
 }
 
+template <int RT, bool MASKED>
 __device__ __forceinline__ void mma_q6k(const unsigned char* wst, int tile_stride, const float* quads, int mask,
                                         const signed char* const (&xcol)[kColTiles], int lane, int g,
-                                        float (&acc)[kRowTiles][kColTiles][4]) {
+                                        float (&acc)[RT][kColTiles][4]) {
 #pragma unroll 1
     for (int c = 0; c < 2; ++c) {
         uint2 bb[4][kColTiles];
@@ -224,8 +238,8 @@ __device__ __forceinline__ void mma_q6k(const unsigned char* wst, int tile_strid
 #pragma unroll
             for (int j = 0; j < kColTiles; ++j) bb[v][j] = *reinterpret_cast<const uint2*>(xcol[j] + (c * 4 + v) * 32);
 #pragma unroll
-        for (int r = 0; r < kRowTiles; ++r) {
-            if (!(mask >> r & 1)) continue;
+        for (int r = 0; r < RT; ++r) {
+            if (MASKED && !(mask >> r & 1)) continue;
             const unsigned char* tile = wst + r * tile_stride + lane * 16;
             const uint4 qh = *reinterpret_cast<const uint4*>(tile + 2048 + c * 512);
             const uint4 w0 = *reinterpret_cast<const uint4*>(tile + (c * 2) * 512);       // inputs 0..15 of each group
@@ -259,37 +273,41 @@ __device__ __forceinline__ void mma_q6k(const unsigned char* wst, int tile_strid
     }
 }
 
+template <int RT>
 __global__ void __launch_bounds__(kThreads, 1) gemm_imma_kernel(const GemmArgs a, const StageLayout lay) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int K = a.k, k_tiles = K / kTileCols;
     const int mp = (a.members + kMemberPad - 1) / kMemberPad * kMemberPad;
     unsigned char* stage[2] = {smem, smem + lay.stage_bytes};
-    float* quads = reinterpret_cast<float*>(smem + 2 * lay.stage_bytes);   // [kRowTiles][kQuadFloats]
-    float* coef = quads + kRowTiles * kQuadFloats;                          // [kCtaRows][kCoefStride]
-    const uint32_t bars = smem_u32(coef + kCtaRows * kCoefStride);          // full[2]
+    // per stage: fold scales [RT][kQuadFloats] and offset coefficients [(RT * 16)][kCoefStride]
+    float* quads = reinterpret_cast<float*>(smem + 2 * lay.stage_bytes);
+    float* coef = quads + 2 * RT * kQuadFloats;
+    // mbarriers: full[2] (copies landed), ready[2] (headers decoded), empty[2] (MMA warps left the stage)
+    const uint32_t bars = smem_u32(coef + 2 * (RT * 16) * kCoefStride);
+    const uint32_t bar_full = bars, bar_ready = bars + 16, bar_empty = bars + 32;
     const bool swiglu = a.epilogue == kSwiGLU;
 
-    // This CTA's row tiles: kRowTiles consecutive tiles of one segment (SwiGLU: 2 gate + the 2 matching up tiles).
+    // This CTA's row tiles: RT consecutive tiles of one segment (SwiGLU: 2 gate + the 2 matching up tiles).
     int seg = 0, unit = blockIdx.x;
     if (!swiglu) {
-        while (seg + 1 < a.n_segments && unit >= (a.seg[seg].row_tiles + kRowTiles - 1) / kRowTiles) {
-            unit -= (a.seg[seg].row_tiles + kRowTiles - 1) / kRowTiles;
+        while (seg + 1 < a.n_segments && unit >= (a.seg[seg].row_tiles + RT - 1) / RT) {
+            unit -= (a.seg[seg].row_tiles + RT - 1) / RT;
             ++seg;
         }
     }
-    const int rows_per_unit = swiglu ? kRowTiles / 2 : kRowTiles;
+    const int rows_per_unit = swiglu ? RT / 2 : RT;
     auto tile_of = [&](int r, const GemvSegment*& s, int& rt) -> bool {
         s = &a.seg[swiglu ? (r & 1) : seg];
         rt = unit * rows_per_unit + (swiglu ? (r >> 1) : r);
         return rt < s->row_tiles;
     };
 
-    int tile_type[kRowTiles];              // -1: beyond the segment's last row tile
-    const unsigned char* tile_src[kRowTiles];
+    int tile_type[RT];              // -1: beyond the segment's last row tile
+    const unsigned char* tile_src[RT];
     int mask_q4k = 0, mask_q6k = 0, mask_q8 = 0;
 #pragma unroll
-    for (int r = 0; r < kRowTiles; ++r) {
+    for (int r = 0; r < RT; ++r) {
         const GemvSegment* s; int rt;
         const bool ok = tile_of(r, s, rt);
         tile_type[r] = ok ? s->type : -1;
@@ -298,44 +316,26 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_imma_kernel(const GemmArgs a
         if (tile_type[r] == kQ6_K) mask_q6k |= 1 << r;
         if (tile_type[r] == kQ8_0) mask_q8 |= 1 << r;
     }
+    // One format across the present row tiles (the usual case): the branch-free MMA path serves.
+    const int uniform_type = (mask_q6k | mask_q8) == 0 ? kQ4_K : (mask_q4k | mask_q8) == 0 ? kQ6_K
+                           : (mask_q4k | mask_q6k) == 0 ? kQ8_0 : -1;
 
     if (threadIdx.x == 0) {
-        mbar_init(bars, 1);
-        mbar_init(bars + 8, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_full + 8 * b, 1);
+            mbar_init(bar_ready + 8 * b, 1);
+            mbar_init(bar_empty + 8 * b, kWarps);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // Coefficients of absent row tiles read as zero (their offset sums are computed but never stored).
-    for (int i = threadIdx.x; i < kCtaRows * kCoefStride; i += kThreads) coef[i] = 0.0f;
+    for (int i = threadIdx.x; i < 2 * (RT * 16) * kCoefStride; i += kThreads) coef[i] = 0.0f;
     __syncthreads();
 
-    const int tile_stride = lay.w_bytes / kRowTiles;
-    auto issue = [&](int kb) {  // thread 0: fill stage kb & 1 with the weights and activations of k tile kb
-        const int b = kb & 1;
-        const uint32_t bar = bars + b * 8;
-        uint32_t bytes = (uint32_t)(lay.x_bytes + lay.s_bytes);
+    const int tile_stride = lay.w_bytes / RT;
+    float acc[RT][kColTiles][4];  // [row tile][column tile][c fragment]
 #pragma unroll
-        for (int r = 0; r < kRowTiles; ++r)
-            if (tile_type[r] >= 0) bytes += (uint32_t)packed_tile_bytes(tile_type[r]);
-        mbar_expect_tx(bar, bytes);
-#pragma unroll
-        for (int r = 0; r < kRowTiles; ++r) {
-            if (tile_type[r] >= 0) {
-                const uint32_t tb = (uint32_t)packed_tile_bytes(tile_type[r]);
-                bulk_g2s(smem_u32(stage[b] + r * tile_stride), tile_src[r] + (size_t)kb * tb, tb, bar);
-            }
-        }
-        bulk_g2s(smem_u32(stage[b] + lay.w_bytes), a.dig + (size_t)kb * lay.x_bytes, (uint32_t)lay.x_bytes, bar);
-        bulk_g2s(smem_u32(stage[b] + lay.w_bytes + lay.x_bytes), a.sum16 + (size_t)kb * (lay.s_bytes / 4),
-                 (uint32_t)lay.s_bytes, bar);
-    };
-    if (threadIdx.x == 0) {
-        issue(0);
-        if (k_tiles > 1) issue(1);
-    }
-
-    float acc[kRowTiles][kColTiles][4];  // [row tile][column tile][c fragment]
-#pragma unroll
-    for (int r = 0; r < kRowTiles; ++r)
+    for (int r = 0; r < RT; ++r)
 #pragma unroll
         for (int j = 0; j < kColTiles; ++j) acc[r][j][0] = acc[r][j][1] = acc[r][j][2] = acc[r][j][3] = 0.0f;
     // Offset role: row groups of four rows, `warp` and (for the first four warps) `warp + 12`;
@@ -345,67 +345,111 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_imma_kernel(const GemmArgs a
     for (int p = 0; p < 2; ++p)
 #pragma unroll
         for (int i = 0; i < 4; ++i) off[p][i][0] = off[p][i][1] = 0.0f;
-    const bool off_live0 = lane < mp, off_live1 = lane + 32 < mp;
-
-    bool alive = true;
     // Column tiles 2 warp, 2 warp + 1 of the 3 mp / 8 in use; warps beyond them skip the MMA part
     // (the stage holds digit planes for the padded member count and nothing further).
     const int col_tiles = 3 * mp / 8;
-    const bool warp_live = kColTiles * warp < col_tiles;
-    for (int kb = 0; kb < k_tiles; ++kb) {
-        const int b = kb & 1;
-        if (alive) alive = mbar_wait(bars + b * 8, (kb >> 1) & 1, a.error_flag, 4);
-        const unsigned char* wst = stage[b];
-        const signed char* xst = reinterpret_cast<const signed char*>(stage[b] + lay.w_bytes);
-        const float4* sst = reinterpret_cast<const float4*>(stage[b] + lay.w_bytes + lay.x_bytes);  // [4][mp]
+
+    if (warp == kProducerWarp) {
+        // ---- copies: stage kb & 1 receives the weights and activations of k tile kb -------------------
+        if (lane == 0) {
+            bool alive = true;
+            for (int kb = 0; kb < k_tiles; ++kb) {
+                const int b = kb & 1;
+                if (kb >= 2 && alive) alive = mbar_wait(bar_empty + 8 * b, ((kb >> 1) - 1) & 1, a.error_flag, 5);
+                const uint32_t bar = bar_full + 8 * b;
+                uint32_t bytes = (uint32_t)(lay.x_bytes + lay.s_bytes);
 #pragma unroll
-        for (int r = 0; r < kRowTiles; ++r)
-            if (warp == r && tile_type[r] >= 0)
-                decode_header(tile_type[r], wst + r * tile_stride, quads + r * kQuadFloats, coef + r * 16 * kCoefStride, lane);
-        __syncthreads();
-        // ---- offsets -------------------------------------------------------------------------------
+                for (int r = 0; r < RT; ++r)
+                    if (tile_type[r] >= 0) bytes += (uint32_t)packed_tile_bytes(tile_type[r]);
+                mbar_expect_tx(bar, bytes);
+                // digits and sums of a k tile are adjacent in memory: one copy
+                bulk_g2s(smem_u32(stage[b] + lay.w_bytes), a.chunks + (size_t)kb * (lay.x_bytes + lay.s_bytes),
+                         (uint32_t)(lay.x_bytes + lay.s_bytes), bar);
 #pragma unroll
-        for (int p = 0; p < 2; ++p) {
-            const int group = warp + p * kWarps;
-            if (group >= kCtaRows / 4) break;                                  // warp-uniform
-            const float* cf = coef + (size_t)(4 * group) * kCoefStride;        // warp-uniform: broadcast reads
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-                const float4 s0 = off_live0 ? sst[q4 * mp + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
-                const float4 s1 = off_live1 ? sst[q4 * mp + lane + 32] : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float4 c = *reinterpret_cast<const float4*>(cf + i * kCoefStride + 4 * q4);
-                    off[p][i][0] = fmaf(c.x, s0.x, off[p][i][0]); off[p][i][0] = fmaf(c.y, s0.y, off[p][i][0]);
-                    off[p][i][0] = fmaf(c.z, s0.z, off[p][i][0]); off[p][i][0] = fmaf(c.w, s0.w, off[p][i][0]);
-                    off[p][i][1] = fmaf(c.x, s1.x, off[p][i][1]); off[p][i][1] = fmaf(c.y, s1.y, off[p][i][1]);
-                    off[p][i][1] = fmaf(c.z, s1.z, off[p][i][1]); off[p][i][1] = fmaf(c.w, s1.w, off[p][i][1]);
+                for (int r = 0; r < RT; ++r) {
+                    if (tile_type[r] >= 0) {
+                        const uint32_t tb = (uint32_t)packed_tile_bytes(tile_type[r]);
+                        bulk_g2s(smem_u32(stage[b] + r * tile_stride), tile_src[r] + (size_t)kb * tb, tb, bar);
+                    }
                 }
             }
         }
-        // ---- integer MMAs: column 8 (2 warp + j) + g is digit plane number `column` of the stage --------
-        if (warp_live) {
-            const signed char* xcol[kColTiles];
+    } else if (warp == kHeaderWarp) {
+        // ---- headers: one stage ahead of the MMA warps ----------------------------------------------------
+        bool alive = true;
+        for (int kb = 0; kb < k_tiles; ++kb) {
+            const int b = kb & 1;
+            if (alive) alive = mbar_wait(bar_full + 8 * b, (kb >> 1) & 1, a.error_flag, 4);
 #pragma unroll
-            for (int j = 0; j < kColTiles; ++j) {
-                // an odd count of column tiles leaves the last warp's second tile empty: it re-reads the first
-                const int ct = min(kColTiles * warp + j, col_tiles - 1);
-                xcol[j] = xst + (size_t)(8 * ct + g) * kPlane + 8 * t;
-            }
-            if (mask_q4k) mma_q4k(wst, tile_stride, quads, mask_q4k, xcol, lane, g, acc);
-            if (mask_q6k) mma_q6k(wst, tile_stride, quads, mask_q6k, xcol, lane, g, acc);
-            if (mask_q8) mma_q8_0(wst, tile_stride, quads, mask_q8, xcol, lane, g, acc);
+            for (int r = 0; r < RT; ++r)
+                if (tile_type[r] >= 0)
+                    decode_header(tile_type[r], stage[b] + r * tile_stride, quads + (b * RT + r) * kQuadFloats,
+                                  coef + (b * (RT * 16) + r * 16) * kCoefStride, lane);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_ready + 8 * b);
         }
-        __syncthreads();  // everyone has left stage b and the headers
-        if (threadIdx.x == 0 && kb + 2 < k_tiles) issue(kb + 2);
+    } else {
+        const bool off_live0 = lane < mp, off_live1 = lane + 32 < mp;
+        const bool warp_live = kColTiles * warp < col_tiles;
+        bool alive = true;
+        for (int kb = 0; kb < k_tiles; ++kb) {
+            const int b = kb & 1;
+            if (alive) alive = mbar_wait(bar_ready + 8 * b, (kb >> 1) & 1, a.error_flag, 6);
+            const unsigned char* wst = stage[b];
+            const signed char* xst = reinterpret_cast<const signed char*>(stage[b] + lay.w_bytes);
+            const float4* sst = reinterpret_cast<const float4*>(stage[b] + lay.w_bytes + lay.x_bytes);  // [4][mp]
+            const float* qd = quads + b * RT * kQuadFloats;
+            // ---- offsets ---------------------------------------------------------------------------
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+                if (RIBN_GEMM_PROBE == 2 || RIBN_GEMM_PROBE == 3) break;
+                const int group = warp + p * kWarps;
+                if (group >= (RT * 16) / 4) break;                                         // warp-uniform
+                const float* cf = coef + (size_t)(b * (RT * 16) + 4 * group) * kCoefStride;   // broadcast reads
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const float4 s0 = off_live0 ? sst[q4 * mp + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 s1 = off_live1 ? sst[q4 * mp + lane + 32] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float4 c = *reinterpret_cast<const float4*>(cf + i * kCoefStride + 4 * q4);
+                        off[p][i][0] = fmaf(c.x, s0.x, off[p][i][0]); off[p][i][0] = fmaf(c.y, s0.y, off[p][i][0]);
+                        off[p][i][0] = fmaf(c.z, s0.z, off[p][i][0]); off[p][i][0] = fmaf(c.w, s0.w, off[p][i][0]);
+                        off[p][i][1] = fmaf(c.x, s1.x, off[p][i][1]); off[p][i][1] = fmaf(c.y, s1.y, off[p][i][1]);
+                        off[p][i][1] = fmaf(c.z, s1.z, off[p][i][1]); off[p][i][1] = fmaf(c.w, s1.w, off[p][i][1]);
+                    }
+                }
+            }
+            // ---- integer MMAs: column 8 (2 warp + j) + g is digit plane number `column` of the stage ----
+            if (warp_live && RIBN_GEMM_PROBE != 1 && RIBN_GEMM_PROBE != 2) {
+                const signed char* xcol[kColTiles];
+#pragma unroll
+                for (int j = 0; j < kColTiles; ++j) {
+                    // an odd count of column tiles leaves the last warp's second tile empty: it re-reads the first
+                    const int ct = min(kColTiles * warp + j, col_tiles - 1);
+                    xcol[j] = xst + (size_t)(8 * ct + g) * kPlane + 8 * t;
+                }
+                if (uniform_type == kQ4_K) mma_q4k<RT, false>(wst, tile_stride, qd, 0, xcol, lane, g, acc);
+                else if (uniform_type == kQ6_K) mma_q6k<RT, false>(wst, tile_stride, qd, 0, xcol, lane, g, acc);
+                else if (uniform_type == kQ8_0) mma_q8_0<RT, false>(wst, tile_stride, qd, 0, xcol, lane, g, acc);
+                else {
+                    if (mask_q4k) mma_q4k<RT, true>(wst, tile_stride, qd, mask_q4k, xcol, lane, g, acc);
+                    if (mask_q6k) mma_q6k<RT, true>(wst, tile_stride, qd, mask_q6k, xcol, lane, g, acc);
+                    if (mask_q8) mma_q8_0<RT, true>(wst, tile_stride, qd, mask_q8, xcol, lane, g, acc);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * b);
+        }
     }
+    __syncthreads();  // every copy has landed and every warp has left the stages
 
     // Accumulators and offset totals meet in shared memory (the stages are free now).
-    float* exch = reinterpret_cast<float*>(smem);                  // [kCtaRows][kExchStride]: column 3 m + digit
-    float* offx = exch + kCtaRows * kExchStride;                   // [kCtaRows][kOffStride]
-    if (warp_live) {
+    float* exch = reinterpret_cast<float*>(smem);                  // [(RT * 16)][kExchStride]: column 3 m + digit
+    float* offx = exch + (RT * 16) * kExchStride;                   // [(RT * 16)][kOffStride]
+    if (warp < kWarps) {
 #pragma unroll
-        for (int r = 0; r < kRowTiles; ++r)
+        for (int r = 0; r < RT; ++r)
 #pragma unroll
             for (int j = 0; j < kColTiles; ++j) {
                 const int ct = kColTiles * warp + j;
@@ -419,7 +463,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_imma_kernel(const GemmArgs a
 #pragma unroll
     for (int p = 0; p < 2; ++p) {
         const int group = warp + p * kWarps;
-        if (group >= kCtaRows / 4) break;
+        if (warp >= kWarps || group >= (RT * 16) / 4) break;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             offx[(4 * group + i) * kOffStride + lane] = off[p][i][0];
@@ -429,7 +473,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_imma_kernel(const GemmArgs a
     __syncthreads();
 
     // Epilogue: consecutive threads take consecutive output rows of one member.
-    const int out_rows = swiglu ? kCtaRows / 2 : kCtaRows;
+    const int out_rows = swiglu ? (RT * 16) / 2 : (RT * 16);
     for (int idx = threadIdx.x; idx < out_rows * a.members; idx += kThreads) {
         const int m = idx / out_rows, o = idx % out_rows;
         // SwiGLU: output row o of the unit is gate row (o / 16) * 32 + o % 16 of the CTA, its up row 16 further
@@ -484,9 +528,10 @@ __global__ void batch_scale_kernel(const float* x, const int32_t* index, const f
     }
 }
 
-// Pass 2: digits and per-16 digit sums, laid out per k tile: dig[kt][member][digit][kBatchPlaneBytes], sum16[kt][sub / 4][member][sub % 4].
+// Pass 2: digits and per-16 digit sums, one chunk per k tile:
+// [member][digit][kBatchPlaneBytes] digits, then [sub / 4][member][sub % 4] F32 sums.
 __global__ void batch_digits_kernel(const float* x, const int32_t* index, const float* norm_weight, int members,
-                                    int members_padded, int k, const float* digit_inv, signed char* dig, float* sum16) {
+                                    int members_padded, int k, const float* digit_inv, signed char* chunks) {
     const int lane = threadIdx.x & 31;
     const long long span_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int spans_per_member = k / 32;
@@ -508,40 +553,44 @@ __global__ void batch_digits_kernel(const float* x, const int32_t* index, const 
     float value = f1 + f2 * (1.0f / 128.0f) + f3 * (1.0f / 16384.0f);
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) value += __shfl_xor_sync(0xffffffffu, value, o);
-    signed char* base = dig + (((size_t)kt * members_padded + m) * 3) * kPlane + operand_position(in_tile);
+    const size_t digit_bytes = (size_t)members_padded * 3 * kPlane, chunk_bytes = digit_bytes + (size_t)members_padded * 64;
+    signed char* chunk = chunks + (size_t)kt * chunk_bytes;
+    signed char* base = chunk + ((size_t)m * 3) * kPlane + operand_position(in_tile);
     base[0] = (signed char)(int)f1;
     base[kPlane] = (signed char)(int)f2;
     base[2 * kPlane] = (signed char)(int)f3;
     if ((lane & 15) == 0) {
         const int sub = in_tile >> 4;
-        sum16[(((size_t)kt * 4 + (sub >> 2)) * members_padded + m) * 4 + (sub & 3)] = value;
+        reinterpret_cast<float*>(chunk + digit_bytes)[((size_t)(sub >> 2) * members_padded + m) * 4 + (sub & 3)] = value;
     }
 }
 
-StageLayout layout_for(const GemmArgs& a) {
+size_t exchange_bytes(int row_tiles) { return (size_t)row_tiles * 16 * (kExchStride + kOffStride) * 4; }
+
+StageLayout layout_for(const GemmArgs& a, int row_tiles) {
     StageLayout l{};
     int tile = 0;
     for (int i = 0; i < a.n_segments; ++i) tile = std::max(tile, packed_tile_bytes(a.seg[i].type));
     const int members_padded = (a.members + kMemberPad - 1) / kMemberPad * kMemberPad;
-    l.w_bytes = kRowTiles * tile;
+    l.w_bytes = row_tiles * tile;
     l.x_bytes = members_padded * 3 * kPlane;
     l.s_bytes = members_padded * 16 * 4;
     l.stage_bytes = (l.w_bytes + l.x_bytes + l.s_bytes + 127) / 128 * 128;
     // the epilogue's exchange arrays reuse the two stages
-    const int exchange = kCtaRows * (kExchStride + kOffStride) * 4;
+    const int exchange = (int)exchange_bytes(row_tiles);
     if (2 * l.stage_bytes < exchange) l.stage_bytes = (exchange / 2 + 127) / 128 * 128;
     return l;
 }
 
+size_t smem_for(const StageLayout& lay, int row_tiles) {
+    return (size_t)2 * lay.stage_bytes + (size_t)2 * (row_tiles * kQuadFloats + row_tiles * 16 * kCoefStride) * 4 + 64;
+}
+
 }  // namespace
 
-size_t batch_operand_digit_bytes(int members, int k) {
+size_t batch_operand_bytes(int members, int k) {
     const int mp = (members + kMemberPad - 1) / kMemberPad * kMemberPad;
-    return (size_t)(k / 256) * mp * 3 * kPlane;
-}
-size_t batch_operand_sum_floats(int members, int k) {
-    const int mp = (members + kMemberPad - 1) / kMemberPad * kMemberPad;
-    return (size_t)(k / 256) * mp * 16;
+    return (size_t)(k / 256) * mp * (3 * kPlane + 64);
 }
 
 cudaError_t launch_to_batch_operand(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,
@@ -553,34 +602,54 @@ cudaError_t launch_to_batch_operand(cudaStream_t stream, const float* x, const i
     if (e != cudaSuccess) return e;
     const long long warps = (long long)mp * (k / 32);
     batch_digits_kernel<<<(unsigned int)((warps + 7) / 8), 256, 0, stream>>>(x, index, norm_weight, members, mp, k,
-                                                                           out.digit_inv, out.dig, out.sum16);
+                                                                           out.digit_inv, out.chunks);
     return cudaGetLastError();
 }
 
-cudaError_t launch_gemm_imma(cudaStream_t stream, const GemmArgs& args) {
-    if (args.members < 1 || args.members > kMaxMembers || args.k % kTileCols != 0) return cudaErrorInvalidValue;
-    const bool swiglu = args.epilogue == kSwiGLU;
+namespace {
+
+int units_for(const GemmArgs& args, int row_tiles) {
+    if (args.epilogue == kSwiGLU) return (args.seg[0].row_tiles + row_tiles / 2 - 1) / (row_tiles / 2);
     int units = 0;
-    if (swiglu) {
-        if (args.n_segments != 2 || args.seg[0].row_tiles != args.seg[1].row_tiles) return cudaErrorInvalidValue;
-        units = (args.seg[0].row_tiles + kRowTiles / 2 - 1) / (kRowTiles / 2);
-    } else {
-        for (int i = 0; i < args.n_segments; ++i) units += (args.seg[i].row_tiles + kRowTiles - 1) / kRowTiles;
-    }
-    if (units <= 0) return cudaSuccess;
-    const StageLayout lay = layout_for(args);
-    const size_t tail = (size_t)(kRowTiles * kQuadFloats + kCtaRows * kCoefStride) * 4 + 16;
-    const size_t exchange = (size_t)kCtaRows * (kExchStride + kOffStride) * 4;
-    const size_t smem = std::max((size_t)2 * lay.stage_bytes, exchange) + tail;
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_imma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    for (int i = 0; i < args.n_segments; ++i) units += (args.seg[i].row_tiles + row_tiles - 1) / row_tiles;
+    return units;
+}
+
+template <int RT>
+cudaError_t launch_rt(cudaStream_t stream, const GemmArgs& args, int units) {
+    const StageLayout lay = layout_for(args, RT);
+    const size_t smem = smem_for(lay, RT);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_imma_kernel<RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return e;
-        configured = 200 * 1024;
+        configured = true;
     }
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
-    gemm_imma_kernel<<<units, kThreads, smem, stream>>>(args, lay);
+    gemm_imma_kernel<RT><<<units, kThreads, smem, stream>>>(args, lay);
     return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_gemm_imma(cudaStream_t stream, const GemmArgs& args) {
+    if (args.members < 1 || args.members > kMaxMembers || args.k % kTileCols != 0) return cudaErrorInvalidValue;
+    if (args.epilogue == kSwiGLU && (args.n_segments != 2 || args.seg[0].row_tiles != args.seg[1].row_tiles)) {
+        return cudaErrorInvalidValue;
+    }
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+    }
+    const int units4 = units_for(args, 4);
+    if (units4 <= 0) return cudaSuccess;
+    // Four row tiles per CTA reuse each activation chunk most; when that leaves SMs idle and half-size
+    // CTAs still fit in one wave, two row tiles per CTA finish sooner.
+    const int units2 = units_for(args, 2);
+    if (units4 < sm_count && units2 <= sm_count) return launch_rt<2>(stream, args, units2);
+    return launch_rt<4>(stream, args, units4);
 }
 
 }  // namespace ribn

@@ -129,25 +129,23 @@ cudaError_t gemv_prepare();
 
 // ---- batched form (3..64 members) ---------------------------------------------------------------
 // Activations for the batched kernel: one scale per member for its whole vector
-// (x ~= scale * (d1 + d2/128 + d3/16384), |error| <= max|x| * 2.4e-7), digits laid out per k tile
-// so that one bulk copy brings every member's digits of that k tile:
-//   dig[k tile][member][digit][kBatchPlaneBytes]   (256 digits in `operand_position` order + padding
-//                                                   that spreads the members over the shared-memory banks)
-//   sum16[k tile][sub / 4][member][sub % 4]        digit-value sums per 16 inputs `sub` (offset removal)
-//   member_scale[member]                           digit scale, times the RMSNorm factor when a norm precedes
-// Members are padded to a multiple of 8 with zero digits.
+// (x ~= scale * (d1 + d2/128 + d3/16384), |error| <= max|x| * 2.4e-7), stored as one chunk per
+// k tile so that a single bulk copy brings everything the kernel needs for that k tile:
+//   [member][digit][kBatchPlaneBytes]   256 digits in `operand_position` order + padding that spreads
+//                                       the digit planes over the shared-memory banks
+//   [sub / 4][member][sub % 4] F32      digit-value sums per 16 inputs `sub` (offset removal)
+// and, outside the chunks, member_scale[member]: the digit scale, times the RMSNorm factor when a
+// norm precedes.  Members are padded to a multiple of 8 with zero digits.
 constexpr int kBatchPlaneBytes = 288;
 constexpr int kGemmMaxMembers = 64;
 
 struct BatchOperand {
-    signed char* dig = nullptr;
-    float* sum16 = nullptr;
+    signed char* chunks = nullptr;
     float* member_scale = nullptr;  // [members]
     float* digit_inv = nullptr;     // [members] scratch: 127 / max|x|
 };
 
-size_t batch_operand_digit_bytes(int members, int k);
-size_t batch_operand_sum_floats(int members, int k);
+size_t batch_operand_bytes(int members, int k);
 
 // f32 activations [members][k] (rows gathered through `index` when given), optionally times
 // `norm_weight` with the RMSNorm factor folded into member_scale -> batch operand form.
@@ -159,8 +157,7 @@ struct GemmArgs {
     int n_segments;
     int k;
     int members;          // 1..kGemmMaxMembers
-    const signed char* dig;
-    const float* sum16;
+    const signed char* chunks;
     const float* member_scale;
     int epilogue;         // GemvEpilogue; kSwiGLU writes seg[0].y = silu(gate) * up
     int* error_flag;

@@ -148,11 +148,10 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
             // the batched kernel, in groups of up to kGemmMaxMembers members
             BatchOperand bop;
             const int group = std::min(members, kGemmMaxMembers);
-            bop.dig = s.alloc<signed char>(batch_operand_digit_bytes(group, (int)cols));
-            bop.sum16 = s.alloc<float>(batch_operand_sum_floats(group, (int)cols));
+            bop.chunks = s.alloc<signed char>(batch_operand_bytes(group, (int)cols));
             bop.member_scale = s.alloc<float>((size_t)group);
             bop.digit_inv = s.alloc<float>((size_t)group);
-            OP_PTR(bop.dig); OP_PTR(bop.sum16); OP_PTR(bop.member_scale); OP_PTR(bop.digit_inv);
+            OP_PTR(bop.chunks); OP_PTR(bop.member_scale); OP_PTR(bop.digit_inv);
             for (int m0 = 0; m0 < members; m0 += kGemmMaxMembers) {
                 const int m = std::min(kGemmMaxMembers, members - m0);
                 OP_TRY(launch_to_batch_operand(s.stream, d_x + (size_t)m0 * cols, nullptr, nullptr, m, (int)cols, 0.0f, bop));
@@ -162,7 +161,7 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
                                        d_y + (size_t)m0 * rows};
                 a.k = (int)cols;
                 a.members = m;
-                a.dig = bop.dig; a.sum16 = bop.sum16; a.member_scale = bop.member_scale;
+                a.chunks = bop.chunks; a.member_scale = bop.member_scale;
                 a.epilogue = kStore;
                 a.error_flag = d_err;
                 OP_TRY(launch_gemm_imma(s.stream, a));
