@@ -202,15 +202,17 @@ cudaError_t run_layers_decode(ribn_b200_executor* ex, const StepPlan& plan, int&
     cudaStream_t s = ex->stream;
     const int T = plan.n_tokens;
     const bool pdl = !(c.flags & RIBN_B200_FLAG_NO_GRAPH);
-    STEP_TRY(launch_to_operand(s, ex->hidden, nullptr, (const float*)ex->lt(0, kAttnNorm).raw, T, c.hidden,
-                               ex->op_hidden));
-    for (int l = 0; l < c.layers; ++l) {
-        Tensor* t = &ex->lt(l, 0);
+    auto base_args = [&]() {
         GemvArgs a{};
         a.members = T;
         a.eps = c.rms_eps;
         a.error_flag = ex->d_error;
-        // q | k | v from the normalised residual stream
+        return a;
+    };
+    // q | k | v from the normalised residual stream
+    auto qkv_args = [&](int l) {
+        Tensor* t = &ex->lt(l, 0);
+        GemvArgs a = base_args();
         a.n_segments = 3;
         a.seg[0] = segment_of(t[kAttnQ], ex->q);
         a.seg[1] = segment_of(t[kAttnK], ex->k);
@@ -219,7 +221,56 @@ cudaError_t run_layers_decode(ribn_b200_executor* ex, const StepPlan& plan, int&
         a.in = ex->op_hidden;
         a.in_has_norm = 1;
         a.epilogue = kStore;
-        STEP_TRY(launch_gemv_mma(s, a, pdl));
+        return a;
+    };
+    // attention output projection, residual add, operand form of ffn_norm(hidden)
+    auto o_args = [&](int l) {
+        Tensor* t = &ex->lt(l, 0);
+        GemvArgs a = base_args();
+        a.n_segments = 1;
+        a.seg[0] = segment_of(t[kAttnOutput], ex->hidden);
+        a.k = c.q_heads * c.head_dim;
+        a.in = ex->op_attn;
+        a.in_has_norm = 0;
+        a.epilogue = kResidual;
+        a.out = ex->op_hidden;
+        a.out_norm_weight = (const float*)t[kFfnNorm].raw;
+        return a;
+    };
+    // gate | up with the SwiGLU epilogue, operand form of the gated product
+    auto gate_up_args = [&](int l) {
+        Tensor* t = &ex->lt(l, 0);
+        GemvArgs a = base_args();
+        a.n_segments = 2;
+        a.seg[0] = segment_of(t[kFfnGate], ex->gate);
+        a.seg[1] = segment_of(t[kFfnUp], ex->up);
+        a.k = c.hidden;
+        a.in = ex->op_hidden;
+        a.in_has_norm = 1;
+        a.epilogue = kSwiGLU;
+        a.out = ex->op_act;
+        return a;
+    };
+    // down projection, residual add, operand form of the next norm (next layer's or the output norm)
+    auto down_args = [&](int l) {
+        Tensor* t = &ex->lt(l, 0);
+        GemvArgs a = base_args();
+        a.n_segments = 1;
+        a.seg[0] = segment_of(t[kFfnDown], ex->hidden);
+        a.k = c.ffn;
+        a.in = ex->op_act;
+        a.in_has_norm = 0;
+        a.epilogue = kResidual;
+        a.out = ex->op_hidden;
+        a.out_norm_weight = l + 1 < c.layers ? (const float*)ex->lt(l + 1, kAttnNorm).raw : (const float*)ex->output_norm.raw;
+        return a;
+    };
+
+    STEP_TRY(launch_to_operand(s, ex->hidden, nullptr, (const float*)ex->lt(0, kAttnNorm).raw, T, c.hidden,
+                               ex->op_hidden));
+    STEP_TRY(launch_gemv_mma(s, qkv_args(0), pdl));
+    for (int l = 0; l < c.layers; ++l) {
+        Tensor* t = &ex->lt(l, 0);
         __half* ck = ex->cache_k + (long long)l * ex->layer_stride;
         __half* cv = ex->cache_v + (long long)l * ex->layer_stride;
         if (plan.n_rows == T && c.head_dim >= 64) {
@@ -250,42 +301,10 @@ cudaError_t run_layers_decode(ribn_b200_executor* ex, const StepPlan& plan, int&
             if (e != cudaSuccess) return e;
             STEP_TRY(launch_to_operand(s, ex->attn, nullptr, nullptr, T, c.q_heads * c.head_dim, ex->op_attn));
         }
-        // attention output projection, residual add, operand form of ffn_norm(hidden)
-        a = GemvArgs{};
-        a.members = T; a.eps = c.rms_eps; a.error_flag = ex->d_error;
-        a.n_segments = 1;
-        a.seg[0] = segment_of(t[kAttnOutput], ex->hidden);
-        a.k = c.q_heads * c.head_dim;
-        a.in = ex->op_attn;
-        a.in_has_norm = 0;
-        a.epilogue = kResidual;
-        a.out = ex->op_hidden;
-        a.out_norm_weight = (const float*)t[kFfnNorm].raw;
-        STEP_TRY(launch_gemv_mma(s, a, pdl));
-        // gate | up with the SwiGLU epilogue, operand form of the gated product
-        a = GemvArgs{};
-        a.members = T; a.eps = c.rms_eps; a.error_flag = ex->d_error;
-        a.n_segments = 2;
-        a.seg[0] = segment_of(t[kFfnGate], ex->gate);
-        a.seg[1] = segment_of(t[kFfnUp], ex->up);
-        a.k = c.hidden;
-        a.in = ex->op_hidden;
-        a.in_has_norm = 1;
-        a.epilogue = kSwiGLU;
-        a.out = ex->op_act;
-        STEP_TRY(launch_gemv_mma(s, a, pdl));
-        // down projection, residual add, operand form of the next norm (next layer's or the output norm)
-        a = GemvArgs{};
-        a.members = T; a.eps = c.rms_eps; a.error_flag = ex->d_error;
-        a.n_segments = 1;
-        a.seg[0] = segment_of(t[kFfnDown], ex->hidden);
-        a.k = c.ffn;
-        a.in = ex->op_act;
-        a.in_has_norm = 0;
-        a.epilogue = kResidual;
-        a.out = ex->op_hidden;
-        a.out_norm_weight = l + 1 < c.layers ? (const float*)ex->lt(l + 1, kAttnNorm).raw : (const float*)ex->output_norm.raw;
-        STEP_TRY(launch_gemv_mma(s, a, pdl));
+        STEP_TRY(launch_gemv_mma(s, o_args(l), pdl));
+        STEP_TRY(launch_gemv_mma(s, gate_up_args(l), pdl));
+        STEP_TRY(launch_gemv_mma(s, down_args(l), pdl));
+        if (l + 1 < c.layers) STEP_TRY(launch_gemv_mma(s, qkv_args(l + 1), pdl));
     }
     if (plan.n_sample > 0) {
         ActOperand head = ex->op_hidden;  // already normalised with output_norm
@@ -294,8 +313,8 @@ cudaError_t run_layers_decode(ribn_b200_executor* ex, const StepPlan& plan, int&
                                        plan.n_sample, c.hidden, ex->op_head));
             head = ex->op_head;
         }
-        GemvArgs a{};
-        a.members = plan.n_sample; a.eps = c.rms_eps; a.error_flag = ex->d_error;
+        GemvArgs a = base_args();
+        a.members = plan.n_sample;
         a.n_segments = 1;
         a.seg[0] = segment_of(ex->output, ex->logits);
         a.k = c.hidden;

@@ -673,15 +673,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
     }
 
     // ---------------- consumers: a team of eight warps owns whole units; each warp takes one tile per stage ----------------
-    if (threadIdx.x == 0) {
+    if (warp == 0) {
+        // One copy per lane: digit planes, then the two scale arrays.
         const uint32_t plane_bytes = (uint32_t)K, sx_bytes = (uint32_t)MEMBERS * (K / 32) * 4u,
                        sxs_bytes = (uint32_t)MEMBERS * (K / 16) * 4u;
-        mbar_expect_tx(sh.xbar, plane_bytes * (uint32_t)planes + sx_bytes + sxs_bytes);
-        for (int c = 0; c < planes; ++c) {
-            bulk_g2s(smem_u32(sh.xq + (size_t)c * (K + kPlanePad)), a.in.dig + (size_t)c * K, plane_bytes, sh.xbar);
+        if (lane == 0) mbar_expect_tx(sh.xbar, plane_bytes * (uint32_t)planes + sx_bytes + sxs_bytes);
+        __syncwarp();
+        if (lane < planes) {
+            bulk_g2s(smem_u32(sh.xq + (size_t)lane * (K + kPlanePad)), a.in.dig + (size_t)lane * K, plane_bytes, sh.xbar);
+        } else if (lane == planes) {
+            bulk_g2s(smem_u32(sh.sx), a.in.sx, sx_bytes, sh.xbar);
+        } else if (lane == planes + 1) {
+            bulk_g2s(smem_u32(sh.sxs), a.in.sxs16, sxs_bytes, sh.xbar);
         }
-        bulk_g2s(smem_u32(sh.sx), a.in.sx, sx_bytes, sh.xbar);
-        bulk_g2s(smem_u32(sh.sxs), a.in.sxs16, sxs_bytes, sh.xbar);
     }
     bool alive = mbar_wait(sh.xbar, 0, a.error_flag, 2);
     if (RIBN_PROBE >= 2) alive = false;

@@ -232,15 +232,36 @@ __global__ void argmax_kernel(const float* logits, long long length, uint32_t* o
     // Packed (key << 32) | ~index: the maximum picks the largest key and, among
     // equal keys, the smallest index.
     unsigned long long mine = 0ull;
-    for (long long i = threadIdx.x; i < length; i += blockDim.x) {
-        const float v = row[i];
+    auto consider = [&](float v, long long i) {
         if (v == v) {
             const unsigned long long cand =
                 ((unsigned long long)logit_key(v) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)i);
             // A key of 0 cannot occur for a non-NaN value, so `mine == 0` means "none yet".
             if (cand > mine) mine = cand;
         }
+    };
+    long long done = 0;
+    if ((reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
+        // Four independent 128-bit loads per thread and trip keep enough reads in flight for one
+        // block to stream a vocabulary-sized row; the maximum does not depend on the visiting order.
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const long long quads = length / 4, stride = (long long)blockDim.x * 4;
+        for (long long q0 = 0; q0 < quads; q0 += stride) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const long long q = q0 + (long long)u * blockDim.x + threadIdx.x;
+                v[u] = q < quads ? row4[q] : make_float4(NAN, NAN, NAN, NAN);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const long long i = (q0 + (long long)u * blockDim.x + threadIdx.x) * 4;
+                consider(v[u].x, i); consider(v[u].y, i + 1); consider(v[u].z, i + 2); consider(v[u].w, i + 3);
+            }
+        }
+        done = quads * 4;
     }
+    for (long long i = done + threadIdx.x; i < length; i += blockDim.x) consider(row[i], i);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const unsigned long long other = __shfl_xor_sync(0xffffffffu, mine, o);
