@@ -179,6 +179,10 @@ def oracle_sequence(orc, oracle, ex, model, sequence: int, context: int):
     return seq
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate|up launch of gemv_mma_kernel (ncu capture).
+GATE_UP_DRAM_BYTES = {"qwen3-8b": 56982272, "qwen3-8b-4l": 56982272}
+
+
 def run_ours(args):
     rank, world, local, dist = dist_setup(args.gpus)
     import ribn_b200
@@ -230,14 +234,30 @@ def run_ours(args):
         dev = all_max(dist, sum(device_ms) / 1e3, local)
         return wall, dev, launches, clocks.summary()
 
-    def roofline(batch_rows, dev_seconds):
+    def step_roofline(batch_rows, dev_seconds):
+        """Whole step: algorithmic bytes of one decode step over its device time (every kernel included)."""
         ctx_avg = args.context + args.warmup + args.steps / 2.0
         w_bytes, kv_bytes = ex.step_bytes(int(batch_rows * ctx_avg))
         per_step = w_bytes + kv_bytes
         achieved = per_step / (dev_seconds / args.steps) / 1e9
         return {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
-                "traffic": None, "of": peak_kind, "kernel": "whole decode step (every kernel of the step)",
-                "algorithmic_bytes_per_step": per_step, "weight_bytes": w_bytes, "kv_bytes": kv_bytes}
+                "of": peak_kind, "algorithmic_bytes_per_step": per_step, "weight_bytes": w_bytes, "kv_bytes": kv_bytes}
+
+    def kernel_roofline():
+        """The dominant kernel (gemv_mma_kernel, ~80 % of a batch-1 step) on its largest per-layer launch,
+        ffn gate|up: encoded weight bytes of one launch over its CUDA-event duration, timed live here."""
+        us, nbytes = ex.time_projection("gate_up", repeats=4 * model["layers"])
+        others = {}
+        for name in ("qkv", "attn_output", "down", "head"):
+            t_us, b = ex.time_projection(name, repeats=(8 if name == "head" else 2 * model["layers"]))
+            others[name] = {"us": t_us, "bytes": b, "GB/s": b / t_us / 1e3}
+        achieved = nbytes / us / 1e3
+        # DRAM bytes of the same launch from the ncu capture summarised in profiles/gemv_mma_gate_up_qwen3-8b.md
+        traffic = GATE_UP_DRAM_BYTES.get(args.model)
+        return {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
+                "traffic": traffic, "of": peak_kind,
+                "kernel": "gemv_mma_kernel, ffn gate|up launch (2 x ffn x hidden Q4_K, 1 row)",
+                "algorithmic_bytes_per_launch": nbytes, "us_per_launch": us, "other_launches": others}
 
     # ---- batch 1 -----------------------------------------------------------------------
     wall1, dev1, launches1, clocks1 = phase([1])
@@ -247,14 +267,15 @@ def run_ours(args):
         "metric": f"{args.model} Q4_K_M decode tok/s at batch 1 (per GPU x replicas)", "value": value1,
         "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dev1 / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32 activations / f16 tensor-core operands over Q4_K,Q6_K weights, f16 KV",
+        "dtype": "u8 x s8 integer tensor-core products over Q4_K,Q6_K weights, f32 block scales and accumulation, f16 KV",
         "data": "synthetic",
         "config": {"workload": f"{args.model} Q4_K_M-style decode, batch 1 and {B}, context {args.context}, "
                                f"16-token KV pages, one replica per GPU",
                    "l2": "inputs larger than L2 (4.9 GB of weights streamed per step)",
                    "parallelism": f"replicas x{world}"},
         "e2e": {"value": e2e1, "unit": "tok/s", "h2d_bytes_per_step": 32, "d2h_bytes_per_step": 4},
-        "gpu_launches": launches1, "roofline": roofline(1, dev1), "clocks": clocks1,
+        "gpu_launches": launches1, "roofline": kernel_roofline(), "step_roofline": step_roofline(1, dev1),
+        "clocks": clocks1,
     }
     if cpu:
         out["cpu_baseline"] = cpu
@@ -266,7 +287,7 @@ def run_ours(args):
                           "ms_per_step": devb / args.steps * 1e3,
                           "e2e": {"value": world * B * args.steps / wallb, "unit": "tok/s",
                                   "h2d_bytes_per_step": 32 * B, "d2h_bytes_per_step": 4 * B},
-                          "gpu_launches": launchesb, "roofline": roofline(B, devb), "clocks": clocksb,
+                          "gpu_launches": launchesb, "step_roofline": step_roofline(B, devb), "clocks": clocksb,
                           "x_batch1": (world * B * args.steps / devb) / value1}
     ex.close()
     if rank == 0:

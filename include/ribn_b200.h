@@ -210,6 +210,16 @@ RIBN_B200_API int ribn_b200_last_step_stats(ribn_b200_executor* executor, float*
 RIBN_B200_API int ribn_b200_step_bytes(ribn_b200_executor* executor, uint64_t context_tokens_total,
                                        uint64_t* weight_bytes, uint64_t* kv_bytes);
 
+/* Measurement aid: enqueue `repeats` launches of one of the decode step's projection kernels for a
+ * single row (which: 0 = q|k|v, 1 = attention output, 2 = gate|up, 3 = down, 4 = output head),
+ * launch r on layer r % layers so that every launch streams its weights from HBM, and report the
+ * average device time per launch from CUDA events on the executor's stream together with the
+ * encoded weight bytes one launch reads.  Overwrites the step's activation buffers; call it only
+ * between steps.  Counterpart of the reference's device-side kernel timing loop in
+ * crates/nvidia/examples/qwen_decode_bench.rs. */
+RIBN_B200_API int ribn_b200_time_projection(ribn_b200_executor* executor, int32_t which, uint32_t repeats,
+                                            float* average_us, uint64_t* bytes_per_launch);
+
 /* ---- single operators (host pointers in, host pointers out) ------------- */
 /* Each runs the same device kernels the executor uses, on `device`, and is
  * what the per-primitive parity tests call.  They replace the operator

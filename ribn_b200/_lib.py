@@ -66,6 +66,7 @@ SIGNATURES = {
     "ribn_b200_debug_set_context": (C.c_int, [_P, C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint64]),
     "ribn_b200_last_step_stats": (C.c_int, [_P, C.POINTER(C.c_float), C.POINTER(C.c_uint32)]),
     "ribn_b200_step_bytes": (C.c_int, [_P, C.c_uint64, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "ribn_b200_time_projection": (C.c_int, [_P, C.c_int32, C.c_uint32, C.POINTER(C.c_float), C.POINTER(C.c_uint64)]),
     "ribn_b200_op_dequantize": (C.c_int, [C.c_int32, C.c_int32, _P, C.c_int64, C.c_int64, _P]),
     "ribn_b200_op_gemv": (C.c_int, [C.c_int32, C.c_int32, _P, C.c_int64, C.c_int64, _P, C.c_int32, _P, C.c_int32]),
     "ribn_b200_op_rms_norm": (C.c_int, [C.c_int32, _P, _P, C.c_int32, C.c_int32, C.c_float, _P]),

@@ -197,78 +197,91 @@ GemvSegment segment_of(const Tensor& t, float* y) {
     return GemvSegment{t.packed.data, t.type, (int)t.rows, t.packed.row_tiles, y};
 }
 
+// The decode step's projections as GEMV arguments (T = 1 or 2 rows).
+GemvArgs base_args(ribn_b200_executor* ex, int T) {
+    GemvArgs a{};
+    a.members = T;
+    a.eps = ex->cfg.rms_eps;
+    a.error_flag = ex->d_error;
+    return a;
+}
+// q | k | v from the normalised residual stream
+GemvArgs qkv_args(ribn_b200_executor* ex, int l, int T) {
+    Tensor* t = &ex->lt(l, 0);
+    GemvArgs a = base_args(ex, T);
+    a.n_segments = 3;
+    a.seg[0] = segment_of(t[kAttnQ], ex->q);
+    a.seg[1] = segment_of(t[kAttnK], ex->k);
+    a.seg[2] = segment_of(t[kAttnV], ex->v);
+    a.k = ex->cfg.hidden;
+    a.in = ex->op_hidden;
+    a.in_has_norm = 1;
+    a.epilogue = kStore;
+    return a;
+}
+// attention output projection, residual add, operand form of ffn_norm(hidden)
+GemvArgs o_args(ribn_b200_executor* ex, int l, int T) {
+    Tensor* t = &ex->lt(l, 0);
+    GemvArgs a = base_args(ex, T);
+    a.n_segments = 1;
+    a.seg[0] = segment_of(t[kAttnOutput], ex->hidden);
+    a.k = ex->cfg.q_heads * ex->cfg.head_dim;
+    a.in = ex->op_attn;
+    a.in_has_norm = 0;
+    a.epilogue = kResidual;
+    a.out = ex->op_hidden;
+    a.out_norm_weight = (const float*)t[kFfnNorm].raw;
+    return a;
+}
+// gate | up with the SwiGLU epilogue, operand form of the gated product
+GemvArgs gate_up_args(ribn_b200_executor* ex, int l, int T) {
+    Tensor* t = &ex->lt(l, 0);
+    GemvArgs a = base_args(ex, T);
+    a.n_segments = 2;
+    a.seg[0] = segment_of(t[kFfnGate], ex->gate);
+    a.seg[1] = segment_of(t[kFfnUp], ex->up);
+    a.k = ex->cfg.hidden;
+    a.in = ex->op_hidden;
+    a.in_has_norm = 1;
+    a.epilogue = kSwiGLU;
+    a.out = ex->op_act;
+    return a;
+}
+// down projection, residual add, operand form of the next norm (next layer's or the output norm)
+GemvArgs down_args(ribn_b200_executor* ex, int l, int T) {
+    const ribn_b200_config& c = ex->cfg;
+    Tensor* t = &ex->lt(l, 0);
+    GemvArgs a = base_args(ex, T);
+    a.n_segments = 1;
+    a.seg[0] = segment_of(t[kFfnDown], ex->hidden);
+    a.k = c.ffn;
+    a.in = ex->op_act;
+    a.in_has_norm = 0;
+    a.epilogue = kResidual;
+    a.out = ex->op_hidden;
+    a.out_norm_weight = l + 1 < c.layers ? (const float*)ex->lt(l + 1, kAttnNorm).raw : (const float*)ex->output_norm.raw;
+    return a;
+}
+// output head over `rows` already normalised rows
+GemvArgs head_args(ribn_b200_executor* ex, int rows, const ActOperand& in) {
+    GemvArgs a = base_args(ex, rows);
+    a.n_segments = 1;
+    a.seg[0] = segment_of(ex->output, ex->logits);
+    a.k = ex->cfg.hidden;
+    a.in = in;
+    a.in_has_norm = 1;
+    a.epilogue = kStore;
+    return a;
+}
+
 cudaError_t run_layers_decode(ribn_b200_executor* ex, const StepPlan& plan, int& launches) {
     const ribn_b200_config& c = ex->cfg;
     cudaStream_t s = ex->stream;
     const int T = plan.n_tokens;
     const bool pdl = !(c.flags & RIBN_B200_FLAG_NO_GRAPH);
-    auto base_args = [&]() {
-        GemvArgs a{};
-        a.members = T;
-        a.eps = c.rms_eps;
-        a.error_flag = ex->d_error;
-        return a;
-    };
-    // q | k | v from the normalised residual stream
-    auto qkv_args = [&](int l) {
-        Tensor* t = &ex->lt(l, 0);
-        GemvArgs a = base_args();
-        a.n_segments = 3;
-        a.seg[0] = segment_of(t[kAttnQ], ex->q);
-        a.seg[1] = segment_of(t[kAttnK], ex->k);
-        a.seg[2] = segment_of(t[kAttnV], ex->v);
-        a.k = c.hidden;
-        a.in = ex->op_hidden;
-        a.in_has_norm = 1;
-        a.epilogue = kStore;
-        return a;
-    };
-    // attention output projection, residual add, operand form of ffn_norm(hidden)
-    auto o_args = [&](int l) {
-        Tensor* t = &ex->lt(l, 0);
-        GemvArgs a = base_args();
-        a.n_segments = 1;
-        a.seg[0] = segment_of(t[kAttnOutput], ex->hidden);
-        a.k = c.q_heads * c.head_dim;
-        a.in = ex->op_attn;
-        a.in_has_norm = 0;
-        a.epilogue = kResidual;
-        a.out = ex->op_hidden;
-        a.out_norm_weight = (const float*)t[kFfnNorm].raw;
-        return a;
-    };
-    // gate | up with the SwiGLU epilogue, operand form of the gated product
-    auto gate_up_args = [&](int l) {
-        Tensor* t = &ex->lt(l, 0);
-        GemvArgs a = base_args();
-        a.n_segments = 2;
-        a.seg[0] = segment_of(t[kFfnGate], ex->gate);
-        a.seg[1] = segment_of(t[kFfnUp], ex->up);
-        a.k = c.hidden;
-        a.in = ex->op_hidden;
-        a.in_has_norm = 1;
-        a.epilogue = kSwiGLU;
-        a.out = ex->op_act;
-        return a;
-    };
-    // down projection, residual add, operand form of the next norm (next layer's or the output norm)
-    auto down_args = [&](int l) {
-        Tensor* t = &ex->lt(l, 0);
-        GemvArgs a = base_args();
-        a.n_segments = 1;
-        a.seg[0] = segment_of(t[kFfnDown], ex->hidden);
-        a.k = c.ffn;
-        a.in = ex->op_act;
-        a.in_has_norm = 0;
-        a.epilogue = kResidual;
-        a.out = ex->op_hidden;
-        a.out_norm_weight = l + 1 < c.layers ? (const float*)ex->lt(l + 1, kAttnNorm).raw : (const float*)ex->output_norm.raw;
-        return a;
-    };
-
     STEP_TRY(launch_to_operand(s, ex->hidden, nullptr, (const float*)ex->lt(0, kAttnNorm).raw, T, c.hidden,
                                ex->op_hidden));
-    STEP_TRY(launch_gemv_mma(s, qkv_args(0), pdl));
+    STEP_TRY(launch_gemv_mma(s, qkv_args(ex, 0, T), pdl));
     for (int l = 0; l < c.layers; ++l) {
         Tensor* t = &ex->lt(l, 0);
         __half* ck = ex->cache_k + (long long)l * ex->layer_stride;
@@ -301,10 +314,10 @@ cudaError_t run_layers_decode(ribn_b200_executor* ex, const StepPlan& plan, int&
             if (e != cudaSuccess) return e;
             STEP_TRY(launch_to_operand(s, ex->attn, nullptr, nullptr, T, c.q_heads * c.head_dim, ex->op_attn));
         }
-        STEP_TRY(launch_gemv_mma(s, o_args(l), pdl));
-        STEP_TRY(launch_gemv_mma(s, gate_up_args(l), pdl));
-        STEP_TRY(launch_gemv_mma(s, down_args(l), pdl));
-        if (l + 1 < c.layers) STEP_TRY(launch_gemv_mma(s, qkv_args(l + 1), pdl));
+        STEP_TRY(launch_gemv_mma(s, o_args(ex, l, T), pdl));
+        STEP_TRY(launch_gemv_mma(s, gate_up_args(ex, l, T), pdl));
+        STEP_TRY(launch_gemv_mma(s, down_args(ex, l, T), pdl));
+        if (l + 1 < c.layers) STEP_TRY(launch_gemv_mma(s, qkv_args(ex, l + 1, T), pdl));
     }
     if (plan.n_sample > 0) {
         ActOperand head = ex->op_hidden;  // already normalised with output_norm
@@ -313,14 +326,7 @@ cudaError_t run_layers_decode(ribn_b200_executor* ex, const StepPlan& plan, int&
                                        plan.n_sample, c.hidden, ex->op_head));
             head = ex->op_head;
         }
-        GemvArgs a = base_args();
-        a.members = plan.n_sample;
-        a.n_segments = 1;
-        a.seg[0] = segment_of(ex->output, ex->logits);
-        a.k = c.hidden;
-        a.in = head;
-        a.in_has_norm = 1;
-        a.epilogue = kStore;
+        const GemvArgs a = head_args(ex, plan.n_sample, head);
         STEP_TRY(launch_gemv_mma(s, a, pdl));
     }
     return cudaSuccess;
@@ -1121,6 +1127,46 @@ int ribn_b200_step_bytes(ribn_b200_executor* ex, uint64_t context_tokens_total, 
     w += ex->output_norm.bytes + ex->output.bytes;
     if (weight_bytes) *weight_bytes = w;
     if (kv_bytes) *kv_bytes = context_tokens_total * (uint64_t)c.layers * 2ull * c.kv_heads * c.head_dim * 2ull;
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_time_projection(ribn_b200_executor* ex, int32_t which, uint32_t repeats, float* average_us,
+                              uint64_t* bytes_per_launch) {
+    if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    if (!ex->finalized || ex->pending.active) return fail(ex, "time_projection: executor not idle");
+    if (!packed_family_applies(ex) || repeats == 0 || average_us == nullptr) return fail(ex, "time_projection: unavailable");
+    const ribn_b200_config& c = ex->cfg;
+    cudaStream_t s = ex->stream;
+    auto args_for = [&](int l) {
+        switch (which) {
+            case 0: return qkv_args(ex, l, 1);
+            case 1: return o_args(ex, l, 1);
+            case 2: return gate_up_args(ex, l, 1);
+            case 3: return down_args(ex, l, 1);
+            default: return head_args(ex, 1, ex->op_hidden);
+        }
+    };
+    if (which < 0 || which > 4) return fail(ex, "time_projection: which must be 0..4");
+    uint64_t bytes = 0;
+    {
+        const GemvArgs a = args_for(0);
+        for (int i = 0; i < a.n_segments; ++i) {
+            bytes += (uint64_t)a.seg[i].row_tiles * (uint64_t)(a.k / kTileCols) * (uint64_t)packed_tile_bytes(a.seg[i].type);
+        }
+    }
+    if (bytes_per_launch) *bytes_per_launch = bytes;
+    // Launch r takes layer r % layers, so consecutive launches read different weights from HBM.
+    for (int warm = 0; warm < 3; ++warm) CU_TRY(ex, launch_gemv_mma(s, args_for(warm % c.layers), true));
+    CU_TRY(ex, cudaEventRecord(ex->ev_start, s));
+    for (uint32_t r = 0; r < repeats; ++r) CU_TRY(ex, launch_gemv_mma(s, args_for((int)(r % (uint32_t)c.layers)), true));
+    CU_TRY(ex, cudaEventRecord(ex->ev_done, s));
+    CU_TRY(ex, cudaEventSynchronize(ex->ev_done));
+    float ms = 0.0f;
+    CU_TRY(ex, cudaEventElapsedTime(&ms, ex->ev_start, ex->ev_done));
+    *average_us = ms * 1000.0f / (float)repeats;
+    int err = 0;
+    CU_TRY(ex, cudaMemcpy(&err, ex->d_error, sizeof(int), cudaMemcpyDeviceToHost));
+    if (err != 0) return fail(ex, "time_projection: a bounded wait inside the kernel expired (code %d)", err);
     return RIBN_B200_OK;
 }
 

@@ -225,6 +225,17 @@ class QwenB200:
         self._check(lib().ribn_b200_step_bytes(self._h, context_tokens_total, C.byref(w), C.byref(kv)))
         return w.value, kv.value
 
+    PROJECTIONS = {"qkv": 0, "attn_output": 1, "gate_up": 2, "down": 3, "head": 4}
+
+    def time_projection(self, which: str, repeats: int = 72):
+        """Average device microseconds per launch of one decode projection kernel (one row, weights
+        streamed from HBM: consecutive launches take consecutive layers) and the encoded bytes a
+        launch reads.  Only between steps: it overwrites the step's activation buffers."""
+        us, nbytes = C.c_float(), C.c_uint64()
+        self._check(lib().ribn_b200_time_projection(self._h, self.PROJECTIONS[which], repeats, C.byref(us),
+                                                    C.byref(nbytes)))
+        return us.value, nbytes.value
+
     def close(self) -> None:
         if self._h:
             lib().ribn_b200_destroy(self._h)
