@@ -92,33 +92,49 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.samples)}
 
 
-def dist_setup(n_gpus: int):
+def dist_setup(n_gpus: int, backend: str = "nccl"):
+    """One process per GPU (torchrun's RANK / LOCAL_RANK / WORLD_SIZE / MASTER_*).  Replicas exchange
+    nothing on the data path; the process group only carries the barrier and the max-over-ranks of
+    the timings.  `backend="gloo"` runs the same plumbing on CPU ranks (host-side tests)."""
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
         import torch
         import torch.distributed as dist
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        if backend == "nccl":
+            torch.cuda.set_device(local)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        else:
+            dist.init_process_group(backend)
         return rank, world, local, dist
     return rank, world, local, None
+
+
+def _on_gpu(dist) -> bool:
+    return dist is not None and dist.get_backend() == "nccl"
 
 
 def all_max(dist, value: float, device: int) -> float:
     if dist is None:
         return value
     import torch
-    t = torch.tensor([value], dtype=torch.float64, device=f"cuda:{device}")
+    t = torch.tensor([value], dtype=torch.float64, device=f"cuda:{device}" if _on_gpu(dist) else "cpu")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
 
 
 def barrier(dist, device: int):
     if dist is not None:
-        import torch
         dist.barrier()
-        torch.cuda.synchronize(device)
+        if _on_gpu(dist):
+            import torch
+            torch.cuda.synchronize(device)
+
+
+def replica_throughput(dist, world: int, rows: int, steps: int, seconds: float, device: int) -> float:
+    """Whole-job tokens per second of `world` independent replicas: all ranks' tokens over the slowest rank's time."""
+    return world * rows * steps / all_max(dist, seconds, device)
 
 
 def build_executor(model: dict, batch: int, context: int, decode_tokens: int, device: int, keep_logits: bool):
@@ -232,7 +248,7 @@ def run_ours(args):
         barrier(dist, local)
         wall = all_max(dist, wall, local)
         dev = all_max(dist, sum(device_ms) / 1e3, local)
-        return wall, dev, launches, clocks.summary()
+        return wall, dev, launches, clocks.summary()  # both already the maximum over ranks
 
     def step_roofline(batch_rows, dev_seconds):
         """Whole step: algorithmic bytes of one decode step over its device time (every kernel included)."""
@@ -261,7 +277,7 @@ def run_ours(args):
 
     # ---- batch 1 -----------------------------------------------------------------------
     wall1, dev1, launches1, clocks1 = phase([1])
-    value1 = world * 1 * args.steps / dev1
+    value1 = world * 1 * args.steps / dev1   # dev1 / wall1 are already the maximum over ranks
     e2e1 = world * 1 * args.steps / wall1
     out = {
         "metric": f"{args.model} Q4_K_M decode tok/s at batch 1 (per GPU x replicas)", "value": value1,
