@@ -84,7 +84,8 @@ enum {
     RIBN_B200_FLAG_KEEP_LOGITS = 1,   /* keep F32 logits of sampling rows for copy_logits */
     RIBN_B200_FLAG_REFERENCE_KERNELS = 2, /* run the plain one-warp-per-row CUDA kernels
                                              (slow; used to cross-check the fast path) */
-    RIBN_B200_FLAG_NO_GRAPH = 4       /* launch kernels directly instead of replaying graphs */
+    RIBN_B200_FLAG_NO_GRAPH = 4,      /* launch kernels directly instead of replaying graphs */
+    RIBN_B200_FLAG_NO_TCGEN05 = 8     /* batches of 3+ rows on the integer mma.sync kernel instead of tcgen05 */
 };
 
 /* GenerationLimits (crates/runtime/src/executor.rs:43-51). */
@@ -236,7 +237,8 @@ RIBN_B200_API int ribn_b200_op_dequantize(int32_t device, int32_t ggml_type, con
 /* y[m][n] = sum_k deq(W[n][k]) x[m][k] (CudaQuantizedGemv::execute_warp /
  * gemv_batch, crates/nvidia/src/quantized.rs:303-436).  variant 0 = fast
  * GEMV kernels (members in pairs), 1 = one-warp-per-row reference kernels,
- * 2 = the batched tensor-core kernel (up to 64 members per launch). */
+ * 2 = the batched integer tensor-core kernel (up to 64 members per launch),
+ * 3 = the tcgen05 / tensor-memory dequant-GEMM (up to 128 members per launch). */
 RIBN_B200_API int ribn_b200_op_gemv(int32_t device, int32_t ggml_type, const void* weights,
                                     int64_t rows, int64_t cols, const float* x, int32_t members,
                                     float* y, int32_t variant);

@@ -11,7 +11,7 @@ F32, F16, Q8_0, Q4_K, Q6_K = 0, 1, 8, 12, 14
 OK, PENDING, REJECTED, DEFERRED, ERROR = 0, 1, 2, 3, -1
 PREFILL, DECODE = 0, 1
 SCHEME_Q8_0, SCHEME_Q4_K_M = 0, 1
-FLAG_KEEP_LOGITS, FLAG_REFERENCE_KERNELS, FLAG_NO_GRAPH = 1, 2, 4
+FLAG_KEEP_LOGITS, FLAG_REFERENCE_KERNELS, FLAG_NO_GRAPH, FLAG_NO_TCGEN05 = 1, 2, 4, 8
 
 
 class Config(C.Structure):

@@ -338,12 +338,10 @@ cudaError_t batch_project(ribn_b200_executor* ex, int& launches, const float* x,
                           const float* norm_weight, int tokens, int k, const Tensor* const* mats, float* const* ys,
                           int n_mats, int epilogue) {
     cudaStream_t s = ex->stream;
-    for (int base = 0; base < tokens; base += kGemmMaxMembers) {
-        const int m = std::min(kGemmMaxMembers, tokens - base);
-        cudaError_t e = launch_to_batch_operand(s, index ? x : x + (size_t)base * k, index ? index + base : nullptr,
-                                                norm_weight, m, k, ex->cfg.rms_eps, ex->op_batch);
-        if (e != cudaSuccess) return e;
-        launches += 2;
+    const bool tensor_memory = !(ex->cfg.flags & RIBN_B200_FLAG_NO_TCGEN05);
+    const int group = tensor_memory ? kGemmTcMaxMembers : kGemmMaxMembers;
+    for (int base = 0; base < tokens; base += group) {
+        const int m = std::min(group, tokens - base);
         GemmArgs a{};
         a.n_segments = n_mats;
         for (int i = 0; i < n_mats; ++i) {
@@ -352,11 +350,32 @@ cudaError_t batch_project(ribn_b200_executor* ex, int& launches, const float* x,
         }
         a.k = k;
         a.members = m;
-        a.chunks = ex->op_batch.chunks;
-        a.member_scale = ex->op_batch.member_scale;
-        a.epilogue = epilogue;
         a.error_flag = ex->d_error;
-        STEP_TRY(launch_gemm_imma(s, a));
+        if (tensor_memory) {
+            // tcgen05 dequant-GEMM; SwiGLU runs as a separate elementwise pass over gate and up
+            cudaError_t e = launch_to_tc_operand(s, index ? x : x + (size_t)base * k, index ? index + base : nullptr,
+                                                 norm_weight, m, k, ex->cfg.rms_eps, ex->op_tc);
+            if (e != cudaSuccess) return e;
+            launches += 2;
+            a.chunks = (const signed char*)ex->op_tc.chunks;
+            a.member_scale = ex->op_tc.member_scale;
+            a.epilogue = epilogue == kSwiGLU ? kStore : epilogue;
+            STEP_TRY(launch_gemm_tc(s, a));
+            if (epilogue == kSwiGLU) {
+                float* gate = ys[0] + (size_t)base * mats[0]->rows;
+                float* up = ys[1] + (size_t)base * mats[1]->rows;
+                STEP_TRY(launch_silu_mul(s, gate, up, (long long)m * mats[0]->rows, gate));
+            }
+        } else {
+            cudaError_t e = launch_to_batch_operand(s, index ? x : x + (size_t)base * k, index ? index + base : nullptr,
+                                                    norm_weight, m, k, ex->cfg.rms_eps, ex->op_batch);
+            if (e != cudaSuccess) return e;
+            launches += 2;
+            a.chunks = ex->op_batch.chunks;
+            a.member_scale = ex->op_batch.member_scale;
+            a.epilogue = epilogue;
+            STEP_TRY(launch_gemm_imma(s, a));
+        }
     }
     return cudaSuccess;
 }
@@ -760,6 +779,9 @@ int ribn_b200_finalize(ribn_b200_executor* ex) {
             const int kmax = std::max(std::max(c.hidden, c.ffn), c.q_heads * c.head_dim);
             if (kmax % 256 == 0) {
                 CU_TRY(ex, dev_alloc(ex, &ex->op_batch.chunks, batch_operand_bytes(kGemmMaxMembers, kmax)));
+                CU_TRY(ex, dev_alloc(ex, (unsigned char**)&ex->op_tc.chunks, tc_operand_bytes(kGemmTcMaxMembers, kmax)));
+                CU_TRY(ex, dev_alloc(ex, &ex->op_tc.scale_in, kGemmTcMaxMembers));
+                CU_TRY(ex, dev_alloc(ex, &ex->op_tc.member_scale, kGemmTcMaxMembers));
                 CU_TRY(ex, dev_alloc(ex, &ex->op_batch.member_scale, kGemmMaxMembers));
                 CU_TRY(ex, dev_alloc(ex, &ex->op_batch.digit_inv, kGemmMaxMembers));
             }

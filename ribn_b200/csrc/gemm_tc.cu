@@ -1,0 +1,552 @@
+// Dequant-GEMM on the 5th-generation tensor cores (tcgen05 + TMEM) for batches of 3..128 rows:
+// chunked prefill and batched decode.
+//
+//   y[m][n] = sum_k deq(W[n][k]) x[m][k]
+//
+// The weights stay in their tile-major GGUF repack (16 rows x 256 inputs per tile).  A CTA owns
+// 128 output rows at a time and walks K:
+//   * a producer warp brings the 8 packed tiles of a k tile (bulk copies) and, per 64 inputs, the
+//     activations' operand chunk into shared-memory rings;
+//   * eight dequant warps decode the blocks with the reference's own arithmetic
+//     (w = fl(fl(d * sc) * q) - fl(dmin * m) for Q4_K, two products for Q6_K, one for Q8_0) and split
+//     every F32 weight into two binary16 numbers hi + lo (22 significant bits), stored in the
+//     K-major core-matrix layout `tcgen05.mma` reads;
+//   * one thread issues `tcgen05.mma.kind::f16`: hi x [x_hi | x_lo] and lo x x_hi, F32 accumulation
+//     over the whole K in tensor memory (activations are likewise hi + lo pairs scaled per row by a
+//     power of two, so no product or sum is rounded below F32);
+//   * four epilogue warps read the accumulators back with `tcgen05.ld`, add the two column halves,
+//     apply the row scale (and RMSNorm factor) and store or add into the residual stream, while
+//     the next 128 rows already accumulate in the other half of tensor memory.
+// Every column (batch row) is computed independently of the others and every sum has a fixed
+// order: a row's result does not depend on what it is batched with.  All waits are bounded and
+// raise the caller's error word.
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
+#include "blocks.cuh"
+#include "gemv.cuh"
+
+namespace ribn {
+
+namespace {
+
+constexpr int kRows = 128;                 // output rows per unit (UMMA M)
+constexpr int kRowTilesPerUnit = kRows / kTileRows;
+constexpr int kChunkK = 64;                // inputs per operand chunk
+constexpr int kChunksPerTile = kTileCols / kChunkK;
+constexpr int kEpilogueWarps = 4;          // warps 0..3: TMEM lane quadrant = warp index
+constexpr int kProducerWarp = 4;
+constexpr int kMmaWarp = 5;
+constexpr int kDequantWarp0 = 6;
+constexpr int kDequantWarps = kRowTilesPerUnit;
+constexpr int kThreads = (kDequantWarp0 + kDequantWarps) * 32;
+constexpr int kAHalfBytes = kRows * kChunkK * 2;   // one of hi / lo for a chunk: 16 KB
+constexpr int kABytes = 2 * kAHalfBytes;
+constexpr int kALbo = (kRows / 8) * 128;           // bytes between the 8-input column blocks of A
+constexpr int kTmemCols = 512;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait; on expiry raises the error word and reports false (the caller stops waiting but
+// keeps arriving, so nobody else is left hanging on it).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (error_flag != nullptr) atomicExch(error_flag, code);
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// ---- tcgen05 ---------------------------------------------------------------------------------
+// Shared-memory operand descriptor, K-major, no swizzle: 8 rows x 16 bytes core matrices; `lbo` =
+// bytes between the two 8-element column blocks of one MMA's K = 16, `sbo` = bytes between
+// successive groups of 8 rows.  Bits 46..47 carry the descriptor version (1).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+}
+// Instruction descriptor for kind::f16: F32 accumulate, F16 x F16, both operands K-major, M = 128.
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// ---- dequant to hi + lo binary16 ---------------------------------------------------------------
+// Four consecutive inputs of one row: 8 bytes into the hi plane and 8 into the lo plane.
+__device__ __forceinline__ void store_split4(unsigned char* hi, float w0, float w1, float w2, float w3) {
+    const __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
+    const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+    const __half2 l01 = __floats2half2_rn(w0 - f01.x, w1 - f01.y), l23 = __floats2half2_rn(w2 - f23.x, w3 - f23.y);
+    uint2 a, b;
+    a.x = *reinterpret_cast<const uint32_t*>(&h01); a.y = *reinterpret_cast<const uint32_t*>(&h23);
+    b.x = *reinterpret_cast<const uint32_t*>(&l01); b.y = *reinterpret_cast<const uint32_t*>(&l23);
+    *reinterpret_cast<uint2*>(hi) = a;
+    *reinterpret_cast<uint2*>(hi + kAHalfBytes) = b;
+}
+// Byte offset inside a hi (or lo) plane of input k0 (multiple of 4) of row `r` of the unit.
+__device__ __forceinline__ int a_offset(int r, int k0) { return (k0 >> 3) * kALbo + (r >> 3) * 128 + (r & 7) * 16 + (k0 & 7) * 2; }
+
+__device__ __forceinline__ float byte_of(uint32_t w, int i) { return (float)((w >> (8 * i)) & 0xffu); }
+
+// One 64-input chunk `c` of one packed tile -> rows [row0, row0 + 16) of the A chunk.
+// Lane (g, t) holds rows g and g + 8; the tile's byte order is that of the GEMV kernel's MMA fragments.
+__device__ __forceinline__ void dequant_chunk(int type, const unsigned char* tile, int c, unsigned char* a_hi, int row0, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    if (type == kQ4_K) {
+        const uint4 w = *reinterpret_cast<const uint4*>(tile + c * 512 + lane * 16);
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            const int row = g + 8 * rr;
+            const uint4 h = *reinterpret_cast<const uint4*>(tile + 2048 + row * 16);
+            const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
+            const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
+            const uint32_t sc4 = c < 2 ? (h.y & 0x3F3F3F3Fu) : ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u));
+            const uint32_t mn4 = c < 2 ? (h.z & 0x3F3F3F3Fu) : (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u));
+            const int b0 = (2 * c) & 3;  // byte of the even group inside its half
+            const float gs_e = __fmul_rn(d, byte_of(sc4, b0)), gs_o = __fmul_rn(d, byte_of(sc4, b0 + 1));
+            const float gm_e = __fmul_rn(dmin, byte_of(mn4, b0)), gm_o = __fmul_rn(dmin, byte_of(mn4, b0 + 1));
+            const uint32_t lo16 = rr == 0 ? w.x : w.z, hi16 = rr == 0 ? w.y : w.w;  // inputs 4t.. and 16 + 4t.. of both groups
+            unsigned char* base = a_hi + a_offset(row0 + row, 0);
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+                const uint32_t word = part == 0 ? lo16 : hi16;
+                float e[4], o[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t byte = (word >> (8 * i)) & 0xffu;
+                    e[i] = __fsub_rn(__fmul_rn(gs_e, (float)(byte & 15u)), gm_e);
+                    o[i] = __fsub_rn(__fmul_rn(gs_o, (float)(byte >> 4)), gm_o);
+                }
+                const int k_e = part * 16 + 4 * t, k_o = 32 + part * 16 + 4 * t;
+                store_split4(base + (k_e >> 3) * kALbo + (k_e & 7) * 2, e[0], e[1], e[2], e[3]);
+                store_split4(base + (k_o >> 3) * kALbo + (k_o & 7) * 2, o[0], o[1], o[2], o[3]);
+            }
+        }
+    } else if (type == kQ6_K) {
+        // chunk c covers groups 2c, 2c + 1: super-half cc = c / 2, variants v = 2 (c % 2), + 1
+        const int cc = c >> 1, v0 = (c & 1) * 2;
+        const uint4 qh = *reinterpret_cast<const uint4*>(tile + 2048 + cc * 512 + lane * 16);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint4 w = *reinterpret_cast<const uint4*>(tile + (cc * 2 + h) * 512 + lane * 16);
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int row = g + 8 * rr;
+                const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(tile + 3328 + row * 2)));
+                const signed char* scales = reinterpret_cast<const signed char*>(tile + 3072 + row * 16);
+                const uint32_t high = rr == 0 ? (h == 0 ? qh.x : qh.z) : (h == 0 ? qh.y : qh.w);
+                unsigned char* base = a_hi + a_offset(row0 + row, 0);
+#pragma unroll
+                for (int vv = 0; vv < 2; ++vv) {
+                    const int v = v0 + vv, group = cc * 4 + v;
+                    const uint32_t low = rr == 0 ? ((v & 1) ? w.y : w.x) : ((v & 1) ? w.w : w.z);
+                    const float gs = __fmul_rn(d, (float)scales[group * 2 + h]);
+                    float q[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t lb = (low >> (8 * i)) & 0xffu, hb = (high >> (8 * i)) & 0xffu;
+                        const uint32_t nib = v < 2 ? (lb & 15u) : (lb >> 4);
+                        const int value = (int)(nib | (((hb >> (2 * v)) & 3u) << 4)) - 32;
+                        q[i] = __fmul_rn(gs, (float)value);
+                    }
+                    const int k = vv * 32 + h * 16 + 4 * t;
+                    store_split4(base + (k >> 3) * kALbo + (k & 7) * 2, q[0], q[1], q[2], q[3]);
+                }
+            }
+        }
+    } else {
+        // Q8_0: chunk c covers blocks 2c, 2c + 1; stored byte = q + 128
+#pragma unroll
+        for (int bb = 0; bb < 2; ++bb) {
+            const int block = 2 * c + bb;
+            const uint4 w = *reinterpret_cast<const uint4*>(tile + block * 512 + lane * 16);
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int row = g + 8 * rr;
+                const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(tile + 4096 + row * 16 + block * 2)));
+                unsigned char* base = a_hi + a_offset(row0 + row, 0);
+#pragma unroll
+                for (int part = 0; part < 2; ++part) {
+                    const uint32_t word = rr == 0 ? (part == 0 ? w.x : w.y) : (part == 0 ? w.z : w.w);
+                    float q[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) q[i] = __fmul_rn(d, (float)((int)((word >> (8 * i)) & 0xffu) - 128));
+                    const int k = bb * 32 + part * 16 + 4 * t;
+                    store_split4(base + (k >> 3) * kALbo + (k & 7) * 2, q[0], q[1], q[2], q[3]);
+                }
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void zero_rows(unsigned char* a_hi, int row0, int lane) {
+    // 16 rows x 64 inputs x 2 planes: 8 column blocks x 2 row groups x 128 bytes per plane
+    for (int i = lane; i < 2 * 8 * 2 * 8; i += 32) {
+        const int plane = i >> 7, rest = i & 127, kblock = rest >> 4, rg = (rest >> 3) & 1, q16 = rest & 7;
+        *reinterpret_cast<uint4*>(a_hi + plane * kAHalfBytes + kblock * kALbo + ((row0 >> 3) + rg) * 128 + q16 * 16) =
+            make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+
+struct TcLayout {
+    int w_stage_bytes, w_stages, b_bytes;  // per stage / per chunk
+    int cols;                              // MMA N of the first product: 2 * padded members
+    int members_padded;
+};
+
+// Work list shared by all roles: unit u of the launch -> segment, first row tile.
+struct UnitRef { int seg, rt0; };
+__device__ __forceinline__ UnitRef unit_of(const GemmArgs& a, int u) {
+    UnitRef r{0, u * kRowTilesPerUnit};
+    while (r.seg + 1 < a.n_segments) {
+        const int units = (a.seg[r.seg].row_tiles + kRowTilesPerUnit - 1) / kRowTilesPerUnit;
+        if (r.rt0 < units * kRowTilesPerUnit) break;
+        r.rt0 -= units * kRowTilesPerUnit;
+        ++r.seg;
+    }
+    return r;
+}
+
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmArgs a, const TcLayout lay, const int units) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_tiles = a.k / kTileCols;
+    unsigned char* w_ring = smem;
+    unsigned char* a_buf = w_ring + (size_t)lay.w_stages * lay.w_stage_bytes;   // [2][hi | lo]
+    unsigned char* b_buf = a_buf + 2 * kABytes;                                  // [2][b_bytes]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_buf + 2 * (size_t)lay.b_bytes);
+    const uint32_t bars = smem_u32(tmem_slot + 4);
+    const uint32_t w_full = bars, w_empty = bars + 32, a_full = bars + 64, b_full = bars + 80, ab_empty = bars + 96,
+                   t_full = bars + 112, t_empty = bars + 128;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < lay.w_stages; ++i) { mbar_init(w_full + 8 * i, 1); mbar_init(w_empty + 8 * i, kDequantWarps); }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(a_full + 8 * i, kDequantWarps);
+            mbar_init(b_full + 8 * i, 1);
+            mbar_init(ab_empty + 8 * i, 1);
+            mbar_init(t_full + 8 * i, 1);
+            mbar_init(t_empty + 8 * i, kEpilogueWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+    const int acc_cols = kTmemCols / 2;  // two accumulator buffers
+
+    if (warp == kProducerWarp) {
+        // ---------------- copies: packed weight tiles two k tiles ahead, one activation chunk at a time ----------------
+        bool alive = true;
+        uint32_t w_count = 0, b_count = 0;
+        // position of the next weight stage to issue
+        int wu = blockIdx.x, wkb = 0;
+        auto issue_w = [&]() {
+            if (wu >= units) return;
+            const UnitRef ur = unit_of(a, wu);
+            const GemvSegment& s = a.seg[ur.seg];
+            const uint32_t tb = (uint32_t)packed_tile_bytes(s.type);
+            const uint32_t stage = w_count % (uint32_t)lay.w_stages;
+            if (lane == 0) {
+                if (w_count >= (uint32_t)lay.w_stages && alive) {
+                    alive = mbar_wait(w_empty + 8 * stage, ((w_count / (uint32_t)lay.w_stages) - 1u) & 1u, a.error_flag, 11);
+                }
+                const int present = min(kRowTilesPerUnit, s.row_tiles - ur.rt0);
+                mbar_expect_tx(w_full + 8 * stage, (uint32_t)present * tb);
+            }
+            __syncwarp();
+            if (lane < kRowTilesPerUnit && ur.rt0 + lane < s.row_tiles) {
+                bulk_g2s(smem_u32(w_ring + (size_t)stage * lay.w_stage_bytes + (size_t)lane * tb),
+                         s.data + ((size_t)(ur.rt0 + lane) * k_tiles + wkb) * tb, tb, w_full + 8 * stage);
+            }
+            ++w_count;
+            if (++wkb == k_tiles) { wkb = 0; wu += gridDim.x; }
+        };
+        issue_w();
+        if (lay.w_stages > 2) issue_w();
+        for (int u = blockIdx.x; u < units; u += gridDim.x) {
+            for (int kb = 0; kb < k_tiles; ++kb) {
+                if (lane == 0) {
+                    for (int c = 0; c < kChunksPerTile; ++c, ++b_count) {
+                        const uint32_t bs = b_count & 1u;
+                        if (b_count >= 2u && alive) alive = mbar_wait(ab_empty + 8 * bs, ((b_count >> 1) - 1u) & 1u, a.error_flag, 12);
+                        mbar_expect_tx(b_full + 8 * bs, (uint32_t)lay.b_bytes);
+                        bulk_g2s(smem_u32(b_buf + (size_t)bs * lay.b_bytes),
+                                 a.chunks + ((size_t)kb * kChunksPerTile + c) * lay.b_bytes, (uint32_t)lay.b_bytes, b_full + 8 * bs);
+                    }
+                }
+                __syncwarp();
+                issue_w();
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ---------------- MMA issue (one thread) ----------------
+        if (lane == 0) {
+            bool alive = true;
+            uint32_t count = 0, unit_count = 0;
+            const uint32_t idesc_full = umma_idesc(lay.cols), idesc_half = umma_idesc(lay.members_padded);
+            const uint32_t b_lbo = (uint32_t)(lay.cols / 8) * 128u;
+            for (int u = blockIdx.x; u < units; u += gridDim.x, ++unit_count) {
+                const uint32_t tb = unit_count & 1u;
+                if (unit_count >= 2u && alive) alive = mbar_wait(t_empty + 8 * tb, ((unit_count >> 1) - 1u) & 1u, a.error_flag, 13);
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + tb * (uint32_t)acc_cols;
+                for (int kc = 0; kc < k_tiles * kChunksPerTile; ++kc, ++count) {
+                    const uint32_t st = count & 1u, parity = (count >> 1) & 1u;
+                    if (alive) alive = mbar_wait(a_full + 8 * st, parity, a.error_flag, 14);
+                    if (alive) alive = mbar_wait(b_full + 8 * st, parity, a.error_flag, 15);
+                    tc_fence_after();
+                    const uint32_t a_hi = smem_u32(a_buf + (size_t)st * kABytes), a_lo = a_hi + kAHalfBytes;
+                    const uint32_t b_addr = smem_u32(b_buf + (size_t)st * lay.b_bytes);
+#pragma unroll
+                    for (int s16 = 0; s16 < kChunkK / 16; ++s16) {
+                        const uint64_t da_hi = umma_desc(a_hi + s16 * 2 * kALbo, kALbo, 128);
+                        const uint64_t da_lo = umma_desc(a_lo + s16 * 2 * kALbo, kALbo, 128);
+                        const uint64_t db = umma_desc(b_addr + s16 * 2 * b_lbo, b_lbo, 128);
+                        umma_f16(d_tmem, da_hi, db, idesc_full, (kc | s16) != 0 ? 1u : 0u);   // hi x [x_hi | x_lo]
+                        umma_f16(d_tmem, da_lo, db, idesc_half, 1u);                          // lo x x_hi
+                    }
+                    umma_commit(ab_empty + 8 * st);  // arrives when these MMAs have read the buffers
+                }
+                umma_commit(t_full + 8 * tb);        // ... and when the unit's accumulators are complete
+            }
+        }
+    } else if (warp >= kDequantWarp0) {
+        // ---------------- dequant: warp i decodes row tile i of the unit ----------------
+        const int rt_local = warp - kDequantWarp0;
+        bool alive = true;
+        uint32_t w_count = 0, a_count = 0;
+        for (int u = blockIdx.x; u < units; u += gridDim.x) {
+            const UnitRef ur = unit_of(a, u);
+            const GemvSegment& s = a.seg[ur.seg];
+            const int type = s.type;
+            const bool present = ur.rt0 + rt_local < s.row_tiles;
+            const int tb = packed_tile_bytes(type);
+            for (int kb = 0; kb < k_tiles; ++kb, ++w_count) {
+                const uint32_t stage = w_count % (uint32_t)lay.w_stages;
+                if (alive) alive = mbar_wait(w_full + 8 * stage, (w_count / (uint32_t)lay.w_stages) & 1u, a.error_flag, 16);
+                const unsigned char* tile = w_ring + (size_t)stage * lay.w_stage_bytes + (size_t)rt_local * tb;
+                for (int c = 0; c < kChunksPerTile; ++c, ++a_count) {
+                    const uint32_t st = a_count & 1u;
+                    if (a_count >= 2u && alive) alive = mbar_wait(ab_empty + 8 * st, ((a_count >> 1) - 1u) & 1u, a.error_flag, 17);
+                    unsigned char* a_hi = a_buf + (size_t)st * kABytes;
+                    if (present) dequant_chunk(type, tile, c, a_hi, rt_local * kTileRows, lane);
+                    else zero_rows(a_hi, rt_local * kTileRows, lane);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic stores -> tensor-core reads
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(a_full + 8 * st);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(w_empty + 8 * stage);
+            }
+        }
+    } else {
+        // ---------------- epilogue: warp q reads TMEM lanes 32 q .. 32 q + 31 (one output row per thread) ----------------
+        bool alive = true;
+        uint32_t unit_count = 0;
+        for (int u = blockIdx.x; u < units; u += gridDim.x, ++unit_count) {
+            const uint32_t tb = unit_count & 1u;
+            const UnitRef ur = unit_of(a, u);
+            const GemvSegment& s = a.seg[ur.seg];
+            if (alive) alive = mbar_wait(t_full + 8 * tb, (unit_count >> 1) & 1u, a.error_flag, 18);
+            tc_fence_after();
+            const int n_index = ur.rt0 * kTileRows + warp * 32 + lane;
+            const bool valid = n_index < s.n;
+            const uint32_t taddr = tmem_base + tb * (uint32_t)acc_cols + ((uint32_t)(warp * 32) << 16);
+            for (int m0 = 0; m0 < lay.members_padded; m0 += 16) {
+                float hi[16], lo[16];
+                tmem_ld16(taddr + (uint32_t)m0, hi);
+                tmem_ld16(taddr + (uint32_t)(lay.members_padded + m0), lo);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int m = m0 + i;
+                    if (valid && m < a.members) {
+                        const float v = (hi[i] + lo[i]) * a.member_scale[m];
+                        float* y = s.y + (size_t)m * s.n + n_index;
+                        if (a.epilogue == kResidual) *y += v; else *y = v;
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(t_empty + 8 * tb);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- activations -> hi + lo binary16 operand chunks ------------------------------------------------
+// Pass 1 (one block per member): power-of-two scale that brings max |x * w| into [1, 2), and the
+// epilogue factor (RMSNorm factor / that scale).
+__global__ void tc_scale_kernel(const float* x, const int32_t* index, const float* norm_weight, int k, float eps,
+                                float* scale_in, float* member_scale) {
+    __shared__ float red_max[32], red_sum[32];
+    const int m = blockIdx.x;
+    const float* row = x + (size_t)(index ? index[m] : m) * k;
+    float amax = 0.0f, ss = 0.0f;
+    for (int i = threadIdx.x; i < k; i += blockDim.x) {
+        const float v = row[i];
+        ss = fmaf(v, v, ss);
+        amax = fmaxf(amax, fabsf(norm_weight ? v * norm_weight[i] : v));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    }
+    if ((threadIdx.x & 31) == 0) { red_max[threadIdx.x >> 5] = amax; red_sum[threadIdx.x >> 5] = ss; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float top = 0.0f, total = 0.0f;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { top = fmaxf(top, red_max[w]); total += red_sum[w]; }
+        const float inv_norm = norm_weight ? 1.0f / sqrtf(total / (float)k + eps) : 1.0f;
+        int e = 0;
+        if (top > 0.0f && isfinite(top)) frexpf(top, &e);   // top = f * 2^e, f in [0.5, 1)
+        const float s = ldexpf(1.0f, 1 - e);                // top * s in [1, 2)
+        scale_in[m] = s;
+        member_scale[m] = inv_norm * ldexpf(1.0f, e - 1);
+    }
+}
+
+// Pass 2: chunk c (64 inputs) = [k block 8][column group cols / 8][column 8][8 halves], columns
+// [0, mp) the hi parts and [mp, 2 mp) the lo parts; padded members are zero.
+__global__ void tc_chunks_kernel(const float* x, const int32_t* index, const float* norm_weight, int members, int mp,
+                                 int k, const float* scale_in, __half* chunks) {
+    const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per (member, 8 inputs)
+    const int kblocks = k / 8;
+    if (id >= (long long)mp * kblocks) return;
+    const int m = (int)(id / kblocks), kblk = (int)(id % kblocks);
+    const int cols = 2 * mp;
+    __half hi[8], lo[8];
+    if (m < members) {
+        const float* row = x + (size_t)(index ? index[m] : m) * k + (size_t)kblk * 8;
+        const float s = scale_in[m];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float v = row[i];
+            if (norm_weight != nullptr) v *= norm_weight[kblk * 8 + i];
+            v *= s;
+            hi[i] = __float2half_rn(v);
+            lo[i] = __float2half_rn(v - __half2float(hi[i]));
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) hi[i] = lo[i] = __float2half_rn(0.0f);
+    }
+    const int chunk = kblk / 8, kb8 = kblk % 8;
+    __half* base = chunks + (size_t)chunk * (cols * kChunkK) + (size_t)kb8 * (cols * 8);
+    *reinterpret_cast<uint4*>(base + (size_t)m * 8) = *reinterpret_cast<const uint4*>(hi);
+    *reinterpret_cast<uint4*>(base + (size_t)(mp + m) * 8) = *reinterpret_cast<const uint4*>(lo);
+}
+
+int padded_members(int members) { return (members + 15) / 16 * 16; }
+
+}  // namespace
+
+size_t tc_operand_bytes(int members, int k) { return (size_t)(k / kChunkK) * 2 * padded_members(members) * kChunkK * sizeof(__half); }
+
+cudaError_t launch_to_tc_operand(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,
+                                 int members, int k, float eps, TcOperand out) {
+    if (members <= 0 || members > kGemmTcMaxMembers || k % kTileCols != 0) return cudaErrorInvalidValue;
+    const int mp = padded_members(members);
+    tc_scale_kernel<<<members, 256, 0, stream>>>(x, index, norm_weight, k, eps, out.scale_in, out.member_scale);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    const long long threads = (long long)mp * (k / 8);
+    tc_chunks_kernel<<<(unsigned int)((threads + 255) / 256), 256, 0, stream>>>(x, index, norm_weight, members, mp, k,
+                                                                              out.scale_in, out.chunks);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmArgs& args) {
+    if (args.members < 1 || args.members > kGemmTcMaxMembers || args.k % kTileCols != 0) return cudaErrorInvalidValue;
+    if (args.epilogue != kStore && args.epilogue != kResidual) return cudaErrorInvalidValue;
+    int units = 0, tile = 0;
+    for (int i = 0; i < args.n_segments; ++i) {
+        units += (args.seg[i].row_tiles + kRowTilesPerUnit - 1) / kRowTilesPerUnit;
+        const int b = packed_tile_bytes(args.seg[i].type);
+        if (b == 0) return cudaErrorInvalidValue;
+        tile = std::max(tile, b);
+    }
+    if (units <= 0) return cudaSuccess;
+    TcLayout lay{};
+    lay.members_padded = padded_members(args.members);
+    lay.cols = 2 * lay.members_padded;
+    lay.b_bytes = lay.cols * kChunkK * (int)sizeof(__half);
+    lay.w_stage_bytes = kRowTilesPerUnit * tile;
+    const size_t fixed = (size_t)2 * kABytes + (size_t)2 * lay.b_bytes + 16 + 160;
+    const size_t budget = 220 * 1024;
+    lay.w_stages = (int)std::min<size_t>(3, (budget - fixed) / (size_t)lay.w_stage_bytes);
+    if (lay.w_stages < 2) return cudaErrorInvalidValue;
+    const size_t smem = fixed + (size_t)lay.w_stages * lay.w_stage_bytes;
+    static bool configured = false;
+    static int sm_count = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+        if (e != cudaSuccess) return e;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+        configured = true;
+    }
+    const int grid = std::min(units, sm_count);
+    gemm_tc_kernel<<<grid, kThreads, smem, stream>>>(args, lay, units);
+    return cudaGetLastError();
+}
+
+}  // namespace ribn

@@ -12,6 +12,7 @@
 //   Q6_K 3360 B: 4 x 512 B low nibbles + 2 x 512 B high bits + 16 x 16 B scales + 16 x 2 B d
 //   Q8_0 4352 B: 8 x 512 B offset-binary bytes (q + 128) + 16 x 16 B of f16 d
 #pragma once
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -164,6 +165,26 @@ struct GemmArgs {
 };
 
 cudaError_t launch_gemm_imma(cudaStream_t stream, const GemmArgs& args);
+
+// ---- tensor-memory form (tcgen05, 3..128 members) ---------------------------------------------------
+// Activations as binary16 pairs hi + lo of x * scale_in[member] (scale_in a power of two that brings
+// the member's largest |x| into [1, 2)), in the K-major core-matrix order the tensor core reads:
+// per 64 inputs one chunk [8-input block][column][8 halves] with the hi parts in columns
+// [0, padded members) and the lo parts behind them; members are padded to a multiple of 16.
+// member_scale[member] = RMSNorm factor / scale_in, applied by the kernel's epilogue.
+constexpr int kGemmTcMaxMembers = 128;
+
+struct TcOperand {
+    __half* chunks = nullptr;
+    float* scale_in = nullptr;      // [members]
+    float* member_scale = nullptr;  // [members]
+};
+
+size_t tc_operand_bytes(int members, int k);
+cudaError_t launch_to_tc_operand(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,
+                                 int members, int k, float eps, TcOperand out);
+// GemmArgs::chunks points at TcOperand::chunks; epilogue kStore or kResidual.
+cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmArgs& args);
 
 // Scratch shared by the step kernels: per-span attention accumulators.
 struct StepScratch {

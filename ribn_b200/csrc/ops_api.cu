@@ -144,7 +144,29 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
         int* d_err = s.alloc<int>(1);
         OP_PTR(op.dig); OP_PTR(op.sx); OP_PTR(op.sxs16); OP_PTR(d_err);
         OP_TRY(cudaMemsetAsync(d_err, 0, sizeof(int), s.stream));
-        if (variant == 2) {
+        if (variant == 3) {
+            // the tensor-memory kernel, in groups of up to kGemmTcMaxMembers members
+            TcOperand top;
+            const int group = std::min(members, kGemmTcMaxMembers);
+            top.chunks = (__half*)s.alloc<unsigned char>(tc_operand_bytes(group, (int)cols));
+            top.scale_in = s.alloc<float>((size_t)group);
+            top.member_scale = s.alloc<float>((size_t)group);
+            OP_PTR(top.chunks); OP_PTR(top.scale_in); OP_PTR(top.member_scale);
+            for (int m0 = 0; m0 < members; m0 += kGemmTcMaxMembers) {
+                const int m = std::min(kGemmTcMaxMembers, members - m0);
+                OP_TRY(launch_to_tc_operand(s.stream, d_x + (size_t)m0 * cols, nullptr, nullptr, m, (int)cols, 0.0f, top));
+                GemmArgs a{};
+                a.n_segments = 1;
+                a.seg[0] = GemvSegment{d_w, type, (int)rows, (int)((rows + kTileRows - 1) / kTileRows),
+                                       d_y + (size_t)m0 * rows};
+                a.k = (int)cols;
+                a.members = m;
+                a.chunks = (const signed char*)top.chunks; a.member_scale = top.member_scale;
+                a.epilogue = kStore;
+                a.error_flag = d_err;
+                OP_TRY(launch_gemm_tc(s.stream, a));
+            }
+        } else if (variant == 2) {
             // the batched kernel, in groups of up to kGemmMaxMembers members
             BatchOperand bop;
             const int group = std::min(members, kGemmMaxMembers);
