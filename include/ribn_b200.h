@@ -238,7 +238,8 @@ RIBN_B200_API int ribn_b200_op_dequantize(int32_t device, int32_t ggml_type, con
  * gemv_batch, crates/nvidia/src/quantized.rs:303-436).  variant 0 = fast
  * GEMV kernels (members in pairs), 1 = one-warp-per-row reference kernels,
  * 2 = the batched integer tensor-core kernel (up to 64 members per launch),
- * 3 = the tcgen05 / tensor-memory dequant-GEMM (up to 128 members per launch). */
+ * 3 = the tcgen05 / tensor-memory kernels (K-quant integer form for Q4_K / Q6_K,
+ * decode-and-split form for Q8_0), 4 = the decode-and-split form for every type. */
 RIBN_B200_API int ribn_b200_op_gemv(int32_t device, int32_t ggml_type, const void* weights,
                                     int64_t rows, int64_t cols, const float* x, int32_t members,
                                     float* y, int32_t variant);

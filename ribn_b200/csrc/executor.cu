@@ -339,7 +339,10 @@ cudaError_t batch_project(ribn_b200_executor* ex, int& launches, const float* x,
                           int n_mats, int epilogue) {
     cudaStream_t s = ex->stream;
     const bool tensor_memory = !(ex->cfg.flags & RIBN_B200_FLAG_NO_TCGEN05);
-    const int group = tensor_memory ? kGemmTcMaxMembers : kGemmMaxMembers;
+    GemvSegment probe[3];
+    for (int i = 0; i < n_mats; ++i) probe[i] = GemvSegment{nullptr, mats[i]->type, 0, 0, nullptr};
+    const bool kquant = tensor_memory && gemm_tc_kquant(probe, n_mats, 1);
+    const int group = !tensor_memory ? kGemmMaxMembers : kquant ? 64 : kGemmTcMaxMembers;
     for (int base = 0; base < tokens; base += group) {
         const int m = std::min(group, tokens - base);
         GemmArgs a{};
@@ -354,11 +357,12 @@ cudaError_t batch_project(ribn_b200_executor* ex, int& launches, const float* x,
         if (tensor_memory) {
             // tcgen05 dequant-GEMM; SwiGLU runs as a separate elementwise pass over gate and up
             cudaError_t e = launch_to_tc_operand(s, index ? x : x + (size_t)base * k, index ? index + base : nullptr,
-                                                 norm_weight, m, k, ex->cfg.rms_eps, ex->op_tc);
+                                                 norm_weight, m, k, ex->cfg.rms_eps, kquant, ex->op_tc);
             if (e != cudaSuccess) return e;
             launches += 2;
             a.chunks = (const signed char*)ex->op_tc.chunks;
             a.member_scale = ex->op_tc.member_scale;
+            a.kquant = kquant ? 1 : 0;
             a.epilogue = epilogue == kSwiGLU ? kStore : epilogue;
             STEP_TRY(launch_gemm_tc(s, a));
             if (epilogue == kSwiGLU) {

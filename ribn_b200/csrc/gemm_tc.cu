@@ -39,7 +39,7 @@ constexpr int kEpilogueWarps = 4;          // warps 0..3: TMEM lane quadrant = w
 constexpr int kProducerWarp = 4;
 constexpr int kMmaWarp = 5;
 constexpr int kDequantWarp0 = 6;
-constexpr int kDequantWarps = kRowTilesPerUnit;
+constexpr int kDequantWarps = 2 * kRowTilesPerUnit;  // two per row tile: rows g and rows g + 8 of the MMA-fragment order
 constexpr int kThreads = (kDequantWarp0 + kDequantWarps) * 32;
 constexpr int kAHalfBytes = kRows * kChunkK * 2;   // one of hi / lo for a chunk: 16 KB
 constexpr int kABytes = 2 * kAHalfBytes;
@@ -71,6 +71,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code) {
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (error_flag != nullptr) atomicExch(error_flag, code);
+    return false;
+}
+// The same for waits that usually last microseconds (a whole K loop, a ring turn): sleeps between
+// polls so the waiting warp does not take issue slots from the dequant warps.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, int* error_flag, int code) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(100);
     }
     if (error_flag != nullptr) atomicExch(error_flag, code);
     return false;
@@ -118,16 +128,20 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 
 // ---- dequant to hi + lo binary16 ---------------------------------------------------------------
 // Four consecutive inputs of one row: 8 bytes into the hi plane and 8 into the lo plane.
+// hi = w with its significand cut to 11 bits (exact in binary16), lo = w - hi rounded to binary16.
 __device__ __forceinline__ void store_split4(unsigned char* hi, float w0, float w1, float w2, float w3) {
-    const __half2 h01 = __floats2half2_rn(w0, w1), h23 = __floats2half2_rn(w2, w3);
-    const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-    const __half2 l01 = __floats2half2_rn(w0 - f01.x, w1 - f01.y), l23 = __floats2half2_rn(w2 - f23.x, w3 - f23.y);
+    const float h0 = __uint_as_float(__float_as_uint(w0) & 0xFFFFE000u), h1 = __uint_as_float(__float_as_uint(w1) & 0xFFFFE000u);
+    const float h2 = __uint_as_float(__float_as_uint(w2) & 0xFFFFE000u), h3 = __uint_as_float(__float_as_uint(w3) & 0xFFFFE000u);
+    const __half2 h01 = __floats2half2_rn(h0, h1), h23 = __floats2half2_rn(h2, h3);
+    const __half2 l01 = __floats2half2_rn(w0 - h0, w1 - h1), l23 = __floats2half2_rn(w2 - h2, w3 - h3);
     uint2 a, b;
     a.x = *reinterpret_cast<const uint32_t*>(&h01); a.y = *reinterpret_cast<const uint32_t*>(&h23);
     b.x = *reinterpret_cast<const uint32_t*>(&l01); b.y = *reinterpret_cast<const uint32_t*>(&l23);
     *reinterpret_cast<uint2*>(hi) = a;
     *reinterpret_cast<uint2*>(hi + kAHalfBytes) = b;
 }
+// Small unsigned integer (< 2^23) to float without the conversion pipe.
+__device__ __forceinline__ float small_uint_f32(uint32_t v) { return __uint_as_float(v | 0x4B000000u) - 8388608.0f; }
 // Byte offset inside a hi (or lo) plane of input k0 (multiple of 4) of row `r` of the unit.
 __device__ __forceinline__ int a_offset(int r, int k0) { return (k0 >> 3) * kALbo + (r >> 3) * 128 + (r & 7) * 16 + (k0 & 7) * 2; }
 
@@ -135,12 +149,11 @@ __device__ __forceinline__ float byte_of(uint32_t w, int i) { return (float)((w 
 
 // One 64-input chunk `c` of one packed tile -> rows [row0, row0 + 16) of the A chunk.
 // Lane (g, t) holds rows g and g + 8; the tile's byte order is that of the GEMV kernel's MMA fragments.
-__device__ __forceinline__ void dequant_chunk(int type, const unsigned char* tile, int c, unsigned char* a_hi, int row0, int lane) {
+__device__ __forceinline__ void dequant_chunk(int type, const unsigned char* tile, int c, unsigned char* a_hi, int row0, int rr, int lane) {
     const int g = lane >> 2, t = lane & 3;
     if (type == kQ4_K) {
         const uint4 w = *reinterpret_cast<const uint4*>(tile + c * 512 + lane * 16);
-#pragma unroll
-        for (int rr = 0; rr < 2; ++rr) {
+        {
             const int row = g + 8 * rr;
             const uint4 h = *reinterpret_cast<const uint4*>(tile + 2048 + row * 16);
             const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
@@ -150,6 +163,9 @@ __device__ __forceinline__ void dequant_chunk(int type, const unsigned char* til
             const int b0 = (2 * c) & 3;  // byte of the even group inside its half
             const float gs_e = __fmul_rn(d, byte_of(sc4, b0)), gs_o = __fmul_rn(d, byte_of(sc4, b0 + 1));
             const float gm_e = __fmul_rn(dmin, byte_of(mn4, b0)), gm_o = __fmul_rn(dmin, byte_of(mn4, b0 + 1));
+            // fl(gs * q) from the integer's float pattern 2^23 + q in one fused step: gs * 2^23 is exact,
+            // so fma(gs, 2^23 + q, -(gs * 2^23)) rounds the exact product gs * q once, as the multiplication does.
+            const float ce = -(gs_e * 8388608.0f), co = -(gs_o * 8388608.0f);
             const uint32_t lo16 = rr == 0 ? w.x : w.z, hi16 = rr == 0 ? w.y : w.w;  // inputs 4t.. and 16 + 4t.. of both groups
             unsigned char* base = a_hi + a_offset(row0 + row, 0);
 #pragma unroll
@@ -158,9 +174,10 @@ __device__ __forceinline__ void dequant_chunk(int type, const unsigned char* til
                 float e[4], o[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const uint32_t byte = (word >> (8 * i)) & 0xffu;
-                    e[i] = __fsub_rn(__fmul_rn(gs_e, (float)(byte & 15u)), gm_e);
-                    o[i] = __fsub_rn(__fmul_rn(gs_o, (float)(byte >> 4)), gm_o);
+                    const float fe = __uint_as_float(((word >> (8 * i)) & 15u) | 0x4B000000u);
+                    const float fo = __uint_as_float(((word >> (8 * i + 4)) & 15u) | 0x4B000000u);
+                    e[i] = __fsub_rn(__fmaf_rn(gs_e, fe, ce), gm_e);
+                    o[i] = __fsub_rn(__fmaf_rn(gs_o, fo, co), gm_o);
                 }
                 const int k_e = part * 16 + 4 * t, k_o = 32 + part * 16 + 4 * t;
                 store_split4(base + (k_e >> 3) * kALbo + (k_e & 7) * 2, e[0], e[1], e[2], e[3]);
@@ -174,8 +191,7 @@ __device__ __forceinline__ void dequant_chunk(int type, const unsigned char* til
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const uint4 w = *reinterpret_cast<const uint4*>(tile + (cc * 2 + h) * 512 + lane * 16);
-#pragma unroll
-            for (int rr = 0; rr < 2; ++rr) {
+            {
                 const int row = g + 8 * rr;
                 const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(tile + 3328 + row * 2)));
                 const signed char* scales = reinterpret_cast<const signed char*>(tile + 3072 + row * 16);
@@ -191,8 +207,7 @@ __device__ __forceinline__ void dequant_chunk(int type, const unsigned char* til
                     for (int i = 0; i < 4; ++i) {
                         const uint32_t lb = (low >> (8 * i)) & 0xffu, hb = (high >> (8 * i)) & 0xffu;
                         const uint32_t nib = v < 2 ? (lb & 15u) : (lb >> 4);
-                        const int value = (int)(nib | (((hb >> (2 * v)) & 3u) << 4)) - 32;
-                        q[i] = __fmul_rn(gs, (float)value);
+                        q[i] = __fmul_rn(gs, small_uint_f32(nib | (((hb >> (2 * v)) & 3u) << 4)) - 32.0f);
                     }
                     const int k = vv * 32 + h * 16 + 4 * t;
                     store_split4(base + (k >> 3) * kALbo + (k & 7) * 2, q[0], q[1], q[2], q[3]);
@@ -205,8 +220,7 @@ __device__ __forceinline__ void dequant_chunk(int type, const unsigned char* til
         for (int bb = 0; bb < 2; ++bb) {
             const int block = 2 * c + bb;
             const uint4 w = *reinterpret_cast<const uint4*>(tile + block * 512 + lane * 16);
-#pragma unroll
-            for (int rr = 0; rr < 2; ++rr) {
+            {
                 const int row = g + 8 * rr;
                 const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(tile + 4096 + row * 16 + block * 2)));
                 unsigned char* base = a_hi + a_offset(row0 + row, 0);
@@ -215,7 +229,7 @@ __device__ __forceinline__ void dequant_chunk(int type, const unsigned char* til
                     const uint32_t word = rr == 0 ? (part == 0 ? w.x : w.y) : (part == 0 ? w.z : w.w);
                     float q[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) q[i] = __fmul_rn(d, (float)((int)((word >> (8 * i)) & 0xffu) - 128));
+                    for (int i = 0; i < 4; ++i) q[i] = __fmul_rn(d, small_uint_f32((word >> (8 * i)) & 0xffu) - 128.0f);
                     const int k = bb * 32 + part * 16 + 4 * t;
                     store_split4(base + (k >> 3) * kALbo + (k & 7) * 2, q[0], q[1], q[2], q[3]);
                 }
@@ -224,17 +238,24 @@ __device__ __forceinline__ void dequant_chunk(int type, const unsigned char* til
     }
 }
 
+// Rows [row0, row0 + 8) of both planes: 8 column blocks x 128 bytes per plane.
 __device__ __forceinline__ void zero_rows(unsigned char* a_hi, int row0, int lane) {
-    // 16 rows x 64 inputs x 2 planes: 8 column blocks x 2 row groups x 128 bytes per plane
-    for (int i = lane; i < 2 * 8 * 2 * 8; i += 32) {
-        const int plane = i >> 7, rest = i & 127, kblock = rest >> 4, rg = (rest >> 3) & 1, q16 = rest & 7;
-        *reinterpret_cast<uint4*>(a_hi + plane * kAHalfBytes + kblock * kALbo + ((row0 >> 3) + rg) * 128 + q16 * 16) =
+    for (int i = lane; i < 2 * 8 * 8; i += 32) {
+        const int plane = i >> 6, kblock = (i >> 3) & 7, q16 = i & 7;
+        *reinterpret_cast<uint4*>(a_hi + plane * kAHalfBytes + kblock * kALbo + (row0 >> 3) * 128 + q16 * 16) =
             make_uint4(0u, 0u, 0u, 0u);
     }
 }
 
+// Rows [row0, row0 + 8) of one plane.
+__device__ __forceinline__ void zero_rows_plane(unsigned char* plane, int row0, int lane) {
+    for (int i = lane; i < 8 * 8; i += 32) {
+        *reinterpret_cast<uint4*>(plane + (i >> 3) * kALbo + (row0 >> 3) * 128 + (i & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+
 struct TcLayout {
-    int w_stage_bytes, w_stages, b_bytes;  // per stage / per chunk
+    int w_stage_bytes, w_stages, b_bytes, b_stages;  // per stage / per chunk
     int cols;                              // MMA N of the first product: 2 * padded members
     int members_padded;
 };
@@ -258,21 +279,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmArgs a, 
     const int k_tiles = a.k / kTileCols;
     unsigned char* w_ring = smem;
     unsigned char* a_buf = w_ring + (size_t)lay.w_stages * lay.w_stage_bytes;   // [2][hi | lo]
-    unsigned char* b_buf = a_buf + 2 * kABytes;                                  // [2][b_bytes]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_buf + 2 * (size_t)lay.b_bytes);
+    unsigned char* b_buf = a_buf + 2 * kABytes;                                  // [b_stages][b_bytes]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_buf + (size_t)lay.b_stages * lay.b_bytes);
     const uint32_t bars = smem_u32(tmem_slot + 4);
-    const uint32_t w_full = bars, w_empty = bars + 32, a_full = bars + 64, b_full = bars + 80, ab_empty = bars + 96,
-                   t_full = bars + 112, t_empty = bars + 128;
+    const uint32_t w_full = bars, w_empty = bars + 32, a_full = bars + 64, a_empty = bars + 80, t_full = bars + 96,
+                   t_empty = bars + 112, b_full = bars + 128, b_empty = bars + 192;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < lay.w_stages; ++i) { mbar_init(w_full + 8 * i, 1); mbar_init(w_empty + 8 * i, kDequantWarps); }
         for (int i = 0; i < 2; ++i) {
             mbar_init(a_full + 8 * i, kDequantWarps);
-            mbar_init(b_full + 8 * i, 1);
-            mbar_init(ab_empty + 8 * i, 1);
+            mbar_init(a_empty + 8 * i, 1);
             mbar_init(t_full + 8 * i, 1);
             mbar_init(t_empty + 8 * i, kEpilogueWarps);
         }
+        for (int i = 0; i < lay.b_stages; ++i) { mbar_init(b_full + 8 * i, 1); mbar_init(b_empty + 8 * i, 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == kMmaWarp) {
@@ -299,7 +320,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmArgs a, 
             const uint32_t stage = w_count % (uint32_t)lay.w_stages;
             if (lane == 0) {
                 if (w_count >= (uint32_t)lay.w_stages && alive) {
-                    alive = mbar_wait(w_empty + 8 * stage, ((w_count / (uint32_t)lay.w_stages) - 1u) & 1u, a.error_flag, 11);
+                    alive = mbar_wait_relaxed(w_empty + 8 * stage, ((w_count / (uint32_t)lay.w_stages) - 1u) & 1u, a.error_flag, 11);
                 }
                 const int present = min(kRowTilesPerUnit, s.row_tiles - ur.rt0);
                 mbar_expect_tx(w_full + 8 * stage, (uint32_t)present * tb);
@@ -318,8 +339,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmArgs a, 
             for (int kb = 0; kb < k_tiles; ++kb) {
                 if (lane == 0) {
                     for (int c = 0; c < kChunksPerTile; ++c, ++b_count) {
-                        const uint32_t bs = b_count & 1u;
-                        if (b_count >= 2u && alive) alive = mbar_wait(ab_empty + 8 * bs, ((b_count >> 1) - 1u) & 1u, a.error_flag, 12);
+                        const uint32_t nb = (uint32_t)lay.b_stages, bs = b_count % nb;
+                        if (b_count >= nb && alive) alive = mbar_wait_relaxed(b_empty + 8 * bs, ((b_count / nb) - 1u) & 1u, a.error_flag, 12);
                         mbar_expect_tx(b_full + 8 * bs, (uint32_t)lay.b_bytes);
                         bulk_g2s(smem_u32(b_buf + (size_t)bs * lay.b_bytes),
                                  a.chunks + ((size_t)kb * kChunksPerTile + c) * lay.b_bytes, (uint32_t)lay.b_bytes, b_full + 8 * bs);
@@ -338,16 +359,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmArgs a, 
             const uint32_t b_lbo = (uint32_t)(lay.cols / 8) * 128u;
             for (int u = blockIdx.x; u < units; u += gridDim.x, ++unit_count) {
                 const uint32_t tb = unit_count & 1u;
-                if (unit_count >= 2u && alive) alive = mbar_wait(t_empty + 8 * tb, ((unit_count >> 1) - 1u) & 1u, a.error_flag, 13);
+                if (unit_count >= 2u && alive) alive = mbar_wait_relaxed(t_empty + 8 * tb, ((unit_count >> 1) - 1u) & 1u, a.error_flag, 13);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + tb * (uint32_t)acc_cols;
                 for (int kc = 0; kc < k_tiles * kChunksPerTile; ++kc, ++count) {
                     const uint32_t st = count & 1u, parity = (count >> 1) & 1u;
+                    const uint32_t nb = (uint32_t)lay.b_stages, bs = count % nb;
                     if (alive) alive = mbar_wait(a_full + 8 * st, parity, a.error_flag, 14);
-                    if (alive) alive = mbar_wait(b_full + 8 * st, parity, a.error_flag, 15);
+                    if (alive) alive = mbar_wait(b_full + 8 * bs, (count / nb) & 1u, a.error_flag, 15);
                     tc_fence_after();
                     const uint32_t a_hi = smem_u32(a_buf + (size_t)st * kABytes), a_lo = a_hi + kAHalfBytes;
-                    const uint32_t b_addr = smem_u32(b_buf + (size_t)st * lay.b_bytes);
+                    const uint32_t b_addr = smem_u32(b_buf + (size_t)bs * lay.b_bytes);
 #pragma unroll
                     for (int s16 = 0; s16 < kChunkK / 16; ++s16) {
                         const uint64_t da_hi = umma_desc(a_hi + s16 * 2 * kALbo, kALbo, 128);
@@ -356,14 +378,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmArgs a, 
                         umma_f16(d_tmem, da_hi, db, idesc_full, (kc | s16) != 0 ? 1u : 0u);   // hi x [x_hi | x_lo]
                         umma_f16(d_tmem, da_lo, db, idesc_half, 1u);                          // lo x x_hi
                     }
-                    umma_commit(ab_empty + 8 * st);  // arrives when these MMAs have read the buffers
+                    umma_commit(a_empty + 8 * st);   // arrive when these MMAs have read the buffers
+                    umma_commit(b_empty + 8 * bs);
                 }
                 umma_commit(t_full + 8 * tb);        // ... and when the unit's accumulators are complete
             }
         }
     } else if (warp >= kDequantWarp0) {
-        // ---------------- dequant: warp i decodes row tile i of the unit ----------------
-        const int rt_local = warp - kDequantWarp0;
+        // ---------------- dequant: warps 2 i, 2 i + 1 decode rows g and g + 8 of row tile i of the unit ----------------
+        const int rt_local = (warp - kDequantWarp0) >> 1, rr = (warp - kDequantWarp0) & 1;
         bool alive = true;
         uint32_t w_count = 0, a_count = 0;
         for (int u = blockIdx.x; u < units; u += gridDim.x) {
@@ -378,10 +401,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmArgs a, 
                 const unsigned char* tile = w_ring + (size_t)stage * lay.w_stage_bytes + (size_t)rt_local * tb;
                 for (int c = 0; c < kChunksPerTile; ++c, ++a_count) {
                     const uint32_t st = a_count & 1u;
-                    if (a_count >= 2u && alive) alive = mbar_wait(ab_empty + 8 * st, ((a_count >> 1) - 1u) & 1u, a.error_flag, 17);
+                    if (a_count >= 2u && alive) alive = mbar_wait(a_empty + 8 * st, ((a_count >> 1) - 1u) & 1u, a.error_flag, 17);
                     unsigned char* a_hi = a_buf + (size_t)st * kABytes;
-                    if (present) dequant_chunk(type, tile, c, a_hi, rt_local * kTileRows, lane);
-                    else zero_rows(a_hi, rt_local * kTileRows, lane);
+                    if (present) dequant_chunk(type, tile, c, a_hi, rt_local * kTileRows, rr, lane);
+                    else zero_rows(a_hi, rt_local * kTileRows + 8 * rr, lane);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic stores -> tensor-core reads
                     __syncwarp();
                     if (lane == 0) mbar_arrive(a_full + 8 * st);
@@ -398,7 +421,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmArgs a, 
             const uint32_t tb = unit_count & 1u;
             const UnitRef ur = unit_of(a, u);
             const GemvSegment& s = a.seg[ur.seg];
-            if (alive) alive = mbar_wait(t_full + 8 * tb, (unit_count >> 1) & 1u, a.error_flag, 18);
+            if (alive) alive = mbar_wait_relaxed(t_full + 8 * tb, (unit_count >> 1) & 1u, a.error_flag, 18);
             tc_fence_after();
             const int n_index = ur.rt0 * kTileRows + warp * 32 + lane;
             const bool valid = n_index < s.n;
@@ -420,6 +443,349 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmArgs a, 
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(t_empty + 8 * tb);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// =====================================================================================================
+// K-quant form (Q4_K, Q6_K; up to 64 members): the tensor core multiplies exact small integers.
+//
+// Q4_K:  w = d * (sc * q) - dmin * m      sc, m 6-bit and q 4-bit integers, d and dmin one binary16
+// Q6_K:  w = d * (sc * (q - 32))          sc 8-bit, q 6-bit                   pair per row and 256 inputs
+//
+// The A operand is the integer sc * q (at most 945, exact in binary16), made from the packed nibbles
+// with two instructions per pair of weights (byte permute into the pattern 1024 + q, one fused
+// multiply-add).  For Q6_K sc * (q - 32) can reach 4096, so sc = 16 sh + sl is split into two exact
+// planes, sl * v and (16 sh) * v, accumulated into the same tensor-memory columns.  The Q4_K minimum
+// enters as one more K = 16 MMA per 256 inputs: the eight group minima m against the eight group sums
+// of the activations.  Tensor memory then holds, per 256 inputs, exact-integer-weighted sums; four
+// epilogue warps fold them into F32 registers with the row's d (and dmin) once per k tile, in order,
+// with round-to-nearest FMAs - so the only roundings below F32 are the activations' hi + lo split.
+constexpr int kKqMaxMembers = 64;
+constexpr int kKqDequantWarps = kRowTilesPerUnit;   // one per row tile (the operand conversion is cheap)
+constexpr int kKqThreads = (kDequantWarp0 + kKqDequantWarps) * 32;
+constexpr int kA2Bytes = kRows * 16 * 2;   // the minima operand: 128 rows x 16 (8 groups + 8 zeros) halves
+
+struct KqLayout {
+    int w_stage_bytes, w_stages, b_bytes, b_stages, b2_bytes;
+    int cols, members_padded;
+};
+
+// 4 bytes (each < 64) -> the binary16 pairs (1024 + b0, 1024 + b1) and (1024 + b2, 1024 + b3)
+__device__ __forceinline__ void bytes_to_half_pairs(uint32_t b, __half2& p01, __half2& p23) {
+    const uint32_t x = __byte_perm(b, 0x64646464u, 0x4140), y = __byte_perm(b, 0x64646464u, 0x4342);
+    p01 = *reinterpret_cast<const __half2*>(&x);
+    p23 = *reinterpret_cast<const __half2*>(&y);
+}
+__device__ __forceinline__ void store_half4(unsigned char* dst, __half2 a, __half2 b) {
+    uint2 v;
+    v.x = *reinterpret_cast<const uint32_t*>(&a);
+    v.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(dst) = v;
+}
+
+// One 64-input chunk of one packed tile for the row g + 8 rr of each lane -> integer operand planes.
+// At chunk 0 the lane with t == 0 also leaves the row's d (and dmin) in `row_scales` and, for Q4_K,
+// lanes t = 0..3 write the row's eight group minima into the A2 operand.
+__device__ __forceinline__ void kq_chunk(int type, const unsigned char* tile, int c, unsigned char* a_planes, unsigned char* a2,
+                                         float2* row_scales, int row0, int rr, int lane) {
+    const int g = lane >> 2, t = lane & 3, row = g + 8 * rr, unit_row = row0 + row;
+    unsigned char* base = a_planes + (unit_row >> 3) * 128 + (unit_row & 7) * 16;
+    if (type == kQ4_K) {
+        const uint4 w = *reinterpret_cast<const uint4*>(tile + c * 512 + lane * 16);
+        const uint4 h = *reinterpret_cast<const uint4*>(tile + 2048 + row * 16);
+        const uint32_t sc4 = c < 2 ? (h.y & 0x3F3F3F3Fu) : ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u));
+        const int b0 = (2 * c) & 3;
+        const float sce = (float)((sc4 >> (8 * b0)) & 0xffu), sco = (float)((sc4 >> (8 * b0 + 8)) & 0xffu);
+        const __half2 se = __float2half2_rn(sce), so = __float2half2_rn(sco);
+        const __half2 be = __float2half2_rn(-1024.0f * sce), bo = __float2half2_rn(-1024.0f * sco);
+        if (c == 0) {
+            if (t == 0) {
+                row_scales[unit_row] = make_float2(__half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu))),
+                                                   __half2float(__ushort_as_half((unsigned short)(h.x >> 16))));
+            }
+            // minima of groups 2 t, 2 t + 1 as binary16, into the first 8-input block of A2
+            const uint32_t mlo = h.z & 0x3F3F3F3Fu, mhi = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+            const uint32_t m4 = t < 2 ? mlo : mhi;
+            const int mb = (2 * t) & 3;
+            const __half2 mm = __floats2half2_rn((float)((m4 >> (8 * mb)) & 0xffu), (float)((m4 >> (8 * mb + 8)) & 0xffu));
+            *reinterpret_cast<__half2*>(a2 + (unit_row >> 3) * 128 + (unit_row & 7) * 16 + 4 * t) = mm;
+        }
+        const uint32_t lo16 = rr == 0 ? w.x : w.z, hi16 = rr == 0 ? w.y : w.w;
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+            const uint32_t word = part == 0 ? lo16 : hi16;
+            __half2 e01, e23, o01, o23;
+            bytes_to_half_pairs(word & 0x0F0F0F0Fu, e01, e23);
+            bytes_to_half_pairs((word >> 4) & 0x0F0F0F0Fu, o01, o23);
+            const int k_e = part * 16 + 4 * t, k_o = 32 + k_e;
+            store_half4(base + (k_e >> 3) * kALbo + (k_e & 7) * 2, __hfma2(e01, se, be), __hfma2(e23, se, be));
+            store_half4(base + (k_o >> 3) * kALbo + (k_o & 7) * 2, __hfma2(o01, so, bo), __hfma2(o23, so, bo));
+        }
+    } else {
+        const int cc = c >> 1, v0 = (c & 1) * 2;
+        const uint4 qh = *reinterpret_cast<const uint4*>(tile + 2048 + cc * 512 + lane * 16);
+        const signed char* scales = reinterpret_cast<const signed char*>(tile + 3072 + row * 16);
+        if (c == 0 && t == 0) {
+            row_scales[unit_row] = make_float2(__half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(tile + 3328 + row * 2))), 0.0f);
+        }
+        const __half2 bias = __float2half2_rn(1056.0f);  // 1024 + 32
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint4 w = *reinterpret_cast<const uint4*>(tile + (cc * 2 + h) * 512 + lane * 16);
+            const uint32_t high = rr == 0 ? (h == 0 ? qh.x : qh.z) : (h == 0 ? qh.y : qh.w);
+#pragma unroll
+            for (int vv = 0; vv < 2; ++vv) {
+                const int v = v0 + vv, group = cc * 4 + v;
+                const uint32_t low = rr == 0 ? ((v & 1) ? w.y : w.x) : ((v & 1) ? w.w : w.z);
+                const uint32_t q4 = ((v < 2 ? low : low >> 4) & 0x0F0F0F0Fu) | (((high >> (2 * v)) & 0x03030303u) << 4);
+                const int sc = scales[group * 2 + h];
+                const __half2 sl = __float2half2_rn((float)(sc & 15)), sh = __float2half2_rn((float)((sc >> 4) * 16));
+                __half2 p01, p23;
+                bytes_to_half_pairs(q4, p01, p23);
+                const __half2 v01 = __hsub2(p01, bias), v23 = __hsub2(p23, bias);
+                const int k = vv * 32 + h * 16 + 4 * t;
+                unsigned char* dst = base + (k >> 3) * kALbo + (k & 7) * 2;
+                store_half4(dst, __hmul2(v01, sl), __hmul2(v23, sl));
+                store_half4(dst + kAHalfBytes, __hmul2(v01, sh), __hmul2(v23, sh));
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs a, const KqLayout lay, const int units) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_tiles = a.k / kTileCols;
+    const int a_bytes = 2 * kAHalfBytes;  // room for the two planes of Q6_K
+    unsigned char* w_ring = smem;
+    unsigned char* a_buf = w_ring + (size_t)lay.w_stages * lay.w_stage_bytes;        // [2][planes][16 KB]
+    unsigned char* a2_buf = a_buf + 2 * (size_t)a_bytes;                              // [2][kA2Bytes]
+    unsigned char* b_buf = a2_buf + 2 * kA2Bytes;                                     // [b_stages][b_bytes]
+    unsigned char* b2_buf = b_buf + (size_t)lay.b_stages * lay.b_bytes;               // [2][b2_bytes]
+    float2* row_scales = reinterpret_cast<float2*>(b2_buf + 2 * (size_t)lay.b2_bytes);  // [4][kRows]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(row_scales + 4 * kRows);
+    const uint32_t bars = smem_u32(tmem_slot + 4);
+    const uint32_t w_full = bars, w_empty = bars + 32, a_full = bars + 64, a_empty = bars + 80, t_full = bars + 96,
+                   t_empty = bars + 112, b2_full = bars + 128, b2_empty = bars + 144, b_full = bars + 160, b_empty = bars + 224;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < lay.w_stages; ++i) { mbar_init(w_full + 8 * i, 1); mbar_init(w_empty + 8 * i, kKqDequantWarps); }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(a_full + 8 * i, kKqDequantWarps);
+            mbar_init(a_empty + 8 * i, 1);
+            mbar_init(t_full + 8 * i, 1);
+            mbar_init(t_empty + 8 * i, kEpilogueWarps);
+            mbar_init(b2_full + 8 * i, 1);
+            mbar_init(b2_empty + 8 * i, 1);
+        }
+        for (int i = 0; i < lay.b_stages; ++i) { mbar_init(b_full + 8 * i, 1); mbar_init(b_empty + 8 * i, 1); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // The second 8-input block of the minima operand stays zero for the whole kernel.
+    for (int i = threadIdx.x; i < 2 * kA2Bytes / 16; i += kKqThreads) reinterpret_cast<uint4*>(a2_buf)[i] = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+    // tensor memory: main sums of k tile parity p at columns 128 p, minima sums at 256 + 128 p
+
+    if (warp == kProducerWarp) {
+        bool alive = true;
+        uint32_t w_count = 0, b_count = 0, kt_count = 0;
+        int wu = blockIdx.x, wkb = 0;
+        auto issue_w = [&]() {
+            if (wu >= units) return;
+            const UnitRef ur = unit_of(a, wu);
+            const GemvSegment& s = a.seg[ur.seg];
+            const uint32_t tb = (uint32_t)packed_tile_bytes(s.type);
+            const uint32_t stage = w_count % (uint32_t)lay.w_stages;
+            if (lane == 0) {
+                if (w_count >= (uint32_t)lay.w_stages && alive) {
+                    alive = mbar_wait_relaxed(w_empty + 8 * stage, ((w_count / (uint32_t)lay.w_stages) - 1u) & 1u, a.error_flag, 21);
+                }
+                const int present = min(kRowTilesPerUnit, s.row_tiles - ur.rt0);
+                mbar_expect_tx(w_full + 8 * stage, (uint32_t)present * tb);
+            }
+            __syncwarp();
+            if (lane < kRowTilesPerUnit && ur.rt0 + lane < s.row_tiles) {
+                bulk_g2s(smem_u32(w_ring + (size_t)stage * lay.w_stage_bytes + (size_t)lane * tb),
+                         s.data + ((size_t)(ur.rt0 + lane) * k_tiles + wkb) * tb, tb, w_full + 8 * stage);
+            }
+            ++w_count;
+            if (++wkb == k_tiles) { wkb = 0; wu += gridDim.x; }
+        };
+        issue_w();
+        if (lay.w_stages > 2) issue_w();
+        const size_t tile_stride = (size_t)kChunksPerTile * lay.b_bytes + lay.b2_bytes;  // one k tile of activations
+        for (int u = blockIdx.x; u < units; u += gridDim.x) {
+            for (int kb = 0; kb < k_tiles; ++kb, ++kt_count) {
+                if (lane == 0) {
+                    const signed char* src = a.chunks + (size_t)kb * tile_stride;
+                    for (int c = 0; c < kChunksPerTile; ++c, ++b_count) {
+                        const uint32_t nb = (uint32_t)lay.b_stages, bs = b_count % nb;
+                        if (b_count >= nb && alive) alive = mbar_wait_relaxed(b_empty + 8 * bs, ((b_count / nb) - 1u) & 1u, a.error_flag, 22);
+                        mbar_expect_tx(b_full + 8 * bs, (uint32_t)lay.b_bytes);
+                        bulk_g2s(smem_u32(b_buf + (size_t)bs * lay.b_bytes), src + (size_t)c * lay.b_bytes, (uint32_t)lay.b_bytes, b_full + 8 * bs);
+                    }
+                    {
+                        const uint32_t p = kt_count & 1u;
+                        if (kt_count >= 2u && alive) alive = mbar_wait_relaxed(b2_empty + 8 * p, ((kt_count >> 1) - 1u) & 1u, a.error_flag, 23);
+                        mbar_expect_tx(b2_full + 8 * p, (uint32_t)lay.b2_bytes);
+                        bulk_g2s(smem_u32(b2_buf + (size_t)p * lay.b2_bytes), src + (size_t)kChunksPerTile * lay.b_bytes, (uint32_t)lay.b2_bytes, b2_full + 8 * p);
+                    }
+                }
+                __syncwarp();
+                issue_w();
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        if (lane == 0) {
+            bool alive = true;
+            uint32_t count = 0, kt_count = 0;
+            const uint32_t idesc = umma_idesc(lay.cols);
+            const uint32_t b_lbo = (uint32_t)(lay.cols / 8) * 128u;
+            for (int u = blockIdx.x; u < units; u += gridDim.x) {
+                const bool q4k = a.seg[unit_of(a, u).seg].type == kQ4_K;
+                for (int kb = 0; kb < k_tiles; ++kb, ++kt_count) {
+                    const uint32_t p = kt_count & 1u;
+                    if (kt_count >= 2u && alive) alive = mbar_wait(t_empty + 8 * p, ((kt_count >> 1) - 1u) & 1u, a.error_flag, 24);
+                    tc_fence_after();
+                    const uint32_t d_main = tmem_base + p * 128u, d_min = tmem_base + 256u + p * 128u;
+                    for (int c = 0; c < kChunksPerTile; ++c, ++count) {
+                        const uint32_t st = count & 1u, nb = (uint32_t)lay.b_stages, bs = count % nb;
+                        if (alive) alive = mbar_wait(a_full + 8 * st, (count >> 1) & 1u, a.error_flag, 25);
+                        if (alive) alive = mbar_wait(b_full + 8 * bs, (count / nb) & 1u, a.error_flag, 26);
+                        tc_fence_after();
+                        const uint32_t a_addr = smem_u32(a_buf + (size_t)st * a_bytes);
+                        const uint32_t b_addr = smem_u32(b_buf + (size_t)bs * lay.b_bytes);
+#pragma unroll
+                        for (int s16 = 0; s16 < kChunkK / 16; ++s16) {
+                            const uint64_t db = umma_desc(b_addr + s16 * 2 * b_lbo, b_lbo, 128);
+                            umma_f16(d_main, umma_desc(a_addr + s16 * 2 * kALbo, kALbo, 128), db, idesc, (c | s16) != 0 ? 1u : 0u);
+                            if (!q4k) umma_f16(d_main, umma_desc(a_addr + kAHalfBytes + s16 * 2 * kALbo, kALbo, 128), db, idesc, 1u);
+                        }
+                        if (c == kChunksPerTile - 1) {
+                            // Q4_K: group minima x group sums of the activations (the chunk's a_full covers A2 as well)
+                            if (alive) alive = mbar_wait(b2_full + 8 * p, (kt_count >> 1) & 1u, a.error_flag, 27);
+                            tc_fence_after();
+                            if (q4k) {
+                                umma_f16(d_min, umma_desc(smem_u32(a2_buf + (size_t)p * kA2Bytes), kALbo, 128),
+                                         umma_desc(smem_u32(b2_buf + (size_t)p * lay.b2_bytes), b_lbo, 128), idesc, 0u);
+                            }
+                            umma_commit(b2_empty + 8 * p);
+                        }
+                        umma_commit(a_empty + 8 * st);
+                        umma_commit(b_empty + 8 * bs);
+                    }
+                    umma_commit(t_full + 8 * p);
+                }
+            }
+        }
+    } else if (warp >= kDequantWarp0) {
+        const int rt_local = warp - kDequantWarp0;
+        bool alive = true;
+        uint32_t w_count = 0, a_count = 0;
+        for (int u = blockIdx.x; u < units; u += gridDim.x) {
+            const UnitRef ur = unit_of(a, u);
+            const GemvSegment& s = a.seg[ur.seg];
+            const int type = s.type;
+            const bool present = ur.rt0 + rt_local < s.row_tiles;
+            const int tb = packed_tile_bytes(type);
+            for (int kb = 0; kb < k_tiles; ++kb, ++w_count) {
+                const uint32_t stage = w_count % (uint32_t)lay.w_stages;
+                if (alive) alive = mbar_wait(w_full + 8 * stage, (w_count / (uint32_t)lay.w_stages) & 1u, a.error_flag, 28);
+                const unsigned char* tile = w_ring + (size_t)stage * lay.w_stage_bytes + (size_t)rt_local * tb;
+                for (int c = 0; c < kChunksPerTile; ++c, ++a_count) {
+                    const uint32_t st = a_count & 1u;
+                    if (a_count >= 2u && alive) alive = mbar_wait(a_empty + 8 * st, ((a_count >> 1) - 1u) & 1u, a.error_flag, 29);
+                    unsigned char* planes = a_buf + (size_t)st * a_bytes;
+                    // A2 and the row scales of k tile w_count: written at chunk 0, consumed after chunk 3's MMAs.
+                    // A2's previous reader (two k tiles back) finished before this chunk's buffer was released.
+                    unsigned char* a2 = a2_buf + (size_t)(w_count & 1u) * kA2Bytes;
+                    float2* scales = row_scales + (size_t)(w_count & 3u) * kRows;
+                    if (present) {
+                        kq_chunk(type, tile, c, planes, a2, scales, rt_local * kTileRows, 0, lane);
+                        kq_chunk(type, tile, c, planes, a2, scales, rt_local * kTileRows, 1, lane);
+                    } else {
+                        for (int pl = 0; pl < (type == kQ4_K ? 1 : 2); ++pl) {
+                            zero_rows_plane(planes + (size_t)pl * kAHalfBytes, rt_local * kTileRows, lane);
+                            zero_rows_plane(planes + (size_t)pl * kAHalfBytes, rt_local * kTileRows + 8, lane);
+                        }
+                        if (c == 0 && lane < 16) {
+                            const int unit_row = rt_local * kTileRows + lane;
+                            scales[unit_row] = make_float2(0.0f, 0.0f);
+                            *reinterpret_cast<uint4*>(a2 + (unit_row >> 3) * 128 + (unit_row & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(a_full + 8 * st);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(w_empty + 8 * stage);
+            }
+        }
+    } else {
+        // ---------------- epilogue warps: fold each k tile into registers, store at the end of the unit ----------------
+        bool alive = true;
+        uint32_t kt_count = 0;
+        const int row = warp * 32 + lane;
+        for (int u = blockIdx.x; u < units; u += gridDim.x) {
+            const UnitRef ur = unit_of(a, u);
+            const GemvSegment& s = a.seg[ur.seg];
+            const bool q4k = s.type == kQ4_K;
+            float acc[kKqMaxMembers];
+#pragma unroll
+            for (int i = 0; i < kKqMaxMembers; ++i) acc[i] = 0.0f;
+            for (int kb = 0; kb < k_tiles; ++kb, ++kt_count) {
+                const uint32_t p = kt_count & 1u;
+                if (alive) alive = mbar_wait(t_full + 8 * p, (kt_count >> 1) & 1u, a.error_flag, 30);
+                tc_fence_after();
+                const float2 ds = row_scales[(size_t)(kt_count & 3u) * kRows + row];
+                const uint32_t t_main = tmem_base + p * 128u + ((uint32_t)(warp * 32) << 16), t_min = t_main + 256u;
+#pragma unroll
+                for (int m0 = 0; m0 < kKqMaxMembers; m0 += 16) {
+                    if (m0 < lay.members_padded) {
+                        float hi[16], lo[16];
+                        tmem_ld16(t_main + (uint32_t)m0, hi);
+                        tmem_ld16(t_main + (uint32_t)(lay.members_padded + m0), lo);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) acc[m0 + i] = fmaf(ds.x, hi[i] + lo[i], acc[m0 + i]);
+                        if (q4k) {
+                            tmem_ld16(t_min + (uint32_t)m0, hi);
+                            tmem_ld16(t_min + (uint32_t)(lay.members_padded + m0), lo);
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) acc[m0 + i] = fmaf(-ds.y, hi[i] + lo[i], acc[m0 + i]);
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(t_empty + 8 * p);
+            }
+            const int n_index = ur.rt0 * kTileRows + row;
+            if (n_index < s.n) {
+#pragma unroll
+                for (int m = 0; m < kKqMaxMembers; ++m) {
+                    if (m < a.members) {
+                        const float v = acc[m] * a.member_scale[m];
+                        float* y = s.y + (size_t)m * s.n + n_index;
+                        if (a.epilogue == kResidual) *y += v; else *y = v;
+                    }
+                }
+            }
         }
     }
     tc_fence_before();
@@ -494,24 +860,121 @@ __global__ void tc_chunks_kernel(const float* x, const int32_t* index, const flo
     *reinterpret_cast<uint4*>(base + (size_t)(mp + m) * 8) = *reinterpret_cast<const uint4*>(lo);
 }
 
+// K-quant form of the activations: per k tile (256 inputs) four chunks as above, then the group sums
+// [2 blocks][column][8 halves]: block 0 = sums of the eight 32-input groups, block 1 zeros.
+__global__ void tcq_chunks_kernel(const float* x, const int32_t* index, const float* norm_weight, int members, int mp,
+                                  int k, const float* scale_in, __half* chunks) {
+    const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per (member, 8 inputs)
+    const int kblocks = k / 8;
+    const bool live = id < (long long)mp * kblocks;
+    const int m = live ? (int)(id / kblocks) : 0, kblk = live ? (int)(id % kblocks) : 0;
+    const int cols = 2 * mp;
+    const size_t tile_halves = (size_t)kChunksPerTile * cols * kChunkK + (size_t)cols * 16;
+    __half hi[8], lo[8];
+    float sum = 0.0f;
+    if (live && m < members) {
+        const float* row = x + (size_t)(index ? index[m] : m) * k + (size_t)kblk * 8;
+        const float s = scale_in[m];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float v = row[i];
+            if (norm_weight != nullptr) v *= norm_weight[kblk * 8 + i];
+            v *= s;
+            hi[i] = __float2half_rn(v);
+            lo[i] = __float2half_rn(v - __half2float(hi[i]));
+            sum += __half2float(hi[i]) + __half2float(lo[i]);   // the sum of what the tensor core will see
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) hi[i] = lo[i] = __float2half_rn(0.0f);
+    }
+    // four consecutive threads hold one 32-input group
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (!live) return;
+    const int tile = kblk / 32, in_tile = kblk % 32, chunk = in_tile / 8, kb8 = in_tile % 8;
+    __half* base = chunks + (size_t)tile * tile_halves;
+    __half* cbase = base + (size_t)chunk * (cols * kChunkK) + (size_t)kb8 * (cols * 8);
+    *reinterpret_cast<uint4*>(cbase + (size_t)m * 8) = *reinterpret_cast<const uint4*>(hi);
+    *reinterpret_cast<uint4*>(cbase + (size_t)(mp + m) * 8) = *reinterpret_cast<const uint4*>(lo);
+    __half* sums = base + (size_t)kChunksPerTile * cols * kChunkK;
+    if ((in_tile & 3) == 0) {
+        const int group = in_tile / 4;
+        const __half sh = __float2half_rn(sum);
+        sums[(size_t)m * 8 + group] = sh;
+        sums[(size_t)(mp + m) * 8 + group] = __float2half_rn(sum - __half2float(sh));
+    }
+    if (in_tile == 0) {
+        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(sums + (size_t)cols * 8 + (size_t)m * 8) = zero;
+        *reinterpret_cast<uint4*>(sums + (size_t)cols * 8 + (size_t)(mp + m) * 8) = zero;
+    }
+}
+
 int padded_members(int members) { return (members + 15) / 16 * 16; }
 
 }  // namespace
 
-size_t tc_operand_bytes(int members, int k) { return (size_t)(k / kChunkK) * 2 * padded_members(members) * kChunkK * sizeof(__half); }
+size_t tc_operand_bytes(int members, int k) {
+    const size_t cols = 2 * (size_t)padded_members(members);
+    // chunks of 64 inputs, plus (K-quant form) 16 halves of group sums per column and k tile
+    return ((size_t)(k / kChunkK) * cols * kChunkK + (size_t)(k / kTileCols) * cols * 16) * sizeof(__half);
+}
+
+bool gemm_tc_kquant(const GemvSegment* segments, int n_segments, int members) {
+    if (members > kKqMaxMembers) return false;
+    for (int i = 0; i < n_segments; ++i) {
+        if (segments[i].type != kQ4_K && segments[i].type != kQ6_K) return false;
+    }
+    return true;
+}
 
 cudaError_t launch_to_tc_operand(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,
-                                 int members, int k, float eps, TcOperand out) {
-    if (members <= 0 || members > kGemmTcMaxMembers || k % kTileCols != 0) return cudaErrorInvalidValue;
+                                 int members, int k, float eps, bool kquant, TcOperand out) {
+    if (members <= 0 || members > (kquant ? kKqMaxMembers : kGemmTcMaxMembers) || k % kTileCols != 0) return cudaErrorInvalidValue;
     const int mp = padded_members(members);
     tc_scale_kernel<<<members, 256, 0, stream>>>(x, index, norm_weight, k, eps, out.scale_in, out.member_scale);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     const long long threads = (long long)mp * (k / 8);
-    tc_chunks_kernel<<<(unsigned int)((threads + 255) / 256), 256, 0, stream>>>(x, index, norm_weight, members, mp, k,
-                                                                              out.scale_in, out.chunks);
+    const unsigned int blocks = (unsigned int)((threads + 255) / 256);
+    if (kquant) tcq_chunks_kernel<<<blocks, 256, 0, stream>>>(x, index, norm_weight, members, mp, k, out.scale_in, out.chunks);
+    else tc_chunks_kernel<<<blocks, 256, 0, stream>>>(x, index, norm_weight, members, mp, k, out.scale_in, out.chunks);
     return cudaGetLastError();
 }
+
+namespace {
+
+cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units, int tile) {
+    KqLayout lay{};
+    lay.members_padded = padded_members(args.members);
+    lay.cols = 2 * lay.members_padded;
+    lay.b_bytes = lay.cols * kChunkK * (int)sizeof(__half);
+    lay.b2_bytes = lay.cols * 16 * (int)sizeof(__half);
+    lay.w_stage_bytes = kRowTilesPerUnit * tile;
+    const size_t budget = 220 * 1024;
+    size_t fixed = (size_t)4 * kAHalfBytes + (size_t)2 * kA2Bytes + (size_t)2 * lay.b_bytes + (size_t)2 * lay.b2_bytes +
+                   (size_t)4 * kRows * sizeof(float2) + 16 + 320;
+    lay.w_stages = (int)std::min<size_t>(3, (budget - fixed) / (size_t)lay.w_stage_bytes);
+    if (lay.w_stages < 2) return cudaErrorInvalidValue;
+    lay.b_stages = 2 + (int)std::min<size_t>(6, (budget - fixed - (size_t)lay.w_stages * lay.w_stage_bytes) / (size_t)lay.b_bytes);
+    fixed += (size_t)(lay.b_stages - 2) * lay.b_bytes;
+    const size_t smem = fixed + (size_t)lay.w_stages * lay.w_stage_bytes;
+    static bool configured = false;
+    static int sm_count = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+        if (e != cudaSuccess) return e;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+        configured = true;
+    }
+    gemm_tcq_kernel<<<std::min(units, sm_count), kKqThreads, smem, stream>>>(args, lay, units);
+    return cudaGetLastError();
+}
+
+}  // namespace
 
 cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmArgs& args) {
     if (args.members < 1 || args.members > kGemmTcMaxMembers || args.k % kTileCols != 0) return cudaErrorInvalidValue;
@@ -524,15 +987,23 @@ cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmArgs& args) {
         tile = std::max(tile, b);
     }
     if (units <= 0) return cudaSuccess;
+    if (args.kquant) {
+        if (!gemm_tc_kquant(args.seg, args.n_segments, args.members)) return cudaErrorInvalidValue;
+        return launch_gemm_tcq(stream, args, units, tile);
+    }
     TcLayout lay{};
     lay.members_padded = padded_members(args.members);
     lay.cols = 2 * lay.members_padded;
     lay.b_bytes = lay.cols * kChunkK * (int)sizeof(__half);
     lay.w_stage_bytes = kRowTilesPerUnit * tile;
-    const size_t fixed = (size_t)2 * kABytes + (size_t)2 * lay.b_bytes + 16 + 160;
+    // Two activation chunks at least; what is left after three weight stages deepens the activation ring
+    // (its copies have a longer way than the tensor core needs for a chunk).
     const size_t budget = 220 * 1024;
+    size_t fixed = (size_t)2 * kABytes + (size_t)2 * lay.b_bytes + 16 + 320;
     lay.w_stages = (int)std::min<size_t>(3, (budget - fixed) / (size_t)lay.w_stage_bytes);
     if (lay.w_stages < 2) return cudaErrorInvalidValue;
+    lay.b_stages = 2 + (int)std::min<size_t>(6, (budget - fixed - (size_t)lay.w_stages * lay.w_stage_bytes) / (size_t)lay.b_bytes);
+    fixed += (size_t)(lay.b_stages - 2) * lay.b_bytes;
     const size_t smem = fixed + (size_t)lay.w_stages * lay.w_stage_bytes;
     static bool configured = false;
     static int sm_count = 0;

@@ -162,6 +162,7 @@ struct GemmArgs {
     const float* member_scale;
     int epilogue;         // GemvEpilogue; kSwiGLU writes seg[0].y = silu(gate) * up
     int* error_flag;
+    int kquant;           // tensor-memory kernels: the activations are in the K-quant form (see TcOperand)
 };
 
 cudaError_t launch_gemm_imma(cudaStream_t stream, const GemmArgs& args);
@@ -181,9 +182,15 @@ struct TcOperand {
 };
 
 size_t tc_operand_bytes(int members, int k);
+// True when the launch can take the K-quant form: only Q4_K / Q6_K matrices and at most 64 members.
+// There the tensor core multiplies the blocks' exact integers (scale x quant) and the F32 super-block
+// scales are applied per 256 inputs; the activations then carry, per k tile, the sums of their eight
+// 32-input groups behind the four chunks (`kquant` below).  Otherwise every weight is decoded to F32
+// and split into a binary16 pair.
+bool gemm_tc_kquant(const GemvSegment* segments, int n_segments, int members);
 cudaError_t launch_to_tc_operand(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,
-                                 int members, int k, float eps, TcOperand out);
-// GemmArgs::chunks points at TcOperand::chunks; epilogue kStore or kResidual.
+                                 int members, int k, float eps, bool kquant, TcOperand out);
+// GemmArgs::chunks points at TcOperand::chunks, GemmArgs::kquant says which form; epilogue kStore or kResidual.
 cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmArgs& args);
 
 // Scratch shared by the step kernels: per-span attention accumulators.

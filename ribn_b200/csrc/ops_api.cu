@@ -144,17 +144,21 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
         int* d_err = s.alloc<int>(1);
         OP_PTR(op.dig); OP_PTR(op.sx); OP_PTR(op.sxs16); OP_PTR(d_err);
         OP_TRY(cudaMemsetAsync(d_err, 0, sizeof(int), s.stream));
-        if (variant == 3) {
-            // the tensor-memory kernel, in groups of up to kGemmTcMaxMembers members
+        if (variant == 3 || variant == 4) {
+            // the tensor-memory kernels
             TcOperand top;
-            const int group = std::min(members, kGemmTcMaxMembers);
+            const GemvSegment probe{d_w, type, (int)rows, (int)((rows + kTileRows - 1) / kTileRows), d_y};
+            // variant 3: K-quant form where it applies (at most 64 members per launch); variant 4: always the generic form
+            const bool kquant = variant == 3 && gemm_tc_kquant(&probe, 1, 1);
+            const int per_launch = kquant ? 64 : kGemmTcMaxMembers;
+            const int group = std::min(members, per_launch);
             top.chunks = (__half*)s.alloc<unsigned char>(tc_operand_bytes(group, (int)cols));
             top.scale_in = s.alloc<float>((size_t)group);
             top.member_scale = s.alloc<float>((size_t)group);
             OP_PTR(top.chunks); OP_PTR(top.scale_in); OP_PTR(top.member_scale);
-            for (int m0 = 0; m0 < members; m0 += kGemmTcMaxMembers) {
-                const int m = std::min(kGemmTcMaxMembers, members - m0);
-                OP_TRY(launch_to_tc_operand(s.stream, d_x + (size_t)m0 * cols, nullptr, nullptr, m, (int)cols, 0.0f, top));
+            for (int m0 = 0; m0 < members; m0 += per_launch) {
+                const int m = std::min(per_launch, members - m0);
+                OP_TRY(launch_to_tc_operand(s.stream, d_x + (size_t)m0 * cols, nullptr, nullptr, m, (int)cols, 0.0f, kquant, top));
                 GemmArgs a{};
                 a.n_segments = 1;
                 a.seg[0] = GemvSegment{d_w, type, (int)rows, (int)((rows + kTileRows - 1) / kTileRows),
@@ -164,6 +168,7 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
                 a.chunks = (const signed char*)top.chunks; a.member_scale = top.member_scale;
                 a.epilogue = kStore;
                 a.error_flag = d_err;
+                a.kquant = kquant ? 1 : 0;
                 OP_TRY(launch_gemm_tc(s.stream, a));
             }
         } else if (variant == 2) {

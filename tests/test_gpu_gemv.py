@@ -150,26 +150,33 @@ def test_batched_kernel_random_bytes_and_member_independence(ops, kind):
     assert np.all(zero == 0.0)
 
 
+@pytest.mark.parametrize("variant", [3, 4])
 @pytest.mark.parametrize("kind", [H.Q4_K, H.Q6_K, H.Q8_0])
 @pytest.mark.parametrize("rows,cols,members", [(16, 256, 1), (130, 512, 5), (256, 1024, 64), (300, 4096, 128),
                                                (128, 12288, 33), (64, 768, 150)])
-def test_tensor_memory_kernel_against_oracle(ops, kind, rows, cols, members):
-    # tcgen05 dequant-GEMM: weights and activations enter the tensor core as binary16 hi + lo pairs and
-    # the whole K is accumulated in tensor memory; the tensor core's F32 accumulation is not
-    # round-to-nearest, so the error grows with K (about 3e-5 of the largest output at K = 12288).
+def test_tensor_memory_kernels_against_oracle(ops, kind, rows, cols, members, variant):
+    # tcgen05 kernels.  K-quant form (variant 3 on Q4_K / Q6_K): the tensor core multiplies the blocks'
+    # exact integers and the F32 scales are applied per 256 inputs with round-to-nearest FMAs.
+    # Decode-and-split form (variant 4, and Q8_0): weights and activations enter as binary16 hi + lo
+    # pairs and the whole K is accumulated in tensor memory, whose F32 accumulation is not
+    # round-to-nearest: the error grows with K (about 3e-5 of the largest output at K = 12288).
     # The reference's own tolerance for this operator is 1e-3 absolute (cuda_reference.rs:690-846).
+    if variant == 4 and kind == H.Q8_0:
+        pytest.skip("variant 3 already takes the decode-and-split form for Q8_0")
     rng = np.random.default_rng(rows * 13 + cols + kind + members)
     enc = H.quantize(kind, rng.normal(0, 0.02, size=(rows, cols)).astype(np.float32))
     xs = (rng.normal(0, 1, size=(members, cols)) * rng.uniform(0.01, 100, size=(members, 1))).astype(np.float32)
-    got = ops.gemv(kind, enc, rows, cols, xs, variant=3)
+    got = ops.gemv(kind, enc, rows, cols, xs, variant=variant)
     want = np.stack([orc.gemv(kind, enc, cols, rows, xs[m]) for m in range(members)])
+    tolerance = 2e-5 if (variant == 3 and kind != H.Q8_0) else 1e-4
     for m in range(members):
         scale = float(np.max(np.abs(want[m]))) + 1e-6
-        assert np.max(np.abs(got[m] - want[m])) / scale < 1e-4, m
+        assert np.max(np.abs(got[m] - want[m])) / scale < tolerance, m
 
 
+@pytest.mark.parametrize("variant", [3, 4])
 @pytest.mark.parametrize("kind", [H.Q4_K, H.Q6_K, H.Q8_0])
-def test_tensor_memory_kernel_random_bytes_and_member_independence(ops, kind):
+def test_tensor_memory_kernels_random_bytes_and_member_independence(ops, kind, variant):
     rng = np.random.default_rng(kind + 177)
     elems, size = H.BLOCK[kind]
     rows, cols = 144, 1024
@@ -177,12 +184,12 @@ def test_tensor_memory_kernel_random_bytes_and_member_independence(ops, kind):
     for off in ([0] if kind == H.Q8_0 else [0, 2] if kind == H.Q4_K else [208]):
         blocks[:, off + 1] = (blocks[:, off + 1] & 0x83) | 0x10
     xs = rng.normal(0, 1, size=(20, cols)).astype(np.float32)
-    got = ops.gemv(kind, blocks, rows, cols, xs, variant=3)
+    got = ops.gemv(kind, blocks, rows, cols, xs, variant=variant)
     want = np.stack([orc.gemv(kind, blocks, cols, rows, xs[m]) for m in range(20)])
     assert np.max(np.abs(got - want)) / np.max(np.abs(want)) < 1e-4
-    alone = ops.gemv(kind, blocks, rows, cols, xs[[5, 0, 13]], variant=3)
+    alone = ops.gemv(kind, blocks, rows, cols, xs[[5, 0, 13]], variant=variant)
     assert np.array_equal(alone.view(np.uint32), got[[5, 0, 13]].view(np.uint32))
-    zero = ops.gemv(kind, blocks, rows, cols, np.zeros((3, cols), np.float32), variant=3)
+    zero = ops.gemv(kind, blocks, rows, cols, np.zeros((3, cols), np.float32), variant=variant)
     assert np.all(zero == 0.0)
-    huge = ops.gemv(kind, blocks, rows, cols, xs[:3] * np.float32(1e9), variant=3)
+    huge = ops.gemv(kind, blocks, rows, cols, xs[:3] * np.float32(1e9), variant=variant)
     assert np.max(np.abs(huge / np.float32(1e9) - want[:3])) / np.max(np.abs(want)) < 1e-4
