@@ -312,6 +312,77 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_serving(args):
+    """Continuous batching under Poisson arrivals through the engine (scheduling rules of the reference's
+    Engine restated in ribn_b200/engine.py): prompts ~U[128, 2048], outputs ~U[64, 512], 64 active
+    requests, 2048-token prefill chunks, 16-token KV pages.  Reports whole-job generated tok/s and the
+    time to first token (planned arrival -> first token, as the reference's serving bench measures it)."""
+    rank, world, local, dist = dist_setup(args.gpus)
+    import ribn_b200
+    from ribn_b200.engine import Engine, EngineConfig, SchedulePolicy, TokenRequest
+    model = MODELS[args.model]
+    rng = np.random.default_rng(0xC3 + rank)
+    n = args.requests
+    prompt_hi = min(2048, args.serving_prompt_max)
+    prompts = rng.integers(min(128, prompt_hi), prompt_hi + 1, size=n)
+    outputs = rng.integers(min(64, args.serving_output_max), args.serving_output_max + 1, size=n)
+    arrivals = np.cumsum(rng.exponential(1.0 / args.arrival_rate, size=n))
+    active = min(64, n)
+    chunk = min(2048, prompt_hi)
+    ex = ribn_b200.QwenB200(model, context_tokens=int(prompts.max() + outputs.max() + 16), max_sequences=active,
+                            max_batch_tokens=chunk + active, device=local, flags=0)
+    ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q4_K_M)
+    ex.finalize()
+    engine = Engine(ex, EngineConfig(max_active_requests=active, max_queued_requests=n),
+                    SchedulePolicy(max_batch_tokens=chunk + active, prefill_chunk_tokens=chunk, decode_tokens=1,
+                                   max_decode_only_steps=8))
+    tokens = [rng.integers(0, model["vocab"], size=int(p), dtype=np.uint32) for p in prompts]
+    barrier(dist, local)
+    with ClockSampler(local) as clocks:
+        t0 = time.perf_counter()
+        nxt, ids = 0, {}
+        while nxt < n or not engine.idle():
+            now = time.perf_counter() - t0
+            while nxt < n and arrivals[nxt] <= now:
+                ids[engine.enqueue(TokenRequest(tokens[nxt], int(outputs[nxt])))] = nxt
+                nxt += 1
+            if not engine.step():
+                time.sleep(50e-6 if engine.in_flight else min(1e-3, max(0.0, arrivals[nxt] - now)) if nxt < n else 50e-6)
+        ex.synchronize()
+        makespan = time.perf_counter() - t0
+    barrier(dist, local)
+    ttft, itl, generated = [], [], 0
+    for rid, slot in engine.finished.items():
+        i = ids[rid]
+        generated += len(slot.output)
+        if slot.token_times:
+            ttft.append(slot.token_times[0] - t0 - arrivals[i])
+            itl.extend(np.diff(slot.token_times).tolist())
+    makespan = all_max(dist, makespan, local)
+    out = {
+        "metric": f"{args.model} Q4_K_M continuous-batching generated tok/s (per GPU x replicas)",
+        "value": world * generated / makespan, "unit": "tok/s", "n_gpus": world, "steps": engine.steps, "warmup": 0,
+        "ms_per_step": makespan / max(engine.steps, 1) * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "u8 x s8 / f16 tensor-core products over Q4_K,Q6_K weights, f32 scales and accumulation, f16 KV",
+        "data": "synthetic",
+        "config": {"workload": f"{args.model} Q4_K_M-style serving: {n} requests per GPU, Poisson arrivals "
+                               f"{args.arrival_rate}/s, prompts U[{min(128, prompt_hi)},{prompt_hi}], outputs "
+                               f"U[{min(64, args.serving_output_max)},{args.serving_output_max}], {active} active, "
+                               f"{chunk}-token prefill chunks, 16-token KV pages",
+                   "parallelism": f"replicas x{world}"},
+        "ttft_ms": {"p50": float(np.percentile(ttft, 50) * 1e3), "p95": float(np.percentile(ttft, 95) * 1e3)},
+        "itl_ms": {"p50": float(np.percentile(itl, 50) * 1e3), "p95": float(np.percentile(itl, 95) * 1e3)} if itl else None,
+        "prompt_tokens": int(prompts.sum()), "generated_tokens": int(generated), "makespan_s": makespan,
+        "clocks": clocks.summary(),
+    }
+    ex.close()
+    if rank == 0:
+        print(json.dumps(out))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def run_reference(args):
     """The reference's host CPU decoder (restated: oracle/oracle.c) on the GPU box's host cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -365,11 +436,19 @@ def main():
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / full-size parity leg")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
+                    help="decode: steady batch-1 / batch-N decode steps (the headline); serving: Poisson arrivals through the engine")
+    ap.add_argument("--requests", type=int, default=96, help="serving: requests per GPU")
+    ap.add_argument("--arrival-rate", type=float, default=8.0, help="serving: Poisson arrival rate, requests per second per GPU")
+    ap.add_argument("--serving-prompt-max", type=int, default=2048)
+    ap.add_argument("--serving-output-max", type=int, default=512)
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "serving":
+        run_serving(args)
     else:
         run_ours(args)
 

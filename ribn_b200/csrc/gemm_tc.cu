@@ -27,6 +27,13 @@
 #include "blocks.cuh"
 #include "gemv.cuh"
 
+// Measurement aid (0 in the shipped build), K-quant kernel only: 1 = conversion warps skip their work,
+// 2 = no MMAs are issued, 3 = no activation chunk copies, 4 = the epilogue warps skip the fold,
+// 5 = all of these (barrier traffic and weight copies only).
+#ifndef RIBN_TC_PROBE
+#define RIBN_TC_PROBE 0
+#endif
+
 namespace ribn {
 
 namespace {
@@ -469,12 +476,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmArgs a, 
 // with round-to-nearest FMAs - so the only roundings below F32 are the activations' hi + lo split.
 constexpr int kKqMaxMembers = 64;
 constexpr int kKqDequantWarps = kRowTilesPerUnit;   // one per row tile (the operand conversion is cheap)
-constexpr int kKqThreads = (kDequantWarp0 + kKqDequantWarps) * 32;
+constexpr int kKqChunkWarp0 = kDequantWarp0 + kKqDequantWarps;   // two warps that only copy activation chunks
+constexpr int kKqThreads = (kKqChunkWarp0 + 2) * 32;
 constexpr int kA2Bytes = kRows * 16 * 2;   // the minima operand: 128 rows x 16 (8 groups + 8 zeros) halves
 
 struct KqLayout {
     int w_stage_bytes, w_stages, b_bytes, b_stages, b2_bytes;
-    int cols, members_padded;
+    int cols, members_padded, a_stages, a_planes;
 };
 
 // 4 bytes (each < 64) -> the binary16 pairs (1024 + b0, 1024 + b1) and (1024 + b2, 1024 + b3)
@@ -563,23 +571,23 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_tiles = a.k / kTileCols;
-    const int a_bytes = 2 * kAHalfBytes;  // room for the two planes of Q6_K
+    const int a_bytes = lay.a_planes * kAHalfBytes;  // per stage: two planes when the launch has Q6_K units
+    const uint32_t na = (uint32_t)lay.a_stages;
     unsigned char* w_ring = smem;
     unsigned char* a_buf = w_ring + (size_t)lay.w_stages * lay.w_stage_bytes;        // [2][planes][16 KB]
-    unsigned char* a2_buf = a_buf + 2 * (size_t)a_bytes;                              // [2][kA2Bytes]
+    unsigned char* a2_buf = a_buf + (size_t)lay.a_stages * a_bytes;                   // [2][kA2Bytes]
     unsigned char* b_buf = a2_buf + 2 * kA2Bytes;                                     // [b_stages][b_bytes]
     unsigned char* b2_buf = b_buf + (size_t)lay.b_stages * lay.b_bytes;               // [2][b2_bytes]
     float2* row_scales = reinterpret_cast<float2*>(b2_buf + 2 * (size_t)lay.b2_bytes);  // [4][kRows]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(row_scales + 4 * kRows);
     const uint32_t bars = smem_u32(tmem_slot + 4);
-    const uint32_t w_full = bars, w_empty = bars + 32, a_full = bars + 64, a_empty = bars + 80, t_full = bars + 96,
-                   t_empty = bars + 112, b2_full = bars + 128, b2_empty = bars + 144, b_full = bars + 160, b_empty = bars + 224;
+    const uint32_t w_full = bars, w_empty = bars + 32, a_full = bars + 64, a_empty = bars + 96, t_full = bars + 128,
+                   t_empty = bars + 144, b2_full = bars + 160, b2_empty = bars + 176, b_full = bars + 192, b_empty = bars + 256;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < lay.w_stages; ++i) { mbar_init(w_full + 8 * i, 1); mbar_init(w_empty + 8 * i, kKqDequantWarps); }
+        for (int i = 0; i < lay.a_stages; ++i) { mbar_init(a_full + 8 * i, kKqDequantWarps); mbar_init(a_empty + 8 * i, 1); }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(a_full + 8 * i, kKqDequantWarps);
-            mbar_init(a_empty + 8 * i, 1);
             mbar_init(t_full + 8 * i, 1);
             mbar_init(t_empty + 8 * i, kEpilogueWarps);
             mbar_init(b2_full + 8 * i, 1);
@@ -603,7 +611,7 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
 
     if (warp == kProducerWarp) {
         bool alive = true;
-        uint32_t w_count = 0, b_count = 0, kt_count = 0;
+        uint32_t w_count = 0, kt_count = 0;
         int wu = blockIdx.x, wkb = 0;
         auto issue_w = [&]() {
             if (wu >= units) return;
@@ -632,22 +640,36 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
         for (int u = blockIdx.x; u < units; u += gridDim.x) {
             for (int kb = 0; kb < k_tiles; ++kb, ++kt_count) {
                 if (lane == 0) {
-                    const signed char* src = a.chunks + (size_t)kb * tile_stride;
-                    for (int c = 0; c < kChunksPerTile; ++c, ++b_count) {
-                        const uint32_t nb = (uint32_t)lay.b_stages, bs = b_count % nb;
-                        if (b_count >= nb && alive) alive = mbar_wait_relaxed(b_empty + 8 * bs, ((b_count / nb) - 1u) & 1u, a.error_flag, 22);
-                        mbar_expect_tx(b_full + 8 * bs, (uint32_t)lay.b_bytes);
-                        bulk_g2s(smem_u32(b_buf + (size_t)bs * lay.b_bytes), src + (size_t)c * lay.b_bytes, (uint32_t)lay.b_bytes, b_full + 8 * bs);
-                    }
-                    {
-                        const uint32_t p = kt_count & 1u;
-                        if (kt_count >= 2u && alive) alive = mbar_wait_relaxed(b2_empty + 8 * p, ((kt_count >> 1) - 1u) & 1u, a.error_flag, 23);
-                        mbar_expect_tx(b2_full + 8 * p, (uint32_t)lay.b2_bytes);
-                        bulk_g2s(smem_u32(b2_buf + (size_t)p * lay.b2_bytes), src + (size_t)kChunksPerTile * lay.b_bytes, (uint32_t)lay.b2_bytes, b2_full + 8 * p);
-                    }
+                    const uint32_t p = kt_count & 1u;
+                    if (kt_count >= 2u && alive) alive = mbar_wait_relaxed(b2_empty + 8 * p, ((kt_count >> 1) - 1u) & 1u, a.error_flag, 23);
+                    mbar_expect_tx(b2_full + 8 * p, (uint32_t)lay.b2_bytes);
+                    bulk_g2s(smem_u32(b2_buf + (size_t)p * lay.b2_bytes),
+                             a.chunks + (size_t)kb * tile_stride + (size_t)kChunksPerTile * lay.b_bytes, (uint32_t)lay.b2_bytes, b2_full + 8 * p);
                 }
                 __syncwarp();
                 issue_w();
+            }
+        }
+    } else if (warp >= kKqChunkWarp0) {
+        // ---------------- activation chunks: a bulk copy keeps its issuing thread busy for a few hundred
+        // nanoseconds, so the chunks of a k tile alternate between two copying warps ----------------
+        if (lane == 0) {
+            bool alive = true;
+            const int which = warp - kKqChunkWarp0;
+            const size_t tile_stride = (size_t)kChunksPerTile * lay.b_bytes + lay.b2_bytes;
+            uint32_t b_count = 0;
+            for (int u = blockIdx.x; u < units; u += gridDim.x) {
+                for (int kb = 0; kb < k_tiles; ++kb) {
+                    const signed char* src = a.chunks + (size_t)kb * tile_stride;
+                    for (int c = 0; c < kChunksPerTile; ++c, ++b_count) {
+                        if ((c & 1) != which) continue;
+                        const uint32_t nb = (uint32_t)lay.b_stages, bs = b_count % nb;
+                        if (b_count >= nb && alive) alive = mbar_wait_relaxed(b_empty + 8 * bs, ((b_count / nb) - 1u) & 1u, a.error_flag, 22);
+                        if (RIBN_TC_PROBE == 3 || RIBN_TC_PROBE == 5) { mbar_arrive(b_full + 8 * bs); continue; }
+                        mbar_expect_tx(b_full + 8 * bs, (uint32_t)lay.b_bytes);
+                        bulk_g2s(smem_u32(b_buf + (size_t)bs * lay.b_bytes), src + (size_t)c * lay.b_bytes, (uint32_t)lay.b_bytes, b_full + 8 * bs);
+                    }
+                }
             }
         }
     } else if (warp == kMmaWarp) {
@@ -664,14 +686,15 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                     tc_fence_after();
                     const uint32_t d_main = tmem_base + p * 128u, d_min = tmem_base + 256u + p * 128u;
                     for (int c = 0; c < kChunksPerTile; ++c, ++count) {
-                        const uint32_t st = count & 1u, nb = (uint32_t)lay.b_stages, bs = count % nb;
-                        if (alive) alive = mbar_wait(a_full + 8 * st, (count >> 1) & 1u, a.error_flag, 25);
+                        const uint32_t st = count % na, nb = (uint32_t)lay.b_stages, bs = count % nb;
+                        if (alive) alive = mbar_wait(a_full + 8 * st, (count / na) & 1u, a.error_flag, 25);
                         if (alive) alive = mbar_wait(b_full + 8 * bs, (count / nb) & 1u, a.error_flag, 26);
                         tc_fence_after();
                         const uint32_t a_addr = smem_u32(a_buf + (size_t)st * a_bytes);
                         const uint32_t b_addr = smem_u32(b_buf + (size_t)bs * lay.b_bytes);
 #pragma unroll
                         for (int s16 = 0; s16 < kChunkK / 16; ++s16) {
+                            if (RIBN_TC_PROBE == 2 || RIBN_TC_PROBE == 5) break;
                             const uint64_t db = umma_desc(b_addr + s16 * 2 * b_lbo, b_lbo, 128);
                             umma_f16(d_main, umma_desc(a_addr + s16 * 2 * kALbo, kALbo, 128), db, idesc, (c | s16) != 0 ? 1u : 0u);
                             if (!q4k) umma_f16(d_main, umma_desc(a_addr + kAHalfBytes + s16 * 2 * kALbo, kALbo, 128), db, idesc, 1u);
@@ -680,7 +703,7 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                             // Q4_K: group minima x group sums of the activations (the chunk's a_full covers A2 as well)
                             if (alive) alive = mbar_wait(b2_full + 8 * p, (kt_count >> 1) & 1u, a.error_flag, 27);
                             tc_fence_after();
-                            if (q4k) {
+                            if (q4k && RIBN_TC_PROBE != 2 && RIBN_TC_PROBE != 5) {
                                 umma_f16(d_min, umma_desc(smem_u32(a2_buf + (size_t)p * kA2Bytes), kALbo, 128),
                                          umma_desc(smem_u32(b2_buf + (size_t)p * lay.b2_bytes), b_lbo, 128), idesc, 0u);
                             }
@@ -693,7 +716,7 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                 }
             }
         }
-    } else if (warp >= kDequantWarp0) {
+    } else if (warp >= kDequantWarp0 && warp < kKqChunkWarp0) {
         const int rt_local = warp - kDequantWarp0;
         bool alive = true;
         uint32_t w_count = 0, a_count = 0;
@@ -708,14 +731,16 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                 if (alive) alive = mbar_wait(w_full + 8 * stage, (w_count / (uint32_t)lay.w_stages) & 1u, a.error_flag, 28);
                 const unsigned char* tile = w_ring + (size_t)stage * lay.w_stage_bytes + (size_t)rt_local * tb;
                 for (int c = 0; c < kChunksPerTile; ++c, ++a_count) {
-                    const uint32_t st = a_count & 1u;
-                    if (a_count >= 2u && alive) alive = mbar_wait(a_empty + 8 * st, ((a_count >> 1) - 1u) & 1u, a.error_flag, 29);
+                    const uint32_t st = a_count % na;
+                    if (a_count >= na && alive) alive = mbar_wait(a_empty + 8 * st, ((a_count / na) - 1u) & 1u, a.error_flag, 29);
                     unsigned char* planes = a_buf + (size_t)st * a_bytes;
                     // A2 and the row scales of k tile w_count: written at chunk 0, consumed after chunk 3's MMAs.
-                    // A2's previous reader (two k tiles back) finished before this chunk's buffer was released.
+                    // A2's previous reader (two k tiles back) was issued before the MMAs whose completion released this
+                    // chunk's buffer (at most four chunks back), so it has finished too.
                     unsigned char* a2 = a2_buf + (size_t)(w_count & 1u) * kA2Bytes;
                     float2* scales = row_scales + (size_t)(w_count & 3u) * kRows;
-                    if (present) {
+                    if (RIBN_TC_PROBE == 1 || RIBN_TC_PROBE == 5) {
+                    } else if (present) {
                         kq_chunk(type, tile, c, planes, a2, scales, rt_local * kTileRows, 0, lane);
                         kq_chunk(type, tile, c, planes, a2, scales, rt_local * kTileRows, 1, lane);
                     } else {
@@ -757,7 +782,7 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                 const uint32_t t_main = tmem_base + p * 128u + ((uint32_t)(warp * 32) << 16), t_min = t_main + 256u;
 #pragma unroll
                 for (int m0 = 0; m0 < kKqMaxMembers; m0 += 16) {
-                    if (m0 < lay.members_padded) {
+                    if (m0 < lay.members_padded && RIBN_TC_PROBE != 4 && RIBN_TC_PROBE != 5) {
                         float hi[16], lo[16];
                         tmem_ld16(t_main + (uint32_t)m0, hi);
                         tmem_ld16(t_main + (uint32_t)(lay.members_padded + m0), lo);
@@ -953,8 +978,13 @@ cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units
     lay.b2_bytes = lay.cols * 16 * (int)sizeof(__half);
     lay.w_stage_bytes = kRowTilesPerUnit * tile;
     const size_t budget = 220 * 1024;
+    // 64 KB of A stages: four single-plane stages when every unit is Q4_K, else two two-plane stages
+    bool all_q4k = true;
+    for (int i = 0; i < args.n_segments; ++i) all_q4k = all_q4k && args.seg[i].type == kQ4_K;
+    lay.a_planes = all_q4k ? 1 : 2;
+    lay.a_stages = all_q4k ? 4 : 2;
     size_t fixed = (size_t)4 * kAHalfBytes + (size_t)2 * kA2Bytes + (size_t)2 * lay.b_bytes + (size_t)2 * lay.b2_bytes +
-                   (size_t)4 * kRows * sizeof(float2) + 16 + 320;
+                   (size_t)4 * kRows * sizeof(float2) + 16 + 384;
     lay.w_stages = (int)std::min<size_t>(3, (budget - fixed) / (size_t)lay.w_stage_bytes);
     if (lay.w_stages < 2) return cudaErrorInvalidValue;
     lay.b_stages = 2 + (int)std::min<size_t>(6, (budget - fixed - (size_t)lay.w_stages * lay.w_stage_bytes) / (size_t)lay.b_bytes);
