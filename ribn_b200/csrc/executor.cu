@@ -363,6 +363,8 @@ cudaError_t batch_project(ribn_b200_executor* ex, int& launches, const float* x,
             a.chunks = (const signed char*)ex->op_tc.chunks;
             a.member_scale = ex->op_tc.member_scale;
             a.kquant = kquant ? 1 : 0;
+            a.partial = ex->tc_partial;
+            a.partial_floats = ex->tc_partial_floats;
             a.epilogue = epilogue == kSwiGLU ? kStore : epilogue;
             STEP_TRY(launch_gemm_tc(s, a));
             if (epilogue == kSwiGLU) {
@@ -785,6 +787,9 @@ int ribn_b200_finalize(ribn_b200_executor* ex) {
                 CU_TRY(ex, dev_alloc(ex, &ex->op_batch.chunks, batch_operand_bytes(kGemmMaxMembers, kmax)));
                 CU_TRY(ex, dev_alloc(ex, (unsigned char**)&ex->op_tc.chunks, tc_operand_bytes(kGemmTcMaxMembers, kmax)));
                 CU_TRY(ex, dev_alloc(ex, &ex->op_tc.scale_in, kGemmTcMaxMembers));
+                // room for four K slices of the widest fused projection at 64 rows
+                ex->tc_partial_floats = (size_t)4 * 64 * (size_t)std::max(std::max(2 * c.ffn, c.hidden), (c.q_heads + 2 * c.kv_heads) * c.head_dim);
+                CU_TRY(ex, dev_alloc(ex, &ex->tc_partial, ex->tc_partial_floats));
                 CU_TRY(ex, dev_alloc(ex, &ex->op_tc.member_scale, kGemmTcMaxMembers));
                 CU_TRY(ex, dev_alloc(ex, &ex->op_batch.member_scale, kGemmMaxMembers));
                 CU_TRY(ex, dev_alloc(ex, &ex->op_batch.digit_inv, kGemmMaxMembers));

@@ -100,6 +100,8 @@ struct ribn_b200_executor {
     ribn::ActOperand op_hidden, op_attn, op_act, op_head;
     ribn::BatchOperand op_batch;  // batch form, refilled before every batched projection
     ribn::TcOperand op_tc;        // tensor-memory form (the same, for the tcgen05 kernel)
+    float* tc_partial = nullptr;  // split-K sums of the tcgen05 kernel
+    size_t tc_partial_floats = 0;
     // Captured decode steps, keyed by (tokens, sampling rows, attention span bucket).
     struct StepGraph { cudaGraphExec_t exec = nullptr; int launches = 0; };
     std::map<uint64_t, StepGraph> graphs;

@@ -481,8 +481,9 @@ constexpr int kKqThreads = (kKqChunkWarp0 + 2) * 32;
 constexpr int kA2Bytes = kRows * 16 * 2;   // the minima operand: 128 rows x 16 (8 groups + 8 zeros) halves
 
 struct KqLayout {
-    int w_stage_bytes, w_stages, b_bytes, b_stages, b2_bytes;
+    int w_stage_bytes, w_stages, b_bytes, b2_bytes;
     int cols, members_padded, a_stages, a_planes;
+    int k_slices, total_n;                 // split-K: slices per unit, and the rows of all segments together
 };
 
 // 4 bytes (each < 64) -> the binary16 pairs (1024 + b0, 1024 + b1) and (1024 + b2, 1024 + b3)
@@ -576,13 +577,16 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
     unsigned char* w_ring = smem;
     unsigned char* a_buf = w_ring + (size_t)lay.w_stages * lay.w_stage_bytes;        // [2][planes][16 KB]
     unsigned char* a2_buf = a_buf + (size_t)lay.a_stages * a_bytes;                   // [2][kA2Bytes]
-    unsigned char* b_buf = a2_buf + 2 * kA2Bytes;                                     // [b_stages][b_bytes]
-    unsigned char* b2_buf = b_buf + (size_t)lay.b_stages * lay.b_bytes;               // [2][b2_bytes]
+    unsigned char* b_buf = a2_buf + 2 * kA2Bytes;                                     // [a_stages][b_bytes]
+    unsigned char* b2_buf = b_buf + (size_t)lay.a_stages * lay.b_bytes;               // [2][b2_bytes]
     float2* row_scales = reinterpret_cast<float2*>(b2_buf + 2 * (size_t)lay.b2_bytes);  // [4][kRows]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(row_scales + 4 * kRows);
     const uint32_t bars = smem_u32(tmem_slot + 4);
+    // One commit per chunk frees the A stage and the activation stage of the same index (a_empty); the
+    // commit that completes a k tile (t_full) also frees that k tile's group-sum buffer.
     const uint32_t w_full = bars, w_empty = bars + 32, a_full = bars + 64, a_empty = bars + 96, t_full = bars + 128,
-                   t_empty = bars + 144, b2_full = bars + 160, b2_empty = bars + 176, b_full = bars + 192, b_empty = bars + 256;
+                   t_empty = bars + 144, b2_full = bars + 160, b_full = bars + 192;
+    const int S = lay.k_slices, tps = (k_tiles + S - 1) / S, items = units * S;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < lay.w_stages; ++i) { mbar_init(w_full + 8 * i, 1); mbar_init(w_empty + 8 * i, kKqDequantWarps); }
@@ -591,9 +595,8 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
             mbar_init(t_full + 8 * i, 1);
             mbar_init(t_empty + 8 * i, kEpilogueWarps);
             mbar_init(b2_full + 8 * i, 1);
-            mbar_init(b2_empty + 8 * i, 1);
         }
-        for (int i = 0; i < lay.b_stages; ++i) { mbar_init(b_full + 8 * i, 1); mbar_init(b_empty + 8 * i, 1); }
+        for (int i = 0; i < lay.a_stages; ++i) mbar_init(b_full + 8 * i, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // The second 8-input block of the minima operand stays zero for the whole kernel.
@@ -612,10 +615,10 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
     if (warp == kProducerWarp) {
         bool alive = true;
         uint32_t w_count = 0, kt_count = 0;
-        int wu = blockIdx.x, wkb = 0;
+        int witem = blockIdx.x, wkb = (witem % S) * tps;   // next weight stage to issue: (work item, k tile)
         auto issue_w = [&]() {
-            if (wu >= units) return;
-            const UnitRef ur = unit_of(a, wu);
+            if (witem >= items) return;
+            const UnitRef ur = unit_of(a, witem / S);
             const GemvSegment& s = a.seg[ur.seg];
             const uint32_t tb = (uint32_t)packed_tile_bytes(s.type);
             const uint32_t stage = w_count % (uint32_t)lay.w_stages;
@@ -632,16 +635,17 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                          s.data + ((size_t)(ur.rt0 + lane) * k_tiles + wkb) * tb, tb, w_full + 8 * stage);
             }
             ++w_count;
-            if (++wkb == k_tiles) { wkb = 0; wu += gridDim.x; }
+            if (++wkb == min(k_tiles, ((witem % S) + 1) * tps)) { witem += gridDim.x; wkb = (witem % S) * tps; }
         };
         issue_w();
         if (lay.w_stages > 2) issue_w();
         const size_t tile_stride = (size_t)kChunksPerTile * lay.b_bytes + lay.b2_bytes;  // one k tile of activations
-        for (int u = blockIdx.x; u < units; u += gridDim.x) {
-            for (int kb = 0; kb < k_tiles; ++kb, ++kt_count) {
+        for (int item = blockIdx.x; item < items; item += gridDim.x) {
+            const int kb0 = (item % S) * tps, kb1 = min(k_tiles, kb0 + tps);
+            for (int kb = kb0; kb < kb1; ++kb, ++kt_count) {
                 if (lane == 0) {
                     const uint32_t p = kt_count & 1u;
-                    if (kt_count >= 2u && alive) alive = mbar_wait_relaxed(b2_empty + 8 * p, ((kt_count >> 1) - 1u) & 1u, a.error_flag, 23);
+                    if (kt_count >= 2u && alive) alive = mbar_wait_relaxed(t_full + 8 * p, ((kt_count >> 1) - 1u) & 1u, a.error_flag, 23);
                     mbar_expect_tx(b2_full + 8 * p, (uint32_t)lay.b2_bytes);
                     bulk_g2s(smem_u32(b2_buf + (size_t)p * lay.b2_bytes),
                              a.chunks + (size_t)kb * tile_stride + (size_t)kChunksPerTile * lay.b_bytes, (uint32_t)lay.b2_bytes, b2_full + 8 * p);
@@ -658,13 +662,14 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
             const int which = warp - kKqChunkWarp0;
             const size_t tile_stride = (size_t)kChunksPerTile * lay.b_bytes + lay.b2_bytes;
             uint32_t b_count = 0;
-            for (int u = blockIdx.x; u < units; u += gridDim.x) {
-                for (int kb = 0; kb < k_tiles; ++kb) {
+            for (int item = blockIdx.x; item < items; item += gridDim.x) {
+                const int kb0 = (item % S) * tps, kb1 = min(k_tiles, kb0 + tps);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     const signed char* src = a.chunks + (size_t)kb * tile_stride;
                     for (int c = 0; c < kChunksPerTile; ++c, ++b_count) {
                         if ((c & 1) != which) continue;
-                        const uint32_t nb = (uint32_t)lay.b_stages, bs = b_count % nb;
-                        if (b_count >= nb && alive) alive = mbar_wait_relaxed(b_empty + 8 * bs, ((b_count / nb) - 1u) & 1u, a.error_flag, 22);
+                        const uint32_t bs = b_count % na;
+                        if (b_count >= na && alive) alive = mbar_wait_relaxed(a_empty + 8 * bs, ((b_count / na) - 1u) & 1u, a.error_flag, 22);
                         if (RIBN_TC_PROBE == 3 || RIBN_TC_PROBE == 5) { mbar_arrive(b_full + 8 * bs); continue; }
                         mbar_expect_tx(b_full + 8 * bs, (uint32_t)lay.b_bytes);
                         bulk_g2s(smem_u32(b_buf + (size_t)bs * lay.b_bytes), src + (size_t)c * lay.b_bytes, (uint32_t)lay.b_bytes, b_full + 8 * bs);
@@ -678,17 +683,18 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
             uint32_t count = 0, kt_count = 0;
             const uint32_t idesc = umma_idesc(lay.cols);
             const uint32_t b_lbo = (uint32_t)(lay.cols / 8) * 128u;
-            for (int u = blockIdx.x; u < units; u += gridDim.x) {
-                const bool q4k = a.seg[unit_of(a, u).seg].type == kQ4_K;
-                for (int kb = 0; kb < k_tiles; ++kb, ++kt_count) {
+            for (int item = blockIdx.x; item < items; item += gridDim.x) {
+                const bool q4k = a.seg[unit_of(a, item / S).seg].type == kQ4_K;
+                const int kb0 = (item % S) * tps, kb1 = min(k_tiles, kb0 + tps);
+                for (int kb = kb0; kb < kb1; ++kb, ++kt_count) {
                     const uint32_t p = kt_count & 1u;
                     if (kt_count >= 2u && alive) alive = mbar_wait(t_empty + 8 * p, ((kt_count >> 1) - 1u) & 1u, a.error_flag, 24);
                     tc_fence_after();
                     const uint32_t d_main = tmem_base + p * 128u, d_min = tmem_base + 256u + p * 128u;
                     for (int c = 0; c < kChunksPerTile; ++c, ++count) {
-                        const uint32_t st = count % na, nb = (uint32_t)lay.b_stages, bs = count % nb;
+                        const uint32_t st = count % na, bs = st;
                         if (alive) alive = mbar_wait(a_full + 8 * st, (count / na) & 1u, a.error_flag, 25);
-                        if (alive) alive = mbar_wait(b_full + 8 * bs, (count / nb) & 1u, a.error_flag, 26);
+                        if (alive) alive = mbar_wait(b_full + 8 * bs, (count / na) & 1u, a.error_flag, 26);
                         tc_fence_after();
                         const uint32_t a_addr = smem_u32(a_buf + (size_t)st * a_bytes);
                         const uint32_t b_addr = smem_u32(b_buf + (size_t)bs * lay.b_bytes);
@@ -707,10 +713,8 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                                 umma_f16(d_min, umma_desc(smem_u32(a2_buf + (size_t)p * kA2Bytes), kALbo, 128),
                                          umma_desc(smem_u32(b2_buf + (size_t)p * lay.b2_bytes), b_lbo, 128), idesc, 0u);
                             }
-                            umma_commit(b2_empty + 8 * p);
                         }
                         umma_commit(a_empty + 8 * st);
-                        umma_commit(b_empty + 8 * bs);
                     }
                     umma_commit(t_full + 8 * p);
                 }
@@ -720,13 +724,14 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
         const int rt_local = warp - kDequantWarp0;
         bool alive = true;
         uint32_t w_count = 0, a_count = 0;
-        for (int u = blockIdx.x; u < units; u += gridDim.x) {
-            const UnitRef ur = unit_of(a, u);
+        for (int item = blockIdx.x; item < items; item += gridDim.x) {
+            const UnitRef ur = unit_of(a, item / S);
             const GemvSegment& s = a.seg[ur.seg];
             const int type = s.type;
             const bool present = ur.rt0 + rt_local < s.row_tiles;
             const int tb = packed_tile_bytes(type);
-            for (int kb = 0; kb < k_tiles; ++kb, ++w_count) {
+            const int kb0 = (item % S) * tps, kb1 = min(k_tiles, kb0 + tps);
+            for (int kb = kb0; kb < kb1; ++kb, ++w_count) {
                 const uint32_t stage = w_count % (uint32_t)lay.w_stages;
                 if (alive) alive = mbar_wait(w_full + 8 * stage, (w_count / (uint32_t)lay.w_stages) & 1u, a.error_flag, 28);
                 const unsigned char* tile = w_ring + (size_t)stage * lay.w_stage_bytes + (size_t)rt_local * tb;
@@ -767,14 +772,15 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
         bool alive = true;
         uint32_t kt_count = 0;
         const int row = warp * 32 + lane;
-        for (int u = blockIdx.x; u < units; u += gridDim.x) {
-            const UnitRef ur = unit_of(a, u);
+        for (int item = blockIdx.x; item < items; item += gridDim.x) {
+            const UnitRef ur = unit_of(a, item / S);
             const GemvSegment& s = a.seg[ur.seg];
             const bool q4k = s.type == kQ4_K;
+            const int slice = item % S, kb0 = slice * tps, kb1 = min(k_tiles, kb0 + tps);
             float acc[kKqMaxMembers];
 #pragma unroll
             for (int i = 0; i < kKqMaxMembers; ++i) acc[i] = 0.0f;
-            for (int kb = 0; kb < k_tiles; ++kb, ++kt_count) {
+            for (int kb = kb0; kb < kb1; ++kb, ++kt_count) {
                 const uint32_t p = kt_count & 1u;
                 if (alive) alive = mbar_wait(t_full + 8 * p, (kt_count >> 1) & 1u, a.error_flag, 30);
                 tc_fence_after();
@@ -802,12 +808,23 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
             }
             const int n_index = ur.rt0 * kTileRows + row;
             if (n_index < s.n) {
+                if (S > 1) {
+                    // this K slice's sums, unscaled: [slice][member][all segments' rows]; a second kernel adds the slices in order
+                    int seg_offset = 0;
+                    for (int i = 0; i < ur.seg; ++i) seg_offset += a.seg[i].n;
+                    float* part = a.partial + ((size_t)slice * a.members) * lay.total_n + seg_offset + n_index;
 #pragma unroll
-                for (int m = 0; m < kKqMaxMembers; ++m) {
-                    if (m < a.members) {
-                        const float v = acc[m] * a.member_scale[m];
-                        float* y = s.y + (size_t)m * s.n + n_index;
-                        if (a.epilogue == kResidual) *y += v; else *y = v;
+                    for (int m = 0; m < kKqMaxMembers; ++m) {
+                        if (m < a.members) part[(size_t)m * lay.total_n] = acc[m];
+                    }
+                } else {
+#pragma unroll
+                    for (int m = 0; m < kKqMaxMembers; ++m) {
+                        if (m < a.members) {
+                            const float v = acc[m] * a.member_scale[m];
+                            float* y = s.y + (size_t)m * s.n + n_index;
+                            if (a.epilogue == kResidual) *y += v; else *y = v;
+                        }
                     }
                 }
             }
@@ -819,6 +836,20 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
+}
+
+// Adds the K slices of a split launch in slice order, applies the member scale and the epilogue.
+__global__ void tcq_reduce_kernel(const GemmArgs a, int slices, int total_n) {
+    const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= (long long)a.members * total_n) return;
+    const int m = (int)(id / total_n);
+    int n = (int)(id % total_n), seg = 0;
+    while (seg + 1 < a.n_segments && n >= a.seg[seg].n) { n -= a.seg[seg].n; ++seg; }
+    float sum = 0.0f;
+    for (int sl = 0; sl < slices; ++sl) sum += a.partial[((size_t)sl * a.members + m) * total_n + (id % total_n)];
+    const float v = sum * a.member_scale[m];
+    float* y = a.seg[seg].y + (size_t)m * a.seg[seg].n + n;
+    if (a.epilogue == kResidual) *y += v; else *y = v;
 }
 
 // ---- activations -> hi + lo binary16 operand chunks ------------------------------------------------
@@ -983,12 +1014,10 @@ cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units
     for (int i = 0; i < args.n_segments; ++i) all_q4k = all_q4k && args.seg[i].type == kQ4_K;
     lay.a_planes = all_q4k ? 1 : 2;
     lay.a_stages = all_q4k ? 4 : 2;
-    size_t fixed = (size_t)4 * kAHalfBytes + (size_t)2 * kA2Bytes + (size_t)2 * lay.b_bytes + (size_t)2 * lay.b2_bytes +
+    size_t fixed = (size_t)4 * kAHalfBytes + (size_t)2 * kA2Bytes + (size_t)lay.a_stages * lay.b_bytes + (size_t)2 * lay.b2_bytes +
                    (size_t)4 * kRows * sizeof(float2) + 16 + 384;
     lay.w_stages = (int)std::min<size_t>(3, (budget - fixed) / (size_t)lay.w_stage_bytes);
     if (lay.w_stages < 2) return cudaErrorInvalidValue;
-    lay.b_stages = 2 + (int)std::min<size_t>(6, (budget - fixed - (size_t)lay.w_stages * lay.w_stage_bytes) / (size_t)lay.b_bytes);
-    fixed += (size_t)(lay.b_stages - 2) * lay.b_bytes;
     const size_t smem = fixed + (size_t)lay.w_stages * lay.w_stage_bytes;
     static bool configured = false;
     static int sm_count = 0;
@@ -1000,7 +1029,28 @@ cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units
         if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
         configured = true;
     }
-    gemm_tcq_kernel<<<std::min(units, sm_count), kKqThreads, smem, stream>>>(args, lay, units);
+    // Split K when whole units would leave SMs idle: pick the slice count with the fewest k tiles on the
+    // busiest SM (each work item also pays about one k tile of pipeline fill).
+    const int k_tiles = args.k / kTileCols;
+    lay.total_n = 0;
+    for (int i = 0; i < args.n_segments; ++i) lay.total_n += args.seg[i].n;
+    lay.k_slices = 1;
+    if (args.partial != nullptr) {
+        long long best = -1;
+        for (int slices = 1; slices <= std::min(8, k_tiles); ++slices) {
+            const int tps = (k_tiles + slices - 1) / slices;
+            if ((slices - 1) * tps >= k_tiles) continue;  // an empty slice
+            if ((size_t)slices * args.members * lay.total_n > args.partial_floats) break;
+            const long long waves = ((long long)units * slices + sm_count - 1) / sm_count;
+            const long long cost = waves * (tps + 1);
+            if (best < 0 || cost < best) { best = cost; lay.k_slices = slices; }
+        }
+    }
+    gemm_tcq_kernel<<<std::min(units * lay.k_slices, sm_count), kKqThreads, smem, stream>>>(args, lay, units);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess || lay.k_slices == 1) return e;
+    const long long outputs = (long long)args.members * lay.total_n;
+    tcq_reduce_kernel<<<(unsigned int)((outputs + 255) / 256), 256, 0, stream>>>(args, lay.k_slices, lay.total_n);
     return cudaGetLastError();
 }
 

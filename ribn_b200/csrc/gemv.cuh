@@ -163,6 +163,8 @@ struct GemmArgs {
     int epilogue;         // GemvEpilogue; kSwiGLU writes seg[0].y = silu(gate) * up
     int* error_flag;
     int kquant;           // tensor-memory kernels: the activations are in the K-quant form (see TcOperand)
+    float* partial;       // optional scratch for split-K sums [slices][members][rows of all segments]
+    size_t partial_floats;
 };
 
 cudaError_t launch_gemm_imma(cudaStream_t stream, const GemmArgs& args);

@@ -156,6 +156,9 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
             top.scale_in = s.alloc<float>((size_t)group);
             top.member_scale = s.alloc<float>((size_t)group);
             OP_PTR(top.chunks); OP_PTR(top.scale_in); OP_PTR(top.member_scale);
+            const size_t partial_floats = (size_t)8 * group * (size_t)rows;
+            float* partial = kquant ? s.alloc<float>(partial_floats) : nullptr;
+            if (kquant) OP_PTR(partial);
             for (int m0 = 0; m0 < members; m0 += per_launch) {
                 const int m = std::min(per_launch, members - m0);
                 OP_TRY(launch_to_tc_operand(s.stream, d_x + (size_t)m0 * cols, nullptr, nullptr, m, (int)cols, 0.0f, kquant, top));
@@ -169,6 +172,8 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
                 a.epilogue = kStore;
                 a.error_flag = d_err;
                 a.kquant = kquant ? 1 : 0;
+                a.partial = partial;
+                a.partial_floats = partial_floats;
                 OP_TRY(launch_gemm_tc(s.stream, a));
             }
         } else if (variant == 2) {
