@@ -99,6 +99,187 @@ __global__ void attention_span_kernel(const AttnArgs a) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ __align__(16) unsigned char attn_smem[];
+    constexpr int kRowHalfs = HD + 8;  // staged K / V rows, padded by 16 bytes so that a lane per key reads conflict-free
+    float* q_smem = reinterpret_cast<float*>(attn_smem);                                 // [warps][HD]
+    __half* k_tile = reinterpret_cast<__half*>(attn_smem + (size_t)(blockDim.x >> 5) * HD * sizeof(float));  // [64][kRowHalfs]
+    __half* v_tile = k_tile + kAttnSpanKeys * kRowHalfs;                                 // [64][kRowHalfs]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int q_per_kv = a.q_heads / a.kv_heads;
+    const int t = a.token_base + blockIdx.x / a.kv_heads, kvh = blockIdx.x % a.kv_heads;
+    const int span = blockIdx.y;
+    const int qh = kvh * q_per_kv + warp;
+    const int pos = a.token_pos[t];
+    const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const int n_keys = pos + 1 - first;
+    const int spans = (n_keys + kAttnSpanKeys - 1) / kAttnSpanKeys;
+    if (span >= spans) return;
+    const int begin = first + span * kAttnSpanKeys;
+    const int end = min(pos + 1, begin + kAttnSpanKeys);
+    const int32_t* table = a.page_tables + (long long)(a.token_seq != nullptr ? a.token_seq[t] : 0) * a.pages_per_sequence;
+    const float scale = 1.0f / sqrtf((float)HD);
+    const long long row_stride = (long long)a.kv_heads * HD;
+    const bool owns_self = FUSED && span == spans - 1;  // this CTA's span holds the token's own position
+
+    // The span's K and V rows come to shared memory once for all the query heads of the group
+    // (every thread keeps several independent 16-byte loads in flight).
+    {
+        constexpr int kChunks = HD / 8;  // 16-byte pieces per row
+        const int rows = end - begin;
+        for (int idx = threadIdx.x; idx < 2 * rows * kChunks; idx += blockDim.x) {
+            const int which = idx / (rows * kChunks), rest = idx - which * rows * kChunks;
+            const int r = rest / kChunks, c = rest - r * kChunks;
+            const int key = begin + r;
+            if (owns_self && key == pos) continue;  // the token's own row is produced below
+            const long long phys = (long long)table[key / kPageTokens] * kPageTokens + key % kPageTokens;
+            const __half* src = (which ? a.cache_v : a.cache_k) + phys * row_stride + (long long)kvh * HD + c * 8;
+            *reinterpret_cast<uint4*>((which ? v_tile : k_tile) + r * kRowHalfs + c * 8) = *reinterpret_cast<const uint4*>(src);
+        }
+    }
+
+    float* qs = q_smem + warp * HD;
+    {
+        const float* qp = a.q + ((long long)t * a.q_heads + qh) * HD;
+        float x[DPL];
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) x[i] = qp[lane + 32 * i];
+        if (FUSED) norm_rope<HD>(x, a.q_norm, a.inv_freq, a.eps, (float)pos, lane);
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) qs[lane + 32 * i] = x[i];
+    }
+    if (owns_self && warp == 0) {
+        // The token's own K (normalised, rotated) and V, rounded to F16 exactly as the cache holds them.
+        const float* kp = a.k_new + ((long long)t * a.kv_heads + kvh) * HD;
+        const float* vp = a.v_new + ((long long)t * a.kv_heads + kvh) * HD;
+        float x[DPL];
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) x[i] = kp[lane + 32 * i];
+        norm_rope<HD>(x, a.k_norm, a.inv_freq, a.eps, (float)pos, lane);
+        __half* ck = a.cache_k + (long long)a.token_slot[t] * row_stride + (long long)kvh * HD;
+        __half* cv = a.cache_v + (long long)a.token_slot[t] * row_stride + (long long)kvh * HD;
+        __half* k_self = k_tile + (pos - begin) * kRowHalfs;
+        __half* v_self = v_tile + (pos - begin) * kRowHalfs;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int d = lane + 32 * i;
+            const __half kh = __float2half_rn(x[i]), vh = __float2half_rn(vp[d]);
+            k_self[d] = kh; v_self[d] = vh;
+            ck[d] = kh; cv[d] = vh;
+        }
+    }
+    __syncthreads();
+
+    const int kg = lane >> 3, dc = lane & 7;
+    float acc[CH];
+#pragma unroll
+    for (int d = 0; d < CH; ++d) acc[d] = 0.0f;
+    float run_max = -INFINITY, total = 0.0f;
+    for (int base = begin; base < end; base += 32) {
+        const int key = base + lane;
+        const bool live = key < end;
+        float s = -INFINITY;
+        if (live) {
+            const uint4* kp = reinterpret_cast<const uint4*>(k_tile + (key - begin) * kRowHalfs);
+            uint4 kk[HD / 8];
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) kk[i] = kp[i];
+            float dot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) {
+                const float4 qa = *reinterpret_cast<const float4*>(qs + i * 8);
+                const float4 qb = *reinterpret_cast<const float4*>(qs + i * 8 + 4);
+                const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].x));
+                const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].y));
+                const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].z));
+                const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].w));
+                dot = fmaf(qa.x, k0.x, dot); dot = fmaf(qa.y, k0.y, dot);
+                dot = fmaf(qa.z, k1.x, dot); dot = fmaf(qa.w, k1.y, dot);
+                dot = fmaf(qb.x, k2.x, dot); dot = fmaf(qb.y, k2.y, dot);
+                dot = fmaf(qb.z, k3.x, dot); dot = fmaf(qb.w, k3.y, dot);
+            }
+            s = dot * scale;
+        }
+        const float new_max = fmaxf(run_max, warp_max(s));
+        const float factor = expf(run_max - new_max);  // 0 on the first tile (run_max = -inf)
+        const float p = live ? expf(s - new_max) : 0.0f;
+        total = total * factor + warp_sum(p);
+#pragma unroll
+        for (int d = 0; d < CH; ++d) acc[d] *= factor;
+        run_max = new_max;
+        const int count = min(32, end - base);
+        // P.V: lane (kg, dc) takes keys j = 4 jj + kg and dims [dc * CH, dc * CH + CH)
+        uint4 vv[8][CH / 8];
+        float pj[8];
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+            const int j = jj * 4 + kg;
+            pj[jj] = __shfl_sync(0xffffffffu, p, j);
+            const __half* vp = v_tile + (base - begin + j) * kRowHalfs;
+            if (j < count) {
+#pragma unroll
+                for (int c = 0; c < CH / 8; ++c) vv[jj][c] = *reinterpret_cast<const uint4*>(vp + dc * CH + c * 8);
+            } else {
+#pragma unroll
+                for (int c = 0; c < CH / 8; ++c) vv[jj][c] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+#pragma unroll
+            for (int c = 0; c < CH / 8; ++c) {
+                const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].x));
+                const float2 v1 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].y));
+                const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].z));
+                const float2 v3 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].w));
+                float* o = acc + c * 8;
+                o[0] = fmaf(pj[jj], v0.x, o[0]); o[1] = fmaf(pj[jj], v0.y, o[1]);
+                o[2] = fmaf(pj[jj], v1.x, o[2]); o[3] = fmaf(pj[jj], v1.y, o[3]);
+                o[4] = fmaf(pj[jj], v2.x, o[4]); o[5] = fmaf(pj[jj], v2.y, o[5]);
+                o[6] = fmaf(pj[jj], v3.x, o[6]); o[7] = fmaf(pj[jj], v3.y, o[7]);
+            }
+        }
+    }
+    // Fold the four key groups (fixed order: xor 8, then xor 16).
+#pragma unroll
+    for (int d = 0; d < CH; ++d) {
+        acc[d] += __shfl_xor_sync(0xffffffffu, acc[d], 8);
+        acc[d] += __shfl_xor_sync(0xffffffffu, acc[d], 16);
+    }
+    if (spans == 1) {
+        if (kg == 0) {
+            const float inv = 1.0f / total;
+            float* op = a.out + ((long long)t * a.q_heads + qh) * HD + dc * CH;
+#pragma unroll
+            for (int d = 0; d < CH; ++d) { acc[d] *= inv; op[d] = acc[d]; qs[dc * CH + d] = acc[d]; }
+        }
+        if (a.operand.dig != nullptr) {
+            // back to one input per lane: lane takes dims lane + 32 i of this head
+            __syncwarp();
+            ActOperand op = a.operand;
+            op.ss32 = nullptr;
+            const int K = a.q_heads * HD, m = t - a.token_base;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) operand_store_span(op, m, K, (qh * HD) / 32 + i, lane, qs[lane + 32 * i], 0.0f);
+        }
+    } else if (kg == 0) {
+        float* pp = a.partial + (((long long)(t - a.token_base) * a.q_heads + qh) * a.max_spans + span) * (HD + 2);
+#pragma unroll
+        for (int d = 0; d < CH; ++d) pp[dc * CH + d] = acc[d];
+        if (dc == 0) { pp[HD] = run_max; pp[HD + 1] = total; }
+    }
+}
+
+// The same span computation with every warp reading its keys straight from the cache: fewer steps in
+// series, which wins when the launch has too few CTAs to fill the GPU (decode at batch 1 or 2).  Both
+// kernels perform identical arithmetic in identical order.
+template <int HD, bool FUSED>
+__global__ void attention_span_direct_kernel(const AttnArgs a) {
+    constexpr int DPL = HD / 32;  // dims per lane in the lane-strided layout
+    constexpr int CH = HD / 8;    // dims per lane in the P.V phase (8 chunks x 4 key groups)
+    // Programmatic dependent launch: wait for the projections that produced q/k/v, then let the next
+    // kernel (which first only prefetches weights) start.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    extern __shared__ __align__(16) unsigned char attn_smem[];
     float* q_smem = reinterpret_cast<float*>(attn_smem);                                 // [warps][HD]
     __half* k_self = reinterpret_cast<__half*>(attn_smem + (size_t)(blockDim.x >> 5) * HD * sizeof(float));  // [HD]
     __half* v_self = k_self + HD;                                                         // [HD]
@@ -324,13 +505,32 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
         chunk = (int)std::min<size_t>((size_t)n_tokens, partial_bytes / per_token);
     }
     if (a.operand.dig != nullptr && chunk < n_tokens) return cudaErrorInvalidValue;  // operand rows are launch-relative
-    const size_t smem = (size_t)q_per_kv * HD * sizeof(float) + 2 * HD * sizeof(__half);
+    // Few CTAs: the direct kernel (shorter dependency chain); many: K / V rows staged once per query-head group.
+    const bool staged = (long long)n_tokens * a.kv_heads * a.max_spans >= 1024;
+    const size_t smem = staged ? (size_t)q_per_kv * HD * sizeof(float) + (size_t)2 * kAttnSpanKeys * (HD + 8) * sizeof(__half)
+                               : (size_t)q_per_kv * HD * sizeof(float) + 2 * HD * sizeof(__half);
+    if (smem > 48 * 1024) {
+        // above the default limit (head_dim 256): opt in once per instantiation
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(attention_span_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_span_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+            if (e != cudaSuccess) return e;
+            configured = true;
+        }
+    }
     for (int base = 0; base < n_tokens; base += chunk) {
         const int n = std::min(chunk, n_tokens - base);
         a.token_base = base;
         dim3 grid(n * a.kv_heads, a.max_spans);
-        cudaError_t e = fused ? launch_pdl(stream, attention_span_kernel<HD, true>, grid, q_per_kv * 32, smem, a, programmatic)
-                              : launch_pdl(stream, attention_span_kernel<HD, false>, grid, q_per_kv * 32, smem, a, programmatic);
+        cudaError_t e;
+        if (staged) {
+            e = fused ? launch_pdl(stream, attention_span_kernel<HD, true>, grid, q_per_kv * 32, smem, a, programmatic)
+                      : launch_pdl(stream, attention_span_kernel<HD, false>, grid, q_per_kv * 32, smem, a, programmatic);
+        } else {
+            e = fused ? launch_pdl(stream, attention_span_direct_kernel<HD, true>, grid, q_per_kv * 32, smem, a, programmatic)
+                      : launch_pdl(stream, attention_span_direct_kernel<HD, false>, grid, q_per_kv * 32, smem, a, programmatic);
+        }
         if (e != cudaSuccess) return e;
         if (launches) ++*launches;
         if (a.max_spans > 1) {

@@ -859,12 +859,15 @@ __global__ void tc_scale_kernel(const float* x, const int32_t* index, const floa
                                 float* scale_in, float* member_scale) {
     __shared__ float red_max[32], red_sum[32];
     const int m = blockIdx.x;
-    const float* row = x + (size_t)(index ? index[m] : m) * k;
+    const float4* row = reinterpret_cast<const float4*>(x + (size_t)(index ? index[m] : m) * k);
+    const float4* nw = reinterpret_cast<const float4*>(norm_weight);
     float amax = 0.0f, ss = 0.0f;
-    for (int i = threadIdx.x; i < k; i += blockDim.x) {
-        const float v = row[i];
-        ss = fmaf(v, v, ss);
-        amax = fmaxf(amax, fabsf(norm_weight ? v * norm_weight[i] : v));
+    for (int i = threadIdx.x; i < k / 4; i += blockDim.x) {   // k is a multiple of 256
+        const float4 v = row[i];
+        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        float4 w = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        if (nw != nullptr) w = nw[i];
+        amax = fmaxf(fmaxf(amax, fabsf(v.x * w.x)), fmaxf(fabsf(v.y * w.y), fmaxf(fabsf(v.z * w.z), fabsf(v.w * w.w))));
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -989,7 +992,7 @@ cudaError_t launch_to_tc_operand(cudaStream_t stream, const float* x, const int3
                                  int members, int k, float eps, bool kquant, TcOperand out) {
     if (members <= 0 || members > (kquant ? kKqMaxMembers : kGemmTcMaxMembers) || k % kTileCols != 0) return cudaErrorInvalidValue;
     const int mp = padded_members(members);
-    tc_scale_kernel<<<members, 256, 0, stream>>>(x, index, norm_weight, k, eps, out.scale_in, out.member_scale);
+    tc_scale_kernel<<<members, 512, 0, stream>>>(x, index, norm_weight, k, eps, out.scale_in, out.member_scale);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     const long long threads = (long long)mp * (k / 8);
