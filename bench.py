@@ -137,12 +137,15 @@ def replica_throughput(dist, world: int, rows: int, steps: int, seconds: float, 
     return world * rows * steps / all_max(dist, seconds, device)
 
 
+SCHEME = "q4_k_m"   # set from --scheme: "q4_k_m" (Q4_K; Q6_K for attn_v, ffn_down, output) or "q8_0"
+
+
 def build_executor(model: dict, batch: int, context: int, decode_tokens: int, device: int, keep_logits: bool):
     import ribn_b200
     span = context + decode_tokens + 16
     ex = ribn_b200.QwenB200(model, context_tokens=span, max_sequences=batch, max_batch_tokens=max(batch, 16),
                             device=device, flags=ribn_b200.FLAG_KEEP_LOGITS if keep_logits else 0)
-    ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q4_K_M)
+    ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q8_0 if SCHEME == "q8_0" else ribn_b200.SCHEME_Q4_K_M)
     return ex
 
 
@@ -269,10 +272,10 @@ def run_ours(args):
             others[name] = {"us": t_us, "bytes": b, "GB/s": b / t_us / 1e3}
         achieved = nbytes / us / 1e3
         # DRAM bytes of the same launch from the ncu capture summarised in profiles/gemv_mma_gate_up_qwen3-8b.md
-        traffic = GATE_UP_DRAM_BYTES.get(args.model)
+        traffic = GATE_UP_DRAM_BYTES.get(args.model) if args.scheme == "q4_k_m" else None
         return {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
                 "traffic": traffic, "of": peak_kind,
-                "kernel": "gemv_mma_kernel, ffn gate|up launch (2 x ffn x hidden Q4_K, 1 row)",
+                "kernel": "gemv_mma_kernel, ffn gate|up launch (2 x ffn x hidden, 1 row)",
                 "algorithmic_bytes_per_launch": nbytes, "us_per_launch": us, "other_launches": others}
 
     # ---- batch 1 -----------------------------------------------------------------------
@@ -280,12 +283,12 @@ def run_ours(args):
     value1 = world * 1 * args.steps / dev1   # dev1 / wall1 are already the maximum over ranks
     e2e1 = world * 1 * args.steps / wall1
     out = {
-        "metric": f"{args.model} Q4_K_M decode tok/s at batch 1 (per GPU x replicas)", "value": value1,
+        "metric": f"{args.model} {args.scheme.upper()} decode tok/s at batch 1 (per GPU x replicas)", "value": value1,
         "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dev1 / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "u8 x s8 integer tensor-core products over Q4_K,Q6_K weights, f32 block scales and accumulation, f16 KV",
         "data": "synthetic",
-        "config": {"workload": f"{args.model} Q4_K_M-style decode, batch 1 and {B}, context {args.context}, "
+        "config": {"workload": f"{args.model} {args.scheme.upper()}-style decode, batch 1 and {B}, context {args.context}, "
                                f"16-token KV pages, one replica per GPU",
                    "l2": "inputs larger than L2 (4.9 GB of weights streamed per step)",
                    "parallelism": f"replicas x{world}"},
@@ -442,7 +445,10 @@ def main():
     ap.add_argument("--arrival-rate", type=float, default=8.0, help="serving: Poisson arrival rate, requests per second per GPU")
     ap.add_argument("--serving-prompt-max", type=int, default=2048)
     ap.add_argument("--serving-output-max", type=int, default=512)
+    ap.add_argument("--scheme", default="q4_k_m", choices=["q4_k_m", "q8_0"], help="synthetic checkpoint's block types")
     args = ap.parse_args()
+    global SCHEME
+    SCHEME = args.scheme
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
