@@ -163,6 +163,7 @@ constexpr int kHdrStride = 20;      // floats per header row: 16 scales + offset
 constexpr int kPlanePad = 32;       // bytes between activation digit planes (distinct banks per plane)
 constexpr uint32_t kSpinLimit = 1u << 22;  // bounded waits: iterations before giving up
 constexpr uint32_t kNibbles = 0x0F0F0F0Fu;
+constexpr uint32_t kHighNibbles = 0xF0F0F0F0u;
 constexpr uint32_t kTopBits = 0x30303030u;
 constexpr int kMagicInt = 0x4B400000;      // bits of 12582912.0f: int accumulate on top of it, read as float
 constexpr float kMagic = 12582912.0f;
@@ -332,9 +333,11 @@ __device__ __forceinline__ void tile_q4k(uint32_t tile, const Lane& ln, int kb, 
         const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
         const uint32_t sc = ln.half ? ((h.w & kNibbles) | ((h.y >> 2) & kTopBits)) : (h.y & 0x3F3F3F3Fu);
         const uint32_t mn = ln.half ? (((h.w >> 4) & kNibbles) | ((h.z >> 2) & kTopBits)) : (h.z & 0x3F3F3F3Fu);
+        // Odd groups reach the MMA as 16 q (their nibbles stay in the high half of each byte), so their
+        // scale carries the exact factor 1/16.
         float gs[4], gm[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { gs[i] = d * byte_f32(sc, i); gm[i] = dmin * byte_f32(mn, i); }
+        for (int i = 0; i < 4; ++i) { gs[i] = ((i & 1) ? d * 0.0625f : d) * byte_f32(sc, i); gm[i] = dmin * byte_f32(mn, i); }
 #pragma unroll
         for (int mm = 0; mm < MEMBERS; ++mm) {
             const float4 sx = lds128f(ln.sx + (uint32_t)(mm * (ln.K / 32) + kb * 8 + ln.half * 4) * 4);
@@ -360,8 +363,7 @@ __device__ __forceinline__ void tile_q4k(uint32_t tile, const Lane& ln, int kb, 
         const float2 f0 = lds64f(ln.hdr_rd + j * 8), f1 = lds64f(ln.hdr_rd + 8 * kHdrRow + j * 8);
         int ce[4], co[4];
         imma_k32(ce, w.x & kNibbles, w.z & kNibbles, w.y & kNibbles, w.w & kNibbles, be.x, be.y);
-        imma_k32(co, (w.x >> 4) & kNibbles, (w.z >> 4) & kNibbles, (w.y >> 4) & kNibbles, (w.w >> 4) & kNibbles, bo.x,
-                 bo.y);
+        imma_k32(co, w.x & kHighNibbles, w.z & kHighNibbles, w.y & kHighNibbles, w.w & kHighNibbles, bo.x, bo.y);
         fold(acc, ce, f0.x, f1.x);
         fold(acc, co, f0.y, f1.y);
     }
@@ -711,7 +713,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
     const uint32_t ring = smem_u32(sh.ring);
     const int set = SHARED ? 0 : team, set_warp = SHARED ? warp : member_warp;
     const uint32_t ring_len = SHARED ? (uint32_t)slots : (uint32_t)slots_per_team;
-    uint32_t k = 0;   // the set's stage counter, in step with the producer's
+    // The set's stage counter k, in step with the producer's, kept as (k % ring_len, (k / ring_len) & 1, k % kTeams)
+    // and advanced incrementally: no divisions in the stage loop.
+    uint32_t ring_pos = 0, ring_parity = 0;
+    int turn = 0;
     int buf = 0, done = 0;
     for (int u = u0 + set; u < u1; u += unit_step, buf ^= 1, ++done) {
         Accum acc[kMaxRuns];
@@ -728,19 +733,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
             if (!locate(u, r, seg, rt)) continue;
             const int type = seg->type;
             const int tile_bytes = packed_tile_bytes(type);
-            for (int st = 0; st < stages_per_run; ++st, ++k) {
-                if (SHARED && (int)(k % (uint32_t)kTeams) != team) continue;  // another team's stage
-                const uint32_t slot = SHARED ? k % ring_len : (k % ring_len) * kTeams + team;
-                if (alive) alive = mbar_wait(sh.full + slot * 8, (k / ring_len) & 1u, a.error_flag, 3);
-                const int kb = st * kStageTiles + member_warp;
-                if (kb < k_tiles && RIBN_PROBE != 1 && RIBN_PROBE != 6) {
-                    const uint32_t tile = ring + slot * (uint32_t)slot_bytes + (uint32_t)(member_warp * tile_bytes);
-                    if (type == kQ4_K) tile_q4k<MEMBERS>(tile, ln, kb, lane, acc[r]);
-                    else if (type == kQ6_K) tile_q6k<MEMBERS>(tile, ln, kb, lane, acc[r]);
-                    else tile_q8_0<MEMBERS>(tile, ln, kb, lane, acc[r]);
+            for (int st = 0; st < stages_per_run; ++st) {
+                if (!SHARED || turn == team) {  // SHARED: the teams take the stages in turn
+                    const uint32_t slot = SHARED ? ring_pos : ring_pos * kTeams + team;
+                    if (alive) alive = mbar_wait(sh.full + slot * 8, ring_parity, a.error_flag, 3);
+                    const int kb = st * kStageTiles + member_warp;
+                    if (kb < k_tiles && RIBN_PROBE != 1 && RIBN_PROBE != 6) {
+                        const uint32_t tile = ring + slot * (uint32_t)slot_bytes + (uint32_t)(member_warp * tile_bytes);
+                        if (type == kQ4_K) tile_q4k<MEMBERS>(tile, ln, kb, lane, acc[r]);
+                        else if (type == kQ6_K) tile_q6k<MEMBERS>(tile, ln, kb, lane, acc[r]);
+                        else tile_q8_0<MEMBERS>(tile, ln, kb, lane, acc[r]);
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(sh.empty + slot * 8);  // this warp has left the stage
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(sh.empty + slot * 8);  // this warp has left the stage
+                if (++ring_pos == ring_len) { ring_pos = 0; ring_parity ^= 1u; }
+                if (++turn == kTeams) turn = 0;
             }
         }
         // Per-warp partial of (row, member): digits 1 and 2 are this lane's two columns, digit 3 is the
