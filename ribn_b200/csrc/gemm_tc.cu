@@ -482,7 +482,7 @@ constexpr int kA2Bytes = kRows * 16 * 2;   // the minima operand: 128 rows x 16 
 
 struct KqLayout {
     int w_stage_bytes, w_stages, b_bytes, b2_bytes;
-    int cols, members_padded, a_stages, a_planes;
+    int cols, members_padded, a_stages, a_planes, chunk_k;
     int k_slices, total_n;                 // split-K: slices per unit, and the rows of all segments together
 };
 
@@ -499,13 +499,14 @@ __device__ __forceinline__ void store_half4(unsigned char* dst, __half2 a, __hal
     *reinterpret_cast<uint2*>(dst) = v;
 }
 
-// One 64-input chunk of one packed tile for the row g + 8 rr of each lane -> integer operand planes.
-// At chunk 0 the lane with t == 0 also leaves the row's d (and dmin) in `row_scales` and, for Q4_K,
+// One 64-input piece `c` of one packed tile for the row g + 8 rr of each lane -> integer operand planes.
+// At piece 0 the lane with t == 0 also leaves the row's d (and dmin) in `row_scales` and, for Q4_K,
 // lanes t = 0..3 write the row's eight group minima into the A2 operand.
-__device__ __forceinline__ void kq_chunk(int type, const unsigned char* tile, int c, unsigned char* a_planes, unsigned char* a2,
-                                         float2* row_scales, int row0, int rr, int lane) {
+__device__ __forceinline__ void kq_chunk(int type, const unsigned char* tile, int c, int k_base, unsigned char* a_planes,
+                                         unsigned char* a2, float2* row_scales, int row0, int rr, int lane) {
     const int g = lane >> 2, t = lane & 3, row = g + 8 * rr, unit_row = row0 + row;
-    unsigned char* base = a_planes + (unit_row >> 3) * 128 + (unit_row & 7) * 16;
+    // k_base: where this 64-input piece sits inside the operand stage (stages hold 64 or 128 inputs)
+    unsigned char* base = a_planes + (k_base >> 3) * kALbo + (unit_row >> 3) * 128 + (unit_row & 7) * 16;
     if (type == kQ4_K) {
         const uint4 w = *reinterpret_cast<const uint4*>(tile + c * 512 + lane * 16);
         const uint4 h = *reinterpret_cast<const uint4*>(tile + 2048 + row * 16);
@@ -572,13 +573,16 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_tiles = a.k / kTileCols;
-    const int a_bytes = lay.a_planes * kAHalfBytes;  // per stage: two planes when the launch has Q6_K units
+    // Operand stages hold lay.chunk_k inputs: 128 when every unit is Q4_K (half as many hand-offs per k tile), else 64.
+    const int pieces = lay.chunk_k / kChunkK, chunks_per_tile = kTileCols / lay.chunk_k;
+    const int a_bytes = lay.a_planes * kAHalfBytes * pieces;
+    const int b_stage_bytes = lay.b_bytes * pieces;
     const uint32_t na = (uint32_t)lay.a_stages;
     unsigned char* w_ring = smem;
     unsigned char* a_buf = w_ring + (size_t)lay.w_stages * lay.w_stage_bytes;        // [2][planes][16 KB]
     unsigned char* a2_buf = a_buf + (size_t)lay.a_stages * a_bytes;                   // [2][kA2Bytes]
     unsigned char* b_buf = a2_buf + 2 * kA2Bytes;                                     // [a_stages][b_bytes]
-    unsigned char* b2_buf = b_buf + (size_t)lay.a_stages * lay.b_bytes;               // [2][b2_bytes]
+    unsigned char* b2_buf = b_buf + (size_t)lay.a_stages * b_stage_bytes;             // [2][b2_bytes]
     float2* row_scales = reinterpret_cast<float2*>(b2_buf + 2 * (size_t)lay.b2_bytes);  // [4][kRows]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(row_scales + 4 * kRows);
     const uint32_t bars = smem_u32(tmem_slot + 4);
@@ -666,13 +670,13 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                 const int kb0 = (item % S) * tps, kb1 = min(k_tiles, kb0 + tps);
                 for (int kb = kb0; kb < kb1; ++kb) {
                     const signed char* src = a.chunks + (size_t)kb * tile_stride;
-                    for (int c = 0; c < kChunksPerTile; ++c, ++b_count) {
+                    for (int c = 0; c < chunks_per_tile; ++c, ++b_count) {
                         if ((c & 1) != which) continue;
                         const uint32_t bs = b_count % na;
                         if (b_count >= na && alive) alive = mbar_wait_relaxed(a_empty + 8 * bs, ((b_count / na) - 1u) & 1u, a.error_flag, 22);
                         if (RIBN_TC_PROBE == 3 || RIBN_TC_PROBE == 5) { mbar_arrive(b_full + 8 * bs); continue; }
-                        mbar_expect_tx(b_full + 8 * bs, (uint32_t)lay.b_bytes);
-                        bulk_g2s(smem_u32(b_buf + (size_t)bs * lay.b_bytes), src + (size_t)c * lay.b_bytes, (uint32_t)lay.b_bytes, b_full + 8 * bs);
+                        mbar_expect_tx(b_full + 8 * bs, (uint32_t)b_stage_bytes);
+                        bulk_g2s(smem_u32(b_buf + (size_t)bs * b_stage_bytes), src + (size_t)c * b_stage_bytes, (uint32_t)b_stage_bytes, b_full + 8 * bs);
                     }
                 }
             }
@@ -691,21 +695,20 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                     if (kt_count >= 2u && alive) alive = mbar_wait(t_empty + 8 * p, ((kt_count >> 1) - 1u) & 1u, a.error_flag, 24);
                     tc_fence_after();
                     const uint32_t d_main = tmem_base + p * 128u, d_min = tmem_base + 256u + p * 128u;
-                    for (int c = 0; c < kChunksPerTile; ++c, ++count) {
+                    for (int c = 0; c < chunks_per_tile; ++c, ++count) {
                         const uint32_t st = count % na, bs = st;
                         if (alive) alive = mbar_wait(a_full + 8 * st, (count / na) & 1u, a.error_flag, 25);
                         if (alive) alive = mbar_wait(b_full + 8 * bs, (count / na) & 1u, a.error_flag, 26);
                         tc_fence_after();
                         const uint32_t a_addr = smem_u32(a_buf + (size_t)st * a_bytes);
-                        const uint32_t b_addr = smem_u32(b_buf + (size_t)bs * lay.b_bytes);
-#pragma unroll
-                        for (int s16 = 0; s16 < kChunkK / 16; ++s16) {
+                        const uint32_t b_addr = smem_u32(b_buf + (size_t)bs * b_stage_bytes);
+                        for (int s16 = 0; s16 < lay.chunk_k / 16; ++s16) {
                             if (RIBN_TC_PROBE == 2 || RIBN_TC_PROBE == 5) break;
                             const uint64_t db = umma_desc(b_addr + s16 * 2 * b_lbo, b_lbo, 128);
                             umma_f16(d_main, umma_desc(a_addr + s16 * 2 * kALbo, kALbo, 128), db, idesc, (c | s16) != 0 ? 1u : 0u);
                             if (!q4k) umma_f16(d_main, umma_desc(a_addr + kAHalfBytes + s16 * 2 * kALbo, kALbo, 128), db, idesc, 1u);
                         }
-                        if (c == kChunksPerTile - 1) {
+                        if (c == chunks_per_tile - 1) {
                             // Q4_K: group minima x group sums of the activations (the chunk's a_full covers A2 as well)
                             if (alive) alive = mbar_wait(b2_full + 8 * p, (kt_count >> 1) & 1u, a.error_flag, 27);
                             tc_fence_after();
@@ -735,7 +738,7 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                 const uint32_t stage = w_count % (uint32_t)lay.w_stages;
                 if (alive) alive = mbar_wait(w_full + 8 * stage, (w_count / (uint32_t)lay.w_stages) & 1u, a.error_flag, 28);
                 const unsigned char* tile = w_ring + (size_t)stage * lay.w_stage_bytes + (size_t)rt_local * tb;
-                for (int c = 0; c < kChunksPerTile; ++c, ++a_count) {
+                for (int c = 0; c < chunks_per_tile; ++c, ++a_count) {
                     const uint32_t st = a_count % na;
                     if (a_count >= na && alive) alive = mbar_wait(a_empty + 8 * st, ((a_count / na) - 1u) & 1u, a.error_flag, 29);
                     unsigned char* planes = a_buf + (size_t)st * a_bytes;
@@ -746,12 +749,17 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                     float2* scales = row_scales + (size_t)(w_count & 3u) * kRows;
                     if (RIBN_TC_PROBE == 1 || RIBN_TC_PROBE == 5) {
                     } else if (present) {
-                        kq_chunk(type, tile, c, planes, a2, scales, rt_local * kTileRows, 0, lane);
-                        kq_chunk(type, tile, c, planes, a2, scales, rt_local * kTileRows, 1, lane);
+                        for (int piece = 0; piece < pieces; ++piece) {
+                            kq_chunk(type, tile, c * pieces + piece, piece * kChunkK, planes, a2, scales, rt_local * kTileRows, 0, lane);
+                            kq_chunk(type, tile, c * pieces + piece, piece * kChunkK, planes, a2, scales, rt_local * kTileRows, 1, lane);
+                        }
                     } else {
                         for (int pl = 0; pl < (type == kQ4_K ? 1 : 2); ++pl) {
-                            zero_rows_plane(planes + (size_t)pl * kAHalfBytes, rt_local * kTileRows, lane);
-                            zero_rows_plane(planes + (size_t)pl * kAHalfBytes, rt_local * kTileRows + 8, lane);
+                            for (int piece = 0; piece < pieces; ++piece) {
+                                unsigned char* at = planes + (size_t)pl * kAHalfBytes + (size_t)piece * (kChunkK / 8) * kALbo;
+                                zero_rows_plane(at, rt_local * kTileRows, lane);
+                                zero_rows_plane(at, rt_local * kTileRows + 8, lane);
+                            }
                         }
                         if (c == 0 && lane < 16) {
                             const int unit_row = rt_local * kTileRows + lane;
@@ -1012,12 +1020,13 @@ cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units
     lay.b2_bytes = lay.cols * 16 * (int)sizeof(__half);
     lay.w_stage_bytes = kRowTilesPerUnit * tile;
     const size_t budget = 220 * 1024;
-    // 64 KB of A stages: four single-plane stages when every unit is Q4_K, else two two-plane stages
+    // 64 KB of A stages, two of them: 128 inputs of one plane when every unit is Q4_K, else 64 inputs of two planes
     bool all_q4k = true;
     for (int i = 0; i < args.n_segments; ++i) all_q4k = all_q4k && args.seg[i].type == kQ4_K;
     lay.a_planes = all_q4k ? 1 : 2;
-    lay.a_stages = all_q4k ? 4 : 2;
-    size_t fixed = (size_t)4 * kAHalfBytes + (size_t)2 * kA2Bytes + (size_t)lay.a_stages * lay.b_bytes + (size_t)2 * lay.b2_bytes +
+    lay.a_stages = 2;
+    lay.chunk_k = all_q4k ? 2 * kChunkK : kChunkK;
+    size_t fixed = (size_t)4 * kAHalfBytes + (size_t)2 * kA2Bytes + (size_t)4 * lay.b_bytes + (size_t)2 * lay.b2_bytes +
                    (size_t)4 * kRows * sizeof(float2) + 16 + 384;
     lay.w_stages = (int)std::min<size_t>(3, (budget - fixed) / (size_t)lay.w_stage_bytes);
     if (lay.w_stages < 2) return cudaErrorInvalidValue;
