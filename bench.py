@@ -326,14 +326,31 @@ def run_serving(args):
     model = MODELS[args.model]
     rng = np.random.default_rng(0xC3 + rank)
     n = args.requests
-    prompt_hi = min(2048, args.serving_prompt_max)
-    prompts = rng.integers(min(128, prompt_hi), prompt_hi + 1, size=n)
-    outputs = rng.integers(min(64, args.serving_output_max), args.serving_output_max + 1, size=n)
-    arrivals = np.cumsum(rng.exponential(1.0 / args.arrival_rate, size=n))
+    if args.workload == "mixed":
+        # chunked-prefill mix: half the requests are long prompts (log-uniform 512 .. 16384 tokens, 8 outputs), the
+        # other half decode-heavy (context U[1024, 4096], 256 outputs); everything is queued at time zero
+        long_n = n // 2
+        prompt_hi = args.serving_prompt_max if args.serving_prompt_max > 2048 else 16384
+        prompts = np.concatenate([np.exp(rng.uniform(np.log(512), np.log(prompt_hi), size=long_n)).astype(np.int64),
+                                  rng.integers(1024, 4097, size=n - long_n)])
+        outputs = np.concatenate([np.full(long_n, 8), np.full(n - long_n, min(256, args.serving_output_max))])
+        order = rng.permutation(n)
+        prompts, outputs = prompts[order], outputs[order]
+        arrivals = np.zeros(n)
+        described = (f"{long_n} prompts log-uniform [512,{prompt_hi}] (8 outputs) interleaved with {n - long_n} decode-heavy "
+                     f"requests (context U[1024,4096], {int(outputs.max())} outputs), all queued at time zero")
+    else:
+        prompt_hi = min(2048, args.serving_prompt_max)
+        prompts = rng.integers(min(128, prompt_hi), prompt_hi + 1, size=n)
+        outputs = rng.integers(min(64, args.serving_output_max), args.serving_output_max + 1, size=n)
+        arrivals = np.cumsum(rng.exponential(1.0 / args.arrival_rate, size=n))
+        described = (f"Poisson arrivals {args.arrival_rate}/s, prompts U[{min(128, prompt_hi)},{prompt_hi}], outputs "
+                     f"U[{min(64, args.serving_output_max)},{args.serving_output_max}]")
     active = min(64, n)
-    chunk = min(2048, prompt_hi)
-    ex = ribn_b200.QwenB200(model, context_tokens=int(prompts.max() + outputs.max() + 16), max_sequences=active,
-                            max_batch_tokens=chunk + active, device=local, flags=0)
+    chunk = min(2048, int(prompts.max()))
+    pages = int(sum((int(p) + int(o) + 15) // 16 for p, o in zip(prompts, outputs))) + active
+    ex = ribn_b200.QwenB200(model, context_tokens=int((prompts + outputs).max() + 16), max_sequences=active,
+                            max_batch_tokens=chunk + active, kv_pages=pages, device=local, flags=0)
     ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q4_K_M)
     ex.finalize()
     engine = Engine(ex, EngineConfig(max_active_requests=active, max_queued_requests=n),
@@ -369,9 +386,7 @@ def run_serving(args):
         "vs_baseline": None,
         "dtype": "u8 x s8 / f16 tensor-core products over Q4_K,Q6_K weights, f32 scales and accumulation, f16 KV",
         "data": "synthetic",
-        "config": {"workload": f"{args.model} Q4_K_M-style serving: {n} requests per GPU, Poisson arrivals "
-                               f"{args.arrival_rate}/s, prompts U[{min(128, prompt_hi)},{prompt_hi}], outputs "
-                               f"U[{min(64, args.serving_output_max)},{args.serving_output_max}], {active} active, "
+        "config": {"workload": f"{args.model} Q4_K_M-style {args.workload}: {n} requests per GPU, {described}, {active} active, "
                                f"{chunk}-token prefill chunks, 16-token KV pages",
                    "parallelism": f"replicas x{world}"},
         "ttft_ms": {"p50": float(np.percentile(ttft, 50) * 1e3), "p95": float(np.percentile(ttft, 95) * 1e3)},
@@ -439,8 +454,9 @@ def main():
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / full-size parity leg")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
-                    help="decode: steady batch-1 / batch-N decode steps (the headline); serving: Poisson arrivals through the engine")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "mixed"],
+                    help="decode: steady batch-1 / batch-N decode steps (the headline); serving: Poisson arrivals through the engine; "
+                         "mixed: long chunked prefills interleaved with decode-heavy requests")
     ap.add_argument("--requests", type=int, default=96, help="serving: requests per GPU")
     ap.add_argument("--arrival-rate", type=float, default=8.0, help="serving: Poisson arrival rate, requests per second per GPU")
     ap.add_argument("--serving-prompt-max", type=int, default=2048)
@@ -453,7 +469,7 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
-    elif args.workload == "serving":
+    elif args.workload in ("serving", "mixed"):
         run_serving(args)
     else:
         run_ours(args)
