@@ -192,3 +192,27 @@ def test_batch_metadata_exact(ops):
     big = np.ones(1000, dtype=np.int32)
     cu, row, pos, kv = ops.batch_metadata(np.arange(1000) % 64, np.zeros(1000), big, tables)
     assert cu[-1] == 1000 and np.array_equal(row, np.arange(1000))
+
+
+@pytest.mark.parametrize("QH,KVH,HD,tokens,rows", [(32, 8, 128, 300, 64), (16, 8, 128, 200, 96), (8, 2, 64, 777, 150),
+                                                   (16, 1, 128, 64, 64)])
+def test_attention_large_launches_take_the_staged_span_kernel(ops, QH, KVH, HD, tokens, rows):
+    # rows x kv heads x spans >= 1024: K / V rows staged in shared memory once per query-head group;
+    # compared with the oracle per row, and paged == contiguous bit for bit.
+    rng = np.random.default_rng(QH + tokens)
+    q = rng.normal(0, 1, size=(rows, QH * HD)).astype(np.float32)
+    k = rng.normal(0, 1, tokens * KVH * HD).astype(np.float16).view(np.uint16)
+    v = rng.normal(0, 1, tokens * KVH * HD).astype(np.float16).view(np.uint16)
+    pages = (tokens + 15) // 16
+    results = []
+    for table in (list(range(pages)), list(rng.permutation(pages))):
+        pk = np.zeros((pages * 16, KVH * HD), dtype=np.uint16); pv = np.zeros_like(pk)
+        for t in range(tokens):
+            pk[table[t // 16] * 16 + t % 16] = k.reshape(tokens, -1)[t]
+            pv[table[t // 16] * 16 + t % 16] = v.reshape(tokens, -1)[t]
+        results.append(ops.attention(q, pk, pv, table, tokens, rows, QH, KVH, HD, variant=0))
+    assert np.array_equal(results[0].view(np.uint32), results[1].view(np.uint32))
+    for r in range(0, rows, 7):
+        seen = tokens - rows + 1 + r
+        want = orc.attention(q[r], k[: seen * KVH * HD], v[: seen * KVH * HD], seen, QH, KVH, HD)
+        assert np.max(np.abs(results[0][r] - want)) < 1e-4, r
