@@ -120,19 +120,35 @@ __global__ void attention_span_kernel(const AttnArgs a) {
     const long long row_stride = (long long)a.kv_heads * HD;
     const bool owns_self = FUSED && span == spans - 1;  // this CTA's span holds the token's own position
 
-    // The span's K and V rows come to shared memory once for all the query heads of the group
-    // (every thread keeps several independent 16-byte loads in flight).
+    // The span's K and V rows come to shared memory once for all the query heads of the group.  Eight
+    // 16-byte loads per thread are issued before any of them is stored, so that the copies overlap
+    // instead of each waiting for the previous one.
     {
         constexpr int kChunks = HD / 8;  // 16-byte pieces per row
-        const int rows = end - begin;
-        for (int idx = threadIdx.x; idx < 2 * rows * kChunks; idx += blockDim.x) {
-            const int which = idx / (rows * kChunks), rest = idx - which * rows * kChunks;
-            const int r = rest / kChunks, c = rest - r * kChunks;
-            const int key = begin + r;
-            if (owns_self && key == pos) continue;  // the token's own row is produced below
-            const long long phys = (long long)table[key / kPageTokens] * kPageTokens + key % kPageTokens;
-            const __half* src = (which ? a.cache_v : a.cache_k) + phys * row_stride + (long long)kvh * HD + c * 8;
-            *reinterpret_cast<uint4*>((which ? v_tile : k_tile) + r * kRowHalfs + c * 8) = *reinterpret_cast<const uint4*>(src);
+        constexpr int kBatch = 8;
+        const int rows = end - begin, total = 2 * rows * kChunks;
+        for (int first_idx = threadIdx.x; first_idx < total; first_idx += kBatch * blockDim.x) {
+            uint4 piece[kBatch];
+            __half* dst[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int idx = first_idx + u * blockDim.x;
+                dst[u] = nullptr;
+                if (idx < total) {
+                    const int which = idx / (rows * kChunks), rest = idx - which * rows * kChunks;
+                    const int r = rest / kChunks, c = rest - r * kChunks;
+                    const int key = begin + r;
+                    if (!(owns_self && key == pos)) {  // the token's own row is produced below
+                        const long long phys = (long long)table[key / kPageTokens] * kPageTokens + key % kPageTokens;
+                        piece[u] = *reinterpret_cast<const uint4*>((which ? a.cache_v : a.cache_k) + phys * row_stride + (long long)kvh * HD + c * 8);
+                        dst[u] = (which ? v_tile : k_tile) + r * kRowHalfs + c * 8;
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                if (dst[u] != nullptr) *reinterpret_cast<uint4*>(dst[u]) = piece[u];
+            }
         }
     }
 
