@@ -287,8 +287,8 @@ __global__ void attention_span_kernel(const AttnArgs a) {
 // The same span computation with every warp reading its keys straight from the cache: fewer steps in
 // series, which wins when the launch has too few CTAs to fill the GPU (decode at batch 1 or 2).  Both
 // kernels perform identical arithmetic in identical order.
-template <int HD, bool FUSED>
-__global__ void attention_span_direct_kernel(const AttnArgs a) {
+template <int HD, bool FUSED, bool EARLY>
+__global__ void __launch_bounds__(EARLY ? 256 : 512) attention_span_direct_kernel(const AttnArgs a) {
     constexpr int DPL = HD / 32;  // dims per lane in the lane-strided layout
     constexpr int CH = HD / 8;    // dims per lane in the P.V phase (8 chunks x 4 key groups)
     // Programmatic dependent launch: wait for the projections that produced q/k/v, then let the next
@@ -356,14 +356,39 @@ __global__ void attention_span_direct_kernel(const AttnArgs a) {
         const bool live = key < end;
         long long phys = 0;
         float s = -INFINITY;
+        uint4 kk[HD / 8];
         if (live) {
             phys = (long long)table[key / kPageTokens] * kPageTokens + key % kPageTokens;
             const uint4* kp = (owns_self && key == pos)
                                   ? reinterpret_cast<const uint4*>(k_self)
                                   : reinterpret_cast<const uint4*>(a.cache_k + phys * row_stride + (long long)kvh * HD);
-            uint4 kk[HD / 8];
 #pragma unroll
             for (int i = 0; i < HD / 8; ++i) kk[i] = kp[i];
+        }
+        // The V rows are requested right behind the K rows (their addresses need only the page lookup), so the two
+        // round trips to memory overlap; lane (kg, dc) takes keys j = 4 jj + kg and dims [dc * CH, dc * CH + CH).
+        const int count = min(32, end - base);
+        uint4 vv[8][CH / 8];
+        auto load_values = [&]() {
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+                const int j = jj * 4 + kg;
+                const long long pphys = __shfl_sync(0xffffffffu, phys, j);
+                const bool self = owns_self && base + j == pos;
+                const __half* vp = self ? v_self : a.cache_v + pphys * row_stride + (long long)kvh * HD;
+                if (j < count) {
+#pragma unroll
+                    for (int c = 0; c < CH / 8; ++c) vv[jj][c] = *reinterpret_cast<const uint4*>(vp + dc * CH + c * 8);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < CH / 8; ++c) vv[jj][c] = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+        };
+        // EARLY: groups of at most 8 query heads (256 threads) and head dims up to 128 keep both row sets in registers
+        constexpr bool kEarlyValues = EARLY;
+        if (kEarlyValues) load_values();
+        if (live) {
             float dot = 0.0f;
 #pragma unroll
             for (int i = 0; i < HD / 8; ++i) {
@@ -387,25 +412,10 @@ __global__ void attention_span_direct_kernel(const AttnArgs a) {
 #pragma unroll
         for (int d = 0; d < CH; ++d) acc[d] *= factor;
         run_max = new_max;
-        const int count = min(32, end - base);
-        // P.V: lane (kg, dc) takes keys j = 4 jj + kg and dims [dc * CH, dc * CH + CH)
-        uint4 vv[8][CH / 8];
+        if (!kEarlyValues) load_values();
         float pj[8];
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-            const int j = jj * 4 + kg;
-            pj[jj] = __shfl_sync(0xffffffffu, p, j);
-            const long long pphys = __shfl_sync(0xffffffffu, phys, j);
-            const bool self = owns_self && base + j == pos;
-            const __half* vp = self ? v_self : a.cache_v + pphys * row_stride + (long long)kvh * HD;
-            if (j < count) {
-#pragma unroll
-                for (int c = 0; c < CH / 8; ++c) vv[jj][c] = *reinterpret_cast<const uint4*>(vp + dc * CH + c * 8);
-            } else {
-#pragma unroll
-                for (int c = 0; c < CH / 8; ++c) vv[jj][c] = make_uint4(0u, 0u, 0u, 0u);
-            }
-        }
+        for (int jj = 0; jj < 8; ++jj) pj[jj] = __shfl_sync(0xffffffffu, p, jj * 4 + kg);
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj) {
 #pragma unroll
@@ -482,7 +492,16 @@ __global__ void attention_merge_kernel(const AttnArgs a) {
     __syncthreads();
     const int d = threadIdx.x;
     float sum = 0.0f;
-    for (int s = 0; s < spans; ++s) sum = fmaf(pp[s * (HD + 2) + d], weight[s], sum);
+    // eight spans' values are requested before the first is used (the additions keep span order)
+    for (int s0 = 0; s0 < spans; s0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = s0 + u < spans ? pp[(s0 + u) * (HD + 2) + d] : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (s0 + u < spans) sum = fmaf(v[u], weight[s0 + u], sum);
+        }
+    }
     const float value = sum / denom_s;
     a.out[((long long)t * a.q_heads + qh) * HD + d] = value;
     if (a.operand.dig != nullptr) {
@@ -544,8 +563,13 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
             e = fused ? launch_pdl(stream, attention_span_kernel<HD, true>, grid, q_per_kv * 32, smem, a, programmatic)
                       : launch_pdl(stream, attention_span_kernel<HD, false>, grid, q_per_kv * 32, smem, a, programmatic);
         } else {
-            e = fused ? launch_pdl(stream, attention_span_direct_kernel<HD, true>, grid, q_per_kv * 32, smem, a, programmatic)
-                      : launch_pdl(stream, attention_span_direct_kernel<HD, false>, grid, q_per_kv * 32, smem, a, programmatic);
+            if (HD <= 128 && q_per_kv <= 8) {
+                e = fused ? launch_pdl(stream, attention_span_direct_kernel<HD, true, (HD <= 128)>, grid, q_per_kv * 32, smem, a, programmatic)
+                          : launch_pdl(stream, attention_span_direct_kernel<HD, false, (HD <= 128)>, grid, q_per_kv * 32, smem, a, programmatic);
+            } else {
+                e = fused ? launch_pdl(stream, attention_span_direct_kernel<HD, true, false>, grid, q_per_kv * 32, smem, a, programmatic)
+                          : launch_pdl(stream, attention_span_direct_kernel<HD, false, false>, grid, q_per_kv * 32, smem, a, programmatic);
+            }
         }
         if (e != cudaSuccess) return e;
         if (launches) ++*launches;
