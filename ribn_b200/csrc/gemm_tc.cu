@@ -853,8 +853,13 @@ __global__ void tcq_reduce_kernel(const GemmArgs a, int slices, int total_n) {
     const int m = (int)(id / total_n);
     int n = (int)(id % total_n), seg = 0;
     while (seg + 1 < a.n_segments && n >= a.seg[seg].n) { n -= a.seg[seg].n; ++seg; }
-    float sum = 0.0f;
-    for (int sl = 0; sl < slices; ++sl) sum += a.partial[((size_t)sl * a.members + m) * total_n + (id % total_n)];
+    float sum = 0.0f, part[8];  // at most eight slices: all requested before the first is added
+#pragma unroll
+    for (int sl = 0; sl < 8; ++sl) part[sl] = sl < slices ? a.partial[((size_t)sl * a.members + m) * total_n + (id % total_n)] : 0.0f;
+#pragma unroll
+    for (int sl = 0; sl < 8; ++sl) {
+        if (sl < slices) sum += part[sl];
+    }
     const float v = sum * a.member_scale[m];
     float* y = a.seg[seg].y + (size_t)m * a.seg[seg].n + n;
     if (a.epilogue == kResidual) *y += v; else *y = v;
@@ -870,12 +875,19 @@ __global__ void tc_scale_kernel(const float* x, const int32_t* index, const floa
     const float4* row = reinterpret_cast<const float4*>(x + (size_t)(index ? index[m] : m) * k);
     const float4* nw = reinterpret_cast<const float4*>(norm_weight);
     float amax = 0.0f, ss = 0.0f;
-    for (int i = threadIdx.x; i < k / 4; i += blockDim.x) {   // k is a multiple of 256
-        const float4 v = row[i];
-        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-        float4 w = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-        if (nw != nullptr) w = nw[i];
-        amax = fmaxf(fmaxf(amax, fabsf(v.x * w.x)), fmaxf(fabsf(v.y * w.y), fmaxf(fabsf(v.z * w.z), fabsf(v.w * w.w))));
+    for (int i0 = threadIdx.x; i0 < k / 4; i0 += 4 * blockDim.x) {   // k is a multiple of 256; four loads in flight per trip
+        float4 v[4], w[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * blockDim.x;
+            v[u] = i < k / 4 ? row[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            w[u] = (nw != nullptr && i < k / 4) ? nw[i] : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            ss = fmaf(v[u].x, v[u].x, ss); ss = fmaf(v[u].y, v[u].y, ss); ss = fmaf(v[u].z, v[u].z, ss); ss = fmaf(v[u].w, v[u].w, ss);
+            amax = fmaxf(fmaxf(amax, fabsf(v[u].x * w[u].x)), fmaxf(fabsf(v[u].y * w[u].y), fmaxf(fabsf(v[u].z * w[u].z), fabsf(v[u].w * w[u].w))));
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {

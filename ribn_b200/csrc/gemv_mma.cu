@@ -610,7 +610,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
             if (a.in_has_norm) {
                 const float* ss = a.in.ss32 + (size_t)m * (K / 32);
                 float sum = 0.0f;
-                for (int i = lane; i < K / 32; i += 32) sum += ss[i];
+                // four loads in flight per trip (the additions keep their order)
+                for (int i0 = lane; i0 < K / 32; i0 += 128) {
+                    float part[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) part[u] = i0 + 32 * u < K / 32 ? ss[i0 + 32 * u] : 0.0f;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) sum += part[u];
+                }
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
                 inv_norm[m] = 1.0f / sqrtf(sum / (float)K + a.eps);
