@@ -16,6 +16,7 @@ from .executor import (  # noqa: F401
     StepKind,
 )
 from .engine import Engine, EngineConfig, SchedulePolicy, TokenRequest  # noqa: F401
+from . import gguf  # noqa: F401
 from . import ops  # noqa: F401
 
 QWEN3_0_6B = dict(layers=28, hidden=1024, q_heads=16, kv_heads=8, head_dim=128, ffn=3072, vocab=151936,

@@ -237,3 +237,31 @@ def test_synthetic_checkpoint_round_trips_through_the_oracle(built_library):
     got = ex.copy_logits(0)
     assert close(got, want) and done[0].tokens[0] == orc.argmax(got)
     seq.close(); oracle.close(); ex.close()
+
+
+def test_gguf_file_loads_to_the_same_logits(model, tmp_path):
+    """A checkpoint written as a GGUF file and loaded through the container reader decodes exactly as the
+    same tensors loaded one by one (the encoded bytes travel untouched)."""
+    from ribn_b200 import BatchItem, StepKind, gguf
+    import ribn_b200
+    tensors, _ = model
+    meta = {"general.architecture": "qwen3", "qwen3.block_count": MID["layers"], "qwen3.embedding_length": MID["hidden"],
+            "qwen3.feed_forward_length": MID["ffn"], "qwen3.attention.head_count": MID["q_heads"],
+            "qwen3.attention.head_count_kv": MID["kv_heads"], "qwen3.attention.key_length": MID["head_dim"],
+            "qwen3.rope.freq_base": float(MID["rope_base"]), "qwen3.attention.layer_norm_rms_epsilon": float(MID["rms_eps"])}
+    path = str(tmp_path / "mid.gguf")
+    gguf.write_gguf(path, meta, tensors)
+    loaded, cfg = gguf.load_qwen3(path, context_tokens=64, max_sequences=1, max_batch_tokens=32,
+                                  flags=ribn_b200.FLAG_KEEP_LOGITS)
+    assert {k: cfg[k] for k in ("layers", "hidden", "q_heads", "kv_heads", "head_dim", "ffn", "vocab")} == \
+           {k: MID[k] for k in ("layers", "hidden", "q_heads", "kv_heads", "head_dim", "ffn", "vocab")}
+    direct = build(MID, tensors, context_tokens=64, max_sequences=1, max_batch_tokens=32)
+    prompt = [3, 17, 250, 9, 41]
+    logits = []
+    for ex in (loaded, direct):
+        assert ex.admit(1, 1, prompt, 2).ready
+        item = BatchItem(1, StepKind.PREFILL, 0, len(prompt), 1)
+        ex.prepare([item]); ex.wait(ex.submit([item]))
+        logits.append(ex.copy_logits(0))
+        ex.close()
+    assert np.array_equal(logits[0].view(np.uint32), logits[1].view(np.uint32))
