@@ -85,6 +85,44 @@ SIGNATURES = {
     "ribn_b200_build_info": (C.c_char_p, []),
 }
 
+GEMMA_MAX_LAYERS = 64
+
+
+class GemmaConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in (
+        "layers", "hidden", "heads", "kv_heads", "head_dim", "global_head_dim", "ffn", "vocab", "ple", "ple_vocab",
+        "window", "context", "kv_shared")] + \
+        [(n, C.c_float) for n in ("eps", "softcap", "theta_local", "theta_global")] + \
+        [("full", C.c_int32 * GEMMA_MAX_LAYERS)] + \
+        [(n, C.c_int32) for n in ("max_sequences", "max_batch_tokens", "device", "flags")]
+
+
+class GemmaRow(C.Structure):
+    _fields_ = [("sequence", C.c_uint64), ("tokens", C.POINTER(C.c_uint32)), ("n_tokens", C.c_uint32),
+                ("want_output", C.c_uint32)]
+
+
+_U32P, _U64P = C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)
+# one entry per declaration in include/ribn_b200_gemma.h
+SIGNATURES.update({
+    "ribn_b200_gemma_create": (C.c_int, [C.POINTER(GemmaConfig), C.POINTER(_P), C.c_char_p, C.c_size_t]),
+    "ribn_b200_gemma_destroy": (C.c_int, [_P]),
+    "ribn_b200_gemma_last_error": (C.c_char_p, [_P]),
+    "ribn_b200_gemma_load_tensor": (C.c_int, [_P, C.c_char_p, _P, C.c_size_t]),
+    "ribn_b200_gemma_init_synthetic": (C.c_int, [_P, C.c_uint64]),
+    "ribn_b200_gemma_read_tensor": (C.c_int, [_P, C.c_char_p, _P, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "ribn_b200_gemma_finalize": (C.c_int, [_P]),
+    "ribn_b200_gemma_open": (C.c_int, [_P, _U64P]),
+    "ribn_b200_gemma_advance_prefill": (C.c_int, [_P, C.c_uint64, _P, C.c_uint32]),
+    "ribn_b200_gemma_prefill": (C.c_int, [_P, C.c_uint64, _P, C.c_uint32, _P, _U32P]),
+    "ribn_b200_gemma_decode": (C.c_int, [_P, C.c_uint64, C.c_uint32, _P, _U32P]),
+    "ribn_b200_gemma_position": (C.c_int, [_P, C.c_uint64, _U32P]),
+    "ribn_b200_gemma_close": (C.c_int, [_P, C.c_uint64]),
+    "ribn_b200_gemma_step": (C.c_int, [_P, C.POINTER(GemmaRow), C.c_uint32, _P, _P]),
+    "ribn_b200_gemma_synchronize": (C.c_int, [_P]),
+    "ribn_b200_gemma_last_step_stats": (C.c_int, [_P, C.POINTER(C.c_float), _U32P]),
+})
+
 _LIB = None
 
 
