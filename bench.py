@@ -401,6 +401,106 @@ def run_serving(args):
         dist.destroy_process_group()
 
 
+def run_gemma(args):
+    """The reduced Gemma-4 configuration (6 layers: 5 sliding-512 + 1 full; hidden 1152; 4 q / 1 kv heads of 256;
+    GeGLU 6912; vocab 32768; BF16 random-init N(0, 0.02)): four prompts of 17 / 64 / 129 / 300 uniform-random
+    ids, 32 greedy tokens each, through the executor protocol with all four sequences batched.  A step is one
+    whole job.  The CPU figure is the host decoder restated in oracle/gemma.c (the reference's own CPU path for
+    this configuration), timed on a bounded sample and checked token for token against the GPU."""
+    rank, world, local, dist = dist_setup(args.gpus)
+    import ribn_b200
+    from ribn_b200 import BatchItem, StepKind
+    cfg = ribn_b200.GEMMA4_REDUCED
+    model = ribn_b200.GemmaB200(cfg, max_sequences=4, max_batch_tokens=128, device=local)
+    model.init_synthetic(0x5EED)
+    tensors = None
+    if rank == 0 and not args.no_cpu:
+        tensors = {name: model.read_tensor(name) for name in model.tensor_names()}
+    model.finalize()
+    rng = np.random.default_rng(0xC1 + rank)
+    prompts = {i + 1: rng.integers(0, cfg["vocab"], n).tolist() for i, n in enumerate((17, 64, 129, 300))}
+    new_tokens = 32
+
+    def job():
+        ex = ribn_b200.GemmaExecutor(model)
+        for seq, p in prompts.items():
+            assert ex.admit(seq, seq, p, new_tokens).ready
+        got = {seq: [] for seq in prompts}
+        cursor = {seq: 0 for seq in prompts}
+        launches, device_ms = 0, 0.0
+        while any(len(got[q]) < new_tokens for q in prompts):
+            batch = []
+            for seq, p in prompts.items():
+                if len(got[seq]) >= new_tokens:
+                    continue
+                if cursor[seq] < len(p):
+                    n = min(128 // 4, len(p) - cursor[seq])
+                    batch.append(BatchItem(seq, StepKind.PREFILL, cursor[seq], n, int(cursor[seq] + n == len(p))))
+                else:
+                    batch.append(BatchItem(seq, StepKind.DECODE, cursor[seq], 1, 1))
+            ex.prepare(batch)
+            for done in ex.poll(ex.submit(batch)):
+                cursor[done.sequence] = done.prefix
+                got[done.sequence].extend(done.tokens)
+            ms, n_launch = model.last_step_stats()
+            launches += n_launch
+            device_ms += ms
+        ex.synchronize()
+        return got, launches, device_ms
+
+    for _ in range(args.warmup):
+        job()
+    barrier(dist, local)
+    with ClockSampler(local) as clocks:
+        t0 = time.perf_counter()
+        launches = 0
+        device_ms = 0.0
+        for _ in range(args.steps):
+            got, n_launch, ms = job()
+            launches += n_launch
+            device_ms += ms
+        seconds = time.perf_counter() - t0
+    barrier(dist, local)
+    seconds = all_max(dist, seconds, local)
+    generated = 4 * new_tokens
+    prompt_tokens = sum(len(p) for p in prompts.values())
+    out = {
+        "metric": "reduced Gemma-4 BF16 greedy generation, generated tok/s (per GPU x replicas)",
+        "value": world * generated * args.steps / (device_ms / 1e3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 storage, f32 arithmetic, one bf16 rounding per operation", "data": "synthetic",
+        "config": {"workload": "reduced Gemma-4 (6 layers, hidden 1152, 4q/1kv x 256, GeGLU 6912, vocab 32768): prompts "
+                               "17/64/129/300, 32 greedy tokens each, four sequences batched",
+                   "l2": "weights (0.41 GB) exceed L2", "parallelism": f"replicas x{world}"},
+        "e2e": {"value": world * generated * args.steps / seconds, "unit": "tok/s",
+                "h2d_bytes_per_step": 4 * (prompt_tokens + generated), "d2h_bytes_per_step": 4 * generated},
+        "gpu_launches": launches, "prompt_tokens": prompt_tokens, "generated_tokens": generated,
+        "clocks": clocks.summary(),
+    }
+    if rank == 0 and tensors is not None:
+        from oracle import gemma_binding as G
+        oracle = G.GemmaOracle(cfg, tensors)
+        ref = oracle.new_sequence()
+        t0 = time.perf_counter()
+        token = G.argmax(ref.prefill(prompts[1]))
+        want = [token]
+        for _ in range(7):
+            token = G.argmax(ref.decode(token))
+            want.append(token)
+        cpu_seconds = time.perf_counter() - t0
+        out["cpu_baseline"] = {"value": (len(prompts[1]) + 7) / cpu_seconds, "unit": "tok/s (prompt and generated tokens processed)",
+                               "cores": os.cpu_count(), "kind": "port",
+                               "sample": "the 17-token prompt and 8 greedy tokens, oracle/gemma.c with OpenMP over output columns"}
+        out["parity"] = {"greedy_tokens_equal": want == got[1][:8], "checked": 8}
+        out["tokens_processed_per_s"] = world * (prompt_tokens + generated) * args.steps / seconds
+        oracle.close()
+    model.close()
+    if rank == 0:
+        print(json.dumps(out))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def run_reference(args):
     """The reference's host CPU decoder (restated: oracle/oracle.c) on the GPU box's host cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -454,9 +554,9 @@ def main():
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / full-size parity leg")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "mixed"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "mixed", "gemma"],
                     help="decode: steady batch-1 / batch-N decode steps (the headline); serving: Poisson arrivals through the engine; "
-                         "mixed: long chunked prefills interleaved with decode-heavy requests")
+                         "mixed: long chunked prefills interleaved with decode-heavy requests; gemma: the reduced Gemma-4 BF16 job")
     ap.add_argument("--requests", type=int, default=96, help="serving: requests per GPU")
     ap.add_argument("--arrival-rate", type=float, default=8.0, help="serving: Poisson arrival rate, requests per second per GPU")
     ap.add_argument("--serving-prompt-max", type=int, default=2048)
@@ -471,6 +571,8 @@ def main():
         run_reference(args)
     elif args.workload in ("serving", "mixed"):
         run_serving(args)
+    elif args.workload == "gemma":
+        run_gemma(args)
     else:
         run_ours(args)
 

@@ -113,51 +113,97 @@ __global__ void gm_embed_kernel(const uint32_t* tokens, const bf16_t* embed, con
 }
 
 // ---------------------------------------------------------------------------------------------
-// Projection: out[r][n] = bf16(sum_k in[r][k] * w[n][k]) (linear.rs:23-66), the sum in k order.  A thread
-// owns one output column for a tile of RT rows: it streams its weight row with 128-bit loads (a warp covers
-// 32 rows of the matrix; their cache lines are consumed over the next eight trips) and keeps RT
-// independent accumulation chains, so the row tile costs no extra latency.  The input rows are read at the
-// same address by every thread (broadcast).
+// Projection: out[r][n] = bf16(sum_k in[r][k] * w[n][k]) (linear.rs:23-66), the sum in k order.  One warp
+// per block; a thread owns one output column for a tile of RT rows and keeps RT independent accumulation
+// chains.  Weights and input rows arrive in 256-input tiles through a three-stage cp.async pipeline: the
+// warp copies 32 weight-row segments of 512 bytes each (coalesced, L2-only) plus the RT input segments,
+// then each thread walks its own row of the tile in shared memory (rows are pitched by 528 bytes, so the
+// 128-bit reads of a quarter-warp fall in distinct banks; the input segment is a broadcast read).
 // ---------------------------------------------------------------------------------------------
-constexpr int kProjectThreads = 64;
+constexpr int kProjectCols = 32;                        // output columns (= threads) per block
+constexpr int kTileChunks = 32;                         // 16-byte chunks per row per tile (256 inputs)
+constexpr int kProjectStages = 3;
+constexpr int kRowPitch = kTileChunks * 16 + 16;        // bytes between weight rows of a tile
+
+__host__ __device__ constexpr int project_stage_bytes(int rt) { return rt * kTileChunks * 16 + kProjectCols * kRowPitch; }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
 
 template <int RT>
-__global__ void __launch_bounds__(kProjectThreads) gm_project_kernel(const bf16_t* __restrict__ in,
-                                                                     const int* __restrict__ row_index, int rows,
-                                                                     const bf16_t* __restrict__ w, int n, int k,
-                                                                     bf16_t* __restrict__ out) {
-    const int col = blockIdx.x * kProjectThreads + threadIdx.x;
+__global__ void __launch_bounds__(kProjectCols) gm_project_kernel(const bf16_t* __restrict__ in,
+                                                                  const int* __restrict__ row_index, int rows,
+                                                                  const bf16_t* __restrict__ w, int n, int k,
+                                                                  bf16_t* __restrict__ out) {
+    extern __shared__ __align__(16) unsigned char project_smem[];
+    constexpr int kStageBytes = project_stage_bytes(RT);
+    const int lane = threadIdx.x;
+    const int col0 = blockIdx.x * kProjectCols, col = col0 + lane;
     const int r0 = blockIdx.y * RT;
-    if (col >= n) return;
+    const int live_cols = min(kProjectCols, n - col0);
     const uint4* x[RT];
 #pragma unroll
     for (int r = 0; r < RT; ++r) {
         const int row = min(r0 + r, rows - 1);
         x[r] = reinterpret_cast<const uint4*>(in + (size_t)(row_index ? row_index[row] : row) * k);
     }
-    const uint4* wr = reinterpret_cast<const uint4*>(w + (size_t)col * k);
+    const uint4* wbase = reinterpret_cast<const uint4*>(w + (size_t)col0 * k);
+    const int chunks = k / 8, row_chunks = chunks;  // 16-byte chunks per weight row
+    const int tiles = (chunks + kTileChunks - 1) / kTileChunks;
+    const uint32_t smem = (uint32_t)__cvta_generic_to_shared(project_smem);
+
+    auto issue = [&](int tile) {
+        if (tile < tiles) {
+            const int c = tile * kTileChunks + lane;  // this lane's chunk of every row segment
+            if (c < chunks) {
+                const uint32_t stage = smem + (uint32_t)((tile % kProjectStages) * kStageBytes);
+#pragma unroll
+                for (int r = 0; r < RT; ++r) cp_async16(stage + (uint32_t)(r * kTileChunks * 16 + lane * 16), x[r] + c);
+                const uint32_t wdst = stage + (uint32_t)(RT * kTileChunks * 16 + lane * 16);
+                for (int j = 0; j < live_cols; ++j) cp_async16(wdst + (uint32_t)(j * kRowPitch), wbase + (size_t)j * row_chunks + c);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
     float acc[RT];
 #pragma unroll
     for (int r = 0; r < RT; ++r) acc[r] = 0.0f;
-    const int chunks = k / 8;
+#pragma unroll
+    for (int s = 0; s < kProjectStages - 1; ++s) issue(s);
+    for (int tile = 0; tile < tiles; ++tile) {
+        issue(tile + kProjectStages - 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(kProjectStages - 1) : "memory");
+        __syncwarp();
+        const unsigned char* stage = project_smem + (size_t)(tile % kProjectStages) * kStageBytes;
+        const uint4* xs = reinterpret_cast<const uint4*>(stage);
+        const uint4* ws = reinterpret_cast<const uint4*>(stage + RT * kTileChunks * 16 + lane * kRowPitch);
+        const int count = min(kTileChunks, chunks - tile * kTileChunks);
+        if (lane < live_cols) {
 #pragma unroll 4
-    for (int i = 0; i < chunks; ++i) {
-        const uint4 wv = __ldg(wr + i);
-        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+            for (int i = 0; i < count; ++i) {
+                const uint4 wv = ws[i];
+                const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-        for (int r = 0; r < RT; ++r) {
-            const uint4 xv = __ldg(x[r] + i);
-            const uint32_t xx[4] = {xv.x, xv.y, xv.z, xv.w};
+                for (int r = 0; r < RT; ++r) {
+                    const uint4 xv = xs[r * kTileChunks + i];
+                    const uint32_t xx[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                acc[r] = fmaf(__uint_as_float(xx[j] << 16), __uint_as_float(ww[j] << 16), acc[r]);
-                acc[r] = fmaf(__uint_as_float(xx[j] & 0xffff0000u), __uint_as_float(ww[j] & 0xffff0000u), acc[r]);
+                    for (int j = 0; j < 4; ++j) {
+                        acc[r] = fmaf(__uint_as_float(xx[j] << 16), __uint_as_float(ww[j] << 16), acc[r]);
+                        acc[r] = fmaf(__uint_as_float(xx[j] & 0xffff0000u), __uint_as_float(ww[j] & 0xffff0000u), acc[r]);
+                    }
+                }
             }
         }
+        __syncwarp();  // every lane has left this stage before a later tile's copies overwrite it
     }
+    if (lane < live_cols) {
 #pragma unroll
-    for (int r = 0; r < RT; ++r) {
-        if (r0 + r < rows) out[(size_t)(r0 + r) * n + col] = bf_round(acc[r]);
+        for (int r = 0; r < RT; ++r) {
+            if (r0 + r < rows) out[(size_t)(r0 + r) * n + col] = bf_round(acc[r]);
+        }
     }
 }
 
@@ -769,6 +815,13 @@ RIBN_B200_API int ribn_b200_gemma_finalize(ribn_b200_gemma* m) {
         GM_CUDA(m, cudaMemcpy(m->cosine[kind], cs.data(), sizeof(bf16_t) * cs.size(), cudaMemcpyHostToDevice));
         GM_CUDA(m, cudaMemcpy(m->sine[kind], sn.data(), sizeof(bf16_t) * sn.size(), cudaMemcpyHostToDevice));
     }
+    {
+        const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
+        GM_CUDA(m, cudaFuncSetAttribute(gm_project_kernel<1>, at, kProjectStages * project_stage_bytes(1)));
+        GM_CUDA(m, cudaFuncSetAttribute(gm_project_kernel<2>, at, kProjectStages * project_stage_bytes(2)));
+        GM_CUDA(m, cudaFuncSetAttribute(gm_project_kernel<4>, at, kProjectStages * project_stage_bytes(4)));
+        GM_CUDA(m, cudaFuncSetAttribute(gm_project_kernel<8>, at, kProjectStages * project_stage_bytes(8)));
+    }
     const int max_scores = (int)sizeof(float) * c.context;
     if (max_scores > 48 * 1024) {
         if (max_scores > 200 * 1024) return fail(m, RIBN_B200_ERROR, "context %d exceeds the attention kernel's score buffer", c.context);
@@ -788,13 +841,13 @@ struct Pass {
     uint32_t launches = 0;
 
     void project(const bf16_t* in, const int* row_index, int n_rows, const bf16_t* w, int n, int k, bf16_t* out) {
-        const dim3 block(kProjectThreads);
-        const unsigned col_blocks = (unsigned)((n + kProjectThreads - 1) / kProjectThreads);
+        const dim3 block(kProjectCols);
+        const unsigned col_blocks = (unsigned)((n + kProjectCols - 1) / kProjectCols);
         cudaStream_t s = m->stream;
-        if (n_rows <= 1) gm_project_kernel<1><<<dim3(col_blocks, 1), block, 0, s>>>(in, row_index, n_rows, w, n, k, out);
-        else if (n_rows <= 2) gm_project_kernel<2><<<dim3(col_blocks, 1), block, 0, s>>>(in, row_index, n_rows, w, n, k, out);
-        else if (n_rows <= 4) gm_project_kernel<4><<<dim3(col_blocks, 1), block, 0, s>>>(in, row_index, n_rows, w, n, k, out);
-        else gm_project_kernel<8><<<dim3(col_blocks, (unsigned)((n_rows + 7) / 8)), block, 0, s>>>(in, row_index, n_rows, w, n, k, out);
+        if (n_rows <= 1) gm_project_kernel<1><<<dim3(col_blocks, 1), block, kProjectStages * project_stage_bytes(1), s>>>(in, row_index, n_rows, w, n, k, out);
+        else if (n_rows <= 2) gm_project_kernel<2><<<dim3(col_blocks, 1), block, kProjectStages * project_stage_bytes(2), s>>>(in, row_index, n_rows, w, n, k, out);
+        else if (n_rows <= 4) gm_project_kernel<4><<<dim3(col_blocks, 1), block, kProjectStages * project_stage_bytes(4), s>>>(in, row_index, n_rows, w, n, k, out);
+        else gm_project_kernel<8><<<dim3(col_blocks, (unsigned)((n_rows + 7) / 8)), block, kProjectStages * project_stage_bytes(8), s>>>(in, row_index, n_rows, w, n, k, out);
         ++launches;
     }
     void rms(const bf16_t* in, const int* row_index, int n_rows, int width, const bf16_t* scale, const bf16_t* residual,
