@@ -74,9 +74,15 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 __device__ __forceinline__ float ordered_energy(const float* squares, int n, float* slot) {
     __syncthreads();
     if (threadIdx.x == 0) {
+        // 128-bit reads run ahead of the additions; the additions themselves stay in index order
+        const float4* quads = reinterpret_cast<const float4*>(squares);
         float energy = 0.0f;
 #pragma unroll 8
-        for (int i = 0; i < n; ++i) energy += squares[i];
+        for (int i = 0; i < n / 4; ++i) {
+            const float4 v = quads[i];
+            energy += v.x; energy += v.y; energy += v.z; energy += v.w;
+        }
+        for (int i = n & ~3; i < n; ++i) energy += squares[i];
         *slot = energy;
     }
     __syncthreads();
@@ -131,15 +137,30 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
+// Up to three matrices that read the same input rows share one launch (q | k | v, gate | up): their
+// column blocks are laid side by side in the grid.
+struct ProjectTargets {
+    const bf16_t* w[3];
+    bf16_t* out[3];
+    int n[3];
+    int first_block[3];  // first column block of each matrix
+    int count;
+};
+
 template <int RT>
 __global__ void __launch_bounds__(kProjectCols) gm_project_kernel(const bf16_t* __restrict__ in,
                                                                   const int* __restrict__ row_index, int rows,
-                                                                  const bf16_t* __restrict__ w, int n, int k,
-                                                                  bf16_t* __restrict__ out) {
+                                                                  const ProjectTargets targets, int k) {
     extern __shared__ __align__(16) unsigned char project_smem[];
     constexpr int kStageBytes = project_stage_bytes(RT);
     const int lane = threadIdx.x;
-    const int col0 = blockIdx.x * kProjectCols, col = col0 + lane;
+    int which = 0;
+    if (targets.count > 1 && (int)blockIdx.x >= targets.first_block[1]) which = 1;
+    if (targets.count > 2 && (int)blockIdx.x >= targets.first_block[2]) which = 2;
+    const bf16_t* __restrict__ w = targets.w[which];
+    bf16_t* __restrict__ out = targets.out[which];
+    const int n = targets.n[which];
+    const int col0 = ((int)blockIdx.x - targets.first_block[which]) * kProjectCols, col = col0 + lane;
     const int r0 = blockIdx.y * RT;
     const int live_cols = min(kProjectCols, n - col0);
     const uint4* x[RT];
@@ -217,24 +238,55 @@ __global__ void __launch_bounds__(kProjectCols) gm_project_kernel(const bf16_t* 
 __global__ void __launch_bounds__(256) gm_rms_kernel(const bf16_t* in, const int* row_index, int width, float eps,
                                                      const bf16_t* scale, const bf16_t* residual, const bf16_t* scalar,
                                                      int mode, bf16_t* out) {
-    extern __shared__ float squares[];
+    extern __shared__ __align__(16) float squares[];
     __shared__ float slot;
     const int row = blockIdx.x;
-    const bf16_t* x = in + (size_t)(row_index ? row_index[row] : row) * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float v = bf_load(x[i]);
-        squares[i] = v * v;
+    const uint4* x = reinterpret_cast<const uint4*>(in + (size_t)(row_index ? row_index[row] : row) * width);
+    const uint4* sc = reinterpret_cast<const uint4*>(scale);
+    const uint4* res = reinterpret_cast<const uint4*>(residual + (mode >= 1 ? (size_t)row * width : 0));
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)row * width);
+    const int chunks = width / 8;
+    // Eight values per thread per trip; everything a trip needs is requested before the sum starts.
+    for (int c0 = 0; c0 < chunks; c0 += blockDim.x) {
+        const int c = c0 + threadIdx.x;
+        if (c < chunks) {
+            const uint4 v = __ldg(x + c);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xffff0000u);
+                squares[c * 8 + 2 * j] = lo * lo;
+                squares[c * 8 + 2 * j + 1] = hi * hi;
+            }
+        }
     }
     const float energy = ordered_energy(squares, width, &slot);
     const float inverse = inverse_root(energy / (float)width + eps);
     const float factor = mode == 2 ? bf_load(scalar[0]) : 1.0f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v = bf_load(x[i]) * inverse;
-        if (scale) v *= bf_load(scale[i]);
-        bf16_t r = bf_round(v);
-        if (mode >= 1) r = bf_round(bf_load(residual[(size_t)row * width + i]) + bf_load(r));
-        if (mode == 2) r = bf_round(bf_load(r) * factor);
-        out[(size_t)row * width + i] = r;
+    for (int c0 = 0; c0 < chunks; c0 += blockDim.x) {
+        const int c = c0 + threadIdx.x;
+        if (c >= chunks) continue;
+        const uint4 v = __ldg(x + c);
+        const uint4 sv = scale ? __ldg(sc + c) : make_uint4(0, 0, 0, 0);
+        const uint4 rv = mode >= 1 ? res[c] : make_uint4(0, 0, 0, 0);
+        const uint32_t xw[4] = {v.x, v.y, v.z, v.w}, sw[4] = {sv.x, sv.y, sv.z, sv.w}, rw[4] = {rv.x, rv.y, rv.z, rv.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            bf16_t pair[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const bf16_t xb = (bf16_t)(e ? xw[j] >> 16 : xw[j] & 0xffffu);
+                float value = bf_load(xb) * inverse;
+                if (scale) value *= bf_load((bf16_t)(e ? sw[j] >> 16 : sw[j] & 0xffffu));
+                bf16_t r = bf_round(value);
+                if (mode >= 1) r = bf_round(bf_load((bf16_t)(e ? rw[j] >> 16 : rw[j] & 0xffffu)) + bf_load(r));
+                if (mode == 2) r = bf_round(bf_load(r) * factor);
+                pair[e] = r;
+            }
+            ow[j] = (uint32_t)pair[0] | ((uint32_t)pair[1] << 16);
+        }
+        dst[c] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
 }
 
@@ -251,7 +303,7 @@ __global__ void __launch_bounds__(256) gm_head_kernel(const bf16_t* q_in, const 
                                                       const int* position, const bf16_t* cosine, const bf16_t* sine,
                                                       int heads, int kv_heads, int width, float eps, int context,
                                                       bf16_t* q_out, bf16_t* key_cache, bf16_t* value_cache) {
-    __shared__ float squares[512];
+    __shared__ __align__(16) float squares[512];
     __shared__ float energy_slot;
     __shared__ bf16_t normed[512];
     const int row = blockIdx.x, h = blockIdx.y, half = width / 2, pos = position[row];
@@ -303,15 +355,37 @@ __global__ void __launch_bounds__(256) gm_head_kernel(const bf16_t* q_in, const 
 }
 
 // ---------------------------------------------------------------------------------------------
-// Attention (attention.rs:203-277).  One block per (row, query head).  Scores: one thread per key, the dot
-// product in channel order, BF16 rounded, scaling 1.0.  Softmax in FP32 with the total added in key order;
-// weights rounded to BF16; the output accumulates weight x value in FP32 over the keys in position order,
-// one thread per channel.  window 0 = full attention.  Dynamic shared memory: one float per visible key.
+// Attention (attention.rs:203-277).  One block per (row, query head).  Keys and values pass through shared
+// memory in tiles of 64 positions, copied by the whole block with coalesced 128-bit loads (many loads in
+// flight per thread: the kernel is bound by load latency, not by arithmetic).  Scores: one thread per key,
+// the dot product in channel order, BF16 rounded, scaling 1.0.  Softmax in FP32 with the total added in key
+// order; weights rounded to BF16; the output accumulates weight x value in FP32 over the keys in position
+// order, one thread per channel.  window 0 = full attention.
+// Dynamic shared memory: one float per visible key (rounded up to 16 bytes), then the tile.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) gm_attention_kernel(const bf16_t* q, const int* slot, const int* position,
-                                                           const bf16_t* key_cache, const bf16_t* value_cache, int heads,
-                                                           int kv_heads, int width, int window, int context, bf16_t* out) {
-    extern __shared__ float scores[];
+constexpr int kAttnTile = 64;
+
+__host__ __device__ inline size_t attention_smem_bytes(int visible, int width) {
+    return (((size_t)visible * sizeof(float) + 15) & ~(size_t)15) + (size_t)kAttnTile * ((size_t)width * 2 + 16);
+}
+
+// Copies rows [t0, t0 + count) of a cache (row stride `stride` elements, `chunks` 16-byte chunks used per
+// row) into the tile, whose rows are pitched by 16 extra bytes.
+__device__ __forceinline__ void attention_load_tile(const bf16_t* base, size_t stride, int t0, int count, int chunks,
+                                                    unsigned char* tile, int pitch) {
+    const int total = count * chunks;
+#pragma unroll 8
+    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+        const int key = idx / chunks, c = idx - key * chunks;
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(base + (size_t)(t0 + key) * stride) + c);
+        *reinterpret_cast<uint4*>(tile + (size_t)key * pitch + (size_t)c * 16) = v;
+    }
+}
+
+__global__ void __launch_bounds__(256, 1) gm_attention_kernel(const bf16_t* q, const int* slot, const int* position,
+                                                              const bf16_t* key_cache, const bf16_t* value_cache, int heads,
+                                                              int kv_heads, int width, int window, int context, bf16_t* out) {
+    extern __shared__ __align__(16) unsigned char attention_smem[];
     __shared__ float scratch[8];
     __shared__ float total_slot;
     __shared__ uint4 query[64];  // up to 512 BF16 channels
@@ -319,6 +393,9 @@ __global__ void __launch_bounds__(256) gm_attention_kernel(const bf16_t* q, cons
     const int kv_head = h / (heads / kv_heads);
     const int last = pos, first = window > 0 ? max(0, pos - (window - 1)) : 0;
     const int visible = last - first + 1;
+    float* scores = reinterpret_cast<float*>(attention_smem);
+    unsigned char* tile = attention_smem + (((size_t)visible * sizeof(float) + 15) & ~(size_t)15);
+    const int pitch = width * 2 + 16;
     const size_t stride = (size_t)kv_heads * width;
     const bf16_t* kbase = key_cache + ((size_t)slot[row] * context + first) * stride + (size_t)kv_head * width;
     const bf16_t* vbase = value_cache + ((size_t)slot[row] * context + first) * stride + (size_t)kv_head * width;
@@ -326,44 +403,69 @@ __global__ void __launch_bounds__(256) gm_attention_kernel(const bf16_t* q, cons
     for (int i = threadIdx.x; i < chunks; i += blockDim.x) {
         query[i] = reinterpret_cast<const uint4*>(q + ((size_t)row * heads + h) * width)[i];
     }
-    __syncthreads();
     float maximum = -INFINITY;
-    for (int t = threadIdx.x; t < visible; t += blockDim.x) {
-        const uint4* key = reinterpret_cast<const uint4*>(kbase + (size_t)t * stride);
-        float sum = 0.0f;
+    for (int t0 = 0; t0 < visible; t0 += kAttnTile) {
+        const int count = min(kAttnTile, visible - t0);
+        __syncthreads();  // the previous tile has been consumed (and the query is in place)
+        attention_load_tile(kbase, stride, t0, count, chunks, tile, pitch);
+        __syncthreads();
+        if ((int)threadIdx.x < count) {
+            const uint4* key = reinterpret_cast<const uint4*>(tile + (size_t)threadIdx.x * pitch);
+            float sum = 0.0f;
 #pragma unroll 4
-        for (int i = 0; i < chunks; ++i) {
-            const uint4 kv = __ldg(key + i);
-            const uint4 qq = query[i];
-            const uint32_t kk[4] = {kv.x, kv.y, kv.z, kv.w}, q4[4] = {qq.x, qq.y, qq.z, qq.w};
+            for (int i = 0; i < chunks; ++i) {
+                const uint4 kv = key[i];
+                const uint4 qq = query[i];
+                const uint32_t kk[4] = {kv.x, kv.y, kv.z, kv.w}, q4[4] = {qq.x, qq.y, qq.z, qq.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                sum = fmaf(__uint_as_float(q4[j] << 16), __uint_as_float(kk[j] << 16), sum);
-                sum = fmaf(__uint_as_float(q4[j] & 0xffff0000u), __uint_as_float(kk[j] & 0xffff0000u), sum);
+                for (int j = 0; j < 4; ++j) {
+                    sum = fmaf(__uint_as_float(q4[j] << 16), __uint_as_float(kk[j] << 16), sum);
+                    sum = fmaf(__uint_as_float(q4[j] & 0xffff0000u), __uint_as_float(kk[j] & 0xffff0000u), sum);
+                }
             }
+            const float score = bf_load(bf_round(sum));
+            scores[t0 + threadIdx.x] = score;
+            maximum = fmaxf(maximum, score);
         }
-        const float score = bf_load(bf_round(sum));
-        scores[t] = score;
-        maximum = fmaxf(maximum, score);
     }
-    maximum = block_max(maximum, scratch);
+    maximum = block_max(maximum, scratch);  // its barriers also order the score writes before the reads below
     for (int t = threadIdx.x; t < visible; t += blockDim.x) scores[t] = (float)exp((double)(scores[t] - maximum));
     __syncthreads();
     if (threadIdx.x == 0) {
+        const float4* quads = reinterpret_cast<const float4*>(scores);
         float total = 0.0f;
 #pragma unroll 8
-        for (int t = 0; t < visible; ++t) total += scores[t];
+        for (int t = 0; t < visible / 4; ++t) {
+            const float4 v = quads[t];
+            total += v.x; total += v.y; total += v.z; total += v.w;
+        }
+        for (int t = visible & ~3; t < visible; ++t) total += scores[t];
         total_slot = total;
     }
     __syncthreads();
     const float total = total_slot;
     for (int t = threadIdx.x; t < visible; t += blockDim.x) scores[t] = bf_load(bf_round(scores[t] / total));
-    __syncthreads();
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float acc = 0.0f;
-#pragma unroll 4
-        for (int t = 0; t < visible; ++t) acc = fmaf(scores[t], bf_load(vbase[(size_t)t * stride + c]), acc);
-        out[((size_t)row * heads + h) * width + c] = bf_round(acc);
+    // weight x value, two channels per thread at most (width <= 512)
+    float acc[2] = {0.0f, 0.0f};
+    for (int t0 = 0; t0 < visible; t0 += kAttnTile) {
+        const int count = min(kAttnTile, visible - t0);
+        __syncthreads();  // weights are final; the previous tile has been consumed
+        attention_load_tile(vbase, stride, t0, count, chunks, tile, pitch);
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int c = threadIdx.x + u * 256;
+            if (c < width) {
+                const bf16_t* column = reinterpret_cast<const bf16_t*>(tile) + c;
+#pragma unroll 8
+                for (int t = 0; t < count; ++t) acc[u] = fmaf(scores[t0 + t], bf_load(column[(size_t)t * (pitch / 2)]), acc[u]);
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int c = threadIdx.x + u * 256;
+        if (c < width) out[((size_t)row * heads + h) * width + c] = bf_round(acc[u]);
     }
 }
 
@@ -379,7 +481,7 @@ __global__ void gm_gelu_mul_kernel(const bf16_t* gate, const bf16_t* other, size
 __global__ void __launch_bounds__(256) gm_ple_kernel(const bf16_t* projection, const bf16_t* identity, const bf16_t* norm,
                                                      int rows, int ple, int packed, float projection_scale, float eps,
                                                      bf16_t* out) {
-    __shared__ float squares[1024];
+    __shared__ __align__(16) float squares[1024];
     __shared__ float energy_slot;
     __shared__ bf16_t scaled[1024];
     const int row = blockIdx.x, layer = blockIdx.y;
@@ -822,10 +924,10 @@ RIBN_B200_API int ribn_b200_gemma_finalize(ribn_b200_gemma* m) {
         GM_CUDA(m, cudaFuncSetAttribute(gm_project_kernel<4>, at, kProjectStages * project_stage_bytes(4)));
         GM_CUDA(m, cudaFuncSetAttribute(gm_project_kernel<8>, at, kProjectStages * project_stage_bytes(8)));
     }
-    const int max_scores = (int)sizeof(float) * c.context;
-    if (max_scores > 48 * 1024) {
-        if (max_scores > 200 * 1024) return fail(m, RIBN_B200_ERROR, "context %d exceeds the attention kernel's score buffer", c.context);
-        GM_CUDA(m, cudaFuncSetAttribute(gm_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_scores));
+    const size_t attention_bytes = attention_smem_bytes(c.context, c.head_dim > c.global_head_dim ? c.head_dim : c.global_head_dim);
+    if (attention_bytes > 48 * 1024) {
+        if (attention_bytes > 200 * 1024) return fail(m, RIBN_B200_ERROR, "context %d exceeds the attention kernel's score buffer", c.context);
+        GM_CUDA(m, cudaFuncSetAttribute(gm_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attention_bytes));
     }
     m->finalized = true;
     return RIBN_B200_OK;
@@ -840,15 +942,26 @@ struct Pass {
     int rows;
     uint32_t launches = 0;
 
-    void project(const bf16_t* in, const int* row_index, int n_rows, const bf16_t* w, int n, int k, bf16_t* out) {
+    void project_many(const bf16_t* in, const int* row_index, int n_rows, int k, int count, const bf16_t* const* w,
+                      const int* n, bf16_t* const* out) {
+        ProjectTargets t{};
+        t.count = count;
+        unsigned col_blocks = 0;
+        for (int i = 0; i < count; ++i) {
+            t.w[i] = w[i]; t.out[i] = out[i]; t.n[i] = n[i];
+            t.first_block[i] = (int)col_blocks;
+            col_blocks += (unsigned)((n[i] + kProjectCols - 1) / kProjectCols);
+        }
         const dim3 block(kProjectCols);
-        const unsigned col_blocks = (unsigned)((n + kProjectCols - 1) / kProjectCols);
         cudaStream_t s = m->stream;
-        if (n_rows <= 1) gm_project_kernel<1><<<dim3(col_blocks, 1), block, kProjectStages * project_stage_bytes(1), s>>>(in, row_index, n_rows, w, n, k, out);
-        else if (n_rows <= 2) gm_project_kernel<2><<<dim3(col_blocks, 1), block, kProjectStages * project_stage_bytes(2), s>>>(in, row_index, n_rows, w, n, k, out);
-        else if (n_rows <= 4) gm_project_kernel<4><<<dim3(col_blocks, 1), block, kProjectStages * project_stage_bytes(4), s>>>(in, row_index, n_rows, w, n, k, out);
-        else gm_project_kernel<8><<<dim3(col_blocks, (unsigned)((n_rows + 7) / 8)), block, kProjectStages * project_stage_bytes(8), s>>>(in, row_index, n_rows, w, n, k, out);
+        if (n_rows <= 1) gm_project_kernel<1><<<dim3(col_blocks, 1), block, kProjectStages * project_stage_bytes(1), s>>>(in, row_index, n_rows, t, k);
+        else if (n_rows <= 2) gm_project_kernel<2><<<dim3(col_blocks, 1), block, kProjectStages * project_stage_bytes(2), s>>>(in, row_index, n_rows, t, k);
+        else if (n_rows <= 4) gm_project_kernel<4><<<dim3(col_blocks, 1), block, kProjectStages * project_stage_bytes(4), s>>>(in, row_index, n_rows, t, k);
+        else gm_project_kernel<8><<<dim3(col_blocks, (unsigned)((n_rows + 7) / 8)), block, kProjectStages * project_stage_bytes(8), s>>>(in, row_index, n_rows, t, k);
         ++launches;
+    }
+    void project(const bf16_t* in, const int* row_index, int n_rows, const bf16_t* w, int n, int k, bf16_t* out) {
+        project_many(in, row_index, n_rows, k, 1, &w, &n, &out);
     }
     void rms(const bf16_t* in, const int* row_index, int n_rows, int width, const bf16_t* scale, const bf16_t* residual,
              const bf16_t* scalar, int mode, bf16_t* out) {
@@ -888,10 +1001,11 @@ int run_pass(ribn_b200_gemma* m, int rows, int n_out, int max_position, uint32_t
         const int w = width_of(c, l), kind = c.full[l] ? 1 : 0, owner = m->owner[l], cache = m->cache_of[owner];
         const bool owns = owner == l;
         p.rms(m->hidden, nullptr, rows, H, L[L_IN].data, nullptr, nullptr, 0, m->normed);
-        p.project(m->normed, nullptr, rows, L[L_Q].data, c.heads * w, H, m->q);
-        if (owns) {
-            p.project(m->normed, nullptr, rows, L[L_K].data, c.kv_heads * w, H, m->k);
-            p.project(m->normed, nullptr, rows, L[L_V].data, c.kv_heads * w, H, m->v);
+        {
+            const bf16_t* ws[3] = {L[L_Q].data, L[L_K].data, L[L_V].data};
+            const int ns[3] = {c.heads * w, c.kv_heads * w, c.kv_heads * w};
+            bf16_t* outs[3] = {m->q, m->k, m->v};
+            p.project_many(m->normed, nullptr, rows, H, owns ? 3 : 1, ws, ns, outs);
         }
         gm_head_kernel<<<dim3((unsigned)rows, (unsigned)(c.heads + (owns ? 2 * c.kv_heads : 0))), 128, 0, s>>>(
             m->q, m->k, m->v, L[L_QNORM].data, owns ? L[L_KNORM].data : nullptr, m->d_slot, m->d_position, m->cosine[kind],
@@ -900,7 +1014,7 @@ int run_pass(ribn_b200_gemma* m, int rows, int n_out, int max_position, uint32_t
         ++p.launches;
         const int window = kind ? 0 : c.window;
         const int visible = window > 0 && window < max_position + 1 ? window : max_position + 1;
-        gm_attention_kernel<<<dim3((unsigned)rows, (unsigned)c.heads), 256, sizeof(float) * (size_t)visible, s>>>(
+        gm_attention_kernel<<<dim3((unsigned)rows, (unsigned)c.heads), 256, attention_smem_bytes(visible, w), s>>>(
             m->q2, m->d_slot, m->d_position, m->key_cache[(size_t)cache], m->value_cache[(size_t)cache], c.heads, c.kv_heads, w,
             window, c.context, m->attended);
         ++p.launches;
@@ -908,8 +1022,12 @@ int run_pass(ribn_b200_gemma* m, int rows, int n_out, int max_position, uint32_t
         p.rms(m->projected, nullptr, rows, H, L[L_POST_ATTN].data, m->hidden, nullptr, 1, m->mid);
         // feed-forward (decoder.rs:570-600)
         p.rms(m->mid, nullptr, rows, H, L[L_PRE_FFN].data, nullptr, nullptr, 0, m->normed);
-        p.project(m->normed, nullptr, rows, L[L_GATE].data, c.ffn, H, m->gate);
-        p.project(m->normed, nullptr, rows, L[L_UP].data, c.ffn, H, m->up);
+        {
+            const bf16_t* ws[2] = {L[L_GATE].data, L[L_UP].data};
+            const int ns[2] = {c.ffn, c.ffn};
+            bf16_t* outs[2] = {m->gate, m->up};
+            p.project_many(m->normed, nullptr, rows, H, 2, ws, ns, outs);
+        }
         p.gelu_mul(m->gate, m->up, (size_t)rows * c.ffn, m->gate);
         p.project(m->gate, nullptr, rows, L[L_DOWN].data, H, c.ffn, m->projected);
         p.rms(m->projected, nullptr, rows, H, L[L_POST_FFN].data, m->mid, nullptr, 1, m->hidden);
