@@ -419,7 +419,7 @@ def run_gemma(args):
     model.finalize()
     rng = np.random.default_rng(0xC1 + rank)
     prompts = {i + 1: rng.integers(0, cfg["vocab"], n).tolist() for i, n in enumerate((17, 64, 129, 300))}
-    new_tokens = 32
+    new_tokens = args.gemma_new_tokens
 
     def job():
         ex = ribn_b200.GemmaExecutor(model)
@@ -470,7 +470,7 @@ def run_gemma(args):
         "warmup": args.warmup, "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16 storage, f32 arithmetic, one bf16 rounding per operation", "data": "synthetic",
         "config": {"workload": "reduced Gemma-4 (6 layers, hidden 1152, 4q/1kv x 256, GeGLU 6912, vocab 32768): prompts "
-                               "17/64/129/300, 32 greedy tokens each, four sequences batched",
+                               f"17/64/129/300, {new_tokens} greedy tokens each, four sequences batched",
                    "l2": "weights (0.41 GB) exceed L2", "parallelism": f"replicas x{world}"},
         "e2e": {"value": world * generated * args.steps / seconds, "unit": "tok/s",
                 "h2d_bytes_per_step": 4 * (prompt_tokens + generated), "d2h_bytes_per_step": 4 * generated},
@@ -561,6 +561,7 @@ def main():
     ap.add_argument("--arrival-rate", type=float, default=8.0, help="serving: Poisson arrival rate, requests per second per GPU")
     ap.add_argument("--serving-prompt-max", type=int, default=2048)
     ap.add_argument("--serving-output-max", type=int, default=512)
+    ap.add_argument("--gemma-new-tokens", type=int, default=32, help="gemma: greedy tokens per prompt")
     ap.add_argument("--scheme", default="q4_k_m", choices=["q4_k_m", "q8_0"], help="synthetic checkpoint's block types")
     args = ap.parse_args()
     global SCHEME

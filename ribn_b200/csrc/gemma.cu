@@ -132,6 +132,8 @@ constexpr int kProjectStages = 3;
 constexpr int kRowPitch = kTileChunks * 16 + 16;        // bytes between weight rows of a tile
 
 __host__ __device__ constexpr int project_stage_bytes(int rt) { return rt * kTileChunks * 16 + kProjectCols * kRowPitch; }
+// all stages, then the current tile's input rows expanded to FP32 (one conversion per value instead of one per column)
+__host__ __device__ constexpr int project_smem_bytes(int rt) { return kProjectStages * project_stage_bytes(rt) + rt * kTileChunks * 32; }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -181,8 +183,9 @@ __global__ void __launch_bounds__(kProjectCols) gm_project_kernel(const bf16_t* 
                 const uint32_t stage = smem + (uint32_t)((tile % kProjectStages) * kStageBytes);
 #pragma unroll
                 for (int r = 0; r < RT; ++r) cp_async16(stage + (uint32_t)(r * kTileChunks * 16 + lane * 16), x[r] + c);
-                const uint32_t wdst = stage + (uint32_t)(RT * kTileChunks * 16 + lane * 16);
-                for (int j = 0; j < live_cols; ++j) cp_async16(wdst + (uint32_t)(j * kRowPitch), wbase + (size_t)j * row_chunks + c);
+                uint32_t wdst = stage + (uint32_t)(RT * kTileChunks * 16 + lane * 16);
+                const uint4* src = wbase + c;
+                for (int j = 0; j < live_cols; ++j, wdst += kRowPitch, src += row_chunks) cp_async16(wdst, src);
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -198,27 +201,40 @@ __global__ void __launch_bounds__(kProjectCols) gm_project_kernel(const bf16_t* 
         asm volatile("cp.async.wait_group %0;" ::"n"(kProjectStages - 1) : "memory");
         __syncwarp();
         const unsigned char* stage = project_smem + (size_t)(tile % kProjectStages) * kStageBytes;
-        const uint4* xs = reinterpret_cast<const uint4*>(stage);
         const uint4* ws = reinterpret_cast<const uint4*>(stage + RT * kTileChunks * 16 + lane * kRowPitch);
         const int count = min(kTileChunks, chunks - tile * kTileChunks);
+        // lane l expands chunk l of every input row to FP32
+        float4* xf = reinterpret_cast<float4*>(project_smem + kProjectStages * kStageBytes);
+        if (lane < count) {
+#pragma unroll
+            for (int r = 0; r < RT; ++r) {
+                const uint4 xv = reinterpret_cast<const uint4*>(stage)[r * kTileChunks + lane];
+                xf[(r * kTileChunks + lane) * 2] = make_float4(__uint_as_float(xv.x << 16), __uint_as_float(xv.x & 0xffff0000u),
+                                                               __uint_as_float(xv.y << 16), __uint_as_float(xv.y & 0xffff0000u));
+                xf[(r * kTileChunks + lane) * 2 + 1] = make_float4(__uint_as_float(xv.z << 16), __uint_as_float(xv.z & 0xffff0000u),
+                                                                   __uint_as_float(xv.w << 16), __uint_as_float(xv.w & 0xffff0000u));
+            }
+        }
+        __syncwarp();
         if (lane < live_cols) {
 #pragma unroll 4
             for (int i = 0; i < count; ++i) {
                 const uint4 wv = ws[i];
-                const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+                const float w0 = __uint_as_float(wv.x << 16), w1 = __uint_as_float(wv.x & 0xffff0000u);
+                const float w2 = __uint_as_float(wv.y << 16), w3 = __uint_as_float(wv.y & 0xffff0000u);
+                const float w4 = __uint_as_float(wv.z << 16), w5 = __uint_as_float(wv.z & 0xffff0000u);
+                const float w6 = __uint_as_float(wv.w << 16), w7 = __uint_as_float(wv.w & 0xffff0000u);
 #pragma unroll
                 for (int r = 0; r < RT; ++r) {
-                    const uint4 xv = xs[r * kTileChunks + i];
-                    const uint32_t xx[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        acc[r] = fmaf(__uint_as_float(xx[j] << 16), __uint_as_float(ww[j] << 16), acc[r]);
-                        acc[r] = fmaf(__uint_as_float(xx[j] & 0xffff0000u), __uint_as_float(ww[j] & 0xffff0000u), acc[r]);
-                    }
+                    const float4 a = xf[(r * kTileChunks + i) * 2], b = xf[(r * kTileChunks + i) * 2 + 1];
+                    acc[r] = fmaf(a.x, w0, acc[r]); acc[r] = fmaf(a.y, w1, acc[r]);
+                    acc[r] = fmaf(a.z, w2, acc[r]); acc[r] = fmaf(a.w, w3, acc[r]);
+                    acc[r] = fmaf(b.x, w4, acc[r]); acc[r] = fmaf(b.y, w5, acc[r]);
+                    acc[r] = fmaf(b.z, w6, acc[r]); acc[r] = fmaf(b.w, w7, acc[r]);
                 }
             }
         }
-        __syncwarp();  // every lane has left this stage before a later tile's copies overwrite it
+        __syncwarp();  // every lane has left this stage (and the expanded rows) before they are overwritten
     }
     if (lane < live_cols) {
 #pragma unroll
@@ -374,11 +390,25 @@ __host__ __device__ inline size_t attention_smem_bytes(int visible, int width) {
 __device__ __forceinline__ void attention_load_tile(const bf16_t* base, size_t stride, int t0, int count, int chunks,
                                                     unsigned char* tile, int pitch) {
     const int total = count * chunks;
-#pragma unroll 8
-    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
-        const int key = idx / chunks, c = idx - key * chunks;
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(base + (size_t)(t0 + key) * stride) + c);
-        *reinterpret_cast<uint4*>(tile + (size_t)key * pitch + (size_t)c * 16) = v;
+    for (int first = 0; first < total; first += 8 * 256) {
+        // eight requests per thread leave before the first value is stored
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int idx = first + u * 256 + (int)threadIdx.x;
+            if (idx < total) {
+                const int key = idx / chunks, c = idx - key * chunks;
+                v[u] = __ldg(reinterpret_cast<const uint4*>(base + (size_t)(t0 + key) * stride) + c);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int idx = first + u * 256 + (int)threadIdx.x;
+            if (idx < total) {
+                const int key = idx / chunks, c = idx - key * chunks;
+                *reinterpret_cast<uint4*>(tile + (size_t)key * pitch + (size_t)c * 16) = v[u];
+            }
+        }
     }
 }
 
@@ -919,10 +949,10 @@ RIBN_B200_API int ribn_b200_gemma_finalize(ribn_b200_gemma* m) {
     }
     {
         const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
-        GM_CUDA(m, cudaFuncSetAttribute(gm_project_kernel<1>, at, kProjectStages * project_stage_bytes(1)));
-        GM_CUDA(m, cudaFuncSetAttribute(gm_project_kernel<2>, at, kProjectStages * project_stage_bytes(2)));
-        GM_CUDA(m, cudaFuncSetAttribute(gm_project_kernel<4>, at, kProjectStages * project_stage_bytes(4)));
-        GM_CUDA(m, cudaFuncSetAttribute(gm_project_kernel<8>, at, kProjectStages * project_stage_bytes(8)));
+        GM_CUDA(m, cudaFuncSetAttribute(gm_project_kernel<1>, at, project_smem_bytes(1)));
+        GM_CUDA(m, cudaFuncSetAttribute(gm_project_kernel<2>, at, project_smem_bytes(2)));
+        GM_CUDA(m, cudaFuncSetAttribute(gm_project_kernel<4>, at, project_smem_bytes(4)));
+        GM_CUDA(m, cudaFuncSetAttribute(gm_project_kernel<8>, at, project_smem_bytes(8)));
     }
     const size_t attention_bytes = attention_smem_bytes(c.context, c.head_dim > c.global_head_dim ? c.head_dim : c.global_head_dim);
     if (attention_bytes > 48 * 1024) {
@@ -954,10 +984,10 @@ struct Pass {
         }
         const dim3 block(kProjectCols);
         cudaStream_t s = m->stream;
-        if (n_rows <= 1) gm_project_kernel<1><<<dim3(col_blocks, 1), block, kProjectStages * project_stage_bytes(1), s>>>(in, row_index, n_rows, t, k);
-        else if (n_rows <= 2) gm_project_kernel<2><<<dim3(col_blocks, 1), block, kProjectStages * project_stage_bytes(2), s>>>(in, row_index, n_rows, t, k);
-        else if (n_rows <= 4) gm_project_kernel<4><<<dim3(col_blocks, 1), block, kProjectStages * project_stage_bytes(4), s>>>(in, row_index, n_rows, t, k);
-        else gm_project_kernel<8><<<dim3(col_blocks, (unsigned)((n_rows + 7) / 8)), block, kProjectStages * project_stage_bytes(8), s>>>(in, row_index, n_rows, t, k);
+        if (n_rows <= 1) gm_project_kernel<1><<<dim3(col_blocks, 1), block, project_smem_bytes(1), s>>>(in, row_index, n_rows, t, k);
+        else if (n_rows <= 2) gm_project_kernel<2><<<dim3(col_blocks, 1), block, project_smem_bytes(2), s>>>(in, row_index, n_rows, t, k);
+        else if (n_rows <= 4) gm_project_kernel<4><<<dim3(col_blocks, 1), block, project_smem_bytes(4), s>>>(in, row_index, n_rows, t, k);
+        else gm_project_kernel<8><<<dim3(col_blocks, (unsigned)((n_rows + 7) / 8)), block, project_smem_bytes(8), s>>>(in, row_index, n_rows, t, k);
         ++launches;
     }
     void project(const bf16_t* in, const int* row_index, int n_rows, const bf16_t* w, int n, int k, bf16_t* out) {
