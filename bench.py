@@ -309,6 +309,9 @@ def run_ours(args):
                           "gpu_launches": launchesb, "step_roofline": step_roofline(B, devb), "clocks": clocksb,
                           "x_batch1": (world * B * args.steps / devb) / value1}
     ex.close()
+    if world == 1 and not args.no_cpu and not args.no_gemma:
+        # the reference's CPU-runnable configuration, as a second workload of the same library
+        out["gemma_reduced"] = gemma_job(args, rank, world, local, dist, 3, 3, True)
     if rank == 0:
         print(json.dumps(out))
     if dist is not None:
@@ -408,13 +411,22 @@ def run_gemma(args):
     whole job.  The CPU figure is the host decoder restated in oracle/gemma.c (the reference's own CPU path for
     this configuration), timed on a bounded sample and checked token for token against the GPU."""
     rank, world, local, dist = dist_setup(args.gpus)
+    out = gemma_job(args, rank, world, local, dist, args.steps, args.warmup, not args.no_cpu)
+    if rank == 0:
+        print(json.dumps(out))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def gemma_job(args, rank, world, local, dist, steps, warmup, with_cpu):
+    """Runs the reduced Gemma-4 job `steps` times and returns its result line."""
     import ribn_b200
     from ribn_b200 import BatchItem, StepKind
     cfg = ribn_b200.GEMMA4_REDUCED
     model = ribn_b200.GemmaB200(cfg, max_sequences=4, max_batch_tokens=128, device=local)
     model.init_synthetic(0x5EED)
     tensors = None
-    if rank == 0 and not args.no_cpu:
+    if rank == 0 and with_cpu:
         tensors = {name: model.read_tensor(name) for name in model.tensor_names()}
     model.finalize()
     rng = np.random.default_rng(0xC1 + rank)
@@ -448,14 +460,14 @@ def run_gemma(args):
         ex.synchronize()
         return got, launches, device_ms
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         job()
     barrier(dist, local)
     with ClockSampler(local) as clocks:
         t0 = time.perf_counter()
         launches = 0
         device_ms = 0.0
-        for _ in range(args.steps):
+        for _ in range(steps):
             got, n_launch, ms = job()
             launches += n_launch
             device_ms += ms
@@ -466,13 +478,13 @@ def run_gemma(args):
     prompt_tokens = sum(len(p) for p in prompts.values())
     out = {
         "metric": "reduced Gemma-4 BF16 greedy generation, generated tok/s (per GPU x replicas)",
-        "value": world * generated * args.steps / (device_ms / 1e3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "value": world * generated * steps / (device_ms / 1e3), "unit": "tok/s", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": seconds / steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16 storage, f32 arithmetic, one bf16 rounding per operation", "data": "synthetic",
         "config": {"workload": "reduced Gemma-4 (6 layers, hidden 1152, 4q/1kv x 256, GeGLU 6912, vocab 32768): prompts "
                                f"17/64/129/300, {new_tokens} greedy tokens each, four sequences batched",
                    "l2": "weights (0.41 GB) exceed L2", "parallelism": f"replicas x{world}"},
-        "e2e": {"value": world * generated * args.steps / seconds, "unit": "tok/s",
+        "e2e": {"value": world * generated * steps / seconds, "unit": "tok/s",
                 "h2d_bytes_per_step": 4 * (prompt_tokens + generated), "d2h_bytes_per_step": 4 * generated},
         "gpu_launches": launches, "prompt_tokens": prompt_tokens, "generated_tokens": generated,
         "clocks": clocks.summary(),
@@ -492,13 +504,10 @@ def run_gemma(args):
                                "cores": os.cpu_count(), "kind": "port",
                                "sample": "the 17-token prompt and 8 greedy tokens, oracle/gemma.c with OpenMP over output columns"}
         out["parity"] = {"greedy_tokens_equal": want == got[1][:8], "checked": 8}
-        out["tokens_processed_per_s"] = world * (prompt_tokens + generated) * args.steps / seconds
+        out["tokens_processed_per_s"] = world * (prompt_tokens + generated) * steps / seconds
         oracle.close()
     model.close()
-    if rank == 0:
-        print(json.dumps(out))
-    if dist is not None:
-        dist.destroy_process_group()
+    return out
 
 
 def run_reference(args):
@@ -561,6 +570,7 @@ def main():
     ap.add_argument("--arrival-rate", type=float, default=8.0, help="serving: Poisson arrival rate, requests per second per GPU")
     ap.add_argument("--serving-prompt-max", type=int, default=2048)
     ap.add_argument("--serving-output-max", type=int, default=512)
+    ap.add_argument("--no-gemma", action="store_true", help="decode: skip the reduced Gemma-4 job appended to the default line")
     ap.add_argument("--gemma-new-tokens", type=int, default=32, help="gemma: greedy tokens per prompt")
     ap.add_argument("--scheme", default="q4_k_m", choices=["q4_k_m", "q8_0"], help="synthetic checkpoint's block types")
     args = ap.parse_args()

@@ -121,19 +121,19 @@ __global__ void gm_embed_kernel(const uint32_t* tokens, const bf16_t* embed, con
 // ---------------------------------------------------------------------------------------------
 // Projection: out[r][n] = bf16(sum_k in[r][k] * w[n][k]) (linear.rs:23-66), the sum in k order.  One warp
 // per block; a thread owns one output column for a tile of RT rows and keeps RT independent accumulation
-// chains.  Weights and input rows arrive in 256-input tiles through a three-stage cp.async pipeline: the
+// chains.  Weights and input rows arrive in 256-input tiles through a two- or three-stage cp.async pipeline: the
 // warp copies 32 weight-row segments of 512 bytes each (coalesced, L2-only) plus the RT input segments,
 // then each thread walks its own row of the tile in shared memory (rows are pitched by 528 bytes, so the
 // 128-bit reads of a quarter-warp fall in distinct banks; the input segment is a broadcast read).
 // ---------------------------------------------------------------------------------------------
 constexpr int kProjectCols = 32;                        // output columns (= threads) per block
 constexpr int kTileChunks = 32;                         // 16-byte chunks per row per tile (256 inputs)
-constexpr int kProjectStages = 3;
+__host__ __device__ constexpr int project_stages(int rt) { return rt >= 8 ? 2 : 3; }  // an 8-row tile spends four times longer per stage
 constexpr int kRowPitch = kTileChunks * 16 + 16;        // bytes between weight rows of a tile
 
 __host__ __device__ constexpr int project_stage_bytes(int rt) { return rt * kTileChunks * 16 + kProjectCols * kRowPitch; }
 // all stages, then the current tile's input rows expanded to FP32 (one conversion per value instead of one per column)
-__host__ __device__ constexpr int project_smem_bytes(int rt) { return kProjectStages * project_stage_bytes(rt) + rt * kTileChunks * 32; }
+__host__ __device__ constexpr int project_smem_bytes(int rt) { return project_stages(rt) * project_stage_bytes(rt) + rt * kTileChunks * 32; }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -155,6 +155,7 @@ __global__ void __launch_bounds__(kProjectCols) gm_project_kernel(const bf16_t* 
                                                                   const ProjectTargets targets, int k) {
     extern __shared__ __align__(16) unsigned char project_smem[];
     constexpr int kStageBytes = project_stage_bytes(RT);
+    constexpr int kProjectStages = project_stages(RT);
     const int lane = threadIdx.x;
     int which = 0;
     if (targets.count > 1 && (int)blockIdx.x >= targets.first_block[1]) which = 1;
