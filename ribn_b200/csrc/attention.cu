@@ -120,36 +120,28 @@ __global__ void attention_span_kernel(const AttnArgs a) {
     const long long row_stride = (long long)a.kv_heads * HD;
     const bool owns_self = FUSED && span == spans - 1;  // this CTA's span holds the token's own position
 
-    // The span's K and V rows come to shared memory once for all the query heads of the group.  Eight
-    // 16-byte loads per thread are issued before any of them is stored, so that the copies overlap
-    // instead of each waiting for the previous one.
+    // The span's K and V rows come to shared memory once for all the query heads of the group, as
+    // asynchronous 16-byte copies that bypass the registers: every piece of the span is in flight at once.
+    // The span's page-table entries (at most five 16-token pages) are fetched first, so that no copy waits
+    // on a table lookup of its own.
+    __shared__ long long page_base[8];
     {
+        const int page0 = begin / kPageTokens, pages = (end - 1) / kPageTokens - page0 + 1;
+        if ((int)threadIdx.x < pages) page_base[threadIdx.x] = (long long)table[page0 + threadIdx.x] * kPageTokens;
+        __syncthreads();
         constexpr int kChunks = HD / 8;  // 16-byte pieces per row
-        constexpr int kBatch = 8;
         const int rows = end - begin, total = 2 * rows * kChunks;
-        for (int first_idx = threadIdx.x; first_idx < total; first_idx += kBatch * blockDim.x) {
-            uint4 piece[kBatch];
-            __half* dst[kBatch];
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                const int idx = first_idx + u * blockDim.x;
-                dst[u] = nullptr;
-                if (idx < total) {
-                    const int which = idx / (rows * kChunks), rest = idx - which * rows * kChunks;
-                    const int r = rest / kChunks, c = rest - r * kChunks;
-                    const int key = begin + r;
-                    if (!(owns_self && key == pos)) {  // the token's own row is produced below
-                        const long long phys = (long long)table[key / kPageTokens] * kPageTokens + key % kPageTokens;
-                        piece[u] = *reinterpret_cast<const uint4*>((which ? a.cache_v : a.cache_k) + phys * row_stride + (long long)kvh * HD + c * 8);
-                        dst[u] = (which ? v_tile : k_tile) + r * kRowHalfs + c * 8;
-                    }
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                if (dst[u] != nullptr) *reinterpret_cast<uint4*>(dst[u]) = piece[u];
-            }
+        for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+            const int which = idx / (rows * kChunks), rest = idx - which * rows * kChunks;
+            const int r = rest / kChunks, c = rest - r * kChunks;
+            const int key = begin + r;
+            if (owns_self && key == pos) continue;  // the token's own row is produced below
+            const long long phys = page_base[key / kPageTokens - page0] + key % kPageTokens;
+            const __half* src = (which ? a.cache_v : a.cache_k) + phys * row_stride + (long long)kvh * HD + c * 8;
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared((which ? v_tile : k_tile) + r * kRowHalfs + c * 8);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     }
 
     float* qs = q_smem + warp * HD;
@@ -182,6 +174,7 @@ __global__ void attention_span_kernel(const AttnArgs a) {
             ck[d] = kh; cv[d] = vh;
         }
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
 
     const int kg = lane >> 3, dc = lane & 7;
