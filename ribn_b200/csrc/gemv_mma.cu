@@ -240,6 +240,13 @@ __device__ __forceinline__ float byte_f32(uint32_t w, int i) {
     return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | (uint32_t)i)) - 8388608.0f;
 }
 
+// bytes i and i + 1 of w as floats minus `bias` (both exact), as one packed subtraction
+__device__ __forceinline__ float2 bytes_f32x2(uint32_t w, int i, float bias) {
+    const float2 raw = make_float2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | (uint32_t)i)),
+                                   __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | (uint32_t)(i + 1))));
+    return __fadd2_rn(raw, make_float2(-bias, -bias));
+}
+
 // Shared-memory accesses by 32-bit shared-space address: the hot loop then needs one add per access
 // instead of generic 64-bit pointer arithmetic.
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -339,20 +346,24 @@ __device__ __forceinline__ void tile_q4k(uint32_t tile, const Lane& ln, int kb, 
         const uint32_t mn = ln.half ? (((h.w >> 4) & kNibbles) | ((h.z >> 2) & kTopBits)) : (h.z & 0x3F3F3F3Fu);
         // Odd groups reach the MMA as 16 q (their nibbles stay in the high half of each byte), so their
         // scale carries the exact factor 1/16.
-        float gs[4], gm[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { gs[i] = ((i & 1) ? d * 0.0625f : d) * byte_f32(sc, i); gm[i] = dmin * byte_f32(mn, i); }
+        // pair form of the same operations (packed FP32, sm_100): components 0 / 1 and 2 / 3
+        const float2 dd = make_float2(d, d * 0.0625f), mm2 = make_float2(dmin, dmin);
+        const float2 gs01 = __fmul2_rn(dd, bytes_f32x2(sc, 0, 8388608.0f)), gs23 = __fmul2_rn(dd, bytes_f32x2(sc, 2, 8388608.0f));
+        const float2 gm01 = __fmul2_rn(mm2, bytes_f32x2(mn, 0, 8388608.0f)), gm23 = __fmul2_rn(mm2, bytes_f32x2(mn, 2, 8388608.0f));
 #pragma unroll
         for (int mm = 0; mm < MEMBERS; ++mm) {
             const float4 sx = lds128f(ln.sx + (uint32_t)(mm * (ln.K / 32) + kb * 8 + ln.half * 4) * 4);
             const uint32_t sxs = ln.sxs + (uint32_t)(mm * (ln.K / 16) + kb * 16 + ln.half * 8) * 4;
             const float4 sa = lds128f(sxs), sb = lds128f(sxs + 16);
             const uint32_t out = ln.hdr_wr + mm * kHdrMember;
-            sts128f(out + ln.half * 16, gs[0] * sx.x, gs[1] * sx.y, gs[2] * sx.z, gs[3] * sx.w);
-            float off = gm[0] * (sa.x + sa.y);
-            off = fmaf(gm[1], sa.z + sa.w, off);
-            off = fmaf(gm[2], sb.x + sb.y, off);
-            off = fmaf(gm[3], sb.z + sb.w, off);
+            const float2 h01 = __fmul2_rn(gs01, make_float2(sx.x, sx.y)), h23 = __fmul2_rn(gs23, make_float2(sx.z, sx.w));
+            sts128f(out + ln.half * 16, h01.x, h01.y, h23.x, h23.y);
+            const float2 ta = __fadd2_rn(make_float2(sa.x, sa.z), make_float2(sa.y, sa.w));
+            const float2 tb = __fadd2_rn(make_float2(sb.x, sb.z), make_float2(sb.y, sb.w));
+            float off = gm01.x * ta.x;
+            off = fmaf(gm01.y, ta.y, off);
+            off = fmaf(gm23.x, tb.x, off);
+            off = fmaf(gm23.y, tb.y, off);
             off += __shfl_xor_sync(0xffffffffu, off, 1);
             if (ln.half == 0) sts32f(out + kHdrOff, -off);
         }
@@ -385,11 +396,14 @@ __device__ __forceinline__ void tile_q6k(uint32_t tile, const Lane& ln, int kb, 
         const uint2 s8 = lds64(tile + 3072 + row * 16 + ln.half * 8);
         const float d = __half2float(__ushort_as_half((unsigned short)lds16(tile + 3328 + row * 2)));
         float gs[8];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            // signed byte: flip the sign bit, convert as unsigned, subtract 128
-            gs[i] = d * (byte_f32(s8.x ^ 0x80808080u, i) - 128.0f);
-            gs[4 + i] = d * (byte_f32(s8.y ^ 0x80808080u, i) - 128.0f);
+        {
+            // signed byte: flip the sign bit, read as unsigned on top of 2^23, subtract 2^23 + 128 (exact); pair form
+            const float2 dd = make_float2(d, d);
+            const uint32_t lo = s8.x ^ 0x80808080u, hi = s8.y ^ 0x80808080u;
+            const float2 g01 = __fmul2_rn(dd, bytes_f32x2(lo, 0, 8388736.0f)), g23 = __fmul2_rn(dd, bytes_f32x2(lo, 2, 8388736.0f));
+            const float2 g45 = __fmul2_rn(dd, bytes_f32x2(hi, 0, 8388736.0f)), g67 = __fmul2_rn(dd, bytes_f32x2(hi, 2, 8388736.0f));
+            gs[0] = g01.x; gs[1] = g01.y; gs[2] = g23.x; gs[3] = g23.y;
+            gs[4] = g45.x; gs[5] = g45.y; gs[6] = g67.x; gs[7] = g67.y;
         }
 #pragma unroll
         for (int mm = 0; mm < MEMBERS; ++mm) {
@@ -397,8 +411,12 @@ __device__ __forceinline__ void tile_q6k(uint32_t tile, const Lane& ln, int kb, 
             const uint32_t sxs = ln.sxs + (uint32_t)(mm * (ln.K / 16) + kb * 16 + ln.half * 8) * 4;
             const float4 sa = lds128f(sxs), sb = lds128f(sxs + 16);
             const uint32_t out = ln.hdr_wr + mm * kHdrMember;
-            sts128f(out + ln.half * 32, gs[0] * sx.x, gs[1] * sx.x, gs[2] * sx.y, gs[3] * sx.y);
-            sts128f(out + ln.half * 32 + 16, gs[4] * sx.z, gs[5] * sx.z, gs[6] * sx.w, gs[7] * sx.w);
+            const float2 h01 = __fmul2_rn(make_float2(gs[0], gs[1]), make_float2(sx.x, sx.x));
+            const float2 h23 = __fmul2_rn(make_float2(gs[2], gs[3]), make_float2(sx.y, sx.y));
+            const float2 h45 = __fmul2_rn(make_float2(gs[4], gs[5]), make_float2(sx.z, sx.z));
+            const float2 h67 = __fmul2_rn(make_float2(gs[6], gs[7]), make_float2(sx.w, sx.w));
+            sts128f(out + ln.half * 32, h01.x, h01.y, h23.x, h23.y);
+            sts128f(out + ln.half * 32 + 16, h45.x, h45.y, h67.x, h67.y);
             float off = gs[0] * sa.x;
             off = fmaf(gs[1], sa.y, off); off = fmaf(gs[2], sa.z, off); off = fmaf(gs[3], sa.w, off);
             off = fmaf(gs[4], sb.x, off); off = fmaf(gs[5], sb.y, off); off = fmaf(gs[6], sb.z, off); off = fmaf(gs[7], sb.w, off);
