@@ -265,3 +265,52 @@ def test_gguf_file_loads_to_the_same_logits(model, tmp_path):
         logits.append(ex.copy_logits(0))
         ex.close()
     assert np.array_equal(logits[0].view(np.uint32), logits[1].view(np.uint32))
+
+
+def test_qwen3_0_6b_q8_0_greedy_agreement_over_256_tokens(built_library):
+    """The full Qwen3-0.6B Q8_0 configuration (28 layers, hidden 1024, 16 q / 8 kv heads, vocab 151936): a
+    128-token uniform-random prompt, then 256 greedy tokens.  The oracle is teacher-forced with the device's
+    token; the stated bar is logits within max-abs 2e-2 / rel 1e-2 and at least 99 % greedy agreement."""
+    import os
+    import ribn_b200
+    from ribn_b200 import BatchItem, StepKind
+    cfg = ribn_b200.QWEN3_0_6B
+    orc.set_threads(os.cpu_count() or 8)
+    ex = ribn_b200.QwenB200(cfg, context_tokens=512, max_sequences=1, max_batch_tokens=128,
+                            flags=ribn_b200.FLAG_KEEP_LOGITS)
+    ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q8_0)
+    tensors = {name: ex.read_tensor(name) for name in ex.tensor_names()}
+    ex.finalize()
+    oracle = orc.Qwen3Oracle(dict(cfg, context=512, eps=cfg["rms_eps"]), tensors)
+    seq = oracle.new_sequence()
+    rng = np.random.default_rng(2)
+    prompt = rng.integers(0, cfg["vocab"], size=128).tolist()
+    new_tokens = 256
+    assert ex.admit(1, 1, prompt, new_tokens).ready
+    item = BatchItem(1, StepKind.PREFILL, 0, len(prompt), 1)
+    ex.prepare([item])
+    done = ex.wait(ex.submit([item]))
+    for t in prompt[:-1]:
+        seq.step(t, want_logits=False)
+    want = seq.step(prompt[-1])
+    got = ex.copy_logits(0)
+    worst = float(np.max(np.abs(got - want)))
+    assert close(got, want), worst
+    token = done[0].tokens[0]
+    agree = int(token == orc.argmax(want))
+    for step in range(new_tokens - 1):
+        item = BatchItem(1, StepKind.DECODE, len(prompt) + step, 1, 1)
+        ex.prepare([item])
+        done = ex.wait(ex.submit([item]))
+        want = seq.step(token)
+        got = ex.copy_logits(0)
+        err = float(np.max(np.abs(got - want)))
+        worst = max(worst, err)
+        assert close(got, want), (step, err)
+        token = done[0].tokens[0]
+        assert token == orc.argmax(got)
+        agree += int(token == orc.argmax(want))
+    print(f"qwen3-0.6b q8_0: greedy agreement {agree}/{new_tokens}, max |logit diff| {worst:.3e}")
+    assert agree >= 0.99 * new_tokens
+    ex.release(1)
+    seq.close(); oracle.close(); ex.close()
