@@ -387,7 +387,8 @@ __global__ void __launch_bounds__(EARLY ? 256 : 512) attention_span_direct_kerne
         constexpr bool kEarlyValues = EARLY;
         if (kEarlyValues) load_values();
         if (live) {
-            float dot = 0.0f;
+            // packed FP32 pairs (sm_100): even and odd dimensions accumulate side by side
+            float2 dot2 = make_float2(0.0f, 0.0f);
 #pragma unroll
             for (int i = 0; i < HD / 8; ++i) {
                 const float4 qa = *reinterpret_cast<const float4*>(qs + i * 8);
@@ -396,12 +397,12 @@ __global__ void __launch_bounds__(EARLY ? 256 : 512) attention_span_direct_kerne
                 const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].y));
                 const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].z));
                 const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].w));
-                dot = fmaf(qa.x, k0.x, dot); dot = fmaf(qa.y, k0.y, dot);
-                dot = fmaf(qa.z, k1.x, dot); dot = fmaf(qa.w, k1.y, dot);
-                dot = fmaf(qb.x, k2.x, dot); dot = fmaf(qb.y, k2.y, dot);
-                dot = fmaf(qb.z, k3.x, dot); dot = fmaf(qb.w, k3.y, dot);
+                dot2 = __ffma2_rn(make_float2(qa.x, qa.y), k0, dot2);
+                dot2 = __ffma2_rn(make_float2(qa.z, qa.w), k1, dot2);
+                dot2 = __ffma2_rn(make_float2(qb.x, qb.y), k2, dot2);
+                dot2 = __ffma2_rn(make_float2(qb.z, qb.w), k3, dot2);
             }
-            s = dot * scale;
+            s = (dot2.x + dot2.y) * scale;
         }
         const float new_max = fmaxf(run_max, warp_max(s));
         const float factor = expf(run_max - new_max);  // 0 on the first tile (run_max = -inf)
@@ -423,10 +424,12 @@ __global__ void __launch_bounds__(EARLY ? 256 : 512) attention_span_direct_kerne
                 const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].z));
                 const float2 v3 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].w));
                 float* o = acc + c * 8;
-                o[0] = fmaf(pj[jj], v0.x, o[0]); o[1] = fmaf(pj[jj], v0.y, o[1]);
-                o[2] = fmaf(pj[jj], v1.x, o[2]); o[3] = fmaf(pj[jj], v1.y, o[3]);
-                o[4] = fmaf(pj[jj], v2.x, o[4]); o[5] = fmaf(pj[jj], v2.y, o[5]);
-                o[6] = fmaf(pj[jj], v3.x, o[6]); o[7] = fmaf(pj[jj], v3.y, o[7]);
+                const float2 pp = make_float2(pj[jj], pj[jj]);
+                const float2 o0 = __ffma2_rn(pp, v0, make_float2(o[0], o[1]));
+                const float2 o1 = __ffma2_rn(pp, v1, make_float2(o[2], o[3]));
+                const float2 o2 = __ffma2_rn(pp, v2, make_float2(o[4], o[5]));
+                const float2 o3 = __ffma2_rn(pp, v3, make_float2(o[6], o[7]));
+                o[0] = o0.x; o[1] = o0.y; o[2] = o1.x; o[3] = o1.y; o[4] = o2.x; o[5] = o2.y; o[6] = o3.x; o[7] = o3.y;
             }
         }
     }
