@@ -734,7 +734,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
         ln.sx = smem_u32(sh.sx);
         ln.sxs = smem_u32(sh.sxs);
         ln.hdr_wr = hdr + (lane >> 1) * kHdrRow;
-        ln.hdr_rd = hdr + (uint32_t)(t >> 1) * kHdrMember + g * kHdrRow;
+        // lanes whose columns belong to no member (t >= 2 with one member) read member 0's rows: the same
+        // addresses as their neighbours (a broadcast) instead of another block in the same banks
+        ln.hdr_rd = hdr + (uint32_t)min(t >> 1, MEMBERS - 1) * kHdrMember + g * kHdrRow;
         ln.members = MEMBERS;
         ln.K = K;
         ln.half = lane & 1;
