@@ -343,6 +343,13 @@ cudaError_t batch_project(ribn_b200_executor* ex, int& launches, const float* x,
     for (int i = 0; i < n_mats; ++i) probe[i] = GemvSegment{nullptr, mats[i]->type, 0, 0, nullptr};
     const bool kquant = tensor_memory && gemm_tc_kquant(probe, n_mats, 1);
     const int group = !tensor_memory ? kGemmMaxMembers : kquant ? 64 : kGemmTcMaxMembers;
+    // K-quant form: one conversion of every row of the step, laid out as one operand per group
+    const bool converted = kquant && tokens > group;
+    if (converted) {
+        cudaError_t e = launch_to_tc_operand_groups(s, x, index, norm_weight, tokens, group, k, ex->cfg.rms_eps, ex->op_tc);
+        if (e != cudaSuccess) return e;
+        launches += 2;
+    }
     for (int base = 0; base < tokens; base += group) {
         const int m = std::min(group, tokens - base);
         GemmArgs a{};
@@ -356,12 +363,17 @@ cudaError_t batch_project(ribn_b200_executor* ex, int& launches, const float* x,
         a.error_flag = ex->d_error;
         if (tensor_memory) {
             // tcgen05 dequant-GEMM; SwiGLU runs as a separate elementwise pass over gate and up
-            cudaError_t e = launch_to_tc_operand(s, index ? x : x + (size_t)base * k, index ? index + base : nullptr,
-                                                 norm_weight, m, k, ex->cfg.rms_eps, kquant, ex->op_tc);
-            if (e != cudaSuccess) return e;
-            launches += 2;
-            a.chunks = (const signed char*)ex->op_tc.chunks;
-            a.member_scale = ex->op_tc.member_scale;
+            if (!converted) {
+                cudaError_t e = launch_to_tc_operand(s, index ? x : x + (size_t)base * k, index ? index + base : nullptr,
+                                                     norm_weight, m, k, ex->cfg.rms_eps, kquant, ex->op_tc);
+                if (e != cudaSuccess) return e;
+                launches += 2;
+                a.chunks = (const signed char*)ex->op_tc.chunks;
+                a.member_scale = ex->op_tc.member_scale;
+            } else {
+                a.chunks = (const signed char*)ex->op_tc.chunks + (size_t)(base / group) * tc_operand_bytes(group, k);
+                a.member_scale = ex->op_tc.member_scale + base;
+            }
             a.kquant = kquant ? 1 : 0;
             a.partial = ex->tc_partial;
             a.partial_floats = ex->tc_partial_floats;
@@ -785,12 +797,16 @@ int ribn_b200_finalize(ribn_b200_executor* ex) {
             const int kmax = std::max(std::max(c.hidden, c.ffn), c.q_heads * c.head_dim);
             if (kmax % 256 == 0) {
                 CU_TRY(ex, dev_alloc(ex, &ex->op_batch.chunks, batch_operand_bytes(kGemmMaxMembers, kmax)));
-                CU_TRY(ex, dev_alloc(ex, (unsigned char**)&ex->op_tc.chunks, tc_operand_bytes(kGemmTcMaxMembers, kmax)));
-                CU_TRY(ex, dev_alloc(ex, &ex->op_tc.scale_in, kGemmTcMaxMembers));
+                // room for every 64-row group of the largest step (one conversion per projection), or one 128-row operand
+                const size_t tc_groups = ((size_t)c.max_batch_tokens + 63) / 64;
+                const size_t tc_rows = std::max<size_t>(tc_groups * 64, kGemmTcMaxMembers);
+                CU_TRY(ex, dev_alloc(ex, (unsigned char**)&ex->op_tc.chunks,
+                                     std::max(tc_operand_bytes(kGemmTcMaxMembers, kmax), tc_groups * tc_operand_bytes(64, kmax))));
+                CU_TRY(ex, dev_alloc(ex, &ex->op_tc.scale_in, tc_rows));
                 // room for four K slices of the widest fused projection at 64 rows
                 ex->tc_partial_floats = (size_t)4 * 64 * (size_t)std::max(std::max(2 * c.ffn, c.hidden), (c.q_heads + 2 * c.kv_heads) * c.head_dim);
                 CU_TRY(ex, dev_alloc(ex, &ex->tc_partial, ex->tc_partial_floats));
-                CU_TRY(ex, dev_alloc(ex, &ex->op_tc.member_scale, kGemmTcMaxMembers));
+                CU_TRY(ex, dev_alloc(ex, &ex->op_tc.member_scale, tc_rows));
                 CU_TRY(ex, dev_alloc(ex, &ex->op_batch.member_scale, kGemmMaxMembers));
                 CU_TRY(ex, dev_alloc(ex, &ex->op_batch.digit_inv, kGemmMaxMembers));
             }

@@ -941,8 +941,16 @@ __global__ void tc_chunks_kernel(const float* x, const int32_t* index, const flo
 
 // K-quant form of the activations: per k tile (256 inputs) four chunks as above, then the group sums
 // [2 blocks][column][8 halves]: block 0 = sums of the eight 32-input groups, block 1 zeros.
-__global__ void tcq_chunks_kernel(const float* x, const int32_t* index, const float* norm_weight, int members, int mp,
-                                  int k, const float* scale_in, __half* chunks) {
+// blockIdx.y selects a group of `group` consecutive members (the last one may be shorter); each group gets
+// its own operand, `group_halves` halves apart, laid out for its own padded member count.
+__global__ void tcq_chunks_kernel(const float* x, const int32_t* index, const float* norm_weight, int total_members,
+                                  int group, int k, const float* scale_in, __half* chunks, size_t group_halves) {
+    const int member0 = (int)blockIdx.y * group;
+    const int members = min(group, total_members - member0);
+    const int mp = (members + 15) / 16 * 16;
+    if (index != nullptr) index += member0; else x += (size_t)member0 * k;
+    scale_in += member0;
+    chunks += (size_t)blockIdx.y * group_halves;
     const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per (member, 8 inputs)
     const int kblocks = k / 8;
     const bool live = id < (long long)mp * kblocks;
@@ -1017,8 +1025,22 @@ cudaError_t launch_to_tc_operand(cudaStream_t stream, const float* x, const int3
     if (e != cudaSuccess) return e;
     const long long threads = (long long)mp * (k / 8);
     const unsigned int blocks = (unsigned int)((threads + 255) / 256);
-    if (kquant) tcq_chunks_kernel<<<blocks, 256, 0, stream>>>(x, index, norm_weight, members, mp, k, out.scale_in, out.chunks);
+    if (kquant) tcq_chunks_kernel<<<blocks, 256, 0, stream>>>(x, index, norm_weight, members, members, k, out.scale_in, out.chunks, 0);
     else tc_chunks_kernel<<<blocks, 256, 0, stream>>>(x, index, norm_weight, members, mp, k, out.scale_in, out.chunks);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_to_tc_operand_groups(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,
+                                        int members, int group, int k, float eps, TcOperand out) {
+    if (members <= 0 || group <= 0 || group > kKqMaxMembers || k % kTileCols != 0) return cudaErrorInvalidValue;
+    tc_scale_kernel<<<members, 512, 0, stream>>>(x, index, norm_weight, k, eps, out.scale_in, out.member_scale);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    const int groups = (members + group - 1) / group;
+    const long long threads = (long long)padded_members(std::min(group, members)) * (k / 8);
+    const dim3 grid((unsigned int)((threads + 255) / 256), (unsigned int)groups);
+    tcq_chunks_kernel<<<grid, 256, 0, stream>>>(x, index, norm_weight, members, group, k, out.scale_in, out.chunks,
+                                                tc_operand_bytes(group, k) / sizeof(__half));
     return cudaGetLastError();
 }
 

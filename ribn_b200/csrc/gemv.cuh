@@ -192,6 +192,11 @@ size_t tc_operand_bytes(int members, int k);
 bool gemm_tc_kquant(const GemvSegment* segments, int n_segments, int members);
 cudaError_t launch_to_tc_operand(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,
                                  int members, int k, float eps, bool kquant, TcOperand out);
+// The K-quant form for `members` input rows at once, as consecutive operands of `group` members each
+// (tc_operand_bytes(group, k) apart; scales indexed by member): one conversion for all the groups of a
+// prefill chunk.  `out` must hold ceil(members / group) operands and `members` scales.
+cudaError_t launch_to_tc_operand_groups(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,
+                                        int members, int group, int k, float eps, TcOperand out);
 // GemmArgs::chunks points at TcOperand::chunks, GemmArgs::kquant says which form; epilogue kStore or kResidual.
 cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmArgs& args);
 

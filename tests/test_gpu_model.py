@@ -314,3 +314,29 @@ def test_qwen3_0_6b_q8_0_greedy_agreement_over_256_tokens(built_library):
     assert agree >= 0.99 * new_tokens
     ex.release(1)
     seq.close(); oracle.close(); ex.close()
+
+
+def test_prefill_chunk_of_several_row_groups_matches_oracle(model):
+    """A 150-token chunk runs as three row groups (64 + 64 + 22) over one conversion of all its rows."""
+    from ribn_b200 import BatchItem, StepKind
+    tensors, oracle = model
+    ex = build(MID, tensors, context_tokens=256, max_sequences=1, max_batch_tokens=192)
+    rng = np.random.default_rng(4)
+    prompt = rng.integers(0, MID["vocab"], size=150).tolist()
+    assert ex.admit(1, 1, prompt, 4).ready
+    item = BatchItem(1, StepKind.PREFILL, 0, len(prompt), 1)
+    ex.prepare([item])
+    done = ex.wait(ex.submit([item]))
+    seq = oracle.new_sequence()
+    for t in prompt[:-1]:
+        seq.step(t, want_logits=False)
+    want = seq.step(prompt[-1])
+    got = ex.copy_logits(0)
+    assert close(got, want), float(np.max(np.abs(got - want)))
+    assert done[0].tokens[0] == orc.argmax(got)
+    # the cache rows of the last group's tokens are the oracle's
+    dev = ex.copy_kv(1, MID["layers"] - 1, 0, len(prompt)).view(np.float16).astype(np.float32)
+    ref = seq.cache(MID["layers"] - 1, 0, len(prompt)).view(np.float16).astype(np.float32)
+    assert np.max(np.abs(dev - ref)) < 2e-2
+    ex.release(1)
+    seq.close(); ex.close()
