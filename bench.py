@@ -50,15 +50,56 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: NVML in this process (reads only), or
+    an `nvidia-smi` loop when NVML cannot be opened."""
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.index, self.samples, self.proc = index, [], None
+        self.nvml, self.handle, self.stop = None, None, threading.Event()
+
+    def _nvml_open(self):
+        """NVML in this process (reads only): samples every few milliseconds from the first instant of the timed region."""
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            ids = [v.strip() for v in visible.split(",") if v.strip()]
+            physical = int(ids[self.index]) if ids and all(v.isdigit() for v in ids) and self.index < len(ids) else self.index
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(physical)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.nvml = pynvml
+            return True
+        except Exception:
+            self.nvml = None
+            return False
+
+    def _nvml_sample(self):
+        n = self.nvml
+        mhz = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+        try:
+            bits = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+        except Exception:
+            bits = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+        flag = lambda b: "Active" if bits & b else "Not Active"
+        # order of the fields after the two clocks: hw_slowdown, hw_thermal_slowdown, sw_thermal_slowdown, sw_power_cap
+        self.samples.append([str(mhz), str(self.max_mhz), flag(0x8), flag(0x40), flag(0x20), flag(0x4)])
+
+    def _nvml_loop(self):
+        while not self.stop.is_set():
+            try:
+                self._nvml_sample()
+            except Exception:
+                return
+            self.stop.wait(0.005)
 
     def __enter__(self):
+        if self._nvml_open():
+            self.thread = threading.Thread(target=self._nvml_loop, daemon=True)
+            self.thread.start()
+            return self
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
@@ -76,6 +117,15 @@ class ClockSampler:
                 self.samples.append(parts)
 
     def __exit__(self, *exc):
+        if self.nvml is not None:
+            self.stop.set()
+            self.thread.join(timeout=1)
+            if not self.samples:
+                try:
+                    self._nvml_sample()  # a region shorter than one polling interval: the clock right at its end
+                except Exception:
+                    pass
+            return
         if self.proc:
             self.proc.terminate()
             try:
