@@ -350,7 +350,11 @@ cudaError_t batch_project(ribn_b200_executor* ex, int& launches, const float* x,
         if (e != cudaSuccess) return e;
         launches += 2;
     }
+    // ... and its whole groups in one launch: a weight tile then meets every group while it is in L2
+    const int fused_groups = converted ? tokens / group : 0;
     for (int base = 0; base < tokens; base += group) {
+        const bool fused = fused_groups > 1 && base == 0;
+        if (fused_groups > 1 && base > 0 && base < fused_groups * group) continue;  // covered by the fused launch
         const int m = std::min(group, tokens - base);
         GemmArgs a{};
         a.n_segments = n_mats;
@@ -373,6 +377,10 @@ cudaError_t batch_project(ribn_b200_executor* ex, int& launches, const float* x,
             } else {
                 a.chunks = (const signed char*)ex->op_tc.chunks + (size_t)(base / group) * tc_operand_bytes(group, k);
                 a.member_scale = ex->op_tc.member_scale + base;
+                if (fused) {
+                    a.groups = fused_groups;
+                    a.group_chunk_bytes = tc_operand_bytes(group, k);
+                }
             }
             a.kquant = kquant ? 1 : 0;
             a.partial = ex->tc_partial;
@@ -382,7 +390,8 @@ cudaError_t batch_project(ribn_b200_executor* ex, int& launches, const float* x,
             if (epilogue == kSwiGLU) {
                 float* gate = ys[0] + (size_t)base * mats[0]->rows;
                 float* up = ys[1] + (size_t)base * mats[1]->rows;
-                STEP_TRY(launch_silu_mul(s, gate, up, (long long)m * mats[0]->rows, gate));
+                const long long rows_done = fused ? (long long)fused_groups * group : m;
+                STEP_TRY(launch_silu_mul(s, gate, up, rows_done * mats[0]->rows, gate));
             }
         } else {
             cudaError_t e = launch_to_batch_operand(s, index ? x : x + (size_t)base * k, index ? index + base : nullptr,

@@ -484,6 +484,8 @@ struct KqLayout {
     int w_stage_bytes, w_stages, b_bytes, b2_bytes;
     int cols, members_padded, a_stages, a_planes, chunk_k;
     int k_slices, total_n;                 // split-K: slices per unit, and the rows of all segments together
+    int groups;                            // row groups per launch (work items: unit, then group, then K slice)
+    size_t group_bytes;                    // bytes between the operands of consecutive groups
 };
 
 // 4 bytes (each < 64) -> the binary16 pairs (1024 + b0, 1024 + b1) and (1024 + b2, 1024 + b3)
@@ -590,7 +592,11 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
     // commit that completes a k tile (t_full) also frees that k tile's group-sum buffer.
     const uint32_t w_full = bars, w_empty = bars + 32, a_full = bars + 64, a_empty = bars + 96, t_full = bars + 128,
                    t_empty = bars + 144, b2_full = bars + 160, b_full = bars + 192;
-    const int S = lay.k_slices, tps = (k_tiles + S - 1) / S, items = units * S;
+    const int S = lay.k_slices, tps = (k_tiles + S - 1) / S, G = lay.groups, items = units * G * S;
+    // work item -> (unit, row group, K slice), the slice innermost: the groups of a unit run side by side on
+    // neighbouring CTAs, so the unit's weight tiles come from HBM once
+    auto unit_index = [&](int item) { return item / (G * S); };
+    auto group_index = [&](int item) { return (item / S) % G; };
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < lay.w_stages; ++i) { mbar_init(w_full + 8 * i, 1); mbar_init(w_empty + 8 * i, kKqDequantWarps); }
@@ -622,7 +628,7 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
         int witem = blockIdx.x, wkb = (witem % S) * tps;   // next weight stage to issue: (work item, k tile)
         auto issue_w = [&]() {
             if (witem >= items) return;
-            const UnitRef ur = unit_of(a, witem / S);
+            const UnitRef ur = unit_of(a, unit_index(witem));
             const GemvSegment& s = a.seg[ur.seg];
             const uint32_t tb = (uint32_t)packed_tile_bytes(s.type);
             const uint32_t stage = w_count % (uint32_t)lay.w_stages;
@@ -652,7 +658,8 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                     if (kt_count >= 2u && alive) alive = mbar_wait_relaxed(t_full + 8 * p, ((kt_count >> 1) - 1u) & 1u, a.error_flag, 23);
                     mbar_expect_tx(b2_full + 8 * p, (uint32_t)lay.b2_bytes);
                     bulk_g2s(smem_u32(b2_buf + (size_t)p * lay.b2_bytes),
-                             a.chunks + (size_t)kb * tile_stride + (size_t)kChunksPerTile * lay.b_bytes, (uint32_t)lay.b2_bytes, b2_full + 8 * p);
+                             a.chunks + (size_t)group_index(item) * lay.group_bytes + (size_t)kb * tile_stride + (size_t)kChunksPerTile * lay.b_bytes,
+                             (uint32_t)lay.b2_bytes, b2_full + 8 * p);
                 }
                 __syncwarp();
                 issue_w();
@@ -669,7 +676,7 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
             for (int item = blockIdx.x; item < items; item += gridDim.x) {
                 const int kb0 = (item % S) * tps, kb1 = min(k_tiles, kb0 + tps);
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    const signed char* src = a.chunks + (size_t)kb * tile_stride;
+                    const signed char* src = a.chunks + (size_t)group_index(item) * lay.group_bytes + (size_t)kb * tile_stride;
                     for (int c = 0; c < chunks_per_tile; ++c, ++b_count) {
                         if ((c & 1) != which) continue;
                         const uint32_t bs = b_count % na;
@@ -688,7 +695,7 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
             const uint32_t idesc = umma_idesc(lay.cols);
             const uint32_t b_lbo = (uint32_t)(lay.cols / 8) * 128u;
             for (int item = blockIdx.x; item < items; item += gridDim.x) {
-                const bool q4k = a.seg[unit_of(a, item / S).seg].type == kQ4_K;
+                const bool q4k = a.seg[unit_of(a, unit_index(item)).seg].type == kQ4_K;
                 const int kb0 = (item % S) * tps, kb1 = min(k_tiles, kb0 + tps);
                 for (int kb = kb0; kb < kb1; ++kb, ++kt_count) {
                     const uint32_t p = kt_count & 1u;
@@ -728,7 +735,7 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
         bool alive = true;
         uint32_t w_count = 0, a_count = 0;
         for (int item = blockIdx.x; item < items; item += gridDim.x) {
-            const UnitRef ur = unit_of(a, item / S);
+            const UnitRef ur = unit_of(a, unit_index(item));
             const GemvSegment& s = a.seg[ur.seg];
             const int type = s.type;
             const bool present = ur.rt0 + rt_local < s.row_tiles;
@@ -781,7 +788,7 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
         uint32_t kt_count = 0;
         const int row = warp * 32 + lane;
         for (int item = blockIdx.x; item < items; item += gridDim.x) {
-            const UnitRef ur = unit_of(a, item / S);
+            const UnitRef ur = unit_of(a, unit_index(item));
             const GemvSegment& s = a.seg[ur.seg];
             const bool q4k = s.type == kQ4_K;
             const int slice = item % S, kb0 = slice * tps, kb1 = min(k_tiles, kb0 + tps);
@@ -829,8 +836,9 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
 #pragma unroll
                     for (int m = 0; m < kKqMaxMembers; ++m) {
                         if (m < a.members) {
-                            const float v = acc[m] * a.member_scale[m];
-                            float* y = s.y + (size_t)m * s.n + n_index;
+                            const size_t member = (size_t)group_index(item) * a.members + m;
+                            const float v = acc[m] * a.member_scale[member];
+                            float* y = s.y + member * s.n + n_index;
                             if (a.epilogue == kResidual) *y += v; else *y = v;
                         }
                     }
@@ -1081,7 +1089,9 @@ cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units
     lay.total_n = 0;
     for (int i = 0; i < args.n_segments; ++i) lay.total_n += args.seg[i].n;
     lay.k_slices = 1;
-    if (args.partial != nullptr) {
+    lay.groups = std::max(1, args.groups);
+    lay.group_bytes = args.group_chunk_bytes;
+    if (args.partial != nullptr && lay.groups == 1) {
         long long best = -1;
         for (int slices = 1; slices <= std::min(8, k_tiles); ++slices) {
             const int tps = (k_tiles + slices - 1) / slices;
@@ -1092,7 +1102,7 @@ cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units
             if (best < 0 || cost < best) { best = cost; lay.k_slices = slices; }
         }
     }
-    gemm_tcq_kernel<<<std::min(units * lay.k_slices, sm_count), kKqThreads, smem, stream>>>(args, lay, units);
+    gemm_tcq_kernel<<<std::min(units * lay.k_slices * lay.groups, sm_count), kKqThreads, smem, stream>>>(args, lay, units);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || lay.k_slices == 1) return e;
     const long long outputs = (long long)args.members * lay.total_n;

@@ -165,6 +165,11 @@ struct GemmArgs {
     int kquant;           // tensor-memory kernels: the activations are in the K-quant form (see TcOperand)
     float* partial;       // optional scratch for split-K sums [slices][members][rows of all segments]
     size_t partial_floats;
+    // K-quant tensor-memory form only: `groups` > 1 runs that many consecutive groups of `members` rows in one
+    // launch (their operands `group_chunk_bytes` apart, scales and outputs consecutive), so every weight tile
+    // meets all the row groups of a prefill step while it is in L2.
+    int groups;
+    size_t group_chunk_bytes;
 };
 
 cudaError_t launch_gemm_imma(cudaStream_t stream, const GemmArgs& args);
