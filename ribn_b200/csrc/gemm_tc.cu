@@ -709,11 +709,25 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                         tc_fence_after();
                         const uint32_t a_addr = smem_u32(a_buf + (size_t)st * a_bytes);
                         const uint32_t b_addr = smem_u32(b_buf + (size_t)bs * b_stage_bytes);
-                        for (int s16 = 0; s16 < lay.chunk_k / 16; ++s16) {
-                            if (RIBN_TC_PROBE == 2 || RIBN_TC_PROBE == 5) break;
-                            const uint64_t db = umma_desc(b_addr + s16 * 2 * b_lbo, b_lbo, 128);
-                            umma_f16(d_main, umma_desc(a_addr + s16 * 2 * kALbo, kALbo, 128), db, idesc, (c | s16) != 0 ? 1u : 0u);
-                            if (!q4k) umma_f16(d_main, umma_desc(a_addr + kAHalfBytes + s16 * 2 * kALbo, kALbo, 128), db, idesc, 1u);
+                        // Descriptors of successive 16-input steps differ only in the start address field (bits 0..13,
+                        // in 16-byte units; no carry leaves it inside one stage): one 64-bit add per step.
+                        uint64_t da = umma_desc(a_addr, kALbo, 128), db = umma_desc(b_addr, b_lbo, 128);
+                        const uint64_t da_step = (uint64_t)((2 * kALbo) >> 4), db_step = (uint64_t)((2 * b_lbo) >> 4);
+                        const uint64_t da_plane = (uint64_t)(kAHalfBytes >> 4);
+                        const int steps = lay.chunk_k / 16;
+                        if (RIBN_TC_PROBE != 2 && RIBN_TC_PROBE != 5) {
+                            if (q4k) {
+#pragma unroll 4
+                                for (int s16 = 0; s16 < steps; ++s16, da += da_step, db += db_step) {
+                                    umma_f16(d_main, da, db, idesc, (c | s16) != 0 ? 1u : 0u);
+                                }
+                            } else {
+#pragma unroll 4
+                                for (int s16 = 0; s16 < steps; ++s16, da += da_step, db += db_step) {
+                                    umma_f16(d_main, da, db, idesc, (c | s16) != 0 ? 1u : 0u);
+                                    umma_f16(d_main, da + da_plane, db, idesc, 1u);
+                                }
+                            }
                         }
                         if (c == chunks_per_tile - 1) {
                             // Q4_K: group minima x group sums of the activations (the chunk's a_full covers A2 as well)
