@@ -18,12 +18,15 @@
 // contiguous byte range of weight tiles into a shared-memory ring with bulk
 // (TMA) copies completing on mbarriers; it starts before the programmatic
 // dependency on the previous kernel resolves, so weights are already in
-// flight while that kernel drains.  Sixteen consumer warps in two teams take
-// alternate ring stages; each warp owns one 16 x 256 tile of a stage.  Per
-// unit of 32 output rows the warps leave their partial sums in shared memory
-// and move on; a dedicated epilogue warp adds them in a fixed order
-// (deterministic results) and applies the epilogue: store, residual add,
-// SwiGLU, and the operand form of the result for the next projection.
+// flight while that kernel drains.  Twenty-four consumer warps in three teams
+// take the ring stages in turn (or, for launches with many units per CTA such
+// as the output head, each team owns whole units); each warp owns one
+// 16 x 256 tile of a stage.  Per unit of 32 output rows the warps leave their
+// partial sums in shared memory and move on; a dedicated epilogue warp adds
+// them in a fixed order (deterministic results) and applies the epilogue:
+// store, residual add, SwiGLU, and the operand form of the result for the
+// next projection.  Scale folds and header decodes use the packed FP32 pair
+// instructions of sm_100 (two IEEE operations per issue slot).
 // Every wait is bounded: on expiry the kernel raises an error flag and runs
 // to completion without waiting again.
 #include <cuda_fp16.h>
