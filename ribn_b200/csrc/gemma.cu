@@ -127,13 +127,19 @@ __global__ void gm_embed_kernel(const uint32_t* tokens, const bf16_t* embed, con
 // 128-bit reads of a quarter-warp fall in distinct banks; the input segment is a broadcast read).
 // ---------------------------------------------------------------------------------------------
 constexpr int kProjectCols = 32;                        // output columns (= threads) per block
-constexpr int kTileChunks = 32;                         // 16-byte chunks per row per tile (256 inputs)
-__host__ __device__ constexpr int project_stages(int rt) { return rt >= 8 ? 2 : 3; }  // an 8-row tile spends four times longer per stage
-constexpr int kRowPitch = kTileChunks * 16 + 16;        // bytes between weight rows of a tile
+// 16-byte chunks per row per tile: 256 inputs, or 128 for eight-row tiles (prefill), whose stages then fit eight
+// blocks per SM: those tiles are bound by instruction issue and want two warps per scheduler
+__host__ __device__ constexpr int project_tile_chunks(int rt) { return rt >= 8 ? 16 : 32; }
+__host__ __device__ constexpr int project_stages(int rt) { return rt >= 8 ? 2 : 3; }  // an 8-row tile spends longer per stage
+__host__ __device__ constexpr int project_row_pitch(int rt) { return project_tile_chunks(rt) * 16 + 16; }  // bytes between weight rows of a tile
 
-__host__ __device__ constexpr int project_stage_bytes(int rt) { return rt * kTileChunks * 16 + kProjectCols * kRowPitch; }
+__host__ __device__ constexpr int project_stage_bytes(int rt) {
+    return rt * project_tile_chunks(rt) * 16 + kProjectCols * project_row_pitch(rt);
+}
 // all stages, then the current tile's input rows expanded to FP32 (one conversion per value instead of one per column)
-__host__ __device__ constexpr int project_smem_bytes(int rt) { return project_stages(rt) * project_stage_bytes(rt) + rt * kTileChunks * 32; }
+__host__ __device__ constexpr int project_smem_bytes(int rt) {
+    return project_stages(rt) * project_stage_bytes(rt) + rt * project_tile_chunks(rt) * 32;
+}
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -156,7 +162,11 @@ __global__ void __launch_bounds__(kProjectCols) gm_project_kernel(const bf16_t* 
     extern __shared__ __align__(16) unsigned char project_smem[];
     constexpr int kStageBytes = project_stage_bytes(RT);
     constexpr int kProjectStages = project_stages(RT);
+    constexpr int kTileChunks = project_tile_chunks(RT);
+    constexpr int kRowPitch = project_row_pitch(RT);
+    constexpr int kRowsPerIssue = 32 / kTileChunks;  // rows one warp-wide copy instruction covers
     const int lane = threadIdx.x;
+    const int piece = lane % kTileChunks, sub_row = lane / kTileChunks;
     int which = 0;
     if (targets.count > 1 && (int)blockIdx.x >= targets.first_block[1]) which = 1;
     if (targets.count > 2 && (int)blockIdx.x >= targets.first_block[2]) which = 2;
@@ -179,14 +189,19 @@ __global__ void __launch_bounds__(kProjectCols) gm_project_kernel(const bf16_t* 
 
     auto issue = [&](int tile) {
         if (tile < tiles) {
-            const int c = tile * kTileChunks + lane;  // this lane's chunk of every row segment
+            const int c = tile * kTileChunks + piece;  // this lane's chunk of its row segments
             if (c < chunks) {
                 const uint32_t stage = smem + (uint32_t)((tile % kProjectStages) * kStageBytes);
 #pragma unroll
-                for (int r = 0; r < RT; ++r) cp_async16(stage + (uint32_t)(r * kTileChunks * 16 + lane * 16), x[r] + c);
-                uint32_t wdst = stage + (uint32_t)(RT * kTileChunks * 16 + lane * 16);
-                const uint4* src = wbase + c;
-                for (int j = 0; j < live_cols; ++j, wdst += kRowPitch, src += row_chunks) cp_async16(wdst, src);
+                for (int r = 0; r < RT; ++r) {  // static indices keep the row pointers in registers
+                    if (r % kRowsPerIssue == sub_row) cp_async16(stage + (uint32_t)(r * kTileChunks * 16 + piece * 16), x[r] + c);
+                }
+                uint32_t wdst = stage + (uint32_t)(RT * kTileChunks * 16 + sub_row * kRowPitch + piece * 16);
+                const uint4* src = wbase + (size_t)sub_row * row_chunks + c;
+                for (int j = sub_row; j < live_cols; j += kRowsPerIssue, wdst += kRowsPerIssue * kRowPitch,
+                         src += (size_t)kRowsPerIssue * row_chunks) {
+                    cp_async16(wdst, src);
+                }
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
