@@ -384,6 +384,26 @@ template <int HD, bool FUSED, bool EARLY>
 __global__ void __launch_bounds__(EARLY ? 256 : 512) attention_span_direct_kernel(const AttnArgs a) {
     constexpr int DPL = HD / 32;  // dims per lane in the lane-strided layout
     constexpr int CH = HD / 8;    // dims per lane in the P.V phase (8 chunks x 4 key groups)
+    // Before the programmatic dependency resolves: the span's K / V rows of earlier positions were written by
+    // earlier steps, and the step's positions and page tables by kernels that completed before the projection
+    // ahead of this one began, so warp 0 asks L2 for those rows while that projection drains.
+    if (threadIdx.x < 32) {
+        const int pt = a.token_base + blockIdx.x / a.kv_heads, pkvh = blockIdx.x % a.kv_heads;
+        const int ppos = a.token_pos[pt];
+        const int pfirst = a.window > 0 ? max(0, ppos - a.window + 1) : 0;
+        const int pbegin = pfirst + (int)blockIdx.y * kAttnSpanKeys, pend = min(ppos + 1, pbegin + kAttnSpanKeys);
+        const int32_t* ptable = a.page_tables + (long long)(a.token_seq != nullptr ? a.token_seq[pt] : 0) * a.pages_per_sequence;
+        for (int key = pbegin + (int)threadIdx.x; key < pend; key += 32) {
+            if (FUSED && key == ppos) continue;  // the token's own row does not exist yet
+            const long long phys = (long long)ptable[key / kPageTokens] * kPageTokens + key % kPageTokens;
+            const long long at = phys * (long long)a.kv_heads * HD + (long long)pkvh * HD;
+#pragma unroll
+            for (int line = 0; line < HD * 2 / 128; ++line) {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(a.cache_k + at + line * 64));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(a.cache_v + at + line * 64));
+            }
+        }
+    }
     // Programmatic dependent launch: wait for the projections that produced q/k/v, then let the next
     // kernel (which first only prefetches weights) start.
     asm volatile("griddepcontrol.wait;" ::: "memory");
