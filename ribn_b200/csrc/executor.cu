@@ -348,7 +348,7 @@ cudaError_t batch_project(ribn_b200_executor* ex, int& launches, const float* x,
     if (converted) {
         cudaError_t e = launch_to_tc_operand_groups(s, x, index, norm_weight, tokens, group, k, ex->cfg.rms_eps, ex->op_tc);
         if (e != cudaSuccess) return e;
-        launches += 2;
+        launches += 1;
     }
     // ... and its whole groups in one launch: a weight tile then meets every group while it is in L2
     const int fused_groups = converted ? tokens / group : 0;
@@ -371,7 +371,7 @@ cudaError_t batch_project(ribn_b200_executor* ex, int& launches, const float* x,
                 cudaError_t e = launch_to_tc_operand(s, index ? x : x + (size_t)base * k, index ? index + base : nullptr,
                                                      norm_weight, m, k, ex->cfg.rms_eps, kquant, ex->op_tc);
                 if (e != cudaSuccess) return e;
-                launches += 2;
+                launches += kquant ? 1 : 2;
                 a.chunks = (const signed char*)ex->op_tc.chunks;
                 a.member_scale = ex->op_tc.member_scale;
             } else {

@@ -962,61 +962,103 @@ __global__ void tc_chunks_kernel(const float* x, const int32_t* index, const flo
 }
 
 // K-quant form of the activations: per k tile (256 inputs) four chunks as above, then the group sums
-// [2 blocks][column][8 halves]: block 0 = sums of the eight 32-input groups, block 1 zeros.
-// blockIdx.y selects a group of `group` consecutive members (the last one may be shorter); each group gets
-// its own operand, `group_halves` halves apart, laid out for its own padded member count.
-__global__ void tcq_chunks_kernel(const float* x, const int32_t* index, const float* norm_weight, int total_members,
-                                  int group, int k, const float* scale_in, __half* chunks, size_t group_halves) {
+// [2 blocks][column][8 halves]: block 0 = sums of the eight 32-input groups, block 1 zeros.  blockIdx.y selects a
+// group of `group` consecutive members (the last one may be shorter); each group gets its own operand,
+// `group_halves` halves apart, laid out for its own padded member count.
+// Both passes for the K-quant form in one launch: block (x = member within its group, y = group) first finds the
+// member's scale as tc_scale_kernel does (same arithmetic and order), then writes the member's column of every
+// chunk.  Columns past the group's member count (padding up to a multiple of 16) are zero.
+__global__ void __launch_bounds__(512) tcq_operand_kernel(const float* x, const int32_t* index, const float* norm_weight,
+                                                          int total_members, int group, int k, float eps, float* scale_in,
+                                                          float* member_scale, __half* chunks, size_t group_halves) {
+    __shared__ float red_max[32], red_sum[32];
+    __shared__ float scale_slot;
     const int member0 = (int)blockIdx.y * group;
     const int members = min(group, total_members - member0);
     const int mp = (members + 15) / 16 * 16;
-    if (index != nullptr) index += member0; else x += (size_t)member0 * k;
-    scale_in += member0;
-    chunks += (size_t)blockIdx.y * group_halves;
-    const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per (member, 8 inputs)
-    const int kblocks = k / 8;
-    const bool live = id < (long long)mp * kblocks;
-    const int m = live ? (int)(id / kblocks) : 0, kblk = live ? (int)(id % kblocks) : 0;
-    const int cols = 2 * mp;
-    const size_t tile_halves = (size_t)kChunksPerTile * cols * kChunkK + (size_t)cols * 16;
-    __half hi[8], lo[8];
-    float sum = 0.0f;
-    if (live && m < members) {
-        const float* row = x + (size_t)(index ? index[m] : m) * k + (size_t)kblk * 8;
-        const float s = scale_in[m];
+    const int m = blockIdx.x;
+    if (m >= mp) return;
+    const bool real = m < members;
+    const float* row = real ? x + (size_t)(index ? index[member0 + m] : member0 + m) * k : nullptr;
+    if (real) {
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const float4* nw = reinterpret_cast<const float4*>(norm_weight);
+        float amax = 0.0f, ss = 0.0f;
+        for (int i0 = threadIdx.x; i0 < k / 4; i0 += 4 * blockDim.x) {
+            float4 v[4], w[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            float v = row[i];
-            if (norm_weight != nullptr) v *= norm_weight[kblk * 8 + i];
-            v *= s;
-            hi[i] = __float2half_rn(v);
-            lo[i] = __float2half_rn(v - __half2float(hi[i]));
-            sum += __half2float(hi[i]) + __half2float(lo[i]);   // the sum of what the tensor core will see
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * blockDim.x;
+                v[u] = i < k / 4 ? row4[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                w[u] = (nw != nullptr && i < k / 4) ? nw[i] : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                ss = fmaf(v[u].x, v[u].x, ss); ss = fmaf(v[u].y, v[u].y, ss); ss = fmaf(v[u].z, v[u].z, ss); ss = fmaf(v[u].w, v[u].w, ss);
+                amax = fmaxf(fmaxf(amax, fabsf(v[u].x * w[u].x)), fmaxf(fabsf(v[u].y * w[u].y), fmaxf(fabsf(v[u].z * w[u].z), fabsf(v[u].w * w[u].w))));
+            }
         }
-    } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) hi[i] = lo[i] = __float2half_rn(0.0f);
+        for (int o = 16; o > 0; o >>= 1) {
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        }
+        if ((threadIdx.x & 31) == 0) { red_max[threadIdx.x >> 5] = amax; red_sum[threadIdx.x >> 5] = ss; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float top = 0.0f, total = 0.0f;
+            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { top = fmaxf(top, red_max[w]); total += red_sum[w]; }
+            const float inv_norm = norm_weight ? 1.0f / sqrtf(total / (float)k + eps) : 1.0f;
+            int e = 0;
+            if (top > 0.0f && isfinite(top)) frexpf(top, &e);
+            const float sc = ldexpf(1.0f, 1 - e);
+            scale_in[member0 + m] = sc;
+            member_scale[member0 + m] = inv_norm * ldexpf(1.0f, e - 1);
+            scale_slot = sc;
+        }
+        __syncthreads();
     }
-    // four consecutive threads hold one 32-input group
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    if (!live) return;
-    const int tile = kblk / 32, in_tile = kblk % 32, chunk = in_tile / 8, kb8 = in_tile % 8;
-    __half* base = chunks + (size_t)tile * tile_halves;
-    __half* cbase = base + (size_t)chunk * (cols * kChunkK) + (size_t)kb8 * (cols * 8);
-    *reinterpret_cast<uint4*>(cbase + (size_t)m * 8) = *reinterpret_cast<const uint4*>(hi);
-    *reinterpret_cast<uint4*>(cbase + (size_t)(mp + m) * 8) = *reinterpret_cast<const uint4*>(lo);
-    __half* sums = base + (size_t)kChunksPerTile * cols * kChunkK;
-    if ((in_tile & 3) == 0) {
-        const int group = in_tile / 4;
-        const __half sh = __float2half_rn(sum);
-        sums[(size_t)m * 8 + group] = sh;
-        sums[(size_t)(mp + m) * 8 + group] = __float2half_rn(sum - __half2float(sh));
-    }
-    if (in_tile == 0) {
-        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-        *reinterpret_cast<uint4*>(sums + (size_t)cols * 8 + (size_t)m * 8) = zero;
-        *reinterpret_cast<uint4*>(sums + (size_t)cols * 8 + (size_t)(mp + m) * 8) = zero;
+    const float sc = real ? scale_slot : 0.0f;
+    const int cols = 2 * mp, kblocks = k / 8;
+    const size_t tile_halves = (size_t)kChunksPerTile * cols * kChunkK + (size_t)cols * 16;
+    __half* out = chunks + (size_t)blockIdx.y * group_halves;
+    for (int kblk = threadIdx.x; kblk < kblocks; kblk += blockDim.x) {   // kblocks is a multiple of 32: whole warps
+        __half hi[8], lo[8];
+        float sum = 0.0f;
+        if (real) {
+            const float* src = row + (size_t)kblk * 8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float v = src[i];
+                if (norm_weight != nullptr) v *= norm_weight[kblk * 8 + i];
+                v *= sc;
+                hi[i] = __float2half_rn(v);
+                lo[i] = __float2half_rn(v - __half2float(hi[i]));
+                sum += __half2float(hi[i]) + __half2float(lo[i]);   // the sum of what the tensor core will see
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) hi[i] = lo[i] = __float2half_rn(0.0f);
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);   // four consecutive threads hold one 32-input group
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        const int tile = kblk / 32, in_tile = kblk % 32, chunk = in_tile / 8, kb8 = in_tile % 8;
+        __half* base = out + (size_t)tile * tile_halves;
+        __half* cbase = base + (size_t)chunk * (cols * kChunkK) + (size_t)kb8 * (cols * 8);
+        *reinterpret_cast<uint4*>(cbase + (size_t)m * 8) = *reinterpret_cast<const uint4*>(hi);
+        *reinterpret_cast<uint4*>(cbase + (size_t)(mp + m) * 8) = *reinterpret_cast<const uint4*>(lo);
+        __half* sums = base + (size_t)kChunksPerTile * cols * kChunkK;
+        if ((in_tile & 3) == 0) {
+            const int g = in_tile / 4;
+            const __half sh = __float2half_rn(sum);
+            sums[(size_t)m * 8 + g] = sh;
+            sums[(size_t)(mp + m) * 8 + g] = __float2half_rn(sum - __half2float(sh));
+        }
+        if (in_tile == 0) {
+            const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(sums + (size_t)cols * 8 + (size_t)m * 8) = zero;
+            *reinterpret_cast<uint4*>(sums + (size_t)cols * 8 + (size_t)(mp + m) * 8) = zero;
+        }
     }
 }
 
@@ -1042,27 +1084,27 @@ cudaError_t launch_to_tc_operand(cudaStream_t stream, const float* x, const int3
                                  int members, int k, float eps, bool kquant, TcOperand out) {
     if (members <= 0 || members > (kquant ? kKqMaxMembers : kGemmTcMaxMembers) || k % kTileCols != 0) return cudaErrorInvalidValue;
     const int mp = padded_members(members);
+    if (kquant) {
+        tcq_operand_kernel<<<dim3((unsigned int)mp, 1), 512, 0, stream>>>(x, index, norm_weight, members, members, k, eps, out.scale_in,
+                                                                          out.member_scale, out.chunks, 0);
+        return cudaGetLastError();
+    }
     tc_scale_kernel<<<members, 512, 0, stream>>>(x, index, norm_weight, k, eps, out.scale_in, out.member_scale);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     const long long threads = (long long)mp * (k / 8);
     const unsigned int blocks = (unsigned int)((threads + 255) / 256);
-    if (kquant) tcq_chunks_kernel<<<blocks, 256, 0, stream>>>(x, index, norm_weight, members, members, k, out.scale_in, out.chunks, 0);
-    else tc_chunks_kernel<<<blocks, 256, 0, stream>>>(x, index, norm_weight, members, mp, k, out.scale_in, out.chunks);
+    tc_chunks_kernel<<<blocks, 256, 0, stream>>>(x, index, norm_weight, members, mp, k, out.scale_in, out.chunks);
     return cudaGetLastError();
 }
 
 cudaError_t launch_to_tc_operand_groups(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,
                                         int members, int group, int k, float eps, TcOperand out) {
     if (members <= 0 || group <= 0 || group > kKqMaxMembers || k % kTileCols != 0) return cudaErrorInvalidValue;
-    tc_scale_kernel<<<members, 512, 0, stream>>>(x, index, norm_weight, k, eps, out.scale_in, out.member_scale);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
     const int groups = (members + group - 1) / group;
-    const long long threads = (long long)padded_members(std::min(group, members)) * (k / 8);
-    const dim3 grid((unsigned int)((threads + 255) / 256), (unsigned int)groups);
-    tcq_chunks_kernel<<<grid, 256, 0, stream>>>(x, index, norm_weight, members, group, k, out.scale_in, out.chunks,
-                                                tc_operand_bytes(group, k) / sizeof(__half));
+    const dim3 grid((unsigned int)padded_members(std::min(group, members)), (unsigned int)groups);
+    tcq_operand_kernel<<<grid, 512, 0, stream>>>(x, index, norm_weight, members, group, k, eps, out.scale_in, out.member_scale,
+                                                 out.chunks, tc_operand_bytes(group, k) / sizeof(__half));
     return cudaGetLastError();
 }
 
