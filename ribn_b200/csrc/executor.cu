@@ -387,6 +387,7 @@ cudaError_t batch_project(ribn_b200_executor* ex, int& launches, const float* x,
             a.partial_floats = ex->tc_partial_floats;
             a.epilogue = epilogue == kSwiGLU ? kStore : epilogue;
             STEP_TRY(launch_gemm_tc(s, a));
+            launches += gemm_tc_last_launches() - 1;
             if (epilogue == kSwiGLU) {
                 float* gate = ys[0] + (size_t)base * mats[0]->rows;
                 float* up = ys[1] + (size_t)base * mats[1]->rows;

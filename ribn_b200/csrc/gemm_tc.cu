@@ -1110,6 +1110,8 @@ cudaError_t launch_to_tc_operand_groups(cudaStream_t stream, const float* x, con
 
 namespace {
 
+thread_local int g_last_launches = 1;
+
 cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units, int tile) {
     KqLayout lay{};
     lay.members_padded = padded_members(args.members);
@@ -1160,7 +1162,9 @@ cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units
     }
     gemm_tcq_kernel<<<std::min(units * lay.k_slices * lay.groups, sm_count), kKqThreads, smem, stream>>>(args, lay, units);
     cudaError_t e = cudaGetLastError();
+    g_last_launches = 1;
     if (e != cudaSuccess || lay.k_slices == 1) return e;
+    g_last_launches = 2;
     const long long outputs = (long long)args.members * lay.total_n;
     tcq_reduce_kernel<<<(unsigned int)((outputs + 255) / 256), 256, 0, stream>>>(args, lay.k_slices, lay.total_n);
     return cudaGetLastError();
@@ -1168,7 +1172,10 @@ cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units
 
 }  // namespace
 
+int gemm_tc_last_launches() { return g_last_launches; }
+
 cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmArgs& args) {
+    g_last_launches = 1;
     if (args.members < 1 || args.members > kGemmTcMaxMembers || args.k % kTileCols != 0) return cudaErrorInvalidValue;
     if (args.epilogue != kStore && args.epilogue != kResidual) return cudaErrorInvalidValue;
     int units = 0, tile = 0;

@@ -204,6 +204,8 @@ cudaError_t launch_to_tc_operand_groups(cudaStream_t stream, const float* x, con
                                         int members, int group, int k, float eps, TcOperand out);
 // GemmArgs::chunks points at TcOperand::chunks, GemmArgs::kquant says which form; epilogue kStore or kResidual.
 cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmArgs& args);
+// Kernels the calling thread's last launch_gemm_tc enqueued (2 when a split-K launch adds its ordered reduction).
+int gemm_tc_last_launches();
 
 // Scratch shared by the step kernels: per-span attention accumulators.
 struct StepScratch {
