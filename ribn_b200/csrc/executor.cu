@@ -1002,8 +1002,19 @@ int ribn_b200_submit(ribn_b200_executor* ex, const ribn_b200_batch_item* items, 
         return e;
     };
     int launches = 0;
-    const bool graphable = !(ex->cfg.flags & RIBN_B200_FLAG_NO_GRAPH) && decode_family_applies(ex, plan) &&
-                           plan.n_rows == plan.n_tokens && plan.n_prompt_tokens == 0;
+    // Decode-only steps replay captured graphs: always for one or two rows; for larger batches (several hundred
+    // launches per step, whose launch gaps a graph closes) once the same shape has come up three times, and while
+    // the executor holds fewer than kMaxStepGraphs graphs.
+    constexpr size_t kMaxStepGraphs = 192;
+    bool graphable = !(ex->cfg.flags & RIBN_B200_FLAG_NO_GRAPH) && packed_family_applies(ex) &&
+                     plan.n_rows == plan.n_tokens && plan.n_prompt_tokens == 0;
+    if (graphable && !decode_family_applies(ex, plan)) {
+        const int bucket = (plan.max_keys + 511) / 512;
+        const uint64_t key = (uint64_t)plan.n_tokens | ((uint64_t)plan.n_sample << 16) | ((uint64_t)bucket << 32);
+        if (ex->graphs.find(key) == ex->graphs.end()) {
+            graphable = ++ex->graph_seen[key] >= 3 && ex->graphs.size() < kMaxStepGraphs;
+        }
+    }
     CU_TRY(ex, cudaEventRecord(ex->ev_start, ex->stream));
     if (graphable) {
         // Decode-only steps replay a captured graph.  The attention grid is sized by a bucket of the

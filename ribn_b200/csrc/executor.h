@@ -105,6 +105,7 @@ struct ribn_b200_executor {
     // Captured decode steps, keyed by (tokens, sampling rows, attention span bucket).
     struct StepGraph { cudaGraphExec_t exec = nullptr; int launches = 0; };
     std::map<uint64_t, StepGraph> graphs;
+    std::map<uint64_t, int> graph_seen;  // how often a batched decode shape has come up (hot shapes get a graph)
     int* d_error = nullptr;    // raised by a kernel whose bounded wait expired
     int* h_error = nullptr;    // pinned copy read at poll
     std::vector<void*> allocations;

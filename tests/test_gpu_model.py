@@ -340,3 +340,33 @@ def test_prefill_chunk_of_several_row_groups_matches_oracle(model):
     assert np.max(np.abs(dev - ref)) < 2e-2
     ex.release(1)
     seq.close(); ex.close()
+
+
+def test_batched_decode_graph_replay_changes_no_bit(model):
+    """Batched decode steps of a recurring shape replay a captured graph from their third occurrence on; the
+    logits must equal those of an executor that never captures (RIBN_B200_FLAG_NO_GRAPH), bit for bit."""
+    import ribn_b200
+    from ribn_b200 import BatchItem, StepKind
+    tensors, _ = model
+    rng = np.random.default_rng(5)
+    prompts = {s: rng.integers(0, MID["vocab"], size=n).tolist() for s, n in ((1, 9), (2, 17), (3, 5), (4, 30))}
+    runs = []
+    for flags in (0, ribn_b200.FLAG_NO_GRAPH):
+        ex = build(MID, tensors, flags=flags, context_tokens=128, max_sequences=4, max_batch_tokens=64)
+        for s, p in prompts.items():
+            assert ex.admit(s, s, p, 12).ready
+        items = [BatchItem(s, StepKind.PREFILL, 0, len(p), 1) for s, p in prompts.items()]
+        ex.prepare(items)
+        ex.wait(ex.submit(items))
+        steps = []
+        for step in range(8):
+            items = [BatchItem(s, StepKind.DECODE, len(p) + step, 1, 1) for s, p in prompts.items()]
+            ex.prepare(items)
+            done = ex.wait(ex.submit(items))
+            steps.append(([d.tokens[0] for d in done], [ex.copy_logits(r).copy() for r in range(4)]))
+        runs.append(steps)
+        ex.close()
+    for (tok_a, log_a), (tok_b, log_b) in zip(*runs):
+        assert tok_a == tok_b
+        for a, b in zip(log_a, log_b):
+            assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
