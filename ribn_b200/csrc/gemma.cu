@@ -676,6 +676,10 @@ struct ribn_b200_gemma {
     std::string error;
     float last_ms = 0.0f;
     uint32_t last_launches = 0;
+    // passes of a recurring shape (rows, outputs, context bucket) replay a captured graph
+    struct PassGraph { cudaGraphExec_t exec = nullptr; uint32_t launches = 0; };
+    std::map<uint64_t, PassGraph> graphs;
+    std::map<uint64_t, int> graph_seen;
 };
 
 namespace {
@@ -853,6 +857,7 @@ RIBN_B200_API int ribn_b200_gemma_create(const ribn_b200_gemma_config* config, r
 RIBN_B200_API int ribn_b200_gemma_destroy(ribn_b200_gemma* m) {
     if (!m) return RIBN_B200_OK;
     if (m->stream) cudaStreamSynchronize(m->stream);
+    for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.exec);
     for (auto& t : m->g) cudaFree(t.data);
     for (auto& layer : m->l) for (auto& t : layer) cudaFree(t.data);
     for (bf16_t* p : m->key_cache) cudaFree(p);
@@ -1022,7 +1027,7 @@ struct Pass {
 
 // One pass over `rows` flattened tokens already staged in the model's pinned arrays; n_out of them (their
 // indices in h_out_rows) produce logits and a greedy token.
-int run_pass(ribn_b200_gemma* m, int rows, int n_out, int max_position, uint32_t* launches) {
+int enqueue_pass(ribn_b200_gemma* m, int rows, int n_out, int max_position, uint32_t* launches) {
     const ribn_b200_gemma_config& c = m->cfg;
     cudaStream_t s = m->stream;
     GM_CUDA(m, cudaMemcpyAsync(m->d_tokens, m->h_tokens, sizeof(uint32_t) * (size_t)rows, cudaMemcpyHostToDevice, s));
@@ -1095,6 +1100,35 @@ int run_pass(ribn_b200_gemma* m, int rows, int n_out, int max_position, uint32_t
     }
     GM_CUDA(m, cudaGetLastError());
     *launches += p.launches;
+    return RIBN_B200_OK;
+}
+
+// A pass reads its rows (tokens, slots, positions, output rows) from the pinned staging arrays, so passes of one
+// shape differ only in data: from the third time a shape (rows, outputs, context bucket of 128) comes up it is
+// captured into a CUDA graph, which closes the gaps between its ~100 short launches.
+int run_pass(ribn_b200_gemma* m, int rows, int n_out, int max_position, uint32_t* launches) {
+    constexpr size_t kMaxPassGraphs = 128;
+    const int bucket_end = std::min(((max_position + 1 + 127) / 128) * 128, m->cfg.context);
+    const uint64_t key = (uint64_t)rows | ((uint64_t)n_out << 20) | ((uint64_t)bucket_end << 40);
+    auto found = m->graphs.find(key);
+    if (found == m->graphs.end()) {
+        if (++m->graph_seen[key] < 3 || m->graphs.size() >= kMaxPassGraphs) return enqueue_pass(m, rows, n_out, max_position, launches);
+        cudaGraph_t graph = nullptr;
+        uint32_t captured = 0;
+        GM_CUDA(m, cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+        const int rc = enqueue_pass(m, rows, n_out, bucket_end - 1, &captured);
+        const cudaError_t end = cudaStreamEndCapture(m->stream, &graph);
+        if (rc != RIBN_B200_OK) { if (graph) cudaGraphDestroy(graph); return rc; }
+        GM_CUDA(m, end);
+        ribn_b200_gemma::PassGraph entry;
+        entry.launches = captured;
+        const cudaError_t inst = cudaGraphInstantiate(&entry.exec, graph, 0);
+        cudaGraphDestroy(graph);
+        GM_CUDA(m, inst);
+        found = m->graphs.emplace(key, entry).first;
+    }
+    GM_CUDA(m, cudaGraphLaunch(found->second.exec, m->stream));
+    *launches += found->second.launches;
     return RIBN_B200_OK;
 }
 
