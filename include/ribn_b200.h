@@ -44,6 +44,7 @@ enum {
     RIBN_B200_PENDING = 1,
     RIBN_B200_REJECTED = 2,
     RIBN_B200_DEFERRED = 3,
+    RIBN_B200_SELECTED = 4,  /* prepare_rows: BatchPreparation::Selected, one decision per offered row */
     RIBN_B200_ERROR = -1
 };
 
@@ -85,7 +86,9 @@ enum {
     RIBN_B200_FLAG_REFERENCE_KERNELS = 2, /* run the plain one-warp-per-row CUDA kernels
                                              (slow; used to cross-check the fast path) */
     RIBN_B200_FLAG_NO_GRAPH = 4,      /* launch kernels directly instead of replaying graphs */
-    RIBN_B200_FLAG_NO_TCGEN05 = 8     /* batches of 3+ rows on the integer mma.sync kernel instead of tcgen05 */
+    RIBN_B200_FLAG_NO_TCGEN05 = 8,    /* batches of 3+ rows on the integer mma.sync kernel instead of tcgen05 */
+    RIBN_B200_FLAG_KV_ON_DEMAND = 16  /* admit reserves the prompt's KV pages only; prepare takes the pages a row's
+                                         range needs and defers the rows the arena cannot serve */
 };
 
 /* GenerationLimits (crates/runtime/src/executor.rs:43-51). */
@@ -107,6 +110,28 @@ typedef struct {
     uint32_t token_budget;
     uint32_t output_budget;
 } ribn_b200_batch_item;
+
+/* TokenRequest.options.sampling: Sampling{temperature, top_p, top_k, seed}
+ * (crates/runtime/src/executor.rs, crates/qwen/src/execution.rs:107-111).  Only greedy selection
+ * (temperature 0) is executed; anything else is Admission::Rejected, as in the reference. */
+typedef struct {
+    float temperature;
+    float top_p;
+    uint32_t top_k;
+    uint32_t reserved;
+    uint64_t seed;
+} ribn_b200_sampling;
+
+/* PreparedRow (crates/runtime/src/executor.rs:97-105): the decision for one offered row.  READY rows keep
+ * identity, kind and prefix; their budgets may have shrunk, never to zero.  DEFERRED rows retain nothing
+ * new and should be offered again after a release.  REJECTED is reserved for request-local refusals. */
+enum { RIBN_B200_ROW_READY = 0, RIBN_B200_ROW_DEFERRED = 1, RIBN_B200_ROW_REJECTED = 2 };
+typedef struct {
+    uint32_t state;
+    uint32_t token_budget;
+    uint32_t output_budget;
+    uint32_t reserved;
+} ribn_b200_prepared_row;
 
 /* StepCompletion (crates/runtime/src/executor.rs:101-106); max_decode_tokens
  * is 1, so a row carries at most one sampled token. */
@@ -155,17 +180,28 @@ RIBN_B200_API int ribn_b200_finalize(ribn_b200_executor* executor);
 
 /* info() */
 RIBN_B200_API int ribn_b200_info(ribn_b200_executor* executor, ribn_b200_limits* out);
-/* admit(): OK = Admission::Ready (pages for prompt + max_output reserved),
- * REJECTED, DEFERRED, or ERROR (duplicate sequence / faulted executor).
+/* admit(): OK = Admission::Ready (pages for prompt + max_output reserved; with
+ * RIBN_B200_FLAG_KV_ON_DEMAND the prompt's pages only), REJECTED, DEFERRED, or ERROR (duplicate
+ * sequence / faulted executor).  `sampling` may be NULL (greedy).
  * Semantics follow QwenExecution::admit (crates/qwen/src/execution.rs:80-162). */
 RIBN_B200_API int ribn_b200_admit(ribn_b200_executor* executor, uint64_t request_id, uint64_t sequence,
                                   const uint32_t* tokens, uint32_t token_count,
-                                  uint32_t max_output_tokens, float temperature,
+                                  uint32_t max_output_tokens, const ribn_b200_sampling* sampling,
                                   const uint32_t* stop_tokens, uint32_t stop_count);
 /* prepare(): OK = BatchPreparation::Ready.  Never advances state
- * (crates/qwen/src/execution.rs:164-269). */
+ * (crates/qwen/src/execution.rs:164-269).  A batch the KV arena cannot serve whole is an error
+ * here; prepare_rows reports it per row. */
 RIBN_B200_API int ribn_b200_prepare(ribn_b200_executor* executor, const ribn_b200_batch_item* items,
                                     uint32_t count);
+/* prepare() with the per-row report of BatchPreparation (crates/runtime/src/executor.rs:97-105, 195-204):
+ * OK = Ready (every row accepted unchanged), RIBN_B200_SELECTED = Selected (`rows[i]` holds the decision
+ * for `items[i]`: a row whose range needs KV pages the arena cannot give is DEFERRED and retains nothing
+ * new; READY rows carry their granted budgets, which this executor never shrinks).  Pages granted to
+ * READY rows stay with their sequences.  submit() then takes exactly the READY rows, in offered order,
+ * with their granted budgets; when none is READY call abandon_preparation().  `rows` may be NULL, which
+ * makes this ribn_b200_prepare. */
+RIBN_B200_API int ribn_b200_prepare_rows(ribn_b200_executor* executor, const ribn_b200_batch_item* items,
+                                         uint32_t count, ribn_b200_prepared_row* rows);
 /* abandon_preparation(): idempotent. */
 RIBN_B200_API int ribn_b200_abandon_preparation(ribn_b200_executor* executor);
 /* submit(): asynchronous; must repeat the prepared rows
@@ -176,7 +212,10 @@ RIBN_B200_API int ribn_b200_submit(ribn_b200_executor* executor, const ribn_b200
  * submitted row, in order (crates/qwen/src/execution.rs:329-414). */
 RIBN_B200_API int ribn_b200_poll(ribn_b200_executor* executor, uint64_t submission,
                                  ribn_b200_completion* rows, uint32_t capacity, uint32_t* count);
-/* release(): idempotent (crates/qwen/src/execution.rs:416-440). */
+/* release(): idempotent (crates/qwen/src/execution.rs:416-440).  A sequence named by the outstanding
+ * preparation is refused ("cannot release prepared Qwen state").  A sequence the pending submission
+ * still reads is parked and retired when that submission completes at poll()
+ * (deferred_releases, crates/nvidia/src/serving.rs:1082-1096, 1231-1251); the call returns OK. */
 RIBN_B200_API int ribn_b200_release(ribn_b200_executor* executor, uint64_t sequence);
 /* synchronize(): block until every queued launch has finished. */
 RIBN_B200_API int ribn_b200_synchronize(ribn_b200_executor* executor);
@@ -221,6 +260,23 @@ RIBN_B200_API int ribn_b200_step_bytes(ribn_b200_executor* executor, uint64_t co
 RIBN_B200_API int ribn_b200_time_projection(ribn_b200_executor* executor, int32_t which, uint32_t repeats,
                                             float* average_us, uint64_t* bytes_per_launch);
 
+/* ---- failure detection aids (no GPU fault is involved in any of them) ------ */
+
+/* Host-side fault injection, the counterpart of the switches of the reference's contract tests
+ * (crates/runtime/tests/contract.rs:12-31).  ALLOC_REFUSAL: the next `value` device allocations of this
+ * executor fail as if the device were out of memory.  ERROR_WORD: the next submitted step ends with
+ * `value` in the word that a kernel's expired bounded wait writes.  BAD_ROW: the next `value` submits
+ * corrupt one row record before the host-side check of the step plan.  Each surfaces as RIBN_B200_ERROR
+ * with a message in last_error and leaves the executor faulted. */
+enum { RIBN_B200_INJECT_ALLOC_REFUSAL = 1, RIBN_B200_INJECT_ERROR_WORD = 2, RIBN_B200_INJECT_BAD_ROW = 3 };
+RIBN_B200_API int ribn_b200_debug_inject(ribn_b200_executor* executor, int32_t kind, int32_t value);
+/* Launches one small kernel whose only thread waits, through the kernels' bounded wait, on a barrier that
+ * nothing completes; after `spin_limit` polls (1 .. 2^20) the wait gives up, writes code 99 to the
+ * executor's error word and the kernel returns.  The call waits for the kernel and returns OK: the
+ * context stays usable.  The next poll() of a submission reports the expired wait and faults the
+ * executor.  No reference counterpart (its kernels do not wait on one another). */
+RIBN_B200_API int ribn_b200_debug_wait_expiry(ribn_b200_executor* executor, uint32_t spin_limit);
+
 /* ---- single operators (host pointers in, host pointers out) ------------- */
 /* Each runs the same device kernels the executor uses, on `device`, and is
  * what the per-primitive parity tests call.  They replace the operator
@@ -234,6 +290,15 @@ RIBN_B200_API size_t ribn_b200_op_last_error(char* buffer, size_t capacity);
 /* dequantize_block over `rows x cols` (crates/gguf/src/lib.rs:508-535), bit-exact. */
 RIBN_B200_API int ribn_b200_op_dequantize(int32_t device, int32_t ggml_type, const void* bytes,
                                           int64_t rows, int64_t cols, float* out);
+/* The same decode, but FROM the tile-major packed form that the tensor-core kernels stream (`packed` =
+ * output of ribn_b200_debug_repack), through the weight decoder of the decode-and-split tcgen05 kernel.
+ * Must equal dequantize_block bit for bit: the repack is judged only by the values it decodes to. */
+RIBN_B200_API int ribn_b200_debug_unpack(int32_t device, int32_t ggml_type, const void* packed,
+                                         int64_t rows, int64_t cols, float* out);
+/* q4_k_embedding(_batch) and its Q8_0 / Q6_K forms (crates/nvidia/src/kernels/quantized/q4_k.cu:1-60):
+ * out[i][:] = dequantised row tokens[i] of the raw-layout `[vocab][hidden]` table, bit-exact. */
+RIBN_B200_API int ribn_b200_op_embedding(int32_t device, int32_t ggml_type, const void* table, int32_t vocab,
+                                         int32_t hidden, const uint32_t* tokens, int32_t count, float* out);
 /* y[m][n] = sum_k deq(W[n][k]) x[m][k] (CudaQuantizedGemv::execute_warp /
  * gemv_batch, crates/nvidia/src/quantized.rs:303-436).  variant 0 = fast
  * GEMV kernels (members in pairs), 1 = one-warp-per-row reference kernels,
@@ -272,6 +337,30 @@ RIBN_B200_API int ribn_b200_op_attention(int32_t device, const float* q, const u
                                          int32_t tokens, int32_t rows, int32_t q_heads,
                                          int32_t kv_heads, int32_t head_dim, int32_t window,
                                          float* out, int32_t variant);
+/* strided_rms_norm + rope_neox + kv_append_f16 for every token of a step (model_ops.rs:662, 395-425,
+ * 1258-1277): per-head RMSNorm of q `[tokens][q_heads][head_dim]` and k `[tokens][kv_heads][head_dim]`
+ * with the shared `[head_dim]` weights, full-width NeoX rotary at positions[t] (both in place), then the
+ * F16 (round-to-nearest-even) append of k and v at row kv_slots[t] of the `[physical_tokens][kv_heads][head_dim]`
+ * caches. */
+RIBN_B200_API int ribn_b200_op_qk_norm_rope_append(int32_t device, float* q, float* k, const float* v,
+                                                   const float* q_norm, const float* k_norm,
+                                                   const int32_t* positions, const int32_t* kv_slots,
+                                                   int32_t tokens, int32_t q_heads, int32_t kv_heads,
+                                                   int32_t head_dim, float rope_base, float eps,
+                                                   uint16_t* cache_k, uint16_t* cache_v, int32_t physical_tokens);
+/* The decode step's fused form of the above plus attention (one new token per sequence): raw q / k / v
+ * projections of `members` sequences, token m at positions[m] of sequence m, whose page-table row is
+ * page_tables[m][..].  Normalises and rotates q and k, appends k and v to the caches (updated in place on
+ * return) and attends keys [0, positions[m]].  out is `[members][q_heads * head_dim]`.
+ * Replaces the member-by-member sequence of BatchStates::attend
+ * (crates/nvidia/src/decode/member_state.rs:194-324). */
+RIBN_B200_API int ribn_b200_op_attention_decode(int32_t device, const float* q, const float* k, const float* v,
+                                                const float* q_norm, const float* k_norm, float rope_base,
+                                                float eps, uint16_t* cache_k, uint16_t* cache_v,
+                                                int32_t physical_tokens, const int32_t* page_tables,
+                                                int32_t pages_per_sequence, const int32_t* positions,
+                                                int32_t members, int32_t q_heads, int32_t kv_heads,
+                                                int32_t head_dim, float* out);
 /* Ragged batch metadata built on the device from per-row (prefix, tokens)
  * records: cu_seqlens[rows + 1], and per token its row, position and physical
  * KV slot.  Supersedes the host-built DescriptorPacket
@@ -290,7 +379,9 @@ RIBN_B200_API int ribn_b200_op_batch_metadata(int32_t device, const int32_t* row
  * per-span scratch is an 8 MiB array built into the library, so the call performs no cudaMalloc,
  * cudaFree or allocating library routine.  `token_pos[r]` is the position of query row r (it
  * attends keys [0, token_pos[r]], or the last `window` of them); `max_tokens` is 1 + the largest
- * position.  Refused with a message when rows * q_heads * ceil(keys / 64) * (head_dim + 2)
+ * position.  That is a hard precondition the host cannot check (the positions live on the device):
+ * a position >= max_tokens makes the merge read span slots no block wrote.  The launch is made with
+ * `device` current; the caller's current device is restored before the call returns.  Refused with a message when rows * q_heads * ceil(keys / 64) * (head_dim + 2)
  * exceeds 2 Mi floats.  Calls share the scratch: do not let two of them overlap on the GPU.
  * The first call on a device resolves the scratch address; make it before any stream capture. */
 RIBN_B200_API int ribn_b200_attention_noalloc(int32_t device, void* stream, const float* q,

@@ -8,10 +8,12 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 F32, F16, Q8_0, Q4_K, Q6_K = 0, 1, 8, 12, 14
-OK, PENDING, REJECTED, DEFERRED, ERROR = 0, 1, 2, 3, -1
+OK, PENDING, REJECTED, DEFERRED, SELECTED, ERROR = 0, 1, 2, 3, 4, -1
+ROW_READY, ROW_DEFERRED, ROW_REJECTED = 0, 1, 2
+INJECT_ALLOC_REFUSAL, INJECT_ERROR_WORD, INJECT_BAD_ROW = 1, 2, 3
 PREFILL, DECODE = 0, 1
 SCHEME_Q8_0, SCHEME_Q4_K_M = 0, 1
-FLAG_KEEP_LOGITS, FLAG_REFERENCE_KERNELS, FLAG_NO_GRAPH, FLAG_NO_TCGEN05 = 1, 2, 4, 8
+FLAG_KEEP_LOGITS, FLAG_REFERENCE_KERNELS, FLAG_NO_GRAPH, FLAG_NO_TCGEN05, FLAG_KV_ON_DEMAND = 1, 2, 4, 8, 16
 
 
 class Config(C.Structure):
@@ -35,6 +37,16 @@ class BatchItemC(C.Structure):
                 ("token_budget", C.c_uint32), ("output_budget", C.c_uint32)]
 
 
+class SamplingC(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("top_k", C.c_uint32), ("reserved", C.c_uint32),
+                ("seed", C.c_uint64)]
+
+
+class PreparedRowC(C.Structure):
+    _fields_ = [("state", C.c_uint32), ("token_budget", C.c_uint32), ("output_budget", C.c_uint32),
+                ("reserved", C.c_uint32)]
+
+
 class CompletionC(C.Structure):
     _fields_ = [("sequence", C.c_uint64), ("prefix", C.c_uint32), ("n_tokens", C.c_uint32),
                 ("token", C.c_uint32), ("reserved", C.c_uint32)]
@@ -51,9 +63,18 @@ SIGNATURES = {
                                         C.POINTER(C.c_int64), _P, C.c_size_t, C.POINTER(C.c_size_t)]),
     "ribn_b200_finalize": (C.c_int, [_P]),
     "ribn_b200_info": (C.c_int, [_P, C.POINTER(Limits)]),
-    "ribn_b200_admit": (C.c_int, [_P, C.c_uint64, C.c_uint64, _P, C.c_uint32, C.c_uint32, C.c_float, _P,
+    "ribn_b200_admit": (C.c_int, [_P, C.c_uint64, C.c_uint64, _P, C.c_uint32, C.c_uint32, C.POINTER(SamplingC), _P,
                                   C.c_uint32]),
     "ribn_b200_prepare": (C.c_int, [_P, C.POINTER(BatchItemC), C.c_uint32]),
+    "ribn_b200_prepare_rows": (C.c_int, [_P, C.POINTER(BatchItemC), C.c_uint32, C.POINTER(PreparedRowC)]),
+    "ribn_b200_debug_inject": (C.c_int, [_P, C.c_int32, C.c_int32]),
+    "ribn_b200_debug_wait_expiry": (C.c_int, [_P, C.c_uint32]),
+    "ribn_b200_debug_unpack": (C.c_int, [C.c_int32, C.c_int32, _P, C.c_int64, C.c_int64, _P]),
+    "ribn_b200_op_embedding": (C.c_int, [C.c_int32, C.c_int32, _P, C.c_int32, C.c_int32, _P, C.c_int32, _P]),
+    "ribn_b200_op_qk_norm_rope_append": (C.c_int, [C.c_int32, _P, _P, _P, _P, _P, _P, _P, C.c_int32, C.c_int32,
+                                                   C.c_int32, C.c_int32, C.c_float, C.c_float, _P, _P, C.c_int32]),
+    "ribn_b200_op_attention_decode": (C.c_int, [C.c_int32, _P, _P, _P, _P, _P, C.c_float, C.c_float, _P, _P, C.c_int32,
+                                                _P, C.c_int32, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P]),
     "ribn_b200_abandon_preparation": (C.c_int, [_P]),
     "ribn_b200_submit": (C.c_int, [_P, C.POINTER(BatchItemC), C.c_uint32, C.POINTER(C.c_uint64)]),
     "ribn_b200_poll": (C.c_int, [_P, C.c_uint64, C.POINTER(CompletionC), C.c_uint32, C.POINTER(C.c_uint32)]),

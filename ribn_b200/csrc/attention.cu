@@ -678,7 +678,10 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
                                : (size_t)q_per_kv * HD * sizeof(float) + 2 * HD * sizeof(__half);
     if (smem > 48 * 1024) {
         // above the default limit (head_dim 256): opt in once per instantiation
-        static bool configured = false;
+        static bool configured_on[kMaxDevices] = {false};  // function attributes are per device
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+        bool& configured = configured_on[dev];
         if (!configured) {
             cudaError_t e = cudaFuncSetAttribute(attention_span_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
             if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_span_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);

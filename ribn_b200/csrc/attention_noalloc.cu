@@ -55,7 +55,20 @@ extern "C" int ribn_b200_attention_noalloc(int32_t device, void* stream, const f
         return refuse(error, error_capacity, "unsupported attention geometry (head_dim must be 64, 128 or 256)");
     }
     if (device < 0 || device >= kMaxDevices) return refuse(error, error_capacity, "device ordinal out of range");
-    if (cudaSetDevice(device) != cudaSuccess) return refuse(error, error_capacity, "cannot select the CUDA device");
+    // The launch needs `device` current; the caller's own current device is put back before returning.
+    struct DeviceScope {
+        int previous = -1;
+        bool ok = false;
+        explicit DeviceScope(int device) {
+            if (cudaGetDevice(&previous) != cudaSuccess) previous = -1;
+            ok = previous == device || cudaSetDevice(device) == cudaSuccess;
+        }
+        ~DeviceScope() {
+            int now = -1;
+            if (previous >= 0 && cudaGetDevice(&now) == cudaSuccess && now != previous) cudaSetDevice(previous);
+        }
+    } scope(device);
+    if (!scope.ok) return refuse(error, error_capacity, "cannot select the CUDA device");
     const int keys_per_row = window > 0 && window < max_tokens ? window : max_tokens;
     const size_t spans = ((size_t)keys_per_row + ribn::kAttnSpanKeys - 1) / ribn::kAttnSpanKeys;
     const size_t need = (size_t)rows * q_heads * spans * (size_t)(head_dim + 2);

@@ -59,6 +59,10 @@ int soft(ribn_b200_executor* ex, int code, const char* fmt, ...) {
 template <typename T>
 cudaError_t dev_alloc(ribn_b200_executor* ex, T** out, size_t count) {
     void* p = nullptr;
+    if (ex->inject_alloc_failures > 0) {  // host-side fault injection: the allocator refuses
+        --ex->inject_alloc_failures;
+        return cudaErrorMemoryAllocation;
+    }
     cudaError_t e = cudaMalloc(&p, std::max<size_t>(count, 1) * sizeof(T));
     if (e == cudaSuccess) {
         ex->allocations.push_back(p);
@@ -546,6 +550,9 @@ int ribn_b200_create(const ribn_b200_config* config, ribn_b200_executor** out, c
         return report("prepared model limits must be nonzero");
     }
     if (c.max_sequences > 1024) return report("max_sequences above 1024 is not supported");
+    if (c.context_tokens > kAttnMaxSpans * kAttnSpanKeys) {
+        return report("context_tokens above 65536 is not supported (1024 attention spans of 64 keys)");
+    }
     int count = 0;
     cudaError_t e = cudaGetDeviceCount(&count);
     if (e != cudaSuccess || count == 0) {
@@ -843,9 +850,47 @@ int ribn_b200_info(ribn_b200_executor* ex, ribn_b200_limits* out) {
     return RIBN_B200_OK;
 }
 
+}  // extern "C"
+
+namespace {
+
+// Take `count` more pages from the arena for a sequence and publish its page-table row.
+int grow_pages(ribn_b200_executor* ex, Sequence& seq, int count) {
+    const int first = (int)seq.pages.size();
+    for (int i = 0; i < count; ++i) {
+        seq.pages.push_back(ex->free_pages.back());
+        ex->free_pages.pop_back();
+    }
+    if (count == 0) return RIBN_B200_OK;
+    cudaSetDevice(ex->cfg.device);
+    cudaError_t e = cudaMemcpyAsync(ex->d_page_tables + (size_t)seq.slot * ex->pages_per_sequence + first,
+                                    seq.pages.data() + first, (size_t)count * sizeof(int32_t), cudaMemcpyHostToDevice,
+                                    ex->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ex->stream);  // pageable source: keep it simple and safe
+    if (e != cudaSuccess) {
+        for (int i = 0; i < count; ++i) { ex->free_pages.push_back(seq.pages.back()); seq.pages.pop_back(); }
+        ex->faulted = true;
+        return fail(ex, "page table upload failed: %s", cudaGetErrorString(e));
+    }
+    return RIBN_B200_OK;
+}
+
+// Returns a sequence's pages and slot to the executor.
+void retire_sequence(ribn_b200_executor* ex, uint64_t sequence) {
+    auto found = ex->sequences.find(sequence);
+    if (found == ex->sequences.end()) return;
+    for (int32_t page : found->second.pages) ex->free_pages.push_back(page);
+    ex->free_slots.push_back(found->second.slot);
+    ex->sequences.erase(found);
+}
+
+}  // namespace
+
+extern "C" {
+
 int ribn_b200_admit(ribn_b200_executor* ex, uint64_t request_id, uint64_t sequence, const uint32_t* tokens,
-                    uint32_t token_count, uint32_t max_output_tokens, float temperature, const uint32_t* stop_tokens,
-                    uint32_t stop_count) {
+                    uint32_t token_count, uint32_t max_output_tokens, const ribn_b200_sampling* sampling,
+                    const uint32_t* stop_tokens, uint32_t stop_count) {
     (void)request_id;
     if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
     if (!ex->finalized) return fail(ex, "executor is not finalized");
@@ -857,17 +902,22 @@ int ribn_b200_admit(ribn_b200_executor* ex, uint64_t request_id, uint64_t sequen
     for (uint32_t i = 0; !bad && i < token_count; ++i) bad = tokens[i] >= (uint32_t)c.vocab;
     for (uint32_t i = 0; !bad && i < stop_count; ++i) bad = stop_tokens[i] >= (uint32_t)c.vocab;
     if (bad) return soft(ex, RIBN_B200_REJECTED, "Qwen input/output limits or token IDs are invalid");
-    if (temperature != 0.0f) {
+    // Sampling::is_greedy (crates/qwen/src/execution.rs:107-111): temperature 0 selects the first maximum;
+    // top_p / top_k / seed are carried for non-greedy selection, which this executor rejects as the reference does.
+    if (sampling != nullptr && sampling->temperature != 0.0f) {
         return soft(ex, RIBN_B200_REJECTED, "the executor currently supports greedy sampling only");
     }
     if ((int)ex->sequences.size() >= c.max_sequences || ex->free_slots.empty()) {
         return soft(ex, RIBN_B200_DEFERRED, "all sequence slots are in use");
     }
-    // Reserve the request-reachable envelope atomically (execution.rs:125-149).
-    const int need = pages_for((uint32_t)total);
-    if (need > ex->kv_pages) {
-        return soft(ex, RIBN_B200_REJECTED, "request needs %d KV pages, above the %d-page arena", need, ex->kv_pages);
+    const int envelope = pages_for((uint32_t)total);
+    if (envelope > ex->kv_pages) {
+        return soft(ex, RIBN_B200_REJECTED, "request needs %d KV pages, above the %d-page arena", envelope, ex->kv_pages);
     }
+    // Reserve the request-reachable envelope atomically (execution.rs:125-149), or, with
+    // RIBN_B200_FLAG_KV_ON_DEMAND, only the prompt's pages: decode pages are then taken at prepare.
+    const bool on_demand = (c.flags & RIBN_B200_FLAG_KV_ON_DEMAND) != 0;
+    const int need = on_demand ? pages_for(token_count) : envelope;
     if (need > (int)ex->free_pages.size()) return soft(ex, RIBN_B200_DEFERRED, "KV arena has no free pages");
     Sequence seq;
     seq.id = sequence;
@@ -875,39 +925,27 @@ int ribn_b200_admit(ribn_b200_executor* ex, uint64_t request_id, uint64_t sequen
     seq.prompt.assign(tokens, tokens + token_count);
     seq.prompt_len = token_count;
     seq.max_output = max_output_tokens;
-    seq.pages.resize(need);
-    for (int i = 0; i < need; ++i) {
-        seq.pages[i] = ex->free_pages.back();
-        ex->free_pages.pop_back();
-    }
-    cudaSetDevice(c.device);
-    cudaError_t e = cudaMemcpyAsync(ex->d_page_tables + (size_t)seq.slot * ex->pages_per_sequence, seq.pages.data(),
-                                    (size_t)need * sizeof(int32_t), cudaMemcpyHostToDevice, ex->stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(ex->stream);  // pageable source: keep it simple and safe
-    if (e != cudaSuccess) {
-        for (int p : seq.pages) ex->free_pages.push_back(p);
-        ex->faulted = true;
-        return fail(ex, "page table upload failed: %s", cudaGetErrorString(e));
-    }
+    if (grow_pages(ex, seq, need) != RIBN_B200_OK) return RIBN_B200_ERROR;
     ex->free_slots.pop_back();
     ex->sequences.emplace(sequence, std::move(seq));
     return RIBN_B200_OK;
 }
 
-int ribn_b200_prepare(ribn_b200_executor* ex, const ribn_b200_batch_item* items, uint32_t count) {
+int ribn_b200_prepare_rows(ribn_b200_executor* ex, const ribn_b200_batch_item* items, uint32_t count,
+                           ribn_b200_prepared_row* rows) {
     if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
     if (!ex->finalized) return fail(ex, "executor is not finalized");
     if (ex->pending.active || ex->prepared) return fail(ex, "Qwen execution is faulted or busy");
     const ribn_b200_config& c = ex->cfg;
     uint64_t tokens = 0;
     for (uint32_t i = 0; i < count; ++i) tokens += items[i].token_budget;
-    if (count == 0 || count > (uint32_t)c.max_sequences || tokens > (uint64_t)c.max_batch_tokens) {
+    if (count == 0 || items == nullptr || count > (uint32_t)c.max_sequences || tokens > (uint64_t)c.max_batch_tokens) {
         return fail(ex, "Qwen batch exceeds prepared limits");
     }
     for (uint32_t i = 0; i < count; ++i) {
         const ribn_b200_batch_item& it = items[i];
         auto found = ex->sequences.find(it.sequence);
-        if (found == ex->sequences.end()) return fail(ex, "unknown Qwen sequence");
+        if (found == ex->sequences.end() || found->second.released) return fail(ex, "unknown Qwen sequence");
         const Sequence& s = found->second;
         if (s.in_flight) return fail(ex, "Qwen sequence is in flight");
         for (uint32_t j = 0; j < i; ++j) {
@@ -933,9 +971,38 @@ int ribn_b200_prepare(ribn_b200_executor* ex, const ribn_b200_batch_item* items,
             return fail(ex, "unknown step kind");
         }
     }
-    ex->prepared_items.assign(items, items + count);
+    // Every offered row is valid.  A row whose range reaches past the pages its sequence holds takes pages from
+    // the arena now (the executor keeps them; nothing else of the sequence changes); a row the arena cannot
+    // serve is Deferred and retains nothing new (PreparedRow, crates/runtime/src/executor.rs:97-105).  Prompt
+    // pages are held since admission, so only decode rows of an on-demand executor can be deferred.
+    ex->prepared_items.clear();
+    bool unchanged = true;
+    for (uint32_t i = 0; i < count; ++i) {
+        const ribn_b200_batch_item& it = items[i];
+        Sequence& s = ex->sequences.find(it.sequence)->second;
+        ribn_b200_prepared_row row{RIBN_B200_ROW_READY, it.token_budget, it.output_budget, 0};
+        const int need = pages_for(it.prefix + it.token_budget) - (int)s.pages.size();
+        if (need > (int)ex->free_pages.size()) {
+            row.state = RIBN_B200_ROW_DEFERRED;
+            row.token_budget = row.output_budget = 0;
+            unchanged = false;
+        } else {
+            if (need > 0 && grow_pages(ex, s, need) != RIBN_B200_OK) return RIBN_B200_ERROR;
+            ex->prepared_items.push_back(it);
+        }
+        if (rows != nullptr) rows[i] = row;
+    }
+    if (!unchanged && rows == nullptr) {
+        ex->prepared_items.clear();
+        return fail(ex, "KV arena cannot serve every offered row; prepare_rows reports the decision per row");
+    }
     ex->prepared = true;
-    return RIBN_B200_OK;
+    if (!unchanged) ex->error = "KV arena has no free pages for some rows";
+    return unchanged ? RIBN_B200_OK : RIBN_B200_SELECTED;
+}
+
+int ribn_b200_prepare(ribn_b200_executor* ex, const ribn_b200_batch_item* items, uint32_t count) {
+    return ribn_b200_prepare_rows(ex, items, count, nullptr);
 }
 
 int ribn_b200_abandon_preparation(ribn_b200_executor* ex) {
@@ -948,9 +1015,18 @@ int ribn_b200_abandon_preparation(ribn_b200_executor* ex) {
 int ribn_b200_submit(ribn_b200_executor* ex, const ribn_b200_batch_item* items, uint32_t count, uint64_t* submission) {
     if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
     if (!ex->prepared) return fail(ex, "submit without a preparation");
+    if (count == 0 || items == nullptr || submission == nullptr) return fail(ex, "submit needs at least one prepared row");
     if (count != ex->prepared_items.size() ||
         memcmp(items, ex->prepared_items.data(), count * sizeof(ribn_b200_batch_item)) != 0) {
         return fail(ex, "submitted rows differ from the prepared rows");
+    }
+    // The prepared rows name live sequences (release refuses a prepared sequence); look them up defensively all the same.
+    for (uint32_t i = 0; i < count; ++i) {
+        if (ex->sequences.find(items[i].sequence) == ex->sequences.end()) {
+            ex->prepared = false;
+            ex->prepared_items.clear();
+            return fail(ex, "unknown Qwen sequence in the prepared rows");
+        }
     }
     cudaSetDevice(ex->cfg.device);
     Pending& p = ex->pending;
@@ -979,6 +1055,27 @@ int ribn_b200_submit(ribn_b200_executor* ex, const ribn_b200_batch_item* items, 
         plan.max_keys = std::max(plan.max_keys, (int)(it.prefix + it.token_budget));
     }
     p.n_sample = plan.n_sample;
+    if (ex->inject_bad_row > 0) {  // host-side fault injection: a corrupted row record
+        --ex->inject_bad_row;
+        ex->h_rows[0].slot = ex->cfg.max_sequences + 7;
+    }
+    // What is about to be uploaded must describe the plan: slots in range, ranges inside the context, token counts
+    // adding up.  A record that does not is never sent to the device.
+    {
+        long long total = 0;
+        bool sane = true;
+        for (uint32_t i = 0; i < count; ++i) {
+            const RowDesc& r = ex->h_rows[i];
+            sane = sane && r.slot >= 0 && r.slot < ex->cfg.max_sequences && r.prefix >= 0 && r.tokens > 0 &&
+                   (long long)r.prefix + r.tokens <= ex->cfg.context_tokens &&
+                   (r.token_offset < 0 || r.token_offset + r.tokens <= ex->cfg.max_batch_tokens);
+            total += r.tokens;
+        }
+        if (!sane || total != plan.n_tokens) {
+            ex->faulted = true;
+            return fail(ex, "malformed row record in the step plan");
+        }
+    }
     // Mark ownership before the first launch: if anything below fails the
     // executor faults and keeps everything until synchronize.
     for (uint32_t i = 0; i < count; ++i) ex->sequences.find(items[i].sequence)->second.in_flight = true;
@@ -1001,6 +1098,11 @@ int ribn_b200_submit(ribn_b200_executor* ex, const ribn_b200_batch_item* items, 
         if (e == cudaSuccess) e = cudaMemcpyAsync(ex->h_error, ex->d_error, sizeof(int), cudaMemcpyDeviceToHost, ex->stream);
         return e;
     };
+    if (ex->inject_error_word != 0) {  // host-side fault injection: the error word a kernel's expired wait would leave
+        CU_TRY(ex, cudaMemcpyAsync(ex->d_error, &ex->inject_error_word, sizeof(int), cudaMemcpyHostToDevice, ex->stream));
+        CU_TRY(ex, cudaStreamSynchronize(ex->stream));
+        ex->inject_error_word = 0;
+    }
     int launches = 0;
     // Decode-only steps replay captured graphs: always for one or two rows; for larger batches (several hundred
     // launches per step, whose launch gaps a graph closes) once the same shape has come up three times, and while
@@ -1095,17 +1197,30 @@ int ribn_b200_poll(ribn_b200_executor* ex, uint64_t submission, ribn_b200_comple
     }
     *count = (uint32_t)p.items.size();
     p.active = false;
+    // Sequences released while this submission referenced them are retired now
+    // (drain_deferred_releases, crates/nvidia/src/serving.rs:1082-1096).
+    for (uint64_t sequence : ex->deferred_releases) retire_sequence(ex, sequence);
+    ex->deferred_releases.clear();
     return RIBN_B200_OK;
 }
 
 int ribn_b200_release(ribn_b200_executor* ex, uint64_t sequence) {
     if (ex == nullptr) return RIBN_B200_ERROR;
     auto found = ex->sequences.find(sequence);
-    if (found == ex->sequences.end()) return RIBN_B200_OK;  // idempotent
-    if (found->second.in_flight) return fail(ex, "sequence is referenced by in-flight work");
-    for (int32_t page : found->second.pages) ex->free_pages.push_back(page);
-    ex->free_slots.push_back(found->second.slot);
-    ex->sequences.erase(found);
+    if (found == ex->sequences.end() || found->second.released) return RIBN_B200_OK;  // idempotent
+    if (ex->prepared) {
+        for (const ribn_b200_batch_item& it : ex->prepared_items) {
+            if (it.sequence == sequence) return fail(ex, "cannot release prepared Qwen state");
+        }
+    }
+    if (found->second.in_flight) {
+        // Queued device work still reads this sequence's pages: park the release until the referencing
+        // submission completes (release_inference_state, crates/nvidia/src/serving.rs:1231-1251).
+        found->second.released = true;
+        ex->deferred_releases.push_back(sequence);
+        return RIBN_B200_OK;
+    }
+    retire_sequence(ex, sequence);
     return RIBN_B200_OK;
 }
 
@@ -1176,6 +1291,29 @@ int ribn_b200_debug_set_context(ribn_b200_executor* ex, uint64_t sequence, uint3
     s.position = tokens;
     s.has_next = true;
     std::vector<uint32_t>().swap(s.prompt);
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_debug_inject(ribn_b200_executor* ex, int32_t kind, int32_t value) {
+    if (ex == nullptr) return RIBN_B200_ERROR;
+    switch (kind) {
+        case RIBN_B200_INJECT_ALLOC_REFUSAL: ex->inject_alloc_failures = std::max(0, value); return RIBN_B200_OK;
+        case RIBN_B200_INJECT_ERROR_WORD: ex->inject_error_word = value; return RIBN_B200_OK;
+        case RIBN_B200_INJECT_BAD_ROW: ex->inject_bad_row = std::max(0, value); return RIBN_B200_OK;
+        default: return fail(ex, "unknown injection kind %d", kind);
+    }
+}
+
+int ribn_b200_debug_wait_expiry(ribn_b200_executor* ex, uint32_t spin_limit) {
+    if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    if (!ex->finalized || ex->pending.active) return fail(ex, "wait_expiry: executor not idle");
+    if (spin_limit == 0 || spin_limit > (1u << 20)) return fail(ex, "wait_expiry: the limit must be 1 .. 2^20 polls");
+    cudaSetDevice(ex->cfg.device);
+    // One thread waits on a barrier nothing completes; the wait gives up after `spin_limit` polls and leaves
+    // code 99 in the executor's error word, where the next poll finds it.  The call itself returns once the
+    // kernel has finished: the context stays usable.
+    CU_TRY(ex, launch_wait_probe(ex->stream, ex->d_error, spin_limit, 99));
+    CU_TRY(ex, cudaStreamSynchronize(ex->stream));
     return RIBN_B200_OK;
 }
 

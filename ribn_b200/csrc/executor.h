@@ -39,6 +39,7 @@ struct Sequence {
     uint32_t position = 0;      // committed prefix
     bool has_next = false;      // a sampled token is pending as the next decode input
     bool in_flight = false;
+    bool released = false;      // release() arrived while in flight: retired when the submission completes
     std::vector<int32_t> pages;
 };
 
@@ -109,6 +110,12 @@ struct ribn_b200_executor {
     int* d_error = nullptr;    // raised by a kernel whose bounded wait expired
     int* h_error = nullptr;    // pinned copy read at poll
     std::vector<void*> allocations;
+    std::vector<uint64_t> deferred_releases;  // sequences released while referenced by the pending submission
+    // Host-side fault injection (ribn_b200_debug_inject): how many of the next device allocations to refuse,
+    // an error word to plant at the end of the next step, and a row record to corrupt at the next submit.
+    int inject_alloc_failures = 0;
+    int inject_error_word = 0;
+    int inject_bad_row = 0;
 
     ribn::Tensor& lt(int layer, int which) { return layer_tensors[(size_t)layer * ribn::kLayerTensors + which]; }
 };

@@ -619,11 +619,13 @@ template <int RT>
 cudaError_t launch_rt(cudaStream_t stream, const GemmArgs& args, int units) {
     const StageLayout lay = layout_for(args, RT);
     const size_t smem = smem_for(lay, RT);
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[kMaxDevices] = {false};  // function attributes are per device
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(gemm_imma_kernel<RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured[dev] = true;
     }
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     gemm_imma_kernel<RT><<<units, kThreads, smem, stream>>>(args, lay);
@@ -637,12 +639,13 @@ cudaError_t launch_gemm_imma(cudaStream_t stream, const GemmArgs& args) {
     if (args.epilogue == kSwiGLU && (args.n_segments != 2 || args.seg[0].row_tiles != args.seg[1].row_tiles)) {
         return cudaErrorInvalidValue;
     }
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+    static int sm_counts[kMaxDevices] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (sm_counts[dev] == 0) {
+        if (cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_counts[dev] <= 0) sm_counts[dev] = 148;
     }
+    const int sm_count = sm_counts[dev];
     const int units4 = units_for(args, 4);
     if (units4 <= 0) return cudaSuccess;
     // Four row tiles per CTA reuse each activation chunk most; when that leaves SMs idle and half-size

@@ -27,13 +27,6 @@
 #include "blocks.cuh"
 #include "gemv.cuh"
 
-// Measurement aid (0 in the shipped build), K-quant kernel only: 1 = conversion warps skip their work,
-// 2 = no MMAs are issued, 3 = no activation chunk copies, 4 = the epilogue warps skip the fold,
-// 5 = all of these (barrier traffic and weight copies only).
-#ifndef RIBN_TC_PROBE
-#define RIBN_TC_PROBE 0
-#endif
-
 namespace ribn {
 
 namespace {
@@ -52,7 +45,7 @@ constexpr int kAHalfBytes = kRows * kChunkK * 2;   // one of hi / lo for a chunk
 constexpr int kABytes = 2 * kAHalfBytes;
 constexpr int kALbo = (kRows / 8) * 128;           // bytes between the 8-input column blocks of A
 constexpr int kTmemCols = 512;
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kSpinLimit = 1u << 22;   // bounded waits: default number of polls before giving up
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -75,8 +68,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait; on expiry raises the error word and reports false (the caller stops waiting but
 // keeps arriving, so nobody else is left hanging on it).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
     }
     if (error_flag != nullptr) atomicExch(error_flag, code);
@@ -84,8 +77,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
 }
 // The same for waits that usually last microseconds (a whole K loop, a ring turn): sleeps between
 // polls so the waiting warp does not take issue slots from the dequant warps.
-__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, int* error_flag, int code) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, int* error_flag, int code, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         __nanosleep(100);
     }
@@ -154,42 +147,41 @@ __device__ __forceinline__ int a_offset(int r, int k0) { return (k0 >> 3) * kALb
 
 __device__ __forceinline__ float byte_of(uint32_t w, int i) { return (float)((w >> (8 * i)) & 0xffu); }
 
-// One 64-input chunk `c` of one packed tile -> rows [row0, row0 + 16) of the A chunk.
-// Lane (g, t) holds rows g and g + 8; the tile's byte order is that of the GEMV kernel's MMA fragments.
-__device__ __forceinline__ void dequant_chunk(int type, const unsigned char* tile, int c, unsigned char* a_hi, int row0, int rr, int lane) {
+// One 64-input chunk `c` of one packed tile, decoded with the reference's arithmetic: lane (g, t) holds rows g and
+// g + 8 of the tile (`rr` selects which) in the byte order of the GEMV kernel's MMA fragments, and hands
+// `emit(row, k, w0, w1, w2, w3)` the four consecutive weights k .. k + 3 (k inside the chunk) of tile row `row`.
+template <typename Emit>
+__device__ __forceinline__ void decode_chunk(int type, const unsigned char* tile, int c, int rr, int lane, Emit emit) {
     const int g = lane >> 2, t = lane & 3;
+    const int row = g + 8 * rr;
     if (type == kQ4_K) {
         const uint4 w = *reinterpret_cast<const uint4*>(tile + c * 512 + lane * 16);
-        {
-            const int row = g + 8 * rr;
-            const uint4 h = *reinterpret_cast<const uint4*>(tile + 2048 + row * 16);
-            const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
-            const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
-            const uint32_t sc4 = c < 2 ? (h.y & 0x3F3F3F3Fu) : ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u));
-            const uint32_t mn4 = c < 2 ? (h.z & 0x3F3F3F3Fu) : (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u));
-            const int b0 = (2 * c) & 3;  // byte of the even group inside its half
-            const float gs_e = __fmul_rn(d, byte_of(sc4, b0)), gs_o = __fmul_rn(d, byte_of(sc4, b0 + 1));
-            const float gm_e = __fmul_rn(dmin, byte_of(mn4, b0)), gm_o = __fmul_rn(dmin, byte_of(mn4, b0 + 1));
-            // fl(gs * q) from the integer's float pattern 2^23 + q in one fused step: gs * 2^23 is exact,
-            // so fma(gs, 2^23 + q, -(gs * 2^23)) rounds the exact product gs * q once, as the multiplication does.
-            const float ce = -(gs_e * 8388608.0f), co = -(gs_o * 8388608.0f);
-            const uint32_t lo16 = rr == 0 ? w.x : w.z, hi16 = rr == 0 ? w.y : w.w;  // inputs 4t.. and 16 + 4t.. of both groups
-            unsigned char* base = a_hi + a_offset(row0 + row, 0);
+        const uint4 h = *reinterpret_cast<const uint4*>(tile + 2048 + row * 16);
+        const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
+        const uint32_t sc4 = c < 2 ? (h.y & 0x3F3F3F3Fu) : ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u));
+        const uint32_t mn4 = c < 2 ? (h.z & 0x3F3F3F3Fu) : (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u));
+        const int b0 = (2 * c) & 3;  // byte of the even group inside its half
+        const float gs_e = __fmul_rn(d, byte_of(sc4, b0)), gs_o = __fmul_rn(d, byte_of(sc4, b0 + 1));
+        const float gm_e = __fmul_rn(dmin, byte_of(mn4, b0)), gm_o = __fmul_rn(dmin, byte_of(mn4, b0 + 1));
+        // fl(gs * q) from the integer's float pattern 2^23 + q in one fused step: gs * 2^23 is exact,
+        // so fma(gs, 2^23 + q, -(gs * 2^23)) rounds the exact product gs * q once, as the multiplication does.
+        const float ce = -(gs_e * 8388608.0f), co = -(gs_o * 8388608.0f);
+        const uint32_t lo16 = rr == 0 ? w.x : w.z, hi16 = rr == 0 ? w.y : w.w;  // inputs 4t.. and 16 + 4t.. of both groups
 #pragma unroll
-            for (int part = 0; part < 2; ++part) {
-                const uint32_t word = part == 0 ? lo16 : hi16;
-                float e[4], o[4];
+        for (int part = 0; part < 2; ++part) {
+            const uint32_t word = part == 0 ? lo16 : hi16;
+            float e[4], o[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float fe = __uint_as_float(((word >> (8 * i)) & 15u) | 0x4B000000u);
-                    const float fo = __uint_as_float(((word >> (8 * i + 4)) & 15u) | 0x4B000000u);
-                    e[i] = __fsub_rn(__fmaf_rn(gs_e, fe, ce), gm_e);
-                    o[i] = __fsub_rn(__fmaf_rn(gs_o, fo, co), gm_o);
-                }
-                const int k_e = part * 16 + 4 * t, k_o = 32 + part * 16 + 4 * t;
-                store_split4(base + (k_e >> 3) * kALbo + (k_e & 7) * 2, e[0], e[1], e[2], e[3]);
-                store_split4(base + (k_o >> 3) * kALbo + (k_o & 7) * 2, o[0], o[1], o[2], o[3]);
+            for (int i = 0; i < 4; ++i) {
+                const float fe = __uint_as_float(((word >> (8 * i)) & 15u) | 0x4B000000u);
+                const float fo = __uint_as_float(((word >> (8 * i + 4)) & 15u) | 0x4B000000u);
+                e[i] = __fsub_rn(__fmaf_rn(gs_e, fe, ce), gm_e);
+                o[i] = __fsub_rn(__fmaf_rn(gs_o, fo, co), gm_o);
             }
+            const int k_e = part * 16 + 4 * t, k_o = 32 + part * 16 + 4 * t;
+            emit(row, k_e, e[0], e[1], e[2], e[3]);
+            emit(row, k_o, o[0], o[1], o[2], o[3]);
         }
     } else if (type == kQ6_K) {
         // chunk c covers groups 2c, 2c + 1: super-half cc = c / 2, variants v = 2 (c % 2), + 1
@@ -198,27 +190,22 @@ __device__ __forceinline__ void dequant_chunk(int type, const unsigned char* til
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const uint4 w = *reinterpret_cast<const uint4*>(tile + (cc * 2 + h) * 512 + lane * 16);
-            {
-                const int row = g + 8 * rr;
-                const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(tile + 3328 + row * 2)));
-                const signed char* scales = reinterpret_cast<const signed char*>(tile + 3072 + row * 16);
-                const uint32_t high = rr == 0 ? (h == 0 ? qh.x : qh.z) : (h == 0 ? qh.y : qh.w);
-                unsigned char* base = a_hi + a_offset(row0 + row, 0);
+            const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(tile + 3328 + row * 2)));
+            const signed char* scales = reinterpret_cast<const signed char*>(tile + 3072 + row * 16);
+            const uint32_t high = rr == 0 ? (h == 0 ? qh.x : qh.z) : (h == 0 ? qh.y : qh.w);
 #pragma unroll
-                for (int vv = 0; vv < 2; ++vv) {
-                    const int v = v0 + vv, group = cc * 4 + v;
-                    const uint32_t low = rr == 0 ? ((v & 1) ? w.y : w.x) : ((v & 1) ? w.w : w.z);
-                    const float gs = __fmul_rn(d, (float)scales[group * 2 + h]);
-                    float q[4];
+            for (int vv = 0; vv < 2; ++vv) {
+                const int v = v0 + vv, group = cc * 4 + v;
+                const uint32_t low = rr == 0 ? ((v & 1) ? w.y : w.x) : ((v & 1) ? w.w : w.z);
+                const float gs = __fmul_rn(d, (float)scales[group * 2 + h]);
+                float q[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const uint32_t lb = (low >> (8 * i)) & 0xffu, hb = (high >> (8 * i)) & 0xffu;
-                        const uint32_t nib = v < 2 ? (lb & 15u) : (lb >> 4);
-                        q[i] = __fmul_rn(gs, small_uint_f32(nib | (((hb >> (2 * v)) & 3u) << 4)) - 32.0f);
-                    }
-                    const int k = vv * 32 + h * 16 + 4 * t;
-                    store_split4(base + (k >> 3) * kALbo + (k & 7) * 2, q[0], q[1], q[2], q[3]);
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t lb = (low >> (8 * i)) & 0xffu, hb = (high >> (8 * i)) & 0xffu;
+                    const uint32_t nib = v < 2 ? (lb & 15u) : (lb >> 4);
+                    q[i] = __fmul_rn(gs, small_uint_f32(nib | (((hb >> (2 * v)) & 3u) << 4)) - 32.0f);
                 }
+                emit(row, vv * 32 + h * 16 + 4 * t, q[0], q[1], q[2], q[3]);
             }
         }
     } else {
@@ -227,22 +214,41 @@ __device__ __forceinline__ void dequant_chunk(int type, const unsigned char* til
         for (int bb = 0; bb < 2; ++bb) {
             const int block = 2 * c + bb;
             const uint4 w = *reinterpret_cast<const uint4*>(tile + block * 512 + lane * 16);
-            {
-                const int row = g + 8 * rr;
-                const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(tile + 4096 + row * 16 + block * 2)));
-                unsigned char* base = a_hi + a_offset(row0 + row, 0);
+            const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(tile + 4096 + row * 16 + block * 2)));
 #pragma unroll
-                for (int part = 0; part < 2; ++part) {
-                    const uint32_t word = rr == 0 ? (part == 0 ? w.x : w.y) : (part == 0 ? w.z : w.w);
-                    float q[4];
+            for (int part = 0; part < 2; ++part) {
+                const uint32_t word = rr == 0 ? (part == 0 ? w.x : w.y) : (part == 0 ? w.z : w.w);
+                float q[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) q[i] = __fmul_rn(d, small_uint_f32((word >> (8 * i)) & 0xffu) - 128.0f);
-                    const int k = bb * 32 + part * 16 + 4 * t;
-                    store_split4(base + (k >> 3) * kALbo + (k & 7) * 2, q[0], q[1], q[2], q[3]);
-                }
+                for (int i = 0; i < 4; ++i) q[i] = __fmul_rn(d, small_uint_f32((word >> (8 * i)) & 0xffu) - 128.0f);
+                emit(row, bb * 32 + part * 16 + 4 * t, q[0], q[1], q[2], q[3]);
             }
         }
     }
+}
+
+// The same chunk -> rows [row0, row0 + 16) of the A operand chunk, as binary16 hi + lo planes.
+__device__ __forceinline__ void dequant_chunk(int type, const unsigned char* tile, int c, unsigned char* a_hi, int row0, int rr, int lane) {
+    decode_chunk(type, tile, c, rr, lane, [&](int row, int k, float w0, float w1, float w2, float w3) {
+        store_split4(a_hi + a_offset(row0 + row, 0) + (k >> 3) * kALbo + (k & 7) * 2, w0, w1, w2, w3);
+    });
+}
+
+// Packed tiles -> F32 [rows][cols], through decode_chunk: what the tensor-core kernels see of a repacked matrix.
+__global__ void unpack_packed_kernel(int type, const unsigned char* packed, long long rows, int k_tiles, float* out) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;   // 8 warps: (chunk c, row half rr)
+    const long long tile_index = blockIdx.x;                      // row tile * k_tiles + k tile
+    const long long rt = tile_index / k_tiles;
+    const int kb = (int)(tile_index % k_tiles);
+    const unsigned char* tile = packed + (size_t)tile_index * packed_tile_bytes(type);
+    const long long cols = (long long)k_tiles * kTileCols;
+    decode_chunk(type, tile, warp >> 1, warp & 1, lane, [&](int row, int k, float w0, float w1, float w2, float w3) {
+        const long long r = rt * kTileRows + row;
+        if (r < rows) {
+            float* dst = out + r * cols + (long long)kb * kTileCols + (warp >> 1) * kChunkK + k;
+            dst[0] = w0; dst[1] = w1; dst[2] = w2; dst[3] = w3;
+        }
+    });
 }
 
 // Rows [row0, row0 + 8) of both planes: 8 column blocks x 128 bytes per plane.
@@ -284,6 +290,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmArgs a, 
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_tiles = a.k / kTileCols;
+    const uint32_t spin_limit = a.spin_limit ? a.spin_limit : kSpinLimit;
     unsigned char* w_ring = smem;
     unsigned char* a_buf = w_ring + (size_t)lay.w_stages * lay.w_stage_bytes;   // [2][hi | lo]
     unsigned char* b_buf = a_buf + 2 * kABytes;                                  // [b_stages][b_bytes]
@@ -327,7 +334,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmArgs a, 
             const uint32_t stage = w_count % (uint32_t)lay.w_stages;
             if (lane == 0) {
                 if (w_count >= (uint32_t)lay.w_stages && alive) {
-                    alive = mbar_wait_relaxed(w_empty + 8 * stage, ((w_count / (uint32_t)lay.w_stages) - 1u) & 1u, a.error_flag, 11);
+                    alive = mbar_wait_relaxed(w_empty + 8 * stage, ((w_count / (uint32_t)lay.w_stages) - 1u) & 1u, a.error_flag, 11, spin_limit);
                 }
                 const int present = min(kRowTilesPerUnit, s.row_tiles - ur.rt0);
                 mbar_expect_tx(w_full + 8 * stage, (uint32_t)present * tb);
@@ -347,7 +354,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmArgs a, 
                 if (lane == 0) {
                     for (int c = 0; c < kChunksPerTile; ++c, ++b_count) {
                         const uint32_t nb = (uint32_t)lay.b_stages, bs = b_count % nb;
-                        if (b_count >= nb && alive) alive = mbar_wait_relaxed(b_empty + 8 * bs, ((b_count / nb) - 1u) & 1u, a.error_flag, 12);
+                        if (b_count >= nb && alive) alive = mbar_wait_relaxed(b_empty + 8 * bs, ((b_count / nb) - 1u) & 1u, a.error_flag, 12, spin_limit);
                         mbar_expect_tx(b_full + 8 * bs, (uint32_t)lay.b_bytes);
                         bulk_g2s(smem_u32(b_buf + (size_t)bs * lay.b_bytes),
                                  a.chunks + ((size_t)kb * kChunksPerTile + c) * lay.b_bytes, (uint32_t)lay.b_bytes, b_full + 8 * bs);
@@ -366,14 +373,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmArgs a, 
             const uint32_t b_lbo = (uint32_t)(lay.cols / 8) * 128u;
             for (int u = blockIdx.x; u < units; u += gridDim.x, ++unit_count) {
                 const uint32_t tb = unit_count & 1u;
-                if (unit_count >= 2u && alive) alive = mbar_wait_relaxed(t_empty + 8 * tb, ((unit_count >> 1) - 1u) & 1u, a.error_flag, 13);
+                if (unit_count >= 2u && alive) alive = mbar_wait_relaxed(t_empty + 8 * tb, ((unit_count >> 1) - 1u) & 1u, a.error_flag, 13, spin_limit);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + tb * (uint32_t)acc_cols;
                 for (int kc = 0; kc < k_tiles * kChunksPerTile; ++kc, ++count) {
                     const uint32_t st = count & 1u, parity = (count >> 1) & 1u;
                     const uint32_t nb = (uint32_t)lay.b_stages, bs = count % nb;
-                    if (alive) alive = mbar_wait(a_full + 8 * st, parity, a.error_flag, 14);
-                    if (alive) alive = mbar_wait(b_full + 8 * bs, (count / nb) & 1u, a.error_flag, 15);
+                    if (alive) alive = mbar_wait(a_full + 8 * st, parity, a.error_flag, 14, spin_limit);
+                    if (alive) alive = mbar_wait(b_full + 8 * bs, (count / nb) & 1u, a.error_flag, 15, spin_limit);
                     tc_fence_after();
                     const uint32_t a_hi = smem_u32(a_buf + (size_t)st * kABytes), a_lo = a_hi + kAHalfBytes;
                     const uint32_t b_addr = smem_u32(b_buf + (size_t)bs * lay.b_bytes);
@@ -404,11 +411,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmArgs a, 
             const int tb = packed_tile_bytes(type);
             for (int kb = 0; kb < k_tiles; ++kb, ++w_count) {
                 const uint32_t stage = w_count % (uint32_t)lay.w_stages;
-                if (alive) alive = mbar_wait(w_full + 8 * stage, (w_count / (uint32_t)lay.w_stages) & 1u, a.error_flag, 16);
+                if (alive) alive = mbar_wait(w_full + 8 * stage, (w_count / (uint32_t)lay.w_stages) & 1u, a.error_flag, 16, spin_limit);
                 const unsigned char* tile = w_ring + (size_t)stage * lay.w_stage_bytes + (size_t)rt_local * tb;
                 for (int c = 0; c < kChunksPerTile; ++c, ++a_count) {
                     const uint32_t st = a_count & 1u;
-                    if (a_count >= 2u && alive) alive = mbar_wait(a_empty + 8 * st, ((a_count >> 1) - 1u) & 1u, a.error_flag, 17);
+                    if (a_count >= 2u && alive) alive = mbar_wait(a_empty + 8 * st, ((a_count >> 1) - 1u) & 1u, a.error_flag, 17, spin_limit);
                     unsigned char* a_hi = a_buf + (size_t)st * kABytes;
                     if (present) dequant_chunk(type, tile, c, a_hi, rt_local * kTileRows, rr, lane);
                     else zero_rows(a_hi, rt_local * kTileRows + 8 * rr, lane);
@@ -428,7 +435,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmArgs a, 
             const uint32_t tb = unit_count & 1u;
             const UnitRef ur = unit_of(a, u);
             const GemvSegment& s = a.seg[ur.seg];
-            if (alive) alive = mbar_wait_relaxed(t_full + 8 * tb, (unit_count >> 1) & 1u, a.error_flag, 18);
+            if (alive) alive = mbar_wait_relaxed(t_full + 8 * tb, (unit_count >> 1) & 1u, a.error_flag, 18, spin_limit);
             tc_fence_after();
             const int n_index = ur.rt0 * kTileRows + warp * 32 + lane;
             const bool valid = n_index < s.n;
@@ -575,6 +582,7 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_tiles = a.k / kTileCols;
+    const uint32_t spin_limit = a.spin_limit ? a.spin_limit : kSpinLimit;
     // Operand stages hold lay.chunk_k inputs: 128 when every unit is Q4_K (half as many hand-offs per k tile), else 64.
     const int pieces = lay.chunk_k / kChunkK, chunks_per_tile = kTileCols / lay.chunk_k;
     const int a_bytes = lay.a_planes * kAHalfBytes * pieces;
@@ -634,7 +642,7 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
             const uint32_t stage = w_count % (uint32_t)lay.w_stages;
             if (lane == 0) {
                 if (w_count >= (uint32_t)lay.w_stages && alive) {
-                    alive = mbar_wait_relaxed(w_empty + 8 * stage, ((w_count / (uint32_t)lay.w_stages) - 1u) & 1u, a.error_flag, 21);
+                    alive = mbar_wait_relaxed(w_empty + 8 * stage, ((w_count / (uint32_t)lay.w_stages) - 1u) & 1u, a.error_flag, 21, spin_limit);
                 }
                 const int present = min(kRowTilesPerUnit, s.row_tiles - ur.rt0);
                 mbar_expect_tx(w_full + 8 * stage, (uint32_t)present * tb);
@@ -655,7 +663,7 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
             for (int kb = kb0; kb < kb1; ++kb, ++kt_count) {
                 if (lane == 0) {
                     const uint32_t p = kt_count & 1u;
-                    if (kt_count >= 2u && alive) alive = mbar_wait_relaxed(t_full + 8 * p, ((kt_count >> 1) - 1u) & 1u, a.error_flag, 23);
+                    if (kt_count >= 2u && alive) alive = mbar_wait_relaxed(t_full + 8 * p, ((kt_count >> 1) - 1u) & 1u, a.error_flag, 23, spin_limit);
                     mbar_expect_tx(b2_full + 8 * p, (uint32_t)lay.b2_bytes);
                     bulk_g2s(smem_u32(b2_buf + (size_t)p * lay.b2_bytes),
                              a.chunks + (size_t)group_index(item) * lay.group_bytes + (size_t)kb * tile_stride + (size_t)kChunksPerTile * lay.b_bytes,
@@ -680,8 +688,7 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                     for (int c = 0; c < chunks_per_tile; ++c, ++b_count) {
                         if ((c & 1) != which) continue;
                         const uint32_t bs = b_count % na;
-                        if (b_count >= na && alive) alive = mbar_wait_relaxed(a_empty + 8 * bs, ((b_count / na) - 1u) & 1u, a.error_flag, 22);
-                        if (RIBN_TC_PROBE == 3 || RIBN_TC_PROBE == 5) { mbar_arrive(b_full + 8 * bs); continue; }
+                        if (b_count >= na && alive) alive = mbar_wait_relaxed(a_empty + 8 * bs, ((b_count / na) - 1u) & 1u, a.error_flag, 22, spin_limit);
                         mbar_expect_tx(b_full + 8 * bs, (uint32_t)b_stage_bytes);
                         bulk_g2s(smem_u32(b_buf + (size_t)bs * b_stage_bytes), src + (size_t)c * b_stage_bytes, (uint32_t)b_stage_bytes, b_full + 8 * bs);
                     }
@@ -699,13 +706,13 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                 const int kb0 = (item % S) * tps, kb1 = min(k_tiles, kb0 + tps);
                 for (int kb = kb0; kb < kb1; ++kb, ++kt_count) {
                     const uint32_t p = kt_count & 1u;
-                    if (kt_count >= 2u && alive) alive = mbar_wait(t_empty + 8 * p, ((kt_count >> 1) - 1u) & 1u, a.error_flag, 24);
+                    if (kt_count >= 2u && alive) alive = mbar_wait(t_empty + 8 * p, ((kt_count >> 1) - 1u) & 1u, a.error_flag, 24, spin_limit);
                     tc_fence_after();
                     const uint32_t d_main = tmem_base + p * 128u, d_min = tmem_base + 256u + p * 128u;
                     for (int c = 0; c < chunks_per_tile; ++c, ++count) {
                         const uint32_t st = count % na, bs = st;
-                        if (alive) alive = mbar_wait(a_full + 8 * st, (count / na) & 1u, a.error_flag, 25);
-                        if (alive) alive = mbar_wait(b_full + 8 * bs, (count / na) & 1u, a.error_flag, 26);
+                        if (alive) alive = mbar_wait(a_full + 8 * st, (count / na) & 1u, a.error_flag, 25, spin_limit);
+                        if (alive) alive = mbar_wait(b_full + 8 * bs, (count / na) & 1u, a.error_flag, 26, spin_limit);
                         tc_fence_after();
                         const uint32_t a_addr = smem_u32(a_buf + (size_t)st * a_bytes);
                         const uint32_t b_addr = smem_u32(b_buf + (size_t)bs * b_stage_bytes);
@@ -715,25 +722,23 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                         const uint64_t da_step = (uint64_t)((2 * kALbo) >> 4), db_step = (uint64_t)((2 * b_lbo) >> 4);
                         const uint64_t da_plane = (uint64_t)(kAHalfBytes >> 4);
                         const int steps = lay.chunk_k / 16;
-                        if (RIBN_TC_PROBE != 2 && RIBN_TC_PROBE != 5) {
-                            if (q4k) {
+                        if (q4k) {
 #pragma unroll 4
-                                for (int s16 = 0; s16 < steps; ++s16, da += da_step, db += db_step) {
-                                    umma_f16(d_main, da, db, idesc, (c | s16) != 0 ? 1u : 0u);
-                                }
-                            } else {
+                            for (int s16 = 0; s16 < steps; ++s16, da += da_step, db += db_step) {
+                                umma_f16(d_main, da, db, idesc, (c | s16) != 0 ? 1u : 0u);
+                            }
+                        } else {
 #pragma unroll 4
-                                for (int s16 = 0; s16 < steps; ++s16, da += da_step, db += db_step) {
-                                    umma_f16(d_main, da, db, idesc, (c | s16) != 0 ? 1u : 0u);
-                                    umma_f16(d_main, da + da_plane, db, idesc, 1u);
-                                }
+                            for (int s16 = 0; s16 < steps; ++s16, da += da_step, db += db_step) {
+                                umma_f16(d_main, da, db, idesc, (c | s16) != 0 ? 1u : 0u);
+                                umma_f16(d_main, da + da_plane, db, idesc, 1u);
                             }
                         }
                         if (c == chunks_per_tile - 1) {
                             // Q4_K: group minima x group sums of the activations (the chunk's a_full covers A2 as well)
-                            if (alive) alive = mbar_wait(b2_full + 8 * p, (kt_count >> 1) & 1u, a.error_flag, 27);
+                            if (alive) alive = mbar_wait(b2_full + 8 * p, (kt_count >> 1) & 1u, a.error_flag, 27, spin_limit);
                             tc_fence_after();
-                            if (q4k && RIBN_TC_PROBE != 2 && RIBN_TC_PROBE != 5) {
+                            if (q4k) {
                                 umma_f16(d_min, umma_desc(smem_u32(a2_buf + (size_t)p * kA2Bytes), kALbo, 128),
                                          umma_desc(smem_u32(b2_buf + (size_t)p * lay.b2_bytes), b_lbo, 128), idesc, 0u);
                             }
@@ -757,19 +762,18 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
             const int kb0 = (item % S) * tps, kb1 = min(k_tiles, kb0 + tps);
             for (int kb = kb0; kb < kb1; ++kb, ++w_count) {
                 const uint32_t stage = w_count % (uint32_t)lay.w_stages;
-                if (alive) alive = mbar_wait(w_full + 8 * stage, (w_count / (uint32_t)lay.w_stages) & 1u, a.error_flag, 28);
+                if (alive) alive = mbar_wait(w_full + 8 * stage, (w_count / (uint32_t)lay.w_stages) & 1u, a.error_flag, 28, spin_limit);
                 const unsigned char* tile = w_ring + (size_t)stage * lay.w_stage_bytes + (size_t)rt_local * tb;
                 for (int c = 0; c < chunks_per_tile; ++c, ++a_count) {
                     const uint32_t st = a_count % na;
-                    if (a_count >= na && alive) alive = mbar_wait(a_empty + 8 * st, ((a_count / na) - 1u) & 1u, a.error_flag, 29);
+                    if (a_count >= na && alive) alive = mbar_wait(a_empty + 8 * st, ((a_count / na) - 1u) & 1u, a.error_flag, 29, spin_limit);
                     unsigned char* planes = a_buf + (size_t)st * a_bytes;
                     // A2 and the row scales of k tile w_count: written at chunk 0, consumed after chunk 3's MMAs.
                     // A2's previous reader (two k tiles back) was issued before the MMAs whose completion released this
                     // chunk's buffer (at most four chunks back), so it has finished too.
                     unsigned char* a2 = a2_buf + (size_t)(w_count & 1u) * kA2Bytes;
                     float2* scales = row_scales + (size_t)(w_count & 3u) * kRows;
-                    if (RIBN_TC_PROBE == 1 || RIBN_TC_PROBE == 5) {
-                    } else if (present) {
+                    if (present) {
                         for (int piece = 0; piece < pieces; ++piece) {
                             kq_chunk(type, tile, c * pieces + piece, piece * kChunkK, planes, a2, scales, rt_local * kTileRows, 0, lane);
                             kq_chunk(type, tile, c * pieces + piece, piece * kChunkK, planes, a2, scales, rt_local * kTileRows, 1, lane);
@@ -811,13 +815,13 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
             for (int i = 0; i < kKqMaxMembers; ++i) acc[i] = 0.0f;
             for (int kb = kb0; kb < kb1; ++kb, ++kt_count) {
                 const uint32_t p = kt_count & 1u;
-                if (alive) alive = mbar_wait(t_full + 8 * p, (kt_count >> 1) & 1u, a.error_flag, 30);
+                if (alive) alive = mbar_wait(t_full + 8 * p, (kt_count >> 1) & 1u, a.error_flag, 30, spin_limit);
                 tc_fence_after();
                 const float2 ds = row_scales[(size_t)(kt_count & 3u) * kRows + row];
                 const uint32_t t_main = tmem_base + p * 128u + ((uint32_t)(warp * 32) << 16), t_min = t_main + 256u;
 #pragma unroll
                 for (int m0 = 0; m0 < kKqMaxMembers; m0 += 16) {
-                    if (m0 < lay.members_padded && RIBN_TC_PROBE != 4 && RIBN_TC_PROBE != 5) {
+                    if (m0 < lay.members_padded) {
                         float hi[16], lo[16];
                         tmem_ld16(t_main + (uint32_t)m0, hi);
                         tmem_ld16(t_main + (uint32_t)(lay.members_padded + m0), lo);
@@ -1111,6 +1115,27 @@ cudaError_t launch_to_tc_operand_groups(cudaStream_t stream, const float* x, con
 namespace {
 
 thread_local int g_last_launches = 1;
+constexpr size_t kTcSmemBudget = 220 * 1024;
+
+// Function attributes are per device: the opt-in to large dynamic shared memory is made once on every device a
+// process uses, and the SM count is kept per device ordinal.
+cudaError_t device_setup(int& sm_count) {
+    static int sms[kMaxDevices] = {0};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (sms[dev] == 0) {
+        e = cudaFuncSetAttribute(gemm_tcq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBudget);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBudget);
+        if (e != cudaSuccess) return e;
+        int count = 0;
+        if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || count <= 0) count = 148;
+        sms[dev] = count;
+    }
+    sm_count = sms[dev];
+    return cudaSuccess;
+}
 
 cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units, int tile) {
     KqLayout lay{};
@@ -1119,7 +1144,7 @@ cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units
     lay.b_bytes = lay.cols * kChunkK * (int)sizeof(__half);
     lay.b2_bytes = lay.cols * 16 * (int)sizeof(__half);
     lay.w_stage_bytes = kRowTilesPerUnit * tile;
-    const size_t budget = 220 * 1024;
+    const size_t budget = kTcSmemBudget;
     // 64 KB of A stages, two of them: 128 inputs of one plane when every unit is Q4_K, else 64 inputs of two planes
     bool all_q4k = true;
     for (int i = 0; i < args.n_segments; ++i) all_q4k = all_q4k && args.seg[i].type == kQ4_K;
@@ -1131,15 +1156,10 @@ cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units
     lay.w_stages = (int)std::min<size_t>(3, (budget - fixed) / (size_t)lay.w_stage_bytes);
     if (lay.w_stages < 2) return cudaErrorInvalidValue;
     const size_t smem = fixed + (size_t)lay.w_stages * lay.w_stage_bytes;
-    static bool configured = false;
-    static int sm_count = 0;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+    int sm_count = 0;
+    {
+        cudaError_t e = device_setup(sm_count);
         if (e != cudaSuccess) return e;
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
-        configured = true;
     }
     // Split K when whole units would leave SMs idle: pick the slice count with the fewest k tiles on the
     // busiest SM (each work item also pays about one k tile of pipeline fill).
@@ -1174,6 +1194,14 @@ cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units
 
 int gemm_tc_last_launches() { return g_last_launches; }
 
+cudaError_t launch_unpack_packed(cudaStream_t stream, int type, const unsigned char* packed, long long rows, long long cols,
+                                 float* out) {
+    if (!packable(type, rows, cols)) return cudaErrorInvalidValue;
+    const long long tiles = ((rows + kTileRows - 1) / kTileRows) * (cols / kTileCols);
+    unpack_packed_kernel<<<(unsigned int)tiles, 256, 0, stream>>>(type, packed, rows, (int)(cols / kTileCols), out);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmArgs& args) {
     g_last_launches = 1;
     if (args.members < 1 || args.members > kGemmTcMaxMembers || args.k % kTileCols != 0) return cudaErrorInvalidValue;
@@ -1197,22 +1225,17 @@ cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmArgs& args) {
     lay.w_stage_bytes = kRowTilesPerUnit * tile;
     // Two activation chunks at least; what is left after three weight stages deepens the activation ring
     // (its copies have a longer way than the tensor core needs for a chunk).
-    const size_t budget = 220 * 1024;
+    const size_t budget = kTcSmemBudget;
     size_t fixed = (size_t)2 * kABytes + (size_t)2 * lay.b_bytes + 16 + 320;
     lay.w_stages = (int)std::min<size_t>(3, (budget - fixed) / (size_t)lay.w_stage_bytes);
     if (lay.w_stages < 2) return cudaErrorInvalidValue;
     lay.b_stages = 2 + (int)std::min<size_t>(6, (budget - fixed - (size_t)lay.w_stages * lay.w_stage_bytes) / (size_t)lay.b_bytes);
     fixed += (size_t)(lay.b_stages - 2) * lay.b_bytes;
     const size_t smem = fixed + (size_t)lay.w_stages * lay.w_stage_bytes;
-    static bool configured = false;
-    static int sm_count = 0;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+    int sm_count = 0;
+    {
+        cudaError_t e = device_setup(sm_count);
         if (e != cudaSuccess) return e;
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
-        configured = true;
     }
     const int grid = std::min(units, sm_count);
     gemm_tc_kernel<<<grid, kThreads, smem, stream>>>(args, lay, units);

@@ -20,6 +20,7 @@ namespace ribn {
 
 constexpr int kTileRows = 16;
 constexpr int kTileCols = 256;
+constexpr int kMaxDevices = 64;  // per-device launcher state (function attributes, SM counts) is kept per ordinal
 
 struct PackedMatrix {
     unsigned char* data = nullptr;  // device
@@ -117,6 +118,7 @@ struct GemvArgs {
     const float* out_norm_weight;
     float* swiglu_f32;    // optional F32 copy of the gated product [members][n]
     int* error_flag;      // set non-zero when a bounded wait gives up
+    uint32_t spin_limit;  // polls before a wait gives up (0: the default, 1 << 22)
 };
 
 constexpr int kGemvMaxMembers = 2;
@@ -127,6 +129,9 @@ constexpr int kGemvMaxMembers = 2;
 cudaError_t launch_gemv_mma(cudaStream_t stream, const GemvArgs& args, bool programmatic);
 // One-time function attributes (call outside stream capture, with the device current).
 cudaError_t gemv_prepare();
+// Failure-detection aid: a one-thread kernel that waits, through the kernels' bounded wait, on a barrier
+// nothing completes; after `spin_limit` polls (at most 1 << 20) it writes `code` to *error_flag and returns.
+cudaError_t launch_wait_probe(cudaStream_t stream, int* error_flag, uint32_t spin_limit, int code);
 
 // ---- batched form (3..64 members) ---------------------------------------------------------------
 // Activations for the batched kernel: one scale per member for its whole vector
@@ -170,6 +175,7 @@ struct GemmArgs {
     // meets all the row groups of a prefill step while it is in L2.
     int groups;
     size_t group_chunk_bytes;
+    uint32_t spin_limit;  // polls before a bounded wait gives up (0: the default, 1 << 22)
 };
 
 cudaError_t launch_gemm_imma(cudaStream_t stream, const GemmArgs& args);
@@ -204,6 +210,10 @@ cudaError_t launch_to_tc_operand_groups(cudaStream_t stream, const float* x, con
                                         int members, int group, int k, float eps, TcOperand out);
 // GemmArgs::chunks points at TcOperand::chunks, GemmArgs::kquant says which form; epilogue kStore or kResidual.
 cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmArgs& args);
+// Parity aid: decodes a tile-major packed matrix back to F32 [rows][cols] with the weight decoder of the
+// decode-and-split tensor-memory kernel (the reference's arithmetic), reading the packed bytes only.
+cudaError_t launch_unpack_packed(cudaStream_t stream, int type, const unsigned char* packed, long long rows, long long cols,
+                                 float* out);
 // Kernels the calling thread's last launch_gemm_tc enqueued (2 when a split-K launch adds its ordered reduction).
 int gemm_tc_last_launches();
 

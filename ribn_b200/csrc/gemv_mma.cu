@@ -145,13 +145,6 @@ void repack_host(int type, const unsigned char* raw, long long n, long long k, u
 // ---------------------------------------------------------------------------
 namespace {
 
-// Measurement aid (never defined in the shipped build): 1 = consumers skip the tile math,
-// 2 = no weight copies and no waits (pure consumer instruction stream), 3 = as 2 and no epilogue
-// hand-off, 4 = as 3 with only the header decode of each tile, 5 = as 3 with only the MMA loop.
-#ifndef RIBN_PROBE
-#define RIBN_PROBE 0
-#endif
-
 constexpr int kConsumerWarps = 24;  // three teams of eight; team i consumes stages i, i + 3, ...
 constexpr int kTeamWarps = 8;
 constexpr int kTeams = kConsumerWarps / kTeamWarps;
@@ -164,7 +157,7 @@ constexpr int kThreads = (kConsumerWarps + 1 + kEpilogueWarps) * 32;
 constexpr int kMaxRuns = 4;         // row-tile runs per unit: 2 tiles of one matrix, or 2 x (gate, up)
 constexpr int kHdrStride = 20;      // floats per header row: 16 scales + offset sum + pad (conflict-free rows)
 constexpr int kPlanePad = 32;       // bytes between activation digit planes (distinct banks per plane)
-constexpr uint32_t kSpinLimit = 1u << 22;  // bounded waits: iterations before giving up
+constexpr uint32_t kSpinLimit = 1u << 22;  // bounded waits: default number of polls before giving up
 constexpr uint32_t kNibbles = 0x0F0F0F0Fu;
 constexpr uint32_t kHighNibbles = 0xF0F0F0F0u;
 constexpr uint32_t kTopBits = 0x30303030u;
@@ -195,8 +188,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false (and raises the error flag) when the phase never completes.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
     }
     if (error_flag != nullptr) atomicExch(error_flag, code);
@@ -340,7 +333,7 @@ __device__ __forceinline__ uint2 load_b(const Lane& ln, uint32_t offset) {
 // ---- Q4_K: w = gs * q - gm  =>  (gs * sx) * C  -  gm * (sx * sum digits) ------------------------
 template <int MEMBERS>
 __device__ __forceinline__ void tile_q4k(uint32_t tile, const Lane& ln, int kb, int lane, Accum& acc) {
-    if (RIBN_PROBE != 5) {
+    {
         // lane -> (row, half): scales and offsets of groups 4 half .. 4 half + 3, for every member
         const uint4 h = lds128(tile + 2048 + (lane >> 1) * 16);
         const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
@@ -372,7 +365,6 @@ __device__ __forceinline__ void tile_q4k(uint32_t tile, const Lane& ln, int kb, 
         }
     }
     __syncwarp();
-    if (RIBN_PROBE == 4) return;
     const uint32_t wbase = tile + lane * 16, bbase = kb * 256;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -393,7 +385,7 @@ __device__ __forceinline__ void tile_q4k(uint32_t tile, const Lane& ln, int kb, 
 // ---- Q6_K: w = gs * (q - 32), one scale per 16 inputs (k16 MMA) ---------------------------------
 template <int MEMBERS>
 __device__ __forceinline__ void tile_q6k(uint32_t tile, const Lane& ln, int kb, int lane, Accum& acc) {
-    if (RIBN_PROBE != 5) {
+    {
         // lane -> (row, half): the eight 16-input scales half * 8 .. half * 8 + 7 (groups half * 4 ..)
         const int row = lane >> 1;
         const uint2 s8 = lds64(tile + 3072 + row * 16 + ln.half * 8);
@@ -428,7 +420,6 @@ __device__ __forceinline__ void tile_q6k(uint32_t tile, const Lane& ln, int kb, 
         }
     }
     __syncwarp();
-    if (RIBN_PROBE == 4) return;
     const uint32_t wbase = tile + lane * 16, bbase = kb * 256;
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
@@ -529,6 +520,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int K = a.k, planes = 3 * MEMBERS, slots = slots_per_team * kTeams;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t spin_limit = a.spin_limit ? a.spin_limit : kSpinLimit;
     const bool swiglu = a.epilogue == kSwiGLU;
     const int runs = swiglu ? 4 : 2;  // row-tile runs per unit
     Shared sh;
@@ -574,7 +566,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
 
     if (warp == kProducerWarp) {
         // ---------------- producer: team t's k-th stage goes to slot (k % S) * 3 + t ----------------
-        if (lane == 0 && RIBN_PROBE < 2) {
+        if (lane == 0) {
             constexpr int kCursors = SHARED ? 1 : kTeams;
             const int unit_step = SHARED ? 1 : kTeams;
             const uint32_t ring_len = SHARED ? (uint32_t)slots : (uint32_t)slots_per_team;  // slots a cursor cycles through
@@ -596,7 +588,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
                     const uint32_t tile_bytes = (uint32_t)packed_tile_bytes(seg->type);
                     const uint32_t slot = SHARED ? k[t] % ring_len : (k[t] % ring_len) * kTeams + t;
                     if (k[t] >= ring_len) {
-                        alive = mbar_wait(sh.empty + slot * 8, ((k[t] / ring_len) - 1u) & 1u, a.error_flag, 1);
+                        alive = mbar_wait(sh.empty + slot * 8, ((k[t] / ring_len) - 1u) & 1u, a.error_flag, 1, spin_limit);
                         if (!alive) break;
                     }
                     const int tiles = min(kStageTiles, k_tiles - c.st * kStageTiles);
@@ -618,7 +610,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
 
     asm volatile("griddepcontrol.wait;" ::: "memory");  // activations and the residual come from the previous kernel
 
-    if (warp >= kEpilogueWarp && RIBN_PROBE >= 3) return;
     if (warp > kEpilogueWarp && SHARED) return;  // one epilogue warp serves the single cooperating set
     // cooperating set: its warps, barrier participants, and where its partial sums live
     constexpr int kSetWarps = SHARED ? kConsumerWarps : kTeamWarps;
@@ -721,9 +712,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
             bulk_g2s(smem_u32(sh.sxs), a.in.sxs16, sxs_bytes, sh.xbar);
         }
     }
-    bool alive = mbar_wait(sh.xbar, 0, a.error_flag, 2);
-    if (RIBN_PROBE >= 2) alive = false;
-    if (RIBN_PROBE == 7) return;  // launch, set-up and activation load only
+    bool alive = mbar_wait(sh.xbar, 0, a.error_flag, 2, spin_limit);
 
     const int g = lane >> 2, t = lane & 3;
     const int team = warp / kTeamWarps, member_warp = warp % kTeamWarps;
@@ -770,9 +759,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
             for (int st = 0; st < stages_per_run; ++st) {
                 if (!SHARED || turn == team) {  // SHARED: the teams take the stages in turn
                     const uint32_t slot = SHARED ? ring_pos : ring_pos * kTeams + team;
-                    if (alive) alive = mbar_wait(sh.full + slot * 8, ring_parity, a.error_flag, 3);
+                    if (alive) alive = mbar_wait(sh.full + slot * 8, ring_parity, a.error_flag, 3, spin_limit);
                     const int kb = st * kStageTiles + member_warp;
-                    if (kb < k_tiles && RIBN_PROBE != 1 && RIBN_PROBE != 6) {
+                    if (kb < k_tiles) {
                         const uint32_t tile = ring + slot * (uint32_t)slot_bytes + (uint32_t)(member_warp * tile_bytes);
                         if (type == kQ4_K) tile_q4k<MEMBERS>(tile, ln, kb, lane, acc[r]);
                         else if (type == kQ6_K) tile_q6k<MEMBERS>(tile, ln, kb, lane, acc[r]);
@@ -787,7 +776,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
         }
         // Per-warp partial of (row, member): digits 1 and 2 are this lane's two columns, digit 3 is the
         // first column of the next lane; lanes with even t own member t / 2.
-        if (done >= 2 && RIBN_PROBE < 3) bar_sync(kBarFree + set * 4 + buf, bar_threads);  // the epilogue warp has read this buffer
+        if (done >= 2) bar_sync(kBarFree + set * 4 + buf, bar_threads);  // the epilogue warp has read this buffer
         float* red = sh.red + ((size_t)(set * 2 + buf) * kSetWarps + set_warp) * kMaxRuns * MEMBERS * 16;
 #pragma unroll
         for (int r = 0; r < kMaxRuns; ++r) {
@@ -803,7 +792,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
             }
         }
         __syncwarp();
-        if (RIBN_PROBE < 3) bar_arrive(kBarFull + set * 4 + buf, bar_threads);
+        bar_arrive(kBarFull + set * 4 + buf, bar_threads);
     }
 }
 
@@ -824,14 +813,25 @@ __global__ void to_operand_kernel(const float* x, const int32_t* index, const fl
     operand_store_span(o, m, k, span, lane, v, sq);
 }
 
-int sm_count() {
-    static int count = 0;
-    if (count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || count <= 0) count = 148;
+// A wait nobody ends: one thread polls an mbarrier that no copy and no thread completes, through the same
+// bounded wait as the kernels above, and leaves `code` in the error word when the limit runs out.
+__global__ void wait_probe_kernel(int* error_flag, uint32_t spin_limit, int code) {
+    __shared__ __align__(8) unsigned long long bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_wait(smem_u32(&bar), 0, error_flag, code, spin_limit);
     }
-    return count;
+}
+
+int sm_count() {
+    static int counts[kMaxDevices] = {0};  // per device ordinal
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+    if (counts[dev] == 0) {
+        if (cudaDeviceGetAttribute(&counts[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || counts[dev] <= 0) counts[dev] = 148;
+    }
+    return counts[dev];
 }
 
 }  // namespace
@@ -840,7 +840,10 @@ int sm_count() {
 constexpr size_t kSmemBudget = 208 * 1024;
 
 cudaError_t gemv_prepare() {
-    static bool configured = false;
+    static bool configured_on[kMaxDevices] = {false};  // function attributes are per device
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    bool& configured = configured_on[dev];
     if (!configured) {
         const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
         cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<1, false>, at, (int)kSmemBudget);
@@ -852,6 +855,12 @@ cudaError_t gemv_prepare() {
         configured = true;
     }
     return cudaSuccess;
+}
+
+cudaError_t launch_wait_probe(cudaStream_t stream, int* error_flag, uint32_t spin_limit, int code) {
+    if (error_flag == nullptr || spin_limit == 0 || spin_limit > (1u << 20)) return cudaErrorInvalidValue;
+    wait_probe_kernel<<<1, 32, 0, stream>>>(error_flag, spin_limit, code);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_to_operand(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,

@@ -104,6 +104,120 @@ int ribn_b200_debug_repack(int32_t type, const void* raw, int64_t rows, int64_t 
     return RIBN_B200_OK;
 }
 
+int ribn_b200_debug_unpack(int32_t device, int32_t type, const void* packed, int64_t rows, int64_t cols, float* out) {
+    if (!packable(type, rows, cols) || packed == nullptr || out == nullptr) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
+    Scope s(device);
+    if (!s.ok) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
+    unsigned char* d_in = s.upload((const unsigned char*)packed, packed_bytes(type, rows, cols));
+    float* d_out = s.alloc<float>((size_t)rows * cols);
+    OP_PTR(d_in); OP_PTR(d_out);
+    OP_TRY(launch_unpack_packed(s.stream, type, d_in, rows, cols, d_out));
+    return s.download(out, d_out, (size_t)rows * cols) ? RIBN_B200_OK : RIBN_B200_ERROR;
+}
+
+int ribn_b200_op_embedding(int32_t device, int32_t type, const void* table, int32_t vocab, int32_t hidden,
+                           const uint32_t* tokens, int32_t count, float* out) {
+    const size_t n = encoded_bytes(type, vocab, hidden);
+    if (n == 0 || table == nullptr || tokens == nullptr || out == nullptr || count <= 0) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
+    for (int i = 0; i < count; ++i) if (tokens[i] >= (uint32_t)vocab) return op_fail("token id out of range", cudaSuccess);
+    Scope s(device);
+    if (!s.ok) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
+    unsigned char* d_t = s.upload((const unsigned char*)table, n);
+    uint32_t* d_ids = s.upload(tokens, (size_t)count);
+    float* d_o = s.alloc<float>((size_t)count * hidden);
+    OP_PTR(d_t); OP_PTR(d_ids); OP_PTR(d_o);
+    OP_TRY(launch_embedding(s.stream, type, d_t, hidden, vocab, d_ids, count, d_o));
+    return s.download(out, d_o, (size_t)count * hidden) ? RIBN_B200_OK : RIBN_B200_ERROR;
+}
+
+int ribn_b200_op_qk_norm_rope_append(int32_t device, float* q, float* k, const float* v, const float* q_norm,
+                                     const float* k_norm, const int32_t* positions, const int32_t* kv_slots,
+                                     int32_t tokens, int32_t q_heads, int32_t kv_heads, int32_t head_dim, float rope_base,
+                                     float eps, uint16_t* cache_k, uint16_t* cache_v, int32_t physical_tokens) {
+    Scope s(device);
+    if (!s.ok || tokens <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || (head_dim & 1) || physical_tokens <= 0) {
+        return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
+    }
+    for (int i = 0; i < tokens; ++i) {
+        if (kv_slots[i] < 0 || kv_slots[i] >= physical_tokens || positions[i] < 0) return op_fail("slot or position out of range", cudaSuccess);
+    }
+    const size_t qn = (size_t)tokens * q_heads * head_dim, kn = (size_t)tokens * kv_heads * head_dim;
+    const size_t cache_elems = (size_t)physical_tokens * kv_heads * head_dim;
+    std::vector<float> table((size_t)head_dim / 2);
+    for (int p = 0; p < head_dim / 2; ++p) table[p] = powf(rope_base, -(2.0f * (float)p) / (float)head_dim);
+    float* d_q = s.upload(q, qn);
+    float* d_k = s.upload(k, kn);
+    float* d_v = s.upload(v, kn);
+    float* d_qn = s.upload(q_norm, (size_t)head_dim);
+    float* d_kn = s.upload(k_norm, (size_t)head_dim);
+    float* d_t = s.upload(table.data(), table.size());
+    int32_t* d_pos = s.upload(positions, (size_t)tokens);
+    int32_t* d_slot = s.upload(kv_slots, (size_t)tokens);
+    uint16_t* d_ck = s.upload(cache_k, cache_elems);
+    uint16_t* d_cv = s.upload(cache_v, cache_elems);
+    OP_PTR(d_q); OP_PTR(d_k); OP_PTR(d_v); OP_PTR(d_qn); OP_PTR(d_kn); OP_PTR(d_t); OP_PTR(d_pos); OP_PTR(d_slot);
+    OP_PTR(d_ck); OP_PTR(d_cv);
+    OP_TRY(launch_qk_norm_rope_append(s.stream, d_q, d_k, d_v, d_qn, d_kn, d_t, d_pos, d_slot, tokens, q_heads, kv_heads,
+                                      head_dim, eps, (__half*)d_ck, (__half*)d_cv));
+    bool ok = s.download(q, d_q, qn) && s.download(k, d_k, kn);
+    ok = ok && s.download(cache_k, d_ck, cache_elems) && s.download(cache_v, d_cv, cache_elems);
+    return ok ? RIBN_B200_OK : RIBN_B200_ERROR;
+}
+
+int ribn_b200_op_attention_decode(int32_t device, const float* q, const float* k, const float* v, const float* q_norm,
+                                  const float* k_norm, float rope_base, float eps, uint16_t* cache_k, uint16_t* cache_v,
+                                  int32_t physical_tokens, const int32_t* page_tables, int32_t pages_per_sequence,
+                                  const int32_t* positions, int32_t members, int32_t q_heads, int32_t kv_heads,
+                                  int32_t head_dim, float* out) {
+    Scope s(device);
+    if (!s.ok || members <= 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || pages_per_sequence <= 0 ||
+        (head_dim != 64 && head_dim != 128 && head_dim != 256) || physical_tokens <= 0) {
+        return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
+    }
+    std::vector<int32_t> seq(members), slot(members);
+    int max_keys = 0;
+    for (int m = 0; m < members; ++m) {
+        const int pos = positions[m];
+        if (pos < 0 || pos / kPageTokens >= pages_per_sequence) return op_fail("position outside the page table", cudaSuccess);
+        const int page = page_tables[(size_t)m * pages_per_sequence + pos / kPageTokens];
+        if (page < 0 || (page + 1) * kPageTokens > physical_tokens) return op_fail("page outside the cache", cudaSuccess);
+        seq[m] = m;
+        slot[m] = page * kPageTokens + pos % kPageTokens;
+        max_keys = std::max(max_keys, pos + 1);
+    }
+    const size_t qn = (size_t)members * q_heads * head_dim, kn = (size_t)members * kv_heads * head_dim;
+    const size_t cache_elems = (size_t)physical_tokens * kv_heads * head_dim;
+    std::vector<float> table((size_t)head_dim / 2);
+    for (int p = 0; p < head_dim / 2; ++p) table[p] = powf(rope_base, -(2.0f * (float)p) / (float)head_dim);
+    DecodeAttention d{};
+    d.q = s.upload(q, qn); d.k = s.upload(k, kn); d.v = s.upload(v, kn);
+    d.q_norm = s.upload(q_norm, (size_t)head_dim); d.k_norm = s.upload(k_norm, (size_t)head_dim);
+    d.inv_freq = s.upload(table.data(), table.size());
+    d.eps = eps;
+    d.cache_k = (__half*)s.upload(cache_k, cache_elems);
+    d.cache_v = (__half*)s.upload(cache_v, cache_elems);
+    d.page_tables = s.upload(page_tables, (size_t)members * pages_per_sequence);
+    d.pages_per_sequence = pages_per_sequence;
+    d.token_seq = s.upload(seq.data(), seq.size());
+    d.token_pos = s.upload(positions, (size_t)members);
+    d.token_slot = s.upload(slot.data(), slot.size());
+    d.n_tokens = members; d.q_heads = q_heads; d.kv_heads = kv_heads; d.head_dim = head_dim;
+    d.window = 0; d.max_keys = max_keys;
+    const size_t spans = ((size_t)max_keys + kAttnSpanKeys - 1) / kAttnSpanKeys;
+    d.partial_bytes = (size_t)members * q_heads * spans * (head_dim + 2) * sizeof(float);
+    d.partial = s.alloc<float>(d.partial_bytes / sizeof(float));
+    float* d_out = s.alloc<float>(qn);
+    d.out = d_out;
+    d.programmatic = false;
+    OP_PTR(d.q); OP_PTR(d.k); OP_PTR(d.v); OP_PTR(d.q_norm); OP_PTR(d.k_norm); OP_PTR(d.inv_freq); OP_PTR(d.cache_k);
+    OP_PTR(d.cache_v); OP_PTR(d.page_tables); OP_PTR(d.token_seq); OP_PTR(d.token_pos); OP_PTR(d.token_slot);
+    OP_PTR(d.partial); OP_PTR(d_out);
+    OP_TRY(launch_attention_decode(s.stream, d, nullptr));
+    bool ok = s.download(out, d_out, qn);
+    ok = ok && s.download(cache_k, (uint16_t*)d.cache_k, cache_elems) && s.download(cache_v, (uint16_t*)d.cache_v, cache_elems);
+    return ok ? RIBN_B200_OK : RIBN_B200_ERROR;
+}
+
 int ribn_b200_op_dequantize(int32_t device, int32_t type, const void* bytes, int64_t rows, int64_t cols, float* out) {
     const size_t n = encoded_bytes(type, rows, cols);
     if (n == 0 || bytes == nullptr || out == nullptr) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
@@ -308,7 +422,9 @@ int ribn_b200_op_attention(int32_t device, const float* q, const uint16_t* keys,
                                     head_dim, window, d_o));
     } else {
         const size_t spans = ((size_t)tokens + kAttnSpanKeys - 1) / kAttnSpanKeys;
-        const size_t bytes = (size_t)rows * q_heads * spans * (head_dim + 2) * sizeof(float);
+        // span accumulators for every row when that is small, else 256 MiB (the rows then run in several launches)
+        const size_t per_row = (size_t)q_heads * spans * (head_dim + 2) * sizeof(float);
+        const size_t bytes = std::max(per_row, std::min(per_row * (size_t)rows, (size_t)256 << 20));
         float* d_partial = s.alloc<float>(bytes / sizeof(float));
         OP_PTR(d_partial);
         OP_TRY(launch_attention(s.stream, d_q, d_k, d_v, d_table, pages, d_seq, d_pos, rows, q_heads, kv_heads,

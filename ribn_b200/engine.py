@@ -5,8 +5,10 @@ sees — decode rows first, then prefill chunks, under a token budget, with a
 forced prefill after ``max_decode_only_steps`` decode-only steps
 (crates/runtime/src/engine/scheduling.rs:6-96), one batch in flight
 (crates/runtime/src/engine.rs:344-398), whole-batch validation before any
-commit (crates/runtime/src/engine/completion.rs:45-131) — and nothing else of
-the runtime (no mailboxes, credits, cancellation or driver thread)."""
+commit (crates/runtime/src/engine/completion.rs:45-131), the pre-submit
+negotiation over the offered rows with parked (deferred) sequences
+(crates/runtime/src/engine/preparation.rs:5-140) — and nothing else of the
+runtime (no mailboxes, credits, cancellation or driver thread)."""
 from __future__ import annotations
 
 import time
@@ -51,6 +53,7 @@ class _Slot:
     finish: Optional[str] = None
     enqueue_time: float = 0.0
     token_times: List[float] = field(default_factory=list)
+    parked_epoch: int = -1
 
 
 class Engine:
@@ -67,6 +70,8 @@ class Engine:
         self.waiting: Deque[int] = deque()
         self.prefill: Deque[int] = deque()
         self.decode: Deque[int] = deque()
+        self.parked: Deque[int] = deque()   # rows the executor deferred: offered again after a release
+        self.resource_epoch = 0             # bumped by every release (the ReadinessWait's `changed`)
         self.slots: Dict[int, _Slot] = {}
         self.finished: Dict[int, _Slot] = {}
         self.decode_only_steps = 0
@@ -86,10 +91,11 @@ class Engine:
         return rid
 
     def active(self) -> int:
-        return len(self.prefill) + len(self.decode) + (len(self.in_flight[2]) if self.in_flight else 0)
+        return (len(self.prefill) + len(self.decode) + len(self.parked)
+                + (len(self.in_flight[2]) if self.in_flight else 0))
 
     def idle(self) -> bool:
-        return not (self.waiting or self.prefill or self.decode or self.in_flight)
+        return not (self.waiting or self.prefill or self.decode or self.parked or self.in_flight)
 
     # -- one step -------------------------------------------------------------
     def step(self) -> bool:
@@ -105,14 +111,19 @@ class Engine:
                     return False
                 self._commit(done)
                 progressed = True
+            self._reactivate_parked()
             self._admit_waiters()
             batch, keys = self._build_batch()
             if batch:
-                self.model.prepare(batch)
+                batch, keys = self._prepare(batch, keys)
+            if batch:
                 sid = self.model.submit(batch)
                 self.in_flight = (sid, batch, keys)
                 self._record(batch)
                 self.steps += 1
+                progressed = True
+            elif self.parked and self.in_flight is None and not (self.prefill or self.decode):
+                self._unblock_parked()
                 progressed = True
         except ExecutionError:
             self.faulted = True  # fault_all, crates/runtime/src/engine.rs:578-594
@@ -124,6 +135,68 @@ class Engine:
             self.step()
 
     # -- internals --------------------------------------------------------------
+    def _prepare(self, batch, keys):
+        """Engine::prepare_batch (preparation.rs:5-86): Ready keeps the batch; Selected keeps its ready rows
+        (with the granted budgets), parks the deferred ones and fails the rejected ones."""
+        negotiate = getattr(self.model, "prepare_rows", None)
+        prepared = negotiate(batch) if negotiate else self.model.prepare(batch)
+        if prepared == "ready":
+            return batch, keys
+        if len(prepared) != len(batch):
+            self.model.abandon_preparation()
+            raise ExecutionError("preparation does not match its offered rows or budgets")
+        kept, kept_keys = [], []
+        for row, offered, rid in zip(prepared, batch, keys):
+            s = self.slots[rid]
+            if row.state == "ready":
+                it = row.item
+                end = it.prefix + it.token_budget
+                ok = (it.sequence == offered.sequence and it.kind == offered.kind and it.prefix == offered.prefix
+                      and 0 < it.token_budget <= offered.token_budget and it.output_budget <= offered.output_budget)
+                if it.kind == StepKind.PREFILL:
+                    ok = ok and end <= s.prompt_tokens and it.output_budget == int(end == s.prompt_tokens)
+                else:
+                    ok = ok and it.output_budget == it.token_budget
+                if not ok:
+                    self.model.abandon_preparation()
+                    raise ExecutionError("preparation does not match its offered rows or budgets")
+                kept.append(it)
+                kept_keys.append(rid)
+            elif row.state == "deferred":
+                s.parked_epoch = self.resource_epoch
+                self.parked.append(rid)
+            else:
+                self._finish(rid, "failed: rejected at preparation")
+        if not kept:
+            self.model.abandon_preparation()
+        return kept, kept_keys
+
+    def _reactivate_parked(self):
+        """reactivate_parked (preparation.rs:118-140): a parked row returns to its queue once the resource it
+        waits for has changed (here: any release since it was parked)."""
+        for _ in range(len(self.parked)):
+            rid = self.parked.popleft()
+            s = self.slots[rid]
+            if s.parked_epoch == self.resource_epoch:
+                self.parked.append(rid)
+                continue
+            (self.prefill if s.prefix < s.prompt_tokens else self.decode).append(rid)
+
+    def _unblock_parked(self):
+        """Every live sequence is parked and nothing is in flight, so no release can come: the most recently
+        admitted one gives its pages back (it fails with a resource diagnostic) and the others are offered again.
+        The reference leaves this policy to the executor's ReadinessWait source."""
+        victim = max(self.parked)
+        self.parked.remove(victim)
+        self._finish(victim, "failed: KV arena exhausted")
+
+    def _finish(self, rid, reason):
+        s = self.slots[rid]
+        s.finish = reason
+        self.model.release(s.sequence)
+        self.resource_epoch += 1
+        self.finished[rid] = self.slots.pop(rid)
+
     def _admit_waiters(self):
         for _ in range(len(self.waiting)):
             if self.active() >= self.config.max_active_requests:
@@ -213,9 +286,7 @@ class Engine:
                     reason = "length"
                     break
             if reason:
-                s.finish = reason
-                self.model.release(s.sequence)
-                self.finished[rid] = self.slots.pop(rid)
+                self._finish(rid, reason)
             elif s.prefix < s.prompt_tokens:
                 self.prefill.append(rid)
             else:

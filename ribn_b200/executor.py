@@ -17,7 +17,7 @@ from typing import List, Optional, Sequence
 import numpy as np
 
 from . import _lib
-from ._lib import BatchItemC, CompletionC, Config, Limits, lib
+from ._lib import BatchItemC, CompletionC, Config, Limits, PreparedRowC, SamplingC, lib
 
 
 class ExecutionError(RuntimeError):
@@ -36,6 +36,23 @@ class BatchItem:
     prefix: int
     token_budget: int
     output_budget: int
+
+
+@dataclass(frozen=True)
+class Sampling:
+    """TokenRequest.options.sampling (temperature 0 = greedy; anything else is rejected, as in the
+    reference: crates/qwen/src/execution.rs:107-111)."""
+    temperature: float = 0.0
+    top_p: float = 1.0
+    top_k: int = 0
+    seed: int = 0
+
+
+@dataclass(frozen=True)
+class PreparedRow:
+    """PreparedRow::{Ready(item), Deferred, Rejected} (crates/runtime/src/executor.rs:97-105)."""
+    state: str                      # "ready" | "deferred" | "rejected"
+    item: Optional[BatchItem] = None   # the granted row (budgets may have shrunk) when ready
 
 
 @dataclass(frozen=True)
@@ -151,11 +168,13 @@ class QwenB200:
         return lim.kv_pages_total, lim.kv_pages_free
 
     def admit(self, request_id: int, sequence: int, tokens: Sequence[int], max_output_tokens: int,
-              temperature: float = 0.0, stop_tokens: Sequence[int] = ()) -> Admission:
+              temperature: float = 0.0, stop_tokens: Sequence[int] = (), sampling: Optional[Sampling] = None) -> Admission:
         toks = np.ascontiguousarray(tokens, dtype=np.uint32)
         stops = np.ascontiguousarray(stop_tokens, dtype=np.uint32)
+        sm = sampling or Sampling(temperature=temperature)
+        sc = SamplingC(sm.temperature, sm.top_p, sm.top_k, 0, sm.seed)
         rc = lib().ribn_b200_admit(self._h, request_id, sequence, toks.ctypes.data_as(C.c_void_p), toks.size,
-                                   max_output_tokens, temperature,
+                                   max_output_tokens, C.byref(sc),
                                    stops.ctypes.data_as(C.c_void_p) if stops.size else None, stops.size)
         if rc == _lib.OK:
             return Admission(Admission.READY)
@@ -169,6 +188,29 @@ class QwenB200:
         """Returns "ready" (BatchPreparation::Ready); raises on Err."""
         self._check(lib().ribn_b200_prepare(self._h, _items(batch), len(batch)))
         return "ready"
+
+    def prepare_rows(self, batch: Sequence[BatchItem]):
+        """prepare() with the per-row report: returns "ready" (BatchPreparation::Ready) or a list with one
+        :class:`PreparedRow` per offered row (BatchPreparation::Selected); raises on Err."""
+        rows = (PreparedRowC * max(len(batch), 1))()
+        rc = lib().ribn_b200_prepare_rows(self._h, _items(batch), len(batch), rows)
+        if rc == _lib.OK:
+            return "ready"
+        if rc != _lib.SELECTED:
+            raise ExecutionError(self._err())
+        out = []
+        for it, r in zip(batch, rows):
+            if r.state == _lib.ROW_READY:
+                out.append(PreparedRow("ready", BatchItem(it.sequence, it.kind, it.prefix, r.token_budget, r.output_budget)))
+            else:
+                out.append(PreparedRow("deferred" if r.state == _lib.ROW_DEFERRED else "rejected"))
+        return out
+
+    def debug_inject(self, kind: int, value: int) -> None:
+        self._check(lib().ribn_b200_debug_inject(self._h, kind, value))
+
+    def debug_wait_expiry(self, spin_limit: int = 4096) -> None:
+        self._check(lib().ribn_b200_debug_wait_expiry(self._h, spin_limit))
 
     def abandon_preparation(self) -> None:
         self._check(lib().ribn_b200_abandon_preparation(self._h))

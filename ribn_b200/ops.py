@@ -31,6 +31,63 @@ def dequantize(ggml_type: int, encoded, rows: int, cols: int, device: int = 0) -
     return out
 
 
+def unpack(ggml_type: int, packed, rows: int, cols: int, device: int = 0) -> np.ndarray:
+    """Decode FROM the tile-major packed form (output of :func:`repack`) on the device."""
+    pk = np.ascontiguousarray(packed).view(np.uint8).reshape(-1)
+    out = np.empty((rows, cols), dtype=np.float32)
+    _check(lib().ribn_b200_debug_unpack(device, ggml_type, _p(pk), rows, cols, _p(out)), "unpack")
+    return out
+
+
+def embedding(ggml_type: int, table, vocab: int, hidden: int, tokens, device: int = 0) -> np.ndarray:
+    t = np.ascontiguousarray(table).view(np.uint8).reshape(-1)
+    ids = np.ascontiguousarray(tokens, dtype=np.uint32)
+    out = np.empty((ids.size, hidden), dtype=np.float32)
+    _check(lib().ribn_b200_op_embedding(device, ggml_type, _p(t), vocab, hidden, _p(ids), ids.size, _p(out)), "embedding")
+    return out
+
+
+def qk_norm_rope_append(q, k, v, q_norm, k_norm, positions, kv_slots, q_heads: int, kv_heads: int, head_dim: int,
+                        rope_base: float, eps: float, cache_k, cache_v, device: int = 0):
+    """Returns (q, k, cache_k, cache_v) after per-head RMSNorm, NeoX rotary and the F16 cache append."""
+    q = np.ascontiguousarray(q, dtype=np.float32).copy()
+    k = np.ascontiguousarray(k, dtype=np.float32).copy()
+    v = np.ascontiguousarray(v, dtype=np.float32)
+    qn = np.ascontiguousarray(q_norm, dtype=np.float32)
+    kn = np.ascontiguousarray(k_norm, dtype=np.float32)
+    pos = np.ascontiguousarray(positions, dtype=np.int32)
+    slots = np.ascontiguousarray(kv_slots, dtype=np.int32)
+    ck = np.ascontiguousarray(cache_k, dtype=np.uint16).copy()
+    cv = np.ascontiguousarray(cache_v, dtype=np.uint16).copy()
+    physical = ck.size // (kv_heads * head_dim)
+    _check(lib().ribn_b200_op_qk_norm_rope_append(device, _p(q), _p(k), _p(v), _p(qn), _p(kn), _p(pos), _p(slots),
+                                                  pos.size, q_heads, kv_heads, head_dim, rope_base, eps, _p(ck), _p(cv),
+                                                  physical), "qk_norm_rope_append")
+    return q, k, ck, cv
+
+
+def attention_decode(q, k, v, q_norm, k_norm, rope_base: float, eps: float, cache_k, cache_v, page_tables, positions,
+                     q_heads: int, kv_heads: int, head_dim: int, device: int = 0):
+    """The decode step's fused norm + rotary + append + attention, one new token per sequence.
+    Returns (out [members][q_heads * head_dim], cache_k, cache_v)."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    k = np.ascontiguousarray(k, dtype=np.float32)
+    v = np.ascontiguousarray(v, dtype=np.float32)
+    qn = np.ascontiguousarray(q_norm, dtype=np.float32)
+    kn = np.ascontiguousarray(k_norm, dtype=np.float32)
+    ck = np.ascontiguousarray(cache_k, dtype=np.uint16).copy()
+    cv = np.ascontiguousarray(cache_v, dtype=np.uint16).copy()
+    tables = np.ascontiguousarray(page_tables, dtype=np.int32)
+    pos = np.ascontiguousarray(positions, dtype=np.int32)
+    members = pos.size
+    physical = ck.size // (kv_heads * head_dim)
+    out = np.empty((members, q_heads * head_dim), dtype=np.float32)
+    _check(lib().ribn_b200_op_attention_decode(device, _p(q), _p(k), _p(v), _p(qn), _p(kn), rope_base, eps, _p(ck), _p(cv),
+                                               physical, _p(tables), tables.shape[1], _p(pos), members, q_heads, kv_heads,
+                                               head_dim, _p(out)), "attention_decode")
+    return out, ck, cv
+
+
 def gemv(ggml_type: int, weights, rows: int, cols: int, x, variant: int = 0, device: int = 0) -> np.ndarray:
     w = np.ascontiguousarray(weights).view(np.uint8).reshape(-1)
     x = np.ascontiguousarray(x, dtype=np.float32)

@@ -7,8 +7,8 @@ from dataclasses import dataclass, field
 import pytest
 
 from ribn_b200.engine import Engine, EngineConfig, SchedulePolicy, TokenRequest
-from ribn_b200.executor import (Admission, ExecutionError, ExecutorInfo, GenerationLimits, StepCompletion,
-                                StepKind)
+from ribn_b200.executor import (Admission, BatchItem, ExecutionError, ExecutorInfo, GenerationLimits, PreparedRow,
+                                StepCompletion, StepKind)
 
 
 @dataclass
@@ -182,3 +182,72 @@ def test_policy_must_fit_executor_limits():
         Engine(Fake(Control(), max_batch_tokens=32), EngineConfig(2), SchedulePolicy(64, 16, 1, 8))
     with pytest.raises(ValueError):
         Engine(Fake(Control(), max_sequences=2), EngineConfig(4), SchedulePolicy(32, 16, 1, 8))
+
+
+class PagedFake(Fake):
+    """A fake whose `prepare_rows` negotiates 16-token pages from a small pool the way the executor does:
+    a row that needs more pages than are free is deferred (or, for a prefill row, shortened)."""
+
+    def __init__(self, control, pages):
+        super().__init__(control)
+        self.free, self.held = pages, {}
+
+    def admit(self, request_id, sequence, tokens, max_output_tokens, temperature=0.0, stop_tokens=()):
+        self.held[sequence] = 0
+        return Admission(Admission.READY)
+
+    def prepare_rows(self, batch):
+        assert self.pending is None and self.prepared is None
+        rows, unchanged = [], True
+        for it in batch:
+            need = -(-(it.prefix + it.token_budget) // 16) - self.held[it.sequence]
+            if need <= self.free:
+                self.free -= max(need, 0)
+                self.held[it.sequence] += max(need, 0)
+                rows.append(PreparedRow("ready", it))
+                continue
+            unchanged = False
+            fits = (self.held[it.sequence] + self.free) * 16
+            if it.kind == StepKind.PREFILL and fits > it.prefix:
+                self.held[it.sequence] += self.free
+                self.free = 0
+                rows.append(PreparedRow("ready", BatchItem(it.sequence, it.kind, it.prefix, fits - it.prefix, 0)))
+            else:
+                rows.append(PreparedRow("deferred"))
+        self.prepared = [r.item for r in rows if r.state == "ready"]
+        return "ready" if unchanged else rows
+
+    def abandon_preparation(self):
+        self.prepared = None
+
+    def release(self, sequence):
+        super().release(sequence)
+        self.free += self.held.pop(sequence)
+
+
+def test_deferred_rows_are_parked_and_offered_again_after_a_release():
+    c = Control()
+    fake = PagedFake(c, pages=3)
+    e = Engine(fake, EngineConfig(max_active_requests=4), SchedulePolicy(64, 32, 1, 8))
+    a = e.enqueue(TokenRequest(list(range(20)), 2))     # 2 pages for the prompt, decode stays inside them
+    b = e.enqueue(TokenRequest(list(range(30)), 2))     # needs 2 pages: only 1 is free at first
+    run(e)
+    assert e.finished[a].finish == "length" and e.finished[b].finish == "length"
+    first = c.batches[0]
+    assert [(it.sequence, it.token_budget, it.output_budget) for it in first] == [(a, 20, 1), (b, 16, 0)]  # b shortened
+    # b's remaining 14 prompt tokens waited (parked) until a finished and gave its pages back
+    later = [it for batch in c.batches[1:] for it in batch if it.sequence == b and it.kind == StepKind.PREFILL]
+    assert [(it.prefix, it.token_budget, it.output_budget) for it in later] == [(16, 14, 1)]
+    assert fake.free == 3 and not e.parked
+
+
+def test_a_pool_that_can_never_serve_every_sequence_fails_the_newest_one():
+    c = Control()
+    fake = PagedFake(c, pages=2)
+    e = Engine(fake, EngineConfig(max_active_requests=4), SchedulePolicy(64, 16, 1, 8))
+    a = e.enqueue(TokenRequest(list(range(16)), 40))    # grows to 4 pages: can never finish beside b
+    b = e.enqueue(TokenRequest(list(range(16)), 40))
+    run(e)
+    assert sorted([e.finished[a].finish, e.finished[b].finish]) == ["failed: KV arena exhausted"] * 2 or \
+        "failed: KV arena exhausted" in (e.finished[a].finish, e.finished[b].finish)
+    assert fake.free == 2 and e.idle()

@@ -370,3 +370,158 @@ def test_batched_decode_graph_replay_changes_no_bit(model):
         assert tok_a == tok_b
         for a, b in zip(log_a, log_b):
             assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_release_of_prepared_and_in_flight_sequences(model):
+    """release() refuses a sequence named by the outstanding preparation ("cannot release prepared Qwen
+    state", crates/qwen/src/execution.rs:416-426) and parks one the pending submission still reads until
+    that submission completes (crates/nvidia/src/serving.rs:1082-1096)."""
+    from ribn_b200 import BatchItem, ExecutionError, StepKind
+    tensors, _ = model
+    ex = build(MID, tensors, context_tokens=64, max_sequences=2, max_batch_tokens=32)
+    total, _ = ex.kv_pages()
+    assert ex.admit(1, 1, [3, 4, 5, 6], 4).ready and ex.admit(2, 2, [7, 8], 4).ready
+    items = [BatchItem(1, StepKind.PREFILL, 0, 4, 1), BatchItem(2, StepKind.PREFILL, 0, 2, 1)]
+    ex.prepare(items)
+    with pytest.raises(ExecutionError, match="cannot release prepared"):
+        ex.release(1)
+    sid = ex.submit(items)                     # the prepared rows are intact: the step runs
+    ex.release(2)                              # in flight: parked, no error
+    assert ex.kv_pages()[1] < total            # ... and its pages are still held
+    with pytest.raises(ExecutionError, match="duplicate"):
+        ex.admit(9, 2, [1], 1)                 # the identity stays taken until the release is drained
+    done = ex.wait(sid)
+    assert [d.sequence for d in done] == [1, 2] and all(len(d.tokens) == 1 for d in done)
+    ex.release(1)
+    assert ex.kv_pages() == (total, total)     # the parked release was drained at poll
+    assert ex.admit(9, 2, [1], 1).ready
+    ex.release(2); ex.release(2)
+    ex.close()
+
+
+def test_prepare_rows_defers_the_row_the_arena_cannot_serve(model):
+    """KV pages on demand (RIBN_B200_FLAG_KV_ON_DEMAND): admission holds the prompt's pages only, prepare
+    takes what a row's range needs, and a batch the arena cannot serve whole comes back as
+    BatchPreparation::Selected: one row of three is Deferred, the other two run, and the deferred row
+    runs once a release has returned pages."""
+    import ribn_b200
+    from ribn_b200 import BatchItem, ExecutionError, StepKind
+    tensors, oracle = model
+    ex = build(MID, tensors, flags=ribn_b200.FLAG_KV_ON_DEMAND, context_tokens=64, max_sequences=3, max_batch_tokens=48,
+               kv_pages=4)
+    prompts = {1: list(range(10, 26)), 2: list(range(40, 56)), 3: list(range(70, 86))}      # one page each
+    for s, p in prompts.items():
+        assert ex.admit(s, s, p, 8).ready
+    assert ex.kv_pages() == (4, 1)
+    items = [BatchItem(s, StepKind.PREFILL, 0, 16, 1) for s in prompts]
+    assert ex.prepare_rows(items) == "ready"                                    # inside the pages held: unchanged
+    tokens = {d.sequence: d.tokens[0] for d in ex.wait(ex.submit(items))}
+    decode = [BatchItem(s, StepKind.DECODE, 16, 1, 1) for s in prompts]           # position 16: a second page each
+    with pytest.raises(ExecutionError, match="prepare_rows"):
+        ex.prepare(decode)                                                       # the plain call cannot say "Selected"
+    ex.abandon_preparation()
+    rows = ex.prepare_rows(decode)
+    assert [r.state for r in rows] == ["ready", "deferred", "deferred"] and rows[0].item == decode[0]
+    done = ex.wait(ex.submit([decode[0]]))
+    assert done[0].sequence == 1 and done[0].prefix == 17
+    # the oracle agrees with what sequence 1 generated
+    seq = oracle.new_sequence()
+    for t in prompts[1][:-1]:
+        seq.step(t, want_logits=False)
+    assert orc.argmax(seq.step(prompts[1][-1])) == tokens[1]
+    assert orc.argmax(seq.step(tokens[1])) == done[0].tokens[0]
+    seq.close()
+    ex.release(1)                                                                # two pages come back
+    rows = ex.prepare_rows(decode[1:])
+    assert rows == "ready"
+    done = ex.wait(ex.submit(decode[1:]))
+    assert [d.sequence for d in done] == [2, 3]
+    # admission holds the prompt's pages, so a prompt the arena cannot hold now is deferred at admit
+    ex.release(2); ex.release(3)
+    assert ex.admit(4, 4, list(range(48)), 4).ready
+    assert ex.admit(5, 5, list(range(32)), 4).state == "deferred" and ex.kv_pages() == (4, 1)
+    ex.close()
+
+
+def test_engine_runs_more_requests_than_the_arena_holds_at_once(model):
+    """With pages on demand the engine keeps every request moving through a pool that could not hold
+    their full envelopes together; outputs equal those of an executor with a roomy arena."""
+    import ribn_b200
+    tensors, _ = model
+    rng = np.random.default_rng(8)
+    prompts = [rng.integers(0, MID["vocab"], size=n).tolist() for n in (20, 33, 9, 40)]
+    outputs = []
+    for flags, pages in ((0, 0), (ribn_b200.FLAG_KV_ON_DEMAND, 9)):
+        ex = build(MID, tensors, flags=flags, context_tokens=96, max_sequences=4, max_batch_tokens=64, kv_pages=pages)
+        engine = ribn_b200.Engine(ex, ribn_b200.EngineConfig(max_active_requests=4),
+                                  ribn_b200.SchedulePolicy(max_batch_tokens=64, prefill_chunk_tokens=32, decode_tokens=1,
+                                                           max_decode_only_steps=4))
+        ids = [engine.enqueue(ribn_b200.TokenRequest(p, 30)) for p in prompts]
+        engine.run_until_idle()
+        assert all(engine.finished[i].finish == "length" for i in ids)
+        outputs.append([engine.finished[i].output for i in ids])
+        total, free = ex.kv_pages()
+        assert total == free
+        ex.close()
+    assert outputs[0] == outputs[1]
+
+
+def test_bounded_wait_expiry_is_reported_and_leaves_the_context_usable(model):
+    """A kernel whose wait nothing ends gives up after its poll limit and leaves an error word; the next
+    poll reports it and faults the executor; a fresh executor in the same process then runs normally."""
+    from ribn_b200 import BatchItem, ExecutionError, StepKind
+    tensors, _ = model
+    ex = build(MID, tensors, context_tokens=64, max_sequences=1, max_batch_tokens=16)
+    assert ex.admit(1, 1, [5, 6, 7], 2).ready
+    ex.debug_wait_expiry(2048)                 # returns: the wait is bounded
+    item = BatchItem(1, StepKind.PREFILL, 0, 3, 1)
+    ex.prepare([item])
+    sid = ex.submit([item])
+    with pytest.raises(ExecutionError, match="bounded wait expired"):
+        ex.wait(sid)
+    with pytest.raises(ExecutionError, match="faulted"):
+        ex.prepare([item])
+    ex.close()
+    fresh = build(MID, tensors, context_tokens=64, max_sequences=1, max_batch_tokens=16)
+    assert fresh.admit(1, 1, [5, 6, 7], 2).ready
+    fresh.prepare([item])
+    done = fresh.wait(fresh.submit([item]))
+    assert len(done[0].tokens) == 1
+    fresh.close()
+
+
+@pytest.mark.parametrize("kind", ["alloc", "error_word", "bad_row"])
+def test_host_side_fault_injection_faults_the_executor(model, kind):
+    """Host-side injection in the library (no GPU fault): a refused device allocation, a planted error
+    word and a corrupted row record each come back as an ExecutionError with a diagnostic and leave the
+    executor faulted (the switches of crates/runtime/tests/contract.rs:12-31, one layer down)."""
+    import ribn_b200
+    from ribn_b200 import BatchItem, ExecutionError, StepKind
+    tensors, _ = model
+    if kind == "alloc":
+        ex = ribn_b200.QwenB200(MID, context_tokens=64, max_sequences=1, max_batch_tokens=16)
+        for name, (k, rows, cols, data) in tensors.items():
+            ex.load_tensor(name, k, rows, cols, data)
+        ex.debug_inject(ribn_b200.INJECT_ALLOC_REFUSAL, 1)
+        with pytest.raises(ExecutionError, match="out of memory"):
+            ex.finalize()
+        with pytest.raises(ExecutionError, match="faulted"):
+            ex.finalize()
+        ex.close()
+        return
+    ex = build(MID, tensors, context_tokens=64, max_sequences=1, max_batch_tokens=16)
+    assert ex.admit(1, 1, [5, 6, 7], 2).ready
+    item = BatchItem(1, StepKind.PREFILL, 0, 3, 1)
+    ex.prepare([item])
+    if kind == "error_word":
+        ex.debug_inject(ribn_b200.INJECT_ERROR_WORD, 7)
+        sid = ex.submit([item])
+        with pytest.raises(ExecutionError, match=r"bounded wait expired \(code 7\)"):
+            ex.wait(sid)
+    else:
+        ex.debug_inject(ribn_b200.INJECT_BAD_ROW, 1)
+        with pytest.raises(ExecutionError, match="malformed row record"):
+            ex.submit([item])
+    with pytest.raises(ExecutionError, match="faulted"):
+        ex.admit(2, 2, [1], 1)
+    ex.close()

@@ -216,3 +216,132 @@ def test_attention_large_launches_take_the_staged_span_kernel(ops, QH, KVH, HD, 
         seen = tokens - rows + 1 + r
         want = orc.attention(q[r], k[: seen * KVH * HD], v[: seen * KVH * HD], seen, QH, KVH, HD)
         assert np.max(np.abs(results[0][r] - want)) < 1e-4, r
+
+
+# ---- the packed layout decodes to the reference's values, bit for bit ------------------------------
+@pytest.mark.parametrize("kind", [H.Q8_0, H.Q4_K, H.Q6_K])
+@pytest.mark.parametrize("rows,cols", [(16, 256), (37, 768), (1, 512), (130, 1024)])
+def test_decode_from_packed_tiles_is_bit_exact(ops, kind, rows, cols):
+    """The tile-major repack keeps every bit: decoding FROM the packed tiles on the device (the weight
+    decoder of the decode-and-split tensor-memory kernel) equals dequantize_block on the raw blocks,
+    ragged row counts (padding rows of the last tile) included."""
+    elems, size = H.BLOCK[kind]
+    rng = np.random.default_rng(31 * kind + rows)
+    raw = rng.integers(0, 256, size=(rows * (cols // elems), size), dtype=np.uint8)
+    for off in ([0] if kind == H.Q8_0 else [0, 2] if kind == H.Q4_K else [208]):
+        raw[:, off + 1] &= 0x7B  # finite f16 scales, both signs
+    packed = ops.repack(kind, raw, rows, cols)
+    got = ops.unpack(kind, packed, rows, cols)
+    want = orc.dequantize_rows(kind, raw, rows, cols)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    enc = H.quantize(kind, rng.normal(0, 0.02, size=(rows, cols)).astype(np.float32))
+    got = ops.unpack(kind, ops.repack(kind, enc, rows, cols), rows, cols)
+    assert np.array_equal(got.view(np.uint32), orc.dequantize_rows(kind, enc, rows, cols).view(np.uint32))
+
+
+# ---- embedding rows: bit-exact (q4_k_embedding, crates/nvidia/src/kernels/quantized/q4_k.cu:1-60) ------
+@pytest.mark.parametrize("kind", [H.Q4_K, H.Q8_0, H.Q6_K])
+def test_embedding_rows_bit_exact(ops, kind):
+    vocab, hidden = 300, 512
+    rng = np.random.default_rng(40 + kind)
+    table = H.quantize(kind, rng.normal(0, 0.02, size=(vocab, hidden)).astype(np.float32))
+    tokens = np.array([0, 299, 17, 17, 128, 1, 254], dtype=np.uint32)
+    got = ops.embedding(kind, table, vocab, hidden, tokens)
+    want = orc.dequantize_rows(kind, table, vocab, hidden)[tokens]
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+# ---- per-head Q/K RMSNorm + rotary + F16 cache append (cuda_reference.rs:902-963, 1929-1972, 3368-3436) ------
+def _qk_reference(q, k, v, qn, kn, positions, QH, KVH, HD, base, eps):
+    """Oracle composition: per-head rms_norm with the shared weight, NeoX rotary, F16 bits of k and v."""
+    T = len(positions)
+    q2, k2 = np.empty_like(q), np.empty_like(k)
+    for t in range(T):
+        qh = np.concatenate([orc.rms_norm(q[t].reshape(QH, HD)[h], qn, eps) for h in range(QH)])
+        kh = np.concatenate([orc.rms_norm(k[t].reshape(KVH, HD)[h], kn, eps) for h in range(KVH)])
+        q2[t] = orc.rope_neox(qh, QH, HD, HD, base, int(positions[t]))
+        k2[t] = orc.rope_neox(kh, KVH, HD, HD, base, int(positions[t]))
+    return q2, k2, orc.f32_to_f16_bits(k2), orc.f32_to_f16_bits(v)
+
+
+def test_qk_norm_rope_append_against_oracle(ops):
+    QH, KVH, HD, T, base, eps = 8, 2, 128, 5, 1.0e6, 1.0e-6
+    rng = np.random.default_rng(61)
+    q = rng.normal(0, 1.5, size=(T, QH * HD)).astype(np.float32)
+    k = rng.normal(0, 1.5, size=(T, KVH * HD)).astype(np.float32)
+    v = rng.normal(0, 1.0, size=(T, KVH * HD)).astype(np.float32)
+    qn = (1.0 + rng.normal(0, 0.2, HD)).astype(np.float32)
+    kn = (1.0 + rng.normal(0, 0.2, HD)).astype(np.float32)
+    positions = np.array([0, 1, 77, 4097, 16383], dtype=np.int32)
+    slots = np.array([5, 0, 31, 18, 9], dtype=np.int32)
+    cache_k = rng.integers(0, 65536, size=(32, KVH * HD)).astype(np.uint16)
+    cache_v = rng.integers(0, 65536, size=(32, KVH * HD)).astype(np.uint16)
+    gq, gk, ck, cv = ops.qk_norm_rope_append(q, k, v, qn, kn, positions, slots, QH, KVH, HD, base, eps, cache_k, cache_v)
+    wq, wk, wkb, wvb = _qk_reference(q, k, v, qn, kn, positions, QH, KVH, HD, base, eps)
+    assert np.max(np.abs(gq - wq)) < 1e-5 and np.max(np.abs(gk - wk)) < 1e-5
+    assert np.array_equal(cv[slots], wvb)                               # v is rounded once: bit-exact
+    assert np.array_equal(ck[slots], orc.f32_to_f16_bits(gk))           # the rounding of the device's own k is exact
+    assert np.max(np.abs(ck[slots].view(np.float16).astype(np.float32) - wkb.view(np.float16).astype(np.float32))) < 4e-3
+    untouched = np.setdiff1d(np.arange(32), slots)
+    assert np.array_equal(ck[untouched], cache_k[untouched]) and np.array_equal(cv[untouched], cache_v[untouched])
+
+
+@pytest.mark.parametrize("members,context", [(1, 1000), (2, 333), (16, 600)], ids=["direct-1", "direct-2", "staged-16"])
+def test_fused_decode_attention_against_oracle(ops, members, context):
+    """The decode step's fused kernels (Q/K norm, rotary, cache append, split-KV attention) on their own:
+    one new token per sequence onto a cached context; appended rows and outputs against the oracle's."""
+    QH, KVH, HD, base, eps = 32, 8, 128, 1.0e6, 1.0e-6
+    rng = np.random.default_rng(70 + members)
+    pages_per = (context + 16) // 16 + 1
+    positions = np.array([context - 3 * m for m in range(members)], dtype=np.int32)
+    tables = rng.permutation(members * pages_per).astype(np.int32).reshape(members, pages_per)
+    physical = members * pages_per * 16
+    cache_k = np.zeros((physical, KVH * HD), dtype=np.uint16)
+    cache_v = np.zeros_like(cache_k)
+    hist_k = rng.normal(0, 1, size=(members, context, KVH * HD)).astype(np.float16)
+    hist_v = rng.normal(0, 1, size=(members, context, KVH * HD)).astype(np.float16)
+    for m in range(members):
+        for t in range(positions[m]):
+            row = tables[m, t // 16] * 16 + t % 16
+            cache_k[row] = hist_k[m, t].view(np.uint16)
+            cache_v[row] = hist_v[m, t].view(np.uint16)
+    q = rng.normal(0, 1.5, size=(members, QH * HD)).astype(np.float32)
+    k = rng.normal(0, 1.5, size=(members, KVH * HD)).astype(np.float32)
+    v = rng.normal(0, 1.0, size=(members, KVH * HD)).astype(np.float32)
+    qn = (1.0 + rng.normal(0, 0.2, HD)).astype(np.float32)
+    kn = (1.0 + rng.normal(0, 0.2, HD)).astype(np.float32)
+    out, ck, cv = ops.attention_decode(q, k, v, qn, kn, base, eps, cache_k, cache_v, tables, positions, QH, KVH, HD)
+    wq, wk, wkb, wvb = _qk_reference(q, k, v, qn, kn, positions, QH, KVH, HD, base, eps)
+    for m in range(members):
+        p = int(positions[m])
+        row = tables[m, p // 16] * 16 + p % 16
+        assert np.array_equal(cv[row], wvb[m])
+        got_k = ck[row].view(np.float16).astype(np.float32)
+        assert np.max(np.abs(got_k - wkb[m].view(np.float16).astype(np.float32))) < 4e-3   # one F16 step of |k| < 8
+        keys = np.concatenate([hist_k[m, :p].reshape(-1).view(np.uint16), ck[row]])
+        vals = np.concatenate([hist_v[m, :p].reshape(-1).view(np.uint16), cv[row]])
+        want = orc.attention(wq[m], keys, vals, p + 1, QH, KVH, HD)
+        assert np.max(np.abs(out[m] - want)) < 1e-3, m
+
+
+def test_prefill_chunk_attention_at_16k_context(ops):
+    """The chunked-prefill mix's largest shape: a 2048-token chunk onto a 14,336-token cached prefix
+    (Qwen3-8B head geometry); sampled rows against the oracle, first and last rows included."""
+    QH, KVH, HD, tokens, rows = 32, 8, 128, 16384, 2048
+    rng = np.random.default_rng(16384)
+    q = rng.normal(0, 1, size=(rows, QH * HD)).astype(np.float32)
+    k = rng.normal(0, 1, size=(tokens, KVH * HD)).astype(np.float16)
+    v = rng.normal(0, 1, size=(tokens, KVH * HD)).astype(np.float16)
+    pages = tokens // 16
+    table = rng.permutation(pages).astype(np.int32)
+    pk = np.empty((tokens, KVH * HD), dtype=np.uint16)
+    pv = np.empty_like(pk)
+    order = (table[np.arange(tokens) // 16] * 16 + np.arange(tokens) % 16)
+    pk[order] = k.view(np.uint16)
+    pv[order] = v.view(np.uint16)
+    got = ops.attention(q, pk, pv, table, tokens, rows, QH, KVH, HD, variant=0)
+    kb, vb = k.view(np.uint16).reshape(-1), v.view(np.uint16).reshape(-1)
+    for r in (0, 1, 511, 1024, 2046, 2047):
+        seen = tokens - rows + 1 + r
+        want = orc.attention(q[r], kb[: seen * KVH * HD], vb[: seen * KVH * HD], seen, QH, KVH, HD)
+        assert np.max(np.abs(got[r] - want)) < 1e-3, r

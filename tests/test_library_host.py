@@ -177,3 +177,11 @@ def test_compute_entry_points_fail_loudly_without_a_gpu(built_library):
         ribn_b200.QwenB200(H.TINY)
     with pytest.raises(RuntimeError, match="no usable CUDA device"):
         ribn_b200.ops.rms_norm(np.ones(4, np.float32), np.ones(4, np.float32), 1e-6)
+
+
+def test_create_rejects_a_context_beyond_the_attention_span_limit(built_library):
+    """context_tokens above 1024 spans x 64 keys is refused when the executor is created (before any
+    device is touched), not at the first step that would exceed the attention launcher's limit."""
+    import ribn_b200
+    with pytest.raises(ribn_b200.ExecutionError, match="65536"):
+        ribn_b200.QwenB200(H.TINY, context_tokens=65537, max_sequences=1, max_batch_tokens=16)

@@ -43,14 +43,22 @@ def test_noalloc_attention_matches_allocating_entry_point_twice(built_library):
         torch.cuda.synchronize()
         err = C.create_string_buffer(512)
         stream = torch.cuda.current_stream(dev).cuda_stream
+        before = torch.cuda.current_device()
         rc = lib().ribn_b200_attention_noalloc(0, C.c_void_p(stream), C.c_void_p(d_q.data_ptr()),
                                                C.c_void_p(d_k.data_ptr()), C.c_void_p(d_v.data_ptr()),
                                                C.c_void_p(d_table.data_ptr()), C.c_void_p(d_pos.data_ptr()), rows,
                                                tokens, qh, kvh, hd, window, C.c_void_p(d_out.data_ptr()), err, len(err))
         assert rc == 0, err.value.decode()
+        assert torch.cuda.current_device() == before   # the caller's current device is left as it was
         torch.cuda.synchronize()
         got = d_out.cpu().numpy()
         assert np.max(np.abs(got - want)) < TOLERANCE, (call, float(np.max(np.abs(got - want))))
+        if window == 0:
+            # ... and directly against the CPU oracle, for the last row (it sees every key)
+            from oracle import binding as orc
+            order = table[np.arange(tokens) // 16] * 16 + np.arange(tokens) % 16
+            ref = orc.attention(q[rows - 1], k[order].reshape(-1), v[order].reshape(-1), tokens, qh, kvh, hd)
+            assert np.max(np.abs(got[rows - 1] - ref)) < TOLERANCE
 
 
 def test_noalloc_attention_refuses_sizes_beyond_its_scratch(built_library):
