@@ -9,6 +9,9 @@ bandwidth).  Weights are seeded N(0, 0.02) quantised on the device; token ids
 and cached K/V are seeded synthetic; every step streams 4.9 GB of weights, far
 beyond L2, so no explicit L2 flush is needed between steps.
 
+The default line also carries a bounded serving leg (Poisson arrivals below saturation through the
+engine: p50 / p95 time to first token and inter-token latency) and the reduced Gemma-4 job.
+
 `--impl reference` times the reference's host CPU decoder (restated in
 oracle/oracle.c; the Rust original cannot be built here) on the same weights.
 """
@@ -248,8 +251,10 @@ def oracle_sequence(orc, oracle, ex, model, sequence: int, context: int):
     return seq
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one gate|up launch of gemv_mma_kernel (ncu capture).
+# dram__bytes_read.sum + dram__bytes_write.sum of one ffn gate|up launch of gemv_mma_kernel, from an ncu
+# capture of this kernel on the 4-layer model (the per-layer launch is the same at 36 layers).
 GATE_UP_DRAM_BYTES = {"qwen3-8b": 56982272, "qwen3-8b-4l": 56982272}
+REPEATS = 5   # the headline is the median over this many blocks of --steps steps
 
 
 def run_ours(args):
@@ -257,7 +262,7 @@ def run_ours(args):
     import ribn_b200
     model = MODELS[args.model]
     B = args.batch
-    total_steps = args.steps + args.warmup + 2
+    total_steps = REPEATS * args.steps + args.warmup + 2
     ex = build_executor(model, B, args.context, 2 * total_steps + 4, local, keep_logits=True)
     ex.finalize()
     seed_sequences(ex, model, B, args.context, 2 * total_steps + 4, seed=1 + rank)
@@ -287,25 +292,41 @@ def run_ours(args):
         cpu_s = time.perf_counter() - t0
         err = np.abs(got - want)
         parity = {"max_abs_logit_diff": float(err.max()), "argmax_equal": bool(orc.argmax(want) == done[0].tokens[0]),
-                  "tolerance": "max-abs 2e-2 / rel 1e-2"}
+                  "tolerance": "max-abs 2e-2 / rel 1e-2", "checked": "1 decode step at full size here; 256 greedy tokens and a "
+                  "batch-64 step at full size in tests/test_gpu_fullsize.py",
+                  "oracle": "CPU restatement pinned primitive by primitive; the reference has no end-to-end vector for dense Qwen3"}
         cpu = {"value": 1.0 / cpu_s, "unit": "tok/s", "cores": cores, "kind": "port",
-               "sample": f"1 decode token at batch 1, context {args.context}, {args.model} Q4_K_M-style, "
+               "sample": f"1 decode token at batch 1, context {args.context}, {args.model} {args.scheme.upper()}-style, "
                          f"oracle/oracle.c with OpenMP over output rows"}
+        # the reference's CPU decoder is single-threaded: the same token step on one thread
+        orc.set_threads(1)
+        t0 = time.perf_counter()
+        seq.step(orc.argmax(want))
+        cpu["single_thread"] = {"value": 1.0 / (time.perf_counter() - t0), "unit": "tok/s", "cores": 1,
+                                "sample": "the next decode token of the same sequence on one thread"}
+        orc.set_threads(cores)
         seq.close(); oracle.close()
 
-    def phase(sequences):
+    def phase(sequences, repeats):
+        """`repeats` blocks of exactly --steps steps, each bracketed by a barrier and timed on the device as the
+        maximum over ranks; the reported block is the median one (by device time)."""
         decode_steps(ex, sequences, positions, args.warmup)
-        barrier(dist, local)
+        blocks = []
         with ClockSampler(local) as clocks:
-            wall, device_ms, launches = decode_steps(ex, sequences, positions, args.steps)
-        barrier(dist, local)
-        wall = all_max(dist, wall, local)
-        dev = all_max(dist, sum(device_ms) / 1e3, local)
-        return wall, dev, launches, clocks.summary()  # both already the maximum over ranks
+            for _ in range(repeats):
+                barrier(dist, local)
+                wall, device_ms, launches = decode_steps(ex, sequences, positions, args.steps)
+                barrier(dist, local)
+                blocks.append((all_max(dist, sum(device_ms) / 1e3, local), all_max(dist, wall, local), launches))
+        blocks.sort()
+        dev, wall, launches = blocks[len(blocks) // 2]
+        spread = {"repeats": repeats, "ms_per_step_min": blocks[0][0] / args.steps * 1e3,
+                  "ms_per_step_max": blocks[-1][0] / args.steps * 1e3}
+        return wall, dev, launches, clocks.summary(), spread
 
     def step_roofline(batch_rows, dev_seconds):
         """Whole step: algorithmic bytes of one decode step over its device time (every kernel included)."""
-        ctx_avg = args.context + args.warmup + args.steps / 2.0
+        ctx_avg = args.context + args.warmup + REPEATS * args.steps / 2.0
         w_bytes, kv_bytes = ex.step_bytes(int(batch_rows * ctx_avg))
         per_step = w_bytes + kv_bytes
         achieved = per_step / (dev_seconds / args.steps) / 1e9
@@ -313,23 +334,31 @@ def run_ours(args):
                 "of": peak_kind, "algorithmic_bytes_per_step": per_step, "weight_bytes": w_bytes, "kv_bytes": kv_bytes}
 
     def kernel_roofline():
-        """The dominant kernel (gemv_mma_kernel, ~80 % of a batch-1 step) on its largest per-layer launch,
-        ffn gate|up: encoded weight bytes of one launch over its CUDA-event duration, timed live here."""
-        us, nbytes = ex.time_projection("gate_up", repeats=4 * model["layers"])
-        others = {}
-        for name in ("qkv", "attn_output", "down", "head"):
-            t_us, b = ex.time_projection(name, repeats=(8 if name == "head" else 2 * model["layers"]))
-            others[name] = {"us": t_us, "bytes": b, "GB/s": b / t_us / 1e3}
-        achieved = nbytes / us / 1e3
-        # DRAM bytes of the same launch from the ncu capture summarised in profiles/gemv_mma_gate_up_qwen3-8b.md
+        """The dominant kernel (gemv_mma_kernel: every projection of a batch-1 step) over ALL its launches of one
+        step: encoded weight bytes of the 4 x layers + 1 launches over the sum of their CUDA-event durations, each
+        launch kind timed live here on the executor's stream with weights streamed from HBM."""
+        L = model["layers"]
+        kinds = {}
+        for name in ("qkv", "attn_output", "gate_up", "down", "head"):
+            t_us, b = ex.time_projection(name, repeats=(8 if name == "head" else 2 * L))
+            count = 1 if name == "head" else L
+            kinds[name] = {"us": t_us, "bytes": b, "GB/s": b / t_us / 1e3, "frac": b / t_us / 1e3 / hbm_gbs,
+                           "launches_per_step": count}
+        total_bytes = sum(k["bytes"] * k["launches_per_step"] for k in kinds.values())
+        total_us = sum(k["us"] * k["launches_per_step"] for k in kinds.values())
+        launches = sum(k["launches_per_step"] for k in kinds.values())
+        achieved = total_bytes / total_us / 1e3
         traffic = GATE_UP_DRAM_BYTES.get(args.model) if args.scheme == "q4_k_m" else None
         return {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
-                "traffic": traffic, "of": peak_kind,
-                "kernel": "gemv_mma_kernel, ffn gate|up launch (2 x ffn x hidden, 1 row)",
-                "algorithmic_bytes_per_launch": nbytes, "us_per_launch": us, "other_launches": others}
+                "traffic": traffic, "traffic_of": "one ffn gate|up launch (ncu dram bytes; its algorithmic bytes are "
+                                                  f"{kinds['gate_up']['bytes']})",
+                "of": peak_kind,
+                "kernel": f"gemv_mma_kernel, byte-weighted over its {launches} launches of one batch-1 step",
+                "algorithmic_bytes_per_launch": total_bytes / launches, "us_per_launch": total_us / launches,
+                "algorithmic_bytes_per_step": total_bytes, "us_per_step": total_us, "other_launches": kinds}
 
     # ---- batch 1 -----------------------------------------------------------------------
-    wall1, dev1, launches1, clocks1 = phase([1])
+    wall1, dev1, launches1, clocks1, spread1 = phase([1], REPEATS)
     value1 = world * 1 * args.steps / dev1   # dev1 / wall1 are already the maximum over ranks
     e2e1 = world * 1 * args.steps / wall1
     out = {
@@ -344,21 +373,29 @@ def run_ours(args):
                    "parallelism": f"replicas x{world}"},
         "e2e": {"value": e2e1, "unit": "tok/s", "h2d_bytes_per_step": 32, "d2h_bytes_per_step": 4},
         "gpu_launches": launches1, "roofline": kernel_roofline(), "step_roofline": step_roofline(1, dev1),
-        "clocks": clocks1,
+        "clocks": clocks1, "spread": spread1,
     }
     if cpu:
         out["cpu_baseline"] = cpu
         out["parity"] = parity
     # ---- batch B -------------------------------------------------------------------------
     if B > 1:
-        wallb, devb, launchesb, clocksb = phase(list(range(1, B + 1)))
+        wallb, devb, launchesb, clocksb, spreadb = phase(list(range(1, B + 1)), 3)
         out["batch64"] = {"batch": B, "value": world * B * args.steps / devb, "unit": "tok/s",
                           "ms_per_step": devb / args.steps * 1e3,
                           "e2e": {"value": world * B * args.steps / wallb, "unit": "tok/s",
                                   "h2d_bytes_per_step": 32 * B, "d2h_bytes_per_step": 4 * B},
                           "gpu_launches": launchesb, "step_roofline": step_roofline(B, devb), "clocks": clocksb,
+                          "spread": spreadb,
                           "x_batch1": (world * B * args.steps / devb) / value1}
     ex.close()
+    if not args.no_serving:
+        # p50 time to first token is part of the metric: a bounded serving leg below saturation
+        srv = serving_job(args, rank, world, local, dist, n=args.serving_requests, rate=args.arrival_rate_default,
+                          workload="serving")
+        out["ttft_ms"], out["itl_ms"] = srv["ttft_ms"], srv["itl_ms"]
+        out["serving"] = {k: srv[k] for k in ("value", "unit", "prompt_tokens", "generated_tokens", "makespan_s", "clocks")}
+        out["serving"]["workload"] = srv["config"]["workload"]
     if world == 1 and not args.no_cpu and not args.no_gemma:
         # the reference's CPU-runnable configuration, as a second workload of the same library
         out["gemma_reduced"] = gemma_job(args, rank, world, local, dist, 3, 3, True)
@@ -369,19 +406,27 @@ def run_ours(args):
 
 
 def run_serving(args):
-    """Continuous batching under Poisson arrivals through the engine (scheduling rules of the reference's
-    Engine restated in ribn_b200/engine.py): prompts ~U[128, 2048], outputs ~U[64, 512], 64 active
-    requests, 2048-token prefill chunks, 16-token KV pages.  Reports whole-job generated tok/s and the
-    time to first token (planned arrival -> first token, as the reference's serving bench measures it)."""
+    """`--workload serving|mixed`: the serving job alone, one line."""
     rank, world, local, dist = dist_setup(args.gpus)
+    out = serving_job(args, rank, world, local, dist, n=args.requests, rate=args.arrival_rate, workload=args.workload)
+    if rank == 0:
+        print(json.dumps(out))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def serving_job(args, rank, world, local, dist, n, rate, workload):
+    """Continuous batching through the engine (scheduling rules of the reference's Engine restated in
+    ribn_b200/engine.py).  serving: Poisson arrivals, prompts ~U[128, 2048], outputs ~U[64, 512], up to 64 active
+    requests, 2048-token prefill chunks, 16-token KV pages.  mixed: 32 long prompts (log-uniform 512 .. 16384,
+    chunk 2048) interleaved with 32 decode-heavy requests at context 1024 .. 4096, all queued at time zero.
+    Reports whole-job generated tok/s, the time to first token (planned arrival -> first token, as the
+    reference's serving bench measures it) and the gaps between a request's successive tokens."""
     import ribn_b200
     from ribn_b200.engine import Engine, EngineConfig, SchedulePolicy, TokenRequest
     model = MODELS[args.model]
     rng = np.random.default_rng(0xC3 + rank)
-    n = args.requests
-    if args.workload == "mixed":
-        # chunked-prefill mix: half the requests are long prompts (log-uniform 512 .. 16384 tokens, 8 outputs), the
-        # other half decode-heavy (context U[1024, 4096], 256 outputs); everything is queued at time zero
+    if workload == "mixed":
         long_n = n // 2
         prompt_hi = args.serving_prompt_max if args.serving_prompt_max > 2048 else 16384
         prompts = np.concatenate([np.exp(rng.uniform(np.log(512), np.log(prompt_hi), size=long_n)).astype(np.int64),
@@ -396,15 +441,15 @@ def run_serving(args):
         prompt_hi = min(2048, args.serving_prompt_max)
         prompts = rng.integers(min(128, prompt_hi), prompt_hi + 1, size=n)
         outputs = rng.integers(min(64, args.serving_output_max), args.serving_output_max + 1, size=n)
-        arrivals = np.cumsum(rng.exponential(1.0 / args.arrival_rate, size=n))
-        described = (f"Poisson arrivals {args.arrival_rate}/s, prompts U[{min(128, prompt_hi)},{prompt_hi}], outputs "
+        arrivals = np.cumsum(rng.exponential(1.0 / rate, size=n))
+        described = (f"Poisson arrivals {rate}/s, prompts U[{min(128, prompt_hi)},{prompt_hi}], outputs "
                      f"U[{min(64, args.serving_output_max)},{args.serving_output_max}]")
     active = min(64, n)
     chunk = min(2048, int(prompts.max()))
     pages = int(sum((int(p) + int(o) + 15) // 16 for p, o in zip(prompts, outputs))) + active
     ex = ribn_b200.QwenB200(model, context_tokens=int((prompts + outputs).max() + 16), max_sequences=active,
                             max_batch_tokens=chunk + active, kv_pages=pages, device=local, flags=0)
-    ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q4_K_M)
+    ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q8_0 if SCHEME == "q8_0" else ribn_b200.SCHEME_Q4_K_M)
     ex.finalize()
     engine = Engine(ex, EngineConfig(max_active_requests=active, max_queued_requests=n),
                     SchedulePolicy(max_batch_tokens=chunk + active, prefill_chunk_tokens=chunk, decode_tokens=1,
@@ -433,25 +478,24 @@ def run_serving(args):
             itl.extend(np.diff(slot.token_times).tolist())
     makespan = all_max(dist, makespan, local)
     out = {
-        "metric": f"{args.model} Q4_K_M continuous-batching generated tok/s (per GPU x replicas)",
+        "metric": f"{args.model} {args.scheme.upper()} continuous-batching generated tok/s (per GPU x replicas)",
         "value": world * generated / makespan, "unit": "tok/s", "n_gpus": world, "steps": engine.steps, "warmup": 0,
         "ms_per_step": makespan / max(engine.steps, 1) * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None,
         "dtype": "u8 x s8 / f16 tensor-core products over Q4_K,Q6_K weights, f32 scales and accumulation, f16 KV",
         "data": "synthetic",
-        "config": {"workload": f"{args.model} Q4_K_M-style {args.workload}: {n} requests per GPU, {described}, {active} active, "
+        "config": {"workload": f"{args.model} {args.scheme.upper()}-style {workload}: {n} requests per GPU, {described}, {active} active, "
                                f"{chunk}-token prefill chunks, 16-token KV pages",
                    "parallelism": f"replicas x{world}"},
-        "ttft_ms": {"p50": float(np.percentile(ttft, 50) * 1e3), "p95": float(np.percentile(ttft, 95) * 1e3)},
+        "ttft_ms": {"p50": float(np.percentile(ttft, 50) * 1e3), "p95": float(np.percentile(ttft, 95) * 1e3),
+                    "definition": "planned arrival -> first token", "arrival_rate_per_s": rate if workload != "mixed" else None,
+                    "requests": n},
         "itl_ms": {"p50": float(np.percentile(itl, 50) * 1e3), "p95": float(np.percentile(itl, 95) * 1e3)} if itl else None,
         "prompt_tokens": int(prompts.sum()), "generated_tokens": int(generated), "makespan_s": makespan,
         "clocks": clocks.summary(),
     }
     ex.close()
-    if rank == 0:
-        print(json.dumps(out))
-    if dist is not None:
-        dist.destroy_process_group()
+    return out
 
 
 def run_gemma(args):
@@ -483,6 +527,8 @@ def gemma_job(args, rank, world, local, dist, steps, warmup, with_cpu):
     prompts = {i + 1: rng.integers(0, cfg["vocab"], n).tolist() for i, n in enumerate((17, 64, 129, 300))}
     new_tokens = args.gemma_new_tokens
 
+    decode_ms = []   # device time of the last job's decode steps with all four sequences
+
     def job():
         ex = ribn_b200.GemmaExecutor(model)
         for seq, p in prompts.items():
@@ -490,6 +536,7 @@ def gemma_job(args, rank, world, local, dist, steps, warmup, with_cpu):
         got = {seq: [] for seq in prompts}
         cursor = {seq: 0 for seq in prompts}
         launches, device_ms = 0, 0.0
+        decode_ms.clear()
         while any(len(got[q]) < new_tokens for q in prompts):
             batch = []
             for seq, p in prompts.items():
@@ -507,6 +554,8 @@ def gemma_job(args, rank, world, local, dist, steps, warmup, with_cpu):
             ms, n_launch = model.last_step_stats()
             launches += n_launch
             device_ms += ms
+            if len(batch) == 4 and all(it.kind == StepKind.DECODE for it in batch):
+                decode_ms.append(ms)
         ex.synchronize()
         return got, launches, device_ms
 
@@ -539,6 +588,22 @@ def gemma_job(args, rank, world, local, dist, steps, warmup, with_cpu):
         "gpu_launches": launches, "prompt_tokens": prompt_tokens, "generated_tokens": generated,
         "clocks": clocks.summary(),
     }
+    if decode_ms:
+        # one decode step of the four sequences: every BF16 matrix read once (the tied head included; the per-layer
+        # token table is only gathered) over the step's CUDA-event time
+        H, F, ple, L = cfg["hidden"], cfg["ffn"], cfg["ple"], cfg["layers"]
+        qd, kd = cfg["heads"] * cfg["head_dim"], cfg["kv_heads"] * cfg["head_dim"]
+        per_layer = 2 * qd * H + 2 * kd * H + 3 * F * H + 2 * ple * H
+        weight_bytes = 2 * (L * per_layer + cfg["vocab"] * H + L * ple * H)
+        step_ms = statistics.median(decode_ms)
+        hbm_gbs, peak_kind = measured_peaks()
+        achieved = weight_bytes / (step_ms / 1e3) / 1e9
+        out["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
+                           "of": peak_kind, "traffic": None,
+                           "kernel": "one decode step of four sequences (every kernel; gm_project_kernel is ~80 % of it)",
+                           "algorithmic_bytes_per_step": weight_bytes, "ms_per_step": step_ms,
+                           "note": "the projections add every FP32 sum in source order (bit parity with the host decoder), "
+                                   "which bounds them by latency, not by HBM"}
     if rank == 0 and tensors is not None:
         from oracle import gemma_binding as G
         oracle = G.GemmaOracle(cfg, tensors)
@@ -616,7 +681,11 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "serving", "mixed", "gemma"],
                     help="decode: steady batch-1 / batch-N decode steps (the headline); serving: Poisson arrivals through the engine; "
                          "mixed: long chunked prefills interleaved with decode-heavy requests; gemma: the reduced Gemma-4 BF16 job")
-    ap.add_argument("--requests", type=int, default=96, help="serving: requests per GPU")
+    ap.add_argument("--requests", type=int, default=None, help="requests per GPU (default: serving 96; mixed 64 = 32 long prompts + 32 decodes)")
+    ap.add_argument("--no-serving", action="store_true", help="decode: skip the bounded serving leg (time to first token)")
+    ap.add_argument("--serving-requests", type=int, default=32, help="decode: requests of the bounded serving leg")
+    ap.add_argument("--arrival-rate-default", type=float, default=4.0,
+                    help="decode: Poisson arrival rate of the bounded serving leg (below saturation), requests per second per GPU")
     ap.add_argument("--arrival-rate", type=float, default=8.0, help="serving: Poisson arrival rate, requests per second per GPU")
     ap.add_argument("--serving-prompt-max", type=int, default=2048)
     ap.add_argument("--serving-output-max", type=int, default=512)
@@ -628,6 +697,8 @@ def main():
     SCHEME = args.scheme
     if args.warmup < 3:
         args.warmup = 3
+    if args.requests is None:
+        args.requests = 64 if args.workload == "mixed" else 96
     if args.impl == "reference":
         run_reference(args)
     elif args.workload in ("serving", "mixed"):

@@ -450,15 +450,16 @@ def test_engine_runs_more_requests_than_the_arena_holds_at_once(model):
     tensors, _ = model
     rng = np.random.default_rng(8)
     prompts = [rng.integers(0, MID["vocab"], size=n).tolist() for n in (20, 33, 9, 40)]
+    budgets = (4, 30, 10, 20)       # envelopes of 2 + 4 + 2 + 4 = 12 pages; the prompts alone take 9
     outputs = []
-    for flags, pages in ((0, 0), (ribn_b200.FLAG_KV_ON_DEMAND, 9)):
+    for flags, pages in ((0, 0), (ribn_b200.FLAG_KV_ON_DEMAND, 10)):
         ex = build(MID, tensors, flags=flags, context_tokens=96, max_sequences=4, max_batch_tokens=64, kv_pages=pages)
         engine = ribn_b200.Engine(ex, ribn_b200.EngineConfig(max_active_requests=4),
                                   ribn_b200.SchedulePolicy(max_batch_tokens=64, prefill_chunk_tokens=32, decode_tokens=1,
                                                            max_decode_only_steps=4))
-        ids = [engine.enqueue(ribn_b200.TokenRequest(p, 30)) for p in prompts]
+        ids = [engine.enqueue(ribn_b200.TokenRequest(p, n)) for p, n in zip(prompts, budgets)]
         engine.run_until_idle()
-        assert all(engine.finished[i].finish == "length" for i in ids)
+        assert [engine.finished[i].finish for i in ids] == ["length"] * 4
         outputs.append([engine.finished[i].output for i in ids])
         total, free = ex.kv_pages()
         assert total == free
