@@ -39,6 +39,8 @@ MODELS = {
     # profiling aid: Qwen3-8B layer and head shapes, 4 layers (fits an ncu capture's size rule)
     "qwen3-8b-4l": dict(layers=4, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, ffn=12288, vocab=151936,
                         rope_base=1.0e6, rms_eps=1.0e-6),
+    "qwen3-32b": dict(layers=64, hidden=5120, q_heads=64, kv_heads=8, head_dim=128, ffn=25600, vocab=151936,
+                      rope_base=1.0e6, rms_eps=1.0e-6),
     "tiny": dict(layers=2, hidden=512, q_heads=8, kv_heads=2, head_dim=128, ffn=1024, vocab=2048,
                  rope_base=1.0e6, rms_eps=1.0e-6),
 }
@@ -498,6 +500,81 @@ def serving_job(args, rank, world, local, dist, n, rate, workload):
     return out
 
 
+def run_tp(args):
+    """Tensor-parallel decode (`--tp N`, one rank per GPU): the Qwen3-32B-class configuration.  Every rank holds one
+    shard of each layer (heads for q | k | v, columns for gate | up, K blocks for the attention output and ffn down
+    projections, kv heads for the cache) and the replicated head; the ranks' partial sums meet in an NCCL
+    all-reduce after o_proj and down_proj.  All ranks run the same schedule: `--batch` sequences at contexts
+    U[512, --context-max], one decode token per step.  Strong scaling: the model is fixed, N grows."""
+    rank, world, local, dist = dist_setup(args.gpus)
+    import torch
+    import ribn_b200
+    if world != args.tp:
+        raise SystemExit(f"--tp {args.tp} needs {args.tp} ranks (torchrun --nproc-per-node {args.tp}), got {world}")
+    model = MODELS[args.model]
+    B = args.batch
+    rng = np.random.default_rng(0xC5)                         # the same on every rank
+    contexts = rng.integers(512, args.context_max + 1, size=B)
+    steps_total = args.warmup + REPEATS * args.steps + 4
+    span = int(contexts.max()) + steps_total + 16
+    pages = int(sum((int(c) + steps_total + 16 + 15) // 16 for c in contexts)) + B
+    ex = ribn_b200.QwenB200(model, context_tokens=span, max_sequences=B, max_batch_tokens=max(B, 16), kv_pages=pages,
+                            device=local, flags=0, tp_size=world, tp_rank=rank)
+    ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q8_0 if SCHEME == "q8_0" else ribn_b200.SCHEME_Q4_K_M)
+    ids = [ribn_b200.tp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0)
+    ex.tp_init(ids[0])
+    ex.finalize()
+    positions = {}
+    for s in range(B):
+        prompt = rng.integers(0, model["vocab"], size=int(contexts[s]), dtype=np.uint32)
+        adm = ex.admit(s + 1, s + 1, prompt, steps_total + 8)
+        if not adm.ready:
+            raise RuntimeError(f"admission failed: {adm}")
+        ex.debug_set_context(s + 1, int(contexts[s]), int(rng.integers(0, model["vocab"])), seed=5000 + s)
+        positions[s + 1] = int(contexts[s])
+    sequences = list(range(1, B + 1))
+    hbm_gbs, peak_kind = measured_peaks()
+    decode_steps(ex, sequences, positions, args.warmup)
+    blocks = []
+    with ClockSampler(local) as clocks:
+        for _ in range(REPEATS):
+            barrier(dist, local)
+            wall, device_ms, launches = decode_steps(ex, sequences, positions, args.steps)
+            barrier(dist, local)
+            blocks.append((all_max(dist, sum(device_ms) / 1e3, local), all_max(dist, wall, local), launches))
+    blocks.sort()
+    dev, wall, launches = blocks[len(blocks) // 2]
+    ar_us = ex.tp_time_allreduce(B, 50)
+    w_bytes, kv_bytes = ex.step_bytes(int(contexts.sum()) + B * (args.warmup + REPEATS * args.steps // 2))
+    step_s = dev / args.steps
+    achieved = (w_bytes + kv_bytes) / step_s / 1e9
+    out = {
+        "metric": f"{args.model} {args.scheme.upper()} tensor-parallel decode tok/s (whole job, tp{world})",
+        "value": B * args.steps / dev, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16 x f16 tensor-core products over exact K-quant integers, f32 scales and accumulation, f16 KV, f32 all-reduce",
+        "data": "synthetic",
+        "config": {"workload": f"{args.model} {args.scheme.upper()}-style decode, {B} concurrent sequences, contexts U[512,{args.context_max}], "
+                               f"16-token KV pages, tensor parallel over {world} GPUs (NCCL all-reduce after o_proj and down_proj)",
+                   "l2": "inputs larger than L2", "parallelism": f"tp{world}"},
+        "e2e": {"value": B * args.steps / wall, "unit": "tok/s", "h2d_bytes_per_step": 32 * B, "d2h_bytes_per_step": 4 * B},
+        "gpu_launches": launches, "clocks": clocks.summary(),
+        "per_rank": {"weight_bytes": w_bytes, "kv_bytes_per_step": kv_bytes,
+                     "step_roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
+                                       "frac": achieved / hbm_gbs, "of": peak_kind}},
+        "all_reduce": {"us": ar_us, "per_step": 2 * model["layers"], "bytes": B * model["hidden"] * 4,
+                       "share_of_step": 2 * model["layers"] * ar_us * 1e-6 / step_s},
+        "spread": {"repeats": REPEATS, "ms_per_step_min": blocks[0][0] / args.steps * 1e3,
+                   "ms_per_step_max": blocks[-1][0] / args.steps * 1e3},
+    }
+    ex.close()
+    if rank == 0:
+        print(json.dumps(out))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def run_gemma(args):
     """The reduced Gemma-4 configuration (6 layers: 5 sliding-512 + 1 full; hidden 1152; 4 q / 1 kv heads of 256;
     GeGLU 6912; vocab 32768; BF16 random-init N(0, 0.02)): four prompts of 17 / 64 / 129 / 300 uniform-random
@@ -691,6 +768,8 @@ def main():
     ap.add_argument("--serving-output-max", type=int, default=512)
     ap.add_argument("--no-gemma", action="store_true", help="decode: skip the reduced Gemma-4 job appended to the default line")
     ap.add_argument("--gemma-new-tokens", type=int, default=32, help="gemma: greedy tokens per prompt")
+    ap.add_argument("--tp", type=int, default=0, help="tensor-parallel group size (= ranks); runs the tensor-parallel decode workload")
+    ap.add_argument("--context-max", type=int, default=8192, help="tp: contexts are uniform in [512, this]")
     ap.add_argument("--scheme", default="q4_k_m", choices=["q4_k_m", "q8_0"], help="synthetic checkpoint's block types")
     args = ap.parse_args()
     global SCHEME
@@ -701,6 +780,8 @@ def main():
         args.requests = 64 if args.workload == "mixed" else 96
     if args.impl == "reference":
         run_reference(args)
+    elif args.tp > 1:
+        run_tp(args)
     elif args.workload in ("serving", "mixed"):
         run_serving(args)
     elif args.workload == "gemma":

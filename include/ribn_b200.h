@@ -79,6 +79,8 @@ typedef struct {
                                  max_sequences full contexts */
     int32_t device;           /* CUDA ordinal */
     int32_t flags;            /* RIBN_B200_FLAG_* */
+    int32_t tp_size;          /* tensor-parallel group size: 0 or 1 = none, else 2, 4 or 8 */
+    int32_t tp_rank;          /* this executor's rank in the group */
 } ribn_b200_config;
 
 enum {
@@ -222,6 +224,33 @@ RIBN_B200_API int ribn_b200_synchronize(ribn_b200_executor* executor);
 /* ExecutionError text of the last failing call, at most 4096 bytes
  * (crates/runtime/src/executor.rs:134-152).  Returns the length written. */
 RIBN_B200_API size_t ribn_b200_last_error(ribn_b200_executor* executor, char* buffer, size_t capacity);
+
+/* ---- tensor parallelism (one executor per GPU, one process per GPU) ------- */
+/* No reference counterpart: the reference runs on one device (docs/architecture.md).  With tp_size > 1 an
+ * executor holds one shard of every layer: q / k / v split by head and ffn gate / up by output column, the
+ * attention output and ffn down projections split along K on 256-input block boundaries (the ffn blocks are
+ * dealt out as evenly as they go: FFN 25600 = 100 blocks gives 13,13,13,13,12,12,12,12 at eight ranks), the KV
+ * cache by kv head; norms, the embedding and the output head are replicated (every rank selects the same token).
+ * After the attention output and the ffn down projection the ranks' F32 partial sums `[tokens, hidden]` meet in an
+ * NCCL all-reduce(sum) on the executor's stream (captured into the step graphs), then join the residual stream.
+ * Every rank must be driven with the same admit / prepare / submit sequence.
+ * load_tensor takes the WHOLE tensor on every rank and keeps its shard; read_tensor returns the shard. */
+typedef struct { char bytes[128]; } ribn_b200_nccl_id;   /* ncclUniqueId */
+/* Rank 0: make the group's id with the NCCL library at `nccl_library` (a path to libnccl.so.2) and hand it to the
+ * other ranks out of band (the host's own channel: a store, a pipe, a gloo broadcast). */
+RIBN_B200_API int ribn_b200_tp_unique_id(const char* nccl_library, ribn_b200_nccl_id* id, char* error,
+                                         size_t error_capacity);
+/* Every rank, after create and before finalize: join the group (collective: returns once all ranks called). */
+RIBN_B200_API int ribn_b200_tp_init(ribn_b200_executor* executor, const char* nccl_library,
+                                    const ribn_b200_nccl_id* id);
+/* Measurement aid (collective: every rank calls it with the same arguments): average device time of one
+ * all-reduce of `tokens` x hidden F32 values on the executor's stream, as the step issues it. */
+RIBN_B200_API int ribn_b200_tp_time_allreduce(ribn_b200_executor* executor, uint32_t tokens, uint32_t repeats,
+                                              float* average_us);
+/* Which part of a whole tensor a rank keeps (no device work): rows [row0, row0 + rows) and columns
+ * [col0, col0 + cols) of the `[full_rows][full_cols]` tensor `name`, for config->tp_rank of config->tp_size. */
+RIBN_B200_API int ribn_b200_tp_shard(const ribn_b200_config* config, const char* name, int64_t full_rows,
+                                     int64_t full_cols, int64_t* row0, int64_t* rows, int64_t* col0, int64_t* cols);
 
 /* ---- parity / measurement taps ------------------------------------------ */
 

@@ -14,7 +14,7 @@ from ._lib import (  # noqa: F401
 )
 from .executor import (  # noqa: F401
     Admission, BatchItem, ExecutionError, ExecutorInfo, GenerationLimits, PreparedRow, QwenB200, Sampling,
-    StepCompletion, StepKind,
+    StepCompletion, StepKind, nccl_library_path, tp_shard, tp_unique_id,
 )
 from .engine import Engine, EngineConfig, SchedulePolicy, TokenRequest  # noqa: F401
 from . import gemma  # noqa: F401

@@ -23,6 +23,7 @@ class Config(C.Structure):
         ("rope_base", C.c_float), ("rms_eps", C.c_float),
         ("context_tokens", C.c_int32), ("max_sequences", C.c_int32), ("max_batch_tokens", C.c_int32),
         ("kv_pages", C.c_int32), ("device", C.c_int32), ("flags", C.c_int32),
+        ("tp_size", C.c_int32), ("tp_rank", C.c_int32),
     ]
 
 
@@ -47,6 +48,10 @@ class PreparedRowC(C.Structure):
                 ("reserved", C.c_uint32)]
 
 
+class NcclId(C.Structure):
+    _fields_ = [("bytes", C.c_char * 128)]
+
+
 class CompletionC(C.Structure):
     _fields_ = [("sequence", C.c_uint64), ("prefix", C.c_uint32), ("n_tokens", C.c_uint32),
                 ("token", C.c_uint32), ("reserved", C.c_uint32)]
@@ -67,6 +72,11 @@ SIGNATURES = {
                                   C.c_uint32]),
     "ribn_b200_prepare": (C.c_int, [_P, C.POINTER(BatchItemC), C.c_uint32]),
     "ribn_b200_prepare_rows": (C.c_int, [_P, C.POINTER(BatchItemC), C.c_uint32, C.POINTER(PreparedRowC)]),
+    "ribn_b200_tp_unique_id": (C.c_int, [C.c_char_p, C.POINTER(NcclId), C.c_char_p, C.c_size_t]),
+    "ribn_b200_tp_init": (C.c_int, [_P, C.c_char_p, C.POINTER(NcclId)]),
+    "ribn_b200_tp_time_allreduce": (C.c_int, [_P, C.c_uint32, C.c_uint32, C.POINTER(C.c_float)]),
+    "ribn_b200_tp_shard": (C.c_int, [C.POINTER(Config), C.c_char_p, C.c_int64, C.c_int64, C.POINTER(C.c_int64),
+                                     C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
     "ribn_b200_debug_inject": (C.c_int, [_P, C.c_int32, C.c_int32]),
     "ribn_b200_debug_wait_expiry": (C.c_int, [_P, C.c_uint32]),
     "ribn_b200_debug_unpack": (C.c_int, [C.c_int32, C.c_int32, _P, C.c_int64, C.c_int64, _P]),

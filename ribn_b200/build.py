@@ -35,7 +35,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not is_stale():
         return LIB
     cmd = [nvcc_path(), "--threads", "0", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-           "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared", "-o", LIB, *sources()]
+           "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared", "-o", LIB, *sources(), "-ldl"]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

@@ -10,6 +10,7 @@
 // (crates/nvidia/src/decode.rs:550-640, 2161-2334).
 #include "executor.h"
 
+#include <dlfcn.h>
 #include <math.h>
 #include <stdarg.h>
 #include <stdio.h>
@@ -132,6 +133,63 @@ int check_open(ribn_b200_executor* ex) {
     return RIBN_B200_OK;
 }
 
+// ---- tensor parallelism: which part of a whole tensor a rank keeps -----------------------------------------
+constexpr int kRoleEmbedding = 100, kRoleOutputNorm = 101, kRoleOutput = 102;
+
+int role_from_name(const char* name) {
+    if (name == nullptr) return -1;
+    if (!strcmp(name, "token_embd.weight")) return kRoleEmbedding;
+    if (!strcmp(name, "output_norm.weight")) return kRoleOutputNorm;
+    if (!strcmp(name, "output.weight")) return kRoleOutput;
+    int layer = -1;
+    char rest[64];
+    if (sscanf(name, "blk.%d.%63s", &layer, rest) != 2 || layer < 0) return -1;
+    for (int i = 0; i < kLayerTensors; ++i) if (!strcmp(rest, kLayerNames[i])) return i;
+    return -1;
+}
+
+// The ffn dimension is dealt out in 256-column blocks, the first (blocks % ranks) ranks taking one block more.
+void ffn_shard(int ffn, int tp, int rank, int* first, int* count) {
+    const int blocks = ffn / 256, base = blocks / tp, rem = blocks % tp;
+    *first = (rank * base + std::min(rank, rem)) * 256;
+    *count = (base + (rank < rem ? 1 : 0)) * 256;
+}
+
+// `full` is the whole model's geometry.  Rows and columns are those of the tensor as stored ([out][in]).
+void shard_of(const ribn_b200_config& full, int tp, int rank, int role, long long full_rows, long long full_cols,
+              long long* r0, long long* nr, long long* c0, long long* nc) {
+    *r0 = 0; *nr = full_rows; *c0 = 0; *nc = full_cols;
+    if (tp <= 1) return;
+    const long long qd = (long long)(full.q_heads / tp) * full.head_dim, kd = (long long)(full.kv_heads / tp) * full.head_dim;
+    int f0 = 0, fn = 0;
+    ffn_shard(full.ffn, tp, rank, &f0, &fn);
+    switch (role) {
+        case kAttnQ: *r0 = rank * qd; *nr = qd; break;                  // by query head
+        case kAttnK: case kAttnV: *r0 = rank * kd; *nr = kd; break;    // by kv head
+        case kFfnGate: case kFfnUp: *r0 = f0; *nr = fn; break;         // by output column
+        case kAttnOutput: *c0 = rank * qd; *nc = qd; break;            // along K: the heads this rank attends
+        case kFfnDown: *c0 = f0; *nc = fn; break;                      // along K: this rank's ffn columns
+        default: break;                                                // norms, embedding, output head: replicated
+    }
+}
+
+bool load_nccl(NcclApi& api, const char* path, std::string& why) {
+    if (api.handle != nullptr) return true;
+    void* h = dlopen(path != nullptr && path[0] ? path : "libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (h == nullptr) { why = std::string("cannot load the NCCL library: ") + dlerror(); return false; }
+    api.get_unique_id = (int (*)(void*))dlsym(h, "ncclGetUniqueId");
+    api.comm_init_rank = (int (*)(void**, int, ribn_b200_nccl_id, int))dlsym(h, "ncclCommInitRank");
+    api.all_reduce = (int (*)(const void*, void*, size_t, int, int, void*, cudaStream_t))dlsym(h, "ncclAllReduce");
+    api.comm_destroy = (int (*)(void*))dlsym(h, "ncclCommDestroy");
+    api.get_error_string = (const char* (*)(int))dlsym(h, "ncclGetErrorString");
+    if (!api.get_unique_id || !api.comm_init_rank || !api.all_reduce || !api.comm_destroy || !api.get_error_string) {
+        why = "the NCCL library lacks an expected entry point";
+        return false;
+    }
+    api.handle = h;
+    return true;
+}
+
 int pages_for(uint32_t tokens) { return (int)((tokens + kPageTokens - 1) / kPageTokens); }
 
 // ---------------------------------------------------------------------------
@@ -148,6 +206,20 @@ struct StepPlan {
         if (e_ != cudaSuccess) return e_;       \
         ++launches;                             \
     } while (0)
+
+// Tensor parallelism: the ranks' partial sums `proj` [tokens][hidden] meet in one NCCL all-reduce(sum) on the
+// executor's stream, then join the residual stream.
+cudaError_t tp_reduce_add(ribn_b200_executor* ex, int tokens, int& launches) {
+    constexpr int kNcclFloat = 7, kNcclSum = 0;
+    const size_t count = (size_t)tokens * ex->cfg.hidden;
+    if (ex->nccl.all_reduce(ex->proj, ex->proj, count, kNcclFloat, kNcclSum, ex->comm, ex->stream) != 0) {
+        return cudaErrorUnknown;
+    }
+    ++launches;
+    cudaError_t e = launch_residual_add(ex->stream, ex->hidden, ex->proj, (long long)count);
+    if (e == cudaSuccess) ++launches;
+    return e;
+}
 
 // ---- reference family: plain kernels over raw GGUF blocks, any number of tokens ----------
 cudaError_t run_layers_reference(ribn_b200_executor* ex, const StepPlan& plan, int& launches) {
@@ -178,13 +250,26 @@ cudaError_t run_layers_reference(ribn_b200_executor* ex, const StepPlan& plan, i
                                              ex->scratch.attn_partial_bytes, ex->attn, &launches);
             if (e != cudaSuccess) return e;
         }
-        STEP_TRY(launch_gemv_ref(s, t[kAttnOutput].type, t[kAttnOutput].raw, c.hidden, t[kAttnOutput].cols, ex->attn, T,
-                                 ex->hidden, true));
+        if (ex->tp > 1) {
+            STEP_TRY(launch_gemv_ref(s, t[kAttnOutput].type, t[kAttnOutput].raw, c.hidden, t[kAttnOutput].cols, ex->attn, T,
+                                     ex->proj, false));
+            cudaError_t e = tp_reduce_add(ex, T, launches);
+            if (e != cudaSuccess) return e;
+        } else {
+            STEP_TRY(launch_gemv_ref(s, t[kAttnOutput].type, t[kAttnOutput].raw, c.hidden, t[kAttnOutput].cols, ex->attn, T,
+                                     ex->hidden, true));
+        }
         STEP_TRY(launch_rms_norm(s, ex->hidden, (const float*)t[kFfnNorm].raw, T, c.hidden, c.rms_eps, ex->normed));
         STEP_TRY(launch_gemv_ref(s, t[kFfnGate].type, t[kFfnGate].raw, c.ffn, c.hidden, ex->normed, T, ex->gate, false));
         STEP_TRY(launch_gemv_ref(s, t[kFfnUp].type, t[kFfnUp].raw, c.ffn, c.hidden, ex->normed, T, ex->up, false));
         STEP_TRY(launch_silu_mul(s, ex->gate, ex->up, (long long)T * c.ffn, ex->gate));
-        STEP_TRY(launch_gemv_ref(s, t[kFfnDown].type, t[kFfnDown].raw, c.hidden, c.ffn, ex->gate, T, ex->hidden, true));
+        if (ex->tp > 1) {
+            STEP_TRY(launch_gemv_ref(s, t[kFfnDown].type, t[kFfnDown].raw, c.hidden, c.ffn, ex->gate, T, ex->proj, false));
+            cudaError_t e = tp_reduce_add(ex, T, launches);
+            if (e != cudaSuccess) return e;
+        } else {
+            STEP_TRY(launch_gemv_ref(s, t[kFfnDown].type, t[kFfnDown].raw, c.hidden, c.ffn, ex->gate, T, ex->hidden, true));
+        }
     }
     if (plan.n_sample > 0) {
         // Only sampling rows reach the head (crates/nvidia/src/decode.rs:686-704).
@@ -228,8 +313,8 @@ GemvArgs o_args(ribn_b200_executor* ex, int l, int T) {
     Tensor* t = &ex->lt(l, 0);
     GemvArgs a = base_args(ex, T, ex->attn, ex->cfg.q_heads * ex->cfg.head_dim, nullptr);
     a.n_segments = 1;
-    a.seg[0] = segment_of(t[kAttnOutput], ex->hidden);
-    a.epilogue = kResidual;
+    a.seg[0] = segment_of(t[kAttnOutput], ex->tp > 1 ? ex->proj : ex->hidden);
+    a.epilogue = ex->tp > 1 ? kStore : kResidual;   // tensor parallel: a partial sum for the all-reduce
     return a;
 }
 // gate | up of ffn_norm(hidden) with the SwiGLU epilogue: the gated product lands in `gate`
@@ -247,8 +332,8 @@ GemvArgs down_args(ribn_b200_executor* ex, int l, int T) {
     Tensor* t = &ex->lt(l, 0);
     GemvArgs a = base_args(ex, T, ex->gate, ex->cfg.ffn, nullptr);
     a.n_segments = 1;
-    a.seg[0] = segment_of(t[kFfnDown], ex->hidden);
-    a.epilogue = kResidual;
+    a.seg[0] = segment_of(t[kFfnDown], ex->tp > 1 ? ex->proj : ex->hidden);
+    a.epilogue = ex->tp > 1 ? kStore : kResidual;
     return a;
 }
 // output head over output_norm of `rows` rows of the residual stream (gathered through `index` when given)
@@ -298,8 +383,10 @@ cudaError_t run_layers_decode(ribn_b200_executor* ex, const StepPlan& plan, int&
             if (e != cudaSuccess) return e;
         }
         STEP_TRY(launch_gemv_mma(s, o_args(ex, l, T), pdl));
+        if (ex->tp > 1) { cudaError_t e = tp_reduce_add(ex, T, launches); if (e != cudaSuccess) return e; }
         STEP_TRY(launch_gemv_mma(s, gate_up_args(ex, l, T), pdl));
         STEP_TRY(launch_gemv_mma(s, down_args(ex, l, T), pdl));
+        if (ex->tp > 1) { cudaError_t e = tp_reduce_add(ex, T, launches); if (e != cudaSuccess) return e; }
     }
     if (plan.n_sample > 0) {
         // Only sampling rows reach the head (crates/nvidia/src/decode.rs:686-704).
@@ -429,8 +516,9 @@ cudaError_t run_layers_batch(ribn_b200_executor* ex, const StepPlan& plan, int& 
         }
         {
             const Tensor* mats[1] = {&t[kAttnOutput]};
-            float* ys[1] = {ex->hidden};
-            cudaError_t e = batch_project(ex, launches, ex->attn, nullptr, nullptr, T, QD, mats, ys, 1, kResidual);
+            float* ys[1] = {ex->tp > 1 ? ex->proj : ex->hidden};
+            cudaError_t e = batch_project(ex, launches, ex->attn, nullptr, nullptr, T, QD, mats, ys, 1, ex->tp > 1 ? kStore : kResidual);
+            if (e == cudaSuccess && ex->tp > 1) e = tp_reduce_add(ex, T, launches);
             if (e != cudaSuccess) return e;
         }
         {
@@ -442,8 +530,9 @@ cudaError_t run_layers_batch(ribn_b200_executor* ex, const StepPlan& plan, int& 
         }
         {
             const Tensor* mats[1] = {&t[kFfnDown]};
-            float* ys[1] = {ex->hidden};
-            cudaError_t e = batch_project(ex, launches, ex->gate, nullptr, nullptr, T, c.ffn, mats, ys, 1, kResidual);
+            float* ys[1] = {ex->tp > 1 ? ex->proj : ex->hidden};
+            cudaError_t e = batch_project(ex, launches, ex->gate, nullptr, nullptr, T, c.ffn, mats, ys, 1, ex->tp > 1 ? kStore : kResidual);
+            if (e == cudaSuccess && ex->tp > 1) e = tp_reduce_add(ex, T, launches);
             if (e != cudaSuccess) return e;
         }
     }
@@ -523,6 +612,14 @@ int ribn_b200_create(const ribn_b200_config* config, ribn_b200_executor** out, c
         return report("prepared model limits must be nonzero");
     }
     if (c.max_sequences > 1024) return report("max_sequences above 1024 is not supported");
+    const int tp = c.tp_size > 1 ? c.tp_size : 1;
+    if (tp > 1) {
+        // heads split by rank; K splits must fall on 256-input block boundaries (K-quant super-blocks)
+        if (c.tp_rank < 0 || c.tp_rank >= tp) return report("tp_rank out of range");
+        if (c.q_heads % tp != 0 || c.kv_heads % tp != 0) return report("tensor parallelism needs q_heads and kv_heads divisible by tp_size");
+        if (((c.q_heads / tp) * c.head_dim) % 256 != 0) return report("tensor parallelism needs (q_heads / tp_size) * head_dim to be a multiple of 256");
+        if (c.ffn % 256 != 0 || c.ffn / 256 < tp) return report("tensor parallelism needs ffn to be a multiple of 256 with at least one block per rank");
+    }
     if (c.context_tokens > kAttnMaxSpans * kAttnSpanKeys) {
         return report("context_tokens above 65536 is not supported (1024 attention spans of 64 keys)");
     }
@@ -540,6 +637,17 @@ int ribn_b200_create(const ribn_b200_config* config, ribn_b200_executor** out, c
     if (cudaSetDevice(c.device) != cudaSuccess) return report("cannot select the CUDA device");
     auto* ex = new ribn_b200_executor();
     ex->cfg = c;
+    ex->full = c;
+    ex->tp = tp;
+    ex->rank = tp > 1 ? c.tp_rank : 0;
+    if (tp > 1) {
+        // this rank's shard: the step's kernels see the local geometry
+        int count = 0;
+        ffn_shard(c.ffn, tp, ex->rank, &ex->ffn_first, &count);
+        ex->cfg.q_heads = c.q_heads / tp;
+        ex->cfg.kv_heads = c.kv_heads / tp;
+        ex->cfg.ffn = count;
+    }
     ex->layer_tensors.resize((size_t)c.layers * kLayerTensors);
     if (cudaStreamCreateWithFlags(&ex->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreate(&ex->ev_start) != cudaSuccess || cudaEventCreate(&ex->ev_done) != cudaSuccess) {
@@ -557,6 +665,7 @@ int ribn_b200_destroy(ribn_b200_executor* ex) {
     // (crates/runtime/src/engine.rs:597-607).
     if (cudaStreamSynchronize(ex->stream) != cudaSuccess) return RIBN_B200_ERROR;
     for (auto& g : ex->graphs) cudaGraphExecDestroy(g.second.exec);
+    if (ex->comm != nullptr && ex->nccl.comm_destroy != nullptr) ex->nccl.comm_destroy(ex->comm);
     for (void* p : ex->allocations) cudaFree(p);
     if (ex->h_rows) cudaFreeHost(ex->h_rows);
     if (ex->h_tokens) cudaFreeHost(ex->h_tokens);
@@ -577,6 +686,31 @@ size_t ribn_b200_last_error(ribn_b200_executor* ex, char* buffer, size_t capacit
     return n;
 }
 
+// Role of a tensor slot of this executor (a LayerTensor index, or one of the kRole* constants).
+static int role_of(ribn_b200_executor* ex, const Tensor* t) {
+    if (t == &ex->token_embd) return kRoleEmbedding;
+    if (t == &ex->output_norm) return kRoleOutputNorm;
+    if (t == &ex->output) return kRoleOutput;
+    return (int)((t - ex->layer_tensors.data()) % kLayerTensors);
+}
+
+// Copies this rank's shard of a whole tensor (`src`: host or device memory holding [rows][cols] blocks) into `t`.
+static int store_shard(ribn_b200_executor* ex, Tensor* t, int type, long long rows, long long cols, const unsigned char* src,
+                       cudaMemcpyKind kind) {
+    long long r0, nr, c0, nc;
+    shard_of(ex->full, ex->tp, ex->rank, role_of(ex, t), rows, cols, &r0, &nr, &c0, &nc);
+    const int elems = block_elems(type);
+    if (elems == 0 || cols % elems != 0 || c0 % elems != 0 || nc % elems != 0) {
+        return fail(ex, "tensor type %d with shape [%lld, %lld] cannot be split for this rank", type, rows, cols);
+    }
+    if (set_tensor_storage(ex, t, type, nr, nc) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    const size_t bb = (size_t)block_bytes(type);
+    const size_t src_pitch = (size_t)(cols / elems) * bb, dst_pitch = (size_t)(nc / elems) * bb;
+    const unsigned char* from = src + (size_t)r0 * src_pitch + (size_t)(c0 / elems) * bb;
+    CU_TRY(ex, cudaMemcpy2DAsync(t->raw, dst_pitch, from, src_pitch, dst_pitch, (size_t)nr, kind, ex->stream));
+    return RIBN_B200_OK;
+}
+
 int ribn_b200_load_tensor(ribn_b200_executor* ex, const char* name, int32_t type, int64_t rows, int64_t cols,
                           const void* bytes, size_t byte_count) {
     if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
@@ -584,11 +718,18 @@ int ribn_b200_load_tensor(ribn_b200_executor* ex, const char* name, int32_t type
     cudaSetDevice(ex->cfg.device);
     Tensor* t = name ? find_tensor(ex, name) : nullptr;
     if (t == nullptr) return fail(ex, "unknown tensor name '%s'", name ? name : "(null)");
-    if (set_tensor_storage(ex, t, type, rows, cols) != RIBN_B200_OK) return RIBN_B200_ERROR;
-    if (byte_count != t->bytes || bytes == nullptr) {
-        return fail(ex, "tensor '%s' needs %zu encoded bytes, got %zu", name, t->bytes, byte_count);
+    const int elems = block_elems(type);
+    if (elems == 0 || rows <= 0 || cols <= 0 || cols % elems != 0) {
+        return fail(ex, "tensor type %d with shape [%lld, %lld] is not supported", type, (long long)rows, (long long)cols);
     }
-    CU_TRY(ex, cudaMemcpyAsync(t->raw, bytes, byte_count, cudaMemcpyHostToDevice, ex->stream));
+    const size_t whole = (size_t)rows * (size_t)(cols / elems) * (size_t)block_bytes(type);
+    if (byte_count != whole || bytes == nullptr) {
+        return fail(ex, "tensor '%s' needs %zu encoded bytes, got %zu", name, whole, byte_count);
+    }
+    // The caller passes the whole tensor; a tensor-parallel rank keeps its shard of it.
+    if (store_shard(ex, t, type, rows, cols, (const unsigned char*)bytes, cudaMemcpyHostToDevice) != RIBN_B200_OK) {
+        return RIBN_B200_ERROR;
+    }
     CU_TRY(ex, cudaStreamSynchronize(ex->stream));
     return RIBN_B200_OK;
 }
@@ -602,20 +743,40 @@ int ribn_b200_init_synthetic(ribn_b200_executor* ex, uint64_t seed, int32_t sche
     const int base = scheme == RIBN_B200_SCHEME_Q8_0 ? kQ8_0 : kQ4_K;
     const int wide = scheme == RIBN_B200_SCHEME_Q8_0 ? kQ8_0 : kQ6_K;  // attn_v, ffn_down, output
     uint64_t index = 0;
+    // Every rank generates the WHOLE tensor from the same seed (into a scratch buffer when it keeps only a shard),
+    // so the shards of a tensor-parallel group are slices of the one-GPU checkpoint with the same seed.
+    unsigned char* scratch = nullptr;
+    size_t scratch_bytes = 0;
     auto fill = [&](Tensor* t, int type, long long rows, long long cols) -> int {
-        if (set_tensor_storage(ex, t, type, rows, cols) != RIBN_B200_OK) return RIBN_B200_ERROR;
         const uint64_t tensor_seed = seed * 0x9e3779b97f4a7c15ull + (++index) * 0xd1342543de82ef95ull;
-        if (type == kF32) {
-            CU_TRY(ex, launch_fill_f32(ex->stream, (float*)t->raw, rows * cols, 1.0f));
+        long long r0, nr, c0, nc;
+        shard_of(ex->full, ex->tp, ex->rank, role_of(ex, t), rows, cols, &r0, &nr, &c0, &nc);
+        const bool whole = nr == rows && nc == cols;
+        unsigned char* target = nullptr;
+        if (whole) {
+            if (set_tensor_storage(ex, t, type, rows, cols) != RIBN_B200_OK) return RIBN_B200_ERROR;
+            target = t->raw;
         } else {
-            CU_TRY(ex, launch_synth_quantized(ex->stream, type, t->raw, rows, cols, tensor_seed, 0.02f));
+            const size_t need = (size_t)rows * (size_t)(cols / block_elems(type)) * (size_t)block_bytes(type);
+            if (need > scratch_bytes) {
+                if (scratch != nullptr) { CU_TRY(ex, cudaStreamSynchronize(ex->stream)); cudaFree(scratch); scratch = nullptr; }
+                CU_TRY(ex, cudaMalloc((void**)&scratch, need));
+                scratch_bytes = need;
+            }
+            target = scratch;
         }
+        if (type == kF32) {
+            CU_TRY(ex, launch_fill_f32(ex->stream, (float*)target, rows * cols, 1.0f));
+        } else {
+            CU_TRY(ex, launch_synth_quantized(ex->stream, type, target, rows, cols, tensor_seed, 0.02f));
+        }
+        if (!whole && store_shard(ex, t, type, rows, cols, scratch, cudaMemcpyDeviceToDevice) != RIBN_B200_OK) return RIBN_B200_ERROR;
         return RIBN_B200_OK;
     };
     for (int l = 0; l < c.layers; ++l) {
         for (int w = 0; w < kLayerTensors; ++w) {
             long long rows, cols;
-            expected_shape(c, w, &rows, &cols);
+            expected_shape(ex->full, w, &rows, &cols);
             int type = is_norm(w) ? kF32 : ((w == kAttnV || w == kFfnDown) ? wide : base);
             if (fill(&ex->lt(l, w), type, rows, cols) != RIBN_B200_OK) return RIBN_B200_ERROR;
         }
@@ -624,6 +785,7 @@ int ribn_b200_init_synthetic(ribn_b200_executor* ex, uint64_t seed, int32_t sche
     if (fill(&ex->output_norm, kF32, 1, c.hidden) != RIBN_B200_OK) return RIBN_B200_ERROR;
     if (fill(&ex->output, wide, c.vocab, c.hidden) != RIBN_B200_OK) return RIBN_B200_ERROR;
     CU_TRY(ex, cudaStreamSynchronize(ex->stream));
+    if (scratch != nullptr) cudaFree(scratch);
     return RIBN_B200_OK;
 }
 
@@ -648,6 +810,7 @@ int ribn_b200_read_tensor(ribn_b200_executor* ex, const char* name, int32_t* typ
 int ribn_b200_finalize(ribn_b200_executor* ex) {
     if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
     if (ex->finalized) return fail(ex, "finalize called twice");
+    if (ex->tp > 1 && ex->comm == nullptr) return fail(ex, "a tensor-parallel executor must join its group (tp_init) before finalize");
     cudaSetDevice(ex->cfg.device);
     const ribn_b200_config& c = ex->cfg;
     // Model plan validation (validate_model_plan, crates/nvidia/src/decode.rs:364-368).
@@ -761,6 +924,7 @@ int ribn_b200_finalize(ribn_b200_executor* ex) {
     CU_TRY(ex, dev_alloc(ex, &ex->attn, T * QD));
     CU_TRY(ex, dev_alloc(ex, &ex->gate, T * c.ffn));
     CU_TRY(ex, dev_alloc(ex, &ex->up, T * c.ffn));
+    if (ex->tp > 1) CU_TRY(ex, dev_alloc(ex, &ex->proj, T * c.hidden));
     CU_TRY(ex, dev_alloc(ex, &ex->head_in, S * c.hidden));
     CU_TRY(ex, dev_alloc(ex, &ex->logits, S * c.vocab));
     {
@@ -797,6 +961,74 @@ int ribn_b200_finalize(ribn_b200_executor* ex) {
     }
     CU_TRY(ex, cudaStreamSynchronize(ex->stream));
     ex->finalized = true;
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_tp_unique_id(const char* nccl_library, ribn_b200_nccl_id* id, char* error, size_t error_capacity) {
+    auto report = [&](const char* msg) {
+        if (error != nullptr && error_capacity > 0) snprintf(error, error_capacity, "%s", msg);
+        return RIBN_B200_ERROR;
+    };
+    if (id == nullptr) return report("null argument");
+    static NcclApi api;  // the process's one NCCL library
+    std::string why;
+    if (!load_nccl(api, nccl_library, why)) return report(why.c_str());
+    const int rc = api.get_unique_id(id);
+    if (rc != 0) return report(api.get_error_string(rc));
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_tp_init(ribn_b200_executor* ex, const char* nccl_library, const ribn_b200_nccl_id* id) {
+    if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    if (ex->tp <= 1) return fail(ex, "this executor was created without tensor parallelism");
+    if (ex->comm != nullptr) return fail(ex, "the executor already joined its group");
+    if (id == nullptr) return fail(ex, "null group id");
+    std::string why;
+    if (!load_nccl(ex->nccl, nccl_library, why)) return fail(ex, "%s", why.c_str());
+    cudaSetDevice(ex->cfg.device);
+    const int rc = ex->nccl.comm_init_rank(&ex->comm, ex->tp, *id, ex->rank);
+    if (rc != 0) {
+        ex->comm = nullptr;
+        return fail(ex, "ncclCommInitRank failed: %s", ex->nccl.get_error_string(rc));
+    }
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_tp_time_allreduce(ribn_b200_executor* ex, uint32_t tokens, uint32_t repeats, float* average_us) {
+    if (check_open(ex) != RIBN_B200_OK) return RIBN_B200_ERROR;
+    if (ex->tp <= 1 || ex->comm == nullptr || !ex->finalized || ex->pending.active) return fail(ex, "time_allreduce: no idle tensor-parallel executor");
+    if (tokens == 0 || tokens > (uint32_t)ex->cfg.max_batch_tokens || repeats == 0 || average_us == nullptr) return fail(ex, "time_allreduce: bad argument");
+    cudaSetDevice(ex->cfg.device);
+    int launches = 0;
+    CU_TRY(ex, cudaMemsetAsync(ex->proj, 0, (size_t)tokens * ex->cfg.hidden * sizeof(float), ex->stream));
+    for (int warm = 0; warm < 3; ++warm) {
+        if (ex->nccl.all_reduce(ex->proj, ex->proj, (size_t)tokens * ex->cfg.hidden, 7, 0, ex->comm, ex->stream) != 0) return fail(ex, "ncclAllReduce failed");
+    }
+    CU_TRY(ex, cudaEventRecord(ex->ev_start, ex->stream));
+    for (uint32_t r = 0; r < repeats; ++r) {
+        if (ex->nccl.all_reduce(ex->proj, ex->proj, (size_t)tokens * ex->cfg.hidden, 7, 0, ex->comm, ex->stream) != 0) return fail(ex, "ncclAllReduce failed");
+    }
+    CU_TRY(ex, cudaEventRecord(ex->ev_done, ex->stream));
+    CU_TRY(ex, cudaEventSynchronize(ex->ev_done));
+    float ms = 0.0f;
+    CU_TRY(ex, cudaEventElapsedTime(&ms, ex->ev_start, ex->ev_done));
+    *average_us = ms * 1000.0f / (float)repeats;
+    (void)launches;
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_tp_shard(const ribn_b200_config* config, const char* name, int64_t full_rows, int64_t full_cols,
+                       int64_t* row0, int64_t* rows, int64_t* col0, int64_t* cols) {
+    if (config == nullptr || row0 == nullptr || rows == nullptr || col0 == nullptr || cols == nullptr) return RIBN_B200_ERROR;
+    const int role = role_from_name(name);
+    const int tp = config->tp_size > 1 ? config->tp_size : 1;
+    if (role < 0 || config->tp_rank < 0 || config->tp_rank >= tp) return RIBN_B200_ERROR;
+    if (tp > 1 && (config->q_heads % tp != 0 || config->kv_heads % tp != 0 || config->ffn % 256 != 0 || config->ffn / 256 < tp)) {
+        return RIBN_B200_ERROR;
+    }
+    long long r0, nr, c0, nc;
+    shard_of(*config, tp, config->tp_rank, role, full_rows, full_cols, &r0, &nr, &c0, &nc);
+    *row0 = r0; *rows = nr; *col0 = c0; *cols = nc;
     return RIBN_B200_OK;
 }
 

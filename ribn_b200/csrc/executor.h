@@ -54,8 +54,25 @@ struct Pending {
 
 }  // namespace ribn
 
+// The handful of NCCL entry points tensor parallelism needs, resolved at run time from the libnccl the host
+// process names (a single-GPU process never loads it).
+struct NcclApi {
+    void* handle = nullptr;
+    int (*get_unique_id)(void*) = nullptr;
+    int (*comm_init_rank)(void**, int, ribn_b200_nccl_id, int) = nullptr;
+    int (*all_reduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*comm_destroy)(void*) = nullptr;
+    const char* (*get_error_string)(int) = nullptr;
+};
+
 struct ribn_b200_executor {
-    ribn_b200_config cfg{};
+    ribn_b200_config cfg{};    // this rank's geometry: q_heads, kv_heads and ffn are the LOCAL shard's
+    ribn_b200_config full{};   // the whole model's geometry (equal to cfg without tensor parallelism)
+    int tp = 1, rank = 0;      // tensor-parallel group size and this executor's rank in it
+    int ffn_first = 0;         // first ffn column of this rank's shard
+    NcclApi nccl;
+    void* comm = nullptr;      // ncclComm_t
+    float* proj = nullptr;     // [max_batch_tokens][hidden]: this rank's partial o_proj / ffn_down sums before the all-reduce
     cudaStream_t stream = nullptr;
     cudaEvent_t ev_start = nullptr, ev_done = nullptr;
     std::string error;
@@ -95,7 +112,7 @@ struct ribn_b200_executor {
     uint32_t* d_sampled = nullptr;
     ribn::StepMeta meta{};
     float *hidden = nullptr, *normed = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr,
-          *gate = nullptr, *up = nullptr, *proj = nullptr, *head_in = nullptr, *logits = nullptr;
+          *gate = nullptr, *up = nullptr, *head_in = nullptr, *logits = nullptr;
     ribn::StepScratch scratch;
     ribn::BatchOperand op_batch;  // batch form, refilled before every batched projection
     ribn::TcOperand op_tc;        // tensor-memory form (the same, for the tcgen05 kernel)

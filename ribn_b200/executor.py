@@ -94,6 +94,39 @@ class Admission:
         return self.state == Admission.READY
 
 
+def nccl_library_path() -> str:
+    """The libnccl the host process uses: the one bundled with the Python environment when there is one."""
+    import importlib.util
+    import os
+    spec = importlib.util.find_spec("nvidia.nccl")
+    if spec is not None and spec.submodule_search_locations:
+        for root in spec.submodule_search_locations:
+            path = os.path.join(root, "lib", "libnccl.so.2")
+            if os.path.exists(path):
+                return path
+    return "libnccl.so.2"
+
+
+def tp_unique_id(nccl_library: Optional[str] = None) -> bytes:
+    """Rank 0 of a tensor-parallel group: a fresh group id (128 bytes) to hand to the other ranks."""
+    nid = _lib.NcclId()
+    err = C.create_string_buffer(1024)
+    rc = lib().ribn_b200_tp_unique_id((nccl_library or nccl_library_path()).encode(), C.byref(nid), err, len(err))
+    if rc != _lib.OK:
+        raise ExecutionError(err.value.decode(errors="replace"))
+    return bytes(C.string_at(C.byref(nid), 128))
+
+
+def tp_shard(model: dict, name: str, rows: int, cols: int, tp_size: int, tp_rank: int):
+    """(row0, rows, col0, cols) of the part of whole tensor `name` that rank `tp_rank` of `tp_size` keeps."""
+    cfg = Config(tp_size=tp_size, tp_rank=tp_rank, **model)
+    out = [C.c_int64() for _ in range(4)]
+    rc = lib().ribn_b200_tp_shard(C.byref(cfg), name.encode(), rows, cols, *[C.byref(o) for o in out])
+    if rc != _lib.OK:
+        raise ValueError(f"no tensor-parallel split of {name} for rank {tp_rank} of {tp_size}")
+    return tuple(o.value for o in out)
+
+
 def _items(items: Sequence[BatchItem]):
     arr = (BatchItemC * max(len(items), 1))()
     for i, it in enumerate(items):
@@ -105,9 +138,11 @@ class QwenB200:
     """Dense-Qwen3 GGUF executor on one B200 (the `QwenCuda` replacement)."""
 
     def __init__(self, model: dict, *, context_tokens: int = 4096, max_sequences: int = 1,
-                 max_batch_tokens: int = 128, kv_pages: int = 0, device: int = 0, flags: int = 0):
+                 max_batch_tokens: int = 128, kv_pages: int = 0, device: int = 0, flags: int = 0,
+                 tp_size: int = 1, tp_rank: int = 0):
         cfg = Config(context_tokens=context_tokens, max_sequences=max_sequences,
-                     max_batch_tokens=max_batch_tokens, kv_pages=kv_pages, device=device, flags=flags, **model)
+                     max_batch_tokens=max_batch_tokens, kv_pages=kv_pages, device=device, flags=flags,
+                     tp_size=tp_size, tp_rank=tp_rank, **model)
         self.cfg = cfg
         self._h = C.c_void_p()
         err = C.create_string_buffer(4096)
@@ -151,6 +186,18 @@ class QwenB200:
                       "ffn_norm", "ffn_gate", "ffn_up", "ffn_down"):
                 names.append(f"blk.{l}.{n}.weight")
         return names + ["token_embd.weight", "output_norm.weight", "output.weight"]
+
+    def tp_init(self, group_id: bytes, nccl_library: Optional[str] = None) -> None:
+        """Join the tensor-parallel group (collective over all its ranks; call after create, before finalize)."""
+        nid = _lib.NcclId()
+        C.memmove(C.byref(nid), group_id, 128)
+        self._check(lib().ribn_b200_tp_init(self._h, (nccl_library or nccl_library_path()).encode(), C.byref(nid)))
+
+    def tp_time_allreduce(self, tokens: int, repeats: int = 50) -> float:
+        """Average microseconds of one [tokens, hidden] F32 all-reduce (collective: every rank calls it)."""
+        us = C.c_float()
+        self._check(lib().ribn_b200_tp_time_allreduce(self._h, tokens, repeats, C.byref(us)))
+        return us.value
 
     def finalize(self) -> None:
         self._check(lib().ribn_b200_finalize(self._h))
