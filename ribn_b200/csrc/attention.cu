@@ -15,7 +15,8 @@
 // The decode form (FUSED) also applies the per-head Q/K RMSNorm and the NeoX
 // rotary and appends the new K/V row to the paged cache: the CTA that owns
 // the span holding the token's own position computes that row, stores it, and
-// serves it to its warps from shared memory.  Results leave in F32.
+// serves it to its warps from shared memory.  Results leave in F32 and,
+// optionally, in the tensor-core operand form the output projection consumes.
 //
 // The reference's two-pass form with a global scores buffer
 // (crates/nvidia/src/model_ops.rs:441-545) is replaced, not translated.
@@ -26,6 +27,7 @@
 
 #include "gemv.cuh"
 #include "kernels.cuh"
+#include "operand.cuh"
 
 namespace ribn {
 
@@ -61,6 +63,7 @@ struct AttnArgs {
     int q_heads, kv_heads, window, max_spans;
     float* partial;
     float* out;                // [T][q_heads][HD]
+    ActOperand operand;        // optional operand form of `out`, K = q_heads * HD
 };
 
 // RMSNorm + NeoX rotary of one head vector held lane-strided: element i of a
@@ -181,7 +184,16 @@ __device__ __forceinline__ void span_compute(const AttnArgs& a, float* qs, const
             const float inv = 1.0f / total;
             float* op = a.out + ((long long)t * a.q_heads + qh) * HD + dc * CH;
 #pragma unroll
-            for (int d = 0; d < CH; ++d) op[d] = acc[d] * inv;
+            for (int d = 0; d < CH; ++d) { acc[d] *= inv; op[d] = acc[d]; qs[dc * CH + d] = acc[d]; }
+        }
+        if (a.operand.dig != nullptr) {
+            // back to one input per lane: lane takes dims lane + 32 i of this head
+            __syncwarp();
+            ActOperand op = a.operand;
+            op.ss32 = nullptr;
+            const int K = a.q_heads * HD, m = t - a.token_base;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) operand_store_span(op, m, K, (qh * HD) / 32 + i, lane, qs[lane + 32 * i], 0.0f);
         }
     } else if (kg == 0) {
         float* pp = a.partial + (((long long)(t - a.token_base) * a.q_heads + qh) * a.max_spans + span) * (HD + 2);
@@ -547,7 +559,16 @@ __global__ void __launch_bounds__(EARLY ? 256 : 512) attention_span_direct_kerne
             const float inv = 1.0f / total;
             float* op = a.out + ((long long)t * a.q_heads + qh) * HD + dc * CH;
 #pragma unroll
-            for (int d = 0; d < CH; ++d) op[d] = acc[d] * inv;
+            for (int d = 0; d < CH; ++d) { acc[d] *= inv; op[d] = acc[d]; qs[dc * CH + d] = acc[d]; }
+        }
+        if (a.operand.dig != nullptr) {
+            // back to one input per lane: lane takes dims lane + 32 i of this head
+            __syncwarp();
+            ActOperand op = a.operand;
+            op.ss32 = nullptr;
+            const int K = a.q_heads * HD, m = t - a.token_base;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) operand_store_span(op, m, K, (qh * HD) / 32 + i, lane, qs[lane + 32 * i], 0.0f);
         }
     } else if (kg == 0) {
         float* pp = a.partial + (((long long)(t - a.token_base) * a.q_heads + qh) * a.max_spans + span) * (HD + 2);
@@ -599,6 +620,11 @@ __global__ void attention_merge_kernel(const AttnArgs a) {
     }
     const float value = sum / denom_s;
     a.out[((long long)t * a.q_heads + qh) * HD + d] = value;
+    if (a.operand.dig != nullptr) {
+        ActOperand op = a.operand;
+        op.ss32 = nullptr;
+        operand_store_span(op, t - a.token_base, a.q_heads * HD, (qh * HD + d) / 32, d & 31, value, 0.0f);
+    }
 }
 
 template <typename Kernel>
@@ -645,6 +671,7 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
         if (a.partial == nullptr || partial_bytes < per_token) return cudaErrorInvalidValue;
         chunk = (int)std::min<size_t>((size_t)n_tokens, partial_bytes / per_token);
     }
+    if (a.operand.dig != nullptr && chunk < n_tokens) return cudaErrorInvalidValue;  // operand rows are launch-relative
     // Few CTAs: the direct kernel (shorter dependency chain); many: K / V rows staged once per query-head group.
     const bool staged = (long long)n_tokens * a.kv_heads * a.max_spans >= 1024;
     const size_t smem = staged ? (size_t)q_per_kv * HD * sizeof(float) + (size_t)2 * kAttnSpanKeys * (HD + 8) * sizeof(__half)
@@ -668,7 +695,7 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
         a.token_base = base;
         dim3 grid(n * a.kv_heads, a.max_spans);
         cudaError_t e;
-        if (staged && !fused && n >= 4 * kAttnRowsPerCta) {
+        if (staged && !fused && a.operand.dig == nullptr && n >= 4 * kAttnRowsPerCta) {
             // prefill-sized launches of tokens whose K / V rows are all in the cache: several tokens per staged span
             const dim3 row_grid((unsigned)((n + kAttnRowsPerCta - 1) / kAttnRowsPerCta) * a.kv_heads, a.max_spans);
             e = launch_pdl(stream, attention_span_rows_kernel<HD>, row_grid, q_per_kv * 32, smem, a, programmatic, n);
@@ -748,7 +775,7 @@ cudaError_t launch_attention_decode(cudaStream_t stream, const DecodeAttention& 
     a.page_tables = d.page_tables; a.pages_per_sequence = d.pages_per_sequence;
     a.token_seq = d.token_seq; a.token_pos = d.token_pos; a.token_slot = d.token_slot;
     a.q_heads = d.q_heads; a.kv_heads = d.kv_heads; a.window = d.window;
-    a.partial = d.partial; a.out = d.out;
+    a.partial = d.partial; a.out = d.out; a.operand = d.operand;
     const int max_keys = d.window > 0 ? std::min(d.max_keys, d.window) : d.max_keys;
     return dispatch(stream, a, true, d.head_dim, d.n_tokens, max_keys, d.partial_bytes, launches, d.programmatic);
 }

@@ -281,67 +281,93 @@ cudaError_t run_layers_reference(ribn_b200_executor* ex, const StepPlan& plan, i
     return cudaSuccess;
 }
 
-// ---- decode family: tensor-core GEMV chain over F32 activations (<= 2 tokens) ---------
+// ---- decode family: tensor-core GEMV chain over operand-form activations (<= 2 tokens) ---------
 GemvSegment segment_of(const Tensor& t, float* y) {
     return GemvSegment{t.packed.data, t.type, (int)t.rows, t.packed.row_tiles, y};
 }
 
 // The decode step's projections as GEMV arguments (T = 1 or 2 rows).
-GemvArgs base_args(ribn_b200_executor* ex, int T, const float* x, int k, const float* norm_weight) {
+GemvArgs base_args(ribn_b200_executor* ex, int T) {
     GemvArgs a{};
     a.members = T;
-    a.x = x;
-    a.k = k;
-    a.norm_weight = norm_weight;
     a.eps = ex->cfg.rms_eps;
-    a.epilogue = kStore;
     a.error_flag = ex->d_error;
     return a;
 }
-// q | k | v from attn_norm(hidden)
+// q | k | v from the normalised residual stream
 GemvArgs qkv_args(ribn_b200_executor* ex, int l, int T) {
     Tensor* t = &ex->lt(l, 0);
-    GemvArgs a = base_args(ex, T, ex->hidden, ex->cfg.hidden, (const float*)t[kAttnNorm].raw);
+    GemvArgs a = base_args(ex, T);
     a.n_segments = 3;
     a.seg[0] = segment_of(t[kAttnQ], ex->q);
     a.seg[1] = segment_of(t[kAttnK], ex->k);
     a.seg[2] = segment_of(t[kAttnV], ex->v);
+    a.k = ex->cfg.hidden;
+    a.in = ex->op_hidden;
+    a.in_has_norm = 1;
+    a.epilogue = kStore;
     return a;
 }
-// attention output projection, added into the residual stream
+// attention output projection, residual add, operand form of ffn_norm(hidden)
 GemvArgs o_args(ribn_b200_executor* ex, int l, int T) {
     Tensor* t = &ex->lt(l, 0);
-    GemvArgs a = base_args(ex, T, ex->attn, ex->cfg.q_heads * ex->cfg.head_dim, nullptr);
+    GemvArgs a = base_args(ex, T);
     a.n_segments = 1;
     a.seg[0] = segment_of(t[kAttnOutput], ex->tp > 1 ? ex->proj : ex->hidden);
-    a.epilogue = ex->tp > 1 ? kStore : kResidual;   // tensor parallel: a partial sum for the all-reduce
+    a.k = ex->cfg.q_heads * ex->cfg.head_dim;
+    a.in = ex->op_attn;
+    a.in_has_norm = 0;
+    if (ex->tp > 1) {
+        a.epilogue = kStore;   // tensor parallel: a partial sum for the all-reduce; the operand form follows it
+    } else {
+        a.epilogue = kResidual;
+        a.out = ex->op_hidden;
+        a.out_norm_weight = (const float*)t[kFfnNorm].raw;
+    }
     return a;
 }
-// gate | up of ffn_norm(hidden) with the SwiGLU epilogue: the gated product lands in `gate`
+// gate | up with the SwiGLU epilogue, operand form of the gated product
 GemvArgs gate_up_args(ribn_b200_executor* ex, int l, int T) {
     Tensor* t = &ex->lt(l, 0);
-    GemvArgs a = base_args(ex, T, ex->hidden, ex->cfg.hidden, (const float*)t[kFfnNorm].raw);
+    GemvArgs a = base_args(ex, T);
     a.n_segments = 2;
     a.seg[0] = segment_of(t[kFfnGate], ex->gate);
     a.seg[1] = segment_of(t[kFfnUp], ex->up);
+    a.k = ex->cfg.hidden;
+    a.in = ex->op_hidden;
+    a.in_has_norm = 1;
     a.epilogue = kSwiGLU;
+    a.out = ex->op_act;
     return a;
 }
-// down projection, added into the residual stream
+// down projection, residual add, operand form of the next norm (next layer's or the output norm)
 GemvArgs down_args(ribn_b200_executor* ex, int l, int T) {
+    const ribn_b200_config& c = ex->cfg;
     Tensor* t = &ex->lt(l, 0);
-    GemvArgs a = base_args(ex, T, ex->gate, ex->cfg.ffn, nullptr);
+    GemvArgs a = base_args(ex, T);
     a.n_segments = 1;
     a.seg[0] = segment_of(t[kFfnDown], ex->tp > 1 ? ex->proj : ex->hidden);
-    a.epilogue = ex->tp > 1 ? kStore : kResidual;
+    a.k = c.ffn;
+    a.in = ex->op_act;
+    a.in_has_norm = 0;
+    if (ex->tp > 1) {
+        a.epilogue = kStore;
+    } else {
+        a.epilogue = kResidual;
+        a.out = ex->op_hidden;
+        a.out_norm_weight = l + 1 < c.layers ? (const float*)ex->lt(l + 1, kAttnNorm).raw : (const float*)ex->output_norm.raw;
+    }
     return a;
 }
-// output head over output_norm of `rows` rows of the residual stream (gathered through `index` when given)
-GemvArgs head_args(ribn_b200_executor* ex, int rows, const int32_t* index) {
-    GemvArgs a = base_args(ex, rows, ex->hidden, ex->cfg.hidden, (const float*)ex->output_norm.raw);
-    a.x_index = index;
+// output head over `rows` already normalised rows
+GemvArgs head_args(ribn_b200_executor* ex, int rows, const ActOperand& in) {
+    GemvArgs a = base_args(ex, rows);
     a.n_segments = 1;
     a.seg[0] = segment_of(ex->output, ex->logits);
+    a.k = ex->cfg.hidden;
+    a.in = in;
+    a.in_has_norm = 1;
+    a.epilogue = kStore;
     return a;
 }
 
@@ -350,13 +376,15 @@ cudaError_t run_layers_decode(ribn_b200_executor* ex, const StepPlan& plan, int&
     cudaStream_t s = ex->stream;
     const int T = plan.n_tokens;
     const bool pdl = !(c.flags & RIBN_B200_FLAG_NO_GRAPH);
+    STEP_TRY(launch_to_operand(s, ex->hidden, nullptr, (const float*)ex->lt(0, kAttnNorm).raw, T, c.hidden,
+                               ex->op_hidden));
+    STEP_TRY(launch_gemv_mma(s, qkv_args(ex, 0, T), pdl));
     for (int l = 0; l < c.layers; ++l) {
         Tensor* t = &ex->lt(l, 0);
         __half* ck = ex->cache_k + (long long)l * ex->layer_stride;
         __half* cv = ex->cache_v + (long long)l * ex->layer_stride;
-        STEP_TRY(launch_gemv_mma(s, qkv_args(ex, l, T), pdl));
         if (plan.n_rows == T && c.head_dim >= 64) {
-            // every row adds one token: norm, rotary, cache append and attention in one pass
+            // every row adds one token: norm, rotary, cache append, attention and operand form in one pass
             DecodeAttention d{};
             d.q = ex->q; d.k = ex->k; d.v = ex->v;
             d.q_norm = (const float*)t[kAttnQNorm].raw; d.k_norm = (const float*)t[kAttnKNorm].raw;
@@ -367,7 +395,7 @@ cudaError_t run_layers_decode(ribn_b200_executor* ex, const StepPlan& plan, int&
             d.n_tokens = T; d.q_heads = c.q_heads; d.kv_heads = c.kv_heads; d.head_dim = c.head_dim;
             d.window = 0; d.max_keys = plan.max_keys;
             d.partial = ex->scratch.attn_partial; d.partial_bytes = ex->scratch.attn_partial_bytes;
-            d.out = ex->attn;
+            d.out = ex->attn; d.operand = ex->op_attn;
             d.programmatic = pdl;
             cudaError_t e = launch_attention_decode(s, d, &launches);
             if (e != cudaSuccess) return e;
@@ -381,16 +409,32 @@ cudaError_t run_layers_decode(ribn_b200_executor* ex, const StepPlan& plan, int&
                                              c.head_dim, 0, plan.max_keys, ex->scratch.attn_partial,
                                              ex->scratch.attn_partial_bytes, ex->attn, &launches);
             if (e != cudaSuccess) return e;
+            STEP_TRY(launch_to_operand(s, ex->attn, nullptr, nullptr, T, c.q_heads * c.head_dim, ex->op_attn));
         }
         STEP_TRY(launch_gemv_mma(s, o_args(ex, l, T), pdl));
-        if (ex->tp > 1) { cudaError_t e = tp_reduce_add(ex, T, launches); if (e != cudaSuccess) return e; }
+        if (ex->tp > 1) {
+            cudaError_t e = tp_reduce_add(ex, T, launches);
+            if (e != cudaSuccess) return e;
+            STEP_TRY(launch_to_operand(s, ex->hidden, nullptr, (const float*)t[kFfnNorm].raw, T, c.hidden, ex->op_hidden));
+        }
         STEP_TRY(launch_gemv_mma(s, gate_up_args(ex, l, T), pdl));
         STEP_TRY(launch_gemv_mma(s, down_args(ex, l, T), pdl));
-        if (ex->tp > 1) { cudaError_t e = tp_reduce_add(ex, T, launches); if (e != cudaSuccess) return e; }
+        if (ex->tp > 1) {
+            cudaError_t e = tp_reduce_add(ex, T, launches);
+            if (e != cudaSuccess) return e;
+            const float* next_norm = l + 1 < c.layers ? (const float*)ex->lt(l + 1, kAttnNorm).raw : (const float*)ex->output_norm.raw;
+            STEP_TRY(launch_to_operand(s, ex->hidden, nullptr, next_norm, T, c.hidden, ex->op_hidden));
+        }
+        if (l + 1 < c.layers) STEP_TRY(launch_gemv_mma(s, qkv_args(ex, l + 1, T), pdl));
     }
     if (plan.n_sample > 0) {
-        // Only sampling rows reach the head (crates/nvidia/src/decode.rs:686-704).
-        const GemvArgs a = head_args(ex, plan.n_sample, plan.n_sample != T ? ex->meta.sample_token : nullptr);
+        ActOperand head = ex->op_hidden;  // already normalised with output_norm
+        if (plan.n_sample != T) {
+            STEP_TRY(launch_to_operand(s, ex->hidden, ex->meta.sample_token, (const float*)ex->output_norm.raw,
+                                       plan.n_sample, c.hidden, ex->op_head));
+            head = ex->op_head;
+        }
+        const GemvArgs a = head_args(ex, plan.n_sample, head);
         STEP_TRY(launch_gemv_mma(s, a, pdl));
     }
     return cudaSuccess;
@@ -936,6 +980,17 @@ int ribn_b200_finalize(ribn_b200_executor* ex) {
         CU_TRY(ex, dev_alloc(ex, (unsigned char**)&ex->scratch.attn_partial, ex->scratch.attn_partial_bytes));
     }
     {
+        auto alloc_operand = [&](ActOperand* op, int k) -> cudaError_t {
+            cudaError_t e = dev_alloc(ex, &op->dig, (size_t)kGemvMaxMembers * 3 * k);
+            if (e == cudaSuccess) e = dev_alloc(ex, &op->sx, (size_t)kGemvMaxMembers * (k / 32));
+            if (e == cudaSuccess) e = dev_alloc(ex, &op->sxs16, (size_t)kGemvMaxMembers * (k / 16));
+            if (e == cudaSuccess) e = dev_alloc(ex, &op->ss32, (size_t)kGemvMaxMembers * (k / 32));
+            return e;
+        };
+        CU_TRY(ex, alloc_operand(&ex->op_hidden, c.hidden));
+        CU_TRY(ex, alloc_operand(&ex->op_attn, c.q_heads * c.head_dim));
+        CU_TRY(ex, alloc_operand(&ex->op_act, c.ffn));
+        CU_TRY(ex, alloc_operand(&ex->op_head, c.hidden));
         {
             const int kmax = std::max(std::max(c.hidden, c.ffn), c.q_heads * c.head_dim);
             if (kmax % 256 == 0) {
@@ -1543,7 +1598,7 @@ int ribn_b200_time_projection(ribn_b200_executor* ex, int32_t which, uint32_t re
             case 1: return o_args(ex, l, 1);
             case 2: return gate_up_args(ex, l, 1);
             case 3: return down_args(ex, l, 1);
-            default: return head_args(ex, 1, nullptr);
+            default: return head_args(ex, 1, ex->op_hidden);
         }
     };
     if (which < 0 || which > 4) return fail(ex, "time_projection: which must be 0..4");

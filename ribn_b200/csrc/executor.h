@@ -114,6 +114,8 @@ struct ribn_b200_executor {
     float *hidden = nullptr, *normed = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr,
           *gate = nullptr, *up = nullptr, *head_in = nullptr, *logits = nullptr;
     ribn::StepScratch scratch;
+    // tensor-core operand forms of the activations (decode rows on the fast path)
+    ribn::ActOperand op_hidden, op_attn, op_act, op_head;
     ribn::BatchOperand op_batch;  // batch form, refilled before every batched projection
     ribn::TcOperand op_tc;        // tensor-memory form (the same, for the tcgen05 kernel)
     float* tc_partial = nullptr;  // split-K sums of the tcgen05 kernel

@@ -55,12 +55,37 @@ inline size_t packed_bytes(int type, long long n, long long k) {
 void repack_host(int type, const unsigned char* raw, long long n, long long k, unsigned char* out,
                  int threads);
 
-// Byte order of 32 consecutive signed 8-bit activation digits as the integer MMA's B fragment reads them:
-// lane t's fragment (inputs 4t..4t+3 and 16+4t..16+4t+3) is one 8-byte word,
+// Activations in tensor-core operand form: signed 8-bit digits for the
+// integer MMA.  Every 32 consecutive inputs share a scale sx = max|x| / 127 and
+// each input is carried as three digits d1, d2, d3 in [-127, 127] with
+//     x ~= sx * (d1 + d2 / 128 + d3 / 16384)           (|error| <= max|x| * 2.4e-7)
+// so the integer dot products are exact and the only rounding is this one.
+// Inside a 32-span the bytes are permuted so that lane t's MMA fragment
+// (inputs 4t..4t+3 and 16+4t..16+4t+3) is one 8-byte word:
 //     position(k) = ((k & 15) >> 2) * 8 + ((k >> 4) & 1) * 4 + (k & 3).
+// Alongside: `sxs16` = sx * (sum of the digit values over each 16-span), used
+// to remove the formats' offsets (Q4_K minimum, Q6_K -32, Q8_0 -128), and,
+// when an RMSNorm precedes the projection, `ss32` = sums of squares of the
+// *unscaled* input per 32-span.  The norm weight is already folded into x; the
+// consumer multiplies its result by 1 / sqrt(mean square + eps).  The kernel
+// that produces x writes this form in its epilogue, so the consuming GEMV
+// loads its B operand with plain bulk copies.
+struct ActOperand {
+    signed char* dig = nullptr;  // [members][3][k]
+    float* sx = nullptr;         // [members][k / 32]
+    float* sxs16 = nullptr;      // [members][k / 16]
+    float* ss32 = nullptr;       // [members][k / 32]
+};
+
 __host__ __device__ inline int operand_position(int k) {
     return (k & ~31) + (((k & 15) >> 2) * 8) + (((k >> 4) & 1) * 4) + (k & 3);
 }
+
+// f32 activations -> operand form (standalone; producers fuse the same math).
+// norm_weight == nullptr: x is used as is and ss32 is not written.
+// `index` (optional) gathers rows of x.
+cudaError_t launch_to_operand(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,
+                              int members, int k, ActOperand out);
 
 // One fused GEMV launch covers up to three matrices that share the input
 // vector (q|k|v, gate|up) as consecutive row-tile segments.
@@ -75,22 +100,25 @@ struct GemvSegment {
 enum GemvEpilogue : int {
     kStore = 0,     // y = W x
     kResidual = 1,  // y += W x           (y is the residual stream)
-    kSwiGLU = 2     // two segments (gate, up): silu(gate x) * (up x), written to the first segment's y
+    kSwiGLU = 2     // two segments (gate, up): silu(gate x) * (up x)
 };
 
 struct GemvArgs {
     GemvSegment seg[3];
     int n_segments;
     int k;
-    int members;              // 1..kGemvMaxMembers input vectors
-    const float* x;           // [members][k] F32 input vectors (row m is x_index[m] when an index is given)
-    const int32_t* x_index;   // optional row gather
-    const float* norm_weight; // optional [k]: the inputs are x * norm_weight and the result is multiplied by
-                              // rsqrt(mean(x^2) + eps) (an RMSNorm ahead of the projection)
+    int members;          // 1..kGemvMaxMembers input vectors
+    ActOperand in;        // B operand
+    int in_has_norm;      // multiply the result by rsqrt(mean(ss32) + eps)
     float eps;
-    int epilogue;             // kSwiGLU writes seg[0].y = silu(gate x) * (up x)
-    int* error_flag;          // set non-zero when a bounded wait gives up
-    uint32_t spin_limit;      // polls before a wait gives up (0: the default, 1 << 22)
+    int epilogue;
+    // Optional operand-form copy of the result (kResidual: of the updated
+    // residual stream times `out_norm_weight`; kSwiGLU: of the gated product).
+    ActOperand out;
+    const float* out_norm_weight;
+    float* swiglu_f32;    // optional F32 copy of the gated product [members][n]
+    int* error_flag;      // set non-zero when a bounded wait gives up
+    uint32_t spin_limit;  // polls before a wait gives up (0: the default, 1 << 22)
 };
 
 constexpr int kGemvMaxMembers = 2;

@@ -6,17 +6,13 @@
 // (extract, int->float, FMA) needs far more than that, so the dot products run
 // on the integer tensor-core path, `mma.sync.m16n8k32.s32.u8.s8`, where a
 // quantised weight needs no conversion at all: four packed nibbles become four
-// u8 operands with one AND (a Q8_0 byte is an operand as stored) and products
-// and sums are exact in int32.  The K-quants' integer group scales (6-bit for
-// Q4_K, signed 8-bit per 16 inputs for Q6_K) multiply those integer sums as
-// integers; one F32 step per 256 inputs applies the super-block scale and the
-// activations' scale.  The formats' offsets (Q4_K minimum, Q6_K -32, Q8_0 -128)
-// are removed through per-group sums of the activations.
-//
-// Activations arrive as plain F32 vectors (optionally with an RMSNorm weight to
-// fold in) and every CTA converts them itself, once, into three signed 8-bit
-// digit planes with one scale per 256 inputs: no operand-form hand-over between
-// kernels, and a producer's epilogue is a plain F32 store.
+// u8 operands with one AND (a Q8_0 byte is an operand as stored), products and
+// sums are exact in int32, and one F32 scale per 32 (Q4_K, Q8_0) or 16 (Q6_K)
+// inputs folds the block's scale and the activation span's scale into the
+// accumulator.  The formats' offsets (Q4_K minimum, Q6_K -32, Q8_0 -128) are
+// removed through per-16-input sums of the activations.  Activations arrive as
+// three signed 8-bit digits per input (see ActOperand), produced by the
+// previous kernel's epilogue.
 //
 // Execution: one persistent CTA per SM.  A producer warp streams the CTA's
 // contiguous byte range of weight tiles into a shared-memory ring with bulk
@@ -28,7 +24,9 @@
 // 16 x 256 tile of a stage.  Per unit of 32 output rows the warps leave their
 // partial sums in shared memory and move on; a dedicated epilogue warp adds
 // them in a fixed order (deterministic results) and applies the epilogue:
-// RMSNorm factor, then store, residual add or SwiGLU.
+// store, residual add, SwiGLU, and the operand form of the result for the
+// next projection.  Scale folds and header decodes use the packed FP32 pair
+// instructions of sm_100 (two IEEE operations per issue slot).
 // Every wait is bounded: on expiry the kernel raises an error flag and runs
 // to completion without waiting again.
 #include <cuda_fp16.h>
@@ -157,12 +155,12 @@ constexpr int kEpilogueWarps = kTeams;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = (kConsumerWarps + 1 + kEpilogueWarps) * 32;
 constexpr int kMaxRuns = 4;         // row-tile runs per unit: 2 tiles of one matrix, or 2 x (gate, up)
+constexpr int kHdrStride = 20;      // floats per header row: 16 scales + offset sum + pad (conflict-free rows)
 constexpr int kPlanePad = 32;       // bytes between activation digit planes (distinct banks per plane)
 constexpr uint32_t kSpinLimit = 1u << 22;  // bounded waits: default number of polls before giving up
 constexpr uint32_t kNibbles = 0x0F0F0F0Fu;
 constexpr uint32_t kHighNibbles = 0xF0F0F0F0u;
 constexpr uint32_t kTopBits = 0x30303030u;
-constexpr uint32_t kSixBits = 0x3F3F3F3Fu;
 constexpr int kMagicInt = 0x4B400000;      // bits of 12582912.0f: int accumulate on top of it, read as float
 constexpr float kMagic = 12582912.0f;
 constexpr int kBarFull = 1, kBarFree = 3;  // named barriers of team t, buffer b: full = 1 + 4 t + b, free = 3 + 4 t + b
@@ -209,24 +207,23 @@ __device__ __forceinline__ void bar_arrive(int id, int threads) {
 __device__ __forceinline__ void bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
-// All consumer warps (a barrier id of its own: 1..12 belong to the teams' full / free barriers).
 __device__ __forceinline__ void consumer_barrier() {
-    asm volatile("bar.sync 13, %0;" ::"n"(kConsumerThreads) : "memory");
+    asm volatile("bar.sync 5, %0;" ::"n"(kConsumerThreads) : "memory");
 }
 
-// D = A(u8, 16 x 32) * B(s8, 32 x 8), int32 results.
+// D = A(u8, 16 x 32) * B(s8, 32 x 8) + magic; the result registers are read as floats.
 __device__ __forceinline__ void imma_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1, int init) {
+                                         uint32_t b1) {
     asm(
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(init));
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(kMagicInt));
 }
 __device__ __forceinline__ void imma_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
     asm(
         "mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-        : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+        : "r"(a0), "r"(a1), "r"(b0), "r"(kMagicInt));
 }
 // (a & mask) | other in one LOP3
 __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t other) {
@@ -234,13 +231,17 @@ __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t o
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(other));
     return r;
 }
-// byte i (compile-time) of w, zero- or sign-extended
-template <int I>
-__device__ __forceinline__ int ubyte(uint32_t w) { return (int)__byte_perm(w, 0u, 0x4440u | (uint32_t)I); }
-template <int I>
-__device__ __forceinline__ int sbyte(uint32_t w) { return (int)(signed char)(w >> (8 * I)); }
-__device__ __forceinline__ float half_lo(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu))); }
-__device__ __forceinline__ float half_hi(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w >> 16))); }
+// byte i of w as a float, without the conversion pipe
+__device__ __forceinline__ float byte_f32(uint32_t w, int i) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | (uint32_t)i)) - 8388608.0f;
+}
+
+// bytes i and i + 1 of w as floats minus `bias` (both exact), as one packed subtraction
+__device__ __forceinline__ float2 bytes_f32x2(uint32_t w, int i, float bias) {
+    const float2 raw = make_float2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | (uint32_t)i)),
+                                   __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | (uint32_t)(i + 1))));
+    return __fadd2_rn(raw, make_float2(-bias, -bias));
+}
 
 // Shared-memory accesses by 32-bit shared-space address: the hot loop then needs one add per access
 // instead of generic 64-bit pointer arithmetic.
@@ -264,188 +265,231 @@ __device__ __forceinline__ float2 lds64f(uint32_t addr) {
     asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
     return v;
 }
+__device__ __forceinline__ float lds32f(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
     uint32_t v;
     asm volatile("{\n\t.reg .u16 t;\n\tld.shared.u16 t, [%1];\n\tcvt.u32.u16 %0, t;\n\t}" : "=r"(v) : "r"(addr));
     return v;
 }
+__device__ __forceinline__ void sts128f(uint32_t addr, float a, float b, float c, float d) {
+    asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void sts32f(uint32_t addr, float a) {
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(a) : "memory");
+}
 
 // Shared-memory map of the CTA (generic pointers for set-up and the epilogue warps).
-//
-// The input vectors arrive as F32 and every CTA turns them into the integer-MMA operand form itself, once,
-// before its first tile: per 256 inputs (one k tile) of a member one scale sxt = max|x| / 127 and three signed
-// 8-bit digit planes with  x ~= sxt * (d1 + d2 / 128 + d3 / 16384)  (|error| <= max|x| * 2.4e-7), stored in the
-// MMA's B-fragment byte order (`operand_position`).  Alongside, per k tile: `cs` = the eight MMA columns'
-// scales (sxt times the plane's weight; 0 for the unused columns), so that a row's result is the plain sum
-// over columns of  scale * integer sum;  `t32` / `t16` = the sums of the dequantised inputs over each
-// 32-input group / 16-input sub-group, which remove the formats' offsets (Q4_K minimum, Q6_K -32, Q8_0 -128).
 struct Shared {
     unsigned char* ring;
     signed char* xq;   // [3 * members][K + kPlanePad] digit planes
-    float* cs;         // [k_tiles][8]
-    float* t32;        // [members][k_tiles][8]
-    float* t16;        // [members][k_tiles][16]
-    float* ssw;        // [members][32]: per-warp sums of squares of the raw inputs (RMSNorm)
+    float* sx;         // [members][K / 32]
+    float* sxs;        // [members][K / 16]
+    float* hdr;        // [kConsumerWarps][members][16][kHdrStride]
     float* red;        // [kTeams][2][kTeamWarps][kMaxRuns][members][16]
-    float* zero;       // a zeroed 16-byte word read by the empty MMA columns
-    uint32_t full, empty;  // shared-space addresses of the mbarrier arrays
+    float* scale;      // [kGemvMaxMembers]
+    uint32_t full, empty, xbar;  // shared-space addresses of the mbarrier arrays
+    int K, members;
 };
 
 // Per-lane shared-space addresses of a consumer warp, fixed for the whole kernel.
 struct Lane {
-    uint32_t b;        // this lane's MMA column in the digit planes (+ 8 t), or the zeroed word
+    uint32_t b;        // this lane's MMA column in the digit planes (+ 8 t), or a zeroed word
     uint32_t b_mask;   // all ones for a live column, zero for the empty columns (they read the zeroed word)
-    uint32_t cs;       // column scales of this lane's two columns: cs + kb * 32
-    uint32_t t32, t16; // this lane's member's offset sums: + kb * 32 / + kb * 64
-    int g, t;
-    bool has_member;   // this lane's columns belong to a member (t / 2 < members)
+    uint32_t sx, sxs;  // scale arrays
+    uint32_t hdr_wr;   // decode role: header row (lane >> 1) of member 0
+    uint32_t hdr_rd;   // fold role: header row g of this lane's member (row g + 8 is 8 rows further)
+    int members, K;
+    int half;          // decode role: which half of the row's scales
 };
+
+constexpr uint32_t kHdrRow = kHdrStride * 4;        // bytes per header row
+constexpr uint32_t kHdrMember = 16 * kHdrRow;       // bytes per member's header block
+constexpr uint32_t kHdrOff = 64;                    // byte offset of the row's offset sum
+
+struct Accum {
+    float c[4];  // (row g, col 2t), (row g, col 2t+1), (row g+8, col 2t), (row g+8, col 2t+1)
+    float s[2];  // offset terms of rows g, g+8
+};
+
+// Packed FP32 pairs (sm_100): each component is the same IEEE operation as the scalar form, so the
+// results do not change; the pair form halves the instructions issued for the fold.
+__device__ __forceinline__ void fold(Accum& a, const int (&c)[4], float s0, float s1) {
+    const float2 minus = make_float2(-kMagic, -kMagic);
+    const float2 lo = __fadd2_rn(make_float2(__int_as_float(c[0]), __int_as_float(c[1])), minus);
+    const float2 hi = __fadd2_rn(make_float2(__int_as_float(c[2]), __int_as_float(c[3])), minus);
+    const float2 r0 = __ffma2_rn(make_float2(s0, s0), lo, make_float2(a.c[0], a.c[1]));
+    const float2 r1 = __ffma2_rn(make_float2(s1, s1), hi, make_float2(a.c[2], a.c[3]));
+    a.c[0] = r0.x; a.c[1] = r0.y; a.c[2] = r1.x; a.c[3] = r1.y;
+}
 
 __device__ __forceinline__ uint2 load_b(const Lane& ln, uint32_t offset) {
     return lds64(ln.b + (offset & ln.b_mask));
 }
 
-// A lane's share of the result: rows g and g + 8, the sum over its two MMA columns (both belong to member
-// t / 2).  Lanes whose columns belong to no member (t >= 2 with one member) carry exact zeros, so a row's
-// sums are added in the same order whatever the number of members: batching changes no bit.
-struct Accum {
-    float r[2];
-};
-
-// A tile is processed as two halves of 128 inputs (`hf`), one after the other.
-
-// ---- Q4_K: w = d * (sc * q) - dmin * m ------------------------------------------------------------
-// The 6-bit group scales multiply the integer MMA results as integers (exact); one F32 step per half tile
-// applies d and the column scales; the minima meet the group sums of the inputs.
+// ---- Q4_K: w = gs * q - gm  =>  (gs * sx) * C  -  gm * (sx * sum digits) ------------------------
 template <int MEMBERS>
-__device__ __forceinline__ void tile_q4k(uint32_t tile, const Lane& ln, int kb, int hf, int lane, Accum& acc) {
-    const uint4 h0 = lds128(tile + 2048 + ln.g * 16), h1 = lds128(tile + 2048 + (ln.g + 8) * 16);
-    // scales of this half's four groups as bytes (groups 0..3 sit in word y, 4..7 in w plus two bits of y)
-    const uint32_t s0 = hf ? and_or(h0.w, kNibbles, (h0.y >> 2) & kTopBits) : (h0.y & kSixBits);
-    const uint32_t s1 = hf ? and_or(h1.w, kNibbles, (h1.y >> 2) & kTopBits) : (h1.y & kSixBits);
-    int ae[4] = {0, 0, 0, 0}, ao[4] = {0, 0, 0, 0};  // even groups; odd groups (carrying a factor 16)
-    const uint32_t wbase = tile + hf * 1024 + lane * 16, bbase = kb * 256 + hf * 128;
-#define RIBN_Q4K_STEP(J, BE, BO)                                                                             \
-    {                                                                                                        \
-        const uint4 w = lds128(wbase + J * 512);                                                             \
-        const uint2 be = load_b(ln, bbase + J * 64), bo = load_b(ln, bbase + J * 64 + 32);                   \
-        int ce[4], co[4];                                                                                    \
-        imma_k32(ce, w.x & kNibbles, w.z & kNibbles, w.y & kNibbles, w.w & kNibbles, be.x, be.y, 0);        \
-        imma_k32(co, w.x & kHighNibbles, w.z & kHighNibbles, w.y & kHighNibbles, w.w & kHighNibbles, bo.x, bo.y, 0); \
-        const int e0 = ubyte<BE>(s0), e1 = ubyte<BE>(s1), o0 = ubyte<BO>(s0), o1 = ubyte<BO>(s1);            \
-        ae[0] += e0 * ce[0]; ae[1] += e0 * ce[1]; ae[2] += e1 * ce[2]; ae[3] += e1 * ce[3];                  \
-        ao[0] += o0 * co[0]; ao[1] += o0 * co[1]; ao[2] += o1 * co[2]; ao[3] += o1 * co[3];                  \
-    }
-    RIBN_Q4K_STEP(0, 0, 1)
-    RIBN_Q4K_STEP(1, 2, 3)
-#undef RIBN_Q4K_STEP
-    const float2 cs = lds64f(ln.cs + kb * 32);
-    const float u0 = fmaf((float)ao[0], 0.0625f, (float)ae[0]), u1 = fmaf((float)ao[1], 0.0625f, (float)ae[1]);
-    const float u2 = fmaf((float)ao[2], 0.0625f, (float)ae[2]), u3 = fmaf((float)ao[3], 0.0625f, (float)ae[3]);
-    const float r0 = fmaf(cs.y, u1, cs.x * u0) * half_lo(h0.x), r1 = fmaf(cs.y, u3, cs.x * u2) * half_lo(h1.x);
-    // minima: lane (member t / 2, t % 2) takes two of this half's four groups for both of its rows
-    float off0 = 0.0f, off1 = 0.0f;
-    if (ln.has_member) {
-        const uint32_t m0 = hf ? and_or(h0.w >> 4, kNibbles, (h0.z >> 2) & kTopBits) : (h0.z & kSixBits);
-        const uint32_t m1 = hf ? and_or(h1.w >> 4, kNibbles, (h1.z >> 2) & kTopBits) : (h1.z & kSixBits);
-        const uint32_t p0 = (ln.t & 1) ? m0 >> 16 : m0, p1 = (ln.t & 1) ? m1 >> 16 : m1;
-        const float2 ts = lds64f(ln.t32 + kb * 32 + hf * 16 + (ln.t & 1) * 8);
-        off0 = fmaf((float)ubyte<1>(p0), ts.y, (float)ubyte<0>(p0) * ts.x);
-        off1 = fmaf((float)ubyte<1>(p1), ts.y, (float)ubyte<0>(p1) * ts.x);
-    }
-    acc.r[0] += fmaf(-half_hi(h0.x), off0, r0);
-    acc.r[1] += fmaf(-half_hi(h1.x), off1, r1);
-}
-
-// ---- Q6_K: w = d * sc * (q - 32), one signed 8-bit scale per 16 inputs (k16 MMA) ------------------------
-template <int MEMBERS>
-__device__ __forceinline__ void tile_q6k(uint32_t tile, const Lane& ln, int kb, int hf, int lane, Accum& acc) {
-    // the eight sub-group scales of this half, rows g and g + 8
-    const uint2 s0 = lds64(tile + 3072 + ln.g * 16 + hf * 8), s1 = lds64(tile + 3072 + (ln.g + 8) * 16 + hf * 8);
-    const float d0 = __half2float(__ushort_as_half((unsigned short)lds16(tile + 3328 + ln.g * 2)));
-    const float d1 = __half2float(__ushort_as_half((unsigned short)lds16(tile + 3328 + (ln.g + 8) * 2)));
-    int ai[4] = {0, 0, 0, 0};
-    const uint32_t wbase = tile + lane * 16, bbase = kb * 256 + hf * 128;
-    const uint4 qh = lds128(wbase + 2048 + hf * 512);
-    // sub-group V * 2 + H of the half: word V / 2 of its scales, byte (V % 2) * 2 + H
-#define RIBN_Q6K_STEP(H, V, W0, W1)                                                                           \
-    {                                                                                                         \
-        const uint32_t l0 = (V & 1) ? w.y : w.x, l1 = (V & 1) ? w.w : w.z;                                    \
-        uint32_t t0, t1;                                                                                      \
-        if (V == 0) { t0 = wh0 << 4; t1 = wh1 << 4; }                                                         \
-        else if (V == 1) { t0 = wh0 << 2; t1 = wh1 << 2; }                                                    \
-        else if (V == 2) { t0 = wh0; t1 = wh1; }                                                              \
-        else { t0 = wh0 >> 2; t1 = wh1 >> 2; }                                                                \
-        const uint32_t a0 = and_or(V < 2 ? l0 : l0 >> 4, kNibbles, t0 & kTopBits);                            \
-        const uint32_t a1 = and_or(V < 2 ? l1 : l1 >> 4, kNibbles, t1 & kTopBits);                            \
-        const uint2 b = load_b(ln, bbase + V * 32);                                                           \
-        int cc[4];                                                                                            \
-        imma_k16(cc, a0, a1, H == 0 ? b.x : b.y);                                                             \
-        const int sa = sbyte<(V & 1) * 2 + H>(W0), sb = sbyte<(V & 1) * 2 + H>(W1);                           \
-        ai[0] += sa * cc[0]; ai[1] += sa * cc[1]; ai[2] += sb * cc[2]; ai[3] += sb * cc[3];                   \
-    }
-#define RIBN_Q6K_HALF(H)                                                                                      \
-    {                                                                                                         \
-        const uint4 w = lds128(wbase + (hf * 2 + H) * 512);                                                   \
-        const uint32_t wh0 = H == 0 ? qh.x : qh.z, wh1 = H == 0 ? qh.y : qh.w;                                \
-        RIBN_Q6K_STEP(H, 0, s0.x, s1.x)                                                                       \
-        RIBN_Q6K_STEP(H, 1, s0.x, s1.x)                                                                       \
-        RIBN_Q6K_STEP(H, 2, s0.y, s1.y)                                                                       \
-        RIBN_Q6K_STEP(H, 3, s0.y, s1.y)                                                                       \
-    }
-    RIBN_Q6K_HALF(0)
-    RIBN_Q6K_HALF(1)
-#undef RIBN_Q6K_HALF
-#undef RIBN_Q6K_STEP
-    const float2 cs = lds64f(ln.cs + kb * 32);
-    const float r0 = fmaf(cs.y, (float)ai[1], cs.x * (float)ai[0]);
-    const float r1 = fmaf(cs.y, (float)ai[3], cs.x * (float)ai[2]);
-    // the -32 offset: sum over sub-groups of scale x (sum of the inputs); lane (member t / 2, t % 2) takes four of
-    // this half's eight sub-groups
-    float off0 = 0.0f, off1 = 0.0f;
-    if (ln.has_member) {
-        const uint32_t w0 = (ln.t & 1) ? s0.y : s0.x, w1 = (ln.t & 1) ? s1.y : s1.x;
-        const float4 ts = lds128f(ln.t16 + kb * 64 + hf * 32 + (ln.t & 1) * 16);
-        off0 = (float)sbyte<0>(w0) * ts.x; off0 = fmaf((float)sbyte<1>(w0), ts.y, off0);
-        off0 = fmaf((float)sbyte<2>(w0), ts.z, off0); off0 = fmaf((float)sbyte<3>(w0), ts.w, off0);
-        off1 = (float)sbyte<0>(w1) * ts.x; off1 = fmaf((float)sbyte<1>(w1), ts.y, off1);
-        off1 = fmaf((float)sbyte<2>(w1), ts.z, off1); off1 = fmaf((float)sbyte<3>(w1), ts.w, off1);
-    }
-    acc.r[0] = fmaf(d0, fmaf(-32.0f, off0, r0), acc.r[0]);
-    acc.r[1] = fmaf(d1, fmaf(-32.0f, off1, r1), acc.r[1]);
-}
-
-// ---- Q8_0: stored byte u = q + 128 is the u8 operand as is; w = d_b * (u - 128), one binary16 d per 32 -----
-template <int MEMBERS>
-__device__ __forceinline__ void tile_q8_0(uint32_t tile, const Lane& ln, int kb, int hf, int lane, Accum& acc) {
-    // the four block scales of this half, rows g and g + 8
-    const uint2 e0 = lds64(tile + 4096 + ln.g * 16 + hf * 8), e1 = lds64(tile + 4096 + (ln.g + 8) * 16 + hf * 8);
-    const float2 cs = lds64f(ln.cs + kb * 32);
-    const uint32_t wbase = tile + hf * 2048 + lane * 16, bbase = kb * 256 + hf * 128;
-    const float dd0[4] = {half_lo(e0.x), half_hi(e0.x), half_lo(e0.y), half_hi(e0.y)};
-    const float dd1[4] = {half_lo(e1.x), half_hi(e1.x), half_lo(e1.y), half_hi(e1.y)};
-    float r0 = 0.0f, r1 = 0.0f;
+__device__ __forceinline__ void tile_q4k(uint32_t tile, const Lane& ln, int kb, int lane, Accum& acc) {
+    {
+        // lane -> (row, half): scales and offsets of groups 4 half .. 4 half + 3, for every member
+        const uint4 h = lds128(tile + 2048 + (lane >> 1) * 16);
+        const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
+        const uint32_t sc = ln.half ? ((h.w & kNibbles) | ((h.y >> 2) & kTopBits)) : (h.y & 0x3F3F3F3Fu);
+        const uint32_t mn = ln.half ? (((h.w >> 4) & kNibbles) | ((h.z >> 2) & kTopBits)) : (h.z & 0x3F3F3F3Fu);
+        // Odd groups reach the MMA as 16 q (their nibbles stay in the high half of each byte), so their
+        // scale carries the exact factor 1/16.
+        // pair form of the same operations (packed FP32, sm_100): components 0 / 1 and 2 / 3
+        const float2 dd = make_float2(d, d * 0.0625f), mm2 = make_float2(dmin, dmin);
+        const float2 gs01 = __fmul2_rn(dd, bytes_f32x2(sc, 0, 8388608.0f)), gs23 = __fmul2_rn(dd, bytes_f32x2(sc, 2, 8388608.0f));
+        const float2 gm01 = __fmul2_rn(mm2, bytes_f32x2(mn, 0, 8388608.0f)), gm23 = __fmul2_rn(mm2, bytes_f32x2(mn, 2, 8388608.0f));
 #pragma unroll
-    for (int b4 = 0; b4 < 4; ++b4) {
-        const uint4 w = lds128(wbase + b4 * 512);
-        const uint2 b = load_b(ln, bbase + b4 * 32);
+        for (int mm = 0; mm < MEMBERS; ++mm) {
+            const float4 sx = lds128f(ln.sx + (uint32_t)(mm * (ln.K / 32) + kb * 8 + ln.half * 4) * 4);
+            const uint32_t sxs = ln.sxs + (uint32_t)(mm * (ln.K / 16) + kb * 16 + ln.half * 8) * 4;
+            const float4 sa = lds128f(sxs), sb = lds128f(sxs + 16);
+            const uint32_t out = ln.hdr_wr + mm * kHdrMember;
+            const float2 h01 = __fmul2_rn(gs01, make_float2(sx.x, sx.y)), h23 = __fmul2_rn(gs23, make_float2(sx.z, sx.w));
+            sts128f(out + ln.half * 16, h01.x, h01.y, h23.x, h23.y);
+            const float2 ta = __fadd2_rn(make_float2(sa.x, sa.z), make_float2(sa.y, sa.w));
+            const float2 tb = __fadd2_rn(make_float2(sb.x, sb.z), make_float2(sb.y, sb.w));
+            float off = gm01.x * ta.x;
+            off = fmaf(gm01.y, ta.y, off);
+            off = fmaf(gm23.x, tb.x, off);
+            off = fmaf(gm23.y, tb.y, off);
+            off += __shfl_xor_sync(0xffffffffu, off, 1);
+            if (ln.half == 0) sts32f(out + kHdrOff, -off);
+        }
+    }
+    __syncwarp();
+    const uint32_t wbase = tile + lane * 16, bbase = kb * 256;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint4 w = lds128(wbase + j * 512);
+        const uint2 be = load_b(ln, bbase + j * 64), bo = load_b(ln, bbase + j * 64 + 32);
+        const float2 f0 = lds64f(ln.hdr_rd + j * 8), f1 = lds64f(ln.hdr_rd + 8 * kHdrRow + j * 8);
+        int ce[4], co[4];
+        imma_k32(ce, w.x & kNibbles, w.z & kNibbles, w.y & kNibbles, w.w & kNibbles, be.x, be.y);
+        imma_k32(co, w.x & kHighNibbles, w.z & kHighNibbles, w.y & kHighNibbles, w.w & kHighNibbles, bo.x, bo.y);
+        fold(acc, ce, f0.x, f1.x);
+        fold(acc, co, f0.y, f1.y);
+    }
+    acc.s[0] += lds32f(ln.hdr_rd + kHdrOff);
+    acc.s[1] += lds32f(ln.hdr_rd + 8 * kHdrRow + kHdrOff);
+    __syncwarp();
+}
+
+// ---- Q6_K: w = gs * (q - 32), one scale per 16 inputs (k16 MMA) ---------------------------------
+template <int MEMBERS>
+__device__ __forceinline__ void tile_q6k(uint32_t tile, const Lane& ln, int kb, int lane, Accum& acc) {
+    {
+        // lane -> (row, half): the eight 16-input scales half * 8 .. half * 8 + 7 (groups half * 4 ..)
+        const int row = lane >> 1;
+        const uint2 s8 = lds64(tile + 3072 + row * 16 + ln.half * 8);
+        const float d = __half2float(__ushort_as_half((unsigned short)lds16(tile + 3328 + row * 2)));
+        float gs[8];
+        {
+            // signed byte: flip the sign bit, read as unsigned on top of 2^23, subtract 2^23 + 128 (exact); pair form
+            const float2 dd = make_float2(d, d);
+            const uint32_t lo = s8.x ^ 0x80808080u, hi = s8.y ^ 0x80808080u;
+            const float2 g01 = __fmul2_rn(dd, bytes_f32x2(lo, 0, 8388736.0f)), g23 = __fmul2_rn(dd, bytes_f32x2(lo, 2, 8388736.0f));
+            const float2 g45 = __fmul2_rn(dd, bytes_f32x2(hi, 0, 8388736.0f)), g67 = __fmul2_rn(dd, bytes_f32x2(hi, 2, 8388736.0f));
+            gs[0] = g01.x; gs[1] = g01.y; gs[2] = g23.x; gs[3] = g23.y;
+            gs[4] = g45.x; gs[5] = g45.y; gs[6] = g67.x; gs[7] = g67.y;
+        }
+#pragma unroll
+        for (int mm = 0; mm < MEMBERS; ++mm) {
+            const float4 sx = lds128f(ln.sx + (uint32_t)(mm * (ln.K / 32) + kb * 8 + ln.half * 4) * 4);
+            const uint32_t sxs = ln.sxs + (uint32_t)(mm * (ln.K / 16) + kb * 16 + ln.half * 8) * 4;
+            const float4 sa = lds128f(sxs), sb = lds128f(sxs + 16);
+            const uint32_t out = ln.hdr_wr + mm * kHdrMember;
+            const float2 h01 = __fmul2_rn(make_float2(gs[0], gs[1]), make_float2(sx.x, sx.x));
+            const float2 h23 = __fmul2_rn(make_float2(gs[2], gs[3]), make_float2(sx.y, sx.y));
+            const float2 h45 = __fmul2_rn(make_float2(gs[4], gs[5]), make_float2(sx.z, sx.z));
+            const float2 h67 = __fmul2_rn(make_float2(gs[6], gs[7]), make_float2(sx.w, sx.w));
+            sts128f(out + ln.half * 32, h01.x, h01.y, h23.x, h23.y);
+            sts128f(out + ln.half * 32 + 16, h45.x, h45.y, h67.x, h67.y);
+            float off = gs[0] * sa.x;
+            off = fmaf(gs[1], sa.y, off); off = fmaf(gs[2], sa.z, off); off = fmaf(gs[3], sa.w, off);
+            off = fmaf(gs[4], sb.x, off); off = fmaf(gs[5], sb.y, off); off = fmaf(gs[6], sb.z, off); off = fmaf(gs[7], sb.w, off);
+            off += __shfl_xor_sync(0xffffffffu, off, 1);
+            if (ln.half == 0) sts32f(out + kHdrOff, -32.0f * off);
+        }
+    }
+    __syncwarp();
+    const uint32_t wbase = tile + lane * 16, bbase = kb * 256;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const uint4 qh = lds128(wbase + 2048 + c * 512);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint4 w = lds128(wbase + (c * 2 + h) * 512);
+            const uint32_t wh0 = h == 0 ? qh.x : qh.z, wh1 = h == 0 ? qh.y : qh.w;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const uint32_t l0 = (v & 1) ? w.y : w.x, l1 = (v & 1) ? w.w : w.z;
+                // the variant's two high bits sit at bits 2v..2v+1 of each high-bit byte: move them to bits 4..5
+                uint32_t t0, t1;
+                if (v == 0) { t0 = wh0 << 4; t1 = wh1 << 4; }
+                else if (v == 1) { t0 = wh0 << 2; t1 = wh1 << 2; }
+                else if (v == 2) { t0 = wh0; t1 = wh1; }
+                else { t0 = wh0 >> 2; t1 = wh1 >> 2; }
+                const uint32_t a0 = and_or(v < 2 ? l0 : l0 >> 4, kNibbles, t0 & kTopBits);
+                const uint32_t a1 = and_or(v < 2 ? l1 : l1 >> 4, kNibbles, t1 & kTopBits);
+                const int sub = (c * 4 + v) * 2 + h;
+                const uint2 b = load_b(ln, bbase + (c * 4 + v) * 32);
+                int cc[4];
+                imma_k16(cc, a0, a1, h == 0 ? b.x : b.y);
+                fold(acc, cc, lds32f(ln.hdr_rd + sub * 4), lds32f(ln.hdr_rd + 8 * kHdrRow + sub * 4));
+            }
+        }
+    }
+    acc.s[0] += lds32f(ln.hdr_rd + kHdrOff);
+    acc.s[1] += lds32f(ln.hdr_rd + 8 * kHdrRow + kHdrOff);
+    __syncwarp();
+}
+
+// ---- Q8_0: stored byte u = q + 128 is the u8 operand as is; w = d * (u - 128) -----------------------
+template <int MEMBERS>
+__device__ __forceinline__ void tile_q8_0(uint32_t tile, const Lane& ln, int kb, int lane, Accum& acc) {
+    {
+        const uint2 d4 = lds64(tile + 4096 + (lane >> 1) * 16 + ln.half * 8);
+        float d[4];
+        d[0] = __half2float(__ushort_as_half((unsigned short)(d4.x & 0xffffu)));
+        d[1] = __half2float(__ushort_as_half((unsigned short)(d4.x >> 16)));
+        d[2] = __half2float(__ushort_as_half((unsigned short)(d4.y & 0xffffu)));
+        d[3] = __half2float(__ushort_as_half((unsigned short)(d4.y >> 16)));
+#pragma unroll
+        for (int mm = 0; mm < MEMBERS; ++mm) {
+            const float4 sx = lds128f(ln.sx + (uint32_t)(mm * (ln.K / 32) + kb * 8 + ln.half * 4) * 4);
+            const uint32_t sxs = ln.sxs + (uint32_t)(mm * (ln.K / 16) + kb * 16 + ln.half * 8) * 4;
+            const float4 sa = lds128f(sxs), sb = lds128f(sxs + 16);
+            const uint32_t out = ln.hdr_wr + mm * kHdrMember;
+            sts128f(out + ln.half * 16, d[0] * sx.x, d[1] * sx.y, d[2] * sx.z, d[3] * sx.w);
+            float off = d[0] * (sa.x + sa.y);
+            off = fmaf(d[1], sa.z + sa.w, off);
+            off = fmaf(d[2], sb.x + sb.y, off);
+            off = fmaf(d[3], sb.z + sb.w, off);
+            off += __shfl_xor_sync(0xffffffffu, off, 1);
+            if (ln.half == 0) sts32f(out + kHdrOff, -128.0f * off);
+        }
+    }
+    __syncwarp();
+    const uint32_t wbase = tile + lane * 16, bbase = kb * 256;
+#pragma unroll
+    for (int b8 = 0; b8 < 8; ++b8) {
+        const uint4 w = lds128(wbase + b8 * 512);
+        const uint2 b = load_b(ln, bbase + b8 * 32);
         int cc[4];
-        imma_k32(cc, w.x, w.z, w.y, w.w, b.x, b.y, kMagicInt);
-        const float c0 = __int_as_float(cc[0]) - kMagic, c1 = __int_as_float(cc[1]) - kMagic;
-        const float c2 = __int_as_float(cc[2]) - kMagic, c3 = __int_as_float(cc[3]) - kMagic;
-        r0 = fmaf(dd0[b4], fmaf(cs.y, c1, cs.x * c0), r0);
-        r1 = fmaf(dd1[b4], fmaf(cs.y, c3, cs.x * c2), r1);
+        imma_k32(cc, w.x, w.z, w.y, w.w, b.x, b.y);
+        fold(acc, cc, lds32f(ln.hdr_rd + b8 * 4), lds32f(ln.hdr_rd + 8 * kHdrRow + b8 * 4));
     }
-    // the -128 offset: lane (member t / 2, t % 2) takes two of this half's four blocks
-    float off0 = 0.0f, off1 = 0.0f;
-    if (ln.has_member) {
-        const float2 ts = lds64f(ln.t32 + kb * 32 + hf * 16 + (ln.t & 1) * 8);
-        const bool upper = (ln.t & 1) != 0;
-        off0 = fmaf(upper ? dd0[3] : dd0[1], ts.y, (upper ? dd0[2] : dd0[0]) * ts.x);
-        off1 = fmaf(upper ? dd1[3] : dd1[1], ts.y, (upper ? dd1[2] : dd1[0]) * ts.x);
-    }
-    acc.r[0] += fmaf(-128.0f, off0, r0);
-    acc.r[1] += fmaf(-128.0f, off1, r1);
+    acc.s[0] += lds32f(ln.hdr_rd + kHdrOff);
+    acc.s[1] += lds32f(ln.hdr_rd + 8 * kHdrRow + kHdrOff);
+    __syncwarp();
 }
 
 // Where a unit's rows live: segment index and first row tile.
@@ -467,12 +511,6 @@ struct Cursor {
     int u, r, st;
 };
 
-__device__ __forceinline__ float warp_sum_fixed(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-
 // SHARED = false: each team of eight warps owns whole units (many units per CTA: the output head).
 // SHARED = true: all 24 warps cooperate on every unit, the teams taking alternate stages (the layer
 // projections, which give a CTA only one to three units).
@@ -485,21 +523,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
     const uint32_t spin_limit = a.spin_limit ? a.spin_limit : kSpinLimit;
     const bool swiglu = a.epilogue == kSwiGLU;
     const int runs = swiglu ? 4 : 2;  // row-tile runs per unit
-    const int k_tiles = K / kTileCols;
     Shared sh;
     {
         unsigned char* p = smem_raw;
         sh.ring = p; p += (size_t)slots * slot_bytes;
         sh.xq = reinterpret_cast<signed char*>(p); p += (size_t)planes * (K + kPlanePad);
-        sh.cs = reinterpret_cast<float*>(p); p += (size_t)k_tiles * 8 * sizeof(float);
-        sh.t32 = reinterpret_cast<float*>(p); p += (size_t)MEMBERS * k_tiles * 8 * sizeof(float);
-        sh.t16 = reinterpret_cast<float*>(p); p += (size_t)MEMBERS * k_tiles * 16 * sizeof(float);
-        sh.ssw = reinterpret_cast<float*>(p); p += (size_t)MEMBERS * 32 * sizeof(float);
+        sh.sx = reinterpret_cast<float*>(p); p += (size_t)MEMBERS * (K / 32) * sizeof(float);
+        sh.sxs = reinterpret_cast<float*>(p); p += (size_t)MEMBERS * (K / 16) * sizeof(float);
+        sh.hdr = reinterpret_cast<float*>(p); p += (size_t)kConsumerWarps * MEMBERS * 16 * kHdrStride * sizeof(float);
         sh.red = reinterpret_cast<float*>(p); p += (size_t)2 * kConsumerWarps * kMaxRuns * MEMBERS * 16 * sizeof(float);
-        sh.zero = reinterpret_cast<float*>(p); p += 16;
+        sh.scale = reinterpret_cast<float*>(p); p += 16;  // the zeroed word read by the empty MMA columns
         sh.full = smem_u32(p); p += (size_t)slots * 8;
-        sh.empty = smem_u32(p);
+        sh.empty = smem_u32(p); p += (size_t)slots * 8;
+        sh.xbar = smem_u32(p);
+        sh.K = K; sh.members = MEMBERS;
     }
+    const int k_tiles = K / kTileCols;
     const int stages_per_run = (k_tiles + kStageTiles - 1) / kStageTiles;
     int total_units = 0;
     if (swiglu) total_units = (a.seg[0].row_tiles + 1) / 2;
@@ -509,7 +548,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < slots; ++i) { mbar_init(sh.full + i * 8, 1); mbar_init(sh.empty + i * 8, kTeamWarps); }
-        sh.zero[0] = sh.zero[1] = sh.zero[2] = sh.zero[3] = 0.0f;
+        mbar_init(sh.xbar, 1);
+        sh.scale[0] = sh.scale[1] = sh.scale[2] = sh.scale[3] = 0.0f;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -526,7 +566,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
 
     if (warp == kProducerWarp) {
         // ---------------- producer: team t's k-th stage goes to slot (k % S) * 3 + t ----------------
-        // The weights do not depend on the previous kernel: the ring fills before that kernel has finished.
         if (lane == 0) {
             constexpr int kCursors = SHARED ? 1 : kTeams;
             const int unit_step = SHARED ? 1 : kTeams;
@@ -580,7 +619,26 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
         // ---------------- epilogue warp: lane = one of the unit's 32 output rows ----------------
         const int team = SHARED ? 0 : warp - kEpilogueWarp;
         float inv_norm[MEMBERS];
-        bool have_norm = false;
+#pragma unroll
+        for (int m = 0; m < MEMBERS; ++m) {
+            // RMSNorm factor: fixed-order sum of the producer's per-32 sums of squares.
+            inv_norm[m] = 1.0f;
+            if (a.in_has_norm) {
+                const float* ss = a.in.ss32 + (size_t)m * (K / 32);
+                float sum = 0.0f;
+                // four loads in flight per trip (the additions keep their order)
+                for (int i0 = lane; i0 < K / 32; i0 += 128) {
+                    float part[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) part[u] = i0 + 32 * u < K / 32 ? ss[i0 + 32 * u] : 0.0f;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) sum += part[u];
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                inv_norm[m] = 1.0f / sqrtf(sum / (float)K + a.eps);
+            }
+        }
         int buf = 0;
         for (int u = u0 + team; u < u1; u += unit_step, buf ^= 1) {
             const UnitPlace pl = place_unit(a, swiglu, u);
@@ -595,21 +653,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
             for (int m = 0; m < MEMBERS; ++m) {
                 prior[m] = (valid && a.epilogue == kResidual) ? s.y[(size_t)m * s.n + n_index] : 0.0f;
             }
+            const float norm_w = (valid && a.out.dig != nullptr && a.out_norm_weight != nullptr) ? a.out_norm_weight[n_index] : 1.0f;
             bar_sync(kBarFull + team * 4 + buf, bar_threads);  // the set's warps have left their partial sums of this unit
-            if (!have_norm) {
-                // RMSNorm factor: the consumer warps' sums of squares, added in warp order (they were written
-                // before the consumers' first arrival at this barrier).
-#pragma unroll
-                for (int m = 0; m < MEMBERS; ++m) {
-                    inv_norm[m] = 1.0f;
-                    if (a.norm_weight != nullptr) {
-                        float sum = 0.0f;
-                        for (int w = 0; w < kConsumerWarps; ++w) sum += sh.ssw[m * 32 + w];
-                        inv_norm[m] = 1.0f / sqrtf(sum / (float)K + a.eps);
-                    }
-                }
-                have_norm = true;
-            }
             float v0[MEMBERS], v1[MEMBERS];
             const float* base = sh.red + (size_t)(team * 2 + buf) * kSetWarps * kMaxRuns * MEMBERS * 16;
             const int run0 = swiglu ? 2 * half : half;
@@ -628,96 +673,65 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
             bar_arrive(kBarFree + team * 4 + buf, bar_threads);  // the buffer may be overwritten
 #pragma unroll
             for (int m = 0; m < MEMBERS; ++m) {
+                float result = 0.0f, square = 0.0f;
                 if (valid) {
-                    float* y = s.y + (size_t)m * s.n + n_index;
-                    if (a.epilogue == kResidual) *y = prior[m] + v0[m];
-                    else if (swiglu) *y = v0[m] / (1.0f + expf(-v0[m])) * v1[m];
-                    else *y = v0[m];
+                    if (a.epilogue == kResidual) {
+                        result = prior[m] + v0[m];
+                        s.y[(size_t)m * s.n + n_index] = result;
+                        square = result * result;
+                    } else if (swiglu) {
+                        result = v0[m] / (1.0f + expf(-v0[m])) * v1[m];
+                        if (a.swiglu_f32 != nullptr) a.swiglu_f32[(size_t)m * s.n + n_index] = result;
+                    } else {
+                        result = v0[m];
+                        s.y[(size_t)m * s.n + n_index] = result;
+                    }
+                }
+                if (a.out.dig != nullptr && pl.rt0 * kTileRows < s.n) {
+                    ActOperand out = a.out;
+                    if (a.epilogue != kResidual) out.ss32 = nullptr;
+                    operand_store_span(out, m, s.n, pl.rt0 / 2, lane, result * norm_w, square);
                 }
             }
         }
         return;
     }
 
-    // ---------------- consumers ----------------
-    // First every consumer warp turns its share of the input vectors into the operand form (see Shared).
-    {
-        float ss_local[MEMBERS];
-#pragma unroll
-        for (int m = 0; m < MEMBERS; ++m) ss_local[m] = 0.0f;
-        for (int item = warp; item < MEMBERS * k_tiles; item += kConsumerWarps) {
-            const int m = item / k_tiles, kt = item - m * k_tiles;
-            const float* src = a.x + (size_t)(a.x_index != nullptr ? a.x_index[m] : m) * K + (size_t)kt * kTileCols + lane * 8;
-            const float4 xa = *reinterpret_cast<const float4*>(src), xb = *reinterpret_cast<const float4*>(src + 4);
-            float v[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-            float ssq = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) ssq = fmaf(v[i], v[i], ssq);
-            if (a.norm_weight != nullptr) {
-                const float* wsrc = a.norm_weight + (size_t)kt * kTileCols + lane * 8;
-                const float4 wa = *reinterpret_cast<const float4*>(wsrc), wb = *reinterpret_cast<const float4*>(wsrc + 4);
-                v[0] *= wa.x; v[1] *= wa.y; v[2] *= wa.z; v[3] *= wa.w; v[4] *= wb.x; v[5] *= wb.y; v[6] *= wb.z; v[7] *= wb.w;
-            }
-            float amax = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-            amax = operand_warp_max(amax);
-            const float sxt = amax / 127.0f;
-            const float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
-            uint32_t p1[2] = {0u, 0u}, p2[2] = {0u, 0u}, p3[2] = {0u, 0u};
-            float total = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                int d1, d2, d3;
-                total += operand_digits(v[i], inv, d1, d2, d3);
-                p1[i >> 2] |= ((uint32_t)d1 & 0xffu) << (8 * (i & 3));
-                p2[i >> 2] |= ((uint32_t)d2 & 0xffu) << (8 * (i & 3));
-                p3[i >> 2] |= ((uint32_t)d3 & 0xffu) << (8 * (i & 3));
-            }
-            // inputs 8 lane .. 8 lane + 7 of the tile: span lane / 4, then `operand_position` inside the span
-            signed char* plane = sh.xq + (size_t)(m * 3) * (K + kPlanePad) + kt * kTileCols + (lane >> 2) * 32 +
-                                 16 * (lane & 1) + 4 * ((lane >> 1) & 1);
-            *reinterpret_cast<uint32_t*>(plane) = p1[0];
-            *reinterpret_cast<uint32_t*>(plane + 8) = p1[1];
-            *reinterpret_cast<uint32_t*>(plane + (K + kPlanePad)) = p2[0];
-            *reinterpret_cast<uint32_t*>(plane + (K + kPlanePad) + 8) = p2[1];
-            *reinterpret_cast<uint32_t*>(plane + 2 * (K + kPlanePad)) = p3[0];
-            *reinterpret_cast<uint32_t*>(plane + 2 * (K + kPlanePad) + 8) = p3[1];
-            const float s16 = total + __shfl_xor_sync(0xffffffffu, total, 1);
-            const float s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
-            if ((lane & 1) == 0) sh.t16[((size_t)m * k_tiles + kt) * 16 + (lane >> 1)] = sxt * s16;
-            if ((lane & 3) == 0) sh.t32[((size_t)m * k_tiles + kt) * 8 + (lane >> 2)] = sxt * s32;
-            // column scales: columns 4 m .. 4 m + 2 are this member's digit planes, column 4 m + 3 stays empty
-            if (lane < 4) {
-                const float weight = lane == 0 ? 1.0f : lane == 1 ? (1.0f / 128.0f) : lane == 2 ? (1.0f / 16384.0f) : 0.0f;
-                sh.cs[kt * 8 + m * 4 + lane] = sxt * weight;
-                if (MEMBERS == 1) sh.cs[kt * 8 + 4 + lane] = 0.0f;
-            }
-            ss_local[m] += warp_sum_fixed(ssq);
-        }
-        if (lane == 0) {
-#pragma unroll
-            for (int m = 0; m < MEMBERS; ++m) sh.ssw[m * 32 + warp] = ss_local[m];
+    // ---------------- consumers: a team of eight warps owns whole units; each warp takes one tile per stage ----------------
+    if (warp == 0) {
+        // One copy per lane: digit planes, then the two scale arrays.
+        const uint32_t plane_bytes = (uint32_t)K, sx_bytes = (uint32_t)MEMBERS * (K / 32) * 4u,
+                       sxs_bytes = (uint32_t)MEMBERS * (K / 16) * 4u;
+        if (lane == 0) mbar_expect_tx(sh.xbar, plane_bytes * (uint32_t)planes + sx_bytes + sxs_bytes);
+        __syncwarp();
+        if (lane < planes) {
+            bulk_g2s(smem_u32(sh.xq + (size_t)lane * (K + kPlanePad)), a.in.dig + (size_t)lane * K, plane_bytes, sh.xbar);
+        } else if (lane == planes) {
+            bulk_g2s(smem_u32(sh.sx), a.in.sx, sx_bytes, sh.xbar);
+        } else if (lane == planes + 1) {
+            bulk_g2s(smem_u32(sh.sxs), a.in.sxs16, sxs_bytes, sh.xbar);
         }
     }
-    consumer_barrier();
-    bool alive = true;
+    bool alive = mbar_wait(sh.xbar, 0, a.error_flag, 2, spin_limit);
 
     const int g = lane >> 2, t = lane & 3;
     const int team = warp / kTeamWarps, member_warp = warp % kTeamWarps;
     Lane ln;
     {
+        const uint32_t hdr = smem_u32(sh.hdr) + (uint32_t)warp * MEMBERS * kHdrMember;
         const bool live = (g & 3) < 3 && (g >> 2) < MEMBERS;
-        const int member = (t >> 1) < MEMBERS ? (t >> 1) : 0;
-        ln.has_member = (t >> 1) < MEMBERS;
         ln.b_mask = live ? 0xffffffffu : 0u;
         ln.b = live ? smem_u32(sh.xq) + (uint32_t)((g >> 2) * 3 + (g & 3)) * (uint32_t)(K + kPlanePad) + 8 * t
-                    : smem_u32(sh.zero);
-        ln.cs = smem_u32(sh.cs) + 8 * t;
-        ln.t32 = smem_u32(sh.t32) + (uint32_t)member * k_tiles * 32;
-        ln.t16 = smem_u32(sh.t16) + (uint32_t)member * k_tiles * 64;
-        ln.g = g;
-        ln.t = t;
+                    : smem_u32(sh.scale);
+        ln.sx = smem_u32(sh.sx);
+        ln.sxs = smem_u32(sh.sxs);
+        ln.hdr_wr = hdr + (lane >> 1) * kHdrRow;
+        // lanes whose columns belong to no member (t >= 2 with one member) read member 0's rows: the same
+        // addresses as their neighbours (a broadcast) instead of another block in the same banks
+        ln.hdr_rd = hdr + (uint32_t)min(t >> 1, MEMBERS - 1) * kHdrMember + g * kHdrRow;
+        ln.members = MEMBERS;
+        ln.K = K;
+        ln.half = lane & 1;
     }
     const uint32_t ring = smem_u32(sh.ring);
     const int set = SHARED ? 0 : team, set_warp = SHARED ? warp : member_warp;
@@ -730,7 +744,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
     for (int u = u0 + set; u < u1; u += unit_step, buf ^= 1, ++done) {
         Accum acc[kMaxRuns];
 #pragma unroll
-        for (int r = 0; r < kMaxRuns; ++r) acc[r].r[0] = acc[r].r[1] = 0.0f;
+        for (int r = 0; r < kMaxRuns; ++r) {
+            acc[r].c[0] = acc[r].c[1] = acc[r].c[2] = acc[r].c[3] = 0.0f;
+            acc[r].s[0] = acc[r].s[1] = 0.0f;
+        }
 #pragma unroll
         for (int r = 0; r < kMaxRuns; ++r) {
             if (r >= runs) break;
@@ -746,16 +763,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
                     const int kb = st * kStageTiles + member_warp;
                     if (kb < k_tiles) {
                         const uint32_t tile = ring + slot * (uint32_t)slot_bytes + (uint32_t)(member_warp * tile_bytes);
-                        if (type == kQ4_K) {
-                            tile_q4k<MEMBERS>(tile, ln, kb, 0, lane, acc[r]);
-                            tile_q4k<MEMBERS>(tile, ln, kb, 1, lane, acc[r]);
-                        } else if (type == kQ6_K) {
-                            tile_q6k<MEMBERS>(tile, ln, kb, 0, lane, acc[r]);
-                            tile_q6k<MEMBERS>(tile, ln, kb, 1, lane, acc[r]);
-                        } else {
-                            tile_q8_0<MEMBERS>(tile, ln, kb, 0, lane, acc[r]);
-                            tile_q8_0<MEMBERS>(tile, ln, kb, 1, lane, acc[r]);
-                        }
+                        if (type == kQ4_K) tile_q4k<MEMBERS>(tile, ln, kb, lane, acc[r]);
+                        else if (type == kQ6_K) tile_q6k<MEMBERS>(tile, ln, kb, lane, acc[r]);
+                        else tile_q8_0<MEMBERS>(tile, ln, kb, lane, acc[r]);
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(sh.empty + slot * 8);  // this warp has left the stage
@@ -764,16 +774,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
                 if (++turn == kTeams) turn = 0;
             }
         }
-        // Per-warp partial of (row, member): the lanes of one member's columns are folded in a fixed order.
+        // Per-warp partial of (row, member): digits 1 and 2 are this lane's two columns, digit 3 is the
+        // first column of the next lane; lanes with even t own member t / 2.
         if (done >= 2) bar_sync(kBarFree + set * 4 + buf, bar_threads);  // the epilogue warp has read this buffer
         float* red = sh.red + ((size_t)(set * 2 + buf) * kSetWarps + set_warp) * kMaxRuns * MEMBERS * 16;
 #pragma unroll
         for (int r = 0; r < kMaxRuns; ++r) {
             if (r >= runs) break;
-            float va = acc[r].r[0], vb = acc[r].r[1];
-            va += __shfl_xor_sync(0xffffffffu, va, 1);
-            vb += __shfl_xor_sync(0xffffffffu, vb, 1);
+            const float d3a = __shfl_down_sync(0xffffffffu, acc[r].c[0], 1);
+            const float d3b = __shfl_down_sync(0xffffffffu, acc[r].c[2], 1);
             if ((t & 1) == 0 && (t >> 1) < MEMBERS) {
+                const float va = acc[r].c[0] + acc[r].c[1] * (1.0f / 128.0f) + d3a * (1.0f / 16384.0f) + acc[r].s[0];
+                const float vb = acc[r].c[2] + acc[r].c[3] * (1.0f / 128.0f) + d3b * (1.0f / 16384.0f) + acc[r].s[1];
                 float* dst = red + ((size_t)r * MEMBERS + (t >> 1)) * 16;
                 dst[g] = va;
                 dst[g + 8] = vb;
@@ -784,8 +796,25 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs a,
     }
 }
 
+// f32 rows -> operand form: one warp per 32-span of one member.
+__global__ void to_operand_kernel(const float* x, const int32_t* index, const float* norm_weight, int members, int k,
+                                  ActOperand out) {
+    const int lane = threadIdx.x & 31;
+    const long long span_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long spans = (long long)members * (k / 32);
+    if (span_id >= spans) return;
+    const int m = (int)(span_id / (k / 32)), span = (int)(span_id - (long long)m * (k / 32));
+    const int kk = span * 32 + lane;
+    float v = x[(size_t)(index ? index[m] : m) * k + kk];
+    const float sq = v * v;
+    if (norm_weight != nullptr) v *= norm_weight[kk];
+    ActOperand o = out;
+    if (norm_weight == nullptr) o.ss32 = nullptr;
+    operand_store_span(o, m, k, span, lane, v, sq);
+}
+
 // A wait nobody ends: one thread polls an mbarrier that no copy and no thread completes, through the same
-// bounded wait as the kernel above, and leaves `code` in the error word when the limit runs out.
+// bounded wait as the kernels above, and leaves `code` in the error word when the limit runs out.
 __global__ void wait_probe_kernel(int* error_flag, uint32_t spin_limit, int code) {
     __shared__ __align__(8) unsigned long long bar;
     if (threadIdx.x == 0) {
@@ -834,8 +863,17 @@ cudaError_t launch_wait_probe(cudaStream_t stream, int* error_flag, uint32_t spi
     return cudaGetLastError();
 }
 
+cudaError_t launch_to_operand(cudaStream_t stream, const float* x, const int32_t* index, const float* norm_weight,
+                              int members, int k, ActOperand out) {
+    if (members <= 0 || k % 32 != 0) return cudaErrorInvalidValue;
+    const long long warps = (long long)members * (k / 32);
+    to_operand_kernel<<<(unsigned int)((warps + 3) / 4), 128, 0, stream>>>(x, index, norm_weight, members, k, out);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_gemv_mma(cudaStream_t stream, const GemvArgs& args, bool programmatic) {
-    if (args.members < 1 || args.members > kGemvMaxMembers || args.k % kTileCols != 0 || args.x == nullptr) {
+    if (args.members < 1 || args.members > kGemvMaxMembers || args.k % kTileCols != 0 || args.in.dig == nullptr ||
+        args.in.sx == nullptr || args.in.sxs16 == nullptr || (args.in_has_norm && args.in.ss32 == nullptr)) {
         return cudaErrorInvalidValue;
     }
     int units = 0, slot_bytes = 0;
@@ -851,12 +889,14 @@ cudaError_t launch_gemv_mma(cudaStream_t stream, const GemvArgs& args, bool prog
         const int b = packed_tile_bytes(args.seg[i].type);
         if (b == 0) return cudaErrorInvalidValue;
         slot_bytes = std::max(slot_bytes, b);
+        if (args.out.dig != nullptr && args.seg[i].n % 32 != 0) return cudaErrorInvalidValue;
     }
     if (units <= 0) return cudaSuccess;
-    const int K = args.k, planes = 3 * args.members, k_tiles = K / kTileCols;
+    const int K = args.k, planes = 3 * args.members;
     slot_bytes *= kStageTiles;
-    const size_t fixed = (size_t)planes * (K + kPlanePad) + (size_t)k_tiles * 8 * 4 +
-                         (size_t)args.members * k_tiles * (8 + 16) * 4 + (size_t)args.members * 32 * 4 +
+    const size_t fixed = (size_t)planes * (K + kPlanePad) + (size_t)args.members * (K / 32) * 4 +
+                         (size_t)args.members * (K / 16) * 4 +
+                         (size_t)kConsumerWarps * args.members * 16 * kHdrStride * 4 +
                          (size_t)2 * kConsumerWarps * kMaxRuns * args.members * 16 * 4 + 16 + 8;
     const size_t budget = kSmemBudget;
     if (fixed + (size_t)kTeams * (slot_bytes + 16) > budget) {
@@ -866,8 +906,16 @@ cudaError_t launch_gemv_mma(cudaStream_t stream, const GemvArgs& args, bool prog
             GemvArgs one = args;
             one.members = 1;
             for (int i = 0; i < args.n_segments; ++i) one.seg[i].y = args.seg[i].y + (size_t)m * args.seg[i].n;
-            if (args.x_index != nullptr) one.x_index = args.x_index + m;
-            else one.x = args.x + (size_t)m * K;
+            one.in.dig = args.in.dig + (size_t)m * 3 * K;
+            one.in.sx = args.in.sx + (size_t)m * (K / 32);
+            one.in.sxs16 = args.in.sxs16 + (size_t)m * (K / 16);
+            if (args.in.ss32) one.in.ss32 = args.in.ss32 + (size_t)m * (K / 32);
+            const int n_out = args.seg[0].n;
+            if (args.out.dig) one.out.dig = args.out.dig + (size_t)m * 3 * n_out;
+            if (args.out.sx) one.out.sx = args.out.sx + (size_t)m * (n_out / 32);
+            if (args.out.sxs16) one.out.sxs16 = args.out.sxs16 + (size_t)m * (n_out / 16);
+            if (args.out.ss32) one.out.ss32 = args.out.ss32 + (size_t)m * (n_out / 32);
+            if (args.swiglu_f32) one.swiglu_f32 = args.swiglu_f32 + (size_t)m * n_out;
             cudaError_t e = launch_gemv_mma(stream, one, programmatic);
             if (e != cudaSuccess) return e;
         }

@@ -108,7 +108,8 @@ cudaError_t launch_attention(cudaStream_t stream, const float* q, const __half* 
 
 // Decode form of the same attention for rows that add exactly one token: it
 // also applies the per-head Q/K RMSNorm and rotary to the raw projections,
-// and appends the token's K/V row to the paged cache.
+// appends the token's K/V row to the paged cache, and can emit the result in
+// tensor-core operand form (K = q_heads * head_dim) for the output projection.
 struct DecodeAttention {
     const float* q;   // [T][q_heads][hd] raw q projection
     const float* k;   // [T][kv_heads][hd] raw k projection
@@ -128,6 +129,7 @@ struct DecodeAttention {
     float* partial;
     size_t partial_bytes;
     float* out;
+    ActOperand operand;
     bool programmatic;  // launch as programmatic dependents of the previous kernel in the stream
 };
 cudaError_t launch_attention_decode(cudaStream_t stream, const DecodeAttention& d, int* launches);

@@ -250,8 +250,13 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
                     (int)std::max(1u, std::min(16u, std::thread::hardware_concurrency())));
         unsigned char* d_w = s.upload(packed.data(), packed.size());
         OP_PTR(d_w);
+        ActOperand op;
+        op.dig = s.alloc<signed char>((size_t)members * 3 * cols);
+        op.sx = s.alloc<float>((size_t)members * (cols / 32));
+        op.sxs16 = s.alloc<float>((size_t)members * (cols / 16));
+        op.ss32 = nullptr;
         int* d_err = s.alloc<int>(1);
-        OP_PTR(d_err);
+        OP_PTR(op.dig); OP_PTR(op.sx); OP_PTR(op.sxs16); OP_PTR(d_err);
         OP_TRY(cudaMemsetAsync(d_err, 0, sizeof(int), s.stream));
         if (variant == 3 || variant == 4) {
             // the tensor-memory kernels
@@ -308,6 +313,7 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
                 OP_TRY(launch_gemm_imma(s.stream, a));
             }
         } else {
+        OP_TRY(launch_to_operand(s.stream, d_x, nullptr, nullptr, members, (int)cols, op));
         for (int m0 = 0; m0 < members; m0 += kGemvMaxMembers) {
             GemvArgs a{};
             a.n_segments = 1;
@@ -315,7 +321,11 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
                                    d_y + (size_t)m0 * rows};
             a.k = (int)cols;
             a.members = std::min(kGemvMaxMembers, members - m0);
-            a.x = d_x + (size_t)m0 * cols;
+            a.in.dig = op.dig + (size_t)m0 * 3 * cols;
+            a.in.sx = op.sx + (size_t)m0 * (cols / 32);
+            a.in.sxs16 = op.sxs16 + (size_t)m0 * (cols / 16);
+            a.in_has_norm = 0;
+            a.eps = 0.0f;
             a.epilogue = kStore;
             a.error_flag = d_err;
             OP_TRY(launch_gemv_mma(s.stream, a, false));
