@@ -579,6 +579,64 @@ __device__ __forceinline__ void kq_chunk(int type, const unsigned char* tile, in
     }
 }
 
+// The Q4_K form of kq_chunk for a whole 128-input operand stage (64-input pieces 2 c and 2 c + 1, both row halves
+// of the lane): every shared-memory load is issued before the first use, the 6-bit scales become binary16 through
+// the same byte permute as the quants (no conversion pipe), and the four (piece, row half) conversions are
+// independent instruction streams the scheduler can interleave.
+__device__ __forceinline__ void kq_stage_q4k(const unsigned char* __restrict__ tile, int c, unsigned char* __restrict__ a_planes,
+                                             unsigned char* __restrict__ a2, float2* __restrict__ row_scales, int row0, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint4 w0 = *reinterpret_cast<const uint4*>(tile + (2 * c) * 512 + lane * 16);
+    const uint4 w1 = *reinterpret_cast<const uint4*>(tile + (2 * c + 1) * 512 + lane * 16);
+    const uint4 ha = *reinterpret_cast<const uint4*>(tile + 2048 + g * 16);
+    const uint4 hb = *reinterpret_cast<const uint4*>(tile + 2048 + (g + 8) * 16);
+    const __half2 k1024 = __float2half2_rn(1024.0f), kneg = __float2half2_rn(-1024.0f);
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const uint4 h = rr == 0 ? ha : hb;
+        const int unit_row = row0 + g + 8 * rr;
+        // scales of groups 4 c .. 4 c + 3 of this row, as binary16 (exact)
+        const uint32_t sc4 = c == 0 ? (h.y & 0x3F3F3F3Fu) : ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u));
+        __half2 s01, s23;
+        bytes_to_half_pairs(sc4, s01, s23);
+        s01 = __hsub2(s01, k1024);
+        s23 = __hsub2(s23, k1024);
+        if (c == 0) {
+            if (t == 0) {
+                row_scales[unit_row] = make_float2(__half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu))),
+                                                   __half2float(__ushort_as_half((unsigned short)(h.x >> 16))));
+            }
+            // minima of groups 2 t, 2 t + 1 as binary16, into the first 8-input block of A2
+            const uint32_t mlo = h.z & 0x3F3F3F3Fu, mhi = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+            const uint32_t m4 = t < 2 ? mlo : mhi;
+            __half2 m01, m23;
+            bytes_to_half_pairs(m4, m01, m23);
+            const __half2 mm = __hsub2((t & 1) ? m23 : m01, k1024);
+            *reinterpret_cast<__half2*>(a2 + (unit_row >> 3) * 128 + (unit_row & 7) * 16 + 4 * t) = mm;
+        }
+        unsigned char* row_base = a_planes + (unit_row >> 3) * 128 + (unit_row & 7) * 16;
+#pragma unroll
+        for (int piece = 0; piece < 2; ++piece) {
+            const uint4 w = piece == 0 ? w0 : w1;
+            const __half2 sp = piece == 0 ? s01 : s23;               // (even group's scale, odd group's scale)
+            const __half2 se = __low2half2(sp), so = __high2half2(sp);
+            const __half2 be = __hmul2(se, kneg), bo = __hmul2(so, kneg);
+            unsigned char* base = row_base + ((piece * kChunkK) >> 3) * kALbo;
+            const uint32_t lo16 = rr == 0 ? w.x : w.z, hi16 = rr == 0 ? w.y : w.w;
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+                const uint32_t word = part == 0 ? lo16 : hi16;
+                __half2 e01, e23, o01, o23;
+                bytes_to_half_pairs(word & 0x0F0F0F0Fu, e01, e23);
+                bytes_to_half_pairs((word >> 4) & 0x0F0F0F0Fu, o01, o23);
+                const int k_e = part * 16 + 4 * t, k_o = 32 + k_e;
+                store_half4(base + (k_e >> 3) * kALbo + (k_e & 7) * 2, __hfma2(e01, se, be), __hfma2(e23, se, be));
+                store_half4(base + (k_o >> 3) * kALbo + (k_o & 7) * 2, __hfma2(o01, so, bo), __hfma2(o23, so, bo));
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs a, const KqLayout lay, const int units) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -774,7 +832,9 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
                     // chunk's buffer (at most four chunks back), so it has finished too.
                     unsigned char* a2 = a2_buf + (size_t)(w_count & 1u) * kA2Bytes;
                     float2* scales = row_scales + (size_t)(w_count & 3u) * kRows;
-                    if (present) {
+                    if (present && type == kQ4_K && pieces == 2) {
+                        kq_stage_q4k(tile, c, planes, a2, scales, rt_local * kTileRows, lane);
+                    } else if (present) {
                         for (int piece = 0; piece < pieces; ++piece) {
                             kq_chunk(type, tile, c * pieces + piece, piece * kChunkK, planes, a2, scales, rt_local * kTileRows, 0, lane);
                             kq_chunk(type, tile, c * pieces + piece, piece * kChunkK, planes, a2, scales, rt_local * kTileRows, 1, lane);
