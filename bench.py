@@ -259,6 +259,13 @@ GATE_UP_DRAM_BYTES = {"qwen3-8b": 56982272, "qwen3-8b-4l": 56982272}
 REPEATS = 5   # the headline is the median over this many blocks of --steps steps
 
 
+def decode_workload(args, batch: int) -> dict:
+    """The `config` object of the decode workload: the same for both arms."""
+    return {"workload": f"{args.model} {args.scheme.upper()}-style decode, batch 1 and {batch}, context {args.context}, "
+                        f"16-token KV pages, one replica per GPU",
+            "l2": "inputs larger than L2 (4.9 GB of weights streamed per step)"}
+
+
 def run_ours(args):
     rank, world, local, dist = dist_setup(args.gpus)
     import ribn_b200
@@ -369,10 +376,7 @@ def run_ours(args):
         "ms_per_step": dev1 / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "u8 x s8 integer tensor-core products over Q4_K,Q6_K weights, f32 block scales and accumulation, f16 KV",
         "data": "synthetic",
-        "config": {"workload": f"{args.model} {args.scheme.upper()}-style decode, batch 1 and {B}, context {args.context}, "
-                               f"16-token KV pages, one replica per GPU",
-                   "l2": "inputs larger than L2 (4.9 GB of weights streamed per step)",
-                   "parallelism": f"replicas x{world}"},
+        "config": dict(decode_workload(args, B), parallelism=f"replicas x{world}"),
         "e2e": {"value": e2e1, "unit": "tok/s", "h2d_bytes_per_step": 32, "d2h_bytes_per_step": 4},
         "gpu_launches": launches1, "roofline": kernel_roofline(), "step_roofline": step_roofline(1, dev1),
         "clocks": clocks1, "spread": spread1,
@@ -735,11 +739,11 @@ def run_reference(args):
     sample = (f"{len(times)} decode tokens at batch 1, context {args.context}, {args.model} Q4_K_M-style, "
               f"oracle/oracle.c (restated host decoder), OpenMP over output rows")
     print(json.dumps({
-        "impl": "reference", "metric": f"{args.model} Q4_K_M decode tok/s at batch 1 (per GPU x replicas)",
+        "impl": "reference", "metric": f"{args.model} {args.scheme.upper()} decode tok/s at batch 1 (per GPU x replicas)",
         "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup,
         "ms_per_step": total / len(times) * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.model} Q4_K_M-style decode, batch 1, context {args.context}"},
+        "config": dict(decode_workload(args, args.batch), parallelism=f"replicas x{args.gpus}"),
         "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
