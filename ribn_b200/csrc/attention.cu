@@ -1,16 +1,14 @@
 // Paged-KV ragged attention for decode rows and prefill chunks: split-KV
-// ("flash-decoding") over fixed 64-key spans with an online softmax, then a
+// ("flash-decoding") over spans of 64-key tiles with an online softmax, then a
 // deterministic merge of the spans.
 //
-// One CTA serves one (token, kv head, span); its warps are the q heads of the
-// GQA group, so the group's K/V rows are fetched once per CTA and shared
-// through L1.  Inside a warp the 32 lanes first take 32 different keys (a full
-// head_dim dot product each, no cross-lane reduction, all loads in flight at
-// once), then regroup as 4 key groups x 8 dim chunks for P.V, so every lane
-// again issues independent 128-bit loads; the key groups are folded together
-// once at the end of the span.  Spans depend only on the token's own key
-// range, never on what else is in the batch, so a token's result is
-// bit-identical whatever it is batched with and wherever its pages live.
+// Decode-sized launches run the tensor-core span kernel below (the GQA group's
+// query heads against 16-key slices as m16n8k16 MMAs, K / V staged in shared
+// memory once per group by asynchronous copies).  Prefill-sized launches run
+// the FP32 rows kernel: a CTA serves (4 consecutive tokens, kv head, 64-key
+// span), its warps are the q heads of the group, and the span's K / V rows
+// are staged once for the four tokens.  A token's result depends only on its
+// own keys and on the launch's size class, never on where its pages live.
 //
 // The decode form (FUSED) also applies the per-head Q/K RMSNorm and the NeoX
 // rotary and appends the new K/V row to the paged cache: the CTA that owns
@@ -61,6 +59,7 @@ struct AttnArgs {
     const int32_t* token_slot; // physical slot of the token's own position (fused only)
     int token_base;
     int q_heads, kv_heads, window, max_spans;
+    int tiles;                 // 64-key tiles per span (tensor-core span kernel and its merge); 1 elsewhere
     float* partial;
     float* out;                // [T][q_heads][HD]
     ActOperand operand;        // optional operand form of `out`, K = q_heads * HD
@@ -203,98 +202,6 @@ __device__ __forceinline__ void span_compute(const AttnArgs& a, float* qs, const
     }
 }
 
-template <int HD, bool FUSED>
-__global__ void attention_span_kernel(const AttnArgs a) {
-    constexpr int DPL = HD / 32;  // dims per lane in the lane-strided layout
-    constexpr int CH = HD / 8;    // dims per lane in the P.V phase (8 chunks x 4 key groups)
-    // Programmatic dependent launch: wait for the projections that produced q/k/v, then let the next
-    // kernel (which first only prefetches weights) start.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    extern __shared__ __align__(16) unsigned char attn_smem[];
-    constexpr int kRowHalfs = HD + 8;  // staged K / V rows, padded by 16 bytes so that a lane per key reads conflict-free
-    float* q_smem = reinterpret_cast<float*>(attn_smem);                                 // [warps][HD]
-    __half* k_tile = reinterpret_cast<__half*>(attn_smem + (size_t)(blockDim.x >> 5) * HD * sizeof(float));  // [64][kRowHalfs]
-    __half* v_tile = k_tile + kAttnSpanKeys * kRowHalfs;                                 // [64][kRowHalfs]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int q_per_kv = a.q_heads / a.kv_heads;
-    const int t = a.token_base + blockIdx.x / a.kv_heads, kvh = blockIdx.x % a.kv_heads;
-    const int span = blockIdx.y;
-    const int qh = kvh * q_per_kv + warp;
-    const int pos = a.token_pos[t];
-    const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-    const int n_keys = pos + 1 - first;
-    const int spans = (n_keys + kAttnSpanKeys - 1) / kAttnSpanKeys;
-    if (span >= spans) return;
-    const int begin = first + span * kAttnSpanKeys;
-    const int end = min(pos + 1, begin + kAttnSpanKeys);
-    const int32_t* table = a.page_tables + (long long)(a.token_seq != nullptr ? a.token_seq[t] : 0) * a.pages_per_sequence;
-    const float scale = 1.0f / sqrtf((float)HD);
-    const long long row_stride = (long long)a.kv_heads * HD;
-    const bool owns_self = FUSED && span == spans - 1;  // this CTA's span holds the token's own position
-
-    // The span's K and V rows come to shared memory once for all the query heads of the group, as
-    // asynchronous 16-byte copies that bypass the registers: every piece of the span is in flight at once.
-    // The span's page-table entries (at most five 16-token pages) are fetched first, so that no copy waits
-    // on a table lookup of its own.
-    __shared__ long long page_base[8];
-    {
-        const int page0 = begin / kPageTokens, pages = (end - 1) / kPageTokens - page0 + 1;
-        if ((int)threadIdx.x < pages) page_base[threadIdx.x] = (long long)table[page0 + threadIdx.x] * kPageTokens;
-        __syncthreads();
-        constexpr int kChunks = HD / 8;  // 16-byte pieces per row (a power of two: index arithmetic is shifts)
-        const int pieces = (end - begin) * kChunks;
-        for (int idx = threadIdx.x; idx < pieces; idx += blockDim.x) {
-            const int r = idx / kChunks, c = idx % kChunks;
-            const int key = begin + r;
-            if (owns_self && key == pos) continue;  // the token's own row is produced below
-            const long long phys = page_base[key / kPageTokens - page0] + key % kPageTokens;
-            const long long at = phys * row_stride + (long long)kvh * HD + c * 8;
-            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(k_tile + r * kRowHalfs + c * 8);
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(a.cache_k + at) : "memory");
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)(kAttnSpanKeys * kRowHalfs * sizeof(__half))),
-                         "l"(a.cache_v + at)
-                         : "memory");
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    }
-
-    float* qs = q_smem + warp * HD;
-    {
-        const float* qp = a.q + ((long long)t * a.q_heads + qh) * HD;
-        float x[DPL];
-#pragma unroll
-        for (int i = 0; i < DPL; ++i) x[i] = qp[lane + 32 * i];
-        if (FUSED) norm_rope<HD>(x, a.q_norm, a.inv_freq, a.eps, (float)pos, lane);
-#pragma unroll
-        for (int i = 0; i < DPL; ++i) qs[lane + 32 * i] = x[i];
-    }
-    if (owns_self && warp == 0) {
-        // The token's own K (normalised, rotated) and V, rounded to F16 exactly as the cache holds them.
-        const float* kp = a.k_new + ((long long)t * a.kv_heads + kvh) * HD;
-        const float* vp = a.v_new + ((long long)t * a.kv_heads + kvh) * HD;
-        float x[DPL];
-#pragma unroll
-        for (int i = 0; i < DPL; ++i) x[i] = kp[lane + 32 * i];
-        norm_rope<HD>(x, a.k_norm, a.inv_freq, a.eps, (float)pos, lane);
-        __half* ck = a.cache_k + (long long)a.token_slot[t] * row_stride + (long long)kvh * HD;
-        __half* cv = a.cache_v + (long long)a.token_slot[t] * row_stride + (long long)kvh * HD;
-        __half* k_self = k_tile + (pos - begin) * kRowHalfs;
-        __half* v_self = v_tile + (pos - begin) * kRowHalfs;
-#pragma unroll
-        for (int i = 0; i < DPL; ++i) {
-            const int d = lane + 32 * i;
-            const __half kh = __float2half_rn(x[i]), vh = __float2half_rn(vp[d]);
-            k_self[d] = kh; v_self[d] = vh;
-            ck[d] = kh; cv[d] = vh;
-        }
-    }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();
-
-    span_compute<HD>(a, qs, k_tile, v_tile, begin, begin, end, t, qh, span, spans, scale, lane);
-}
-
 // Prefill steps: consecutive tokens of one sequence see the same keys of a span (up to the diagonal), so a
 // CTA walks kAttnRowsPerCta consecutive tokens and stages the span's K / V rows once for all of them (the
 // copies from L2 into shared memory are what bounds a per-token launch at these sizes).  A token of another
@@ -377,254 +284,515 @@ __global__ void attention_span_rows_kernel(const AttnArgs a, const int n_tokens)
     }
 }
 
-// The same span computation with every warp reading its keys straight from the cache: fewer steps in
-// series, which wins when the launch has too few CTAs to fill the GPU (decode at batch 1 or 2).  Both
-// kernels perform identical arithmetic in identical order.
-template <int HD, bool FUSED, bool EARLY>
-__global__ void __launch_bounds__(EARLY ? 256 : 512) attention_span_direct_kernel(const AttnArgs a) {
-    constexpr int DPL = HD / 32;  // dims per lane in the lane-strided layout
-    constexpr int CH = HD / 8;    // dims per lane in the P.V phase (8 chunks x 4 key groups)
-    // Before the programmatic dependency resolves: the span's K / V rows of earlier positions were written by
-    // earlier steps, and the step's positions and page tables by kernels that completed before the projection
-    // ahead of this one began, so warp 0 asks L2 for those rows while that projection drains.
-    if (threadIdx.x < 32) {
-        const int pt = a.token_base + blockIdx.x / a.kv_heads, pkvh = blockIdx.x % a.kv_heads;
-        const int ppos = a.token_pos[pt];
-        const int pfirst = a.window > 0 ? max(0, ppos - a.window + 1) : 0;
-        const int pbegin = pfirst + (int)blockIdx.y * kAttnSpanKeys, pend = min(ppos + 1, pbegin + kAttnSpanKeys);
-        const int32_t* ptable = a.page_tables + (long long)(a.token_seq != nullptr ? a.token_seq[pt] : 0) * a.pages_per_sequence;
-        for (int key = pbegin + (int)threadIdx.x; key < pend; key += 32) {
-            if (FUSED && key == ppos) continue;  // the token's own row does not exist yet
-            const long long phys = (long long)ptable[key / kPageTokens] * kPageTokens + key % kPageTokens;
-            const long long at = phys * (long long)a.kv_heads * HD + (long long)pkvh * HD;
-#pragma unroll
-            for (int line = 0; line < HD * 2 / 128; ++line) {
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(a.cache_k + at + line * 64));
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(a.cache_v + at + line * 64));
-            }
-        }
-    }
-    // Programmatic dependent launch: wait for the projections that produced q/k/v, then let the next
-    // kernel (which first only prefetches weights) start.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    extern __shared__ __align__(16) unsigned char attn_smem[];
-    float* q_smem = reinterpret_cast<float*>(attn_smem);                                 // [warps][HD]
-    __half* k_self = reinterpret_cast<__half*>(attn_smem + (size_t)(blockDim.x >> 5) * HD * sizeof(float));  // [HD]
-    __half* v_self = k_self + HD;                                                         // [HD]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int q_per_kv = a.q_heads / a.kv_heads;
-    const int t = a.token_base + blockIdx.x / a.kv_heads, kvh = blockIdx.x % a.kv_heads;
-    const int span = blockIdx.y;
-    const int qh = kvh * q_per_kv + warp;
-    const int pos = a.token_pos[t];
+// ---- tensor-core span kernel -----------------------------------------------------------------------
+//
+// A CTA of four warps walks (token, kv head, span) items; a span is `tiles` consecutive 64-key tiles and
+// warp w takes keys [16 w, 16 w + 16) of every tile.  The 16 keys of a slice are the rows of an m16n8k16
+// MMA and the query heads of the GQA group its (up to 8, or 2 x 8) columns, so the K / V rows are read
+// from shared memory once for the whole group:
+//   S^T = K Q^T   A = the K rows as they lie in the cache,
+//                 B = Q as binary16 hi + lo (two MMAs: the F32 query loses nothing that matters), held
+//                     in registers for the whole item;
+//   O^T = V^T P^T A = the V rows through a transposing matrix load,
+//                 B = the probabilities as binary16 hi + lo, moved from the S^T accumulator layout to
+//                     the operand layout by an 8 x 8 matrix transpose across the warp.
+// Products of binary16 values are exact in the F32 accumulators.  Each warp is a pipeline of its own: it
+// copies its next 16-row slice into the second of two shared-memory slots while it multiplies the first
+// (asynchronous copies it alone waits for; no CTA-wide barrier inside the loop) and keeps an online
+// softmax over its slices; the first slice of the CTA's next item is requested under the last slice of
+// the current one.  The four warps' results are folded in warp order and the spans in span order,
+// so a token's result depends on its own keys and on `tiles`, never on its neighbours in the batch or on
+// where its pages live.
+constexpr int kMmaWarps = 4;
+constexpr int kMmaKeys = kAttnSpanKeys / kMmaWarps;  // keys per warp and tile
+static_assert(kMmaKeys == 16, "one k16 step of P.V per warp");
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+// x = hi + lo with both binary16; returns the pair packed for two neighbouring values
+__device__ __forceinline__ void split_pair(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+    const __half2 h = __floats2half2_rn(x0, x1);
+    const float2 back = __half22float2(h);
+    const __half2 l = __floats2half2_rn(x0 - back.x, x1 - back.y);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+__device__ __forceinline__ int token_spans(const AttnArgs& a, int pos) {
     const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-    const int n_keys = pos + 1 - first;
-    const int spans = (n_keys + kAttnSpanKeys - 1) / kAttnSpanKeys;
-    if (span >= spans) return;
-    const int begin = first + span * kAttnSpanKeys;
-    const int end = min(pos + 1, begin + kAttnSpanKeys);
-    const int32_t* table = a.page_tables + (long long)(a.token_seq != nullptr ? a.token_seq[t] : 0) * a.pages_per_sequence;
-    const float scale = 1.0f / sqrtf((float)HD);
-    const long long row_stride = (long long)a.kv_heads * HD;
-    const bool owns_self = FUSED && span == spans - 1;  // this CTA's span holds the token's own position
+    const int span_keys = kAttnSpanKeys * a.tiles;
+    return (pos + 1 - first + span_keys - 1) / span_keys;
+}
 
-    float* qs = q_smem + warp * HD;
-    {
-        const float* qp = a.q + ((long long)t * a.q_heads + qh) * HD;
-        float x[DPL];
+// One warp merges the spans of one (token, q head) in span order:
+// out = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M).  Lane = dimension lane + 32 i.  The first
+// group of spans' values is requested together with the maxima, so a short context costs one round trip.
+template <int HD>
+__device__ __forceinline__ void merge_head(const AttnArgs& a, int t, int qh, int spans, int lane) {
+    constexpr int DPL = HD / 32;
+    constexpr int REC = HD + 2;
+    constexpr int GROUP = DPL <= 4 ? 16 : 8;  // spans whose values are in flight together
+    const float* pp = a.partial + ((long long)(t - a.token_base) * a.q_heads + qh) * a.max_spans * REC;
+    float v[GROUP][DPL];
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) x[i] = qp[lane + 32 * i];
-        if (FUSED) norm_rope<HD>(x, a.q_norm, a.inv_freq, a.eps, (float)pos, lane);
+    for (int u = 0; u < GROUP; ++u) {
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) qs[lane + 32 * i] = x[i];
+        for (int i = 0; i < DPL; ++i) v[u][i] = u < spans ? __ldcg(pp + u * REC + lane + 32 * i) : 0.0f;
     }
-    if (owns_self && warp == 0) {
-        // The token's own K (normalised, rotated) and V, rounded to F16 exactly as the cache holds them.
-        const float* kp = a.k_new + ((long long)t * a.kv_heads + kvh) * HD;
-        const float* vp = a.v_new + ((long long)t * a.kv_heads + kvh) * HD;
-        float x[DPL];
+    float top = -INFINITY;
+    float denom = 0.0f;  // per-lane partial sums in span order, folded in a fixed shuffle order
+    for (int s = lane; s < spans; s += 32) top = fmaxf(top, __ldcg(pp + s * REC + HD));
+    top = warp_max(top);
+    for (int s = lane; s < spans; s += 32) denom = fmaf(__ldcg(pp + s * REC + HD + 1), __expf(__ldcg(pp + s * REC + HD) - top), denom);
+    denom = warp_sum(denom);
+    float sum[DPL];
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) x[i] = kp[lane + 32 * i];
-        norm_rope<HD>(x, a.k_norm, a.inv_freq, a.eps, (float)pos, lane);
-        __half* ck = a.cache_k + (long long)a.token_slot[t] * row_stride + (long long)kvh * HD;
-        __half* cv = a.cache_v + (long long)a.token_slot[t] * row_stride + (long long)kvh * HD;
+    for (int i = 0; i < DPL; ++i) sum[i] = 0.0f;
+    for (int s0 = 0; s0 < spans; s0 += GROUP) {
+        const float mine = s0 + lane < spans ? __expf(__ldcg(pp + (s0 + lane) * REC + HD) - top) : 0.0f;
+        if (s0 > 0) {
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) {
-            const int d = lane + 32 * i;
-            const __half kh = __float2half_rn(x[i]), vh = __float2half_rn(vp[d]);
-            k_self[d] = kh; v_self[d] = vh;
-            ck[d] = kh; cv[d] = vh;
-        }
-    }
-    if (FUSED) __syncthreads(); else __syncwarp();
-
-    const int kg = lane >> 3, dc = lane & 7;
-    float acc[CH];
+            for (int u = 0; u < GROUP; ++u) {
 #pragma unroll
-    for (int d = 0; d < CH; ++d) acc[d] = 0.0f;
-    float run_max = -INFINITY, total = 0.0f;
-    for (int base = begin; base < end; base += 32) {
-        const int key = base + lane;
-        const bool live = key < end;
-        long long phys = 0;
-        float s = -INFINITY;
-        uint4 kk[HD / 8];
-        if (live) {
-            phys = (long long)table[key / kPageTokens] * kPageTokens + key % kPageTokens;
-            const uint4* kp = (owns_self && key == pos)
-                                  ? reinterpret_cast<const uint4*>(k_self)
-                                  : reinterpret_cast<const uint4*>(a.cache_k + phys * row_stride + (long long)kvh * HD);
-#pragma unroll
-            for (int i = 0; i < HD / 8; ++i) kk[i] = kp[i];
-        }
-        // The V rows are requested right behind the K rows (their addresses need only the page lookup), so the two
-        // round trips to memory overlap; lane (kg, dc) takes keys j = 4 jj + kg and dims [dc * CH, dc * CH + CH).
-        const int count = min(32, end - base);
-        uint4 vv[8][CH / 8];
-        auto load_values = [&]() {
-#pragma unroll
-            for (int jj = 0; jj < 8; ++jj) {
-                const int j = jj * 4 + kg;
-                const long long pphys = __shfl_sync(0xffffffffu, phys, j);
-                const bool self = owns_self && base + j == pos;
-                const __half* vp = self ? v_self : a.cache_v + pphys * row_stride + (long long)kvh * HD;
-                if (j < count) {
-#pragma unroll
-                    for (int c = 0; c < CH / 8; ++c) vv[jj][c] = *reinterpret_cast<const uint4*>(vp + dc * CH + c * 8);
-                } else {
-#pragma unroll
-                    for (int c = 0; c < CH / 8; ++c) vv[jj][c] = make_uint4(0u, 0u, 0u, 0u);
-                }
+                for (int i = 0; i < DPL; ++i) v[u][i] = s0 + u < spans ? __ldcg(pp + (s0 + u) * REC + lane + 32 * i) : 0.0f;
             }
-        };
-        // EARLY: groups of at most 8 query heads (256 threads) and head dims up to 128 keep both row sets in registers
-        constexpr bool kEarlyValues = EARLY;
-        if (kEarlyValues) load_values();
-        if (live) {
-            // packed FP32 pairs (sm_100): even and odd dimensions accumulate side by side
-            float2 dot2 = make_float2(0.0f, 0.0f);
-#pragma unroll
-            for (int i = 0; i < HD / 8; ++i) {
-                const float4 qa = *reinterpret_cast<const float4*>(qs + i * 8);
-                const float4 qb = *reinterpret_cast<const float4*>(qs + i * 8 + 4);
-                const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].x));
-                const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].y));
-                const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].z));
-                const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].w));
-                dot2 = __ffma2_rn(make_float2(qa.x, qa.y), k0, dot2);
-                dot2 = __ffma2_rn(make_float2(qa.z, qa.w), k1, dot2);
-                dot2 = __ffma2_rn(make_float2(qb.x, qb.y), k2, dot2);
-                dot2 = __ffma2_rn(make_float2(qb.z, qb.w), k3, dot2);
-            }
-            s = (dot2.x + dot2.y) * scale;
         }
-        const float new_max = fmaxf(run_max, warp_max(s));
-        const float factor = expf(run_max - new_max);  // 0 on the first tile (run_max = -inf)
-        const float p = live ? expf(s - new_max) : 0.0f;
-        total = total * factor + warp_sum(p);
 #pragma unroll
-        for (int d = 0; d < CH; ++d) acc[d] *= factor;
-        run_max = new_max;
-        if (!kEarlyValues) load_values();
-        float pj[8];
+        for (int u = 0; u < GROUP; ++u) {
+            const float w = __shfl_sync(0xffffffffu, mine, u);
+            if (s0 + u < spans) {
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) pj[jj] = __shfl_sync(0xffffffffu, p, jj * 4 + kg);
-#pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-#pragma unroll
-            for (int c = 0; c < CH / 8; ++c) {
-                const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].x));
-                const float2 v1 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].y));
-                const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].z));
-                const float2 v3 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].w));
-                float* o = acc + c * 8;
-                const float2 pp = make_float2(pj[jj], pj[jj]);
-                const float2 o0 = __ffma2_rn(pp, v0, make_float2(o[0], o[1]));
-                const float2 o1 = __ffma2_rn(pp, v1, make_float2(o[2], o[3]));
-                const float2 o2 = __ffma2_rn(pp, v2, make_float2(o[4], o[5]));
-                const float2 o3 = __ffma2_rn(pp, v3, make_float2(o[6], o[7]));
-                o[0] = o0.x; o[1] = o0.y; o[2] = o1.x; o[3] = o1.y; o[4] = o2.x; o[5] = o2.y; o[6] = o3.x; o[7] = o3.y;
+                for (int i = 0; i < DPL; ++i) sum[i] = fmaf(v[u][i], w, sum[i]);
             }
         }
     }
-    // Fold the four key groups (fixed order: xor 8, then xor 16).
+    ActOperand op = a.operand;
+    op.ss32 = nullptr;
 #pragma unroll
-    for (int d = 0; d < CH; ++d) {
-        acc[d] += __shfl_xor_sync(0xffffffffu, acc[d], 8);
-        acc[d] += __shfl_xor_sync(0xffffffffu, acc[d], 16);
-    }
-    if (spans == 1) {
-        if (kg == 0) {
-            const float inv = 1.0f / total;
-            float* op = a.out + ((long long)t * a.q_heads + qh) * HD + dc * CH;
-#pragma unroll
-            for (int d = 0; d < CH; ++d) { acc[d] *= inv; op[d] = acc[d]; qs[dc * CH + d] = acc[d]; }
-        }
-        if (a.operand.dig != nullptr) {
-            // back to one input per lane: lane takes dims lane + 32 i of this head
-            __syncwarp();
-            ActOperand op = a.operand;
-            op.ss32 = nullptr;
-            const int K = a.q_heads * HD, m = t - a.token_base;
-#pragma unroll
-            for (int i = 0; i < DPL; ++i) operand_store_span(op, m, K, (qh * HD) / 32 + i, lane, qs[lane + 32 * i], 0.0f);
-        }
-    } else if (kg == 0) {
-        float* pp = a.partial + (((long long)(t - a.token_base) * a.q_heads + qh) * a.max_spans + span) * (HD + 2);
-#pragma unroll
-        for (int d = 0; d < CH; ++d) pp[dc * CH + d] = acc[d];
-        if (dc == 0) { pp[HD] = run_max; pp[HD + 1] = total; }
+    for (int i = 0; i < DPL; ++i) {
+        const float value = sum[i] / denom;
+        a.out[((long long)t * a.q_heads + qh) * HD + lane + 32 * i] = value;
+        if (op.dig != nullptr) operand_store_span(op, t - a.token_base, a.q_heads * HD, (qh * HD) / 32 + i, lane, value, 0.0f);
     }
 }
 
-// Merge a token's spans in span order: out = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M).
-// One block of HD threads per (token, q head).
 template <int HD>
-__global__ void attention_merge_kernel(const AttnArgs a) {
-    __shared__ float weight[kAttnMaxSpans];
-    __shared__ float denom_s;
+struct MmaLayout {
+    static constexpr int RH = HD + 8;                    // halfs per staged row: 16 bytes of padding keep the matrix loads conflict-free
+    static constexpr int STAGES = 2;                     // ring slots per warp: one slice multiplied, the next in flight
+    static constexpr int SLOT = 2 * kMmaKeys * RH;       // halfs per slot: 16 K rows, then 16 V rows
+    // [q rows] hi, the same lo, the token's own K / V row, then the rings
+    static size_t bytes(int q_per_kv) {
+        return ((size_t)2 * q_per_kv * RH + 2 * RH + (size_t)kMmaWarps * STAGES * SLOT) * sizeof(__half);
+    }
+};
+
+// One unit of work: a span of one (token, kv head).
+struct SpanItem {
+    int t, kvh, span, pos, spans, begin, end, n_tiles;
+    const int32_t* table;
+    bool owns_self;
+};
+
+template <int HD, bool FUSED, int NT>
+__global__ void __launch_bounds__(kMmaWarps * 32, HD <= 128 && NT == 1 ? 3 : 1) attention_span_mma_kernel(const AttnArgs a, const int n_tokens) {
+    using L = MmaLayout<HD>;
+    constexpr int DPL = HD / 32;
+    constexpr int RH = L::RH;
+    constexpr int CPR = HD / 8;       // 16-byte pieces per row
+    constexpr int REC = HD + 2;       // floats per head record: accumulators, maximum, sum
+    constexpr int STAGES = L::STAGES;
+    static_assert(STAGES == 2, "the slot arithmetic below alternates two slots");
+    extern __shared__ __align__(16) unsigned char attn_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int q_per_kv = a.q_heads / a.kv_heads;
+    __half* q_hi = reinterpret_cast<__half*>(attn_smem);       // [q_per_kv][RH]
+    __half* q_lo = q_hi + q_per_kv * RH;
+    __half* k_self = q_lo + q_per_kv * RH;                     // [RH]
+    __half* v_self = k_self + RH;                              // [RH]
+    __half* ring = v_self + RH + warp * (STAGES * L::SLOT);    // this warp's slots
+    const long long row_stride = (long long)a.kv_heads * HD;
+    const int span_keys = kAttnSpanKeys * a.tiles;
+    const int total_items = n_tokens * a.kv_heads * a.max_spans;
+
+    // The CTA walks items blockIdx.x, blockIdx.x + gridDim.x, ...; spans past a token's last key are skipped.
+    // Positions and page tables were written by kernels that completed before the projection ahead of
+    // this one began, so they may be read before the programmatic dependency resolves.
+    auto next_item = [&](int& id, SpanItem& it) -> bool {
+        for (id += gridDim.x; id < total_items; id += gridDim.x) {
+            it.span = id % a.max_spans;
+            const int tk = id / a.max_spans;
+            it.kvh = tk % a.kv_heads;
+            it.t = a.token_base + tk / a.kv_heads;
+            it.pos = a.token_pos[it.t];
+            const int first = a.window > 0 ? max(0, it.pos - a.window + 1) : 0;
+            it.spans = (it.pos + 1 - first + span_keys - 1) / span_keys;
+            if (it.span >= it.spans) continue;
+            it.table = a.page_tables + (long long)(a.token_seq != nullptr ? a.token_seq[it.t] : 0) * a.pages_per_sequence;
+            it.begin = first + it.span * span_keys;
+            it.end = min(it.pos + 1, it.begin + span_keys);
+            it.n_tiles = (it.end - it.begin + kAttnSpanKeys - 1) / kAttnSpanKeys;
+            it.owns_self = FUSED && it.span == it.spans - 1;  // this span holds the token's own position
+            return true;
+        }
+        return false;
+    };
+    // Slice i of this warp: keys [begin + 64 i + 16 warp, + 16).  Lane l looks up the cache row of key l & 15.
+    auto slice_rows = [&](const SpanItem& it, int i) -> int {
+        const int key = it.begin + i * kAttnSpanKeys + warp * kMmaKeys + (lane & 15);
+        if (i >= it.n_tiles || key >= it.end) return 0;
+        return it.table[key / kPageTokens] * kPageTokens + key % kPageTokens;
+    };
+    // Asynchronous 16-byte copies of the slice's K and V rows into slot `slot` (every piece in flight at
+    // once): lane l takes piece l % CPR of rows l / CPR, l / CPR + 32 / CPR, ...  Rows past the token's last
+    // key are zero, so that a zero probability meets no NaN.  One copy group per call, empty or not.
+    const uint32_t ring_at = smem_u32(ring) + ((lane / CPR) * RH + (lane % CPR) * 8) * 2;
+    constexpr int kRowsPerPass = 32 / CPR;
+    auto issue = [&](const SpanItem& it, int i, int rows, int slot) {
+        const __half* k_src = a.cache_k + (long long)it.kvh * HD + (lane % CPR) * 8;
+        const __half* v_src = a.cache_v + (long long)it.kvh * HD + (lane % CPR) * 8;
+        const int wbegin = it.begin + i * kAttnSpanKeys + warp * kMmaKeys;
+        const int wcount = max(0, min(kMmaKeys, it.end - wbegin));
+        const uint32_t k_at = ring_at + slot * (L::SLOT * 2);
+        const uint32_t v_at = k_at + kMmaKeys * RH * 2;
+        if (wcount == kMmaKeys && !(it.owns_self && it.pos < wbegin + kMmaKeys)) {
+#pragma unroll
+            for (int j = 0; j < kMmaKeys / kRowsPerPass; ++j) {
+                const long long at = (long long)__shfl_sync(0xffffffffu, rows, j * kRowsPerPass + lane / CPR) * row_stride;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(k_at + j * (kRowsPerPass * RH * 2)), "l"(k_src + at) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(v_at + j * (kRowsPerPass * RH * 2)), "l"(v_src + at) : "memory");
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < kMmaKeys / kRowsPerPass; ++j) {
+                const int r = j * kRowsPerPass + lane / CPR;
+                const long long at = (long long)__shfl_sync(0xffffffffu, rows, r) * row_stride;
+                if (it.owns_self && wbegin + r == it.pos) continue;  // the token's own row arrives from k_self / v_self
+                if (r < wcount) {
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(k_at + j * (kRowsPerPass * RH * 2)), "l"(k_src + at) : "memory");
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(v_at + j * (kRowsPerPass * RH * 2)), "l"(v_src + at) : "memory");
+                } else {
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(k_at + j * (kRowsPerPass * RH * 2)), "r"(0) : "memory");
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_at + j * (kRowsPerPass * RH * 2)), "r"(0) : "memory");
+                }
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    SpanItem cur;
+    int id = (int)blockIdx.x - (int)gridDim.x;
+    bool valid = next_item(id, cur);
+    // This warp's slices form one sequence across the CTA's items: slice c lives in slot c & 1, and while
+    // slice c is multiplied slice c + 1 (the item's next, or the first of the next item) is in flight.
+    int c = 0;
+    int rows0 = 0, rows1 = 0;  // cache rows of the current item's slices 0 and 1
+    if (valid) { rows0 = slice_rows(cur, 0); rows1 = slice_rows(cur, 1); }
+    // Decode rows: every earlier key was written by an earlier step, so the first copies start while the
+    // projection ahead of this kernel drains.  Otherwise the rows may come from the kernel just before.
+    if (FUSED && valid) issue(cur, 0, rows0, 0);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int t = a.token_base + blockIdx.x / a.q_heads, qh = blockIdx.x % a.q_heads;
-    const int pos = a.token_pos[t];
-    const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-    const int spans = (pos + 1 - first + kAttnSpanKeys - 1) / kAttnSpanKeys;
+    if (!FUSED && valid) issue(cur, 0, rows0, 0);
+
+    const int g = lane >> 2, t4 = lane & 3;
+    const float scale = 1.0f / sqrtf((float)HD);
+    // matrix-load offsets inside a slot: K rows as the A operand, V rows transposed as the A operand
+    const uint32_t k_off = ((lane & 15) * RH + (lane >> 4) * 8) * 2;
+    const uint32_t v_off = (kMmaKeys * RH + ((lane & 7) + (lane >> 4) * 8) * RH + ((lane >> 3) & 1) * 8) * 2;
+    // Raw projections of an item, requested one item ahead: this warp's first two query heads, and the
+    // token's new K / V row for the warp that produces it.
+    constexpr int kAhead = 2;
+    const int self_warp = q_per_kv & (kMmaWarps - 1);
+    float qx[kAhead][DPL], kx[DPL], vx[DPL];
+    auto fetch_raw = [&](const SpanItem& it) {
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+            const int h = warp + u * kMmaWarps;
+            if (h < q_per_kv) {
+                const float* qp = a.q + ((long long)it.t * a.q_heads + it.kvh * q_per_kv + h) * HD;
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) qx[u][i] = qp[lane + 32 * i];
+            }
+        }
+        if (it.owns_self && warp == self_warp) {
+            const float* kp = a.k_new + ((long long)it.t * a.kv_heads + it.kvh) * HD;
+            const float* vp = a.v_new + ((long long)it.t * a.kv_heads + it.kvh) * HD;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) { kx[i] = kp[lane + 32 * i]; vx[i] = vp[lane + 32 * i]; }
+        }
+    };
+    if (valid) fetch_raw(cur);
+
+    while (valid) {
+        // The item after this one: its first copies are issued under this item's last slice, so the stream of
+        // copies does not pause for this item's fold or the next item's set-up.
+        SpanItem nxt;
+        int nid = id;
+        const bool nvalid = next_item(nid, nxt);
+        int nrows0 = 0, nrows1 = 0;
+        if (nvalid) { nrows0 = slice_rows(nxt, 0); nrows1 = slice_rows(nxt, 1); }
+
+        // The group's queries (normalised and rotated here for decode rows) as binary16 hi + lo rows.
+        {
+            int u = 0;
+            for (int h = warp; h < q_per_kv; h += kMmaWarps, ++u) {
+                float x[DPL];
+                if (u < kAhead) {
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) x[i] = u == 0 ? qx[0][i] : qx[1][i];
+                } else {
+                    const float* qp = a.q + ((long long)cur.t * a.q_heads + cur.kvh * q_per_kv + h) * HD;
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) x[i] = qp[lane + 32 * i];
+                }
+                if (FUSED) norm_rope<HD>(x, a.q_norm, a.inv_freq, a.eps, (float)cur.pos, lane);
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) {
+                    const __half hi = __float2half_rn(x[i]);
+                    q_hi[h * RH + lane + 32 * i] = hi;
+                    q_lo[h * RH + lane + 32 * i] = __float2half_rn(x[i] - __half2float(hi));
+                }
+            }
+        }
+        if (cur.owns_self && warp == self_warp) {
+            // The token's own K (normalised, rotated) and V, rounded to F16 exactly as the cache holds them.
+            norm_rope<HD>(kx, a.k_norm, a.inv_freq, a.eps, (float)cur.pos, lane);
+            __half* ck = a.cache_k + (long long)a.token_slot[cur.t] * row_stride + (long long)cur.kvh * HD;
+            __half* cv = a.cache_v + (long long)a.token_slot[cur.t] * row_stride + (long long)cur.kvh * HD;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) {
+                const int d = lane + 32 * i;
+                const __half kh = __float2half_rn(kx[i]), vh = __float2half_rn(vx[i]);
+                k_self[d] = kh; v_self[d] = vh;
+                ck[d] = kh; cv[d] = vh;
+            }
+        }
+        if (nvalid) fetch_raw(nxt);
+        __syncthreads();  // queries and own row in place; every warp is done with the previous item's records
+        // This lane's B fragments of Q^T: head 8 nt + g, dimensions 16 ks + 2 t4 + {0, 1} and + 8.
+        uint32_t qh[NT][HD / 16][2], ql[NT][HD / 16][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const int h = nt * 8 + g;
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int at = h * RH + ks * 16 + 2 * t4 + 8 * u;
+                    qh[nt][ks][u] = h < q_per_kv ? *reinterpret_cast<const uint32_t*>(q_hi + at) : 0u;
+                    ql[nt][ks][u] = h < q_per_kv ? *reinterpret_cast<const uint32_t*>(q_lo + at) : 0u;
+                }
+            }
+        }
+        // O^T accumulators: [dims 16 mt + g (values 0, 1) and + 8 (values 2, 3)] x [heads 8 nt + 2 t4 + {0, 1}]
+        float o[NT][HD / 16][4];
+        float run_m[NT][2], run_l[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+            for (int mt = 0; mt < HD / 16; ++mt) { o[nt][mt][0] = o[nt][mt][1] = o[nt][mt][2] = o[nt][mt][3] = 0.0f; }
+            run_m[nt][0] = run_m[nt][1] = -INFINITY;
+            run_l[nt][0] = run_l[nt][1] = 0.0f;
+        }
+        for (int i = 0; i < cur.n_tiles; ++i, ++c) {
+            if (i + 1 < cur.n_tiles) {
+                issue(cur, i + 1, rows1, (c + 1) & 1);
+                rows1 = slice_rows(cur, i + 2);
+            } else if (nvalid) {
+                issue(nxt, 0, nrows0, (c + 1) & 1);
+            } else {
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            }
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+            const int wbegin = cur.begin + i * kAttnSpanKeys + warp * kMmaKeys;
+            if (wbegin >= cur.end) continue;  // a short last tile: nothing for this warp
+            __half* k_w = ring + (c & 1) * L::SLOT;
+            if (cur.owns_self && cur.pos >= wbegin && cur.pos < wbegin + kMmaKeys) {
+                // the token's own row takes its place in the slice (8 bytes per lane and row)
+                for (int q4 = lane; q4 < HD / 4; q4 += 32) {
+                    *reinterpret_cast<uint2*>(k_w + (cur.pos - wbegin) * RH + q4 * 4) = *reinterpret_cast<const uint2*>(k_self + q4 * 4);
+                    *reinterpret_cast<uint2*>(k_w + (kMmaKeys + cur.pos - wbegin) * RH + q4 * 4) = *reinterpret_cast<const uint2*>(v_self + q4 * 4);
+                }
+            }
+            __syncwarp();
+            // S^T: keys g (values 0, 1) and g + 8 (values 2, 3) x heads 8 nt + 2 t4 + {0, 1}; the hi and lo
+            // products accumulate apart (two shorter dependency chains) and meet at the end
+            float sh[NT][4], sl[NT][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) { sh[nt][0] = sh[nt][1] = sh[nt][2] = sh[nt][3] = 0.0f; sl[nt][0] = sl[nt][1] = sl[nt][2] = sl[nt][3] = 0.0f; }
+            {
+                const uint32_t k_at = smem_u32(k_w) + k_off;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    uint32_t ka[4];
+                    ldmatrix_x4(ka, k_at + ks * 32);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        mma_f16(sh[nt], ka, qh[nt][ks][0], qh[nt][ks][1]);
+                        mma_f16(sl[nt], ka, ql[nt][ks][0], ql[nt][ks][1]);
+                    }
+                }
+            }
+            const bool live0 = wbegin + g < cur.end, live1 = wbegin + g + 8 < cur.end;
+            uint32_t ph[NT][2], pl[NT][2];
+            bool moved = false;
+            float f[NT][2];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const float s0 = live0 ? (sh[nt][0] + sl[nt][0]) * scale : -INFINITY;
+                const float s1 = live0 ? (sh[nt][1] + sl[nt][1]) * scale : -INFINITY;
+                const float s2 = live1 ? (sh[nt][2] + sl[nt][2]) * scale : -INFINITY;
+                const float s3 = live1 ? (sh[nt][3] + sl[nt][3]) * scale : -INFINITY;
+                float ma = fmaxf(s0, s2), mb = fmaxf(s1, s3);  // heads 2 t4 and 2 t4 + 1 over this lane's keys
+#pragma unroll
+                for (int x = 4; x < 32; x <<= 1) {
+                    ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, x));
+                    mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, x));
+                }
+                ma = fmaxf(ma, run_m[nt][0]); mb = fmaxf(mb, run_m[nt][1]);
+                moved = moved || ma != run_m[nt][0] || mb != run_m[nt][1];
+                f[nt][0] = __expf(run_m[nt][0] - ma); f[nt][1] = __expf(run_m[nt][1] - mb);  // 0 on the first slice
+                run_m[nt][0] = ma; run_m[nt][1] = mb;
+                const float p0 = __expf(s0 - ma), p1 = __expf(s1 - mb), p2 = __expf(s2 - ma), p3 = __expf(s3 - mb);
+                float la = p0 + p2, lb = p1 + p3;
+#pragma unroll
+                for (int x = 4; x < 32; x <<= 1) {
+                    la += __shfl_xor_sync(0xffffffffu, la, x);
+                    lb += __shfl_xor_sync(0xffffffffu, lb, x);
+                }
+                run_l[nt][0] = fmaf(run_l[nt][0], f[nt][0], la);
+                run_l[nt][1] = fmaf(run_l[nt][1], f[nt][1], lb);
+                // (key, head pair) -> (head, key pair): the operand layout of P^T
+                uint32_t h0, l0, h1, l1;
+                split_pair(p0, p1, h0, l0);
+                split_pair(p2, p3, h1, l1);
+                ph[nt][0] = movmatrix_trans(h0); ph[nt][1] = movmatrix_trans(h1);
+                pl[nt][0] = movmatrix_trans(l0); pl[nt][1] = movmatrix_trans(l1);
+            }
+            if (i > 0 && __any_sync(0xffffffffu, moved)) {  // a factor of exactly 1 changes nothing
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                    for (int mt = 0; mt < HD / 16; ++mt) {
+                        o[nt][mt][0] *= f[nt][0]; o[nt][mt][1] *= f[nt][1]; o[nt][mt][2] *= f[nt][0]; o[nt][mt][3] *= f[nt][1];
+                    }
+                }
+            }
+            const uint32_t v_at = smem_u32(k_w) + v_off;
+#pragma unroll
+            for (int mt = 0; mt < HD / 16; ++mt) {
+                uint32_t va[4];
+                ldmatrix_x4_trans(va, v_at + mt * 32);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    mma_f16(o[nt][mt], va, ph[nt][0], ph[nt][1]);
+                    mma_f16(o[nt][mt], va, pl[nt][0], pl[nt][1]);
+                }
+            }
+            __syncwarp();  // every lane has read the slot before the next copies land in it
+        }
+        // This warp's result goes where its last slice was: that slot receives no copy before the next
+        // item's first barrier, which every warp passes only after the fold below.
+        const int rec_slot = (c - 1) & 1;
+        float* rec = reinterpret_cast<float*>(ring + rec_slot * L::SLOT);
+        if (cur.begin + warp * kMmaKeys < cur.end) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int h = nt * 8 + 2 * t4;
+#pragma unroll
+                for (int mt = 0; mt < HD / 16; ++mt) {
+                    const int d = mt * 16 + g;
+                    if (h < q_per_kv) { rec[h * REC + d] = o[nt][mt][0]; rec[h * REC + d + 8] = o[nt][mt][2]; }
+                    if (h + 1 < q_per_kv) { rec[(h + 1) * REC + d] = o[nt][mt][1]; rec[(h + 1) * REC + d + 8] = o[nt][mt][3]; }
+                }
+                if (g == 0) {
+                    if (h < q_per_kv) { rec[h * REC + HD] = run_m[nt][0]; rec[h * REC + HD + 1] = run_l[nt][0]; }
+                    if (h + 1 < q_per_kv) { rec[(h + 1) * REC + HD] = run_m[nt][1]; rec[(h + 1) * REC + HD + 1] = run_l[nt][1]; }
+                }
+            }
+        }
+        __syncthreads();
+
+        // Fold the warps' results in warp order: a warp per head, lane = dimension lane + 32 i.
+        const int live_warps = min(kMmaWarps, (cur.end - cur.begin + kMmaKeys - 1) / kMmaKeys);
+        const float* recs = reinterpret_cast<const float*>(v_self + RH + rec_slot * L::SLOT);
+        constexpr int kWarpFloats = STAGES * L::SLOT / 2;  // floats between two warps' records
+        for (int h = warp; h < q_per_kv; h += kMmaWarps) {
+            const int qh_index = cur.kvh * q_per_kv + h;
+            float top = -INFINITY;
+            for (int w = 0; w < live_warps; ++w) top = fmaxf(top, recs[w * kWarpFloats + h * REC + HD]);
+            float acc[DPL], total = 0.0f;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) acc[i] = 0.0f;
+            for (int w = 0; w < live_warps; ++w) {
+                const float fw = __expf(recs[w * kWarpFloats + h * REC + HD] - top);
+                total = fmaf(recs[w * kWarpFloats + h * REC + HD + 1], fw, total);
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) acc[i] = fmaf(recs[w * kWarpFloats + h * REC + lane + 32 * i], fw, acc[i]);
+            }
+            if (cur.spans == 1) {
+                ActOperand op = a.operand;
+                op.ss32 = nullptr;
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) {
+                    const float value = acc[i] / total;
+                    a.out[((long long)cur.t * a.q_heads + qh_index) * HD + lane + 32 * i] = value;
+                    if (op.dig != nullptr) operand_store_span(op, cur.t - a.token_base, a.q_heads * HD, (qh_index * HD) / 32 + i, lane, value, 0.0f);
+                }
+            } else {
+                float* pp = a.partial + (((long long)(cur.t - a.token_base) * a.q_heads + qh_index) * a.max_spans + cur.span) * REC;
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) pp[lane + 32 * i] = acc[i];
+                if (lane == 0) { pp[HD] = top; pp[HD + 1] = total; }
+            }
+        }
+        cur = nxt; id = nid; valid = nvalid;
+        rows0 = nrows0; rows1 = nrows1;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// The merge: one warp per (token, q head).  A launch of its own, so that the span CTAs retire as soon as their
+// sums are stored and the next projection's weight stream can start under the merge.
+template <int HD>
+__global__ void __launch_bounds__(kMmaWarps * 32) attention_merge_kernel(const AttnArgs a, const int n_tokens) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int pair = blockIdx.x * kMmaWarps + (threadIdx.x >> 5);
+    if (pair >= n_tokens * a.q_heads) return;
+    const int t = a.token_base + pair / a.q_heads, qh = pair % a.q_heads;
+    const int spans = token_spans(a, a.token_pos[t]);
     if (spans <= 1) return;  // written directly by the span kernel
-    const float* pp = a.partial + ((long long)(t - a.token_base) * a.q_heads + qh) * a.max_spans * (HD + 2);
-    if (threadIdx.x < 32) {
-        float top = -INFINITY;
-        for (int s = threadIdx.x; s < spans; s += 32) top = fmaxf(top, pp[s * (HD + 2) + HD]);
-        top = warp_max(top);
-        float denom = 0.0f;  // per-lane partial sums in span order, folded in a fixed shuffle order
-        for (int s = threadIdx.x; s < spans; s += 32) {
-            const float w = expf(pp[s * (HD + 2) + HD] - top);
-            weight[s] = w;
-            denom += pp[s * (HD + 2) + HD + 1] * w;
-        }
-        denom = warp_sum(denom);
-        if (threadIdx.x == 0) denom_s = denom;
+    merge_head<HD>(a, t, qh, spans, threadIdx.x & 31);
+}
+
+int attn_sm_count() {
+    static int counts[kMaxDevices] = {0};  // per device ordinal
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+    if (counts[dev] == 0) {
+        if (cudaDeviceGetAttribute(&counts[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || counts[dev] <= 0) counts[dev] = 148;
     }
-    __syncthreads();
-    const int d = threadIdx.x;
-    float sum = 0.0f;
-    // eight spans' values are requested before the first is used (the additions keep span order)
-    for (int s0 = 0; s0 < spans; s0 += 8) {
-        float v[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = s0 + u < spans ? pp[(s0 + u) * (HD + 2) + d] : 0.0f;
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            if (s0 + u < spans) sum = fmaf(v[u], weight[s0 + u], sum);
-        }
-    }
-    const float value = sum / denom_s;
-    a.out[((long long)t * a.q_heads + qh) * HD + d] = value;
-    if (a.operand.dig != nullptr) {
-        ActOperand op = a.operand;
-        op.ss32 = nullptr;
-        operand_store_span(op, t - a.token_base, a.q_heads * HD, (qh * HD + d) / 32, d & 31, value, 0.0f);
-    }
+    return counts[dev];
 }
 
 template <typename Kernel>
@@ -663,8 +831,19 @@ template <int HD>
 cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens, int max_keys, size_t partial_bytes,
                       int* launches, bool programmatic = false) {
     const int q_per_kv = a.q_heads / a.kv_heads;
-    a.max_spans = (max_keys + kAttnSpanKeys - 1) / kAttnSpanKeys;
-    if (a.max_spans > kAttnMaxSpans) return cudaErrorInvalidValue;
+    if (q_per_kv > 16) return cudaErrorInvalidValue;  // the group is the 16 rows of one MMA
+    const int max_tiles = (max_keys + kAttnSpanKeys - 1) / kAttnSpanKeys;
+    if (max_tiles > kAttnMaxSpans) return cudaErrorInvalidValue;
+    // prefill-sized launches of tokens whose K / V rows are all in the cache: several tokens per staged span
+    const bool rows = !fused && a.operand.dig == nullptr && n_tokens >= 4 * kAttnRowsPerCta &&
+                      (long long)n_tokens * a.kv_heads * max_tiles >= 1024;
+    // Tiles per span: as many as leave sixteen CTAs per SM's worth of spans (the per-CTA set-up and the
+    // merge are paid once per span); a launch that cannot fill the GPU keeps one tile per span.
+    a.tiles = 1;
+    if (!rows) {
+        while (a.tiles < 8 && (long long)n_tokens * a.kv_heads * ((max_tiles + 2 * a.tiles - 1) / (2 * a.tiles)) >= 16 * 148) a.tiles *= 2;
+    }
+    a.max_spans = (max_tiles + a.tiles - 1) / a.tiles;
     const size_t per_token = (size_t)a.q_heads * a.max_spans * (HD + 2) * sizeof(float);
     int chunk = n_tokens;
     if (a.max_spans > 1) {
@@ -672,19 +851,19 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
         chunk = (int)std::min<size_t>((size_t)n_tokens, partial_bytes / per_token);
     }
     if (a.operand.dig != nullptr && chunk < n_tokens) return cudaErrorInvalidValue;  // operand rows are launch-relative
-    // Few CTAs: the direct kernel (shorter dependency chain); many: K / V rows staged once per query-head group.
-    const bool staged = (long long)n_tokens * a.kv_heads * a.max_spans >= 1024;
-    const size_t smem = staged ? (size_t)q_per_kv * HD * sizeof(float) + (size_t)2 * kAttnSpanKeys * (HD + 8) * sizeof(__half)
-                               : (size_t)q_per_kv * HD * sizeof(float) + 2 * HD * sizeof(__half);
-    if (smem > 48 * 1024) {
-        // above the default limit (head_dim 256): opt in once per instantiation
+    const size_t mma_smem = MmaLayout<HD>::bytes(q_per_kv);
+    const size_t rows_smem = (size_t)q_per_kv * HD * sizeof(float) + (size_t)2 * kAttnSpanKeys * (HD + 8) * sizeof(__half);
+    {
+        // above the default shared-memory limit: opt in once per instantiation and device
         static bool configured_on[kMaxDevices] = {false};  // function attributes are per device
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
         bool& configured = configured_on[dev];
         if (!configured) {
-            cudaError_t e = cudaFuncSetAttribute(attention_span_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-            if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_span_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+            cudaError_t e = cudaFuncSetAttribute(attention_span_mma_kernel<HD, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_span_mma_kernel<HD, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_span_mma_kernel<HD, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_span_mma_kernel<HD, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
             if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_span_rows_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
             if (e != cudaSuccess) return e;
             configured = true;
@@ -693,28 +872,27 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
     for (int base = 0; base < n_tokens; base += chunk) {
         const int n = std::min(chunk, n_tokens - base);
         a.token_base = base;
-        dim3 grid(n * a.kv_heads, a.max_spans);
         cudaError_t e;
-        if (staged && !fused && a.operand.dig == nullptr && n >= 4 * kAttnRowsPerCta) {
-            // prefill-sized launches of tokens whose K / V rows are all in the cache: several tokens per staged span
+        if (rows) {
             const dim3 row_grid((unsigned)((n + kAttnRowsPerCta - 1) / kAttnRowsPerCta) * a.kv_heads, a.max_spans);
-            e = launch_pdl(stream, attention_span_rows_kernel<HD>, row_grid, q_per_kv * 32, smem, a, programmatic, n);
-        } else if (staged) {
-            e = fused ? launch_pdl(stream, attention_span_kernel<HD, true>, grid, q_per_kv * 32, smem, a, programmatic)
-                      : launch_pdl(stream, attention_span_kernel<HD, false>, grid, q_per_kv * 32, smem, a, programmatic);
+            e = launch_pdl(stream, attention_span_rows_kernel<HD>, row_grid, q_per_kv * 32, rows_smem, a, programmatic, n);
         } else {
-            if (HD <= 128 && q_per_kv <= 8) {
-                e = fused ? launch_pdl(stream, attention_span_direct_kernel<HD, true, (HD <= 128)>, grid, q_per_kv * 32, smem, a, programmatic)
-                          : launch_pdl(stream, attention_span_direct_kernel<HD, false, (HD <= 128)>, grid, q_per_kv * 32, smem, a, programmatic);
+            // persistent CTAs, as many as can be resident, walk the launch's (token, kv head, span) items
+            const int resident = std::max(1, (int)((size_t)227 * 1024 / (mma_smem + 1024)));
+            const dim3 grid((unsigned)std::min<long long>((long long)n * a.kv_heads * a.max_spans, (long long)attn_sm_count() * resident));
+            if (q_per_kv <= 8) {
+                e = fused ? launch_pdl(stream, attention_span_mma_kernel<HD, true, 1>, grid, kMmaWarps * 32, mma_smem, a, programmatic, n)
+                          : launch_pdl(stream, attention_span_mma_kernel<HD, false, 1>, grid, kMmaWarps * 32, mma_smem, a, programmatic, n);
             } else {
-                e = fused ? launch_pdl(stream, attention_span_direct_kernel<HD, true, false>, grid, q_per_kv * 32, smem, a, programmatic)
-                          : launch_pdl(stream, attention_span_direct_kernel<HD, false, false>, grid, q_per_kv * 32, smem, a, programmatic);
+                e = fused ? launch_pdl(stream, attention_span_mma_kernel<HD, true, 2>, grid, kMmaWarps * 32, mma_smem, a, programmatic, n)
+                          : launch_pdl(stream, attention_span_mma_kernel<HD, false, 2>, grid, kMmaWarps * 32, mma_smem, a, programmatic, n);
             }
         }
         if (e != cudaSuccess) return e;
         if (launches) ++*launches;
         if (a.max_spans > 1) {
-            e = launch_pdl(stream, attention_merge_kernel<HD>, dim3(n * a.q_heads), HD, 0, a, programmatic);
+            e = launch_pdl(stream, attention_merge_kernel<HD>, dim3((n * a.q_heads + kMmaWarps - 1) / kMmaWarps), kMmaWarps * 32, 0, a,
+                           programmatic, n);
             if (e != cudaSuccess) return e;
             if (launches) ++*launches;
         }
@@ -740,7 +918,7 @@ cudaError_t launch_attention(cudaStream_t stream, const float* q, const __half* 
                              int window, int max_keys, float* partial, size_t partial_bytes, float* out,
                              int* launches) {
     if (n_tokens <= 0) return cudaSuccess;
-    if (q_heads % kv_heads != 0 || q_heads / kv_heads > 32 || max_keys <= 0) return cudaErrorInvalidValue;
+    if (q_heads % kv_heads != 0 || q_heads / kv_heads > 16 || max_keys <= 0) return cudaErrorInvalidValue;
     if (head_dim == 32) {
         // Below 64 dims the span kernel's lane layout does not apply: the plain kernel serves.
         cudaError_t e = launch_attention_ref(stream, q, cache_k, cache_v, page_tables, pages_per_sequence, token_seq,
@@ -767,7 +945,7 @@ cudaError_t launch_attention(cudaStream_t stream, const float* q, const __half* 
 
 cudaError_t launch_attention_decode(cudaStream_t stream, const DecodeAttention& d, int* launches) {
     if (d.n_tokens <= 0) return cudaSuccess;
-    if (d.q_heads % d.kv_heads != 0 || d.q_heads / d.kv_heads > 32 || d.max_keys <= 0) return cudaErrorInvalidValue;
+    if (d.q_heads % d.kv_heads != 0 || d.q_heads / d.kv_heads > 16 || d.max_keys <= 0) return cudaErrorInvalidValue;
     AttnArgs a{};
     a.q = d.q; a.k_new = d.k; a.v_new = d.v;
     a.q_norm = d.q_norm; a.k_norm = d.k_norm; a.inv_freq = d.inv_freq; a.eps = d.eps;

@@ -51,8 +51,8 @@ extern "C" int ribn_b200_attention_noalloc(int32_t device, void* stream, const f
         return refuse(error, error_capacity, "null device pointer");
     }
     if (rows <= 0 || max_tokens <= 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 ||
-        q_heads / kv_heads > 32 || (head_dim != 64 && head_dim != 128 && head_dim != 256)) {
-        return refuse(error, error_capacity, "unsupported attention geometry (head_dim must be 64, 128 or 256)");
+        q_heads / kv_heads > 16 || (head_dim != 64 && head_dim != 128 && head_dim != 256)) {
+        return refuse(error, error_capacity, "unsupported attention geometry (head_dim must be 64, 128 or 256; at most 16 query heads per kv head)");
     }
     if (device < 0 || device >= kMaxDevices) return refuse(error, error_capacity, "device ordinal out of range");
     // The launch needs `device` current; the caller's own current device is put back before returning.

@@ -93,11 +93,14 @@ cudaError_t launch_attention_ref(cudaStream_t stream, const float* q, const __ha
 
 // Split-KV attention: fixed spans of kAttnSpanKeys keys per CTA, merged in span
 // order.  `max_keys` bounds the longest key range of any token in the launch
-// (it sizes the grid only; results do not depend on it).  `partial` is scratch
+// (with the token count it sizes the grid and sets how many 64-key tiles one
+// span covers, so a token's low bits can differ between launches of different
+// sizes, never inside one).  `partial` is scratch
 // of `partial_bytes` for the per-span accumulators; tokens are processed in
 // as many launches as that scratch requires.  `launches` (optional) is
 // incremented per kernel launch.  `token_seq` may be null: every token then
-// belongs to sequence 0 (one page-table row).
+// belongs to sequence 0 (one page-table row).  A GQA group has at most
+// 16 query heads.
 constexpr int kAttnSpanKeys = 64;
 constexpr int kAttnMaxSpans = 1024;  // 65536 keys per token
 cudaError_t launch_attention(cudaStream_t stream, const float* q, const __half* cache_k, const __half* cache_v,
