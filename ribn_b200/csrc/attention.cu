@@ -2,13 +2,11 @@
 // ("flash-decoding") over spans of 64-key tiles with an online softmax, then a
 // deterministic merge of the spans.
 //
-// Decode-sized launches run the tensor-core span kernel below (the GQA group's
-// query heads against 16-key slices as m16n8k16 MMAs, K / V staged in shared
-// memory once per group by asynchronous copies).  Prefill-sized launches run
-// the FP32 rows kernel: a CTA serves (4 consecutive tokens, kv head, 64-key
-// span), its warps are the q heads of the group, and the span's K / V rows
-// are staged once for the four tokens.  A token's result depends only on its
-// own keys and on the launch's size class, never on where its pages live.
+// Every launch runs the tensor-core span kernel below (the GQA group's query
+// heads against 16-key slices as m16n8k16 MMAs, K / V staged in shared memory
+// once per group by asynchronous copies), then the merge kernel.  A token's
+// result depends only on its own keys and on the launch's size class (tiles
+// per span), never on where its pages live.
 //
 // The decode form (FUSED) also applies the per-head Q/K RMSNorm and the NeoX
 // rotary and appends the new K/V row to the paged cache: the CTA that owns
@@ -86,201 +84,6 @@ __device__ __forceinline__ void norm_rope(float (&x)[HD / 32], const float* weig
         const float x0 = x[i], x1 = x[i + DPL / 2];
         x[i] = x0 * c - x1 * s;
         x[i + DPL / 2] = x0 * s + x1 * c;
-    }
-}
-
-// One warp's share of a span: query head `qh` of token `t` against keys [begin, end), whose K / V rows sit in
-// shared memory from position `tile_begin` on.  Writes the final output when the token has a single span,
-// else this span's partial sums.  Every span kernel runs exactly this arithmetic in this order.
-template <int HD>
-__device__ __forceinline__ void span_compute(const AttnArgs& a, float* qs, const __half* k_tile, const __half* v_tile,
-                                             int tile_begin, int begin, int end, int t, int qh, int span, int spans,
-                                             float scale, int lane) {
-    constexpr int DPL = HD / 32;
-    constexpr int CH = HD / 8;
-    constexpr int kRowHalfs = HD + 8;
-    const int kg = lane >> 3, dc = lane & 7;
-    float acc[CH];
-#pragma unroll
-    for (int d = 0; d < CH; ++d) acc[d] = 0.0f;
-    float run_max = -INFINITY, total = 0.0f;
-    for (int base = begin; base < end; base += 32) {
-        const int key = base + lane;
-        const bool live = key < end;
-        float s = -INFINITY;
-        if (live) {
-            const uint4* kp = reinterpret_cast<const uint4*>(k_tile + (key - tile_begin) * kRowHalfs);
-            uint4 kk[HD / 8];
-#pragma unroll
-            for (int i = 0; i < HD / 8; ++i) kk[i] = kp[i];
-            // packed FP32 pairs (sm_100): even and odd dimensions accumulate side by side
-            float2 dot2 = make_float2(0.0f, 0.0f);
-#pragma unroll
-            for (int i = 0; i < HD / 8; ++i) {
-                const float4 qa = *reinterpret_cast<const float4*>(qs + i * 8);
-                const float4 qb = *reinterpret_cast<const float4*>(qs + i * 8 + 4);
-                const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].x));
-                const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].y));
-                const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].z));
-                const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kk[i].w));
-                dot2 = __ffma2_rn(make_float2(qa.x, qa.y), k0, dot2);
-                dot2 = __ffma2_rn(make_float2(qa.z, qa.w), k1, dot2);
-                dot2 = __ffma2_rn(make_float2(qb.x, qb.y), k2, dot2);
-                dot2 = __ffma2_rn(make_float2(qb.z, qb.w), k3, dot2);
-            }
-            s = (dot2.x + dot2.y) * scale;
-        }
-        const float new_max = fmaxf(run_max, warp_max(s));
-        const float factor = expf(run_max - new_max);  // 0 on the first tile (run_max = -inf)
-        const float p = live ? expf(s - new_max) : 0.0f;
-        total = total * factor + warp_sum(p);
-#pragma unroll
-        for (int d = 0; d < CH; ++d) acc[d] *= factor;
-        run_max = new_max;
-        const int count = min(32, end - base);
-        // P.V: lane (kg, dc) takes keys j = 4 jj + kg and dims [dc * CH, dc * CH + CH)
-        uint4 vv[8][CH / 8];
-        float pj[8];
-#pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-            const int j = jj * 4 + kg;
-            pj[jj] = __shfl_sync(0xffffffffu, p, j);
-            const __half* vp = v_tile + (base - tile_begin + j) * kRowHalfs;
-            if (j < count) {
-#pragma unroll
-                for (int c = 0; c < CH / 8; ++c) vv[jj][c] = *reinterpret_cast<const uint4*>(vp + dc * CH + c * 8);
-            } else {
-#pragma unroll
-                for (int c = 0; c < CH / 8; ++c) vv[jj][c] = make_uint4(0u, 0u, 0u, 0u);
-            }
-        }
-#pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-#pragma unroll
-            for (int c = 0; c < CH / 8; ++c) {
-                const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].x));
-                const float2 v1 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].y));
-                const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].z));
-                const float2 v3 = __half22float2(*reinterpret_cast<const __half2*>(&vv[jj][c].w));
-                float* o = acc + c * 8;
-                const float2 pp = make_float2(pj[jj], pj[jj]);
-                const float2 o0 = __ffma2_rn(pp, v0, make_float2(o[0], o[1]));
-                const float2 o1 = __ffma2_rn(pp, v1, make_float2(o[2], o[3]));
-                const float2 o2 = __ffma2_rn(pp, v2, make_float2(o[4], o[5]));
-                const float2 o3 = __ffma2_rn(pp, v3, make_float2(o[6], o[7]));
-                o[0] = o0.x; o[1] = o0.y; o[2] = o1.x; o[3] = o1.y; o[4] = o2.x; o[5] = o2.y; o[6] = o3.x; o[7] = o3.y;
-            }
-        }
-    }
-    // Fold the four key groups (fixed order: xor 8, then xor 16).
-#pragma unroll
-    for (int d = 0; d < CH; ++d) {
-        acc[d] += __shfl_xor_sync(0xffffffffu, acc[d], 8);
-        acc[d] += __shfl_xor_sync(0xffffffffu, acc[d], 16);
-    }
-    if (spans == 1) {
-        if (kg == 0) {
-            const float inv = 1.0f / total;
-            float* op = a.out + ((long long)t * a.q_heads + qh) * HD + dc * CH;
-#pragma unroll
-            for (int d = 0; d < CH; ++d) { acc[d] *= inv; op[d] = acc[d]; qs[dc * CH + d] = acc[d]; }
-        }
-        if (a.operand.dig != nullptr) {
-            // back to one input per lane: lane takes dims lane + 32 i of this head
-            __syncwarp();
-            ActOperand op = a.operand;
-            op.ss32 = nullptr;
-            const int K = a.q_heads * HD, m = t - a.token_base;
-#pragma unroll
-            for (int i = 0; i < DPL; ++i) operand_store_span(op, m, K, (qh * HD) / 32 + i, lane, qs[lane + 32 * i], 0.0f);
-        }
-    } else if (kg == 0) {
-        float* pp = a.partial + (((long long)(t - a.token_base) * a.q_heads + qh) * a.max_spans + span) * (HD + 2);
-#pragma unroll
-        for (int d = 0; d < CH; ++d) pp[dc * CH + d] = acc[d];
-        if (dc == 0) { pp[HD] = run_max; pp[HD + 1] = total; }
-    }
-}
-
-// Prefill steps: consecutive tokens of one sequence see the same keys of a span (up to the diagonal), so a
-// CTA walks kAttnRowsPerCta consecutive tokens and stages the span's K / V rows once for all of them (the
-// copies from L2 into shared memory are what bounds a per-token launch at these sizes).  A token of another
-// sequence, or one whose span differs, restages.  The cache already holds every K / V row of the step.
-constexpr int kAttnRowsPerCta = 4;
-
-template <int HD>
-__global__ void attention_span_rows_kernel(const AttnArgs a, const int n_tokens) {
-    constexpr int DPL = HD / 32;
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    extern __shared__ __align__(16) unsigned char attn_smem[];
-    constexpr int kRowHalfs = HD + 8;
-    float* q_smem = reinterpret_cast<float*>(attn_smem);                                 // [warps][HD]
-    __half* k_tile = reinterpret_cast<__half*>(attn_smem + (size_t)(blockDim.x >> 5) * HD * sizeof(float));  // [64][kRowHalfs]
-    __half* v_tile = k_tile + kAttnSpanKeys * kRowHalfs;
-    __shared__ long long page_base[8];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int q_per_kv = a.q_heads / a.kv_heads;
-    const int group = blockIdx.x / a.kv_heads, kvh = blockIdx.x % a.kv_heads;
-    const int span = blockIdx.y;
-    const int qh = kvh * q_per_kv + warp;
-    const float scale = 1.0f / sqrtf((float)HD);
-    const long long row_stride = (long long)a.kv_heads * HD;
-    float* qs = q_smem + warp * HD;
-    int staged_seq = -1, staged_begin = -1, staged_end = 0;
-    for (int r = 0; r < kAttnRowsPerCta; ++r) {
-        const int local = group * kAttnRowsPerCta + r;
-        if (local >= n_tokens) break;
-        const int t = a.token_base + local;
-        const int pos = a.token_pos[t];
-        const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-        const int n_keys = pos + 1 - first;
-        const int spans = (n_keys + kAttnSpanKeys - 1) / kAttnSpanKeys;
-        if (span >= spans) continue;
-        const int begin = first + span * kAttnSpanKeys;
-        const int end = min(pos + 1, begin + kAttnSpanKeys);
-        const int seq = a.token_seq != nullptr ? a.token_seq[t] : 0;
-        if (seq != staged_seq || begin != staged_begin || end > staged_end) {
-            // Stage [begin, stage_end): far enough for the following tokens of this sequence in the CTA.
-            int stage_end = end;
-            for (int r2 = r + 1; r2 < kAttnRowsPerCta && group * kAttnRowsPerCta + r2 < n_tokens; ++r2) {
-                const int t2 = t + (r2 - r);
-                if ((a.token_seq != nullptr ? a.token_seq[t2] : 0) != seq) break;
-                const int pos2 = a.token_pos[t2];
-                if (pos2 < pos || (a.window > 0 ? max(0, pos2 - a.window + 1) : 0) != first) break;
-                stage_end = max(stage_end, min(pos2 + 1, begin + kAttnSpanKeys));
-            }
-            __syncthreads();  // every warp has finished with the previous tile
-            const int32_t* table = a.page_tables + (long long)seq * a.pages_per_sequence;
-            const int page0 = begin / kPageTokens, pages = (stage_end - 1) / kPageTokens - page0 + 1;
-            if ((int)threadIdx.x < pages) page_base[threadIdx.x] = (long long)table[page0 + threadIdx.x] * kPageTokens;
-            __syncthreads();
-            constexpr int kChunks = HD / 8;
-            const int pieces = (stage_end - begin) * kChunks;
-            for (int idx = threadIdx.x; idx < pieces; idx += blockDim.x) {
-                const int row = idx / kChunks, c = idx % kChunks;
-                const int key = begin + row;
-                const long long phys = page_base[key / kPageTokens - page0] + key % kPageTokens;
-                const long long at = phys * row_stride + (long long)kvh * HD + c * 8;
-                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(k_tile + row * kRowHalfs + c * 8);
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(a.cache_k + at) : "memory");
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)(kAttnSpanKeys * kRowHalfs * sizeof(__half))),
-                             "l"(a.cache_v + at)
-                             : "memory");
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            __syncthreads();
-            staged_seq = seq; staged_begin = begin; staged_end = stage_end;
-        }
-        {
-            const float* qp = a.q + ((long long)t * a.q_heads + qh) * HD;
-            __syncwarp();  // the previous token's reads of qs are done
-#pragma unroll
-            for (int i = 0; i < DPL; ++i) qs[lane + 32 * i] = qp[lane + 32 * i];
-            __syncwarp();
-        }
-        span_compute<HD>(a, qs, k_tile, v_tile, begin, begin, end, t, qh, span, spans, scale, lane);
     }
 }
 
@@ -834,15 +637,10 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
     if (q_per_kv > 16) return cudaErrorInvalidValue;  // the group is the 16 rows of one MMA
     const int max_tiles = (max_keys + kAttnSpanKeys - 1) / kAttnSpanKeys;
     if (max_tiles > kAttnMaxSpans) return cudaErrorInvalidValue;
-    // prefill-sized launches of tokens whose K / V rows are all in the cache: several tokens per staged span
-    const bool rows = !fused && a.operand.dig == nullptr && n_tokens >= 4 * kAttnRowsPerCta &&
-                      (long long)n_tokens * a.kv_heads * max_tiles >= 1024;
-    // Tiles per span: as many as leave sixteen CTAs per SM's worth of spans (the per-CTA set-up and the
+    // Tiles per span: as many as leave sixteen CTAs per SM's worth of spans (the per-item set-up and the
     // merge are paid once per span); a launch that cannot fill the GPU keeps one tile per span.
     a.tiles = 1;
-    if (!rows) {
-        while (a.tiles < 8 && (long long)n_tokens * a.kv_heads * ((max_tiles + 2 * a.tiles - 1) / (2 * a.tiles)) >= 16 * 148) a.tiles *= 2;
-    }
+    while (a.tiles < 8 && (long long)n_tokens * a.kv_heads * ((max_tiles + 2 * a.tiles - 1) / (2 * a.tiles)) >= 16 * 148) a.tiles *= 2;
     a.max_spans = (max_tiles + a.tiles - 1) / a.tiles;
     const size_t per_token = (size_t)a.q_heads * a.max_spans * (HD + 2) * sizeof(float);
     int chunk = n_tokens;
@@ -852,7 +650,6 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
     }
     if (a.operand.dig != nullptr && chunk < n_tokens) return cudaErrorInvalidValue;  // operand rows are launch-relative
     const size_t mma_smem = MmaLayout<HD>::bytes(q_per_kv);
-    const size_t rows_smem = (size_t)q_per_kv * HD * sizeof(float) + (size_t)2 * kAttnSpanKeys * (HD + 8) * sizeof(__half);
     {
         // above the default shared-memory limit: opt in once per instantiation and device
         static bool configured_on[kMaxDevices] = {false};  // function attributes are per device
@@ -864,7 +661,6 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
             if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_span_mma_kernel<HD, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
             if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_span_mma_kernel<HD, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
             if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_span_mma_kernel<HD, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-            if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_span_rows_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
             if (e != cudaSuccess) return e;
             configured = true;
         }
@@ -873,10 +669,7 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
         const int n = std::min(chunk, n_tokens - base);
         a.token_base = base;
         cudaError_t e;
-        if (rows) {
-            const dim3 row_grid((unsigned)((n + kAttnRowsPerCta - 1) / kAttnRowsPerCta) * a.kv_heads, a.max_spans);
-            e = launch_pdl(stream, attention_span_rows_kernel<HD>, row_grid, q_per_kv * 32, rows_smem, a, programmatic, n);
-        } else {
+        {
             // persistent CTAs, as many as can be resident, walk the launch's (token, kv head, span) items
             const int resident = std::max(1, (int)((size_t)227 * 1024 / (mma_smem + 1024)));
             const dim3 grid((unsigned)std::min<long long>((long long)n * a.kv_heads * a.max_spans, (long long)attn_sm_count() * resident));

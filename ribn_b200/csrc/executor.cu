@@ -1054,7 +1054,6 @@ int ribn_b200_tp_time_allreduce(ribn_b200_executor* ex, uint32_t tokens, uint32_
     if (ex->tp <= 1 || ex->comm == nullptr || !ex->finalized || ex->pending.active) return fail(ex, "time_allreduce: no idle tensor-parallel executor");
     if (tokens == 0 || tokens > (uint32_t)ex->cfg.max_batch_tokens || repeats == 0 || average_us == nullptr) return fail(ex, "time_allreduce: bad argument");
     cudaSetDevice(ex->cfg.device);
-    int launches = 0;
     CU_TRY(ex, cudaMemsetAsync(ex->proj, 0, (size_t)tokens * ex->cfg.hidden * sizeof(float), ex->stream));
     for (int warm = 0; warm < 3; ++warm) {
         if (ex->nccl.all_reduce(ex->proj, ex->proj, (size_t)tokens * ex->cfg.hidden, 7, 0, ex->comm, ex->stream) != 0) return fail(ex, "ncclAllReduce failed");
@@ -1068,7 +1067,7 @@ int ribn_b200_tp_time_allreduce(ribn_b200_executor* ex, uint32_t tokens, uint32_
     float ms = 0.0f;
     CU_TRY(ex, cudaEventElapsedTime(&ms, ex->ev_start, ex->ev_done));
     *average_us = ms * 1000.0f / (float)repeats;
-    (void)launches;
+
     return RIBN_B200_OK;
 }
 

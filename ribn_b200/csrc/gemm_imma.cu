@@ -33,7 +33,6 @@ namespace {
 constexpr int kWarps = 12;              // MMA warps; two more serve them: one issues the copies, one decodes headers
 constexpr int kProducerWarp = kWarps, kHeaderWarp = kWarps + 1;
 constexpr int kThreads = (kWarps + 2) * 32;
-constexpr int kMaxRowTiles = 4;         // row tiles per CTA: 4, or 2 when that fills more SMs
 constexpr int kColTiles = 2;            // MMA column tiles (8 columns each) per warp
 constexpr int kMaxMembers = kGemmMaxMembers;
 constexpr int kMemberPad = 8;           // members are padded to a multiple of this: 3 * 8 columns = 3 column tiles

@@ -207,9 +207,6 @@ __device__ __forceinline__ void bar_arrive(int id, int threads) {
 __device__ __forceinline__ void bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
-__device__ __forceinline__ void consumer_barrier() {
-    asm volatile("bar.sync 5, %0;" ::"n"(kConsumerThreads) : "memory");
-}
 
 // D = A(u8, 16 x 32) * B(s8, 32 x 8) + magic; the result registers are read as floats.
 __device__ __forceinline__ void imma_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -231,11 +228,6 @@ __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t o
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(other));
     return r;
 }
-// byte i of w as a float, without the conversion pipe
-__device__ __forceinline__ float byte_f32(uint32_t w, int i) {
-    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | (uint32_t)i)) - 8388608.0f;
-}
-
 // bytes i and i + 1 of w as floats minus `bias` (both exact), as one packed subtraction
 __device__ __forceinline__ float2 bytes_f32x2(uint32_t w, int i, float bias) {
     const float2 raw = make_float2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | (uint32_t)i)),
