@@ -374,7 +374,7 @@ def run_ours(args):
         "metric": f"{args.model} {args.scheme.upper()} decode tok/s at batch 1 (per GPU x replicas)", "value": value1,
         "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dev1 / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "u8 x s8 integer tensor-core products over Q4_K,Q6_K weights, f32 block scales and accumulation, f16 KV",
+        "dtype": f"u8 x s8 integer tensor-core products over {'Q8_0' if args.scheme == 'q8_0' else 'Q4_K,Q6_K'} weights, f32 block scales and accumulation, f16 KV",
         "data": "synthetic",
         "config": dict(decode_workload(args, B), parallelism=f"replicas x{world}"),
         "e2e": {"value": e2e1, "unit": "tok/s", "h2d_bytes_per_step": 32, "d2h_bytes_per_step": 4},
@@ -488,7 +488,7 @@ def serving_job(args, rank, world, local, dist, n, rate, workload):
         "value": world * generated / makespan, "unit": "tok/s", "n_gpus": world, "steps": engine.steps, "warmup": 0,
         "ms_per_step": makespan / max(engine.steps, 1) * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None,
-        "dtype": "u8 x s8 / f16 tensor-core products over Q4_K,Q6_K weights, f32 scales and accumulation, f16 KV",
+        "dtype": f"u8 x s8 / f16 tensor-core products over {'Q8_0' if args.scheme == 'q8_0' else 'Q4_K,Q6_K'} weights, f32 scales and accumulation, f16 KV",
         "data": "synthetic",
         "config": {"workload": f"{args.model} {args.scheme.upper()}-style {workload}: {n} requests per GPU, {described}, {active} active, "
                                f"{chunk}-token prefill chunks, 16-token KV pages",
