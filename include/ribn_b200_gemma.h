@@ -26,6 +26,12 @@ extern "C" {
  * full-attention layer (global head width, proportional quarter rotary); 0 a sliding-window layer.  The
  * last `kv_shared` layers reuse the keys / values of the last earlier layer of their kind
  * (config.rs:296-385).  Widths (hidden, ffn, ple, both head widths) must be multiples of 8. */
+/* Passes of 16 or more rows (prefill chunks) run their projections on the tensor cores: BF16 products
+ * accumulated in FP32 in the tensor core's order, one BF16 rounding per output.  Off by default: the
+ * default projections add in source order like the reference's host decoder (linear.rs:23-66) and
+ * reproduce its bits; with the flag a logit can move by a rounding step of an intermediate. */
+#define RIBN_B200_GEMMA_FLAG_TENSOR_CORE_PREFILL 1
+
 typedef struct ribn_b200_gemma_config {
     int32_t layers, hidden, heads, kv_heads, head_dim, global_head_dim, ffn, vocab;
     int32_t ple;        /* hidden_size_per_layer_input */
@@ -38,7 +44,7 @@ typedef struct ribn_b200_gemma_config {
     int32_t max_sequences;     /* concurrently open continuations */
     int32_t max_batch_tokens;  /* rows processed per pass; longer chunks run as several passes */
     int32_t device;
-    int32_t flags;             /* reserved, 0 */
+    int32_t flags;             /* RIBN_B200_GEMMA_FLAG_* */
 } ribn_b200_gemma_config;
 
 typedef struct ribn_b200_gemma ribn_b200_gemma;

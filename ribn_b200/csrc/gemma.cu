@@ -261,6 +261,105 @@ __global__ void __launch_bounds__(kProjectCols) gm_project_kernel(const bf16_t* 
 }
 
 // ---------------------------------------------------------------------------------------------
+// The same projection on the tensor cores, for passes of many rows when the model was created with
+// RIBN_B200_GEMMA_FLAG_TENSOR_CORE_PREFILL: BF16 x BF16 products (exact in FP32) accumulated in FP32 by
+// `mma.sync.m16n8k16`, one BF16 rounding of each output.  The sums are no longer in source order, so a result
+// can differ from the host decoder's by a rounding step of the FP32 sum before the BF16 rounding; the
+// ordered kernel above stays the default.  A block of four warps owns 64 rows x 64 columns; warp w owns rows
+// 16 w .. 16 w + 15 against all 64 columns.  Inputs and weights arrive in 32-input stages (rows pitched by 80
+// bytes: conflict-free matrix loads) through a two-stage cp.async pipeline.  k must be a multiple of 32.
+// ---------------------------------------------------------------------------------------------
+constexpr int kMmaTile = 64;           // rows and columns per block
+constexpr int kMmaStageK = 32;         // inputs per stage
+constexpr int kMmaPitch = kMmaStageK * 2 + 16;   // bytes between rows of a stage
+constexpr int kMmaStageBytes = 2 * kMmaTile * kMmaPitch;  // input rows, then weight rows
+
+__global__ void __launch_bounds__(128) gm_project_mma_kernel(const bf16_t* __restrict__ in, const int* __restrict__ row_index,
+                                                             int rows, const ProjectTargets targets, int k) {
+    __shared__ __align__(16) unsigned char stage_smem[2 * kMmaStageBytes];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int which = 0;
+    if (targets.count > 1 && (int)blockIdx.x >= targets.first_block[1]) which = 1;
+    if (targets.count > 2 && (int)blockIdx.x >= targets.first_block[2]) which = 2;
+    const bf16_t* __restrict__ w = targets.w[which];
+    bf16_t* __restrict__ out = targets.out[which];
+    const int n = targets.n[which];
+    const int col0 = ((int)blockIdx.x - targets.first_block[which]) * kMmaTile;
+    const int r0 = blockIdx.y * kMmaTile;
+    const uint32_t smem = (uint32_t)__cvta_generic_to_shared(stage_smem);
+    // copies: a stage holds 64 + 64 rows of 64 bytes = 512 pieces of 16 bytes, four per thread
+    const unsigned char* src[4];
+    uint32_t dst[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int piece = (int)threadIdx.x + 128 * j, row = piece >> 2, part = piece & 3;   // rows 0..63 inputs, 64..127 weights
+        if (row < kMmaTile) {
+            const int r = min(r0 + row, rows - 1);
+            src[j] = reinterpret_cast<const unsigned char*>(in + (size_t)(row_index ? row_index[r] : r) * k) + part * 16;
+        } else {
+            const int c = min(col0 + row - kMmaTile, n - 1);
+            src[j] = reinterpret_cast<const unsigned char*>(w + (size_t)c * k) + part * 16;
+        }
+        dst[j] = (uint32_t)(row * kMmaPitch + part * 16);
+    }
+    const int stages = k / kMmaStageK;
+    auto issue = [&](int st) {
+        if (st < stages) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) cp_async16(smem + (uint32_t)((st & 1) * kMmaStageBytes) + dst[j], src[j] + (size_t)st * (kMmaStageK * 2));
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float acc[8][4];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) { acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f; }
+    // matrix-load offsets: A = this warp's 16 input rows; B = weight rows (the MMA's columns), two column tiles per load
+    const uint32_t a_off = (uint32_t)((warp * 16 + (lane & 15)) * kMmaPitch + (lane >> 4) * 16);
+    const uint32_t b_off = (uint32_t)((kMmaTile + (lane & 7) + (lane >> 4) * 8) * kMmaPitch + ((lane >> 3) & 1) * 16);
+    issue(0);
+    for (int st = 0; st < stages; ++st) {
+        issue(st + 1);
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+        const uint32_t base = smem + (uint32_t)((st & 1) * kMmaStageBytes);
+#pragma unroll
+        for (int ks = 0; ks < kMmaStageK / 16; ++ks) {
+            uint32_t a[4];
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(base + a_off + ks * 32));
+#pragma unroll
+            for (int t2 = 0; t2 < 4; ++t2) {
+                uint32_t b[4];
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(base + b_off + t2 * (16 * kMmaPitch) + ks * 32));
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                             : "+f"(acc[2 * t2][0]), "+f"(acc[2 * t2][1]), "+f"(acc[2 * t2][2]), "+f"(acc[2 * t2][3])
+                             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                             : "+f"(acc[2 * t2 + 1][0]), "+f"(acc[2 * t2 + 1][1]), "+f"(acc[2 * t2 + 1][2]), "+f"(acc[2 * t2 + 1][3])
+                             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[2]), "r"(b[3]));
+            }
+        }
+        __syncthreads();  // every warp has read this stage before the copies of stage st + 2 land in it
+    }
+    // accumulator layout: rows g and g + 8 of the warp's 16, columns 8 t + 2 t4 + {0, 1}
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+        const int c = col0 + t * 8 + 2 * t4;
+        const int ra = r0 + warp * 16 + g, rb = ra + 8;
+        if (ra < rows) {
+            if (c < n) out[(size_t)ra * n + c] = bf_round(acc[t][0]);
+            if (c + 1 < n) out[(size_t)ra * n + c + 1] = bf_round(acc[t][1]);
+        }
+        if (rb < rows) {
+            if (c < n) out[(size_t)rb * n + c] = bf_round(acc[t][2]);
+            if (c + 1 < n) out[(size_t)rb * n + c + 1] = bf_round(acc[t][3]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Row RMS normalisation (norm.rs:38-82) with the decoder's follow-ups fused:
 //   mode 0: out = bf16(x * inverse * scale)
 //   mode 1: out = bf16(residual + mode 0)                         (post-norm + residual add)
@@ -1005,6 +1104,16 @@ struct Pass {
         }
         const dim3 block(kProjectCols);
         cudaStream_t s = m->stream;
+        if ((m->cfg.flags & RIBN_B200_GEMMA_FLAG_TENSOR_CORE_PREFILL) && n_rows >= 16 && k % kMmaStageK == 0) {
+            unsigned tile_blocks = 0;
+            for (int i = 0; i < count; ++i) {
+                t.first_block[i] = (int)tile_blocks;
+                tile_blocks += (unsigned)((n[i] + kMmaTile - 1) / kMmaTile);
+            }
+            gm_project_mma_kernel<<<dim3(tile_blocks, (unsigned)((n_rows + kMmaTile - 1) / kMmaTile)), 128, 0, s>>>(in, row_index, n_rows, t, k);
+            ++launches;
+            return;
+        }
         if (n_rows <= 1) gm_project_kernel<1><<<dim3(col_blocks, 1), block, project_smem_bytes(1), s>>>(in, row_index, n_rows, t, k);
         else if (n_rows <= 2) gm_project_kernel<2><<<dim3(col_blocks, 1), block, project_smem_bytes(2), s>>>(in, row_index, n_rows, t, k);
         else if (n_rows <= 4) gm_project_kernel<4><<<dim3(col_blocks, 1), block, project_smem_bytes(4), s>>>(in, row_index, n_rows, t, k);

@@ -23,6 +23,8 @@ LAYER_TENSORS = ("q_proj", "k_proj", "v_proj", "o_proj", "q_norm", "k_norm", "in
                  "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm", "gate_proj",
                  "up_proj", "down_proj", "per_layer_input_gate", "per_layer_projection", "post_per_layer_input_norm",
                  "layer_scalar")
+FLAG_TENSOR_CORE_PREFILL = 1   # RIBN_B200_GEMMA_FLAG_TENSOR_CORE_PREFILL
+
 CONFIG_FIELDS = ("layers", "hidden", "heads", "kv_heads", "head_dim", "global_head_dim", "ffn", "vocab", "ple",
                  "ple_vocab", "window", "context", "kv_shared", "eps", "softcap", "theta_local", "theta_global")
 
@@ -50,7 +52,8 @@ def tensor_names(cfg: dict) -> List[str]:
 
 
 class GemmaB200:
-    def __init__(self, cfg: dict, *, max_sequences: int = 4, max_batch_tokens: int = 64, device: int = 0):
+    def __init__(self, cfg: dict, *, max_sequences: int = 4, max_batch_tokens: int = 64, device: int = 0,
+                 tensor_core_prefill: bool = False):
         self.cfg = dict(cfg)
         c = _lib.GemmaConfig()
         for name in CONFIG_FIELDS:
@@ -61,7 +64,8 @@ class GemmaB200:
             if kind not in ("sliding", "full"):
                 raise ValueError(f"unsupported attention: {kind}")
             c.full[i] = 1 if kind == "full" else 0
-        c.max_sequences, c.max_batch_tokens, c.device, c.flags = max_sequences, max_batch_tokens, device, 0
+        c.max_sequences, c.max_batch_tokens, c.device = max_sequences, max_batch_tokens, device
+        c.flags = FLAG_TENSOR_CORE_PREFILL if tensor_core_prefill else 0
         self.max_sequences, self.max_batch_tokens = max_sequences, max_batch_tokens
         self._lib = _lib.lib()
         handle = C.c_void_p()
