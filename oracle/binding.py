@@ -45,6 +45,14 @@ def lib() -> C.CDLL:
         L.orc_rms_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_void_p]
         L.orc_rope_neox.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int64]
         L.orc_silu_mul.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        V = C.c_void_p
+        L.orc_gdn_scalar_gate.argtypes = [V, V, V, V, C.c_int, V, V]
+        L.orc_gdn_conv_silu.argtypes = [V, V, V, C.c_int, V, V]
+        L.orc_l2_norm_heads.argtypes = [V, C.c_int, C.c_int, C.c_float]
+        L.orc_gdn_state_update.argtypes = [V, V, V, V, V, V, C.c_int, C.c_int, C.c_int, C.c_int, V]
+        L.orc_gdn_gated_norm.argtypes = [V, V, V, C.c_int, C.c_int, C.c_float, V]
+        L.orc_gdn_step.argtypes = [C.c_int, C.c_int, C.c_int, V, V, V, V, V, V, V, V, V, V, C.c_float, C.c_float, V, V, V, V, V]
+        L.orc_attention_gate.argtypes = [V, V, C.c_int, C.c_int, C.c_int, V]
         L.orc_argmax.restype = C.c_uint32
         L.orc_argmax.argtypes = [C.c_void_p, C.c_int64]
         L.orc_attention.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
@@ -130,6 +138,69 @@ def silu_mul(g, u) -> np.ndarray:
     u = np.ascontiguousarray(u, dtype=np.float32)
     out = np.empty_like(g)
     lib().orc_silu_mul(_p(g), _p(u), g.size, _p(out))
+    return out
+
+
+# ---- Gated-DeltaNet recurrent layer step and the attention output gate (oracle/gdn.c) ----------------
+def _f(v):
+    return np.ascontiguousarray(v, dtype=np.float32)
+
+
+def gdn_scalar_gate(alpha, beta_raw, dt_bias, a):
+    alpha, beta_raw, dt_bias, a = _f(alpha), _f(beta_raw), _f(dt_bias), _f(a)
+    decay, beta = np.empty_like(alpha), np.empty_like(alpha)
+    lib().orc_gdn_scalar_gate(_p(alpha), _p(beta_raw), _p(dt_bias), _p(a), alpha.size, _p(decay), _p(beta))
+    return decay, beta
+
+
+def gdn_conv_silu(x, weight, history):
+    """Returns (raw, activated, advanced history); history [channels][3] oldest first, weight [channels][4]."""
+    x, weight, history = _f(x), _f(weight), _f(history).copy()
+    raw, act = np.empty_like(x), np.empty_like(x)
+    lib().orc_gdn_conv_silu(_p(x), _p(weight), _p(history), x.size, _p(raw), _p(act))
+    return raw, act, history
+
+
+def l2_norm_heads(values, heads: int, head_dim: int, eps: float) -> np.ndarray:
+    v = _f(values).copy()
+    lib().orc_l2_norm_heads(_p(v), heads, head_dim, eps)
+    return v
+
+
+def gdn_state_update(matrix, q, k, conv, decay, beta, v_heads: int, k_heads: int, head_dim: int, v_offset: int):
+    """Returns (out [v_heads * head_dim], updated matrix)."""
+    m = _f(matrix).copy()
+    q, k, conv, decay, beta = _f(q), _f(k), _f(conv), _f(decay), _f(beta)
+    out = np.empty(v_heads * head_dim, dtype=np.float32)
+    lib().orc_gdn_state_update(_p(m), _p(q), _p(k), _p(conv), _p(decay), _p(beta), v_heads, k_heads, head_dim, v_offset, _p(out))
+    return out, m
+
+
+def gdn_gated_norm(o, z, norm, heads: int, head_dim: int, eps: float) -> np.ndarray:
+    o, z, norm = _f(o), _f(z), _f(norm)
+    out = np.empty_like(o)
+    lib().orc_gdn_gated_norm(_p(o), _p(z), _p(norm), heads, head_dim, eps, _p(out))
+    return out
+
+
+def gdn_step(qkv, z, beta_raw, alpha_raw, dt_bias, a, conv_weight, norm_weight, conv_state, state, k_heads: int,
+             v_heads: int, head_dim: int, l2_eps: float, norm_eps: float):
+    """One sequence's step behind the projections; returns the same dict as ribn_b200.ops.gdn_step (one member)."""
+    channels, inner = (2 * k_heads + v_heads) * head_dim, v_heads * head_dim
+    qkv, z, br, ar = _f(qkv), _f(z), _f(beta_raw), _f(alpha_raw)
+    conv, st = _f(conv_state).copy(), _f(state).copy()
+    decay, beta = np.empty(v_heads, np.float32), np.empty(v_heads, np.float32)
+    act, attn, out = np.empty(channels, np.float32), np.empty(inner, np.float32), np.empty(inner, np.float32)
+    dt, aa, cw, nw = _f(dt_bias), _f(a), _f(conv_weight), _f(norm_weight)
+    lib().orc_gdn_step(k_heads, v_heads, head_dim, _p(qkv), _p(z), _p(br), _p(ar), _p(dt), _p(aa), _p(cw), _p(nw), _p(conv),
+                       _p(st), l2_eps, norm_eps, _p(decay), _p(beta), _p(act), _p(attn), _p(out))
+    return dict(out=out, decay=decay, beta=beta, conv_act=act, attn_out=attn, conv_state=conv, state=st)
+
+
+def attention_gate(attn, q_gate, rows: int, heads: int, head_dim: int) -> np.ndarray:
+    attn, q_gate = _f(attn), _f(q_gate)
+    out = np.empty_like(attn)
+    lib().orc_attention_gate(_p(attn), _p(q_gate), rows, heads, head_dim, _p(out))
     return out
 
 

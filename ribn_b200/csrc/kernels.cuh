@@ -137,6 +137,35 @@ struct DecodeAttention {
 };
 cudaError_t launch_attention_decode(cudaStream_t stream, const DecodeAttention& d, int* launches);
 
+// One decode step of a Gated-DeltaNet recurrent layer behind its projections, for `members` sequences with
+// their own states (crates/nvidia/src/qwen_reference.rs:202-278).  Device pointers; [m] = per member.
+struct GdnStep {
+    int members, k_heads, v_heads, head_dim;
+    int channels;            // q | k | v convolution channels: k_heads * hd | k_heads * hd | v_heads * hd
+    int k_offset, v_offset;  // first k channel, first v channel
+    const float* qkv;        // [m][channels] mixed projection of the token
+    const float* z;          // [m][v_heads * hd] gate projection
+    const float* beta_raw;   // [m][v_heads]
+    const float* alpha_raw;  // [m][v_heads]
+    const float* dt_bias;    // [v_heads]
+    const float* a;          // [v_heads], -exp(A_log)
+    const float* conv_weight;  // [channels][4], tap fastest
+    const float* norm_weight;  // [hd], not +1'd
+    float* const* conv_state;  // [m] -> [channels][3], oldest first; advanced in place
+    float* const* state;       // [m] -> [v_heads][hd][hd], row major; updated in place
+    float l2_eps, norm_eps;
+    float* decay;            // [m][v_heads] out
+    float* beta;             // [m][v_heads] out
+    float* conv_act;         // [m][channels] out: convolution + SiLU
+    float* attn_out;         // [m][v_heads * hd] out, optional: S^T q / sqrt(hd) before the gated norm
+    float* out;              // [m][v_heads * hd] out: what the output projection reads
+};
+cudaError_t launch_gdn_step(cudaStream_t stream, const GdnStep& step);
+// out = attn * sigmoid(gate), the gate being the second half of each head's [q | gate] projection
+// (crates/nvidia/src/qwen_reference.rs:386-392, 462-472).
+cudaError_t launch_attention_gate(cudaStream_t stream, const float* attn, const float* q_gate, long long rows, int heads,
+                                  int head_dim, float* out);
+
 // Seeded F16 K/V for the first `tokens` logical positions of one sequence, every layer.
 cudaError_t launch_synth_kv(cudaStream_t stream, __half* cache_k, __half* cache_v, long long layer_stride,
                             int layers, const int32_t* page_table, int tokens, int row_elems, uint64_t seed);

@@ -361,6 +361,68 @@ int ribn_b200_op_silu_mul(int32_t device, const float* gate, const float* up, in
     return s.download(out, d_o, (size_t)length) ? RIBN_B200_OK : RIBN_B200_ERROR;
 }
 
+int ribn_b200_op_gdn_step(int32_t device, int32_t members, int32_t k_heads, int32_t v_heads, int32_t head_dim,
+                          const float* qkv, const float* z, const float* beta_raw, const float* alpha_raw,
+                          const float* dt_bias, const float* a, const float* conv_weight, const float* norm_weight,
+                          float* conv_state, float* state, float l2_eps, float norm_eps, float* decay, float* beta,
+                          float* conv_act, float* attn_out, float* out) {
+    Scope s(device);
+    if (!s.ok || members <= 0 || k_heads <= 0 || v_heads <= 0 || v_heads % k_heads != 0 || (head_dim != 64 && head_dim != 128)) {
+        return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
+    }
+    const size_t hd = (size_t)head_dim, channels = (size_t)(2 * k_heads + v_heads) * hd, inner = (size_t)v_heads * hd;
+    const size_t conv_elems = channels * 3, state_elems = inner * hd;
+    GdnStep g{};
+    g.members = members; g.k_heads = k_heads; g.v_heads = v_heads; g.head_dim = head_dim;
+    g.channels = (int)channels; g.k_offset = (int)(k_heads * hd); g.v_offset = (int)(2 * k_heads * hd);
+    g.qkv = s.upload(qkv, (size_t)members * channels);
+    g.z = s.upload(z, (size_t)members * inner);
+    g.beta_raw = s.upload(beta_raw, (size_t)members * v_heads);
+    g.alpha_raw = s.upload(alpha_raw, (size_t)members * v_heads);
+    g.dt_bias = s.upload(dt_bias, (size_t)v_heads);
+    g.a = s.upload(a, (size_t)v_heads);
+    g.conv_weight = s.upload(conv_weight, channels * 4);
+    g.norm_weight = s.upload(norm_weight, hd);
+    float* d_conv = s.upload(conv_state, (size_t)members * conv_elems);
+    float* d_state = s.upload(state, (size_t)members * state_elems);
+    OP_PTR(g.qkv); OP_PTR(g.z); OP_PTR(g.beta_raw); OP_PTR(g.alpha_raw); OP_PTR(g.dt_bias); OP_PTR(g.a);
+    OP_PTR(g.conv_weight); OP_PTR(g.norm_weight); OP_PTR(d_conv); OP_PTR(d_state);
+    std::vector<float*> conv_ptrs((size_t)members), state_ptrs((size_t)members);
+    for (int m = 0; m < members; ++m) { conv_ptrs[m] = d_conv + (size_t)m * conv_elems; state_ptrs[m] = d_state + (size_t)m * state_elems; }
+    float** d_conv_ptrs = s.upload(conv_ptrs.data(), (size_t)members);
+    float** d_state_ptrs = s.upload(state_ptrs.data(), (size_t)members);
+    OP_PTR(d_conv_ptrs); OP_PTR(d_state_ptrs);
+    g.conv_state = d_conv_ptrs; g.state = d_state_ptrs;
+    g.l2_eps = l2_eps; g.norm_eps = norm_eps;
+    g.decay = s.alloc<float>((size_t)members * v_heads);
+    g.beta = s.alloc<float>((size_t)members * v_heads);
+    g.conv_act = s.alloc<float>((size_t)members * channels);
+    g.attn_out = s.alloc<float>((size_t)members * inner);
+    g.out = s.alloc<float>((size_t)members * inner);
+    OP_PTR(g.decay); OP_PTR(g.beta); OP_PTR(g.conv_act); OP_PTR(g.attn_out); OP_PTR(g.out);
+    OP_TRY(launch_gdn_step(s.stream, g));
+    bool ok = s.download(conv_state, d_conv, (size_t)members * conv_elems) && s.download(state, d_state, (size_t)members * state_elems) &&
+              s.download(out, g.out, (size_t)members * inner);
+    if (ok && decay) ok = s.download(decay, g.decay, (size_t)members * v_heads);
+    if (ok && beta) ok = s.download(beta, g.beta, (size_t)members * v_heads);
+    if (ok && conv_act) ok = s.download(conv_act, g.conv_act, (size_t)members * channels);
+    if (ok && attn_out) ok = s.download(attn_out, g.attn_out, (size_t)members * inner);
+    return ok ? RIBN_B200_OK : op_fail("download of the step's results", cudaGetLastError());
+}
+
+int ribn_b200_op_attention_gate(int32_t device, const float* attn, const float* q_gate, int64_t rows, int32_t heads,
+                                int32_t head_dim, float* out) {
+    Scope s(device);
+    if (!s.ok || rows <= 0 || heads <= 0 || head_dim <= 0) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
+    const size_t n = (size_t)rows * heads * head_dim;
+    float* d_a = s.upload(attn, n);
+    float* d_g = s.upload(q_gate, 2 * n);
+    float* d_o = s.alloc<float>(n);
+    OP_PTR(d_a); OP_PTR(d_g); OP_PTR(d_o);
+    OP_TRY(launch_attention_gate(s.stream, d_a, d_g, rows, heads, head_dim, d_o));
+    return s.download(out, d_o, n) ? RIBN_B200_OK : RIBN_B200_ERROR;
+}
+
 int ribn_b200_op_argmax(int32_t device, const float* logits, int32_t members, int64_t length, uint32_t* out) {
     Scope s(device);
     if (!s.ok || members <= 0 || length <= 0) return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
