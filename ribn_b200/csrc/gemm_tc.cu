@@ -1212,10 +1212,6 @@ cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units
     lay.a_planes = all_q4k ? 1 : 2;
     lay.a_stages = 2;
     lay.chunk_k = all_q4k ? 2 * kChunkK : kChunkK;
-    {
-        static const char* knob = getenv("RIBN_B200_TCQ_ASTAGES");   // experiment switch
-        if (knob != nullptr && all_q4k && atoi(knob) == 4) { lay.a_stages = 4; lay.chunk_k = kChunkK; }
-    }
     size_t fixed = (size_t)4 * kAHalfBytes + (size_t)2 * kA2Bytes + (size_t)4 * lay.b_bytes + (size_t)2 * lay.b2_bytes +
                    (size_t)4 * kRows * sizeof(float2) + 16 + 384;
     lay.w_stages = (int)std::min<size_t>(3, (budget - fixed) / (size_t)lay.w_stage_bytes);
