@@ -58,6 +58,7 @@ struct AttnArgs {
     int token_base;
     int q_heads, kv_heads, window, max_spans;
     int tiles;                 // 64-key tiles per span (tensor-core span kernel and its merge); 1 elsewhere
+    int run_tokens;            // up to this many consecutive tokens of a sequence share one item (prefill launches); 1: none
     float* partial;
     float* out;                // [T][q_heads][HD]
     ActOperand operand;        // optional operand form of `out`, K = q_heads * HD
@@ -202,15 +203,15 @@ struct MmaLayout {
     static constexpr int RH = HD + 8;                    // halfs per staged row: 16 bytes of padding keep the matrix loads conflict-free
     static constexpr int STAGES = 2;                     // ring slots per warp: one slice multiplied, the next in flight
     static constexpr int SLOT = 2 * kMmaKeys * RH;       // halfs per slot: 16 K rows, then 16 V rows
-    // [q rows] hi, the same lo, the token's own K / V row, then the rings
-    static size_t bytes(int q_per_kv) {
-        return ((size_t)2 * q_per_kv * RH + 2 * RH + (size_t)kMmaWarps * STAGES * SLOT) * sizeof(__half);
+    // [query rows: heads of the group x tokens of a run] hi, the same lo, the token's own K / V row, then the rings
+    static size_t bytes(int q_rows) {
+        return ((size_t)2 * q_rows * RH + 2 * RH + (size_t)kMmaWarps * STAGES * SLOT) * sizeof(__half);
     }
 };
 
 // One unit of work: a span of one (token, kv head).
 struct SpanItem {
-    int t, kvh, span, pos, spans, begin, end, n_tiles;
+    int t, len, kvh, span, pos, spans, begin, end, n_tiles;   // tokens t .. t + len - 1 at positions pos ..; spans of the last
     const int32_t* table;
     bool owns_self;
 };
@@ -227,9 +228,10 @@ __global__ void __launch_bounds__(kMmaWarps * 32, HD <= 128 && NT == 1 ? 3 : 1) 
     extern __shared__ __align__(16) unsigned char attn_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int q_per_kv = a.q_heads / a.kv_heads;
-    __half* q_hi = reinterpret_cast<__half*>(attn_smem);       // [q_per_kv][RH]
-    __half* q_lo = q_hi + q_per_kv * RH;
-    __half* k_self = q_lo + q_per_kv * RH;                     // [RH]
+    const int q_rows = q_per_kv * a.run_tokens;
+    __half* q_hi = reinterpret_cast<__half*>(attn_smem);       // [q_rows][RH]: column = token of the run x head of the group
+    __half* q_lo = q_hi + q_rows * RH;
+    __half* k_self = q_lo + q_rows * RH;                       // [RH]
     __half* v_self = k_self + RH;                              // [RH]
     __half* ring = v_self + RH + warp * (STAGES * L::SLOT);    // this warp's slots
     const long long row_stride = (long long)a.kv_heads * HD;
@@ -244,14 +246,32 @@ __global__ void __launch_bounds__(kMmaWarps * 32, HD <= 128 && NT == 1 ? 3 : 1) 
             it.span = id % a.max_spans;
             const int tk = id / a.max_spans;
             it.kvh = tk % a.kv_heads;
-            it.t = a.token_base + tk / a.kv_heads;
+            const int local = tk / a.kv_heads;
+            it.t = a.token_base + local;
             it.pos = a.token_pos[it.t];
-            const int first = a.window > 0 ? max(0, it.pos - a.window + 1) : 0;
-            it.spans = (it.pos + 1 - first + span_keys - 1) / span_keys;
+            it.len = 1;
+            const int seq = a.token_seq != nullptr ? a.token_seq[it.t] : 0;
+            if (a.run_tokens > 1) {
+                // Consecutive tokens of one sequence see the same keys up to the diagonal: the run that starts at an
+                // aligned token, or at one that does not continue its predecessor, is served by its first token's
+                // item; the run's other tokens have no item of their own.
+                const int in_group = local % a.run_tokens;
+                if (in_group != 0) {
+                    const int seq_before = a.token_seq != nullptr ? a.token_seq[it.t - 1] : 0;
+                    if (seq_before == seq && a.token_pos[it.t - 1] + 1 == it.pos) continue;
+                }
+                while (it.len < a.run_tokens - in_group && local + it.len < n_tokens &&
+                       (a.token_seq != nullptr ? a.token_seq[it.t + it.len] : 0) == seq && a.token_pos[it.t + it.len] == it.pos + it.len) {
+                    ++it.len;
+                }
+            }
+            const int last = it.pos + it.len - 1;
+            const int first = a.window > 0 ? max(0, it.pos - a.window + 1) : 0;   // runs only without a window
+            it.spans = (last + 1 - first + span_keys - 1) / span_keys;
             if (it.span >= it.spans) continue;
-            it.table = a.page_tables + (long long)(a.token_seq != nullptr ? a.token_seq[it.t] : 0) * a.pages_per_sequence;
+            it.table = a.page_tables + (long long)seq * a.pages_per_sequence;
             it.begin = first + it.span * span_keys;
-            it.end = min(it.pos + 1, it.begin + span_keys);
+            it.end = min(last + 1, it.begin + span_keys);
             it.n_tiles = (it.end - it.begin + kAttnSpanKeys - 1) / kAttnSpanKeys;
             it.owns_self = FUSED && it.span == it.spans - 1;  // this span holds the token's own position
             return true;
@@ -329,9 +349,9 @@ __global__ void __launch_bounds__(kMmaWarps * 32, HD <= 128 && NT == 1 ? 3 : 1) 
     auto fetch_raw = [&](const SpanItem& it) {
 #pragma unroll
         for (int u = 0; u < kAhead; ++u) {
-            const int h = warp + u * kMmaWarps;
-            if (h < q_per_kv) {
-                const float* qp = a.q + ((long long)it.t * a.q_heads + it.kvh * q_per_kv + h) * HD;
+            const int col = warp + u * kMmaWarps;
+            if (col < it.len * q_per_kv) {
+                const float* qp = a.q + ((long long)(it.t + col / q_per_kv) * a.q_heads + it.kvh * q_per_kv + col % q_per_kv) * HD;
 #pragma unroll
                 for (int i = 0; i < DPL; ++i) qx[u][i] = qp[lane + 32 * i];
             }
@@ -357,13 +377,13 @@ __global__ void __launch_bounds__(kMmaWarps * 32, HD <= 128 && NT == 1 ? 3 : 1) 
         // The group's queries (normalised and rotated here for decode rows) as binary16 hi + lo rows.
         {
             int u = 0;
-            for (int h = warp; h < q_per_kv; h += kMmaWarps, ++u) {
+            for (int col = warp; col < cur.len * q_per_kv; col += kMmaWarps, ++u) {
                 float x[DPL];
                 if (u < kAhead) {
 #pragma unroll
                     for (int i = 0; i < DPL; ++i) x[i] = u == 0 ? qx[0][i] : qx[1][i];
                 } else {
-                    const float* qp = a.q + ((long long)cur.t * a.q_heads + cur.kvh * q_per_kv + h) * HD;
+                    const float* qp = a.q + ((long long)(cur.t + col / q_per_kv) * a.q_heads + cur.kvh * q_per_kv + col % q_per_kv) * HD;
 #pragma unroll
                     for (int i = 0; i < DPL; ++i) x[i] = qp[lane + 32 * i];
                 }
@@ -371,8 +391,8 @@ __global__ void __launch_bounds__(kMmaWarps * 32, HD <= 128 && NT == 1 ? 3 : 1) 
 #pragma unroll
                 for (int i = 0; i < DPL; ++i) {
                     const __half hi = __float2half_rn(x[i]);
-                    q_hi[h * RH + lane + 32 * i] = hi;
-                    q_lo[h * RH + lane + 32 * i] = __float2half_rn(x[i] - __half2float(hi));
+                    q_hi[col * RH + lane + 32 * i] = hi;
+                    q_lo[col * RH + lane + 32 * i] = __float2half_rn(x[i] - __half2float(hi));
                 }
             }
         }
@@ -391,22 +411,27 @@ __global__ void __launch_bounds__(kMmaWarps * 32, HD <= 128 && NT == 1 ? 3 : 1) 
         }
         if (nvalid) fetch_raw(nxt);
         __syncthreads();  // queries and own row in place; every warp is done with the previous item's records
-        // This lane's B fragments of Q^T: head 8 nt + g, dimensions 16 ks + 2 t4 + {0, 1} and + 8.
+        // This lane's B fragments of Q^T: column 8 nt + g, dimensions 16 ks + 2 t4 + {0, 1} and + 8.
+        const int cols = cur.len * q_per_kv;
         uint32_t qh[NT][HD / 16][2], ql[NT][HD / 16][2];
+        int lim[NT][2];   // last key the tokens of columns 8 nt + 2 t4 and + 1 may see; -1 for a column past the run
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            const int h = nt * 8 + g;
+            const int col = nt * 8 + g;
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
-                    const int at = h * RH + ks * 16 + 2 * t4 + 8 * u;
-                    qh[nt][ks][u] = h < q_per_kv ? *reinterpret_cast<const uint32_t*>(q_hi + at) : 0u;
-                    ql[nt][ks][u] = h < q_per_kv ? *reinterpret_cast<const uint32_t*>(q_lo + at) : 0u;
+                    const int at = col * RH + ks * 16 + 2 * t4 + 8 * u;
+                    qh[nt][ks][u] = col < cols ? *reinterpret_cast<const uint32_t*>(q_hi + at) : 0u;
+                    ql[nt][ks][u] = col < cols ? *reinterpret_cast<const uint32_t*>(q_lo + at) : 0u;
                 }
             }
+            const int ca = nt * 8 + 2 * t4;
+            lim[nt][0] = ca < cols ? cur.pos + ca / q_per_kv : -1;
+            lim[nt][1] = ca + 1 < cols ? cur.pos + (ca + 1) / q_per_kv : -1;
         }
-        // O^T accumulators: [dims 16 mt + g (values 0, 1) and + 8 (values 2, 3)] x [heads 8 nt + 2 t4 + {0, 1}]
+        // O^T accumulators: [dims 16 mt + g (values 0, 1) and + 8 (values 2, 3)] x [columns 8 nt + 2 t4 + {0, 1}]
         float o[NT][HD / 16][4];
         float run_m[NT][2], run_l[NT][2];
 #pragma unroll
@@ -437,7 +462,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, HD <= 128 && NT == 1 ? 3 : 1) 
                 }
             }
             __syncwarp();
-            // S^T: keys g (values 0, 1) and g + 8 (values 2, 3) x heads 8 nt + 2 t4 + {0, 1}; the hi and lo
+            // S^T: keys g (values 0, 1) and g + 8 (values 2, 3) x columns 8 nt + 2 t4 + {0, 1}; the hi and lo
             // products accumulate apart (two shorter dependency chains) and meet at the end
             float sh[NT][4], sl[NT][4];
 #pragma unroll
@@ -455,16 +480,16 @@ __global__ void __launch_bounds__(kMmaWarps * 32, HD <= 128 && NT == 1 ? 3 : 1) 
                     }
                 }
             }
-            const bool live0 = wbegin + g < cur.end, live1 = wbegin + g + 8 < cur.end;
+            const int key0 = wbegin + g, key1 = key0 + 8;
             uint32_t ph[NT][2], pl[NT][2];
             bool moved = false;
             float f[NT][2];
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                const float s0 = live0 ? (sh[nt][0] + sl[nt][0]) * scale : -INFINITY;
-                const float s1 = live0 ? (sh[nt][1] + sl[nt][1]) * scale : -INFINITY;
-                const float s2 = live1 ? (sh[nt][2] + sl[nt][2]) * scale : -INFINITY;
-                const float s3 = live1 ? (sh[nt][3] + sl[nt][3]) * scale : -INFINITY;
+                const float s0 = key0 <= lim[nt][0] ? (sh[nt][0] + sl[nt][0]) * scale : -INFINITY;
+                const float s1 = key0 <= lim[nt][1] ? (sh[nt][1] + sl[nt][1]) * scale : -INFINITY;
+                const float s2 = key1 <= lim[nt][0] ? (sh[nt][2] + sl[nt][2]) * scale : -INFINITY;
+                const float s3 = key1 <= lim[nt][1] ? (sh[nt][3] + sl[nt][3]) * scale : -INFINITY;
                 float ma = fmaxf(s0, s2), mb = fmaxf(s1, s3);  // heads 2 t4 and 2 t4 + 1 over this lane's keys
 #pragma unroll
                 for (int x = 4; x < 32; x <<= 1) {
@@ -473,9 +498,11 @@ __global__ void __launch_bounds__(kMmaWarps * 32, HD <= 128 && NT == 1 ? 3 : 1) 
                 }
                 ma = fmaxf(ma, run_m[nt][0]); mb = fmaxf(mb, run_m[nt][1]);
                 moved = moved || ma != run_m[nt][0] || mb != run_m[nt][1];
-                f[nt][0] = __expf(run_m[nt][0] - ma); f[nt][1] = __expf(run_m[nt][1] - mb);  // 0 on the first slice
+                // a column that has seen no key yet (a token of the run whose keys start later) keeps -inf
+                const float za = ma == -INFINITY ? 0.0f : ma, zb = mb == -INFINITY ? 0.0f : mb;
+                f[nt][0] = __expf(run_m[nt][0] - za); f[nt][1] = __expf(run_m[nt][1] - zb);  // 0 on a column's first keys
                 run_m[nt][0] = ma; run_m[nt][1] = mb;
-                const float p0 = __expf(s0 - ma), p1 = __expf(s1 - mb), p2 = __expf(s2 - ma), p3 = __expf(s3 - mb);
+                const float p0 = __expf(s0 - za), p1 = __expf(s1 - zb), p2 = __expf(s2 - za), p3 = __expf(s3 - zb);
                 float la = p0 + p2, lb = p1 + p3;
 #pragma unroll
                 for (int x = 4; x < 32; x <<= 1) {
@@ -520,27 +547,30 @@ __global__ void __launch_bounds__(kMmaWarps * 32, HD <= 128 && NT == 1 ? 3 : 1) 
         if (cur.begin + warp * kMmaKeys < cur.end) {
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                const int h = nt * 8 + 2 * t4;
+                const int h = nt * 8 + 2 * t4;   // this lane's first column
 #pragma unroll
                 for (int mt = 0; mt < HD / 16; ++mt) {
                     const int d = mt * 16 + g;
-                    if (h < q_per_kv) { rec[h * REC + d] = o[nt][mt][0]; rec[h * REC + d + 8] = o[nt][mt][2]; }
-                    if (h + 1 < q_per_kv) { rec[(h + 1) * REC + d] = o[nt][mt][1]; rec[(h + 1) * REC + d + 8] = o[nt][mt][3]; }
+                    if (h < cols) { rec[h * REC + d] = o[nt][mt][0]; rec[h * REC + d + 8] = o[nt][mt][2]; }
+                    if (h + 1 < cols) { rec[(h + 1) * REC + d] = o[nt][mt][1]; rec[(h + 1) * REC + d + 8] = o[nt][mt][3]; }
                 }
                 if (g == 0) {
-                    if (h < q_per_kv) { rec[h * REC + HD] = run_m[nt][0]; rec[h * REC + HD + 1] = run_l[nt][0]; }
-                    if (h + 1 < q_per_kv) { rec[(h + 1) * REC + HD] = run_m[nt][1]; rec[(h + 1) * REC + HD + 1] = run_l[nt][1]; }
+                    if (h < cols) { rec[h * REC + HD] = run_m[nt][0]; rec[h * REC + HD + 1] = run_l[nt][0]; }
+                    if (h + 1 < cols) { rec[(h + 1) * REC + HD] = run_m[nt][1]; rec[(h + 1) * REC + HD + 1] = run_l[nt][1]; }
                 }
             }
         }
         __syncthreads();
 
-        // Fold the warps' results in warp order: a warp per head, lane = dimension lane + 32 i.
+        // Fold the warps' results in warp order: a warp per column, lane = dimension lane + 32 i.
         const int live_warps = min(kMmaWarps, (cur.end - cur.begin + kMmaKeys - 1) / kMmaKeys);
         const float* recs = reinterpret_cast<const float*>(v_self + RH + rec_slot * L::SLOT);
         constexpr int kWarpFloats = STAGES * L::SLOT / 2;  // floats between two warps' records
-        for (int h = warp; h < q_per_kv; h += kMmaWarps) {
-            const int qh_index = cur.kvh * q_per_kv + h;
+        for (int h = warp; h < cols; h += kMmaWarps) {
+            const int token = cur.t + h / q_per_kv, qh_index = cur.kvh * q_per_kv + h % q_per_kv;
+            // the column's own span count; a token of the run whose keys end before this span has nothing here
+            const int col_spans = cur.len == 1 ? cur.spans : (cur.pos + h / q_per_kv + span_keys) / span_keys;
+            if (cur.span >= col_spans) continue;
             float top = -INFINITY;
             for (int w = 0; w < live_warps; ++w) top = fmaxf(top, recs[w * kWarpFloats + h * REC + HD]);
             float acc[DPL], total = 0.0f;
@@ -552,17 +582,17 @@ __global__ void __launch_bounds__(kMmaWarps * 32, HD <= 128 && NT == 1 ? 3 : 1) 
 #pragma unroll
                 for (int i = 0; i < DPL; ++i) acc[i] = fmaf(recs[w * kWarpFloats + h * REC + lane + 32 * i], fw, acc[i]);
             }
-            if (cur.spans == 1) {
+            if (col_spans == 1) {
                 ActOperand op = a.operand;
                 op.ss32 = nullptr;
 #pragma unroll
                 for (int i = 0; i < DPL; ++i) {
                     const float value = acc[i] / total;
-                    a.out[((long long)cur.t * a.q_heads + qh_index) * HD + lane + 32 * i] = value;
-                    if (op.dig != nullptr) operand_store_span(op, cur.t - a.token_base, a.q_heads * HD, (qh_index * HD) / 32 + i, lane, value, 0.0f);
+                    a.out[((long long)token * a.q_heads + qh_index) * HD + lane + 32 * i] = value;
+                    if (op.dig != nullptr) operand_store_span(op, token - a.token_base, a.q_heads * HD, (qh_index * HD) / 32 + i, lane, value, 0.0f);
                 }
             } else {
-                float* pp = a.partial + (((long long)(cur.t - a.token_base) * a.q_heads + qh_index) * a.max_spans + cur.span) * REC;
+                float* pp = a.partial + (((long long)(token - a.token_base) * a.q_heads + qh_index) * a.max_spans + cur.span) * REC;
 #pragma unroll
                 for (int i = 0; i < DPL; ++i) pp[lane + 32 * i] = acc[i];
                 if (lane == 0) { pp[HD] = top; pp[HD + 1] = total; }
@@ -639,8 +669,12 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
     if (max_tiles > kAttnMaxSpans) return cudaErrorInvalidValue;
     // Tiles per span: as many as leave sixteen CTAs per SM's worth of spans (the per-item set-up and the
     // merge are paid once per span); a launch that cannot fill the GPU keeps one tile per span.
+    // Prefill-sized launches: up to 16 / group-size consecutive tokens of a sequence are the columns of one item
+    // and share its staged K / V rows (a token's bits do not depend on the grouping).
+    a.run_tokens = (!fused && a.window <= 0 && a.operand.dig == nullptr && n_tokens >= 16) ? std::max(1, 16 / q_per_kv) : 1;
+    const long long item_tokens = (n_tokens + a.run_tokens - 1) / a.run_tokens;
     a.tiles = 1;
-    while (a.tiles < 8 && (long long)n_tokens * a.kv_heads * ((max_tiles + 2 * a.tiles - 1) / (2 * a.tiles)) >= 16 * 148) a.tiles *= 2;
+    while (a.tiles < 8 && item_tokens * a.kv_heads * ((max_tiles + 2 * a.tiles - 1) / (2 * a.tiles)) >= 16 * 148) a.tiles *= 2;
     a.max_spans = (max_tiles + a.tiles - 1) / a.tiles;
     const size_t per_token = (size_t)a.q_heads * a.max_spans * (HD + 2) * sizeof(float);
     int chunk = n_tokens;
@@ -649,7 +683,7 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
         chunk = (int)std::min<size_t>((size_t)n_tokens, partial_bytes / per_token);
     }
     if (a.operand.dig != nullptr && chunk < n_tokens) return cudaErrorInvalidValue;  // operand rows are launch-relative
-    const size_t mma_smem = MmaLayout<HD>::bytes(q_per_kv);
+    const size_t mma_smem = MmaLayout<HD>::bytes(q_per_kv * a.run_tokens);
     {
         // above the default shared-memory limit: opt in once per instantiation and device
         static bool configured_on[kMaxDevices] = {false};  // function attributes are per device
@@ -671,9 +705,16 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
         cudaError_t e;
         {
             // persistent CTAs, as many as can be resident, walk the launch's (token, kv head, span) items
-            const int resident = std::max(1, (int)((size_t)227 * 1024 / (mma_smem + 1024)));
+            const bool wide = q_per_kv * a.run_tokens > 8;
+            int resident = 0;
+            cudaError_t q = wide ? (fused ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, attention_span_mma_kernel<HD, true, 2>, kMmaWarps * 32, mma_smem)
+                                          : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, attention_span_mma_kernel<HD, false, 2>, kMmaWarps * 32, mma_smem))
+                                 : (fused ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, attention_span_mma_kernel<HD, true, 1>, kMmaWarps * 32, mma_smem)
+                                          : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, attention_span_mma_kernel<HD, false, 1>, kMmaWarps * 32, mma_smem));
+            if (q != cudaSuccess) return q;
+            resident = std::max(1, resident);
             const dim3 grid((unsigned)std::min<long long>((long long)n * a.kv_heads * a.max_spans, (long long)attn_sm_count() * resident));
-            if (q_per_kv <= 8) {
+            if (!wide) {
                 e = fused ? launch_pdl(stream, attention_span_mma_kernel<HD, true, 1>, grid, kMmaWarps * 32, mma_smem, a, programmatic, n)
                           : launch_pdl(stream, attention_span_mma_kernel<HD, false, 1>, grid, kMmaWarps * 32, mma_smem, a, programmatic, n);
             } else {
