@@ -933,6 +933,298 @@ __global__ void __launch_bounds__(kKqThreads, 1) gemm_tcq_kernel(const GemmArgs 
     }
 }
 
+// ---- two row groups per work item ------------------------------------------------------------------
+// Prefill steps and large batches bring several whole groups of 64 rows to a projection.  The kernel above
+// converts every weight stage once per group; this one converts it once per PAIR of groups: the MMA thread
+// multiplies each converted stage by both groups' activation chunks, into two tensor-memory regions (main sums
+// of group g at columns 128 g, minima sums at 256 + 128 g: all 512 columns, one buffer per k tile: the fold
+// of k tile t hides under the conversion of k tile t + 1's first stage, which the MMAs wait for anyway).  Eight
+// epilogue warps (lane quadrant q = warp & 3, member half h = warp >> 2) fold 32 members of both groups each, so
+// a thread still carries 64 accumulators.  Stages hold 64 inputs; whole groups only (64 members), no K split.
+constexpr int kKq2EpilogueWarps = 8;
+constexpr int kKq2ProducerWarp = 8;
+constexpr int kKq2MmaWarp = 9;
+constexpr int kKq2DequantWarp0 = 10;
+constexpr int kKq2ChunkWarp0 = kKq2DequantWarp0 + kKqDequantWarps;
+constexpr int kKq2Threads = (kKq2ChunkWarp0 + 2) * 32;
+
+__global__ void __launch_bounds__(kKq2Threads, 1) gemm_tcq2_kernel(const GemmArgs a, const KqLayout lay, const int units) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_tiles = a.k / kTileCols;
+    const uint32_t spin_limit = a.spin_limit ? a.spin_limit : kSpinLimit;
+    constexpr int chunks_per_tile = kChunksPerTile;   // 64-input stages
+    const int a_bytes = lay.a_planes * kAHalfBytes;
+    const int b_group_bytes = lay.b_bytes;             // one group's chunk
+    const int b_stage_bytes = 2 * b_group_bytes;       // both groups' chunks
+    const uint32_t na = (uint32_t)lay.a_stages;
+    unsigned char* w_ring = smem;
+    unsigned char* a_buf = w_ring + (size_t)lay.w_stages * lay.w_stage_bytes;        // [a_stages][planes][16 KB]
+    unsigned char* a2_buf = a_buf + (size_t)lay.a_stages * a_bytes;                   // [2][kA2Bytes]
+    unsigned char* b_buf = a2_buf + 2 * kA2Bytes;                                     // [a_stages][2 groups][b_bytes]
+    unsigned char* b2_buf = b_buf + (size_t)lay.a_stages * b_stage_bytes;             // [2][2 groups][b2_bytes]
+    float2* row_scales = reinterpret_cast<float2*>(b2_buf + 4 * (size_t)lay.b2_bytes);  // [4][kRows]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(row_scales + 4 * kRows);
+    const uint32_t bars = smem_u32(tmem_slot + 4);
+    const uint32_t w_full = bars, w_empty = bars + 32, a_full = bars + 64, a_empty = bars + 96, t_full = bars + 128,
+                   t_empty = bars + 144, b2_full = bars + 160, b_full = bars + 192;
+    const int P = lay.groups / 2, items = units * P;   // work item -> (unit, pair of groups), the pair innermost
+    auto unit_index = [&](int item) { return item / P; };
+    auto pair_index = [&](int item) { return item % P; };
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < lay.w_stages; ++i) { mbar_init(w_full + 8 * i, 1); mbar_init(w_empty + 8 * i, kKqDequantWarps); }
+        for (int i = 0; i < lay.a_stages; ++i) { mbar_init(a_full + 8 * i, kKqDequantWarps); mbar_init(a_empty + 8 * i, 1); }
+        for (int i = 0; i < 2; ++i) {   // two barriers each, alternating by k tile, so that no wait is two phases behind
+            mbar_init(t_full + 8 * i, 1);
+            mbar_init(t_empty + 8 * i, kKq2EpilogueWarps);
+            mbar_init(b2_full + 8 * i, 1);
+        }
+        for (int i = 0; i < lay.a_stages; ++i) mbar_init(b_full + 8 * i, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = threadIdx.x; i < 2 * kA2Bytes / 16; i += kKq2Threads) reinterpret_cast<uint4*>(a2_buf)[i] = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (warp == kKq2MmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+    const size_t tile_stride = (size_t)kChunksPerTile * lay.b_bytes + lay.b2_bytes;  // one k tile of one group's activations
+
+    if (warp == kKq2ProducerWarp) {
+        bool alive = true;
+        uint32_t w_count = 0, kt_count = 0;
+        int witem = blockIdx.x, wkb = 0;   // next weight stage to issue: (work item, k tile)
+        auto issue_w = [&]() {
+            if (witem >= items) return;
+            const UnitRef ur = unit_of(a, unit_index(witem));
+            const GemvSegment& s = a.seg[ur.seg];
+            const uint32_t tb = (uint32_t)packed_tile_bytes(s.type);
+            const uint32_t stage = w_count % (uint32_t)lay.w_stages;
+            if (lane == 0) {
+                if (w_count >= (uint32_t)lay.w_stages && alive) {
+                    alive = mbar_wait_relaxed(w_empty + 8 * stage, ((w_count / (uint32_t)lay.w_stages) - 1u) & 1u, a.error_flag, 41, spin_limit);
+                }
+                const int present = min(kRowTilesPerUnit, s.row_tiles - ur.rt0);
+                mbar_expect_tx(w_full + 8 * stage, (uint32_t)present * tb);
+            }
+            __syncwarp();
+            if (lane < kRowTilesPerUnit && ur.rt0 + lane < s.row_tiles) {
+                bulk_g2s(smem_u32(w_ring + (size_t)stage * lay.w_stage_bytes + (size_t)lane * tb),
+                         s.data + ((size_t)(ur.rt0 + lane) * k_tiles + wkb) * tb, tb, w_full + 8 * stage);
+            }
+            ++w_count;
+            if (++wkb == k_tiles) { witem += gridDim.x; wkb = 0; }
+        };
+        issue_w();
+        if (lay.w_stages > 2) issue_w();
+        for (int item = blockIdx.x; item < items; item += gridDim.x) {
+            for (int kb = 0; kb < k_tiles; ++kb, ++kt_count) {
+                if (lane == 0) {
+                    // the group sums of k tile kt go where those of k tile kt - 2 were: its minima MMAs ended before
+                    // the commit that completed k tile kt - 2, which the epilogue of kt - 2 and so the MMAs of kt - 1 followed
+                    const uint32_t p = kt_count & 1u;
+                    if (kt_count >= 2u && alive) alive = mbar_wait_relaxed(t_full + 8 * p, ((kt_count >> 1) - 1u) & 1u, a.error_flag, 43, spin_limit);
+                    mbar_expect_tx(b2_full + 8 * p, 2u * (uint32_t)lay.b2_bytes);
+                    for (int g = 0; g < 2; ++g) {
+                        bulk_g2s(smem_u32(b2_buf + (size_t)(2 * p + g) * lay.b2_bytes),
+                                 a.chunks + (size_t)(2 * pair_index(item) + g) * lay.group_bytes + (size_t)kb * tile_stride + (size_t)kChunksPerTile * lay.b_bytes,
+                                 (uint32_t)lay.b2_bytes, b2_full + 8 * p);
+                    }
+                }
+                __syncwarp();
+                issue_w();
+            }
+        }
+    } else if (warp >= kKq2ChunkWarp0) {
+        if (lane == 0) {
+            bool alive = true;
+            const int which = warp - kKq2ChunkWarp0;
+            uint32_t b_count = 0;
+            for (int item = blockIdx.x; item < items; item += gridDim.x) {
+                for (int kb = 0; kb < k_tiles; ++kb) {
+                    for (int c = 0; c < chunks_per_tile; ++c, ++b_count) {
+                        if ((c & 1) != which) continue;
+                        const uint32_t bs = b_count % na;
+                        if (b_count >= na && alive) alive = mbar_wait_relaxed(a_empty + 8 * bs, ((b_count / na) - 1u) & 1u, a.error_flag, 42, spin_limit);
+                        mbar_expect_tx(b_full + 8 * bs, (uint32_t)b_stage_bytes);
+                        for (int g = 0; g < 2; ++g) {
+                            const signed char* src = a.chunks + (size_t)(2 * pair_index(item) + g) * lay.group_bytes + (size_t)kb * tile_stride;
+                            bulk_g2s(smem_u32(b_buf + (size_t)bs * b_stage_bytes + (size_t)g * b_group_bytes), src + (size_t)c * b_group_bytes,
+                                     (uint32_t)b_group_bytes, b_full + 8 * bs);
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == kKq2MmaWarp) {
+        if (lane == 0) {
+            bool alive = true;
+            uint32_t count = 0, kt_count = 0;
+            const uint32_t idesc = umma_idesc(lay.cols);
+            const uint32_t b_lbo = (uint32_t)(lay.cols / 8) * 128u;
+            for (int item = blockIdx.x; item < items; item += gridDim.x) {
+                const bool q4k = a.seg[unit_of(a, unit_index(item)).seg].type == kQ4_K;
+                for (int kb = 0; kb < k_tiles; ++kb, ++kt_count) {
+                    const uint32_t p = kt_count & 1u;
+                    // the one accumulator buffer: the epilogue has folded the previous k tile
+                    if (kt_count >= 1u && alive) alive = mbar_wait(t_empty + 8 * ((kt_count - 1u) & 1u), ((kt_count - 1u) >> 1) & 1u, a.error_flag, 44, spin_limit);
+                    tc_fence_after();
+                    for (int c = 0; c < chunks_per_tile; ++c, ++count) {
+                        const uint32_t st = count % na;
+                        if (alive) alive = mbar_wait(a_full + 8 * st, (count / na) & 1u, a.error_flag, 45, spin_limit);
+                        if (alive) alive = mbar_wait(b_full + 8 * st, (count / na) & 1u, a.error_flag, 46, spin_limit);
+                        tc_fence_after();
+                        const uint32_t a_addr = smem_u32(a_buf + (size_t)st * a_bytes);
+                        const uint64_t da_step = (uint64_t)((2 * kALbo) >> 4), db_step = (uint64_t)((2 * b_lbo) >> 4);
+                        const uint64_t da_plane = (uint64_t)(kAHalfBytes >> 4);
+                        for (int g = 0; g < 2; ++g) {
+                            const uint32_t b_addr = smem_u32(b_buf + (size_t)st * b_stage_bytes + (size_t)g * b_group_bytes);
+                            uint64_t da = umma_desc(a_addr, kALbo, 128), db = umma_desc(b_addr, b_lbo, 128);
+                            const uint32_t d_main = tmem_base + 128u * (uint32_t)g;
+                            if (q4k) {
+#pragma unroll
+                                for (int s16 = 0; s16 < kChunkK / 16; ++s16, da += da_step, db += db_step) {
+                                    umma_f16(d_main, da, db, idesc, (c | s16) != 0 ? 1u : 0u);
+                                }
+                            } else {
+#pragma unroll
+                                for (int s16 = 0; s16 < kChunkK / 16; ++s16, da += da_step, db += db_step) {
+                                    umma_f16(d_main, da, db, idesc, (c | s16) != 0 ? 1u : 0u);
+                                    umma_f16(d_main, da + da_plane, db, idesc, 1u);
+                                }
+                            }
+                        }
+                        if (c == chunks_per_tile - 1) {
+                            // Q4_K: group minima x group sums of the activations (the chunk's a_full covers A2 as well)
+                            if (alive) alive = mbar_wait(b2_full + 8 * p, (kt_count >> 1) & 1u, a.error_flag, 47, spin_limit);
+                            tc_fence_after();
+                            if (q4k) {
+                                for (int g = 0; g < 2; ++g) {
+                                    umma_f16(tmem_base + 256u + 128u * (uint32_t)g, umma_desc(smem_u32(a2_buf + (size_t)p * kA2Bytes), kALbo, 128),
+                                             umma_desc(smem_u32(b2_buf + (size_t)(2 * p + g) * lay.b2_bytes), b_lbo, 128), idesc, 0u);
+                                }
+                            }
+                        }
+                        umma_commit(a_empty + 8 * st);
+                    }
+                    umma_commit(t_full + 8 * p);
+                }
+            }
+        }
+    } else if (warp >= kKq2DequantWarp0 && warp < kKq2ChunkWarp0) {
+        const int rt_local = warp - kKq2DequantWarp0;
+        bool alive = true;
+        uint32_t w_count = 0, a_count = 0;
+        for (int item = blockIdx.x; item < items; item += gridDim.x) {
+            const UnitRef ur = unit_of(a, unit_index(item));
+            const GemvSegment& s = a.seg[ur.seg];
+            const int type = s.type;
+            const bool present = ur.rt0 + rt_local < s.row_tiles;
+            const int tb = packed_tile_bytes(type);
+            for (int kb = 0; kb < k_tiles; ++kb, ++w_count) {
+                const uint32_t stage = w_count % (uint32_t)lay.w_stages;
+                if (alive) alive = mbar_wait(w_full + 8 * stage, (w_count / (uint32_t)lay.w_stages) & 1u, a.error_flag, 48, spin_limit);
+                const unsigned char* tile = w_ring + (size_t)stage * lay.w_stage_bytes + (size_t)rt_local * tb;
+                for (int c = 0; c < chunks_per_tile; ++c, ++a_count) {
+                    const uint32_t st = a_count % na;
+                    if (a_count >= na && alive) alive = mbar_wait(a_empty + 8 * st, ((a_count / na) - 1u) & 1u, a.error_flag, 49, spin_limit);
+                    unsigned char* planes = a_buf + (size_t)st * a_bytes;
+                    unsigned char* a2 = a2_buf + (size_t)(w_count & 1u) * kA2Bytes;
+                    float2* scales = row_scales + (size_t)(w_count & 3u) * kRows;
+                    if (present) {
+                        kq_chunk(type, tile, c, 0, planes, a2, scales, rt_local * kTileRows, 0, lane);
+                        kq_chunk(type, tile, c, 0, planes, a2, scales, rt_local * kTileRows, 1, lane);
+                    } else {
+                        for (int pl = 0; pl < (type == kQ4_K ? 1 : 2); ++pl) {
+                            unsigned char* at = planes + (size_t)pl * kAHalfBytes;
+                            zero_rows_plane(at, rt_local * kTileRows, lane);
+                            zero_rows_plane(at, rt_local * kTileRows + 8, lane);
+                        }
+                        if (c == 0 && lane < 16) {
+                            const int unit_row = rt_local * kTileRows + lane;
+                            scales[unit_row] = make_float2(0.0f, 0.0f);
+                            *reinterpret_cast<uint4*>(a2 + (unit_row >> 3) * 128 + (unit_row & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(a_full + 8 * st);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(w_empty + 8 * stage);
+            }
+        }
+    } else {
+        // ---------------- epilogue warps: (lane quadrant, member half); fold each k tile of both groups ----------------
+        bool alive = true;
+        uint32_t kt_count = 0;
+        const int quadrant = warp & 3, half = warp >> 2;
+        const int row = quadrant * 32 + lane;
+        for (int item = blockIdx.x; item < items; item += gridDim.x) {
+            const UnitRef ur = unit_of(a, unit_index(item));
+            const GemvSegment& s = a.seg[ur.seg];
+            const bool q4k = s.type == kQ4_K;
+            float acc[2][32];
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[g][i] = 0.0f;
+            }
+            for (int kb = 0; kb < k_tiles; ++kb, ++kt_count) {
+                const uint32_t p = kt_count & 1u;
+                if (alive) alive = mbar_wait(t_full + 8 * p, (kt_count >> 1) & 1u, a.error_flag, 50, spin_limit);
+                tc_fence_after();
+                const float2 ds = row_scales[(size_t)(kt_count & 3u) * kRows + row];
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    const uint32_t t_main = tmem_base + 128u * (uint32_t)g + ((uint32_t)(quadrant * 32) << 16), t_min = t_main + 256u;
+#pragma unroll
+                    for (int m0 = 0; m0 < 32; m0 += 16) {
+                        float hi[16], lo[16];
+                        tmem_ld16(t_main + (uint32_t)(32 * half + m0), hi);
+                        tmem_ld16(t_main + (uint32_t)(64 + 32 * half + m0), lo);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) acc[g][m0 + i] = fmaf(ds.x, hi[i] + lo[i], acc[g][m0 + i]);
+                        if (q4k) {
+                            tmem_ld16(t_min + (uint32_t)(32 * half + m0), hi);
+                            tmem_ld16(t_min + (uint32_t)(64 + 32 * half + m0), lo);
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) acc[g][m0 + i] = fmaf(-ds.y, hi[i] + lo[i], acc[g][m0 + i]);
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(t_empty + 8 * p);
+            }
+            const int n_index = ur.rt0 * kTileRows + row;
+            if (n_index < s.n) {
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const size_t member = (size_t)(2 * pair_index(item) + g) * 64 + 32 * half + i;
+                        const float v = acc[g][i] * a.member_scale[member];
+                        float* y = s.y + member * s.n + n_index;
+                        if (a.epilogue == kResidual) *y += v; else *y = v;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kKq2MmaWarp) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
 // Adds the K slices of a split launch in slice order, applies the member scale and the epilogue.
 __global__ void tcq_reduce_kernel(const GemmArgs a, int slices, int total_n) {
     const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -1189,6 +1481,7 @@ cudaError_t device_setup(int& sm_count) {
     if (sms[dev] == 0) {
         e = cudaFuncSetAttribute(gemm_tcq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBudget);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBudget);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcq2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBudget);
         if (e != cudaSuccess) return e;
         int count = 0;
         if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || count <= 0) count = 148;
@@ -1239,6 +1532,33 @@ cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units
             const long long waves = ((long long)units * slices + sm_count - 1) / sm_count;
             const long long cost = waves * (tps + 1);
             if (best < 0 || cost < best) { best = cost; lay.k_slices = slices; }
+        }
+    }
+    if (lay.groups >= 2 && args.members == kKqMaxMembers) {
+        // whole groups in pairs: one conversion of every weight stage per pair; an odd last group takes the kernel above
+        KqLayout two = lay;
+        two.a_stages = 2;
+        two.chunk_k = kChunkK;
+        two.groups = lay.groups & ~1;
+        size_t fixed2 = (size_t)two.a_stages * two.a_planes * kAHalfBytes + (size_t)2 * kA2Bytes + (size_t)two.a_stages * 2 * two.b_bytes +
+                        (size_t)4 * two.b2_bytes + (size_t)4 * kRows * sizeof(float2) + 16 + 384;
+        two.w_stages = (int)std::min<size_t>(3, (budget - fixed2) / (size_t)two.w_stage_bytes);
+        if (two.w_stages >= 2) {
+            const size_t smem2 = fixed2 + (size_t)two.w_stages * two.w_stage_bytes;
+            gemm_tcq2_kernel<<<std::min(units * (two.groups / 2), sm_count), kKq2Threads, smem2, stream>>>(args, two, units);
+            cudaError_t e2 = cudaGetLastError();
+            g_last_launches = 1;
+            if (e2 != cudaSuccess || two.groups == lay.groups) return e2;
+            // the odd group: its operand, scales and outputs follow the pairs'
+            GemmArgs rest = args;
+            rest.groups = 1;
+            rest.chunks = args.chunks + (size_t)two.groups * lay.group_bytes;
+            rest.member_scale = args.member_scale + (size_t)two.groups * args.members;
+            for (int i = 0; i < rest.n_segments; ++i) rest.seg[i].y = args.seg[i].y + (size_t)two.groups * args.members * args.seg[i].n;
+            rest.partial = nullptr;
+            cudaError_t e3 = launch_gemm_tcq(stream, rest, units, tile);
+            g_last_launches = 2;
+            return e3;
         }
     }
     gemm_tcq_kernel<<<std::min(units * lay.k_slices * lay.groups, sm_count), kKqThreads, smem, stream>>>(args, lay, units);

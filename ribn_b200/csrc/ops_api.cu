@@ -273,7 +273,32 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
             const size_t partial_floats = (size_t)8 * group * (size_t)rows;
             float* partial = kquant ? s.alloc<float>(partial_floats) : nullptr;
             if (kquant) OP_PTR(partial);
-            for (int m0 = 0; m0 < members; m0 += per_launch) {
+            int m_first = 0;
+            if (kquant && members >= 2 * per_launch) {
+                // whole groups of 64 rows in one launch, as a prefill step runs them (pairs of groups share
+                // each converted weight stage)
+                const int whole = members / per_launch;
+                TcOperand all;
+                all.chunks = (__half*)s.alloc<unsigned char>((size_t)whole * tc_operand_bytes(per_launch, (int)cols));
+                all.scale_in = s.alloc<float>((size_t)whole * per_launch);
+                all.member_scale = s.alloc<float>((size_t)whole * per_launch);
+                OP_PTR(all.chunks); OP_PTR(all.scale_in); OP_PTR(all.member_scale);
+                OP_TRY(launch_to_tc_operand_groups(s.stream, d_x, nullptr, nullptr, whole * per_launch, per_launch, (int)cols, 0.0f, all));
+                GemmArgs a{};
+                a.n_segments = 1;
+                a.seg[0] = GemvSegment{d_w, type, (int)rows, (int)((rows + kTileRows - 1) / kTileRows), d_y};
+                a.k = (int)cols;
+                a.members = per_launch;
+                a.chunks = (const signed char*)all.chunks; a.member_scale = all.member_scale;
+                a.epilogue = kStore;
+                a.error_flag = d_err;
+                a.kquant = 1;
+                a.groups = whole;
+                a.group_chunk_bytes = tc_operand_bytes(per_launch, (int)cols);
+                OP_TRY(launch_gemm_tc(s.stream, a));
+                m_first = whole * per_launch;
+            }
+            for (int m0 = m_first; m0 < members; m0 += per_launch) {
                 const int m = std::min(per_launch, members - m0);
                 OP_TRY(launch_to_tc_operand(s.stream, d_x + (size_t)m0 * cols, nullptr, nullptr, m, (int)cols, 0.0f, kquant, top));
                 GemmArgs a{};

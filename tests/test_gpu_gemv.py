@@ -153,9 +153,11 @@ def test_batched_kernel_random_bytes_and_member_independence(ops, kind):
 @pytest.mark.parametrize("variant", [3, 4])
 @pytest.mark.parametrize("kind", [H.Q4_K, H.Q6_K, H.Q8_0])
 @pytest.mark.parametrize("rows,cols,members", [(16, 256, 1), (130, 512, 5), (256, 1024, 64), (300, 4096, 128),
-                                               (128, 12288, 33), (64, 768, 150)])
+                                               (128, 12288, 33), (64, 768, 150), (272, 1024, 200), (144, 12288, 128)])
 def test_tensor_memory_kernels_against_oracle(ops, kind, rows, cols, members, variant):
-    # tcgen05 kernels.  K-quant form (variant 3 on Q4_K / Q6_K): the tensor core multiplies the blocks'
+    # tcgen05 kernels.  K-quant form (variant 3 on Q4_K / Q6_K; 128 members and more run their whole groups of 64 in
+    # one launch whose work items take two groups each, 200 members = a pair, an odd group and 8 more rows): the
+    # tensor core multiplies the blocks'
     # exact integers and the F32 scales are applied per 256 inputs with round-to-nearest FMAs.
     # Decode-and-split form (variant 4, and Q8_0): weights and activations enter as binary16 hi + lo
     # pairs and the whole K is accumulated in tensor memory, whose F32 accumulation is not
