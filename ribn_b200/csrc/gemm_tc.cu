@@ -1534,8 +1534,11 @@ cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units
             if (best < 0 || cost < best) { best = cost; lay.k_slices = slices; }
         }
     }
-    if (lay.groups >= 2 && args.members == kKqMaxMembers) {
-        // whole groups in pairs: one conversion of every weight stage per pair; an odd last group takes the kernel above
+    // Whole groups in pairs: one conversion of every weight stage per pair (an odd last group takes the kernel above).
+    // A pair's item takes about 1.45 times a single group's, so pairs pay when they save waves of work items.
+    const long long single_waves = ((long long)units * lay.groups + sm_count - 1) / sm_count;
+    const long long pair_waves = ((long long)units * (lay.groups / 2) + sm_count - 1) / sm_count + (lay.groups & 1 ? (units + sm_count - 1) / sm_count : 0);
+    if (lay.groups >= 2 && args.members == kKqMaxMembers && pair_waves * 29 < single_waves * 20) {
         KqLayout two = lay;
         two.a_stages = 2;
         two.chunk_k = kChunkK;

@@ -195,3 +195,22 @@ def test_tensor_memory_kernels_random_bytes_and_member_independence(ops, kind, v
     assert np.all(zero == 0.0)
     huge = ops.gemv(kind, blocks, rows, cols, xs[:3] * np.float32(1e9), variant=variant)
     assert np.max(np.abs(huge / np.float32(1e9) - want[:3])) / np.max(np.abs(want)) < 1e-4
+
+
+@pytest.mark.parametrize("kind", [H.Q4_K, H.Q6_K])
+@pytest.mark.parametrize("rows,cols,members", [(19200, 512, 256), (37888, 256, 197)], ids=["two-pairs", "pair-odd-group-and-rest"])
+def test_tensor_memory_pair_kernel_against_oracle(ops, kind, rows, cols, members):
+    """Enough output rows that the launcher gives each work item two row groups (one conversion of a weight stage
+    per pair): four whole groups as two pairs; three whole groups as a pair plus an odd group, and five more rows.
+    Sampled members of every group against the oracle, and bit equality with the same rows run alone."""
+    rng = np.random.default_rng(rows + members + kind)
+    enc = H.quantize(kind, rng.normal(0, 0.02, size=(rows, cols)).astype(np.float32))
+    xs = (rng.normal(0, 1, size=(members, cols)) * rng.uniform(0.01, 100, size=(members, 1))).astype(np.float32)
+    got = ops.gemv(kind, enc, rows, cols, xs, variant=3)
+    picks = sorted(set([0, 31, 63, 64, 100, 127, 128, 191, members - 1]))
+    for m in picks:
+        want = orc.gemv(kind, enc, cols, rows, xs[m])
+        scale = float(np.max(np.abs(want))) + 1e-6
+        assert np.max(np.abs(got[m] - want)) / scale < 2e-5, m
+    alone = ops.gemv(kind, enc, rows, cols, xs[[70, 130]], variant=3)   # the single-group kernel
+    assert np.array_equal(alone.view(np.uint32), got[[70, 130]].view(np.uint32))
