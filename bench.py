@@ -411,6 +411,65 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_prefill(args):
+    """`--workload prefill`: one prompt of --context tokens prefilled in 2048-token chunks, per replica; device time of
+    every chunk (the executor's own CUDA events), repeated --steps times after --warmup prompts."""
+    import ribn_b200
+    from ribn_b200 import BatchItem, StepKind
+    rank, world, local, dist = dist_setup(args.gpus)
+    model = MODELS[args.model]
+    chunk = 2048
+    length = max(chunk, args.context // chunk * chunk)
+    ex = ribn_b200.QwenB200(model, context_tokens=length + 16, max_sequences=2, max_batch_tokens=chunk, device=local, flags=0)
+    ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q8_0 if SCHEME == "q8_0" else ribn_b200.SCHEME_Q4_K_M)
+    ex.finalize()
+    rng = np.random.default_rng(7 + rank)
+    chunks = length // chunk
+    per_chunk = np.zeros((args.steps, chunks))
+    launches = 0
+    barrier(dist, local)
+    with ClockSampler(local) as clocks:
+        wall0 = None
+        for rep in range(args.warmup + args.steps):
+            if rep == args.warmup:
+                barrier(dist, local)
+                wall0 = time.perf_counter()
+            prompt = rng.integers(0, model["vocab"], size=length, dtype=np.uint32)
+            assert ex.admit(100 + rep, 100 + rep, prompt, 2).ready
+            for c in range(chunks):
+                item = BatchItem(100 + rep, StepKind.PREFILL, c * chunk, chunk, 1 if c == chunks - 1 else 0)
+                ex.prepare([item])
+                ex.wait(ex.submit([item]))
+                ms, n = ex.last_step_stats()
+                if rep >= args.warmup:
+                    per_chunk[rep - args.warmup, c] = ms
+                    launches += n
+            ex.release(100 + rep)
+        barrier(dist, local)
+        wall = time.perf_counter() - wall0
+    ex.close()
+    dev = all_max(dist, float(per_chunk.sum()) / 1e3, local)
+    wall = all_max(dist, wall, local)
+    tokens = world * args.steps * length
+    out = {
+        "metric": f"{args.model} {args.scheme.upper()} prefill prompt tok/s (per GPU x replicas)", "value": tokens / dev,
+        "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dev / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": f"f16 x f16 tensor-core products over exact {'Q8_0 values' if args.scheme == 'q8_0' else 'K-quant integers'}, f32 scales and accumulation, f16 KV",
+        "data": "synthetic",
+        "config": {"workload": f"{args.model} {args.scheme.upper()}-style prefill of one {length}-token prompt per step in {chunk}-token chunks, "
+                               f"16-token KV pages, one replica per GPU", "l2": "inputs larger than L2", "parallelism": f"replicas x{world}"},
+        "e2e": {"value": tokens / wall, "unit": "tok/s", "h2d_bytes_per_step": 4 * length, "d2h_bytes_per_step": 4},
+        "gpu_launches": launches,
+        "chunk_ms": [float(v) for v in np.median(per_chunk, axis=0)],
+        "clocks": clocks.summary(),
+    }
+    if rank == 0:
+        print(json.dumps(out))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def run_serving(args):
     """`--workload serving|mixed`: the serving job alone, one line."""
     rank, world, local, dist = dist_setup(args.gpus)
@@ -759,9 +818,10 @@ def main():
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / full-size parity leg")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "mixed", "gemma"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "mixed", "gemma", "prefill"],
                     help="decode: steady batch-1 / batch-N decode steps (the headline); serving: Poisson arrivals through the engine; "
-                         "mixed: long chunked prefills interleaved with decode-heavy requests; gemma: the reduced Gemma-4 BF16 job")
+                         "mixed: long chunked prefills interleaved with decode-heavy requests; gemma: the reduced Gemma-4 BF16 job; "
+                         "prefill: one prompt of --context tokens per step in 2048-token chunks")
     ap.add_argument("--requests", type=int, default=None, help="requests per GPU (default: serving 96; mixed 64 = 32 long prompts + 32 decodes)")
     ap.add_argument("--no-serving", action="store_true", help="decode: skip the bounded serving leg (time to first token)")
     ap.add_argument("--serving-requests", type=int, default=32, help="decode: requests of the bounded serving leg")
@@ -790,6 +850,8 @@ def main():
         run_serving(args)
     elif args.workload == "gemma":
         run_gemma(args)
+    elif args.workload == "prefill":
+        run_prefill(args)
     else:
         run_ours(args)
 
