@@ -340,21 +340,24 @@ RIBN_B200_API int ribn_b200_op_gemv(int32_t device, int32_t ggml_type, const voi
 /* rms_norm(_batch) (crates/nvidia/src/model_ops.rs:108-201). */
 RIBN_B200_API int ribn_b200_op_rms_norm(int32_t device, const float* x, const float* weight,
                                         int32_t members, int32_t length, float eps, float* out);
-/* One decode step of a Gated-DeltaNet recurrent layer behind its projections (the Qwen3.5 hybrid model's
- * linear-attention layers), for `members` sequences each with its own state: scalar gates, depth-4 causal
+/* Decode steps of a Gated-DeltaNet recurrent layer behind its projections (the Qwen3.5 hybrid model's
+ * linear-attention layers), for `members` sequences each with its own state and `tokens` consecutive tokens per
+ * sequence (1: a decode step; more: a prefill chunk, advanced token by token inside the kernel with the state
+ * in registers, bit for bit what that many single steps give; rows below = members * tokens, member-major): scalar gates, depth-4 causal
  * convolution + SiLU with history shift, l2-normalised q / k heads tiled over the value heads, the per-head
  * state update and read, and the gated norm.  Replaces the reference's gdn_scalar_gate, gdn_conv_silu,
  * l2_norm_heads, gdn_state_update and gdn_gated_norm launches (crates/nvidia/src/model_ops.rs:372-394,
  * 614-820, 983-1040; host equations crates/nvidia/src/qwen_reference.rs:202-278).  Host pointers:
- * qkv [members][(2 k_heads + v_heads) * head_dim], z [members][v_heads * head_dim], beta_raw / alpha_raw
- * [members][v_heads], dt_bias / a [v_heads], conv_weight [channels][4] (tap fastest), norm_weight
+ * qkv [rows][(2 k_heads + v_heads) * head_dim], z [rows][v_heads * head_dim], beta_raw / alpha_raw
+ * [rows][v_heads], dt_bias / a [v_heads], conv_weight [channels][4] (tap fastest), norm_weight
  * [head_dim]; conv_state [members][channels][3] (oldest first) and state [members][v_heads][head_dim]
- * [head_dim] (row major) are updated in place.  Outputs: out [members][v_heads * head_dim] (what the
- * output projection reads) and, when not NULL, decay, beta [members][v_heads], conv_act
- * [members][channels], attn_out [members][v_heads * head_dim] (before the gated norm).  head_dim 64 or 128.
- * The chunk-parallel prefill scan (gdn_chunk_scan) and the hybrid model's executor are not part of this library. */
-RIBN_B200_API int ribn_b200_op_gdn_step(int32_t device, int32_t members, int32_t k_heads, int32_t v_heads,
-                                        int32_t head_dim, const float* qkv, const float* z,
+ * [head_dim] (row major) are updated in place.  Outputs: out [rows][v_heads * head_dim] (what the
+ * output projection reads) and, when not NULL, decay, beta [rows][v_heads], conv_act
+ * [rows][channels], attn_out [rows][v_heads * head_dim] (before the gated norm).  head_dim 64 or 128.
+ * The reference's chunk-parallel scan (gdn_chunk_scan: another summation order) and the hybrid model's executor
+ * are not part of this library. */
+RIBN_B200_API int ribn_b200_op_gdn_step(int32_t device, int32_t members, int32_t tokens, int32_t k_heads,
+                                        int32_t v_heads, int32_t head_dim, const float* qkv, const float* z,
                                         const float* beta_raw, const float* alpha_raw, const float* dt_bias,
                                         const float* a, const float* conv_weight, const float* norm_weight,
                                         float* conv_state, float* state, float l2_eps, float norm_eps,

@@ -102,7 +102,7 @@ SIGNATURES = {
     "ribn_b200_op_gemv": (C.c_int, [C.c_int32, C.c_int32, _P, C.c_int64, C.c_int64, _P, C.c_int32, _P, C.c_int32]),
     "ribn_b200_op_rms_norm": (C.c_int, [C.c_int32, _P, _P, C.c_int32, C.c_int32, C.c_float, _P]),
     "ribn_b200_op_silu_mul": (C.c_int, [C.c_int32, _P, _P, C.c_int64, _P]),
-    "ribn_b200_op_gdn_step": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P, _P, _P,
+    "ribn_b200_op_gdn_step": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P, _P, _P,
                                         _P, _P, C.c_float, C.c_float, _P, _P, _P, _P, _P]),
     "ribn_b200_op_attention_gate": (C.c_int, [C.c_int32, _P, _P, C.c_int64, C.c_int32, C.c_int32, _P]),
     "ribn_b200_op_argmax": (C.c_int, [C.c_int32, _P, C.c_int32, C.c_int64, _P]),

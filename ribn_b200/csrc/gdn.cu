@@ -35,22 +35,29 @@ __global__ void gdn_prepare_kernel(const GdnStep g) {
     const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const int m = blockIdx.y;
     if (id < g.v_heads) {
-        const long long at = (long long)m * g.v_heads + id;
-        g.beta[at] = gdn_sigmoid(g.beta_raw[at]);
-        g.decay[at] = expf(gdn_softplus(g.alpha_raw[at] + g.dt_bias[id]) * g.a[id]);
+        for (int t = 0; t < g.tokens; ++t) {
+            const long long at = ((long long)m * g.tokens + t) * g.v_heads + id;
+            g.beta[at] = gdn_sigmoid(g.beta_raw[at]);
+            g.decay[at] = expf(gdn_softplus(g.alpha_raw[at] + g.dt_bias[id]) * g.a[id]);
+        }
     }
     if (id < g.channels) {
-        // history is oldest first; the tap weights of channel c sit at c * 4 + tap
+        // history is oldest first; the tap weights of channel c sit at c * 4 + tap; the member's tokens in order
         float* h = g.conv_state[m] + id * (kGdnConvTaps - 1);
-        const float x = g.qkv[(long long)m * g.channels + id];
         const float* w = g.conv_weight + id * kGdnConvTaps;
-        const float h0 = h[0], h1 = h[1], h2 = h[2];
-        float sum = h0 * w[0];
-        sum += h1 * w[1];
-        sum += h2 * w[2];
-        sum += x * w[3];
-        h[0] = h1; h[1] = h2; h[2] = x;
-        g.conv_act[(long long)m * g.channels + id] = gdn_silu(sum);
+        const float w0 = w[0], w1 = w[1], w2 = w[2], w3 = w[3];
+        float h0 = h[0], h1 = h[1], h2 = h[2];
+        for (int t = 0; t < g.tokens; ++t) {
+            const long long row = (long long)m * g.tokens + t;
+            const float x = g.qkv[row * g.channels + id];
+            float sum = h0 * w0;
+            sum += h1 * w1;
+            sum += h2 * w2;
+            sum += x * w3;
+            h0 = h1; h1 = h2; h2 = x;
+            g.conv_act[row * g.channels + id] = gdn_silu(sum);
+        }
+        h[0] = h0; h[1] = h1; h[2] = h2;
     }
 }
 
@@ -62,84 +69,95 @@ __global__ void __launch_bounds__(256) gdn_state_kernel(const GdnStep g) {
     __shared__ float red[kWarps];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int m = blockIdx.y, vh = blockIdx.x, kh = vh % g.k_heads;
-    const float* act = g.conv_act + (long long)m * g.channels;
-    // l2-normalised q and k of the key head this value head is tiled from: 1 / max(|x|, eps)
-    if (warp < 2) {
-        const float* src = act + (warp == 0 ? 0 : g.k_offset) + kh * HD;
-        float x[kCols], ss = 0.0f;
-#pragma unroll
-        for (int i = 0; i < kCols; ++i) { x[i] = src[lane + 32 * i]; ss = fmaf(x[i], x[i], ss); }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        const float scale = 1.0f / fmaxf(sqrtf(ss), g.l2_eps);
-        float* dst = warp == 0 ? q_s : k_s;
-#pragma unroll
-        for (int i = 0; i < kCols; ++i) dst[lane + 32 * i] = x[i] * scale;
-    }
-    __syncthreads();
-    const float decay = g.decay[(long long)m * g.v_heads + vh], beta = g.beta[(long long)m * g.v_heads + vh];
     float* state = g.state[m] + (long long)vh * HD * HD;
+    // The head's state stays in registers for all the member's tokens: read once, written once.
     float s[kRows][kCols];
-    float part[kCols];
-#pragma unroll
-    for (int c = 0; c < kCols; ++c) part[c] = 0.0f;
 #pragma unroll
     for (int r = 0; r < kRows; ++r) {
-        const int row = warp * kRows + r;
-        const float kr = k_s[row];
 #pragma unroll
-        for (int c = 0; c < kCols; ++c) {
-            s[r][c] = state[row * HD + lane + 32 * c] * decay;
-            part[c] = fmaf(s[r][c], kr, part[c]);
+        for (int c = 0; c < kCols; ++c) s[r][c] = state[(warp * kRows + r) * HD + lane + 32 * c];
+    }
+    for (int t = 0; t < g.tokens; ++t) {
+        const long long token = (long long)m * g.tokens + t;
+        const float* act = g.conv_act + token * g.channels;
+        // l2-normalised q and k of the key head this value head is tiled from: 1 / max(|x|, eps)
+        if (warp < 2) {
+            const float* src = act + (warp == 0 ? 0 : g.k_offset) + kh * HD;
+            float x[kCols], ss = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) { x[i] = src[lane + 32 * i]; ss = fmaf(x[i], x[i], ss); }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float scale = 1.0f / fmaxf(sqrtf(ss), g.l2_eps);
+            float* dst = warp == 0 ? q_s : k_s;
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) dst[lane + 32 * i] = x[i] * scale;
         }
+        __syncthreads();
+        const float decay = g.decay[token * g.v_heads + vh], beta = g.beta[token * g.v_heads + vh];
+        float part[kCols];
+#pragma unroll
+        for (int c = 0; c < kCols; ++c) part[c] = 0.0f;
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const float kr = k_s[warp * kRows + r];
+#pragma unroll
+            for (int c = 0; c < kCols; ++c) {
+                s[r][c] *= decay;
+                part[c] = fmaf(s[r][c], kr, part[c]);
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < kCols; ++c) fold[warp][lane + 32 * c] = part[c];
+        __syncthreads();
+        if (threadIdx.x < HD) {
+            float sk = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) sk += fold[w][threadIdx.x];
+            vec[threadIdx.x] = (act[g.v_offset + vh * HD + threadIdx.x] - sk) * beta;   // d
+        }
+        __syncthreads();
+#pragma unroll
+        for (int c = 0; c < kCols; ++c) part[c] = 0.0f;
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const float kr = k_s[warp * kRows + r], qr = q_s[warp * kRows + r];
+#pragma unroll
+            for (int c = 0; c < kCols; ++c) {
+                s[r][c] = fmaf(kr, vec[lane + 32 * c], s[r][c]);
+                part[c] = fmaf(s[r][c], qr, part[c]);
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < kCols; ++c) fold[warp][lane + 32 * c] = part[c];
+        __syncthreads();
+        // o, its mean square, then rms(o) * norm_weight * silu(z)
+        float o = 0.0f;
+        if (threadIdx.x < HD) {
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) o += fold[w][threadIdx.x];
+            o *= 1.0f / sqrtf((float)HD);
+            if (g.attn_out != nullptr) g.attn_out[(token * g.v_heads + vh) * HD + threadIdx.x] = o;
+        }
+        float ss = threadIdx.x < HD ? o * o : 0.0f;
+#pragma unroll
+        for (int x = 16; x > 0; x >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, x);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        if (threadIdx.x < HD) {
+            float total = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) total += red[w];
+            const float inv = 1.0f / sqrtf(total / (float)HD + g.norm_eps);
+            const long long at = (token * g.v_heads + vh) * HD + threadIdx.x;
+            g.out[at] = o * inv * g.norm_weight[threadIdx.x] * gdn_silu(g.z[at]);
+        }
+        // the next token's first barrier orders these reads of q_s, k_s, fold and red before they are rewritten
     }
-#pragma unroll
-    for (int c = 0; c < kCols; ++c) fold[warp][lane + 32 * c] = part[c];
-    __syncthreads();
-    if (threadIdx.x < HD) {
-        float sk = 0.0f;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) sk += fold[w][threadIdx.x];
-        vec[threadIdx.x] = (act[g.v_offset + vh * HD + threadIdx.x] - sk) * beta;   // d
-    }
-    __syncthreads();
-#pragma unroll
-    for (int c = 0; c < kCols; ++c) part[c] = 0.0f;
 #pragma unroll
     for (int r = 0; r < kRows; ++r) {
-        const int row = warp * kRows + r;
-        const float kr = k_s[row], qr = q_s[row];
 #pragma unroll
-        for (int c = 0; c < kCols; ++c) {
-            s[r][c] = fmaf(kr, vec[lane + 32 * c], s[r][c]);
-            state[row * HD + lane + 32 * c] = s[r][c];
-            part[c] = fmaf(s[r][c], qr, part[c]);
-        }
-    }
-    __syncthreads();  // every warp has read d before `fold` is reused
-#pragma unroll
-    for (int c = 0; c < kCols; ++c) fold[warp][lane + 32 * c] = part[c];
-    __syncthreads();
-    // o, its mean square, then rms(o) * norm_weight * silu(z)
-    float o = 0.0f;
-    if (threadIdx.x < HD) {
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) o += fold[w][threadIdx.x];
-        o *= 1.0f / sqrtf((float)HD);
-        if (g.attn_out != nullptr) g.attn_out[((long long)m * g.v_heads + vh) * HD + threadIdx.x] = o;
-    }
-    float ss = threadIdx.x < HD ? o * o : 0.0f;
-#pragma unroll
-    for (int x = 16; x > 0; x >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, x);
-    if (lane == 0) red[warp] = ss;
-    __syncthreads();
-    if (threadIdx.x < HD) {
-        float total = 0.0f;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) total += red[w];
-        const float inv = 1.0f / sqrtf(total / (float)HD + g.norm_eps);
-        const long long at = ((long long)m * g.v_heads + vh) * HD + threadIdx.x;
-        g.out[at] = o * inv * g.norm_weight[threadIdx.x] * gdn_silu(g.z[at]);
+        for (int c = 0; c < kCols; ++c) state[(warp * kRows + r) * HD + lane + 32 * c] = s[r][c];
     }
 }
 
@@ -157,7 +175,7 @@ __global__ void attention_gate_kernel(const float* attn, const float* q_gate, lo
 }  // namespace
 
 cudaError_t launch_gdn_step(cudaStream_t stream, const GdnStep& g) {
-    if (g.members <= 0 || g.v_heads <= 0 || g.k_heads <= 0 || g.v_heads % g.k_heads != 0) return cudaErrorInvalidValue;
+    if (g.members <= 0 || g.tokens <= 0 || g.v_heads <= 0 || g.k_heads <= 0 || g.v_heads % g.k_heads != 0) return cudaErrorInvalidValue;
     if (g.head_dim != 64 && g.head_dim != 128) return cudaErrorInvalidValue;
     if (g.channels < g.v_offset + g.v_heads * g.head_dim || g.k_offset + g.k_heads * g.head_dim > g.channels) return cudaErrorInvalidValue;
     const int widest = g.channels > g.v_heads ? g.channels : g.v_heads;

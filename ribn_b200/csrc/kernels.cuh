@@ -137,16 +137,18 @@ struct DecodeAttention {
 };
 cudaError_t launch_attention_decode(cudaStream_t stream, const DecodeAttention& d, int* launches);
 
-// One decode step of a Gated-DeltaNet recurrent layer behind its projections, for `members` sequences with
-// their own states (crates/nvidia/src/qwen_reference.rs:202-278).  Device pointers; [m] = per member.
+// Decode steps of a Gated-DeltaNet recurrent layer behind its projections, for `members` sequences with their own
+// states, `tokens` consecutive tokens each (1: a decode step; more: a prefill chunk, token by token inside the
+// kernel with the state in registers, the same arithmetic as that many single steps)
+// (crates/nvidia/src/qwen_reference.rs:202-278).  Device pointers; [m] = per member, rows = m * tokens + t.
 struct GdnStep {
-    int members, k_heads, v_heads, head_dim;
+    int members, tokens, k_heads, v_heads, head_dim;
     int channels;            // q | k | v convolution channels: k_heads * hd | k_heads * hd | v_heads * hd
     int k_offset, v_offset;  // first k channel, first v channel
-    const float* qkv;        // [m][channels] mixed projection of the token
-    const float* z;          // [m][v_heads * hd] gate projection
-    const float* beta_raw;   // [m][v_heads]
-    const float* alpha_raw;  // [m][v_heads]
+    const float* qkv;        // [rows][channels] mixed projection of the tokens
+    const float* z;          // [rows][v_heads * hd] gate projection
+    const float* beta_raw;   // [rows][v_heads]
+    const float* alpha_raw;  // [rows][v_heads]
     const float* dt_bias;    // [v_heads]
     const float* a;          // [v_heads], -exp(A_log)
     const float* conv_weight;  // [channels][4], tap fastest
@@ -154,11 +156,11 @@ struct GdnStep {
     float* const* conv_state;  // [m] -> [channels][3], oldest first; advanced in place
     float* const* state;       // [m] -> [v_heads][hd][hd], row major; updated in place
     float l2_eps, norm_eps;
-    float* decay;            // [m][v_heads] out
-    float* beta;             // [m][v_heads] out
-    float* conv_act;         // [m][channels] out: convolution + SiLU
-    float* attn_out;         // [m][v_heads * hd] out, optional: S^T q / sqrt(hd) before the gated norm
-    float* out;              // [m][v_heads * hd] out: what the output projection reads
+    float* decay;            // [rows][v_heads] out
+    float* beta;             // [rows][v_heads] out
+    float* conv_act;         // [rows][channels] out: convolution + SiLU
+    float* attn_out;         // [rows][v_heads * hd] out, optional: S^T q / sqrt(hd) before the gated norm
+    float* out;              // [rows][v_heads * hd] out: what the output projection reads
 };
 cudaError_t launch_gdn_step(cudaStream_t stream, const GdnStep& step);
 // out = attn * sigmoid(gate), the gate being the second half of each head's [q | gate] projection

@@ -386,24 +386,25 @@ int ribn_b200_op_silu_mul(int32_t device, const float* gate, const float* up, in
     return s.download(out, d_o, (size_t)length) ? RIBN_B200_OK : RIBN_B200_ERROR;
 }
 
-int ribn_b200_op_gdn_step(int32_t device, int32_t members, int32_t k_heads, int32_t v_heads, int32_t head_dim,
+int ribn_b200_op_gdn_step(int32_t device, int32_t members, int32_t tokens, int32_t k_heads, int32_t v_heads, int32_t head_dim,
                           const float* qkv, const float* z, const float* beta_raw, const float* alpha_raw,
                           const float* dt_bias, const float* a, const float* conv_weight, const float* norm_weight,
                           float* conv_state, float* state, float l2_eps, float norm_eps, float* decay, float* beta,
                           float* conv_act, float* attn_out, float* out) {
     Scope s(device);
-    if (!s.ok || members <= 0 || k_heads <= 0 || v_heads <= 0 || v_heads % k_heads != 0 || (head_dim != 64 && head_dim != 128)) {
+    if (!s.ok || members <= 0 || tokens <= 0 || k_heads <= 0 || v_heads <= 0 || v_heads % k_heads != 0 || (head_dim != 64 && head_dim != 128)) {
         return op_fail("invalid argument, or no usable CUDA device", cudaGetLastError());
     }
     const size_t hd = (size_t)head_dim, channels = (size_t)(2 * k_heads + v_heads) * hd, inner = (size_t)v_heads * hd;
     const size_t conv_elems = channels * 3, state_elems = inner * hd;
     GdnStep g{};
-    g.members = members; g.k_heads = k_heads; g.v_heads = v_heads; g.head_dim = head_dim;
+    g.members = members; g.tokens = tokens; g.k_heads = k_heads; g.v_heads = v_heads; g.head_dim = head_dim;
     g.channels = (int)channels; g.k_offset = (int)(k_heads * hd); g.v_offset = (int)(2 * k_heads * hd);
-    g.qkv = s.upload(qkv, (size_t)members * channels);
-    g.z = s.upload(z, (size_t)members * inner);
-    g.beta_raw = s.upload(beta_raw, (size_t)members * v_heads);
-    g.alpha_raw = s.upload(alpha_raw, (size_t)members * v_heads);
+    const size_t rows = (size_t)members * tokens;
+    g.qkv = s.upload(qkv, rows * channels);
+    g.z = s.upload(z, rows * inner);
+    g.beta_raw = s.upload(beta_raw, rows * v_heads);
+    g.alpha_raw = s.upload(alpha_raw, rows * v_heads);
     g.dt_bias = s.upload(dt_bias, (size_t)v_heads);
     g.a = s.upload(a, (size_t)v_heads);
     g.conv_weight = s.upload(conv_weight, channels * 4);
@@ -419,19 +420,19 @@ int ribn_b200_op_gdn_step(int32_t device, int32_t members, int32_t k_heads, int3
     OP_PTR(d_conv_ptrs); OP_PTR(d_state_ptrs);
     g.conv_state = d_conv_ptrs; g.state = d_state_ptrs;
     g.l2_eps = l2_eps; g.norm_eps = norm_eps;
-    g.decay = s.alloc<float>((size_t)members * v_heads);
-    g.beta = s.alloc<float>((size_t)members * v_heads);
-    g.conv_act = s.alloc<float>((size_t)members * channels);
-    g.attn_out = s.alloc<float>((size_t)members * inner);
-    g.out = s.alloc<float>((size_t)members * inner);
+    g.decay = s.alloc<float>(rows * v_heads);
+    g.beta = s.alloc<float>(rows * v_heads);
+    g.conv_act = s.alloc<float>(rows * channels);
+    g.attn_out = s.alloc<float>(rows * inner);
+    g.out = s.alloc<float>(rows * inner);
     OP_PTR(g.decay); OP_PTR(g.beta); OP_PTR(g.conv_act); OP_PTR(g.attn_out); OP_PTR(g.out);
     OP_TRY(launch_gdn_step(s.stream, g));
     bool ok = s.download(conv_state, d_conv, (size_t)members * conv_elems) && s.download(state, d_state, (size_t)members * state_elems) &&
-              s.download(out, g.out, (size_t)members * inner);
-    if (ok && decay) ok = s.download(decay, g.decay, (size_t)members * v_heads);
-    if (ok && beta) ok = s.download(beta, g.beta, (size_t)members * v_heads);
-    if (ok && conv_act) ok = s.download(conv_act, g.conv_act, (size_t)members * channels);
-    if (ok && attn_out) ok = s.download(attn_out, g.attn_out, (size_t)members * inner);
+              s.download(out, g.out, rows * inner);
+    if (ok && decay) ok = s.download(decay, g.decay, rows * v_heads);
+    if (ok && beta) ok = s.download(beta, g.beta, rows * v_heads);
+    if (ok && conv_act) ok = s.download(conv_act, g.conv_act, rows * channels);
+    if (ok && attn_out) ok = s.download(attn_out, g.attn_out, rows * inner);
     return ok ? RIBN_B200_OK : op_fail("download of the step's results", cudaGetLastError());
 }
 

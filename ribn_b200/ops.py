@@ -115,21 +115,25 @@ def silu_mul(gate, up, device: int = 0) -> np.ndarray:
 
 
 def gdn_step(qkv, z, beta_raw, alpha_raw, dt_bias, a, conv_weight, norm_weight, conv_state, state, k_heads: int,
-             v_heads: int, head_dim: int, l2_eps: float, norm_eps: float, device: int = 0):
-    """One Gated-DeltaNet decode step behind the projections for `members` sequences (ribn_b200_op_gdn_step).
-    Returns a dict: out, decay, beta, conv_act, attn_out, and the advanced conv_state and state."""
+             v_heads: int, head_dim: int, l2_eps: float, norm_eps: float, tokens: int = 1, device: int = 0):
+    """Gated-DeltaNet decode steps behind the projections for `members` sequences of `tokens` consecutive tokens each
+    (ribn_b200_op_gdn_step; rows are member-major).  Returns a dict: out, decay, beta, conv_act, attn_out (one row
+    per token), and the advanced conv_state and state (one per member)."""
     channels, inner = (2 * k_heads + v_heads) * head_dim, v_heads * head_dim
     x = np.ascontiguousarray(qkv, dtype=np.float32).reshape(-1, channels)
-    members = x.shape[0]
+    rows = x.shape[0]
+    members = rows // tokens
+    if members * tokens != rows:
+        raise ValueError("rows must be members * tokens")
     f = lambda v, shape: np.ascontiguousarray(v, dtype=np.float32).reshape(shape)
-    zz, br, ar = f(z, (members, inner)), f(beta_raw, (members, v_heads)), f(alpha_raw, (members, v_heads))
+    zz, br, ar = f(z, (rows, inner)), f(beta_raw, (rows, v_heads)), f(alpha_raw, (rows, v_heads))
     dt, aa, cw, nw = f(dt_bias, (v_heads,)), f(a, (v_heads,)), f(conv_weight, (channels, 4)), f(norm_weight, (head_dim,))
     conv = f(conv_state, (members, channels, 3)).copy()
     st = f(state, (members, v_heads, head_dim, head_dim)).copy()
-    decay, beta = np.empty((members, v_heads), np.float32), np.empty((members, v_heads), np.float32)
-    act, attn, out = np.empty((members, channels), np.float32), np.empty((members, inner), np.float32), np.empty((members, inner), np.float32)
-    _check(lib().ribn_b200_op_gdn_step(device, members, k_heads, v_heads, head_dim, _p(x), _p(zz), _p(br), _p(ar), _p(dt), _p(aa),
-                                       _p(cw), _p(nw), _p(conv), _p(st), l2_eps, norm_eps, _p(decay), _p(beta), _p(act),
+    decay, beta = np.empty((rows, v_heads), np.float32), np.empty((rows, v_heads), np.float32)
+    act, attn, out = np.empty((rows, channels), np.float32), np.empty((rows, inner), np.float32), np.empty((rows, inner), np.float32)
+    _check(lib().ribn_b200_op_gdn_step(device, members, tokens, k_heads, v_heads, head_dim, _p(x), _p(zz), _p(br), _p(ar), _p(dt),
+                                       _p(aa), _p(cw), _p(nw), _p(conv), _p(st), l2_eps, norm_eps, _p(decay), _p(beta), _p(act),
                                        _p(attn), _p(out)), "gdn_step")
     return dict(out=out, decay=decay, beta=beta, conv_act=act, attn_out=attn, conv_state=conv, state=st)
 

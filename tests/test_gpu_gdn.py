@@ -92,3 +92,29 @@ def test_attention_gate_matches_the_oracle(ops):
     got = ops.attention_gate(attn, q_gate, heads, width)
     want = orc.attention_gate(attn, q_gate, rows, heads, width)
     assert np.max(np.abs(got - want.reshape(got.shape))) < 1e-6
+
+
+def test_several_tokens_in_one_call_equal_single_steps_bit_for_bit(ops):
+    """The prefill form: five consecutive tokens of two sequences in one call (the state stays in registers) against
+    the same tokens as five single-step calls, and the last token against the oracle."""
+    rng = np.random.default_rng(21)
+    members, tokens, k_heads, v_heads, hd = 2, 5, 4, 8, 128
+    weights, _, conv, state = _case(rng, members, k_heads, v_heads, hd)
+    steps = [_case(rng, members, k_heads, v_heads, hd)[1] for _ in range(tokens)]
+    stacked = {k: np.stack([steps[t][k] for t in range(tokens)], axis=1).reshape(members * tokens, -1) for k in steps[0]}
+    chunk = ops.gdn_step(conv_state=conv, state=state, k_heads=k_heads, v_heads=v_heads, head_dim=hd, l2_eps=1e-6, norm_eps=1e-6,
+                         tokens=tokens, **stacked, **weights)
+    c, s_, ref_c, ref_s = conv, state, conv.copy(), state.copy()
+    for t in range(tokens):
+        one = ops.gdn_step(conv_state=c, state=s_, k_heads=k_heads, v_heads=v_heads, head_dim=hd, l2_eps=1e-6, norm_eps=1e-6,
+                           **steps[t], **weights)
+        for m in range(members):
+            assert np.array_equal(chunk["out"][m * tokens + t], one["out"][m])
+            assert np.array_equal(chunk["conv_act"][m * tokens + t], one["conv_act"][m])
+            want = orc.gdn_step(conv_state=ref_c[m], state=ref_s[m], k_heads=k_heads, v_heads=v_heads, head_dim=hd, l2_eps=1e-6,
+                                norm_eps=1e-6, **{k: v[m] for k, v in steps[t].items()}, **weights)
+            ref_c[m], ref_s[m] = want["conv_state"].reshape(ref_c[m].shape), want["state"].reshape(ref_s[m].shape)
+            if t == tokens - 1:
+                assert np.max(np.abs(chunk["out"][m * tokens + t] - want["out"])) < 1e-3
+        c, s_ = one["conv_state"], one["state"]
+    assert np.array_equal(chunk["state"], s_) and np.array_equal(chunk["conv_state"], c)
