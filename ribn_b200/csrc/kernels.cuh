@@ -91,8 +91,8 @@ cudaError_t launch_attention_ref(cudaStream_t stream, const float* q, const __ha
                                  const int32_t* token_seq, const int32_t* token_pos, int n_tokens,
                                  int q_heads, int kv_heads, int head_dim, int window, float* out);
 
-// Split-KV attention: fixed spans of kAttnSpanKeys keys per CTA, merged in span
-// order.  `max_keys` bounds the longest key range of any token in the launch
+// Split-KV attention: spans of one to eight tiles of kAttnSpanKeys keys, merged in
+// span order.  `max_keys` bounds the longest key range of any token in the launch
 // (with the token count it sizes the grid and sets how many 64-key tiles one
 // span covers, so a token's low bits can differ between launches of different
 // sizes, never inside one).  `partial` is scratch
@@ -102,7 +102,7 @@ cudaError_t launch_attention_ref(cudaStream_t stream, const float* q, const __ha
 // belongs to sequence 0 (one page-table row).  A GQA group has at most
 // 16 query heads.
 constexpr int kAttnSpanKeys = 64;
-constexpr int kAttnMaxSpans = 1024;  // 65536 keys per token
+constexpr int kAttnMaxSpans = 1024;  // tiles per token: 65536 keys
 cudaError_t launch_attention(cudaStream_t stream, const float* q, const __half* cache_k, const __half* cache_v,
                              const int32_t* page_tables, int pages_per_sequence, const int32_t* token_seq,
                              const int32_t* token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,

@@ -345,3 +345,25 @@ def test_prefill_chunk_attention_at_16k_context(ops):
         seen = tokens - rows + 1 + r
         want = orc.attention(q[r], kb[: seen * KVH * HD], vb[: seen * KVH * HD], seen, QH, KVH, HD)
         assert np.max(np.abs(got[r] - want)) < 1e-3, r
+
+
+@pytest.mark.parametrize("QH,KVH,HD,tokens", [(32, 8, 128, 40000), (16, 1, 64, 9000), (8, 2, 256, 3000)],
+                         ids=["qwen3-8b-40k", "sixteen-heads-per-kv", "width-256"])
+def test_decode_attention_at_long_contexts(ops, QH, KVH, HD, tokens):
+    """One decode row over a long context: hundreds of spans through the merge (its span groups and shuffles),
+    a group of sixteen query heads (two MMA column tiles) and head width 256; against the oracle, and paged ==
+    contiguous bit for bit."""
+    rng = np.random.default_rng(tokens + QH)
+    q = rng.normal(0, 1, QH * HD).astype(np.float32)
+    k = rng.normal(0, 1, size=(tokens, KVH * HD)).astype(np.float16)
+    v = rng.normal(0, 1, size=(tokens, KVH * HD)).astype(np.float16)
+    pages = (tokens + 15) // 16
+    results = []
+    for table in (np.arange(pages), rng.permutation(pages)):
+        pk = np.zeros((pages * 16, KVH * HD), dtype=np.uint16); pv = np.zeros_like(pk)
+        order = table[np.arange(tokens) // 16] * 16 + np.arange(tokens) % 16
+        pk[order] = k.view(np.uint16); pv[order] = v.view(np.uint16)
+        results.append(ops.attention(q, pk, pv, [int(t) for t in table], tokens, 1, QH, KVH, HD, variant=0)[0])
+    assert np.array_equal(results[0].view(np.uint32), results[1].view(np.uint32))
+    want = orc.attention(q, k.view(np.uint16).reshape(-1), v.view(np.uint16).reshape(-1), tokens, QH, KVH, HD)
+    assert np.max(np.abs(results[0] - want)) < 1e-4
