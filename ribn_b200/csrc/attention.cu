@@ -59,6 +59,7 @@ struct AttnArgs {
     int q_heads, kv_heads, window, max_spans;
     int tiles;                 // 64-key tiles per span (tensor-core span kernel and its merge); 1 elsewhere
     int run_tokens;            // up to this many consecutive tokens of a sequence share one item (prefill launches); 1: none
+    int run_first, run_count;  // host side: tokens [run_first, run_first + run_count) are consecutive tokens of one sequence; -1: unknown
     float* partial;
     float* out;                // [T][q_heads][HD]
     ActOperand operand;        // optional operand form of `out`, K = q_heads * HD
@@ -208,6 +209,92 @@ struct MmaLayout {
         return ((size_t)2 * q_rows * RH + 2 * RH + (size_t)kMmaWarps * STAGES * SLOT) * sizeof(__half);
     }
 };
+
+// One 16-key slice against the item's columns: S^T = K Q^T, the columns' online softmax, O^T += V^T P^T.
+// `k_w`: the slice's 16 K rows followed by its 16 V rows in shared memory; `wbegin`: its first key; lim[nt][j]:
+// the last key column 8 nt + 2 t4 + j may see (-1: no such column); `first`: nothing has been accumulated yet.
+template <int HD, int NT>
+__device__ __forceinline__ void slice_step(const __half* k_w, int wbegin, const int (&lim)[NT][2],
+                                           const uint32_t (&qh)[NT][HD / 16][2], const uint32_t (&ql)[NT][HD / 16][2],
+                                           float (&o)[NT][HD / 16][4], float (&run_m)[NT][2], float (&run_l)[NT][2],
+                                           bool first, float scale, uint32_t k_off, uint32_t v_off, int g) {
+    // S^T: keys g (values 0, 1) and g + 8 (values 2, 3) x columns 8 nt + 2 t4 + {0, 1}; the hi and lo
+    // products accumulate apart (two shorter dependency chains) and meet at the end
+    float sh[NT][4], sl[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) { sh[nt][0] = sh[nt][1] = sh[nt][2] = sh[nt][3] = 0.0f; sl[nt][0] = sl[nt][1] = sl[nt][2] = sl[nt][3] = 0.0f; }
+    {
+        const uint32_t k_at = smem_u32(k_w) + k_off;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            uint32_t ka[4];
+            ldmatrix_x4(ka, k_at + ks * 32);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                mma_f16(sh[nt], ka, qh[nt][ks][0], qh[nt][ks][1]);
+                mma_f16(sl[nt], ka, ql[nt][ks][0], ql[nt][ks][1]);
+            }
+        }
+    }
+    const int key0 = wbegin + g, key1 = key0 + 8;
+    uint32_t ph[NT][2], pl[NT][2];
+    bool moved = false;
+    float f[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const float s0 = key0 <= lim[nt][0] ? (sh[nt][0] + sl[nt][0]) * scale : -INFINITY;
+        const float s1 = key0 <= lim[nt][1] ? (sh[nt][1] + sl[nt][1]) * scale : -INFINITY;
+        const float s2 = key1 <= lim[nt][0] ? (sh[nt][2] + sl[nt][2]) * scale : -INFINITY;
+        const float s3 = key1 <= lim[nt][1] ? (sh[nt][3] + sl[nt][3]) * scale : -INFINITY;
+        float ma = fmaxf(s0, s2), mb = fmaxf(s1, s3);  // heads 2 t4 and 2 t4 + 1 over this lane's keys
+#pragma unroll
+        for (int x = 4; x < 32; x <<= 1) {
+            ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, x));
+            mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, x));
+        }
+        ma = fmaxf(ma, run_m[nt][0]); mb = fmaxf(mb, run_m[nt][1]);
+        moved = moved || ma != run_m[nt][0] || mb != run_m[nt][1];
+        // a column that has seen no key yet (a token of the run whose keys start later) keeps -inf
+        const float za = ma == -INFINITY ? 0.0f : ma, zb = mb == -INFINITY ? 0.0f : mb;
+        f[nt][0] = __expf(run_m[nt][0] - za); f[nt][1] = __expf(run_m[nt][1] - zb);  // 0 on a column's first keys
+        run_m[nt][0] = ma; run_m[nt][1] = mb;
+        const float p0 = __expf(s0 - za), p1 = __expf(s1 - zb), p2 = __expf(s2 - za), p3 = __expf(s3 - zb);
+        float la = p0 + p2, lb = p1 + p3;
+#pragma unroll
+        for (int x = 4; x < 32; x <<= 1) {
+            la += __shfl_xor_sync(0xffffffffu, la, x);
+            lb += __shfl_xor_sync(0xffffffffu, lb, x);
+        }
+        run_l[nt][0] = fmaf(run_l[nt][0], f[nt][0], la);
+        run_l[nt][1] = fmaf(run_l[nt][1], f[nt][1], lb);
+        // (key, head pair) -> (head, key pair): the operand layout of P^T
+        uint32_t h0, l0, h1, l1;
+        split_pair(p0, p1, h0, l0);
+        split_pair(p2, p3, h1, l1);
+        ph[nt][0] = movmatrix_trans(h0); ph[nt][1] = movmatrix_trans(h1);
+        pl[nt][0] = movmatrix_trans(l0); pl[nt][1] = movmatrix_trans(l1);
+    }
+    if (!first && __any_sync(0xffffffffu, moved)) {  // a factor of exactly 1 changes nothing
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+            for (int mt = 0; mt < HD / 16; ++mt) {
+                o[nt][mt][0] *= f[nt][0]; o[nt][mt][1] *= f[nt][1]; o[nt][mt][2] *= f[nt][0]; o[nt][mt][3] *= f[nt][1];
+            }
+        }
+    }
+    const uint32_t v_at = smem_u32(k_w) + v_off;
+#pragma unroll
+    for (int mt = 0; mt < HD / 16; ++mt) {
+        uint32_t va[4];
+        ldmatrix_x4_trans(va, v_at + mt * 32);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            mma_f16(o[nt][mt], va, ph[nt][0], ph[nt][1]);
+            mma_f16(o[nt][mt], va, pl[nt][0], pl[nt][1]);
+        }
+    }
+}
 
 // One unit of work: a span of one (token, kv head).
 struct SpanItem {
@@ -462,82 +549,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, HD <= 128 && NT == 1 ? 3 : 1) 
                 }
             }
             __syncwarp();
-            // S^T: keys g (values 0, 1) and g + 8 (values 2, 3) x columns 8 nt + 2 t4 + {0, 1}; the hi and lo
-            // products accumulate apart (two shorter dependency chains) and meet at the end
-            float sh[NT][4], sl[NT][4];
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) { sh[nt][0] = sh[nt][1] = sh[nt][2] = sh[nt][3] = 0.0f; sl[nt][0] = sl[nt][1] = sl[nt][2] = sl[nt][3] = 0.0f; }
-            {
-                const uint32_t k_at = smem_u32(k_w) + k_off;
-#pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {
-                    uint32_t ka[4];
-                    ldmatrix_x4(ka, k_at + ks * 32);
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-                        mma_f16(sh[nt], ka, qh[nt][ks][0], qh[nt][ks][1]);
-                        mma_f16(sl[nt], ka, ql[nt][ks][0], ql[nt][ks][1]);
-                    }
-                }
-            }
-            const int key0 = wbegin + g, key1 = key0 + 8;
-            uint32_t ph[NT][2], pl[NT][2];
-            bool moved = false;
-            float f[NT][2];
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const float s0 = key0 <= lim[nt][0] ? (sh[nt][0] + sl[nt][0]) * scale : -INFINITY;
-                const float s1 = key0 <= lim[nt][1] ? (sh[nt][1] + sl[nt][1]) * scale : -INFINITY;
-                const float s2 = key1 <= lim[nt][0] ? (sh[nt][2] + sl[nt][2]) * scale : -INFINITY;
-                const float s3 = key1 <= lim[nt][1] ? (sh[nt][3] + sl[nt][3]) * scale : -INFINITY;
-                float ma = fmaxf(s0, s2), mb = fmaxf(s1, s3);  // heads 2 t4 and 2 t4 + 1 over this lane's keys
-#pragma unroll
-                for (int x = 4; x < 32; x <<= 1) {
-                    ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, x));
-                    mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, x));
-                }
-                ma = fmaxf(ma, run_m[nt][0]); mb = fmaxf(mb, run_m[nt][1]);
-                moved = moved || ma != run_m[nt][0] || mb != run_m[nt][1];
-                // a column that has seen no key yet (a token of the run whose keys start later) keeps -inf
-                const float za = ma == -INFINITY ? 0.0f : ma, zb = mb == -INFINITY ? 0.0f : mb;
-                f[nt][0] = __expf(run_m[nt][0] - za); f[nt][1] = __expf(run_m[nt][1] - zb);  // 0 on a column's first keys
-                run_m[nt][0] = ma; run_m[nt][1] = mb;
-                const float p0 = __expf(s0 - za), p1 = __expf(s1 - zb), p2 = __expf(s2 - za), p3 = __expf(s3 - zb);
-                float la = p0 + p2, lb = p1 + p3;
-#pragma unroll
-                for (int x = 4; x < 32; x <<= 1) {
-                    la += __shfl_xor_sync(0xffffffffu, la, x);
-                    lb += __shfl_xor_sync(0xffffffffu, lb, x);
-                }
-                run_l[nt][0] = fmaf(run_l[nt][0], f[nt][0], la);
-                run_l[nt][1] = fmaf(run_l[nt][1], f[nt][1], lb);
-                // (key, head pair) -> (head, key pair): the operand layout of P^T
-                uint32_t h0, l0, h1, l1;
-                split_pair(p0, p1, h0, l0);
-                split_pair(p2, p3, h1, l1);
-                ph[nt][0] = movmatrix_trans(h0); ph[nt][1] = movmatrix_trans(h1);
-                pl[nt][0] = movmatrix_trans(l0); pl[nt][1] = movmatrix_trans(l1);
-            }
-            if (i > 0 && __any_sync(0xffffffffu, moved)) {  // a factor of exactly 1 changes nothing
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-                    for (int mt = 0; mt < HD / 16; ++mt) {
-                        o[nt][mt][0] *= f[nt][0]; o[nt][mt][1] *= f[nt][1]; o[nt][mt][2] *= f[nt][0]; o[nt][mt][3] *= f[nt][1];
-                    }
-                }
-            }
-            const uint32_t v_at = smem_u32(k_w) + v_off;
-#pragma unroll
-            for (int mt = 0; mt < HD / 16; ++mt) {
-                uint32_t va[4];
-                ldmatrix_x4_trans(va, v_at + mt * 32);
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    mma_f16(o[nt][mt], va, ph[nt][0], ph[nt][1]);
-                    mma_f16(o[nt][mt], va, pl[nt][0], pl[nt][1]);
-                }
-            }
+            slice_step<HD, NT>(k_w, wbegin, lim, qh, ql, o, run_m, run_l, i == 0, scale, k_off, v_off, g);
             __syncwarp();  // every lane has read the slot before the next copies land in it
         }
         // This warp's result goes where its last slice was: that slot receives no copy before the next
@@ -604,6 +616,145 @@ __global__ void __launch_bounds__(kMmaWarps * 32, HD <= 128 && NT == 1 ? 3 : 1) 
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
+// ---- prefill kernel: a run of consecutive tokens of one sequence ---------------------------------------
+//
+// A CTA serves (4 x warp_tokens consecutive tokens, kv head); warp w owns warp_tokens of them (their query heads
+// are its MMA columns) and walks ALL their keys, so there are no spans to merge and the result is final.  The
+// four warps see the same keys up to their diagonals: a 64-key tile is staged in shared memory once per CTA
+// (asynchronous copies, two buffers) and every warp multiplies its own columns against the tile's four
+// 16-key slices with the slice arithmetic of the span kernel.  A token's bits depend only on its own keys.
+template <int HD, int NT>
+__global__ void __launch_bounds__(kMmaWarps * 32) attention_prefill_mma_kernel(const AttnArgs a, const int n_tokens, const int warp_tokens) {
+    using L = MmaLayout<HD>;
+    constexpr int DPL = HD / 32;
+    constexpr int RH = L::RH;
+    constexpr int CPR = HD / 8;
+    extern __shared__ __align__(16) unsigned char attn_smem[];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t4 = lane & 3;
+    const int q_per_kv = a.q_heads / a.kv_heads;
+    const int cta_tokens = kMmaWarps * warp_tokens, cols = warp_tokens * q_per_kv;
+    const int groups = n_tokens / cta_tokens;
+    // the groups with the most keys first
+    const int group = groups - 1 - (int)blockIdx.x / a.kv_heads, kvh = (int)blockIdx.x % a.kv_heads;
+    const int t0 = a.token_base + group * cta_tokens;
+    const int pos0 = a.token_pos[t0];
+    const int32_t* table = a.page_tables + (long long)(a.token_seq != nullptr ? a.token_seq[t0] : 0) * a.pages_per_sequence;
+    const int last = pos0 + cta_tokens - 1;                       // the CTA's last key
+    const int warp_first = pos0 + warp * warp_tokens, warp_last = warp_first + warp_tokens - 1;
+    const int n_tiles = last / kAttnSpanKeys + 1;
+    const long long row_stride = (long long)a.kv_heads * HD;
+    __half* q_hi = reinterpret_cast<__half*>(attn_smem) + (size_t)warp * 2 * 8 * NT * RH;   // this warp's [8 NT][RH]
+    __half* q_lo = q_hi + 8 * NT * RH;
+    __half* tiles = reinterpret_cast<__half*>(attn_smem) + (size_t)kMmaWarps * 2 * 8 * NT * RH;   // [2][4 slices][K 16 | V 16][RH]
+    constexpr int kTileHalfs = kMmaWarps * L::SLOT;
+
+    // thread -> (key row of the tile, half of the row's pieces): one page lookup per thread and tile
+    const int srow = threadIdx.x >> 1, shalf = threadIdx.x & 1;
+    auto stage = [&](int tile) {
+        if (tile < n_tiles) {
+            const int key = tile * kAttnSpanKeys + srow;
+            __half* dk = tiles + (tile & 1) * kTileHalfs + (srow >> 4) * L::SLOT + (srow & 15) * RH + shalf * (HD / 2);
+            __half* dv = dk + kMmaKeys * RH;
+            if (key <= last) {
+                const long long phys = (long long)table[key / kPageTokens] * kPageTokens + key % kPageTokens;
+                const __half* sk = a.cache_k + phys * row_stride + (long long)kvh * HD + shalf * (HD / 2);
+                const __half* sv = a.cache_v + phys * row_stride + (long long)kvh * HD + shalf * (HD / 2);
+#pragma unroll
+                for (int j = 0; j < CPR / 2; ++j) {
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dk + j * 8)), "l"(sk + j * 8) : "memory");
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dv + j * 8)), "l"(sv + j * 8) : "memory");
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < CPR / 2; ++j) {
+                    *reinterpret_cast<uint4*>(dk + j * 8) = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(dv + j * 8) = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage(0);
+
+    // this warp's queries as binary16 hi + lo rows, then its B fragments
+    for (int col = 0; col < cols; ++col) {
+        const float* qp = a.q + ((long long)(t0 + warp * warp_tokens + col / q_per_kv) * a.q_heads + kvh * q_per_kv + col % q_per_kv) * HD;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const float x = qp[lane + 32 * i];
+            const __half hi = __float2half_rn(x);
+            q_hi[col * RH + lane + 32 * i] = hi;
+            q_lo[col * RH + lane + 32 * i] = __float2half_rn(x - __half2float(hi));
+        }
+    }
+    __syncwarp();
+    uint32_t qh[NT][HD / 16][2], ql[NT][HD / 16][2];
+    int lim[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const int col = nt * 8 + g;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int at = col * RH + ks * 16 + 2 * t4 + 8 * u;
+                qh[nt][ks][u] = col < cols ? *reinterpret_cast<const uint32_t*>(q_hi + at) : 0u;
+                ql[nt][ks][u] = col < cols ? *reinterpret_cast<const uint32_t*>(q_lo + at) : 0u;
+            }
+        }
+        const int ca = nt * 8 + 2 * t4;
+        lim[nt][0] = ca < cols ? warp_first + ca / q_per_kv : -1;
+        lim[nt][1] = ca + 1 < cols ? warp_first + (ca + 1) / q_per_kv : -1;
+    }
+    float o[NT][HD / 16][4], run_m[NT][2], run_l[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int mt = 0; mt < HD / 16; ++mt) { o[nt][mt][0] = o[nt][mt][1] = o[nt][mt][2] = o[nt][mt][3] = 0.0f; }
+        run_m[nt][0] = run_m[nt][1] = -INFINITY;
+        run_l[nt][0] = run_l[nt][1] = 0.0f;
+    }
+    const float scale = 1.0f / sqrtf((float)HD);
+    const uint32_t k_off = ((lane & 15) * RH + (lane >> 4) * 8) * 2;
+    const uint32_t v_off = (kMmaKeys * RH + ((lane & 7) + (lane >> 4) * 8) * RH + ((lane >> 3) & 1) * 8) * 2;
+    bool first = true;
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        stage(tile + 1);
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();   // the tile is in place for every warp
+        const __half* buf = tiles + (tile & 1) * kTileHalfs;
+#pragma unroll 1
+        for (int sl = 0; sl < kMmaWarps; ++sl) {
+            const int wbegin = tile * kAttnSpanKeys + sl * kMmaKeys;
+            if (wbegin > warp_last) break;   // past this warp's diagonal
+            slice_step<HD, NT>(buf + sl * L::SLOT, wbegin, lim, qh, ql, o, run_m, run_l, first, scale, k_off, v_off, g);
+            first = false;
+        }
+        __syncthreads();   // every warp has read the buffer before the copies of tile + 2 land in it
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    // out[token][head][d] = o / l: dims 16 mt + g (values 0, 1) and + 8 (values 2, 3) of columns 8 nt + 2 t4 + {0, 1}
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int col = nt * 8 + 2 * t4 + j;
+            if (col < cols) {
+                const int token = t0 + warp * warp_tokens + col / q_per_kv, head = kvh * q_per_kv + col % q_per_kv;
+                float* dst = a.out + ((long long)token * a.q_heads + head) * HD;
+                const float total = run_l[nt][j];
+#pragma unroll
+                for (int mt = 0; mt < HD / 16; ++mt) {
+                    dst[mt * 16 + g] = o[nt][mt][j] / total;
+                    dst[mt * 16 + g + 8] = o[nt][mt][2 + j] / total;
+                }
+            }
+        }
+    }
+}
+
 // The merge: one warp per (token, q head).  A launch of its own, so that the span CTAs retire as soon as their
 // sums are stored and the next projection's weight stream can start under the merge.
 template <int HD>
@@ -646,6 +797,22 @@ cudaError_t launch_pdl(cudaStream_t stream, Kernel kernel, dim3 grid, int thread
 
 template <typename Kernel>
 cudaError_t launch_pdl(cudaStream_t stream, Kernel kernel, dim3 grid, int threads, size_t smem, const AttnArgs& a,
+                       bool programmatic, int extra, int extra2) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3((unsigned int)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, a, extra, extra2);
+}
+
+template <typename Kernel>
+cudaError_t launch_pdl(cudaStream_t stream, Kernel kernel, dim3 grid, int threads, size_t smem, const AttnArgs& a,
                        bool programmatic, int extra) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -660,11 +827,11 @@ cudaError_t launch_pdl(cudaStream_t stream, Kernel kernel, dim3 grid, int thread
     return cudaLaunchKernelEx(&cfg, kernel, a, extra);
 }
 
+// The span kernel and its merge over tokens [first_token, first_token + n_tokens) of the launch.
 template <int HD>
-cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens, int max_keys, size_t partial_bytes,
-                      int* launches, bool programmatic = false) {
+cudaError_t launch_spans_hd(cudaStream_t stream, AttnArgs a, bool fused, int first_token, int n_tokens, int max_keys,
+                            size_t partial_bytes, int* launches, bool programmatic) {
     const int q_per_kv = a.q_heads / a.kv_heads;
-    if (q_per_kv > 16) return cudaErrorInvalidValue;  // the group is the 16 rows of one MMA
     const int max_tiles = (max_keys + kAttnSpanKeys - 1) / kAttnSpanKeys;
     if (max_tiles > kAttnMaxSpans) return cudaErrorInvalidValue;
     // Tiles per span: as many as leave sixteen CTAs per SM's worth of spans (the per-item set-up and the
@@ -701,7 +868,7 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
     }
     for (int base = 0; base < n_tokens; base += chunk) {
         const int n = std::min(chunk, n_tokens - base);
-        a.token_base = base;
+        a.token_base = first_token + base;
         cudaError_t e;
         {
             // persistent CTAs, as many as can be resident, walk the launch's (token, kv head, span) items
@@ -734,6 +901,46 @@ cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens,
     return cudaSuccess;
 }
 
+template <int HD>
+cudaError_t launch_hd(cudaStream_t stream, AttnArgs a, bool fused, int n_tokens, int max_keys, size_t partial_bytes,
+                      int* launches, bool programmatic = false) {
+    const int q_per_kv = a.q_heads / a.kv_heads;
+    if (q_per_kv > 16) return cudaErrorInvalidValue;  // the group is the 16 columns of two MMA tiles
+    // A long run of consecutive tokens of one sequence (a prefill chunk; the caller says where it lies) takes the
+    // prefill kernel for as many whole CTA groups as it holds; what lies before, behind and beyond takes the spans.
+    const int warp_tokens = std::max(1, 16 / q_per_kv), cta_tokens = kMmaWarps * warp_tokens;
+    if (!fused && a.window <= 0 && a.operand.dig == nullptr && a.run_first >= 0 && a.run_count >= 64 &&
+        a.run_first + a.run_count <= n_tokens) {
+        const int aligned = a.run_count / cta_tokens * cta_tokens;
+        const bool wide = warp_tokens * q_per_kv > 8;
+        const size_t smem = (size_t)(kMmaWarps * 2 * 8 * (wide ? 2 : 1) + 2 * kMmaWarps * 2 * kMmaKeys) * (HD + 8) * sizeof(__half);
+        static bool configured_on[kMaxDevices] = {false};  // function attributes are per device
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+        if (!configured_on[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(attention_prefill_mma_kernel<HD, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_prefill_mma_kernel<HD, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e != cudaSuccess) return e;
+            configured_on[dev] = true;
+        }
+        AttnArgs p = a;
+        p.token_base = a.run_first;
+        const dim3 grid((unsigned)(aligned / cta_tokens * a.kv_heads));
+        cudaError_t e = wide ? launch_pdl(stream, attention_prefill_mma_kernel<HD, 2>, grid, kMmaWarps * 32, smem, p, programmatic, aligned, warp_tokens)
+                             : launch_pdl(stream, attention_prefill_mma_kernel<HD, 1>, grid, kMmaWarps * 32, smem, p, programmatic, aligned, warp_tokens);
+        if (e != cudaSuccess) return e;
+        if (launches) ++*launches;
+        if (a.run_first > 0) {
+            e = launch_spans_hd<HD>(stream, a, fused, 0, a.run_first, max_keys, partial_bytes, launches, programmatic);
+            if (e != cudaSuccess) return e;
+        }
+        const int behind = a.run_first + aligned;
+        if (behind < n_tokens) e = launch_spans_hd<HD>(stream, a, fused, behind, n_tokens - behind, max_keys, partial_bytes, launches, programmatic);
+        return e;
+    }
+    return launch_spans_hd<HD>(stream, a, fused, 0, n_tokens, max_keys, partial_bytes, launches, programmatic);
+}
+
 cudaError_t dispatch(cudaStream_t stream, const AttnArgs& a, bool fused, int head_dim, int n_tokens, int max_keys,
                      size_t partial_bytes, int* launches, bool programmatic = false) {
     switch (head_dim) {
@@ -750,7 +957,7 @@ cudaError_t launch_attention(cudaStream_t stream, const float* q, const __half* 
                              const int32_t* page_tables, int pages_per_sequence, const int32_t* token_seq,
                              const int32_t* token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,
                              int window, int max_keys, float* partial, size_t partial_bytes, float* out,
-                             int* launches) {
+                             int* launches, int run_first, int run_count) {
     if (n_tokens <= 0) return cudaSuccess;
     if (q_heads % kv_heads != 0 || q_heads / kv_heads > 16 || max_keys <= 0) return cudaErrorInvalidValue;
     if (head_dim == 32) {
@@ -774,6 +981,7 @@ cudaError_t launch_attention(cudaStream_t stream, const float* q, const __half* 
     a.window = window;
     a.partial = partial;
     a.out = out;
+    a.run_first = run_first; a.run_count = run_count;
     return dispatch(stream, a, false, head_dim, n_tokens, max_keys, partial_bytes, launches);
 }
 
@@ -788,6 +996,7 @@ cudaError_t launch_attention_decode(cudaStream_t stream, const DecodeAttention& 
     a.token_seq = d.token_seq; a.token_pos = d.token_pos; a.token_slot = d.token_slot;
     a.q_heads = d.q_heads; a.kv_heads = d.kv_heads; a.window = d.window;
     a.partial = d.partial; a.out = d.out; a.operand = d.operand;
+    a.run_first = -1; a.run_count = 0;
     const int max_keys = d.window > 0 ? std::min(d.max_keys, d.window) : d.max_keys;
     return dispatch(stream, a, true, d.head_dim, d.n_tokens, max_keys, d.partial_bytes, launches, d.programmatic);
 }

@@ -198,6 +198,7 @@ int pages_for(uint32_t tokens) { return (int)((tokens + kPageTokens - 1) / kPage
 struct StepPlan {
     int n_rows = 0, n_tokens = 0, n_sample = 0, n_prompt_tokens = 0;
     int max_keys = 0;  // longest prefix + tokens of any row
+    int run_first = -1, run_count = 0;  // the longest row's tokens: consecutive positions of one sequence (a prefill chunk)
 };
 
 #define STEP_TRY(expr)                          \
@@ -247,7 +248,7 @@ cudaError_t run_layers_reference(ribn_b200_executor* ex, const StepPlan& plan, i
             cudaError_t e = launch_attention(s, ex->q, ck, cv, ex->d_page_tables, ex->pages_per_sequence,
                                              ex->meta.token_seq, ex->meta.token_pos, T, c.q_heads, c.kv_heads,
                                              c.head_dim, 0, plan.max_keys, ex->scratch.attn_partial,
-                                             ex->scratch.attn_partial_bytes, ex->attn, &launches);
+                                             ex->scratch.attn_partial_bytes, ex->attn, &launches, plan.run_first, plan.run_count);
             if (e != cudaSuccess) return e;
         }
         if (ex->tp > 1) {
@@ -407,7 +408,7 @@ cudaError_t run_layers_decode(ribn_b200_executor* ex, const StepPlan& plan, int&
             cudaError_t e = launch_attention(s, ex->q, ck, cv, ex->d_page_tables, ex->pages_per_sequence,
                                              ex->meta.token_seq, ex->meta.token_pos, T, c.q_heads, c.kv_heads,
                                              c.head_dim, 0, plan.max_keys, ex->scratch.attn_partial,
-                                             ex->scratch.attn_partial_bytes, ex->attn, &launches);
+                                             ex->scratch.attn_partial_bytes, ex->attn, &launches, plan.run_first, plan.run_count);
             if (e != cudaSuccess) return e;
             STEP_TRY(launch_to_operand(s, ex->attn, nullptr, nullptr, T, c.q_heads * c.head_dim, ex->op_attn));
         }
@@ -555,7 +556,7 @@ cudaError_t run_layers_batch(ribn_b200_executor* ex, const StepPlan& plan, int& 
             cudaError_t e = launch_attention(s, ex->q, ck, cv, ex->d_page_tables, ex->pages_per_sequence,
                                              ex->meta.token_seq, ex->meta.token_pos, T, c.q_heads, c.kv_heads,
                                              c.head_dim, 0, plan.max_keys, ex->scratch.attn_partial,
-                                             ex->scratch.attn_partial_bytes, ex->attn, &launches);
+                                             ex->scratch.attn_partial_bytes, ex->attn, &launches, plan.run_first, plan.run_count);
             if (e != cudaSuccess) return e;
         }
         {
@@ -1299,6 +1300,7 @@ int ribn_b200_submit(ribn_b200_executor* ex, const ribn_b200_batch_item* items, 
         r.sample_row = it.output_budget > 0 ? plan.n_sample++ : -1;
         p.sample_row[i] = r.sample_row;
         r.pad[0] = r.pad[1] = r.pad[2] = 0;
+        if ((int)it.token_budget > plan.run_count) { plan.run_first = plan.n_tokens; plan.run_count = (int)it.token_budget; }
         plan.n_tokens += (int)it.token_budget;
         plan.max_keys = std::max(plan.max_keys, (int)(it.prefix + it.token_budget));
     }

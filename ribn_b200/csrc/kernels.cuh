@@ -100,14 +100,17 @@ cudaError_t launch_attention_ref(cudaStream_t stream, const float* q, const __ha
 // as many launches as that scratch requires.  `launches` (optional) is
 // incremented per kernel launch.  `token_seq` may be null: every token then
 // belongs to sequence 0 (one page-table row).  A GQA group has at most
-// 16 query heads.
+// 16 query heads.  `run_first`, `run_count` (optional) tell where a run of
+// consecutive tokens of ONE sequence lies in the launch (a prefill chunk):
+// its whole groups of 4 x (16 / group size) tokens take a kernel that stages
+// each key tile once for such a group and walks all its keys, no merge.
 constexpr int kAttnSpanKeys = 64;
 constexpr int kAttnMaxSpans = 1024;  // tiles per token: 65536 keys
 cudaError_t launch_attention(cudaStream_t stream, const float* q, const __half* cache_k, const __half* cache_v,
                              const int32_t* page_tables, int pages_per_sequence, const int32_t* token_seq,
                              const int32_t* token_pos, int n_tokens, int q_heads, int kv_heads, int head_dim,
                              int window, int max_keys, float* partial, size_t partial_bytes, float* out,
-                             int* launches);
+                             int* launches, int run_first = -1, int run_count = 0);
 
 // Decode form of the same attention for rows that add exactly one token: it
 // also applies the per-head Q/K RMSNorm and rotary to the raw projections,

@@ -516,7 +516,7 @@ int ribn_b200_op_attention(int32_t device, const float* q, const uint16_t* keys,
         float* d_partial = s.alloc<float>(bytes / sizeof(float));
         OP_PTR(d_partial);
         OP_TRY(launch_attention(s.stream, d_q, d_k, d_v, d_table, pages, d_seq, d_pos, rows, q_heads, kv_heads,
-                                head_dim, window, tokens, d_partial, bytes, d_o, nullptr));
+                                head_dim, window, tokens, d_partial, bytes, d_o, nullptr, 0, rows));
     }
     return s.download(out, d_o, (size_t)rows * q_heads * head_dim) ? RIBN_B200_OK : RIBN_B200_ERROR;
 }
