@@ -2,11 +2,13 @@
 // ("flash-decoding") over spans of 64-key tiles with an online softmax, then a
 // deterministic merge of the spans.
 //
-// Every launch runs the tensor-core span kernel below (the GQA group's query
-// heads against 16-key slices as m16n8k16 MMAs, K / V staged in shared memory
-// once per group by asynchronous copies), then the merge kernel.  A token's
+// Launches run the tensor-core span kernel below (the GQA group's query heads
+// against 16-key slices as m16n8k16 MMAs, K / V staged in shared memory by
+// asynchronous copies), then the merge kernel; the whole sixteen-token groups
+// of a prefill chunk run the prefill kernel instead (a key tile staged once per
+// group, every warp walks all the keys of its own tokens, no merge).  A token's
 // result depends only on its own keys and on the launch's size class (tiles
-// per span), never on where its pages live.
+// per span; chunk or not), never on where its pages live.
 //
 // The decode form (FUSED) also applies the per-head Q/K RMSNorm and the NeoX
 // rotary and appends the new K/V row to the paged cache: the CTA that owns
