@@ -192,6 +192,7 @@ def replica_throughput(dist, world: int, rows: int, steps: int, seconds: float, 
     return world * rows * steps / all_max(dist, seconds, device)
 
 
+EXTRA_FLAGS = 0      # set from --operand-cache: ribn_b200.FLAG_OPERAND_CACHE on every Qwen executor of the run
 SCHEME = "q4_k_m"   # set from --scheme: "q4_k_m" (Q4_K; Q6_K for attn_v, ffn_down, output) or "q8_0"
 
 
@@ -199,7 +200,7 @@ def build_executor(model: dict, batch: int, context: int, decode_tokens: int, de
     import ribn_b200
     span = context + decode_tokens + 16
     ex = ribn_b200.QwenB200(model, context_tokens=span, max_sequences=batch, max_batch_tokens=max(batch, 16),
-                            device=device, flags=ribn_b200.FLAG_KEEP_LOGITS if keep_logits else 0)
+                            device=device, flags=(ribn_b200.FLAG_KEEP_LOGITS if keep_logits else 0) | EXTRA_FLAGS)
     ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q8_0 if SCHEME == "q8_0" else ribn_b200.SCHEME_Q4_K_M)
     return ex
 
@@ -263,7 +264,8 @@ def decode_workload(args, batch: int) -> dict:
     """The `config` object of the decode workload: the same for both arms."""
     return {"workload": f"{args.model} {args.scheme.upper()}-style decode, batch 1 and {batch}, context {args.context}, "
                         f"16-token KV pages, one replica per GPU",
-            "l2": "inputs larger than L2 (4.9 GB of weights streamed per step)"}
+            "l2": "inputs larger than L2 (4.9 GB of weights streamed per step)",
+            "operand_cache": bool(EXTRA_FLAGS)}
 
 
 def run_ours(args):
@@ -395,6 +397,21 @@ def run_ours(args):
                           "spread": spreadb,
                           "x_batch1": (world * B * args.steps / devb) / value1}
     ex.close()
+    if B >= 3 and not EXTRA_FLAGS and not args.no_cache_leg and args.scheme == "q4_k_m":
+        # the same batch once more on an executor that keeps the K-quant matrices as tensor-core operands
+        # (RIBN_B200_FLAG_OPERAND_CACHE: 2 or 4 bytes of HBM per weight; same logits bit for bit)
+        ex = ribn_b200.QwenB200(model, context_tokens=args.context + 2 * total_steps + 20, max_sequences=B,
+                                max_batch_tokens=max(B, 16), device=local, flags=ribn_b200.FLAG_OPERAND_CACHE)
+        ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q4_K_M)
+        ex.finalize()
+        seed_sequences(ex, model, B, args.context, 2 * total_steps + 4, seed=1 + rank)
+        positions = {s + 1: args.context for s in range(B)}
+        _, devc, launchesc, _, spreadc = phase(list(range(1, B + 1)), 3)
+        out["batch64"]["operand_cache"] = {"value": world * B * args.steps / devc, "unit": "tok/s",
+                                           "ms_per_step": devc / args.steps * 1e3, "gpu_launches": launchesc,
+                                           "spread": spreadc,
+                                           "note": "K-quant matrices also kept as binary16 operand planes (Q4_K 2 B, Q6_K 4 B per weight)"}
+        ex.close()
     if not args.no_serving:
         # p50 time to first token is part of the metric: a bounded serving leg below saturation
         srv = serving_job(args, rank, world, local, dist, n=args.serving_requests, rate=args.arrival_rate_default,
@@ -420,7 +437,7 @@ def run_prefill(args):
     model = MODELS[args.model]
     chunk = 2048
     length = max(chunk, args.context // chunk * chunk)
-    ex = ribn_b200.QwenB200(model, context_tokens=length + 16, max_sequences=2, max_batch_tokens=chunk, device=local, flags=0)
+    ex = ribn_b200.QwenB200(model, context_tokens=length + 16, max_sequences=2, max_batch_tokens=chunk, device=local, flags=EXTRA_FLAGS)
     ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q8_0 if SCHEME == "q8_0" else ribn_b200.SCHEME_Q4_K_M)
     ex.finalize()
     rng = np.random.default_rng(7 + rank)
@@ -458,7 +475,8 @@ def run_prefill(args):
         "dtype": f"f16 x f16 tensor-core products over exact {'Q8_0 values' if args.scheme == 'q8_0' else 'K-quant integers'}, f32 scales and accumulation, f16 KV",
         "data": "synthetic",
         "config": {"workload": f"{args.model} {args.scheme.upper()}-style prefill of one {length}-token prompt per step in {chunk}-token chunks, "
-                               f"16-token KV pages, one replica per GPU", "l2": "inputs larger than L2", "parallelism": f"replicas x{world}"},
+                               f"16-token KV pages, one replica per GPU", "l2": "inputs larger than L2", "parallelism": f"replicas x{world}",
+                   "operand_cache": bool(EXTRA_FLAGS)},
         "e2e": {"value": tokens / wall, "unit": "tok/s", "h2d_bytes_per_step": 4 * length, "d2h_bytes_per_step": 4},
         "gpu_launches": launches,
         "chunk_ms": [float(v) for v in np.median(per_chunk, axis=0)],
@@ -513,7 +531,7 @@ def serving_job(args, rank, world, local, dist, n, rate, workload):
     chunk = min(2048, int(prompts.max()))
     pages = int(sum((int(p) + int(o) + 15) // 16 for p, o in zip(prompts, outputs))) + active
     ex = ribn_b200.QwenB200(model, context_tokens=int((prompts + outputs).max() + 16), max_sequences=active,
-                            max_batch_tokens=chunk + active, kv_pages=pages, device=local, flags=0)
+                            max_batch_tokens=chunk + active, kv_pages=pages, device=local, flags=EXTRA_FLAGS)
     ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q8_0 if SCHEME == "q8_0" else ribn_b200.SCHEME_Q4_K_M)
     ex.finalize()
     engine = Engine(ex, EngineConfig(max_active_requests=active, max_queued_requests=n),
@@ -551,7 +569,7 @@ def serving_job(args, rank, world, local, dist, n, rate, workload):
         "data": "synthetic",
         "config": {"workload": f"{args.model} {args.scheme.upper()}-style {workload}: {n} requests per GPU, {described}, {active} active, "
                                f"{chunk}-token prefill chunks, 16-token KV pages",
-                   "parallelism": f"replicas x{world}"},
+                   "parallelism": f"replicas x{world}", "operand_cache": bool(EXTRA_FLAGS)},
         "ttft_ms": {"p50": float(np.percentile(ttft, 50) * 1e3), "p95": float(np.percentile(ttft, 95) * 1e3),
                     "definition": "planned arrival -> first token", "arrival_rate_per_s": rate if workload != "mixed" else None,
                     "requests": n},
@@ -582,7 +600,7 @@ def run_tp(args):
     span = int(contexts.max()) + steps_total + 16
     pages = int(sum((int(c) + steps_total + 16 + 15) // 16 for c in contexts)) + B
     ex = ribn_b200.QwenB200(model, context_tokens=span, max_sequences=B, max_batch_tokens=max(B, 16), kv_pages=pages,
-                            device=local, flags=0, tp_size=world, tp_rank=rank)
+                            device=local, flags=EXTRA_FLAGS, tp_size=world, tp_rank=rank)
     ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q8_0 if SCHEME == "q8_0" else ribn_b200.SCHEME_Q4_K_M)
     ids = [ribn_b200.tp_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(ids, src=0)
@@ -620,7 +638,7 @@ def run_tp(args):
         "data": "synthetic",
         "config": {"workload": f"{args.model} {args.scheme.upper()}-style decode, {B} concurrent sequences, contexts U[512,{args.context_max}], "
                                f"16-token KV pages, tensor parallel over {world} GPUs (NCCL all-reduce after o_proj and down_proj)",
-                   "l2": "inputs larger than L2", "parallelism": f"tp{world}"},
+                   "l2": "inputs larger than L2", "parallelism": f"tp{world}", "operand_cache": bool(EXTRA_FLAGS)},
         "e2e": {"value": B * args.steps / wall, "unit": "tok/s", "h2d_bytes_per_step": 32 * B, "d2h_bytes_per_step": 4 * B},
         "gpu_launches": launches, "clocks": clocks.summary(),
         "per_rank": {"weight_bytes": w_bytes, "kv_bytes_per_step": kv_bytes,
@@ -834,10 +852,16 @@ def main():
     ap.add_argument("--gemma-new-tokens", type=int, default=32, help="gemma: greedy tokens per prompt")
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel group size (= ranks); runs the tensor-parallel decode workload")
     ap.add_argument("--context-max", type=int, default=8192, help="tp: contexts are uniform in [512, this]")
+    ap.add_argument("--no-cache-leg", action="store_true", help="decode: skip the extra batch leg with the operand cache on")
+    ap.add_argument("--operand-cache", default="off", choices=["on", "off"],
+                    help="keep the K-quant matrices also as tensor-core operands in HBM (RIBN_B200_FLAG_OPERAND_CACHE)")
     ap.add_argument("--scheme", default="q4_k_m", choices=["q4_k_m", "q8_0"], help="synthetic checkpoint's block types")
     args = ap.parse_args()
-    global SCHEME
+    global SCHEME, EXTRA_FLAGS
     SCHEME = args.scheme
+    if args.operand_cache == "on" and args.impl != "reference":
+        import ribn_b200
+        EXTRA_FLAGS = ribn_b200.FLAG_OPERAND_CACHE
     if args.warmup < 3:
         args.warmup = 3
     if args.requests is None:

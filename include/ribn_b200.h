@@ -89,8 +89,11 @@ enum {
                                              (slow; used to cross-check the fast path) */
     RIBN_B200_FLAG_NO_GRAPH = 4,      /* launch kernels directly instead of replaying graphs */
     RIBN_B200_FLAG_NO_TCGEN05 = 8,    /* batches of 3+ rows on the integer mma.sync kernel instead of tcgen05 */
-    RIBN_B200_FLAG_KV_ON_DEMAND = 16  /* admit reserves the prompt's KV pages only; prepare takes the pages a row's
+    RIBN_B200_FLAG_KV_ON_DEMAND = 16, /* admit reserves the prompt's KV pages only; prepare takes the pages a row's
                                          range needs and defers the rows the arena cannot serve */
+    RIBN_B200_FLAG_OPERAND_CACHE = 32 /* finalize also keeps every Q4_K / Q6_K matrix as tcgen05 operands (binary16
+                                         integers, 2 or 4 bytes of HBM per weight); steps of 3+ rows then copy operand
+                                         stages instead of converting packed tiles.  Same results bit for bit. */
 };
 
 /* GenerationLimits (crates/runtime/src/executor.rs:43-51). */
@@ -333,7 +336,9 @@ RIBN_B200_API int ribn_b200_op_embedding(int32_t device, int32_t ggml_type, cons
  * GEMV kernels (members in pairs), 1 = one-warp-per-row reference kernels,
  * 2 = the batched integer tensor-core kernel (up to 64 members per launch),
  * 3 = the tcgen05 / tensor-memory kernels (K-quant integer form for Q4_K / Q6_K,
- * decode-and-split form for Q8_0), 4 = the decode-and-split form for every type. */
+ * decode-and-split form for Q8_0), 4 = the decode-and-split form for every type,
+ * 5 = the K-quant form over operands converted once (what RIBN_B200_FLAG_OPERAND_CACHE
+ * runs; Q4_K / Q6_K only; bit-identical to variant 3). */
 RIBN_B200_API int ribn_b200_op_gemv(int32_t device, int32_t ggml_type, const void* weights,
                                     int64_t rows, int64_t cols, const float* x, int32_t members,
                                     float* y, int32_t variant);

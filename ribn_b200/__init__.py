@@ -9,7 +9,7 @@ computes anything on the CPU and fails loudly when the library is missing.
 from ._lib import (  # noqa: F401
     F32, F16, Q8_0, Q4_K, Q6_K, OK, PENDING, REJECTED, DEFERRED, SELECTED, ERROR, PREFILL, DECODE,
     SCHEME_Q8_0, SCHEME_Q4_K_M, FLAG_KEEP_LOGITS, FLAG_REFERENCE_KERNELS, FLAG_NO_GRAPH, FLAG_NO_TCGEN05,
-    FLAG_KV_ON_DEMAND, INJECT_ALLOC_REFUSAL, INJECT_ERROR_WORD, INJECT_BAD_ROW,
+    FLAG_KV_ON_DEMAND, FLAG_OPERAND_CACHE, INJECT_ALLOC_REFUSAL, INJECT_ERROR_WORD, INJECT_BAD_ROW,
     Config, lib, library_path,
 )
 from .executor import (  # noqa: F401

@@ -14,6 +14,7 @@ INJECT_ALLOC_REFUSAL, INJECT_ERROR_WORD, INJECT_BAD_ROW = 1, 2, 3
 PREFILL, DECODE = 0, 1
 SCHEME_Q8_0, SCHEME_Q4_K_M = 0, 1
 FLAG_KEEP_LOGITS, FLAG_REFERENCE_KERNELS, FLAG_NO_GRAPH, FLAG_NO_TCGEN05, FLAG_KV_ON_DEMAND = 1, 2, 4, 8, 16
+FLAG_OPERAND_CACHE = 32
 
 
 class Config(C.Structure):

@@ -469,7 +469,7 @@ cudaError_t batch_project(ribn_b200_executor* ex, int& launches, const float* x,
         a.n_segments = n_mats;
         for (int i = 0; i < n_mats; ++i) {
             a.seg[i] = GemvSegment{mats[i]->packed.data, mats[i]->type, (int)mats[i]->rows, mats[i]->packed.row_tiles,
-                                   ys[i] + (size_t)base * mats[i]->rows};
+                                   ys[i] + (size_t)base * mats[i]->rows, mats[i]->op_a, mats[i]->op_meta};
         }
         a.k = k;
         a.members = m;
@@ -908,7 +908,15 @@ int ribn_b200_finalize(ribn_b200_executor* ex) {
             repack_host(t->type, raw.data(), t->rows, t->cols, packed.data(), threads);
             CU_TRY(ex, dev_alloc(ex, &p.data, p.bytes));
             CU_TRY(ex, cudaMemcpy(p.data, packed.data(), p.bytes, cudaMemcpyHostToDevice));
+            // the tensor-memory GEMM's operands, converted once instead of on every use
+            if ((c.flags & RIBN_B200_FLAG_OPERAND_CACHE) && !(c.flags & RIBN_B200_FLAG_NO_TCGEN05) &&
+                (t->type == kQ4_K || t->type == kQ6_K)) {
+                CU_TRY(ex, dev_alloc(ex, &t->op_a, tc_cache_a_bytes(t->type, t->rows, t->cols)));
+                CU_TRY(ex, dev_alloc(ex, &t->op_meta, tc_cache_meta_bytes(t->rows, t->cols)));
+                CU_TRY(ex, launch_tc_cache(ex->stream, t->type, p.data, t->rows, t->cols, t->op_a, t->op_meta));
+            }
         }
+        CU_TRY(ex, cudaStreamSynchronize(ex->stream));
     }
 
     CU_TRY(ex, gemv_prepare());

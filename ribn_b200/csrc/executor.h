@@ -22,6 +22,8 @@ struct Tensor {
     size_t bytes = 0;
     unsigned char* raw = nullptr;  // encoded GGUF bytes, verbatim
     PackedMatrix packed;           // tile-major repack for the fast kernels (matrices only)
+    unsigned char* op_a = nullptr;     // K-quant matrices under RIBN_B200_FLAG_OPERAND_CACHE: tensor-core operand
+    unsigned char* op_meta = nullptr;  // pieces and their per-k-tile records (launch_tc_cache)
     bool loaded() const { return raw != nullptr; }
 };
 

@@ -1225,6 +1225,337 @@ __global__ void __launch_bounds__(kKq2Threads, 1) gemm_tcq2_kernel(const GemmArg
     }
 }
 
+}  // namespace
+
+// ---- converted-operand cache ------------------------------------------------------------------------
+// The kernels above convert every packed weight stage into the tensor core's operand form each time it is
+// used.  With 180 GB of HBM the converted form can simply be kept: per unit (128 rows) and k tile, the four
+// 64-input pieces of the A operand exactly as kq_chunk leaves them in shared memory (one binary16 plane of
+// 16 KB per piece for Q4_K, two for Q6_K), and a 5 KB record with the rows' scales and the minima operand.
+// gemm_tcqc_kernel is the K-quant GEMM without conversion warps: a producer thread brings the pieces in with bulk
+// copies, everything downstream (MMA thread, tensor-memory sums, fold, outputs) is the arithmetic of the
+// kernels above on identical operand bytes, so results are identical.  What a launch then streams per step is
+// the converted bytes (2 or 4 per weight), which is what bounds it.
+constexpr int kCachePieceBytes = kAHalfBytes;                        // one plane of one 64-input piece: 16 KB
+constexpr int kCacheMetaBytes = kRows * (int)sizeof(float2) + kA2Bytes;   // row scales, then the minima operand
+
+size_t tc_cache_a_bytes(int type, long long rows, long long cols) {
+    const long long units = (rows + kRows - 1) / kRows, k_tiles = cols / kTileCols;
+    return (size_t)units * k_tiles * kChunksPerTile * (type == kQ4_K ? 1 : 2) * kCachePieceBytes;
+}
+size_t tc_cache_meta_bytes(long long rows, long long cols) {
+    const long long units = (rows + kRows - 1) / kRows, k_tiles = cols / kTileCols;
+    return (size_t)units * k_tiles * kCacheMetaBytes;
+}
+
+namespace {
+
+// One block per (unit, k tile): warp w converts row tile w of the unit with kq_chunk, straight into the cache.
+__global__ void __launch_bounds__(kRowTilesPerUnit * 32) tcq_cache_kernel(int type, const unsigned char* packed, int row_tiles, int k_tiles,
+                                                                          unsigned char* cache_a, unsigned char* cache_meta) {
+    const int unit = blockIdx.x / k_tiles, kb = blockIdx.x % k_tiles, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int planes = type == kQ4_K ? 1 : 2, rt = unit * kRowTilesPerUnit + warp;
+    unsigned char* a_tile = cache_a + ((size_t)unit * k_tiles + kb) * kChunksPerTile * planes * kCachePieceBytes;
+    unsigned char* meta = cache_meta + ((size_t)unit * k_tiles + kb) * kCacheMetaBytes;
+    float2* scales = reinterpret_cast<float2*>(meta);
+    unsigned char* a2 = meta + kRows * sizeof(float2);
+    // the minima operand: eight group minima per row, then eight zeros (all zero for Q6_K)
+    for (int i = threadIdx.x; i < kA2Bytes / 16; i += blockDim.x) reinterpret_cast<uint4*>(a2)[i] = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
+    const bool present = rt < row_tiles;
+    const unsigned char* tile = packed + ((size_t)rt * k_tiles + kb) * packed_tile_bytes(type);
+    for (int c = 0; c < kChunksPerTile; ++c) {
+        unsigned char* planes_at = a_tile + (size_t)c * planes * kCachePieceBytes;
+        if (present) {
+            kq_chunk(type, tile, c, 0, planes_at, a2, scales, warp * kTileRows, 0, lane);
+            kq_chunk(type, tile, c, 0, planes_at, a2, scales, warp * kTileRows, 1, lane);
+        } else {
+            for (int pl = 0; pl < planes; ++pl) {
+                zero_rows_plane(planes_at + (size_t)pl * kCachePieceBytes, warp * kTileRows, lane);
+                zero_rows_plane(planes_at + (size_t)pl * kCachePieceBytes, warp * kTileRows + 8, lane);
+            }
+            if (c == 0 && lane < 16) {
+                const int unit_row = warp * kTileRows + lane;
+                scales[unit_row] = make_float2(0.0f, 0.0f);
+                *reinterpret_cast<uint4*>(a2 + (unit_row >> 3) * 128 + (unit_row & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+    }
+}
+
+constexpr int kKqcEpilogueWarps = 8;
+constexpr int kKqcProducerWarp = 8;
+constexpr int kKqcMmaWarp = 9;
+constexpr int kKqcChunkWarp0 = 10;
+constexpr int kKqcThreads = (kKqcChunkWarp0 + 2) * 32;
+
+struct KqcLayout {
+    int stages, pieces, m_slots, stage_bytes, b_bytes, b2_bytes, cols, members_padded;
+    int k_slices, total_n, groups;
+    size_t group_bytes;
+};
+
+// GROUPS row groups per work item (1: up to 64 members, K may be split; 2: whole groups of 64 in pairs).
+template <int GROUPS>
+__global__ void __launch_bounds__(kKqcThreads, 1) gemm_tcqc_kernel(const GemmArgs a, const KqcLayout lay, const int units) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_tiles = a.k / kTileCols;
+    const uint32_t spin_limit = a.spin_limit ? a.spin_limit : kSpinLimit;
+    // A ring of stages (`pieces` 64-input pieces of the operand with the activation chunks they meet; one commit
+    // frees both), and a ring of the k tiles' records.
+    const uint32_t na = (uint32_t)lay.stages, nm = (uint32_t)lay.m_slots;
+    const int pieces = lay.pieces, stages_per_tile = kChunksPerTile / pieces;
+    const int meta_slot = kCacheMetaBytes + GROUPS * lay.b2_bytes;
+    const int b_stage_bytes = pieces * GROUPS * lay.b_bytes;
+    unsigned char* a_buf = smem;                                                       // [stages][stage_bytes]
+    unsigned char* b_buf = a_buf + (size_t)lay.stages * lay.stage_bytes;               // [stages][GROUPS][pieces][b_bytes]
+    unsigned char* meta_buf = b_buf + (size_t)lay.stages * b_stage_bytes;              // [m_slots][scales | minima operand | GROUPS group sums]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(meta_buf + (size_t)lay.m_slots * meta_slot);
+    const uint32_t bars = smem_u32(tmem_slot + 4);
+    const uint32_t a_full = bars, a_empty = bars + 128, b_full = bars + 256, m_full = bars + 384, m_empty = bars + 416,
+                   t_full = bars + 448, t_empty = bars + 464;   // at most 16 stages and 4 records
+    const int S = lay.k_slices, tps = (k_tiles + S - 1) / S, G = GROUPS == 1 ? lay.groups : lay.groups / 2, items = units * G * S;
+    auto unit_index = [&](int item) { return item / (G * S); };
+    auto group_index = [&](int item) { return (item / S) % G; };   // GROUPS == 2: index of the pair
+    constexpr uint32_t kLag = GROUPS == 1 ? 2u : 1u;   // accumulator buffers: two by k tile parity, or one per group
+    const size_t tile_stride = (size_t)kChunksPerTile * lay.b_bytes + lay.b2_bytes;   // one k tile of one group's activations
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < lay.stages; ++i) { mbar_init(a_full + 8 * i, 1); mbar_init(a_empty + 8 * i, 1); mbar_init(b_full + 8 * i, 1); }
+        for (int i = 0; i < lay.m_slots; ++i) { mbar_init(m_full + 8 * i, 1); mbar_init(m_empty + 8 * i, kKqcEpilogueWarps); }
+        for (int i = 0; i < 2; ++i) { mbar_init(t_full + 8 * i, 1); mbar_init(t_empty + 8 * i, kKqcEpilogueWarps); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kKqcMmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+    if (warp == kKqcProducerWarp) {
+        if (lane == 0) {
+            bool alive = true;
+            uint32_t a_count = 0, kt_count = 0;
+            for (int item = blockIdx.x; item < items; item += gridDim.x) {
+                const UnitRef ur = unit_of(a, unit_index(item));
+                const GemvSegment& s = a.seg[ur.seg];
+                const uint32_t stage_bytes = (uint32_t)(s.type == kQ4_K ? 1 : 2) * kCachePieceBytes * (uint32_t)pieces;
+                const size_t unit_local = (size_t)(ur.rt0 / kRowTilesPerUnit);
+                const int kb0 = (item % S) * tps, kb1 = min(k_tiles, kb0 + tps);
+                for (int kb = kb0; kb < kb1; ++kb, ++kt_count) {
+                    const uint32_t ms = kt_count % nm;
+                    // the record slot was last read by the minima MMAs and the fold of k tile kt - m_slots
+                    if (kt_count >= nm && alive) alive = mbar_wait_relaxed(m_empty + 8 * ms, ((kt_count / nm) - 1u) & 1u, a.error_flag, 61, spin_limit);
+                    unsigned char* slot = meta_buf + (size_t)ms * meta_slot;
+                    mbar_expect_tx(m_full + 8 * ms, (uint32_t)meta_slot);
+                    bulk_g2s(smem_u32(slot), s.op_meta + (unit_local * k_tiles + kb) * kCacheMetaBytes, (uint32_t)kCacheMetaBytes, m_full + 8 * ms);
+                    for (int g = 0; g < GROUPS; ++g) {
+                        bulk_g2s(smem_u32(slot + kCacheMetaBytes + (size_t)g * lay.b2_bytes),
+                                 a.chunks + (size_t)(GROUPS * group_index(item) + g) * lay.group_bytes + (size_t)kb * tile_stride + (size_t)kChunksPerTile * lay.b_bytes,
+                                 (uint32_t)lay.b2_bytes, m_full + 8 * ms);
+                    }
+                    for (int c = 0; c < stages_per_tile; ++c, ++a_count) {
+                        const uint32_t st = a_count % na;
+                        if (a_count >= na && alive) alive = mbar_wait_relaxed(a_empty + 8 * st, ((a_count / na) - 1u) & 1u, a.error_flag, 62, spin_limit);
+                        mbar_expect_tx(a_full + 8 * st, stage_bytes);
+                        bulk_g2s(smem_u32(a_buf + (size_t)st * lay.stage_bytes),
+                                 s.op_a + ((unit_local * k_tiles + kb) * stages_per_tile + c) * stage_bytes, stage_bytes, a_full + 8 * st);
+                    }
+                }
+            }
+        }
+    } else if (warp >= kKqcChunkWarp0) {
+        if (lane == 0) {
+            bool alive = true;
+            const int which = warp - kKqcChunkWarp0;
+            uint32_t b_count = 0;
+            for (int item = blockIdx.x; item < items; item += gridDim.x) {
+                const int kb0 = (item % S) * tps, kb1 = min(k_tiles, kb0 + tps);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    for (int c = 0; c < stages_per_tile; ++c, ++b_count) {
+                        if ((c & 1) != which) continue;
+                        const uint32_t bs = b_count % na;
+                        if (b_count >= na && alive) alive = mbar_wait_relaxed(a_empty + 8 * bs, ((b_count / na) - 1u) & 1u, a.error_flag, 63, spin_limit);
+                        mbar_expect_tx(b_full + 8 * bs, (uint32_t)b_stage_bytes);
+                        for (int g = 0; g < GROUPS; ++g) {
+                            const signed char* src = a.chunks + (size_t)(GROUPS * group_index(item) + g) * lay.group_bytes + (size_t)kb * tile_stride;
+                            bulk_g2s(smem_u32(b_buf + (size_t)bs * b_stage_bytes + (size_t)g * pieces * lay.b_bytes), src + (size_t)c * pieces * lay.b_bytes,
+                                     (uint32_t)(pieces * lay.b_bytes), b_full + 8 * bs);
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == kKqcMmaWarp) {
+        if (lane == 0) {
+            bool alive = true;
+            uint32_t count = 0, kt_count = 0;
+            const uint32_t idesc = umma_idesc(lay.cols);
+            const uint32_t b_lbo = (uint32_t)(lay.cols / 8) * 128u;
+            for (int item = blockIdx.x; item < items; item += gridDim.x) {
+                const bool q4k = a.seg[unit_of(a, unit_index(item)).seg].type == kQ4_K;
+                const int kb0 = (item % S) * tps, kb1 = min(k_tiles, kb0 + tps);
+                for (int kb = kb0; kb < kb1; ++kb, ++kt_count) {
+                    const uint32_t p = kt_count & 1u;
+                    if (kt_count >= kLag && alive) {
+                        const uint32_t before = kt_count - kLag;   // the k tile whose fold frees these accumulators
+                        alive = mbar_wait(t_empty + 8 * (before & 1u), (before >> 1) & 1u, a.error_flag, 64, spin_limit);
+                    }
+                    tc_fence_after();
+                    const uint32_t ms = kt_count % nm;
+                    const unsigned char* slot = meta_buf + (size_t)ms * meta_slot;
+                    for (int c = 0; c < stages_per_tile; ++c, ++count) {
+                        const uint32_t st = count % na;
+                        if (alive) alive = mbar_wait(a_full + 8 * st, (count / na) & 1u, a.error_flag, 65, spin_limit);
+                        if (alive) alive = mbar_wait(b_full + 8 * st, (count / na) & 1u, a.error_flag, 66, spin_limit);
+                        tc_fence_after();
+                        const uint64_t da_step = (uint64_t)((2 * kALbo) >> 4), db_step = (uint64_t)((2 * b_lbo) >> 4);
+                        const uint64_t da_plane = (uint64_t)(kAHalfBytes >> 4);
+                        for (int piece = 0; piece < pieces; ++piece) {
+                            // a stage of several pieces holds one plane each (Q4_K only)
+                            const uint32_t a_addr = smem_u32(a_buf + (size_t)st * lay.stage_bytes + (size_t)piece * kCachePieceBytes);
+                            for (int g = 0; g < GROUPS; ++g) {
+                                const uint32_t b_addr = smem_u32(b_buf + (size_t)st * b_stage_bytes + (size_t)(g * pieces + piece) * lay.b_bytes);
+                                uint64_t da = umma_desc(a_addr, kALbo, 128), db = umma_desc(b_addr, b_lbo, 128);
+                                const uint32_t d_main = tmem_base + 128u * (GROUPS == 1 ? p : (uint32_t)g);
+                                if (q4k) {
+#pragma unroll
+                                    for (int s16 = 0; s16 < kChunkK / 16; ++s16, da += da_step, db += db_step) {
+                                        umma_f16(d_main, da, db, idesc, (c | piece | s16) != 0 ? 1u : 0u);
+                                    }
+                                } else {
+#pragma unroll
+                                    for (int s16 = 0; s16 < kChunkK / 16; ++s16, da += da_step, db += db_step) {
+                                        umma_f16(d_main, da, db, idesc, (c | piece | s16) != 0 ? 1u : 0u);
+                                        umma_f16(d_main, da + da_plane, db, idesc, 1u);
+                                    }
+                                }
+                            }
+                        }
+                        if (c == stages_per_tile - 1) {
+                            if (alive) alive = mbar_wait(m_full + 8 * ms, (kt_count / nm) & 1u, a.error_flag, 67, spin_limit);
+                            tc_fence_after();
+                            if (q4k) {
+                                for (int g = 0; g < GROUPS; ++g) {
+                                    umma_f16(tmem_base + 256u + 128u * (GROUPS == 1 ? p : (uint32_t)g),
+                                             umma_desc(smem_u32(slot + kRows * sizeof(float2)), kALbo, 128),
+                                             umma_desc(smem_u32(slot + kCacheMetaBytes + (size_t)g * lay.b2_bytes), b_lbo, 128), idesc, 0u);
+                                }
+                            }
+                        }
+                        umma_commit(a_empty + 8 * st);
+                    }
+                    umma_commit(t_full + 8 * p);
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue warps: (lane quadrant, member half) ----------------
+        bool alive = true;
+        uint32_t kt_count = 0;
+        const int quadrant = warp & 3, half = warp >> 2;
+        const int row = quadrant * 32 + lane;
+        for (int item = blockIdx.x; item < items; item += gridDim.x) {
+            const UnitRef ur = unit_of(a, unit_index(item));
+            const GemvSegment& s = a.seg[ur.seg];
+            const bool q4k = s.type == kQ4_K;
+            const int slice = item % S, kb0 = slice * tps, kb1 = min(k_tiles, kb0 + tps);
+            float acc[GROUPS][32];
+#pragma unroll
+            for (int g = 0; g < GROUPS; ++g) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[g][i] = 0.0f;
+            }
+            for (int kb = kb0; kb < kb1; ++kb, ++kt_count) {
+                const uint32_t p = kt_count & 1u;
+                if (alive) alive = mbar_wait(t_full + 8 * p, (kt_count >> 1) & 1u, a.error_flag, 68, spin_limit);
+                // the record's own barrier (complete by now: the minima MMAs followed it), for the copy's bytes
+                const uint32_t ms = kt_count % nm;
+                if (alive) alive = mbar_wait(m_full + 8 * ms, (kt_count / nm) & 1u, a.error_flag, 69, spin_limit);
+                tc_fence_after();
+                const float2 ds = reinterpret_cast<const float2*>(meta_buf + (size_t)ms * meta_slot)[row];
+                // the record is free again: its scales are in registers, and the MMAs that read its operands are complete
+                __syncwarp();
+                if (lane == 0) mbar_arrive(m_empty + 8 * ms);
+#pragma unroll
+                for (int g = 0; g < GROUPS; ++g) {
+                    const uint32_t t_main = tmem_base + 128u * (GROUPS == 1 ? p : (uint32_t)g) + ((uint32_t)(quadrant * 32) << 16), t_min = t_main + 256u;
+#pragma unroll
+                    for (int m0 = 0; m0 < 32; m0 += 16) {
+                        if (32 * half + m0 < lay.members_padded) {
+                            float hi[16], lo[16];
+                            tmem_ld16(t_main + (uint32_t)(32 * half + m0), hi);
+                            tmem_ld16(t_main + (uint32_t)(lay.members_padded + 32 * half + m0), lo);
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) acc[g][m0 + i] = fmaf(ds.x, hi[i] + lo[i], acc[g][m0 + i]);
+                            if (q4k) {
+                                tmem_ld16(t_min + (uint32_t)(32 * half + m0), hi);
+                                tmem_ld16(t_min + (uint32_t)(lay.members_padded + 32 * half + m0), lo);
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) acc[g][m0 + i] = fmaf(-ds.y, hi[i] + lo[i], acc[g][m0 + i]);
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(t_empty + 8 * p);
+            }
+            const int n_index = ur.rt0 * kTileRows + row;
+            if (n_index < s.n) {
+                if (GROUPS == 1 && S > 1) {
+                    // this K slice's sums, unscaled: [slice][member][all segments' rows]; a second kernel adds the slices in order
+                    int seg_offset = 0;
+                    for (int i = 0; i < ur.seg; ++i) seg_offset += a.seg[i].n;
+                    float* part = a.partial + ((size_t)slice * a.members) * lay.total_n + seg_offset + n_index;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int m = 32 * half + i;
+                        if (m < a.members) part[(size_t)m * lay.total_n] = acc[0][i];
+                    }
+                } else {
+#pragma unroll
+                    for (int g = 0; g < GROUPS; ++g) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int m = 32 * half + i;
+                            if (m < a.members) {
+                                const size_t member = (size_t)(GROUPS * group_index(item) + g) * a.members + m;
+                                const float v = acc[g][i] * a.member_scale[member];
+                                float* y = s.y + member * s.n + n_index;
+                                if (a.epilogue == kResidual) *y += v; else *y = v;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kKqcMmaWarp) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_tc_cache(cudaStream_t stream, int type, const unsigned char* packed, long long rows, long long cols,
+                            unsigned char* cache_a, unsigned char* cache_meta) {
+    if ((type != kQ4_K && type != kQ6_K) || !packable(type, rows, cols)) return cudaErrorInvalidValue;
+    const int row_tiles = (int)((rows + kTileRows - 1) / kTileRows), k_tiles = (int)(cols / kTileCols);
+    const int units = (row_tiles + kRowTilesPerUnit - 1) / kRowTilesPerUnit;
+    tcq_cache_kernel<<<(unsigned)(units * k_tiles), kRowTilesPerUnit * 32, 0, stream>>>(type, packed, row_tiles, k_tiles, cache_a, cache_meta);
+    return cudaGetLastError();
+}
+
+namespace {
+
 // Adds the K slices of a split launch in slice order, applies the member scale and the epilogue.
 __global__ void tcq_reduce_kernel(const GemmArgs a, int slices, int total_n) {
     const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -1482,6 +1813,8 @@ cudaError_t device_setup(int& sm_count) {
         e = cudaFuncSetAttribute(gemm_tcq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBudget);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBudget);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcq2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBudget);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcqc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBudget);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcqc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBudget);
         if (e != cudaSuccess) return e;
         int count = 0;
         if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || count <= 0) count = 148;
@@ -1491,7 +1824,89 @@ cudaError_t device_setup(int& sm_count) {
     return cudaSuccess;
 }
 
+// The K-quant GEMM over cached operands: every segment carries op_a / op_meta.
+cudaError_t launch_gemm_tcqc(cudaStream_t stream, const GemmArgs& args, int units) {
+    KqcLayout lay{};
+    lay.members_padded = padded_members(args.members);
+    lay.cols = 2 * lay.members_padded;
+    lay.b_bytes = lay.cols * kChunkK * (int)sizeof(__half);
+    lay.b2_bytes = lay.cols * 16 * (int)sizeof(__half);
+    bool all_q4k = true;
+    for (int i = 0; i < args.n_segments; ++i) all_q4k = all_q4k && args.seg[i].type == kQ4_K;
+    // 32 KB of operand per stage: 128 inputs of the one Q4_K plane, or 64 inputs of two planes
+    lay.pieces = all_q4k ? 2 : 1;
+    lay.stage_bytes = 2 * kCachePieceBytes;
+    lay.total_n = 0;
+    for (int i = 0; i < args.n_segments; ++i) lay.total_n += args.seg[i].n;
+    lay.k_slices = 1;
+    lay.groups = std::max(1, args.groups);
+    lay.group_bytes = args.group_chunk_bytes;
+    int sm_count = 0;
+    {
+        cudaError_t e = device_setup(sm_count);
+        if (e != cudaSuccess) return e;
+    }
+    // whole groups of 64 in pairs: one pass over the unit's operand stages (through L2 and shared memory) per pair
+    const bool pairs = lay.groups >= 2 && args.members == kKqMaxMembers;
+    const int per_item = pairs ? 2 : 1;
+    lay.m_slots = 2;
+    const size_t fixed = (size_t)lay.m_slots * (kCacheMetaBytes + (size_t)per_item * lay.b2_bytes) + 16 + 512;
+    size_t per_stage = (size_t)lay.stage_bytes + (size_t)lay.pieces * per_item * lay.b_bytes;
+    if (lay.pieces == 2 && (kTcSmemBudget - fixed) / per_stage < 3) {   // too few of the wide stages: 64 inputs per stage
+        lay.pieces = 1;
+        lay.stage_bytes = kCachePieceBytes;
+        per_stage = (size_t)lay.stage_bytes + (size_t)per_item * lay.b_bytes;
+    }
+    lay.stages = (int)std::min<size_t>(16, (kTcSmemBudget - fixed) / per_stage);
+    if (lay.stages < 2) return cudaErrorInvalidValue;
+    const size_t smem = fixed + (size_t)lay.stages * per_stage;
+    if (pairs) {
+        KqcLayout two = lay;
+        two.groups = lay.groups & ~1;
+        gemm_tcqc_kernel<2><<<std::min(units * (two.groups / 2), sm_count), kKqcThreads, smem, stream>>>(args, two, units);
+        cudaError_t e2 = cudaGetLastError();
+        g_last_launches = 1;
+        if (e2 != cudaSuccess || two.groups == lay.groups) return e2;
+        // the odd group: its operand, scales and outputs follow the pairs'
+        GemmArgs rest = args;
+        rest.groups = 1;
+        rest.chunks = args.chunks + (size_t)two.groups * lay.group_bytes;
+        rest.member_scale = args.member_scale + (size_t)two.groups * args.members;
+        for (int i = 0; i < rest.n_segments; ++i) rest.seg[i].y = args.seg[i].y + (size_t)two.groups * args.members * args.seg[i].n;
+        rest.partial = nullptr;
+        cudaError_t e3 = launch_gemm_tcqc(stream, rest, units);
+        g_last_launches = 2;
+        return e3;
+    }
+    // Split K when whole units would leave SMs idle (every SM then streams its own part of the operands).
+    const int k_tiles = args.k / kTileCols;
+    if (args.partial != nullptr && lay.groups == 1) {
+        long long best = -1;
+        for (int slices = 1; slices <= std::min(8, k_tiles); ++slices) {
+            const int tps = (k_tiles + slices - 1) / slices;
+            if ((slices - 1) * tps >= k_tiles) continue;  // an empty slice
+            if ((size_t)slices * args.members * lay.total_n > args.partial_floats) break;
+            const long long waves = ((long long)units * slices + sm_count - 1) / sm_count;
+            const long long cost = waves * (tps + 1);
+            if (best < 0 || cost < best) { best = cost; lay.k_slices = slices; }
+        }
+    }
+    gemm_tcqc_kernel<1><<<std::min(units * lay.k_slices * lay.groups, sm_count), kKqcThreads, smem, stream>>>(args, lay, units);
+    cudaError_t e = cudaGetLastError();
+    g_last_launches = 1;
+    if (e != cudaSuccess || lay.k_slices == 1) return e;
+    g_last_launches = 2;
+    const long long outputs = (long long)args.members * lay.total_n;
+    tcq_reduce_kernel<<<(unsigned int)((outputs + 255) / 256), 256, 0, stream>>>(args, lay.k_slices, lay.total_n);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_gemm_tcq(cudaStream_t stream, const GemmArgs& args, int units, int tile) {
+    {
+        bool cached = true;
+        for (int i = 0; i < args.n_segments; ++i) cached = cached && args.seg[i].op_a != nullptr && args.seg[i].op_meta != nullptr;
+        if (cached) return launch_gemm_tcqc(stream, args, units);
+    }
     KqLayout lay{};
     lay.members_padded = padded_members(args.members);
     lay.cols = 2 * lay.members_padded;

@@ -95,6 +95,10 @@ struct GemvSegment {
     int n;          // valid output rows
     int row_tiles;
     float* y;       // [members][n] F32 output (the residual stream for kResidual)
+    // K-quant matrices only, optional: the matrix once more as tensor-core operands (launch_tc_cache); the
+    // tensor-memory GEMM then copies operand stages instead of converting packed tiles
+    const unsigned char* op_a = nullptr;
+    const unsigned char* op_meta = nullptr;
 };
 
 enum GemvEpilogue : int {
@@ -212,6 +216,14 @@ cudaError_t launch_to_tc_operand_groups(cudaStream_t stream, const float* x, con
 cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmArgs& args);
 // Parity aid: decodes a tile-major packed matrix back to F32 [rows][cols] with the weight decoder of the
 // decode-and-split tensor-memory kernel (the reference's arithmetic), reading the packed bytes only.
+// A Q4_K / Q6_K packed matrix as tensor-core operands: per 128-row unit and 256-input k tile the four 64-input
+// operand pieces (one binary16 plane of 16 KB for Q4_K, two for Q6_K) into `cache_a`, and the rows' scales with the
+// minima operand (5 KB) into `cache_meta`.  The bytes are the ones the converting kernels build in shared memory.
+size_t tc_cache_a_bytes(int type, long long rows, long long cols);
+size_t tc_cache_meta_bytes(long long rows, long long cols);
+cudaError_t launch_tc_cache(cudaStream_t stream, int type, const unsigned char* packed, long long rows, long long cols,
+                            unsigned char* cache_a, unsigned char* cache_meta);
+
 cudaError_t launch_unpack_packed(cudaStream_t stream, int type, const unsigned char* packed, long long rows, long long cols,
                                  float* out);
 // Kernels the calling thread's last launch_gemm_tc enqueued (2 when a split-K launch adds its ordered reduction).

@@ -258,12 +258,21 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
         int* d_err = s.alloc<int>(1);
         OP_PTR(op.dig); OP_PTR(op.sx); OP_PTR(op.sxs16); OP_PTR(d_err);
         OP_TRY(cudaMemsetAsync(d_err, 0, sizeof(int), s.stream));
-        if (variant == 3 || variant == 4) {
+        if (variant == 3 || variant == 4 || variant == 5) {
             // the tensor-memory kernels
             TcOperand top;
             const GemvSegment probe{d_w, type, (int)rows, (int)((rows + kTileRows - 1) / kTileRows), d_y};
-            // variant 3: K-quant form where it applies (at most 64 members per launch); variant 4: always the generic form
-            const bool kquant = variant == 3 && gemm_tc_kquant(&probe, 1, 1);
+            // variant 3: K-quant form where it applies (at most 64 members per launch); variant 4: always the generic form;
+            // variant 5: the K-quant form over operands converted once (Q4_K and Q6_K only)
+            const bool kquant = variant != 4 && gemm_tc_kquant(&probe, 1, 1);
+            unsigned char *op_a = nullptr, *op_meta = nullptr;
+            if (variant == 5) {
+                if (!kquant) return op_fail("gemv: the operand cache holds Q4_K and Q6_K matrices only", cudaSuccess);
+                op_a = s.alloc<unsigned char>(tc_cache_a_bytes(type, rows, cols));
+                op_meta = s.alloc<unsigned char>(tc_cache_meta_bytes(rows, cols));
+                OP_PTR(op_a); OP_PTR(op_meta);
+                OP_TRY(launch_tc_cache(s.stream, type, d_w, rows, cols, op_a, op_meta));
+            }
             const int per_launch = kquant ? 64 : kGemmTcMaxMembers;
             const int group = std::min(members, per_launch);
             top.chunks = (__half*)s.alloc<unsigned char>(tc_operand_bytes(group, (int)cols));
@@ -286,7 +295,7 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
                 OP_TRY(launch_to_tc_operand_groups(s.stream, d_x, nullptr, nullptr, whole * per_launch, per_launch, (int)cols, 0.0f, all));
                 GemmArgs a{};
                 a.n_segments = 1;
-                a.seg[0] = GemvSegment{d_w, type, (int)rows, (int)((rows + kTileRows - 1) / kTileRows), d_y};
+                a.seg[0] = GemvSegment{d_w, type, (int)rows, (int)((rows + kTileRows - 1) / kTileRows), d_y, op_a, op_meta};
                 a.k = (int)cols;
                 a.members = per_launch;
                 a.chunks = (const signed char*)all.chunks; a.member_scale = all.member_scale;
@@ -304,7 +313,7 @@ int ribn_b200_op_gemv(int32_t device, int32_t type, const void* weights, int64_t
                 GemmArgs a{};
                 a.n_segments = 1;
                 a.seg[0] = GemvSegment{d_w, type, (int)rows, (int)((rows + kTileRows - 1) / kTileRows),
-                                       d_y + (size_t)m0 * rows};
+                                       d_y + (size_t)m0 * rows, op_a, op_meta};
                 a.k = (int)cols;
                 a.members = m;
                 a.chunks = (const signed char*)top.chunks; a.member_scale = top.member_scale;

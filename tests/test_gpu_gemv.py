@@ -214,3 +214,29 @@ def test_tensor_memory_pair_kernel_against_oracle(ops, kind, rows, cols, members
         assert np.max(np.abs(got[m] - want)) / scale < 2e-5, m
     alone = ops.gemv(kind, enc, rows, cols, xs[[70, 130]], variant=3)   # the single-group kernel
     assert np.array_equal(alone.view(np.uint32), got[[70, 130]].view(np.uint32))
+
+
+@pytest.mark.parametrize("kind", [H.Q4_K, H.Q6_K])
+@pytest.mark.parametrize("rows,cols,members", [
+    (200, 256, 3), (1000, 512, 17), (4096, 4096, 64), (19200, 512, 256), (37888, 256, 197), (640, 2048, 130),
+], ids=["one-k-tile-ragged-unit", "ragged-rows", "k-slices", "two-pairs", "pair-odd-group-and-rest", "pair-and-rest-few-units"])
+def test_operand_cache_gemm_changes_no_bit(ops, kind, rows, cols, members):
+    """The K-quant GEMM over operands converted once (variant 5: stages are copied, not converted) gives the bits of
+    the converting kernels (variant 3) at every shape class: a unit with missing row tiles, one k tile, split K,
+    groups in pairs with an odd group and a partial last group.  One member also against the oracle."""
+    rng = np.random.default_rng(rows * 7 + members + kind)
+    enc = H.quantize(kind, rng.normal(0, 0.02, size=(rows, cols)).astype(np.float32))
+    xs = (rng.normal(0, 1, size=(members, cols)) * rng.uniform(0.01, 100, size=(members, 1))).astype(np.float32)
+    converting = ops.gemv(kind, enc, rows, cols, xs, variant=3)
+    cached = ops.gemv(kind, enc, rows, cols, xs, variant=5)
+    assert np.array_equal(cached.view(np.uint32), converting.view(np.uint32))
+    m = members - 1
+    want = orc.gemv(kind, enc, cols, rows, xs[m])
+    assert np.max(np.abs(cached[m] - want)) / (float(np.max(np.abs(want))) + 1e-6) < 2e-5
+
+
+def test_operand_cache_refuses_other_types(ops):
+    rng = np.random.default_rng(5)
+    enc = H.quantize(H.Q8_0, rng.normal(0, 0.02, size=(128, 256)).astype(np.float32))
+    with pytest.raises(RuntimeError):
+        ops.gemv(H.Q8_0, enc, 128, 256, np.ones((4, 256), np.float32), variant=5)

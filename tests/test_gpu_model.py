@@ -342,6 +342,38 @@ def test_prefill_chunk_of_several_row_groups_matches_oracle(model):
     seq.close(); ex.close()
 
 
+def test_operand_cache_changes_no_logit_bit(model):
+    """RIBN_B200_FLAG_OPERAND_CACHE keeps the K-quant matrices as tensor-core operands: a 150-token prefill chunk
+    (a pair of row groups and a partial one) and a ragged decode batch of five rows give the same logits bit for bit
+    and the same tokens as the executor that converts packed tiles on every use."""
+    import ribn_b200
+    from ribn_b200 import BatchItem, StepKind
+    tensors, _ = model
+    rng = np.random.default_rng(9)
+    prompts = [rng.integers(0, MID["vocab"], size=n).tolist() for n in (150, 9, 33, 70, 5)]
+    results = []
+    for flags in (0, ribn_b200.FLAG_OPERAND_CACHE):
+        ex = build(MID, tensors, flags=flags, context_tokens=256, max_sequences=5, max_batch_tokens=192)
+        logits, tokens = [], []
+        for i, prompt in enumerate(prompts):
+            assert ex.admit(i + 1, i + 1, prompt, 8).ready
+            item = BatchItem(i + 1, StepKind.PREFILL, 0, len(prompt), 1)
+            ex.prepare([item])
+            tokens.append(ex.wait(ex.submit([item]))[0].tokens[0])
+            logits.append(ex.copy_logits(0).copy())
+        for step in range(3):
+            items = [BatchItem(i + 1, StepKind.DECODE, len(p) + step, 1, 1) for i, p in enumerate(prompts)]
+            ex.prepare(items)
+            done = ex.wait(ex.submit(items))
+            tokens.extend(d.tokens[0] for d in done)
+            logits.extend(ex.copy_logits(r).copy() for r in range(len(prompts)))
+        results.append((tokens, logits))
+        ex.close()
+    assert results[0][0] == results[1][0]
+    for a, b in zip(results[0][1], results[1][1]):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
 def test_batched_decode_graph_replay_changes_no_bit(model):
     """Batched decode steps of a recurring shape replay a captured graph from their third occurrence on; the
     logits must equal those of an executor that never captures (RIBN_B200_FLAG_NO_GRAPH), bit for bit."""
