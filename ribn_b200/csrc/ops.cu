@@ -3,6 +3,8 @@
 // one-warp-per-row GEMV and attention kernels used as on-device references,
 // SwiGLU gating, residual add, greedy selection, and the seeded synthetic
 // checkpoint generator.
+#include <cooperative_groups.h>
+
 #include "blocks.cuh"
 #include "kernels.cuh"
 
@@ -225,10 +227,18 @@ __device__ __forceinline__ unsigned int logit_key(float v) {
     return (bits >> 31) ? ~bits : (bits ^ 0x80000000u);
 }
 
-__global__ void argmax_kernel(const float* logits, long long length, uint32_t* out, const int32_t* slot,
-                              uint32_t* next_token) {
+// One cluster of kArgmaxParts CTAs per row: a vocabulary-sized row is a latency problem for one CTA (ten trips of
+// loads), so every CTA scans an eighth of it and leaves its best in the first CTA's shared memory.
+constexpr int kArgmaxParts = 8;
+
+__global__ void __cluster_dims__(kArgmaxParts, 1, 1) argmax_kernel(const float* logits, long long length, uint32_t* out,
+                                                                   const int32_t* slot, uint32_t* next_token) {
     __shared__ unsigned long long best[32];
-    const float* row = logits + (long long)blockIdx.x * length;
+    __shared__ unsigned long long part_best[kArgmaxParts];
+    cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
+    const int part = (int)cluster.block_rank();
+    const long long r = blockIdx.x / kArgmaxParts;
+    const float* row = logits + r * length;
     // Packed (key << 32) | ~index: the maximum picks the largest key and, among
     // equal keys, the smallest index.
     unsigned long long mine = 0ull;
@@ -240,18 +250,17 @@ __global__ void argmax_kernel(const float* logits, long long length, uint32_t* o
             if (cand > mine) mine = cand;
         }
     };
-    long long done = 0;
     if ((reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
-        // Four independent 128-bit loads per thread and trip keep enough reads in flight for one
-        // block to stream a vocabulary-sized row; the maximum does not depend on the visiting order.
+        // Four independent 128-bit loads per thread and trip; the maximum does not depend on the visiting order.
         const float4* row4 = reinterpret_cast<const float4*>(row);
-        const long long quads = length / 4, stride = (long long)blockDim.x * 4;
-        for (long long q0 = 0; q0 < quads; q0 += stride) {
+        const long long quads = length / 4, q_begin = quads * part / kArgmaxParts, q_end = quads * (part + 1) / kArgmaxParts;
+        const long long stride = (long long)blockDim.x * 4;
+        for (long long q0 = q_begin; q0 < q_end; q0 += stride) {
             float4 v[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const long long q = q0 + (long long)u * blockDim.x + threadIdx.x;
-                v[u] = q < quads ? row4[q] : make_float4(NAN, NAN, NAN, NAN);
+                v[u] = q < q_end ? row4[q] : make_float4(NAN, NAN, NAN, NAN);
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
@@ -259,9 +268,14 @@ __global__ void argmax_kernel(const float* logits, long long length, uint32_t* o
                 consider(v[u].x, i); consider(v[u].y, i + 1); consider(v[u].z, i + 2); consider(v[u].w, i + 3);
             }
         }
-        done = quads * 4;
+        // the last part also takes what is left behind the last whole quad
+        if (part == kArgmaxParts - 1) {
+            for (long long i = quads * 4 + threadIdx.x; i < length; i += blockDim.x) consider(row[i], i);
+        }
+    } else {
+        const long long begin = length * part / kArgmaxParts, end = length * (part + 1) / kArgmaxParts;
+        for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) consider(row[i], i);
     }
-    for (long long i = done + threadIdx.x; i < length; i += blockDim.x) consider(row[i], i);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const unsigned long long other = __shfl_xor_sync(0xffffffffu, mine, o);
@@ -273,9 +287,15 @@ __global__ void argmax_kernel(const float* logits, long long length, uint32_t* o
     if (threadIdx.x == 0) {
         unsigned long long top = 0ull;
         for (int w = 0; w < (int)((blockDim.x + 31) >> 5); ++w) top = best[w] > top ? best[w] : top;
+        cluster.map_shared_rank(part_best, 0)[part] = top;
+    }
+    cluster.sync();   // every part's best is in the first CTA's shared memory
+    if (part == 0 && threadIdx.x == 0) {
+        unsigned long long top = 0ull;
+        for (int q = 0; q < kArgmaxParts; ++q) top = part_best[q] > top ? part_best[q] : top;
         const uint32_t pick = top == 0ull ? 0u : 0xffffffffu - (uint32_t)(top & 0xffffffffull);
-        out[blockIdx.x] = pick;
-        if (slot != nullptr) next_token[slot[blockIdx.x]] = pick;
+        out[r] = pick;
+        if (slot != nullptr) next_token[slot[r]] = pick;
     }
 }
 
@@ -602,7 +622,7 @@ cudaError_t launch_residual_add(cudaStream_t stream, float* acc, const float* in
 cudaError_t launch_argmax(cudaStream_t stream, const float* logits, int members, long long length,
                           uint32_t* out, const int32_t* slot, uint32_t* next_token) {
     if (members <= 0) return cudaSuccess;
-    argmax_kernel<<<members, 1024, 0, stream>>>(logits, length, out, slot, next_token);
+    argmax_kernel<<<members * kArgmaxParts, 1024, 0, stream>>>(logits, length, out, slot, next_token);
     return cudaGetLastError();
 }
 
