@@ -26,6 +26,20 @@ def test_library_exports_every_declared_symbol(built_library):
     assert b"sm_100a" in handle.ribn_b200_build_info()
 
 
+def test_python_flag_constants_mirror_the_header():
+    """The ctypes mirror's RIBN_B200_FLAG_* values are the header's (a drifted constant would silently set another
+    option on the executor)."""
+    from ribn_b200 import _lib
+    header = open(os.path.join(ROOT, "include", "ribn_b200.h")).read()
+    flags = dict(re.findall(r"RIBN_B200_(FLAG_[A-Z0-9_]+)\s*=\s*(\d+)", header))
+    assert {"FLAG_KEEP_LOGITS", "FLAG_NO_GRAPH", "FLAG_KV_ON_DEMAND", "FLAG_OPERAND_CACHE"} <= set(flags)
+    for name, value in flags.items():
+        assert getattr(_lib, name) == int(value), name
+    assert len(set(flags.values())) == len(flags)
+    for value in flags.values():
+        assert int(value) & (int(value) - 1) == 0, "flags are single bits"
+
+
 def test_product_package_never_imports_the_oracle():
     pkg = os.path.join(ROOT, "ribn_b200")
     for dirpath, _dirs, files in os.walk(pkg):
