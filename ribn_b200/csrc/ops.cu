@@ -227,12 +227,13 @@ __device__ __forceinline__ unsigned int logit_key(float v) {
     return (bits >> 31) ? ~bits : (bits ^ 0x80000000u);
 }
 
-// One cluster of kArgmaxParts CTAs per row: a vocabulary-sized row is a latency problem for one CTA (ten trips of
-// loads), so every CTA scans an eighth of it and leaves its best in the first CTA's shared memory.
-constexpr int kArgmaxParts = 8;
-
-__global__ void __cluster_dims__(kArgmaxParts, 1, 1) argmax_kernel(const float* logits, long long length, uint32_t* out,
-                                                                   const int32_t* slot, uint32_t* next_token) {
+// One cluster of PARTS CTAs per row: a vocabulary-sized row is a latency problem for one CTA (ten trips of loads),
+// so every CTA scans its share of the row and leaves its best in the first CTA's shared memory.  Eight parts for
+// the few rows of a decode step, fewer when the rows alone fill the GPU.
+template <int PARTS>
+__global__ void __cluster_dims__(PARTS, 1, 1) argmax_kernel(const float* logits, long long length, uint32_t* out,
+                                                            const int32_t* slot, uint32_t* next_token) {
+    constexpr int kArgmaxParts = PARTS;
     __shared__ unsigned long long best[32];
     __shared__ unsigned long long part_best[kArgmaxParts];
     cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
@@ -622,7 +623,9 @@ cudaError_t launch_residual_add(cudaStream_t stream, float* acc, const float* in
 cudaError_t launch_argmax(cudaStream_t stream, const float* logits, int members, long long length,
                           uint32_t* out, const int32_t* slot, uint32_t* next_token) {
     if (members <= 0) return cudaSuccess;
-    argmax_kernel<<<members * kArgmaxParts, 1024, 0, stream>>>(logits, length, out, slot, next_token);
+    if (members <= 32) argmax_kernel<8><<<members * 8, 1024, 0, stream>>>(logits, length, out, slot, next_token);
+    else if (members <= 128) argmax_kernel<2><<<members * 2, 1024, 0, stream>>>(logits, length, out, slot, next_token);
+    else argmax_kernel<1><<<members, 1024, 0, stream>>>(logits, length, out, slot, next_token);
     return cudaGetLastError();
 }
 
