@@ -17,6 +17,7 @@ from .executor import (  # noqa: F401
     StepCompletion, StepKind, nccl_library_path, tp_shard, tp_unique_id,
 )
 from .engine import Engine, EngineConfig, SchedulePolicy, TokenRequest  # noqa: F401
+from .native_engine import NativeEngine  # noqa: F401
 from . import gemma  # noqa: F401
 from . import gguf  # noqa: F401
 from .gemma import GemmaB200, GemmaExecutor, GemmaSequence  # noqa: F401

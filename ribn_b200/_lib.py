@@ -158,6 +158,59 @@ SIGNATURES.update({
     "ribn_b200_gemma_last_step_stats": (C.c_int, [_P, C.POINTER(C.c_float), _U32P]),
 })
 
+# ---- include/ribn_b200_engine.h ---------------------------------------------------------------------------
+_INFO_FN = C.CFUNCTYPE(C.c_int, _P, C.POINTER(Limits))
+_ADMIT_FN = C.CFUNCTYPE(C.c_int, _P, C.c_uint64, C.c_uint64, _U32P, C.c_uint32, C.c_uint32, C.POINTER(SamplingC), _U32P, C.c_uint32)
+_PREPARE_FN = C.CFUNCTYPE(C.c_int, _P, C.POINTER(BatchItemC), C.c_uint32, C.POINTER(PreparedRowC))
+_ABANDON_FN = C.CFUNCTYPE(C.c_int, _P)
+_SUBMIT_FN = C.CFUNCTYPE(C.c_int, _P, C.POINTER(BatchItemC), C.c_uint32, _U64P)
+_POLL_FN = C.CFUNCTYPE(C.c_int, _P, C.c_uint64, C.POINTER(CompletionC), C.c_uint32, _U32P)
+_RELEASE_FN = C.CFUNCTYPE(C.c_int, _P, C.c_uint64)
+_LAST_ERROR_FN = C.CFUNCTYPE(C.c_size_t, _P, C.POINTER(C.c_char), C.c_size_t)
+
+
+class ExecutorTable(C.Structure):
+    _fields_ = [("self", _P), ("info", _INFO_FN), ("admit", _ADMIT_FN), ("prepare_rows", _PREPARE_FN),
+                ("abandon_preparation", _ABANDON_FN), ("submit", _SUBMIT_FN), ("poll", _POLL_FN),
+                ("release", _RELEASE_FN), ("last_error", _LAST_ERROR_FN)]
+
+
+class EngineConfigC(C.Structure):
+    _fields_ = [("max_active_requests", C.c_uint32), ("max_queued_requests", C.c_uint32)]
+
+
+class SchedulePolicyC(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("max_batch_tokens", "prefill_chunk_tokens", "decode_tokens", "max_decode_only_steps")]
+
+
+class RequestStatusC(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("state", "finish", "prompt_tokens", "prefix", "generated", "output_tokens")] + \
+        [(n, C.c_uint64) for n in ("enqueue_ns", "first_token_ns", "last_token_ns")]
+
+
+class EngineCountersC(C.Structure):
+    _fields_ = [("steps", C.c_uint64), ("decode_only_steps", C.c_uint32), ("waiting", C.c_uint32), ("prefill", C.c_uint32),
+                ("decode", C.c_uint32), ("parked", C.c_uint32), ("in_flight_rows", C.c_uint32), ("resource_epoch", C.c_uint64),
+                ("faulted", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+# one entry per declaration in include/ribn_b200_engine.h
+SIGNATURES.update({
+    "ribn_b200_engine_create": (C.c_int, [C.POINTER(ExecutorTable), C.POINTER(EngineConfigC), C.POINTER(SchedulePolicyC),
+                                          C.POINTER(_P), C.c_char_p, C.c_size_t]),
+    "ribn_b200_engine_create_for": (C.c_int, [_P, C.POINTER(EngineConfigC), C.POINTER(SchedulePolicyC), C.POINTER(_P),
+                                              C.c_char_p, C.c_size_t]),
+    "ribn_b200_engine_destroy": (C.c_int, [_P]),
+    "ribn_b200_engine_enqueue": (C.c_int, [_P, _P, C.c_uint32, C.c_uint32, _P, C.c_uint32, C.c_float, _U64P]),
+    "ribn_b200_engine_step": (C.c_int, [_P, C.POINTER(C.c_int32)]),
+    "ribn_b200_engine_idle": (C.c_int, [_P]),
+    "ribn_b200_engine_status": (C.c_int, [_P, C.c_uint64, C.POINTER(RequestStatusC)]),
+    "ribn_b200_engine_output": (C.c_int, [_P, C.c_uint64, _P, C.c_uint32, _U32P]),
+    "ribn_b200_engine_finish_reason": (C.c_size_t, [_P, C.c_uint64, C.c_char_p, C.c_size_t]),
+    "ribn_b200_engine_counters": (C.c_int, [_P, C.POINTER(EngineCountersC)]),
+    "ribn_b200_engine_last_error": (C.c_size_t, [_P, C.c_char_p, C.c_size_t]),
+})
+
 _LIB = None
 
 

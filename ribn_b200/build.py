@@ -27,7 +27,8 @@ def is_stale() -> bool:
         return True
     built = os.path.getmtime(LIB)
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [
-        os.path.join(HERE, "..", "include", "ribn_b200.h"), os.path.join(HERE, "..", "include", "ribn_b200_gemma.h")]
+        os.path.join(HERE, "..", "include", "ribn_b200.h"), os.path.join(HERE, "..", "include", "ribn_b200_gemma.h"),
+        os.path.join(HERE, "..", "include", "ribn_b200_engine.h")]
     return any(os.path.getmtime(d) > built for d in deps)
 
 

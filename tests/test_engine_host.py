@@ -6,7 +6,7 @@ from dataclasses import dataclass, field
 
 import pytest
 
-from ribn_b200.engine import Engine, EngineConfig, SchedulePolicy, TokenRequest
+from ribn_b200.engine import Engine as PyEngine, EngineConfig, SchedulePolicy, TokenRequest
 from ribn_b200.executor import (Admission, BatchItem, ExecutionError, ExecutorInfo, GenerationLimits, PreparedRow,
                                 StepCompletion, StepKind)
 
@@ -77,6 +77,142 @@ class Fake:
         self.c.released.append(sequence)
 
 
+class TableAdapter:
+    """A Python executor double behind the C table of include/ribn_b200_engine.h: every callback forwards to the
+    double's method and turns its answer (or its ExecutionError) into the ABI's return codes."""
+
+    def __init__(self, fake):
+        import ctypes as C
+        from ribn_b200 import _lib
+        self.fake, self.error = fake, b""
+        L = _lib
+
+        def guard(fn):
+            def wrapped(*args):
+                try:
+                    return fn(*args)
+                except ExecutionError as exc:
+                    self.error = str(exc).encode()
+                    return L.ERROR
+            return wrapped
+
+        def info(_self, out):
+            lim = fake.info().limits
+            out[0].context_tokens, out[0].max_sequences = lim.context_tokens, lim.max_sequences
+            out[0].max_batch_tokens, out[0].max_decode_tokens = lim.max_batch_tokens, lim.max_decode_tokens
+            return L.OK
+
+        def admit(_self, request_id, sequence, tokens, n, max_out, sampling, stops, n_stops):
+            adm = fake.admit(request_id, sequence, [tokens[i] for i in range(n)], max_out, sampling[0].temperature,
+                             [stops[i] for i in range(n_stops)])
+            self.error = (adm.reason or "").encode()
+            return {Admission.READY: L.OK, Admission.REJECTED: L.REJECTED, Admission.DEFERRED: L.DEFERRED}[adm.state]
+
+        def items_of(items, n):
+            return [BatchItem(items[i].sequence, StepKind(items[i].kind), items[i].prefix, items[i].token_budget,
+                              items[i].output_budget) for i in range(n)]
+
+        def prepare_rows(_self, items, n, rows):
+            batch = items_of(items, n)
+            negotiate = getattr(fake, "prepare_rows", None)
+            got = negotiate(batch) if negotiate else fake.prepare(batch)
+            if got == "ready":
+                return L.OK
+            for i, row in enumerate(got):
+                rows[i].state = {"ready": 0, "deferred": 1, "rejected": 2}[row.state]
+                if row.state == "ready":
+                    rows[i].token_budget, rows[i].output_budget = row.item.token_budget, row.item.output_budget
+            return L.SELECTED
+
+        def abandon(_self):
+            fake.abandon_preparation()
+            return L.OK
+
+        def submit(_self, items, n, sid):
+            sid[0] = fake.submit(items_of(items, n))
+            return L.OK
+
+        def poll(_self, sid, rows, capacity, count):
+            done = fake.poll(sid)
+            if done is None:
+                return L.PENDING
+            count[0] = len(done)
+            for i, row in enumerate(done[:capacity]):
+                rows[i].sequence, rows[i].prefix, rows[i].n_tokens = row.sequence, row.prefix, len(row.tokens)
+                rows[i].token = row.tokens[0] if row.tokens else 0
+            return L.OK
+
+        def release(_self, sequence):
+            fake.release(sequence)
+            return L.OK
+
+        def last_error(_self, buf, capacity):
+            text = self.error[:max(capacity - 1, 0)]
+            C.memmove(buf, text + b"\0", len(text) + 1)
+            return len(text)
+
+        self.table = L.ExecutorTable(None, L._INFO_FN(guard(info)), L._ADMIT_FN(guard(admit)), L._PREPARE_FN(guard(prepare_rows)),
+                                     L._ABANDON_FN(guard(abandon)), L._SUBMIT_FN(guard(submit)), L._POLL_FN(guard(poll)),
+                                     L._RELEASE_FN(guard(release)), L._LAST_ERROR_FN(last_error))
+
+
+class NativeFacade:
+    """The native engine behind the attribute names the tests below use on the Python engine."""
+
+    def __init__(self, fake, config, policy):
+        from ribn_b200.native_engine import NativeEngine
+        self.adapter = TableAdapter(fake)
+        self.engine = NativeEngine(config=config, policy=policy, table=self.adapter.table)
+        self.requests = []
+
+    def enqueue(self, req):
+        rid = self.engine.enqueue(req)
+        self.requests.append(rid)
+        return rid
+
+    def step(self):
+        return self.engine.step()
+
+    def idle(self):
+        return self.engine.idle()
+
+    @property
+    def faulted(self):
+        return self.engine.faulted
+
+    def _by_state(self, states):
+        out = {}
+        for rid in self.requests:
+            st = self.engine.status(rid)
+            if st.state in states:
+                out[rid] = st
+        return out
+
+    @property
+    def finished(self):
+        return self._by_state((2,))
+
+    @property
+    def slots(self):
+        return self._by_state((0, 1))
+
+    @property
+    def waiting(self):
+        return list(self._by_state((0,)))
+
+    @property
+    def parked(self):
+        return [None] * self.engine.counters().parked
+
+
+@pytest.fixture(params=["python", "native"])
+def Engine(request, built_library):
+    """The Python engine and the native one (include/ribn_b200_engine.h) under the same cases."""
+    if request.param == "python":
+        return PyEngine
+    return NativeFacade
+
+
 def run(engine, limit=10000):
     for _ in range(limit):
         if engine.idle():
@@ -85,7 +221,7 @@ def run(engine, limit=10000):
     raise AssertionError("engine did not drain")
 
 
-def test_prefill_is_chunked_then_decode_runs_one_token_steps():
+def test_prefill_is_chunked_then_decode_runs_one_token_steps(Engine):
     c = Control()
     e = Engine(Fake(c), EngineConfig(max_active_requests=4), SchedulePolicy(64, 16, 1, 8))
     rid = e.enqueue(TokenRequest(list(range(40)), 3))
@@ -97,7 +233,7 @@ def test_prefill_is_chunked_then_decode_runs_one_token_steps():
     assert done.finish == "length" and done.output == [132, 140, 141] and c.released == [rid]
 
 
-def test_decode_rows_come_first_and_share_the_token_budget():
+def test_decode_rows_come_first_and_share_the_token_budget(Engine):
     c = Control()
     e = Engine(Fake(c, max_batch_tokens=20), EngineConfig(max_active_requests=4), SchedulePolicy(20, 16, 1, 8))
     a = e.enqueue(TokenRequest(list(range(4)), 50))
@@ -110,7 +246,7 @@ def test_decode_rows_come_first_and_share_the_token_budget():
     assert a != b
 
 
-def test_forced_prefill_after_decode_only_steps():
+def test_forced_prefill_after_decode_only_steps(Engine):
     c = Control()
     # budget 1: a decode row always exhausts it, so prefill starves until forced
     e = Engine(Fake(c), EngineConfig(max_active_requests=4), SchedulePolicy(1, 1, 1, 3))
@@ -126,7 +262,7 @@ def test_forced_prefill_after_decode_only_steps():
     assert first <= 4  # at most max_decode_only_steps (+1 in flight) decode-only steps before the forced prefill
 
 
-def test_pending_poll_makes_no_progress_and_keeps_one_batch_in_flight():
+def test_pending_poll_makes_no_progress_and_keeps_one_batch_in_flight(Engine):
     c = Control(delay=2)
     e = Engine(Fake(c), EngineConfig(max_active_requests=2), SchedulePolicy(64, 64, 1, 8))
     e.enqueue(TokenRequest([1, 2, 3], 1))
@@ -137,7 +273,7 @@ def test_pending_poll_makes_no_progress_and_keeps_one_batch_in_flight():
     assert len(c.batches) == 1 and len(e.finished) == 1
 
 
-def test_malformed_completion_faults_before_any_commit():
+def test_malformed_completion_faults_before_any_commit(Engine):
     c = Control(malformed=True)
     e = Engine(Fake(c), EngineConfig(max_active_requests=2), SchedulePolicy(64, 64, 1, 8))
     rid = e.enqueue(TokenRequest([1, 2, 3], 4))
@@ -150,7 +286,7 @@ def test_malformed_completion_faults_before_any_commit():
 
 
 @pytest.mark.parametrize("switch", ["fail_submit", "fail_poll"])
-def test_executor_errors_fault_the_engine(switch):
+def test_executor_errors_fault_the_engine(Engine, switch):
     c = Control()
     e = Engine(Fake(c), EngineConfig(max_active_requests=2), SchedulePolicy(64, 64, 1, 8))
     e.enqueue(TokenRequest([1, 2, 3], 4))
@@ -162,7 +298,7 @@ def test_executor_errors_fault_the_engine(switch):
     assert e.faulted
 
 
-def test_rejected_and_deferred_admission():
+def test_rejected_and_deferred_admission(Engine):
     c = Control(reject_admission=True)
     e = Engine(Fake(c), EngineConfig(max_active_requests=2), SchedulePolicy(64, 64, 1, 8))
     rid = e.enqueue(TokenRequest([1], 1))
@@ -177,7 +313,7 @@ def test_rejected_and_deferred_admission():
     assert e.finished[rid2].finish == "length"
 
 
-def test_policy_must_fit_executor_limits():
+def test_policy_must_fit_executor_limits(Engine):
     with pytest.raises(ValueError):
         Engine(Fake(Control(), max_batch_tokens=32), EngineConfig(2), SchedulePolicy(64, 16, 1, 8))
     with pytest.raises(ValueError):
@@ -225,7 +361,7 @@ class PagedFake(Fake):
         self.free += self.held.pop(sequence)
 
 
-def test_deferred_rows_are_parked_and_offered_again_after_a_release():
+def test_deferred_rows_are_parked_and_offered_again_after_a_release(Engine):
     c = Control()
     fake = PagedFake(c, pages=3)
     e = Engine(fake, EngineConfig(max_active_requests=4), SchedulePolicy(64, 32, 1, 8))
@@ -241,7 +377,7 @@ def test_deferred_rows_are_parked_and_offered_again_after_a_release():
     assert fake.free == 3 and not e.parked
 
 
-def test_a_pool_that_can_never_serve_every_sequence_fails_the_newest_one():
+def test_a_pool_that_can_never_serve_every_sequence_fails_the_newest_one(Engine):
     c = Control()
     fake = PagedFake(c, pages=2)
     e = Engine(fake, EngineConfig(max_active_requests=4), SchedulePolicy(64, 16, 1, 8))

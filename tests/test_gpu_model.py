@@ -499,6 +499,49 @@ def test_engine_runs_more_requests_than_the_arena_holds_at_once(model):
     assert outputs[0] == outputs[1]
 
 
+def test_native_engine_drives_the_executor_like_the_python_engine(model):
+    """The native host engine (include/ribn_b200_engine.h) over the CUDA executor, with no Python between them:
+    same requests, same policy, pages on demand through a pool too small for all envelopes: every request ends by
+    length with the tokens the Python engine produced, a stop token ends its request early, and the pool is whole
+    again afterwards."""
+    import ribn_b200
+    from ribn_b200.native_engine import NativeEngine
+    tensors, _ = model
+    rng = np.random.default_rng(8)
+    prompts = [rng.integers(0, MID["vocab"], size=n).tolist() for n in (20, 33, 9, 40)]
+    budgets = (4, 30, 10, 20)
+    config = ribn_b200.EngineConfig(max_active_requests=4)
+    policy = ribn_b200.SchedulePolicy(max_batch_tokens=64, prefill_chunk_tokens=32, decode_tokens=1, max_decode_only_steps=4)
+    results = {}
+    for kind in ("python", "native"):
+        ex = build(MID, tensors, flags=ribn_b200.FLAG_KV_ON_DEMAND, context_tokens=96, max_sequences=4, max_batch_tokens=64,
+                   kv_pages=10)
+        if kind == "python":
+            engine = ribn_b200.Engine(ex, config, policy)
+            ids = [engine.enqueue(ribn_b200.TokenRequest(p, n)) for p, n in zip(prompts, budgets)]
+            engine.run_until_idle()
+            results[kind] = [(engine.finished[i].finish, engine.finished[i].output) for i in ids]
+        else:
+            engine = NativeEngine(ex, config, policy)
+            ids = [engine.enqueue(ribn_b200.TokenRequest(p, n)) for p, n in zip(prompts, budgets)]
+            engine.run_until_idle()
+            results[kind] = [(engine.status(i).finish, engine.status(i).output) for i in ids]
+            assert engine.steps > 0 and not engine.faulted
+            # a stop token: the second request again, stopping at its third token
+            stop = results[kind][1][1][2]
+            again = engine.enqueue(ribn_b200.TokenRequest(prompts[1], 30, stop_tokens=[stop]))
+            engine.run_until_idle()
+            st = engine.status(again)
+            assert st.finish == "stop" and st.output == results[kind][1][1][:results[kind][1][1].index(stop)]
+            assert st.enqueue_ns > 0 and (not st.output or st.first_token_ns >= st.enqueue_ns)
+            engine.close()
+        total, free = ex.kv_pages()
+        assert total == free
+        ex.close()
+    assert [r[0] for r in results["native"]] == ["length"] * 4
+    assert results["native"] == results["python"]
+
+
 def test_bounded_wait_expiry_is_reported_and_leaves_the_context_usable(model):
     """A kernel whose wait nothing ends gives up after its poll limit and leaves an error word; the next
     poll reports it and faults the executor; a fresh executor in the same process then runs normally."""

@@ -16,7 +16,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def test_library_exports_every_declared_symbol(built_library):
     import ribn_b200
     from ribn_b200 import _lib
-    header = "".join(open(os.path.join(ROOT, "include", name)).read() for name in ("ribn_b200.h", "ribn_b200_gemma.h"))
+    header = "".join(open(os.path.join(ROOT, "include", name)).read() for name in ("ribn_b200.h", "ribn_b200_gemma.h", "ribn_b200_engine.h"))
     declared = set(re.findall(r"\b(ribn_b200_[a-z0-9_]+)\s*\(", header))
     assert declared, "header declares nothing?"
     assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
