@@ -534,6 +534,9 @@ def serving_job(args, rank, world, local, dist, n, rate, workload):
                             max_batch_tokens=chunk + active, kv_pages=pages, device=local, flags=EXTRA_FLAGS)
     ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q8_0 if SCHEME == "q8_0" else ribn_b200.SCHEME_Q4_K_M)
     ex.finalize()
+    native = getattr(args, "engine", "python") == "native"
+    if native:
+        from ribn_b200.native_engine import NativeEngine as Engine   # the C++ engine of include/ribn_b200_engine.h
     engine = Engine(ex, EngineConfig(max_active_requests=active, max_queued_requests=n),
                     SchedulePolicy(max_batch_tokens=chunk + active, prefill_chunk_tokens=chunk, decode_tokens=1,
                                    max_decode_only_steps=8))
@@ -553,12 +556,16 @@ def serving_job(args, rank, world, local, dist, n, rate, workload):
         makespan = time.perf_counter() - t0
     barrier(dist, local)
     ttft, itl, generated = [], [], 0
-    for rid, slot in engine.finished.items():
+    if native:
+        finished = {rid: list(engine.token_times(rid)) for rid in ids}
+    else:
+        finished = {rid: slot.token_times for rid, slot in engine.finished.items()}
+    for rid, token_times in finished.items():
         i = ids[rid]
-        generated += len(slot.output)
-        if slot.token_times:
-            ttft.append(slot.token_times[0] - t0 - arrivals[i])
-            itl.extend(np.diff(slot.token_times).tolist())
+        generated += len(token_times)
+        if token_times:
+            ttft.append(token_times[0] - t0 - arrivals[i])
+            itl.extend(np.diff(token_times).tolist())
     makespan = all_max(dist, makespan, local)
     out = {
         "metric": f"{args.model} {args.scheme.upper()} continuous-batching generated tok/s (per GPU x replicas)",
@@ -569,7 +576,8 @@ def serving_job(args, rank, world, local, dist, n, rate, workload):
         "data": "synthetic",
         "config": {"workload": f"{args.model} {args.scheme.upper()}-style {workload}: {n} requests per GPU, {described}, {active} active, "
                                f"{chunk}-token prefill chunks, 16-token KV pages",
-                   "parallelism": f"replicas x{world}", "operand_cache": bool(EXTRA_FLAGS)},
+                   "parallelism": f"replicas x{world}", "operand_cache": bool(EXTRA_FLAGS),
+                   "engine": "native" if native else "python"},
         "ttft_ms": {"p50": float(np.percentile(ttft, 50) * 1e3), "p95": float(np.percentile(ttft, 95) * 1e3),
                     "definition": "planned arrival -> first token", "arrival_rate_per_s": rate if workload != "mixed" else None,
                     "requests": n},
@@ -852,6 +860,8 @@ def main():
     ap.add_argument("--gemma-new-tokens", type=int, default=32, help="gemma: greedy tokens per prompt")
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel group size (= ranks); runs the tensor-parallel decode workload")
     ap.add_argument("--context-max", type=int, default=8192, help="tp: contexts are uniform in [512, this]")
+    ap.add_argument("--engine", default="python", choices=["python", "native"],
+                    help="serving / mixed: the host engine that drives the executor (ribn_b200/engine.py or the C++ one)")
     ap.add_argument("--no-cache-leg", action="store_true", help="decode: skip the extra batch leg with the operand cache on")
     ap.add_argument("--operand-cache", default="off", choices=["on", "off"],
                     help="keep the K-quant matrices also as tensor-core operands in HBM (RIBN_B200_FLAG_OPERAND_CACHE)")

@@ -111,6 +111,10 @@ RIBN_B200_API int ribn_b200_engine_status(ribn_b200_engine* engine, uint64_t req
 /* The request's output tokens so far: copies at most `capacity`, reports how many there are. */
 RIBN_B200_API int ribn_b200_engine_output(ribn_b200_engine* engine, uint64_t request, uint32_t* tokens,
                                           uint32_t capacity, uint32_t* count);
+/* When each output token was committed (steady clock, nanoseconds; the clock of enqueue_ns): copies at most
+ * `capacity` stamps, reports how many there are. */
+RIBN_B200_API int ribn_b200_engine_token_times(ribn_b200_engine* engine, uint64_t request, uint64_t* stamps,
+                                               uint32_t capacity, uint32_t* count);
 /* Why the request ended, as text ("length", "stop", "rejected: ...", "failed: ..."); returns the length. */
 RIBN_B200_API size_t ribn_b200_engine_finish_reason(ribn_b200_engine* engine, uint64_t request, char* buffer,
                                                     size_t capacity);

@@ -206,6 +206,7 @@ SIGNATURES.update({
     "ribn_b200_engine_idle": (C.c_int, [_P]),
     "ribn_b200_engine_status": (C.c_int, [_P, C.c_uint64, C.POINTER(RequestStatusC)]),
     "ribn_b200_engine_output": (C.c_int, [_P, C.c_uint64, _P, C.c_uint32, _U32P]),
+    "ribn_b200_engine_token_times": (C.c_int, [_P, C.c_uint64, _P, C.c_uint32, _U32P]),
     "ribn_b200_engine_finish_reason": (C.c_size_t, [_P, C.c_uint64, C.c_char_p, C.c_size_t]),
     "ribn_b200_engine_counters": (C.c_int, [_P, C.POINTER(EngineCountersC)]),
     "ribn_b200_engine_last_error": (C.c_size_t, [_P, C.c_char_p, C.c_size_t]),

@@ -17,6 +17,7 @@ namespace {
 struct Slot {
     uint64_t request = 0, sequence = 0;
     std::vector<uint32_t> prompt, stop, output;
+    std::vector<uint64_t> token_ns;   // when each output token was committed
     uint32_t max_output = 0;
     float temperature = 0.0f;
     uint32_t prefix = 0, generated = 0;
@@ -247,6 +248,7 @@ struct ribn_b200_engine {
                     how = RIBN_B200_FINISH_STOP;
                 } else {
                     s.output.push_back(token);
+                    s.token_ns.push_back(now);
                     if (s.first_token_ns == 0) s.first_token_ns = now;
                     s.last_token_ns = now;
                     if (s.generated == s.max_output) how = RIBN_B200_FINISH_LENGTH;
@@ -456,6 +458,18 @@ int ribn_b200_engine_output(ribn_b200_engine* engine, uint64_t request, uint32_t
     if (count != nullptr) *count = (uint32_t)out.size();
     if (tokens != nullptr && capacity > 0 && !out.empty()) {
         memcpy(tokens, out.data(), std::min<size_t>(capacity, out.size()) * sizeof(uint32_t));
+    }
+    return RIBN_B200_OK;
+}
+
+int ribn_b200_engine_token_times(ribn_b200_engine* engine, uint64_t request, uint64_t* stamps, uint32_t capacity, uint32_t* count) {
+    if (engine == nullptr) return RIBN_B200_ERROR;
+    const auto it = engine->slots.find(request);
+    if (it == engine->slots.end()) return engine->fail("unknown request %llu", (unsigned long long)request);
+    const std::vector<uint64_t>& ns = it->second.token_ns;
+    if (count != nullptr) *count = (uint32_t)ns.size();
+    if (stamps != nullptr && capacity > 0 && !ns.empty()) {
+        memcpy(stamps, ns.data(), std::min<size_t>(capacity, ns.size()) * sizeof(uint64_t));
     }
     return RIBN_B200_OK;
 }

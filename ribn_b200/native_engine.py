@@ -105,6 +105,19 @@ class NativeEngine:
     def steps(self) -> int:
         return int(self.counters().steps)
 
+    def token_times(self, request: int) -> np.ndarray:
+        """Commit times of the request's output tokens in seconds on the monotonic clock (``time.perf_counter``'s
+        clock on Linux)."""
+        count = C.c_uint32()
+        lib().ribn_b200_engine_token_times(self._h, request, None, 0, C.byref(count))
+        out = np.empty(max(count.value, 1), dtype=np.uint64)
+        lib().ribn_b200_engine_token_times(self._h, request, out.ctypes.data_as(C.c_void_p), out.size, C.byref(count))
+        return out[:count.value].astype(np.float64) * 1e-9
+
+    @property
+    def in_flight(self) -> bool:
+        return self.counters().in_flight_rows > 0
+
     def status(self, request: int) -> RequestStatus:
         st = RequestStatusC()
         if lib().ribn_b200_engine_status(self._h, request, C.byref(st)) != _lib.OK:

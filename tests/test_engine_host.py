@@ -387,3 +387,24 @@ def test_a_pool_that_can_never_serve_every_sequence_fails_the_newest_one(Engine)
     assert sorted([e.finished[a].finish, e.finished[b].finish]) == ["failed: KV arena exhausted"] * 2 or \
         "failed: KV arena exhausted" in (e.finished[a].finish, e.finished[b].finish)
     assert fake.free == 2 and e.idle()
+
+
+def test_native_engine_stamps_tokens_on_the_monotonic_clock(built_library):
+    """Token commit times come from the steady clock, the clock of time.perf_counter on Linux: the benchmark
+    subtracts one from the other for the time to first token."""
+    import time
+    from ribn_b200.native_engine import NativeEngine
+    c = Control()
+    adapter = TableAdapter(Fake(c))
+    e = NativeEngine(config=EngineConfig(max_active_requests=2), policy=SchedulePolicy(64, 16, 1, 8), table=adapter.table)
+    before = time.perf_counter()
+    rid = e.enqueue(TokenRequest(list(range(20)), 3))
+    e.run_until_idle()
+    after = time.perf_counter()
+    stamps = e.token_times(rid)
+    st = e.status(rid)
+    assert len(stamps) == 3 == len(st.output) and list(stamps) == sorted(stamps)
+    assert before <= st.enqueue_ns * 1e-9 <= stamps[0] <= stamps[-1] <= after
+    assert abs(stamps[0] - st.first_token_ns * 1e-9) < 1e-6 and abs(stamps[-1] - st.last_token_ns * 1e-9) < 1e-6
+    assert not e.in_flight and e.steps == 4
+    e.close()
