@@ -408,3 +408,36 @@ def test_native_engine_stamps_tokens_on_the_monotonic_clock(built_library):
     assert abs(stamps[0] - st.first_token_ns * 1e-9) < 1e-6 and abs(stamps[-1] - st.last_token_ns * 1e-9) < 1e-6
     assert not e.in_flight and e.steps == 4
     e.close()
+
+
+def test_native_engine_argument_and_queue_errors(built_library):
+    """Creation refuses an incomplete executor table and a policy beyond the executor's limits; a full queue
+    refuses the request without faulting; unknown requests are errors; a stop token ends a request before it
+    reaches the output."""
+    import ctypes as C
+    from ribn_b200 import _lib
+    from ribn_b200.native_engine import NativeEngine
+    c = Control()
+    adapter = TableAdapter(Fake(c))
+    broken = _lib.ExecutorTable()
+    C.memmove(C.byref(broken), C.byref(adapter.table), C.sizeof(broken))
+    broken.submit = _lib._SUBMIT_FN()      # a NULL entry
+    with pytest.raises(ValueError, match="incomplete"):
+        NativeEngine(config=EngineConfig(2), policy=SchedulePolicy(64, 16, 1, 8), table=broken)
+    with pytest.raises(ValueError, match="invalid engine configuration"):
+        NativeEngine(config=EngineConfig(2), policy=SchedulePolicy(64, 0, 1, 8), table=adapter.table)
+    e = NativeEngine(config=EngineConfig(max_active_requests=1, max_queued_requests=2), policy=SchedulePolicy(64, 16, 1, 8),
+                     table=adapter.table)
+    a = e.enqueue(TokenRequest([1, 2, 3], 5, stop_tokens=[103]))    # the fake samples 100 + the row's prefix: 100, then 103
+    b = e.enqueue(TokenRequest([4], 1))
+    with pytest.raises(RuntimeError, match="queue full"):
+        e.enqueue(TokenRequest([5], 1))
+    assert not e.faulted
+    with pytest.raises(ExecutionError, match="unknown request"):
+        e.status(99)
+    e.run_until_idle()
+    sa, sb = e.status(a), e.status(b)
+    assert sa.finish == "stop" and sa.output == [100] and sa.generated == 2
+    assert sb.finish == "length" and sb.output == [100]
+    assert c.released == [a, b] and e.counters().resource_epoch == 2
+    e.close()
