@@ -40,6 +40,44 @@ def test_python_flag_constants_mirror_the_header():
         assert int(value) & (int(value) - 1) == 0, "flags are single bits"
 
 
+C_CLIENT = r"""
+#include <stdio.h>
+#include <string.h>
+#include "ribn_b200.h"
+#include "ribn_b200_gemma.h"
+#include "ribn_b200_engine.h"
+int main(void) {
+    char err[256] = {0};
+    ribn_b200_engine* e = NULL;
+    ribn_b200_engine_config cfg = {2, 4};
+    ribn_b200_schedule_policy pol = {64, 16, 1, 8};
+    int rc = ribn_b200_engine_create(NULL, &cfg, &pol, &e, err, sizeof(err));
+    printf("%s|%d|%s", ribn_b200_build_info(), rc, err);
+    return rc == RIBN_B200_ERROR && strstr(err, "null") ? 0 : 1;
+}
+"""
+
+
+def test_headers_are_strict_c99_and_a_c_client_links(built_library, tmp_path):
+    """The boundary is a C ABI: the three headers compile as pedantic C99 with warnings as errors, and a C program
+    links against the library and calls into it (no device work)."""
+    import shutil
+    import subprocess
+    import ribn_b200
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no gcc")
+    src, exe = tmp_path / "client.c", tmp_path / "client"
+    src.write_text(C_CLIENT)
+    libdir = os.path.dirname(ribn_b200.library_path())
+    build = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", "-I", os.path.join(ROOT, "include"), str(src),
+                            "-o", str(exe), ribn_b200.library_path(), f"-Wl,-rpath,{libdir}"], capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0, run.stdout + run.stderr
+    assert "sm_100a" in run.stdout and "null argument" in run.stdout
+
+
 def test_product_package_never_imports_the_oracle():
     pkg = os.path.join(ROOT, "ribn_b200")
     for dirpath, _dirs, files in os.walk(pkg):
