@@ -441,3 +441,26 @@ def test_native_engine_argument_and_queue_errors(built_library):
     assert sb.finish == "length" and sb.output == [100]
     assert c.released == [a, b] and e.counters().resource_epoch == 2
     e.close()
+
+
+class GreedyFake(PagedFake):
+    """Answers Selected with a row whose granted budget exceeds what was offered."""
+
+    def prepare_rows(self, batch):
+        self.prepared = list(batch)
+        it = batch[0]
+        return [PreparedRow("ready", BatchItem(it.sequence, it.kind, it.prefix, it.token_budget + 1, it.output_budget))]
+
+
+def test_a_preparation_that_grants_more_than_offered_faults_the_engine(Engine):
+    """prepare_batch checks every Selected row against the offer (preparation.rs:40-86): a granted budget above the
+    offered one abandons the preparation and is a final fault."""
+    c = Control()
+    fake = GreedyFake(c, pages=8)
+    e = Engine(fake, EngineConfig(max_active_requests=2), SchedulePolicy(64, 16, 1, 8))
+    e.enqueue(TokenRequest(list(range(10)), 2))
+    with pytest.raises(ExecutionError, match="does not match"):
+        e.step()
+    assert e.faulted and fake.prepared is None and not c.batches
+    with pytest.raises(ExecutionError):
+        e.step()
