@@ -400,18 +400,31 @@ def run_ours(args):
     if B >= 3 and not EXTRA_FLAGS and not args.no_cache_leg and args.scheme == "q4_k_m":
         # the same batch once more on an executor that keeps the K-quant matrices as tensor-core operands
         # (RIBN_B200_FLAG_OPERAND_CACHE: 2 or 4 bytes of HBM per weight; same logits bit for bit)
-        ex = ribn_b200.QwenB200(model, context_tokens=args.context + 2 * total_steps + 20, max_sequences=B,
-                                max_batch_tokens=max(B, 16), device=local, flags=ribn_b200.FLAG_OPERAND_CACHE)
-        ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q4_K_M)
-        ex.finalize()
-        seed_sequences(ex, model, B, args.context, 2 * total_steps + 4, seed=1 + rank)
-        positions = {s + 1: args.context for s in range(B)}
-        _, devc, launchesc, _, spreadc = phase(list(range(1, B + 1)), 3)
-        out["batch64"]["operand_cache"] = {"value": world * B * args.steps / devc, "unit": "tok/s",
-                                           "ms_per_step": devc / args.steps * 1e3, "gpu_launches": launchesc,
-                                           "spread": spreadc,
-                                           "note": "K-quant matrices also kept as binary16 operand planes (Q4_K 2 B, Q6_K 4 B per weight)"}
-        ex.close()
+        # An extra: if the larger executor cannot be built on some rank (memory taken by someone else), every rank
+        # skips the leg together and the line says so.
+        ex, problem = None, ""
+        try:
+            ex = ribn_b200.QwenB200(model, context_tokens=args.context + 2 * total_steps + 20, max_sequences=B,
+                                    max_batch_tokens=max(B, 16), device=local, flags=ribn_b200.FLAG_OPERAND_CACHE)
+            ex.init_synthetic(0x5EED, ribn_b200.SCHEME_Q4_K_M)
+            ex.finalize()
+            seed_sequences(ex, model, B, args.context, 2 * total_steps + 4, seed=1 + rank)
+        except Exception as exc:   # noqa: BLE001
+            problem = str(exc) or type(exc).__name__
+        if all_max(dist, 1.0 if problem else 0.0, local) > 0.0:
+            out["batch64"]["operand_cache"] = {"unavailable": problem or "another rank could not build the executor"}
+        else:
+            positions = {s + 1: args.context for s in range(B)}
+            _, devc, launchesc, _, spreadc = phase(list(range(1, B + 1)), 3)
+            out["batch64"]["operand_cache"] = {"value": world * B * args.steps / devc, "unit": "tok/s",
+                                               "ms_per_step": devc / args.steps * 1e3, "gpu_launches": launchesc,
+                                               "spread": spreadc,
+                                               "note": "K-quant matrices also kept as binary16 operand planes (Q4_K 2 B, Q6_K 4 B per weight)"}
+        if ex is not None:
+            try:
+                ex.close()
+            except Exception:   # noqa: BLE001
+                pass
     if not args.no_serving:
         # p50 time to first token is part of the metric: a bounded serving leg below saturation
         srv = serving_job(args, rank, world, local, dist, n=args.serving_requests, rate=args.arrival_rate_default,
